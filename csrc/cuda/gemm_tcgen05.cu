@@ -1,0 +1,461 @@
+// bf16 GEMM on 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   D[M,N] = epilogue( A[M,K] · B[N,K]^T )      fp32 accumulation in tensor memory
+//
+// One persistent CTA per SM walks over 128 x BN output tiles.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor (2-D tiled, 128-byte swizzle, no cluster
+//               broadcast) fills a ring of shared-memory stages and signals "full" mbarriers
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16) and
+//               releases stages / publishes accumulators with tcgen05.commit
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), apply
+//               the fused epilogue, store bf16 / fp32 rows
+// Two accumulator buffers (2 x BN columns of tensor memory) let the epilogue of tile i
+// overlap the main loop of tile i+1.
+//
+// Operand layouts.  Each operand is given as a row-major matrix in global memory together
+// with a flag saying which of its two dims is contiguous:
+//   "K-major"  A stored [M,K] / B stored [N,K]   (contraction dim contiguous)
+//   "MN-major" A stored [K,M] / B stored [K,N]   (output dim contiguous)
+// so that Y = X·W^T (both K-major), dX = dY·W (B MN-major) and dW = dY^T·X (both MN-major)
+// all run without materialising a transpose.
+//
+// Every wait is bounded (see common.cuh); on expiry the CTA drains and frees its tensor
+// memory before returning, and the launcher's status word is set.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace recml {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+
+enum Epilogue : int {
+  kEpiLinear = 0,    // D = act(acc + bias)
+  kEpiCross = 1,     // V = acc + bias (optional store to out2); D = aux0 * V + aux1
+  kEpiMaskRelu = 2,  // D = acc * (aux0 > 0)              (ReLU backward fused in dgrad)
+  kEpiMulAdd = 3,    // D = acc * aux0 (+ aux1)           (DCN input-gradient paths)
+};
+
+struct Params {
+  int M, N, K;
+  void* d;            // bf16 or fp32 [M, ldd]
+  int ldd;
+  int out_f32;        // 1: D is fp32
+  int accumulate;     // 1: D += result (fp32 output only)
+  const float* bias;  // [N] or null
+  int relu;
+  int epi;
+  const __nv_bfloat16* aux0;  // [M, ldaux]
+  const __nv_bfloat16* aux1;  // [M, ldaux]
+  int ldaux;
+  __nv_bfloat16* out2;        // optional second output [M, ldd] (kEpiCross: V)
+  int* status;
+};
+
+// ---- mbarrier / TMA / tcgen05 wrappers -----------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  `abort_flag` lives in shared memory; once any role sets it every other wait
+// in the CTA gives up quickly, so the CTA can drain and free its tensor memory.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kDefaultWaitNs) {
+      *abort_flag = 1;
+      report(status, kMbarTimeout, where);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((addr >> 4) & 0x3FFF) |
+         (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kSmem = kStages * (kStageA + kStageB) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + C::kStages * C::kStageA;
+  const uint32_t bars = smem_b + C::kStages * C::kStageB;
+  // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
+  auto tempty_bar = [&](int s) { return bars + 8u * (2 * C::kStages + 2 + s); };
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abortp; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % C::kStages;
+          if (!mbar_wait(empty_bar(s), ((it / C::kStages) & 1) ^ 1, abortp, p.status, 10)) break;
+          mbar_expect_tx(full_bar(s), C::kStageA + C::kStageB);
+          const uint32_t sa = smem_a + s * C::kStageA, sb = smem_b + s * C::kStageB;
+          const int k0 = kb * BK;
+          if (A_MN) {
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, m0 + 64 * j, k0, full_bar(s));
+          } else {
+            tma_load_2d(sa, &map_a, k0, m0, full_bar(s));
+          }
+          if (B_MN) {
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, n0 + 64 * j, k0, full_bar(s));
+          } else {
+            tma_load_2d(sb, &map_b, k0, n0, full_bar(s));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, majors, N>>3, M>>4
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                             ((B_MN ? 1u : 0u) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>(BM >> 4) << 24);
+      // K-major: rows of 128 B, 8-row groups 1024 B apart; advance 32 B per K=16.
+      // MN-major: 64-element atoms, 8-k groups 1024 B apart, next 64-wide atom 8192 B on;
+      //           advance 2048 B per K=16.
+      const uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+      const uint32_t a_step = A_MN ? 2048u : 32u, b_step = B_MN ? 2048u : 32u;
+      uint32_t it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abortp; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        if (!mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1, abortp, p.status, 20)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % C::kStages;
+          if (!mbar_wait(full_bar(s), (it / C::kStages) & 1, abortp, p.status, 21)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_a + s * C::kStageA, sb = smem_b + s * C::kStageB;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_desc(sa + k * a_step, a_lbo, 1024);
+            const uint64_t bdesc = make_desc(sb + k * b_step, b_lbo, 1024);
+            tc_mma_bf16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      const int acc = t & 1;
+      if (!mbar_wait(tfull_bar(acc), (t >> 1) & 1, abortp, p.status, 30)) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        if (!row_ok) continue;
+        const size_t off = static_cast<size_t>(row) * p.ldd + col0;
+        const size_t aoff = static_cast<size_t>(row) * p.ldaux + col0;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {  // 4 groups of 8 columns
+          if (col0 + v * 8 >= p.N) break;
+          float x[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]);
+          if (p.bias != nullptr) {
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8 + 4));
+            x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+            x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+          }
+          if (p.epi == kEpiLinear) {
+            if (p.relu) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+            }
+          } else {
+            const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(p.aux0 + aoff + v * 8));
+            const uint32_t a0w[4] = {a0.x, a0.y, a0.z, a0.w};
+            if (p.epi == kEpiCross) {
+              if (p.out2 != nullptr) {
+                uint4 o;
+                o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+                o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+                *reinterpret_cast<uint4*>(p.out2 + off + v * 8) = o;
+              }
+              const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
+              const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                x[2 * j] = bf16_lo(a0w[j]) * x[2 * j] + bf16_lo(a1w[j]);
+                x[2 * j + 1] = bf16_hi(a0w[j]) * x[2 * j + 1] + bf16_hi(a1w[j]);
+              }
+            } else if (p.epi == kEpiMaskRelu) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                x[2 * j] = bf16_lo(a0w[j]) > 0.f ? x[2 * j] : 0.f;
+                x[2 * j + 1] = bf16_hi(a0w[j]) > 0.f ? x[2 * j + 1] : 0.f;
+              }
+            } else {  // kEpiMulAdd
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                x[2 * j] *= bf16_lo(a0w[j]);
+                x[2 * j + 1] *= bf16_hi(a0w[j]);
+              }
+              if (p.aux1 != nullptr) {
+                const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
+                const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  x[2 * j] += bf16_lo(a1w[j]);
+                  x[2 * j + 1] += bf16_hi(a1w[j]);
+                }
+              }
+            }
+          }
+          if (p.out_f32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.d) + off + v * 8);
+            float4 o0 = make_float4(x[0], x[1], x[2], x[3]), o1 = make_float4(x[4], x[5], x[6], x[7]);
+            if (p.accumulate) {
+              const float4 c0 = dst[0], c1 = dst[1];
+              o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
+              o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
+            }
+            dst[0] = o0; dst[1] = o1;
+          } else {
+            uint4 o;
+            o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+            o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + off + v * 8) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  if (*abortp) {
+    // give copies / MMAs already in flight time to land before shared and tensor memory go away
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major matrix [rows, cols] (leading dim ld), box = [box_rows, 64 cols], 128B swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const void* a, int lda, const void* b, int ldb, const Params& p, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  int rc;
+  // K-major operand: matrix [MN, K], box [BM|BN rows, 64 k]; MN-major: matrix [K, MN], box [64 k rows, 64 mn]
+  rc = A_MN ? make_map(&ma, a, p.K, p.M, lda, 64) : make_map(&ma, a, p.M, p.K, lda, BM);
+  if (rc) return rc;
+  rc = B_MN ? make_map(&mb, b, p.K, p.N, ldb, 64) : make_map(&mb, b, p.N, p.K, ldb, BN);
+  if (rc) return rc;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmem) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace gemm
+}  // namespace recml
+
+// D[M,N] = epi(A·B^T).  a_mn / b_mn: 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows].
+// Leading dims are in elements and must be multiples of 8 (16-byte TMA strides); N must be a multiple of 8.
+// Returns 0 on a successful launch, negative on bad arguments / set-up failure.
+extern "C" int recml_gemm_bf16(const void* a, int lda, int a_mn, const void* b, int ldb, int b_mn, void* d,
+                               int ldd, int out_f32, int accumulate, int M, int N, int K, const float* bias,
+                               int relu, int epi, const void* aux0, const void* aux1, int ldaux, void* out2,
+                               int* status, cudaStream_t stream) {
+  using namespace recml::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (N % 8) || (ldd % 4) || (!out_f32 && (ldd % 8))) return -10;
+  if (epi != kEpiLinear && (aux0 == nullptr || (ldaux % 8))) return -11;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return -12;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.d = d; p.ldd = ldd; p.out_f32 = out_f32; p.accumulate = accumulate;
+  p.bias = bias; p.relu = relu; p.epi = epi;
+  p.aux0 = static_cast<const __nv_bfloat16*>(aux0); p.aux1 = static_cast<const __nv_bfloat16*>(aux1);
+  p.ldaux = ldaux; p.out2 = static_cast<__nv_bfloat16*>(out2); p.status = status;
+  const bool wide = N > 128;
+  if (!a_mn && !b_mn) return wide ? launch<256, false, false>(a, lda, b, ldb, p, stream)
+                                  : launch<128, false, false>(a, lda, b, ldb, p, stream);
+  if (!a_mn && b_mn) return wide ? launch<256, false, true>(a, lda, b, ldb, p, stream)
+                                 : launch<128, false, true>(a, lda, b, ldb, p, stream);
+  if (a_mn && b_mn) return wide ? launch<256, true, true>(a, lda, b, ldb, p, stream)
+                                : launch<128, true, true>(a, lda, b, ldb, p, stream);
+  return wide ? launch<256, true, false>(a, lda, b, ldb, p, stream)
+              : launch<128, true, false>(a, lda, b, ldb, p, stream);
+}

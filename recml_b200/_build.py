@@ -1,0 +1,122 @@
+"""In-tree native build: CUDA kernels (sm_100a only) and host C++ into two shared objects.
+
+  recml_b200/lib/librecml_cuda.so   every file under csrc/cuda/*.cu
+  recml_b200/lib/librecml_host.so   every file under csrc/host, csrc/data, csrc/ckpt (*.cpp)
+
+Objects are rebuilt only when a source (or a header next to it) changed, judged by a
+content hash stored beside the library, so a tree whose libraries were built elsewhere
+loads them without invoking a compiler.  Kernels export plain `extern "C"` launchers that
+take raw pointers and a stream; Python binds them with ctypes (`recml_b200.ops._lib`).
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import glob
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(ROOT, "csrc")
+LIB_DIR = os.path.join(ROOT, "recml_b200", "lib")
+OBJ_DIR = os.path.join(LIB_DIR, "obj")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-pthread", "-Wall"]
+
+
+def _nvcc() -> str:
+  return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def _digest(paths: list[str], extra: str = "") -> str:
+  h = hashlib.sha256(extra.encode())
+  for p in sorted(paths):
+    h.update(os.path.relpath(p, ROOT).encode())
+    with open(p, "rb") as f:
+      h.update(f.read())
+  return h.hexdigest()
+
+
+def _sources():
+  cu = sorted(glob.glob(os.path.join(CSRC, "cuda", "*.cu")))
+  cu_hdr = sorted(glob.glob(os.path.join(CSRC, "cuda", "*.cuh")) + glob.glob(os.path.join(CSRC, "cuda", "*.h")))
+  cpp, cpp_hdr = [], []
+  for d in ("host", "data", "ckpt"):
+    cpp += sorted(glob.glob(os.path.join(CSRC, d, "*.cpp")))
+    cpp_hdr += sorted(glob.glob(os.path.join(CSRC, d, "*.h")))
+  return cu, cu_hdr, cpp, cpp_hdr
+
+
+def cuda_lib_path() -> str:
+  return os.path.join(LIB_DIR, "librecml_cuda.so")
+
+
+def host_lib_path() -> str:
+  return os.path.join(LIB_DIR, "librecml_host.so")
+
+
+def _run(cmd: list[str]) -> None:
+  r = subprocess.run(cmd, capture_output=True, text=True)
+  if r.returncode != 0:
+    raise RuntimeError(f"command failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+
+
+def _compile_all(srcs, hdrs, compiler_cmd, tag) -> tuple[list[str], bool]:
+  os.makedirs(OBJ_DIR, exist_ok=True)
+  hdr_digest = _digest(hdrs, tag)
+  jobs, objs = [], []
+  for src in srcs:
+    obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
+    stamp = obj + ".sha"
+    want = _digest([src], hdr_digest)
+    objs.append(obj)
+    if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == want:
+      continue
+    jobs.append((src, obj, stamp, want))
+  def one(job):
+    src, obj, stamp, want = job
+    _run(compiler_cmd(src, obj))
+    with open(stamp, "w") as f:
+      f.write(want)
+  with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+    list(ex.map(one, jobs))
+  return objs, bool(jobs)
+
+
+def build(verbose: bool = False, force: bool = False) -> dict[str, str]:
+  """Builds whatever is out of date and returns the library paths."""
+  os.makedirs(LIB_DIR, exist_ok=True)
+  cu, cu_hdr, cpp, cpp_hdr = _sources()
+  out = {}
+  for name, srcs, hdrs, lib, comp, link in (
+      ("cuda", cu, cu_hdr, cuda_lib_path(),
+       lambda s, o: [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(CSRC, "cuda"), "-c", s, "-o", o],
+       lambda objs, lib: [_nvcc(), "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]),
+      ("host", cpp, cpp_hdr, host_lib_path(),
+       lambda s, o: ["g++", *CXX_FLAGS, "-I", CSRC, "-c", s, "-o", o],
+       lambda objs, lib: ["g++", "-shared", "-pthread", "-o", lib, *objs, "-lz", "-ldl"])):
+    if not srcs:
+      continue
+    want = _digest(srcs + hdrs, name)
+    stamp = lib + ".sha"
+    if not force and os.path.exists(lib) and os.path.exists(stamp) and open(stamp).read() == want:
+      out[name] = lib
+      continue
+    if name == "cuda" and not os.path.exists(_nvcc()):
+      raise RuntimeError("nvcc not found and librecml_cuda.so is missing or stale")
+    if verbose:
+      print(f"[recml_b200] building {os.path.basename(lib)} ...", file=sys.stderr)
+    objs, _ = _compile_all(srcs, hdrs, comp, name)
+    _run(link(objs, lib))
+    with open(stamp, "w") as f:
+      f.write(want)
+    out[name] = lib
+  return out
+
+
+if __name__ == "__main__":
+  print(build(verbose=True, force="--force" in sys.argv))

@@ -1,0 +1,329 @@
+"""Checkpoint manager with the directory layout the reference's trainers produce.
+
+Reference behaviour being reproduced (`recml/core/training/jax_trainer.py:461-552`,
+`recml/core/utils/keras_utils.py:37-137`): checkpoints live in
+`<model_dir>/checkpoints/<step>/` holding one sub-directory per item ("state" for the
+trainer's composite save, "default" for single-item saves) plus a "metrics" JSON item
+and `_CHECKPOINT_METADATA`; saves are asynchronous, a `should_save_fn(step, last)`
+decides which steps are kept, and at most `max_to_keep` steps stay on disk.
+
+A checkpoint is staged in `<step>.orbax-checkpoint-tmp-<n>` and renamed to `<step>`
+once every rank finished writing, so a reader never sees a partial step directory;
+`commit_success.txt` is written last inside it as the completion marker.
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import threading
+import time
+from typing import Any, Callable, Iterator, Mapping
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from recml_b200.ckpt import tree as tree_lib
+from recml_b200.ckpt import zarr_io
+
+CHECKPOINT_METADATA = "_CHECKPOINT_METADATA"
+TREE_METADATA = "_METADATA"
+SHARDING_FILE = "_sharding"
+COMMIT_FILE = "commit_success.txt"
+TMP_MARK = ".orbax-checkpoint-tmp-"
+
+
+class ShardedLeaf:
+  """A tensor that is one block of a larger global array.
+
+  `global_shape` is the full array, `grid_index` the block coordinate of this rank's
+  `local` block and `chunk_shape` the block size; the block grid becomes the zarr
+  chunk grid.  `write` is False on ranks that hold a replica which another rank saves.
+  """
+
+  def __init__(self, local: torch.Tensor, global_shape, grid_index, chunk_shape=None, write=True):
+    self.local = local
+    self.global_shape = tuple(int(s) for s in global_shape)
+    self.grid_index = tuple(int(i) for i in grid_index)
+    self.chunk_shape = tuple(int(s) for s in (chunk_shape or local.shape))
+    self.write = write
+
+
+def _rank_world(group=None) -> tuple[int, int]:
+  if dist.is_available() and dist.is_initialized():
+    return dist.get_rank(group), dist.get_world_size(group)
+  return 0, 1
+
+
+def _barrier(group=None):
+  if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+    dist.barrier(group=group)
+
+
+def is_step_dir(name: str) -> bool:
+  return name.isdigit()
+
+
+def all_steps(directory: str) -> list[int]:
+  if not os.path.isdir(directory):
+    return []
+  return sorted(int(n) for n in os.listdir(directory)
+                if is_step_dir(n) and os.path.isdir(os.path.join(directory, n)))
+
+
+def latest_step(directory: str) -> int | None:
+  steps = all_steps(directory)
+  return steps[-1] if steps else None
+
+
+class CheckpointManager:
+  def __init__(self, directory: str, *, max_to_keep: int | None = 5,
+               should_save_fn: Callable[[int, int | None], bool] | None = None,
+               save_interval_steps: int = 1, async_save: bool = True,
+               item_name: str = "state", compressor: str | None = None, group=None):
+    self.directory = os.fspath(directory)
+    self.max_to_keep = max_to_keep
+    self.should_save_fn = should_save_fn
+    self.save_interval_steps = save_interval_steps
+    self.async_save = async_save
+    self.item_name = item_name
+    self.compressor = compressor
+    self.group = group
+    self._thread: threading.Thread | None = None
+    self._error: BaseException | None = None
+    self._last_saved: int | None = None
+    self._seq = 0
+    rank, _ = _rank_world(group)
+    if rank == 0:
+      os.makedirs(self.directory, exist_ok=True)
+    _barrier(group)
+
+  # -- queries ----------------------------------------------------------------------
+  def all_steps(self) -> list[int]:
+    return all_steps(self.directory)
+
+  def latest_step(self) -> int | None:
+    return latest_step(self.directory)
+
+  def should_save(self, step: int) -> bool:
+    if self.should_save_fn is not None:
+      return bool(self.should_save_fn(step, self._last_saved))
+    return step % self.save_interval_steps == 0
+
+  # -- save ---------------------------------------------------------------------------
+  def save(self, step: int, state: Mapping[str, Any], *, metrics: Mapping[str, Any] | None = None,
+           force: bool = False) -> bool:
+    if not force and not self.should_save(step):
+      return False
+    self.wait_until_finished()
+    rank, world = _rank_world(self.group)
+    # Snapshot to host NOW (the step may mutate device tensors right after we return).
+    staged: list[tuple[tuple[str, ...], Any]] = []
+    for path, leaf in tree_lib.flatten(state):
+      if isinstance(leaf, ShardedLeaf):
+        arr, dt = zarr_io.to_host_numpy(leaf.local) if leaf.write else (None, None)
+        staged.append((path, ("sharded", leaf, arr, dt,
+                              zarr_io.to_host_numpy(leaf.local[:0])[1])))
+      elif rank == 0:
+        staged.append((path, ("full",) + zarr_io.to_host_numpy(leaf)))
+      else:
+        staged.append((path, ("skip",)))
+    kinds = tree_lib.key_types(state)
+    self._seq += 1
+    tmp = os.path.join(self.directory, f"{step}{TMP_MARK}{self._seq}")
+    final = os.path.join(self.directory, str(step))
+    if rank == 0:
+      if os.path.exists(final):
+        shutil.rmtree(final)
+      os.makedirs(os.path.join(tmp, self.item_name), exist_ok=True)
+    _barrier(self.group)
+
+    def work():
+      try:
+        self._write(tmp, staged, kinds, metrics, rank, world)
+      except BaseException as e:  # surfaced by wait_until_finished
+        self._error = e
+
+    if self.async_save and world == 1:
+      self._thread = threading.Thread(target=lambda: (work(), self._finalize(step, tmp, final)),
+                                      name="recml-ckpt", daemon=True)
+      self._thread.start()
+    else:
+      work()
+      _barrier(self.group)
+      if rank == 0:
+        self._finalize(step, tmp, final)
+      _barrier(self.group)
+      if self._error:
+        err, self._error = self._error, None
+        raise err
+    self._last_saved = step
+    return True
+
+  def _write(self, tmp, staged, kinds, metrics, rank, world):
+    item = os.path.join(tmp, self.item_name)
+    meta_tree, sharding = {}, {}
+    for path, rec in staged:
+      key = ".".join(path)
+      leaf_dir = os.path.join(item, key)
+      if rec[0] == "full":
+        _, arr, dt = rec
+        zarr_io.write_zarray(leaf_dir, arr.shape, arr.shape, dt, self.compressor)
+        zarr_io.write_chunk(leaf_dir, [0] * arr.ndim, arr, self.compressor)
+        meta_tree[key] = {"key_path": list(path), "shape": list(arr.shape), "dtype": dt,
+                          "value_type": "array"}
+        sharding[key] = {"sharding_type": "replicated"}
+      elif rec[0] == "sharded":
+        _, leaf, arr, dt, dt_all = rec
+        if rank == 0:
+          zarr_io.write_zarray(leaf_dir, leaf.global_shape, leaf.chunk_shape, dt_all,
+                               self.compressor)
+        else:
+          os.makedirs(leaf_dir, exist_ok=True)
+        if arr is not None:
+          if tuple(arr.shape) != leaf.chunk_shape:  # edge block: pad to the chunk shape
+            full = np.zeros(leaf.chunk_shape, dtype=arr.dtype)
+            full[tuple(slice(0, s) for s in arr.shape)] = arr
+            arr = full
+          zarr_io.write_chunk(leaf_dir, leaf.grid_index, arr, self.compressor)
+        meta_tree[key] = {"key_path": list(path), "shape": list(leaf.global_shape),
+                          "dtype": dt_all, "value_type": "array"}
+        sharding[key] = {"sharding_type": "block", "chunk_shape": list(leaf.chunk_shape)}
+    if rank == 0:
+      with open(os.path.join(item, TREE_METADATA), "w") as f:
+        json.dump({"tree_metadata": meta_tree,
+                   "containers": {".".join(k): v for k, v in kinds.items()},
+                   "use_zarr3": False, "use_ocdbt": False}, f)
+      with open(os.path.join(item, SHARDING_FILE), "w") as f:
+        json.dump(sharding, f)
+      if metrics is not None:
+        os.makedirs(os.path.join(tmp, "metrics"), exist_ok=True)
+        with open(os.path.join(tmp, "metrics", "metrics"), "w") as f:
+          json.dump(_jsonable(metrics), f)
+      with open(os.path.join(tmp, CHECKPOINT_METADATA), "w") as f:
+        json.dump({"item_handlers": {self.item_name: "recml_b200.ckpt.PyTreeZarr",
+                                     **({"metrics": "json"} if metrics is not None else {})},
+                   "metrics": _jsonable(metrics or {}),
+                   "init_timestamp_nsecs": time.time_ns(),
+                   "commit_timestamp_nsecs": time.time_ns()}, f)
+
+  def _finalize(self, step, tmp, final):
+    if self._error:
+      return
+    with open(os.path.join(tmp, COMMIT_FILE), "w") as f:
+      f.write("Checkpoint commit was successful.")
+    os.replace(tmp, final)
+    self._gc()
+
+  def _gc(self):
+    if self.max_to_keep is None:
+      return
+    steps = self.all_steps()
+    for s in steps[:max(0, len(steps) - self.max_to_keep)]:
+      shutil.rmtree(os.path.join(self.directory, str(s)), ignore_errors=True)
+
+  def wait_until_finished(self) -> None:
+    if self._thread is not None:
+      self._thread.join()
+      self._thread = None
+    if self._error:
+      err, self._error = self._error, None
+      raise err
+
+  def close(self) -> None:
+    self.wait_until_finished()
+
+  # -- restore ----------------------------------------------------------------------
+  def restore(self, step: int | None = None, target: Mapping[str, Any] | None = None,
+              item_name: str | None = None) -> Any:
+    """Reads a step.  Without `target` returns the stored tree of host tensors.  With a
+    `target` tree (same structure) only those leaves are read; a `ShardedLeaf` target
+    reads just its own block of the global array, so a checkpoint written by W ranks
+    restores on any other world size."""
+    self.wait_until_finished()
+    if step is None:
+      step = self.latest_step()
+      if step is None:
+        raise FileNotFoundError(f"No checkpoints under {self.directory}")
+    return restore_tree(os.path.join(self.directory, str(step), item_name or self.item_name), target)
+
+  def metrics(self, step: int) -> Any:
+    with open(os.path.join(self.directory, str(step), "metrics", "metrics")) as f:
+      return json.load(f)
+
+
+def restore_tree(item: str, target: Mapping[str, Any] | None = None) -> Any:
+  if not os.path.exists(os.path.join(item, TREE_METADATA)):
+    raise FileNotFoundError(f"{item} is not a complete checkpoint item")
+  with open(os.path.join(item, TREE_METADATA)) as f:
+    meta = json.load(f)
+  if target is None:
+    leaves = {tuple(m["key_path"]): zarr_io.read_region(os.path.join(item, key))
+              for key, m in meta["tree_metadata"].items()}
+    kinds = {tuple(k.split(".")) if k else (): v for k, v in meta.get("containers", {}).items()}
+    return tree_lib.restore_containers(tree_lib.unflatten(leaves), kinds)
+  out = {}
+  for path, leaf in tree_lib.flatten(target):
+    key = ".".join(path)
+    if key not in meta["tree_metadata"]:
+      raise KeyError(f"Checkpoint has no leaf {key!r}")
+    leaf_dir = os.path.join(item, key)
+    if isinstance(leaf, ShardedLeaf):
+      start = [i * c for i, c in zip(leaf.grid_index, leaf.chunk_shape)]
+      stop = [min(s + c, g) for s, c, g in zip(start, leaf.chunk_shape, leaf.global_shape)]
+      out[path] = zarr_io.read_region(leaf_dir, start, stop)
+    else:
+      out[path] = zarr_io.read_region(leaf_dir)
+  return tree_lib.restore_containers(tree_lib.unflatten(out), tree_lib.key_types(target))
+
+
+def _jsonable(x: Any) -> Any:
+  if isinstance(x, Mapping):
+    return {str(k): _jsonable(v) for k, v in x.items()}
+  if isinstance(x, (list, tuple)):
+    return [_jsonable(v) for v in x]
+  if isinstance(x, torch.Tensor):
+    x = x.detach().cpu().numpy()
+  if isinstance(x, np.ndarray):
+    return x.tolist()
+  if isinstance(x, (np.floating, np.integer)):
+    return x.item()
+  return x
+
+
+def checkpoints_iterator(directory: str, *, timeout: float | None = None,
+                         timeout_fn: Callable[[], bool] | None = None,
+                         min_interval_secs: float = 0.0,
+                         poll_secs: float = 0.5) -> Iterator[int]:
+  """Yields each new complete step as it appears.  After `timeout` seconds without a
+  new step, `timeout_fn()` is asked: True ends the iteration, False keeps waiting
+  (the reference's `ocp.checkpoint_utils.checkpoints_iterator`, used by continuous
+  evaluation `jax_trainer.py:871-875`)."""
+  last: int | None = None
+  while True:
+    deadline = None if timeout is None else time.time() + timeout
+    found = None
+    while True:
+      steps = [s for s in all_steps(directory) if last is None or s > last]
+      if steps:
+        found = steps[-1] if last is None and False else steps[0]
+        break
+      if deadline is not None and time.time() >= deadline:
+        break
+      time.sleep(poll_secs)
+    if found is None:
+      if timeout_fn is None or timeout_fn():
+        # one last look so a step committed right before the marker is not lost
+        steps = [s for s in all_steps(directory) if last is None or s > last]
+        if not steps:
+          return
+        found = steps[0]
+      else:
+        continue
+    last = found
+    start = time.time()
+    yield found
+    rest = min_interval_secs - (time.time() - start)
+    if rest > 0:
+      time.sleep(rest)

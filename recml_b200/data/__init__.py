@@ -1,0 +1,2 @@
+"""Data: iterator protocol, synthetic generators, TFRecord input pipeline."""
+from recml_b200.data.iterator import ArraySpec, IterableIterator, Iterator, TFDatasetIterator

@@ -1,0 +1,82 @@
+"""ctypes bindings to the in-tree native libraries.
+
+`cuda()` returns `librecml_cuda.so`; it raises if the library is missing or stale and
+cannot be rebuilt, so a GPU run never silently falls back to library kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import os
+from typing import Any
+
+import torch
+
+from recml_b200 import _build
+
+
+class NativeError(RuntimeError):
+  pass
+
+
+@functools.lru_cache(maxsize=None)
+def cuda() -> ctypes.CDLL:
+  libs = _build.build()
+  if "cuda" not in libs:
+    raise NativeError("librecml_cuda.so could not be built (no CUDA sources / nvcc).")
+  return ctypes.CDLL(libs["cuda"])
+
+
+@functools.lru_cache(maxsize=None)
+def host() -> ctypes.CDLL:
+  libs = _build.build()
+  if "host" not in libs:
+    raise NativeError("librecml_host.so could not be built.")
+  return ctypes.CDLL(libs["host"])
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+  return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+  return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_status: dict[int, torch.Tensor] = {}
+_status_host: dict[int, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device | None = None) -> torch.Tensor:
+  """Per-device int32[4] word that kernels write an error code into (0 = ok)."""
+  idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+  if idx not in _status:
+    _status[idx] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+  return _status[idx]
+
+
+STATUS_NAMES = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument",
+                4: "buffer capacity exceeded"}
+
+
+class DeviceStatusError(RuntimeError):
+  """A kernel reported a bounded-wait timeout or capacity error."""
+
+
+class PeerTimeoutError(DeviceStatusError):
+  pass
+
+
+def check_status(device: torch.device | None = None, sync: bool = True) -> None:
+  """Reads the status word (synchronising) and raises if a kernel reported an error."""
+  buf = status_buffer(device)
+  vals = buf.cpu().tolist() if sync else buf.tolist()
+  if vals[0] != 0:
+    buf.zero_()
+    cls = PeerTimeoutError if vals[0] == 2 else DeviceStatusError
+    raise cls(f"device status {vals[0]} ({STATUS_NAMES.get(vals[0], '?')}), detail {vals[1]}")
+
+
+def check_rc(rc: int, what: str) -> None:
+  if rc != 0:
+    raise NativeError(f"{what} failed with code {rc}")
