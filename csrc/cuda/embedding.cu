@@ -1,0 +1,737 @@
+// Sharded-embedding kernels for sm_100a: the lookup / pooling forward that writes its result
+// straight into the destination rank's buffer over NVLink (the all-to-all IS the store), the
+// activation-gradient push, and the sort-based dedup + row-optimizer backward.
+//
+// Data flow per step on rank `me` of W ranks (B = per-rank batch):
+//   ids      every rank pushes its jagged ids to all peers (emb_push_ids)             flag chan 0
+//   forward  for every (feature it owns a part of, source rank s, sample b) rank `me` gathers the
+//            rows it owns, pools them in fp32 and stores the bf16 vector into rank s's pooled
+//            buffer with plain peer stores (emb_fwd); in training it also appends
+//            (row, gradient-vector index) to an occurrence list                         flag chan 1
+//   combine  rank s sums the per-source slots of row-sharded features and writes the dense
+//            concat input (emb_combine)
+//   backward rank s pushes each feature's activation gradient to the rank(s) owning that
+//            feature (emb_push_grads)                                                   flag chan 2
+//            owners radix-sort the occurrence list by row, reduce each run of equal rows in
+//            fp32 and apply the row optimizer in the same kernel (emb_bwd_update/finalize).
+// Peer flags are monotonically increasing sequence numbers; all waits are bounded.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "common.cuh"
+
+namespace recml {
+namespace emb {
+
+constexpr int kMaxWorld = 8;
+enum Kind : int { kTableWise = 0, kRowWise = 1, kColumnWise = 2 };
+enum Combiner : int { kSum = 0, kMean = 1, kSqrtN = 2 };
+enum Opt : int { kSGD = 0, kAdagrad = 1, kRowAdagrad = 2, kAdam = 3, kRowAdam = 4, kAdagradMomentum = 5,
+                 kFTRL = 6, kLaProp = 7 };
+
+struct FeatDesc {      // one sharded feature as seen by the rank running the kernel
+  int feat_index;      // position of the feature in the jagged batch (offset rows f*B .. f*B+B)
+  int kind;
+  int owner;           // table-wise: owning rank
+  int rot;             // row-wise: shard rotation
+  int row_base;        // first row of the table inside the stack buffer
+  int combiner;
+  int dim;             // full embedding dim D of the feature
+  int col_lo;          // column-wise: first column held by this rank
+  long long slot_off;  // element offset of the feature's block in a destination pooled buffer
+  long long grad_off;  // element offset of the feature's block in THIS rank's gradient buffer
+  int seq_len;         // >0: sequence feature (no pooling), positions beyond seq_len dropped
+  int pad;
+};
+
+struct IdPtrs {        // jagged ids of every source rank, in this rank's memory
+  const int* values[kMaxWorld];
+  const int* offsets[kMaxWorld];
+  const float* weights[kMaxWorld];
+};
+struct PeerBf16 { __nv_bfloat16* p[kMaxWorld]; };
+struct PeerFlags { unsigned long long* p[kMaxWorld]; };
+
+// ---- small vector helpers: each lane owns VPL consecutive elements -------------------------------
+template <int VPL> struct Vec { float v[VPL]; };
+
+template <int VPL>
+__device__ __forceinline__ Vec<VPL> load_f32(const float* p) {
+  Vec<VPL> r;
+  if constexpr (VPL == 1) { r.v[0] = __ldg(p); }
+  else if constexpr (VPL == 2) { float2 t = __ldg(reinterpret_cast<const float2*>(p)); r.v[0] = t.x; r.v[1] = t.y; }
+  else {
+#pragma unroll
+    for (int i = 0; i < VPL / 4; ++i) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(p) + i);
+      r.v[4 * i] = t.x; r.v[4 * i + 1] = t.y; r.v[4 * i + 2] = t.z; r.v[4 * i + 3] = t.w;
+    }
+  }
+  return r;
+}
+template <int VPL>
+__device__ __forceinline__ Vec<VPL> load_f32_rw(const float* p) {  // no read-only path (data is rewritten)
+  Vec<VPL> r;
+  if constexpr (VPL == 1) { r.v[0] = *p; }
+  else if constexpr (VPL == 2) { float2 t = *reinterpret_cast<const float2*>(p); r.v[0] = t.x; r.v[1] = t.y; }
+  else {
+#pragma unroll
+    for (int i = 0; i < VPL / 4; ++i) {
+      float4 t = reinterpret_cast<const float4*>(p)[i];
+      r.v[4 * i] = t.x; r.v[4 * i + 1] = t.y; r.v[4 * i + 2] = t.z; r.v[4 * i + 3] = t.w;
+    }
+  }
+  return r;
+}
+template <int VPL>
+__device__ __forceinline__ void store_f32(float* p, const Vec<VPL>& r) {
+  if constexpr (VPL == 1) { *p = r.v[0]; }
+  else if constexpr (VPL == 2) { *reinterpret_cast<float2*>(p) = make_float2(r.v[0], r.v[1]); }
+  else {
+#pragma unroll
+    for (int i = 0; i < VPL / 4; ++i)
+      reinterpret_cast<float4*>(p)[i] = make_float4(r.v[4 * i], r.v[4 * i + 1], r.v[4 * i + 2], r.v[4 * i + 3]);
+  }
+}
+template <int VPL>
+__device__ __forceinline__ Vec<VPL> load_bf16(const __nv_bfloat16* p) {
+  Vec<VPL> r;
+  if constexpr (VPL == 1) { r.v[0] = __bfloat162float(*p); }
+  else if constexpr (VPL == 2) { uint32_t t = *reinterpret_cast<const uint32_t*>(p); r.v[0] = bf16_lo(t); r.v[1] = bf16_hi(t); }
+  else if constexpr (VPL == 4) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    r.v[0] = bf16_lo(t.x); r.v[1] = bf16_hi(t.x); r.v[2] = bf16_lo(t.y); r.v[3] = bf16_hi(t.y);
+  } else {
+    uint4 t = *reinterpret_cast<const uint4*>(p);
+    r.v[0] = bf16_lo(t.x); r.v[1] = bf16_hi(t.x); r.v[2] = bf16_lo(t.y); r.v[3] = bf16_hi(t.y);
+    r.v[4] = bf16_lo(t.z); r.v[5] = bf16_hi(t.z); r.v[6] = bf16_lo(t.w); r.v[7] = bf16_hi(t.w);
+  }
+  return r;
+}
+template <int VPL>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const Vec<VPL>& r) {
+  if constexpr (VPL == 1) { *p = __float2bfloat16(r.v[0]); }
+  else if constexpr (VPL == 2) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(r.v[0], r.v[1]); }
+  else if constexpr (VPL == 4) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(r.v[0], r.v[1]), pack_bf16(r.v[2], r.v[3]));
+  } else {
+    *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(r.v[0], r.v[1]), pack_bf16(r.v[2], r.v[3]),
+                                              pack_bf16(r.v[4], r.v[5]), pack_bf16(r.v[6], r.v[7]));
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// Raises flag[chan][me] = seq on every rank once ALL blocks of the grid have finished their stores.
+__device__ __forceinline__ void grid_done_then_signal(unsigned int* done_counter, const PeerFlags& flags,
+                                                      int W, unsigned long long seq) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < W; ++r) st_release_sys(flags.p[r], seq);
+    }
+  }
+}
+
+// Every block waits until flags[src] >= seq for all sources (threads 0..W-1 poll one flag each).
+// `flags` points at channel c0, source 0; channels are kMaxWorld flags apart; n_chan consecutive channels.
+__device__ __forceinline__ bool wait_all_sources(const unsigned long long* flags, int W,
+                                                 unsigned long long seq, int* status, int chan,
+                                                 int n_chan = 1) {
+  __shared__ int ok_shared;
+  if (threadIdx.x == 0) ok_shared = 1;
+  __syncthreads();
+  if (threadIdx.x < W * n_chan) {
+    const int c = threadIdx.x / W, src = threadIdx.x % W;
+    if (!wait_flag_ge(flags + c * kMaxWorld + src, seq, kDefaultWaitNs, status, (chan + c) * 16 + src)) ok_shared = 0;
+  }
+  __syncthreads();
+  return ok_shared != 0;
+}
+
+// =================================== ids: push to all peers =======================================
+struct PushIdsParams {
+  const int* values; const int* offsets; const float* weights;
+  long long nnz; int n_offsets; int W; int me;
+  int* dst_values[kMaxWorld]; int* dst_offsets[kMaxWorld]; float* dst_weights[kMaxWorld];
+  unsigned int* done_counter; PeerFlags flags; unsigned long long seq;
+};
+
+__global__ void emb_push_ids_kernel(const PushIdsParams p) {
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int r = 0; r < p.W; ++r) {
+    int* dv = p.dst_values[r];
+    for (long long i = tid; i < p.nnz; i += stride) dv[i] = p.values[i];
+    int* dof = p.dst_offsets[r];
+    for (long long i = tid; i < p.n_offsets; i += stride) dof[i] = p.offsets[i];
+    if (p.weights != nullptr) {
+      float* dw = p.dst_weights[r];
+      for (long long i = tid; i < p.nnz; i += stride) dw[i] = p.weights[i];
+    }
+  }
+  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+}
+
+// =================================== forward: gather + pool + peer store ===========================
+struct FwdParams {
+  IdPtrs ids;
+  const FeatDesc* feats; int n_feats;
+  int W, me, B;
+  int dloc;                 // columns of the stack buffer (== dim except for column-wise features)
+  const float* table;
+  PeerBf16 pooled;          // destination buffers (one per source rank of the ids)
+  uint32_t* occ_key; uint32_t* occ_val; float* occ_gain; unsigned int* occ_count; unsigned int occ_cap;
+  const unsigned long long* wait_flags; unsigned long long wait_seq;   // ids channel (null: no wait)
+  unsigned int* done_counter; PeerFlags flags; unsigned long long seq;  // pooled channel
+  int* status;
+};
+
+template <int VPL, bool TRAIN, bool GAINS>
+__global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 0)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = static_cast<long long>(p.n_feats) * p.W * p.B;
+  const bool lane_on = lane * VPL < p.dloc;
+  for (long long item = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; item < total;
+       item += warps) {
+    const int b = static_cast<int>(item % p.B);
+    const int s = static_cast<int>((item / p.B) % p.W);
+    const FeatDesc f = p.feats[item / (static_cast<long long>(p.B) * p.W)];
+    const int* offs = p.ids.offsets[s] + static_cast<long long>(f.feat_index) * p.B + b;
+    const int o0 = offs[0], o1 = offs[1];
+    const int* vals = p.ids.values[s];
+    const float* wts = GAINS ? p.ids.weights[s] : nullptr;
+    // combiner denominator over the WHOLE bag (not only the rows this rank owns)
+    float scale = 1.f;
+    if (GAINS && f.combiner != kSum && f.seq_len == 0) {
+      float den = 0.f;
+      for (int i = o0 + lane; i < o1; i += 32) {
+        const float w = wts != nullptr ? wts[i] : 1.f;
+        den += f.combiner == kMean ? w : w * w;
+      }
+      den = warp_sum(den);
+      if (f.combiner == kSqrtN) den = sqrtf(den);
+      scale = den != 0.f ? 1.f / den : 0.f;
+    }
+    const long long gv_base = f.grad_off / p.dloc + (static_cast<long long>(s) * p.B + b) * (f.seq_len > 0 ? f.seq_len : 1);
+    Vec<VPL> acc;
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+    __nv_bfloat16* dst_base = p.pooled.p[s] + f.slot_off + (f.kind == kColumnWise ? f.col_lo : 0) + lane * VPL;
+    const long long slot_row = (f.kind == kRowWise ? static_cast<long long>(p.me) * p.B : 0) + b;
+    for (int base = o0; base < o1; base += 32) {
+      const int i = base + lane;
+      int id = -1;
+      float w = 1.f;
+      if (i < o1) {
+        id = vals[i];
+        if (GAINS) w = (wts != nullptr ? wts[i] : 1.f) * scale;
+      }
+      bool owned = id >= 0;
+      unsigned int lrow = 0;
+      if (f.kind == kRowWise) {
+        owned = owned && ((id % p.W + f.rot) % p.W == p.me);
+        lrow = f.row_base + id / p.W;
+      } else {
+        lrow = f.row_base + id;
+      }
+      if (f.seq_len > 0 && i - o0 >= f.seq_len) owned = false;
+      unsigned int mask = __ballot_sync(0xffffffffu, owned);
+      if (TRAIN && mask != 0) {
+        const int n_own = __popc(mask);
+        unsigned int pos = 0;
+        if (lane == 0) pos = atomicAdd(p.occ_count, static_cast<unsigned int>(n_own));
+        pos = __shfl_sync(0xffffffffu, pos, 0);
+        if (pos + n_own <= p.occ_cap) {
+          if (owned) {
+            const unsigned int at = pos + __popc(mask & ((1u << lane) - 1));
+            p.occ_key[at] = lrow;
+            const unsigned int gv = static_cast<unsigned int>(gv_base + (f.seq_len > 0 ? i - o0 : 0));
+            if (GAINS) {
+              p.occ_val[at] = at;                       // index into (occ_gv = occ_key slot of vals, gain)
+              p.occ_gain[2 * static_cast<size_t>(at)] = __uint_as_float(gv);
+              p.occ_gain[2 * static_cast<size_t>(at) + 1] = w;
+            } else {
+              p.occ_val[at] = gv;
+            }
+          }
+        } else {
+          report(p.status, kCapacity, 1);
+        }
+      }
+      if (f.seq_len > 0) {
+        // sequence feature: every position is its own output vector
+        while (mask) {
+          const int j = __ffs(mask) - 1;
+          mask &= mask - 1;
+          const unsigned int rj = __shfl_sync(0xffffffffu, lrow, j);
+          const float wj = __shfl_sync(0xffffffffu, w, j);
+          if (lane_on) {
+            Vec<VPL> r = load_f32<VPL>(p.table + static_cast<size_t>(rj) * p.dloc + lane * VPL);
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) r.v[e] *= wj;
+            store_bf16<VPL>(dst_base + (slot_row * f.seq_len + (base - o0 + j)) * f.dim, r);
+          }
+        }
+        continue;
+      }
+      // gather owned rows, four at a time so several loads are in flight
+      while (mask) {
+        int j[4]; unsigned int rj[4]; float wj[4];
+        int n = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          j[u] = mask ? __ffs(mask) - 1 : 0;
+          if (mask) { mask &= mask - 1; n = u + 1; }
+          rj[u] = __shfl_sync(0xffffffffu, lrow, j[u]);
+          wj[u] = __shfl_sync(0xffffffffu, w, j[u]);
+        }
+        if (lane_on) {
+          Vec<VPL> r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (u < n) r[u] = load_f32<VPL>(p.table + static_cast<size_t>(rj[u]) * p.dloc + lane * VPL);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (u < n) {
+#pragma unroll
+              for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? wj[u] : 1.f, r[u].v[e], acc.v[e]);
+            }
+        }
+      }
+    }
+    if (f.seq_len == 0 && lane_on) store_bf16<VPL>(dst_base + slot_row * f.dim, acc);
+  }
+  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+}
+
+// =================================== combine: sum source slots, write concat =======================
+struct CombineDesc { long long slot_off; int nslots; int dim; int out_col; int seq_len; };
+struct CombineParams {
+  const __nv_bfloat16* pooled; const CombineDesc* feats; int n_feats; int B;
+  __nv_bfloat16* out; long long ld_out;
+  const unsigned long long* wait_flags; int W; int n_chan; unsigned long long wait_seq; int* status;
+};
+
+__global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p) {
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 1, p.n_chan)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = static_cast<long long>(p.n_feats) * p.B;
+  for (long long item = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; item < total;
+       item += warps) {
+    const int fi = static_cast<int>(item % p.n_feats);
+    const long long b = item / p.n_feats;
+    const CombineDesc f = p.feats[fi];
+    const int width = f.dim * (f.seq_len > 0 ? f.seq_len : 1);
+    const __nv_bfloat16* src = p.pooled + f.slot_off + b * width;
+    __nv_bfloat16* dst = p.out + b * p.ld_out + f.out_col;
+    const long long slot_stride = static_cast<long long>(p.B) * width;
+    for (int e = lane * 2; e < width; e += 64) {
+      float x = 0.f, y = 0.f;
+      for (int sl = 0; sl < f.nslots; ++sl) {
+        const uint32_t t = *reinterpret_cast<const uint32_t*>(src + sl * slot_stride + e);
+        x += bf16_lo(t); y += bf16_hi(t);
+      }
+      *reinterpret_cast<uint32_t*>(dst + e) = pack_bf16(x, y);
+    }
+  }
+}
+
+// =================================== backward: push activation gradients ===========================
+struct PushGradDesc {
+  int kind; int owner; int dim; int in_col; int seq_len; int pad;
+  long long grad_off[kMaxWorld];   // element offset of the feature block in rank r's gradient buffer (-1: none)
+};
+struct PushGradParams {
+  const __nv_bfloat16* grad; long long ld; const PushGradDesc* feats; int n_feats; int B; int W; int me;
+  PeerBf16 dst; unsigned int* done_counter; PeerFlags flags; unsigned long long seq;
+};
+
+__global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = static_cast<long long>(p.n_feats) * p.B;
+  for (long long item = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; item < total;
+       item += warps) {
+    const int fi = static_cast<int>(item % p.n_feats);
+    const long long b = item / p.n_feats;
+    const PushGradDesc& f = p.feats[fi];
+    const int width = f.dim * (f.seq_len > 0 ? f.seq_len : 1);
+    const __nv_bfloat16* src = p.grad + b * p.ld + f.in_col;
+    const long long row = static_cast<long long>(p.me) * p.B + b;
+    if (f.kind == kColumnWise) {
+      const int dl = f.dim / p.W;
+      for (int e = lane * 2; e < f.dim; e += 64) {
+        const int r = e / dl;
+        *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * dl + (e - r * dl)) =
+            *reinterpret_cast<const uint32_t*>(src + e);
+      }
+    } else {
+      const int r0 = f.kind == kTableWise ? f.owner : 0;
+      const int r1 = f.kind == kTableWise ? f.owner + 1 : p.W;
+      for (int e = lane * 2; e < width; e += 64) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + e);
+        for (int r = r0; r < r1; ++r)
+          *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+      }
+    }
+  }
+  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+}
+
+// =================================== backward: segmented reduce + row optimizer ====================
+struct BwdParams {
+  const uint32_t* keys; const uint32_t* vals; const float* occ_gain; const unsigned int* n_occ;
+  const __nv_bfloat16* grads;   // [*, dloc] gradient vectors
+  float* table; float* slot0; float* slot1; int dloc;
+  int opt; float hp[6]; float grad_scale; int slot1_rowwise;
+  float* scratch;               // [n_chunks, dloc] partial sums of runs that cross chunk boundaries (kept zero)
+  const unsigned long long* wait_flags; int W; unsigned long long wait_seq; int* status;
+};
+
+template <int VPL>
+__device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned int row, Vec<VPL> g, int lane,
+                                                 bool lane_on) {
+  const size_t off = static_cast<size_t>(row) * p.dloc + lane * VPL;
+  Vec<VPL> w;
+  if (lane_on) w = load_f32_rw<VPL>(p.table + off);
+#pragma unroll
+  for (int e = 0; e < VPL; ++e) g.v[e] *= p.grad_scale;
+  float sq = 0.f;
+  if (lane_on) {
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) sq += g.v[e] * g.v[e];
+  }
+  const float lr = p.hp[0];
+  switch (p.opt) {
+    case kSGD:
+      if (lane_on) {
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) w.v[e] -= lr * g.v[e];
+      }
+      break;
+    case kRowAdagrad: {
+      const float msq = warp_sum(sq) / p.dloc;
+      const float s = p.slot0[row] + msq;
+      __syncwarp();
+      if (lane == 0) p.slot0[row] = s;
+      const float inv = lr / (sqrtf(s) + p.hp[1]);
+      if (lane_on) {
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) w.v[e] -= inv * g.v[e];
+      }
+      break;
+    }
+    case kAdagrad:
+      if (lane_on) {
+        Vec<VPL> a = load_f32_rw<VPL>(p.slot0 + off);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) { a.v[e] += g.v[e] * g.v[e]; w.v[e] -= lr * g.v[e] * rsqrtf(a.v[e]); }
+        store_f32<VPL>(p.slot0 + off, a);
+      }
+      break;
+    case kAdam:
+    case kRowAdam: {
+      const float b1 = p.hp[1], b2 = p.hp[2], eps = p.hp[3];
+      float vrow = 0.f;
+      if (p.opt == kRowAdam) {
+        const float msq = warp_sum(sq) / p.dloc;
+        vrow = p.slot1[row];
+        vrow += (1.f - b2) * (msq - vrow);
+        __syncwarp();
+        if (lane == 0) p.slot1[row] = vrow;
+      }
+      if (lane_on) {
+        Vec<VPL> m = load_f32_rw<VPL>(p.slot0 + off);
+        Vec<VPL> v;
+        if (p.opt == kAdam) v = load_f32_rw<VPL>(p.slot1 + off);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+          m.v[e] += (1.f - b1) * (g.v[e] - m.v[e]);
+          float ve = vrow;
+          if (p.opt == kAdam) { v.v[e] += (1.f - b2) * (g.v[e] * g.v[e] - v.v[e]); ve = v.v[e]; }
+          w.v[e] -= lr * m.v[e] / (sqrtf(ve) + eps);
+        }
+        store_f32<VPL>(p.slot0 + off, m);
+        if (p.opt == kAdam) store_f32<VPL>(p.slot1 + off, v);
+      }
+      break;
+    }
+    case kAdagradMomentum:
+      if (lane_on) {
+        const float k = p.hp[1], beta2 = p.hp[2], eps = p.hp[3], expo = p.hp[4];
+        const bool nesterov = p.hp[5] != 0.f;
+        Vec<VPL> a = load_f32_rw<VPL>(p.slot0 + off), mo = load_f32_rw<VPL>(p.slot1 + off);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+          const float g2 = g.v[e] * g.v[e];
+          a.v[e] = beta2 == 1.f ? a.v[e] + g2 : beta2 * a.v[e] + (1.f - beta2) * g2;
+          const float s = powf(a.v[e] + eps, -1.f / expo) * g.v[e];
+          mo.v[e] = k * mo.v[e] + s;
+          w.v[e] -= lr * (nesterov ? k * mo.v[e] + s : mo.v[e]);
+        }
+        store_f32<VPL>(p.slot0 + off, a);
+        store_f32<VPL>(p.slot1 + off, mo);
+      }
+      break;
+    case kFTRL:
+      if (lane_on) {
+        const float lrp = p.hp[1], l1 = p.hp[2], l2 = p.hp[3], beta = p.hp[4];
+        const bool mult = p.hp[5] != 0.f;
+        Vec<VPL> a = load_f32_rw<VPL>(p.slot0 + off), li = load_f32_rw<VPL>(p.slot1 + off);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+          const float an = a.v[e] + g.v[e] * g.v[e];
+          const float po = powf(a.v[e], -lrp), pn = powf(an, -lrp);
+          float ln, l1s, den;
+          if (mult) { ln = li.v[e] + lr * g.v[e] - (pn - po) * w.v[e]; l1s = l1 * lr; den = pn + 2.f * lr * l2 + beta; }
+          else { ln = li.v[e] + g.v[e] - ((pn - po) / lr) * w.v[e]; l1s = l1; den = (pn + beta) / lr + 2.f * l2; }
+          const float num = l1 == 0.f ? -ln : fminf(fmaxf(ln, -l1s), l1s) - ln;
+          w.v[e] = num / den;
+          a.v[e] = an; li.v[e] = ln;
+        }
+        store_f32<VPL>(p.slot0 + off, a);
+        store_f32<VPL>(p.slot1 + off, li);
+      }
+      break;
+    case kLaProp:
+      if (lane_on) {
+        const float b1 = p.hp[1], decay = p.hp[2], eps = p.hp[3];
+        Vec<VPL> mu = load_f32_rw<VPL>(p.slot0 + off), nu = load_f32_rw<VPL>(p.slot1 + off);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+          nu.v[e] = decay * nu.v[e] + (1.f - decay) * (g.v[e] * g.v[e] + eps);
+          mu.v[e] = b1 * mu.v[e] + sqrtf(1.f - b1 * b1) * g.v[e] * rsqrtf(nu.v[e]);
+          w.v[e] -= lr * mu.v[e];
+        }
+        store_f32<VPL>(p.slot0 + off, mu);
+        store_f32<VPL>(p.slot1 + off, nu);
+      }
+      break;
+    default: break;
+  }
+  if (lane_on) store_f32<VPL>(p.table + off, w);
+}
+
+// first index i in [0, hi) with keys[i] >= key  (keys sorted ascending)
+__device__ __forceinline__ unsigned int lower_bound(const uint32_t* keys, unsigned int hi, uint32_t key) {
+  unsigned int lo = 0;
+  while (lo < hi) {
+    const unsigned int mid = (lo + hi) >> 1;
+    if (keys[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// One warp per chunk of 32 sorted occurrences.  Runs of equal rows that lie inside the chunk are
+// reduced in registers and applied at once; the pieces of a run that crosses chunk boundaries are
+// added (fp32 atomics) into the scratch line of the chunk where the run STARTS, and
+// emb_bwd_finalize applies those afterwards.  Hot rows (Zipf heads with 10^5 occurrences) are
+// thereby reduced by thousands of warps in parallel instead of one.
+template <int VPL, bool GAINS>
+__global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) {
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 2)) return;
+  const int lane = threadIdx.x & 31;
+  const unsigned int n = *p.n_occ;
+  const unsigned int chunk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned int start = chunk * 32u;
+  if (start >= n) return;
+  const int cnt = min(32u, n - start);
+  const bool lane_on = lane * VPL < p.dloc;
+  uint32_t key = 0xffffffffu, val = 0;
+  if (lane < cnt) { key = p.keys[start + lane]; val = p.vals[start + lane]; }
+  unsigned int gv = val;
+  float gain = 1.f;
+  if (GAINS && lane < cnt) {
+    gv = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
+    gain = p.occ_gain[2 * static_cast<size_t>(val) + 1];
+  }
+  const bool has_prev = start > 0, has_next = start + cnt < n;
+  const uint32_t prev_key = has_prev ? p.keys[start - 1] : 0;
+  const uint32_t next_key = has_next ? p.keys[start + cnt] : 0;
+  Vec<VPL> acc;
+#pragma unroll
+  for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+  int seg_start = 0;
+  for (int j0 = 0; j0 < cnt; j0 += 4) {
+    Vec<VPL> g[4]; uint32_t kj[4]; float gj[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = min(j0 + u, cnt - 1);
+      kj[u] = __shfl_sync(0xffffffffu, key, j);
+      const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
+      gj[u] = __shfl_sync(0xffffffffu, gain, j);
+      if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.dloc + lane * VPL);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      if (j >= cnt) break;
+      if (lane_on) {
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? gj[u] : 1.f, g[u].v[e], acc.v[e]);
+      }
+      const uint32_t knext = __shfl_sync(0xffffffffu, key, min(j + 1, 31));
+      const bool last = (j == cnt - 1) || (knext != kj[u]);
+      if (!last) continue;
+      const bool begins = (seg_start > 0) || !has_prev || (prev_key != kj[u]);
+      const bool ends = (j < cnt - 1) || !has_next || (next_key != kj[u]);
+      if (begins && ends) {
+        apply_row_update<VPL>(p, kj[u], acc, lane, lane_on);
+      } else {
+        unsigned int slot = chunk;
+        if (!begins) {
+          if (lane == 0) slot = lower_bound(p.keys, start, kj[u]) >> 5;
+          slot = __shfl_sync(0xffffffffu, slot, 0);
+        }
+        if (lane_on) {
+          float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
+#pragma unroll
+          for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+      seg_start = j + 1;
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) emb_bwd_finalize_kernel(const BwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const unsigned int n = *p.n_occ;
+  const unsigned int chunk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned int start = chunk * 32u;
+  if (start >= n) return;
+  const unsigned int last = min(start + 32u, n) - 1;
+  const uint32_t klast = p.keys[last];
+  if (!(last + 1 < n && p.keys[last + 1] == klast)) return;            // run does not cross into the next chunk
+  if (p.keys[start] == klast && start > 0 && p.keys[start - 1] == klast) return;  // run started earlier
+  const bool lane_on = lane * VPL < p.dloc;
+  float* sp = p.scratch + static_cast<size_t>(chunk) * p.dloc + lane * VPL;
+  Vec<VPL> acc;
+#pragma unroll
+  for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+  if (lane_on) {
+    acc = load_f32_rw<VPL>(sp);
+    Vec<VPL> z;
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) z.v[e] = 0.f;
+    store_f32<VPL>(sp, z);
+  }
+  apply_row_update<VPL>(p, klast, acc, lane, lane_on);
+}
+
+static int blocks_for(long long warps_needed, int max_blocks) {
+  long long b = (warps_needed + 7) / 8;
+  if (b < 1) b = 1;
+  return static_cast<int>(b < max_blocks ? b : max_blocks);
+}
+
+}  // namespace emb
+}  // namespace recml
+
+using namespace recml::emb;
+
+extern "C" int recml_emb_push_ids(const PushIdsParams* p, cudaStream_t stream) {
+  long long work = p->nnz > p->n_offsets ? p->nnz : p->n_offsets;
+  int blocks = static_cast<int>((work + 1023) / 1024);
+  blocks = blocks < 1 ? 1 : (blocks > 296 ? 296 : blocks);
+  emb_push_ids_kernel<<<blocks, 256, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+template <int VPL>
+static void launch_fwd(const FwdParams& p, bool train, bool gains, int blocks, cudaStream_t stream) {
+  if (train) {
+    if (gains) emb_fwd_kernel<VPL, true, true><<<blocks, 256, 0, stream>>>(p);
+    else emb_fwd_kernel<VPL, true, false><<<blocks, 256, 0, stream>>>(p);
+  } else {
+    if (gains) emb_fwd_kernel<VPL, false, true><<<blocks, 256, 0, stream>>>(p);
+    else emb_fwd_kernel<VPL, false, false><<<blocks, 256, 0, stream>>>(p);
+  }
+}
+
+static int vpl_for(int dloc) { return dloc <= 32 ? 1 : dloc <= 64 ? 2 : dloc <= 128 ? 4 : dloc <= 256 ? 8 : 0; }
+
+// Resident-block bound: co-operating grids (a kernel whose blocks wait on peers) must fit the GPU.
+extern "C" int recml_emb_fwd(const FwdParams* p, int train, int gains, cudaStream_t stream) {
+  const int vpl = vpl_for(p->dloc);
+  if (vpl == 0 || (p->dloc % vpl) != 0) return -10;
+  const long long items = static_cast<long long>(p->n_feats) * p->W * p->B;
+  const int blocks = blocks_for(items, 148 * 8);
+  switch (vpl) {
+    case 1: launch_fwd<1>(*p, train, gains, blocks, stream); break;
+    case 2: launch_fwd<2>(*p, train, gains, blocks, stream); break;
+    case 4: launch_fwd<4>(*p, train, gains, blocks, stream); break;
+    default: launch_fwd<8>(*p, train, gains, blocks, stream); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_emb_combine(const CombineParams* p, cudaStream_t stream) {
+  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 8);
+  emb_combine_kernel<<<blocks, 256, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_emb_push_grads(const PushGradParams* p, cudaStream_t stream) {
+  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 8);
+  emb_push_grads_kernel<<<blocks, 256, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" long long recml_sort_temp_bytes(long long n) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
+                                  static_cast<const uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr), n);
+  return static_cast<long long>(bytes);
+}
+
+extern "C" int recml_sort_pairs_u32(const uint32_t* keys_in, uint32_t* keys_out, const uint32_t* vals_in,
+                                    uint32_t* vals_out, long long n, int end_bit, void* temp,
+                                    long long temp_bytes, cudaStream_t stream) {
+  size_t bytes = static_cast<size_t>(temp_bytes);
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, bytes, keys_in, keys_out, vals_in, vals_out, n, 0, end_bit, stream);
+  return e == cudaSuccess ? 0 : -1;
+}
+
+// max_occ: host-side upper bound of *n_occ used to size the grid (chunks beyond n exit at once).
+extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int gains, cudaStream_t stream) {
+  const int vpl = vpl_for(p->dloc);
+  if (vpl == 0 || (p->dloc % vpl) != 0) return -10;
+  if (max_occ <= 0) return 0;
+  const long long chunks = (max_occ + 31) / 32;
+  const int blocks = static_cast<int>((chunks + 7) / 8);
+#define RECML_BWD(V)                                                                      \
+  do {                                                                                    \
+    if (gains) emb_bwd_update_kernel<V, true><<<blocks, 256, 0, stream>>>(*p);            \
+    else emb_bwd_update_kernel<V, false><<<blocks, 256, 0, stream>>>(*p);                 \
+    emb_bwd_finalize_kernel<V><<<blocks, 256, 0, stream>>>(*p);                           \
+  } while (0)
+  switch (vpl) {
+    case 1: RECML_BWD(1); break;
+    case 2: RECML_BWD(2); break;
+    case 4: RECML_BWD(4); break;
+    default: RECML_BWD(8); break;
+  }
+#undef RECML_BWD
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_emb_struct_sizes(int* out) {
+  out[0] = sizeof(FeatDesc); out[1] = sizeof(FwdParams); out[2] = sizeof(CombineDesc); out[3] = sizeof(CombineParams);
+  out[4] = sizeof(PushGradDesc); out[5] = sizeof(PushGradParams); out[6] = sizeof(BwdParams); out[7] = sizeof(PushIdsParams);
+  return 0;
+}

@@ -37,6 +37,7 @@ enum Epilogue : int {
   kEpiCross = 1,     // V = acc + bias (optional store to out2); D = aux0 * V + aux1
   kEpiMaskRelu = 2,  // D = acc * (aux0 > 0)              (ReLU backward fused in dgrad)
   kEpiMulAdd = 3,    // D = acc * aux0 (+ aux1)           (DCN input-gradient paths)
+  kEpiAdd = 4,       // D = acc + aux0                    (residual / skip gradients)
 };
 
 struct Params {
@@ -312,6 +313,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               for (int j = 0; j < 4; ++j) {
                 x[2 * j] = bf16_lo(a0w[j]) > 0.f ? x[2 * j] : 0.f;
                 x[2 * j + 1] = bf16_hi(a0w[j]) > 0.f ? x[2 * j + 1] : 0.f;
+              }
+            } else if (p.epi == kEpiAdd) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                x[2 * j] += bf16_lo(a0w[j]);
+                x[2 * j + 1] += bf16_hi(a0w[j]);
               }
             } else {  // kEpiMulAdd
 #pragma unroll

@@ -91,7 +91,7 @@ class CollectiveBackend:
     return torch.ones_like(ids, dtype=torch.bool), tp.row_base + ids  # COLUMN_WISE
 
   # -- forward -------------------------------------------------------------------------------
-  def forward(self, kjt: jagged_lib.KeyedJagged, training: bool):
+  def forward(self, kjt: jagged_lib.KeyedJagged, training: bool, out=None, out_col: int = 0):
     m = self.m
     B, W, F = kjt.batch_size(), m.world, len(m.feature_names)
     dev = m.device
@@ -135,12 +135,14 @@ class CollectiveBackend:
     if W > 1:
       recv = torch.empty_like(send)
       dist.all_to_all_single(recv, send, group=m.group)
-      out = recv.view(W, B, self.width).sum(dim=0)
-    else:
-      out = send
-    if m.config.output_dtype is not None:
-      out = out.to(m.config.output_dtype)
-    return out, (saved if training else None)
+      out_sum = recv.view(W, B, self.width).sum(dim=0)
+    res = send if W == 1 else out_sum
+    if out is not None:
+      out[:, out_col:out_col + self.width] = res.to(out.dtype)
+      res = out[:, out_col:out_col + self.width]
+    elif m.config.output_dtype is not None:
+      res = res.to(m.config.output_dtype)
+    return res, (saved if training else None)
 
   # -- backward: aggregate per unique row inside each stack, then update ---------------------------
   @torch.no_grad()
@@ -166,6 +168,7 @@ class CollectiveBackend:
       grads = torch.cat([x for _, x in items])
       uniq, inv = torch.unique(rows, return_inverse=True)
       agg = torch.zeros(uniq.numel(), grads.shape[1], device=grads.device).index_add_(0, inv, grads)
+      agg *= m.grad_scale
       opt = m.plan.stacks[si].optimizer
       slots = {k: v[uniq] for k, v in m.stack_slots[si].items()}
       new_w, new_slots = row_optim.apply(opt, m.step_count, m.stack_weights[si][uniq], agg, slots)

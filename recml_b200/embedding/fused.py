@@ -1,0 +1,381 @@
+"""Fused sharded-embedding backend: sm_100a kernels over NVLink peer memory
+(`csrc/cuda/embedding.cu`).
+
+Per step:  ids are pushed to every peer (one kernel, peer stores + flag) → one forward kernel per
+table stack gathers / pools the rows this rank owns for EVERY rank's samples and stores each
+pooled bf16 vector straight into the requesting rank's buffer (the all-to-all is the store) →
+the combine kernel waits for all sources' flags, sums the per-source slots of row-sharded
+features and writes the concatenated dense input.  Backward: one kernel pushes each feature's
+activation gradient into its owner's buffer, the owner radix-sorts the (row, gradient index)
+occurrences recorded during forward, reduces runs of equal rows and applies the row optimizer
+inside the same kernel.  All buffers that peers write are double-buffered by step parity; flags
+are monotonically increasing step sequence numbers, and every wait is bounded.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from recml_b200.comm import symm
+from recml_b200.embedding import collective
+from recml_b200.embedding import jagged as jagged_lib
+from recml_b200.embedding.planner import Placement
+from recml_b200.ops import _lib
+
+MAXW = 8
+c_ll, c_int, c_uint, c_float, c_vp = (ctypes.c_longlong, ctypes.c_int, ctypes.c_uint, ctypes.c_float,
+                                      ctypes.c_void_p)
+KIND = {Placement.TABLE_WISE: 0, Placement.ROW_WISE: 1, Placement.COLUMN_WISE: 2}
+COMBINER = {"sum": 0, "mean": 1, "sqrtn": 2}
+OPT = {"sgd": 0, "adagrad": 1, "rowwise_adagrad": 2, "adam": 3, "rowwise_adam": 4,
+       "adagrad_momentum": 5, "ftrl": 6, "laprop": 7}
+
+
+class FeatDesc(ctypes.Structure):
+  _fields_ = [("feat_index", c_int), ("kind", c_int), ("owner", c_int), ("rot", c_int), ("row_base", c_int),
+              ("combiner", c_int), ("dim", c_int), ("col_lo", c_int), ("slot_off", c_ll), ("grad_off", c_ll),
+              ("seq_len", c_int), ("pad", c_int)]
+
+
+class IdPtrs(ctypes.Structure):
+  _fields_ = [("values", c_vp * MAXW), ("offsets", c_vp * MAXW), ("weights", c_vp * MAXW)]
+
+
+class FwdParams(ctypes.Structure):
+  _fields_ = [("ids", IdPtrs), ("feats", c_vp), ("n_feats", c_int), ("W", c_int), ("me", c_int), ("B", c_int),
+              ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
+              ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("wait_flags", c_vp),
+              ("wait_seq", ctypes.c_ulonglong), ("done_counter", c_vp), ("flags", c_vp * MAXW),
+              ("seq", ctypes.c_ulonglong), ("status", c_vp)]
+
+
+class CombineDesc(ctypes.Structure):
+  _fields_ = [("slot_off", c_ll), ("nslots", c_int), ("dim", c_int), ("out_col", c_int), ("seq_len", c_int)]
+
+
+class CombineParams(ctypes.Structure):
+  _fields_ = [("pooled", c_vp), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("out", c_vp), ("ld_out", c_ll),
+              ("wait_flags", c_vp), ("W", c_int), ("n_chan", c_int), ("wait_seq", ctypes.c_ulonglong),
+              ("status", c_vp)]
+
+
+class PushGradDesc(ctypes.Structure):
+  _fields_ = [("kind", c_int), ("owner", c_int), ("dim", c_int), ("in_col", c_int), ("seq_len", c_int),
+              ("pad", c_int), ("grad_off", c_ll * MAXW)]
+
+
+class PushGradParams(ctypes.Structure):
+  _fields_ = [("grad", c_vp), ("ld", c_ll), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("W", c_int),
+              ("me", c_int), ("dst", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
+              ("seq", ctypes.c_ulonglong)]
+
+
+class BwdParams(ctypes.Structure):
+  _fields_ = [("keys", c_vp), ("vals", c_vp), ("occ_gain", c_vp), ("n_occ", c_vp), ("grads", c_vp),
+              ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
+              ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
+              ("wait_flags", c_vp), ("W", c_int), ("wait_seq", ctypes.c_ulonglong), ("status", c_vp)]
+
+
+class PushIdsParams(ctypes.Structure):
+  _fields_ = [("values", c_vp), ("offsets", c_vp), ("weights", c_vp), ("nnz", c_ll), ("n_offsets", c_int),
+              ("W", c_int), ("me", c_int), ("dst_values", c_vp * MAXW), ("dst_offsets", c_vp * MAXW),
+              ("dst_weights", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
+              ("seq", ctypes.c_ulonglong)]
+
+
+_layout_checked = False
+
+
+def _check_layout(lib):
+  global _layout_checked
+  if _layout_checked:
+    return
+  sizes = (c_int * 8)()
+  lib.recml_emb_struct_sizes(sizes)
+  mine = [ctypes.sizeof(t) for t in (FeatDesc, FwdParams, CombineDesc, CombineParams, PushGradDesc,
+                                     PushGradParams, BwdParams, PushIdsParams)]
+  assert list(sizes) == mine, f"struct layout mismatch: C {list(sizes)} vs ctypes {mine}"
+  _layout_checked = True
+
+
+def _device_struct_array(items, device) -> torch.Tensor:
+  if not items:
+    return torch.zeros(8, dtype=torch.uint8, device=device)
+  raw = b"".join(bytes(x) for x in items)
+  return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+
+
+class FusedBackend:
+  """See the module docstring.  Buffers are sized lazily from the first batch
+  (`capacity_factor` × its id count) and grown when a later batch needs more."""
+
+  def __init__(self, module, capacity_factor: float = 1.25):
+    self.m = module
+    self.lib = _lib.cuda()
+    _check_layout(self.lib)
+    m = module
+    if m.world > MAXW:
+      raise ValueError(f"fused backend supports up to {MAXW} ranks per node, got {m.world}")
+    self.layout, self.width = collective.feature_layout(m)
+    self.capacity_factor = capacity_factor
+    self.seq = 0
+    self.B = None
+    self.status = _lib.status_buffer(m.device)
+    self._sort_temp: dict[int, torch.Tensor] = {}
+    self.has_gains = any(s.combiner != "sum" or s.weight_name is not None
+                         for s in m.config.specs.values())
+
+  # -- one-time set-up for a batch geometry --------------------------------------------------------------
+  def _setup(self, kjt: jagged_lib.KeyedJagged):
+    m = self.m
+    W, B, dev = m.world, kjt.batch_size(), m.device
+    self.B = B
+    F = len(m.feature_names)
+    self.n_offsets = F * B + 1
+    nnz_cap = int(kjt.values.numel() * self.capacity_factor) + 1024
+    if W > 1:  # all ranks must agree on the layout
+      import torch.distributed as dist
+      t = torch.tensor([nnz_cap], device=dev, dtype=torch.int64)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX, group=m.group)
+      nnz_cap = int(t.item())
+    self.nnz_cap = nnz_cap
+    # ---- pooled-buffer layout (identical on every rank) ----
+    slot_off, off = {}, 0
+    self.combine_descs = []
+    for fname, col, width, L in self.layout:
+      tp = m.plan.tables[m.feature_to_table[fname]]
+      nslots = W if tp.placement is Placement.ROW_WISE else 1
+      slot_off[fname] = off
+      self.combine_descs.append(CombineDesc(off, nslots, tp.dim, col, L))
+      off += nslots * B * width
+    pooled_elems = off
+    # ---- gradient-buffer layout per destination rank ----
+    # grad_off[r][fname]: element offset in rank r's gradient buffer of the [W*B, width_local] block
+    self.grad_off = [dict() for _ in range(W)]
+    grad_elems = [0] * W
+    for fname, col, width, L in self.layout:
+      tp = m.plan.tables[m.feature_to_table[fname]]
+      for r in range(W):
+        if tp.placement is Placement.TABLE_WISE and tp.owner != r:
+          continue
+        wl = width // W if tp.placement is Placement.COLUMN_WISE else width
+        unit = tp.dim // W if tp.placement is Placement.COLUMN_WISE else tp.dim
+        grad_elems[r] = (grad_elems[r] + unit - 1) // unit * unit   # block starts on a whole vector
+        self.grad_off[r][fname] = grad_elems[r]
+        grad_elems[r] += W * B * wl
+    grad_cap = max(grad_elems)
+    # ---- carve one symmetric allocation ----
+    cv = symm.Carver()
+    n_chan = 2 + len(m.plan.stacks)
+    self.flag_off = cv.take(n_chan * MAXW * 8)
+    self.ids_off = [[(cv.take(nnz_cap * 4), cv.take(self.n_offsets * 4), cv.take(nnz_cap * 4))
+                     for _ in range(W)] for _ in range(2)] if W > 1 else None
+    self.pooled_off = [cv.take(pooled_elems * 2) for _ in range(2 if W > 1 else 1)]
+    self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
+    self.buf = symm.SymmBuffer(cv.off, m.group, dev)
+    self.pooled_elems, self.grad_cap = pooled_elems, grad_cap
+    # ---- per-stack work lists and occurrence storage ----
+    self.stacks = []
+    for si, st in enumerate(m.plan.stacks):
+      feats, occ_cap = [], 0
+      for fname, col, width, L in self.layout:
+        tp = m.plan.tables[m.feature_to_table[fname]]
+        if tp.stack != si:
+          continue
+        if tp.placement is Placement.TABLE_WISE and tp.owner != m.rank:
+          continue
+        spec = m.config.specs[fname]
+        feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
+                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot_off[fname],
+                              self.grad_off[m.rank][fname], L, 0))
+      info: dict[str, Any] = {"n_feats": len(feats), "feats": _device_struct_array(feats, dev),
+                              "feat_names": [m.feature_names[f.feat_index] for f in feats]}
+      info["count"] = torch.zeros(1, dtype=torch.int32, device=dev)
+      info["done"] = torch.zeros(4, dtype=torch.int32, device=dev)
+      info["count_host"] = torch.zeros(1, dtype=torch.int32).pin_memory()
+      self.stacks.append(info)
+    self.combine_dev = _device_struct_array(self.combine_descs, dev)
+    push = []
+    for fname, col, width, L in self.layout:
+      tp = m.plan.tables[m.feature_to_table[fname]]
+      d = PushGradDesc(KIND[tp.placement], tp.owner, tp.dim, col, L, 0)
+      for r in range(MAXW):
+        d.grad_off[r] = self.grad_off[r].get(fname, -1) if r < W else -1
+      push.append(d)
+    self.push_dev = _device_struct_array(push, dev)
+    self.done_ids = torch.zeros(4, dtype=torch.int32, device=dev)
+    self.done_grads = torch.zeros(4, dtype=torch.int32, device=dev)
+    self._occ_ready = False
+
+  def _ensure_occ(self, kjt):
+    """Occurrence / sort / scratch storage (training only), sized from the batch."""
+    if self._occ_ready:
+      return
+    m, dev, W, B = self.m, self.m.device, self.m.world, self.B
+    per_feat = {}
+    off = kjt.offsets
+    for fi, fname in enumerate(m.feature_names):
+      per_feat[fname] = int(off[(fi + 1) * B].item() - off[fi * B].item())
+    for si, info in enumerate(self.stacks):
+      cap = 0
+      for fname in info["feat_names"]:
+        tp = m.plan.tables[m.feature_to_table[fname]]
+        n = per_feat[fname] * W
+        if tp.placement is Placement.ROW_WISE and W > 1:
+          n = int(n / W * 1.5) + 4096   # MOD sharding spreads ids evenly; 50 % head-room
+        cap += n
+      cap = int(cap * self.capacity_factor) + 1024
+      info["occ_cap"] = cap
+      info["keys"] = torch.empty(2, cap, dtype=torch.int32, device=dev)
+      info["vals"] = torch.empty(2, cap, dtype=torch.int32, device=dev)
+      info["gain"] = torch.empty(cap, 2, dtype=torch.float32, device=dev) if self.has_gains else None
+      dloc = m.plan.stacks[si].dim
+      info["scratch"] = torch.zeros((cap + 31) // 32, dloc, dtype=torch.float32, device=dev)
+      nbytes = int(self.lib.recml_sort_temp_bytes(c_ll(cap)))
+      info["sort_temp"] = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+      rows = m.plan.stacks[si].rows
+      info["end_bit"] = max(1, int(rows - 1).bit_length()) if rows > 1 else 1
+    self._occ_ready = True
+
+  def _flag_ptr(self, rank: int, chan: int, src: int) -> int:
+    return self.buf.peer_ptr(rank, self.flag_off + (chan * MAXW + src) * 8)
+
+  # -- forward ---------------------------------------------------------------------------------------------
+  def forward(self, kjt: jagged_lib.KeyedJagged, training: bool, out: torch.Tensor | None = None,
+              out_col: int = 0):
+    m = self.m
+    W, dev = m.world, m.device
+    if self.B is None:
+      self._setup(kjt)
+    if kjt.batch_size() != self.B:
+      raise ValueError(f"fused backend was set up for batch {self.B}, got {kjt.batch_size()}")
+    if kjt.values.numel() > self.nnz_cap:
+      raise ValueError(f"batch has {kjt.values.numel()} ids, capacity is {self.nnz_cap}")
+    assert kjt.values.dtype == torch.int32 and kjt.offsets.dtype == torch.int32
+    if training:
+      self._ensure_occ(kjt)
+    self.seq += 1
+    seq, par = self.seq, (self.seq & 1) if W > 1 else 0
+    st = _lib.stream()
+    gains = self.has_gains
+    B = self.B
+    ids = IdPtrs()
+    if W > 1:
+      p = PushIdsParams()
+      p.values, p.offsets = kjt.values.data_ptr(), kjt.offsets.data_ptr()
+      p.weights = kjt.weights.data_ptr() if kjt.weights is not None else None
+      p.nnz, p.n_offsets, p.W, p.me = kjt.values.numel(), self.n_offsets, W, m.rank
+      vo, oo, wo = self.ids_off[par][m.rank]
+      for r in range(W):
+        p.dst_values[r] = self.buf.peer_ptr(r, vo)
+        p.dst_offsets[r] = self.buf.peer_ptr(r, oo)
+        p.dst_weights[r] = self.buf.peer_ptr(r, wo)
+        p.flags[r] = self._flag_ptr(r, 0, m.rank)
+      p.done_counter, p.seq = self.done_ids.data_ptr(), seq
+      _lib.check_rc(self.lib.recml_emb_push_ids(ctypes.byref(p), st), "emb_push_ids")
+      for s in range(W):
+        vo, oo, wo = self.ids_off[par][s]
+        ids.values[s] = self.buf.peer_ptr(m.rank, vo)
+        ids.offsets[s] = self.buf.peer_ptr(m.rank, oo)
+        ids.weights[s] = self.buf.peer_ptr(m.rank, wo) if kjt.weights is not None else None
+    else:
+      ids.values[0], ids.offsets[0] = kjt.values.data_ptr(), kjt.offsets.data_ptr()
+      ids.weights[0] = kjt.weights.data_ptr() if kjt.weights is not None else None
+    for si, info in enumerate(self.stacks):
+      if training:
+        info["count"].zero_()
+      fp = FwdParams()
+      fp.ids = ids
+      fp.feats, fp.n_feats = info["feats"].data_ptr(), info["n_feats"]
+      fp.W, fp.me, fp.B, fp.dloc = W, m.rank, B, m.plan.stacks[si].dim
+      fp.table = m.stack_weights[si].data_ptr()
+      for r in range(W):
+        fp.pooled[r] = self.buf.peer_ptr(r, self.pooled_off[par])
+        fp.flags[r] = self._flag_ptr(r, 1 + si, m.rank)
+      if training:
+        fp.occ_key, fp.occ_val = info["keys"][0].data_ptr(), info["vals"][0].data_ptr()
+        fp.occ_gain = info["gain"].data_ptr() if gains else None
+        fp.occ_count, fp.occ_cap = info["count"].data_ptr(), info["occ_cap"]
+      fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
+      fp.wait_seq = seq
+      fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
+      if info["n_feats"] or W > 1:
+        _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
+                      "emb_fwd")
+      if training:
+        info["count_host"].copy_(info["count"], non_blocking=True)
+    ev = None
+    if training:
+      ev = torch.cuda.Event()
+      ev.record()
+    odt = m.config.output_dtype or torch.bfloat16
+    if out is None:
+      out = torch.empty(B, self.width, dtype=torch.bfloat16, device=dev)
+      out_col = 0
+    cp = CombineParams()
+    cp.pooled = self.buf.peer_ptr(m.rank, self.pooled_off[par])
+    cp.feats, cp.n_feats, cp.B = self.combine_dev.data_ptr(), len(self.combine_descs), B
+    cp.out, cp.ld_out = out.data_ptr() + out_col * 2, out.stride(0)
+    # wait on the pooled channels of every stack: channels 1..n_stacks are contiguous
+    cp.wait_flags = self._flag_ptr(m.rank, 1, 0) if W > 1 else None
+    cp.W, cp.n_chan, cp.wait_seq, cp.status = W, len(self.stacks), seq, self.status.data_ptr()
+    _lib.check_rc(self.lib.recml_emb_combine(ctypes.byref(cp), st), "emb_combine")
+    res = out if odt == torch.bfloat16 else out.to(odt)
+    saved = {"seq": seq, "par": par, "event": ev, "kjt": kjt} if training else None
+    return res, saved
+
+  # -- backward ----------------------------------------------------------------------------------------------
+  @torch.no_grad()
+  def backward(self, saved: Any, grad_out: torch.Tensor) -> None:
+    m = self.m
+    W, B = m.world, self.B
+    st = _lib.stream()
+    seq, par = saved["seq"], saved["par"]
+    if grad_out.dtype != torch.bfloat16:
+      grad_out = grad_out.to(torch.bfloat16)
+    if grad_out.stride(-1) != 1:
+      grad_out = grad_out.contiguous()
+    pg = PushGradParams()
+    pg.grad, pg.ld = grad_out.data_ptr(), grad_out.stride(0)
+    pg.feats, pg.n_feats, pg.B, pg.W, pg.me = self.push_dev.data_ptr(), len(self.layout), B, W, m.rank
+    gchan = 1 + len(self.stacks)
+    for r in range(W):
+      pg.dst[r] = self.buf.peer_ptr(r, self.grad_buf_off[par])
+      pg.flags[r] = self._flag_ptr(r, gchan, m.rank)
+    pg.done_counter, pg.seq = self.done_grads.data_ptr(), seq
+    _lib.check_rc(self.lib.recml_emb_push_grads(ctypes.byref(pg), st), "emb_push_grads")
+    saved["event"].synchronize()   # occurrence counts (recorded long ago, during forward)
+    for si, info in enumerate(self.stacks):
+      n = int(info["count_host"][0])
+      if n > info["occ_cap"]:
+        raise _lib.DeviceStatusError(f"occurrence list overflow: {n} > {info['occ_cap']}")
+      opt = m.plan.stacks[si].optimizer
+      if n > 0:
+        _lib.check_rc(self.lib.recml_sort_pairs_u32(
+            _lib.ptr(info["keys"][0]), _lib.ptr(info["keys"][1]), _lib.ptr(info["vals"][0]),
+            _lib.ptr(info["vals"][1]), c_ll(n), c_int(info["end_bit"]), _lib.ptr(info["sort_temp"]),
+            c_ll(info["sort_temp"].numel()), st), "sort_pairs")
+      bp = BwdParams()
+      bp.keys, bp.vals = info["keys"][1].data_ptr(), info["vals"][1].data_ptr()
+      bp.occ_gain = info["gain"].data_ptr() if self.has_gains else None
+      bp.n_occ = info["count"].data_ptr()
+      bp.grads = self.buf.peer_ptr(m.rank, self.grad_buf_off[par])
+      bp.table = m.stack_weights[si].data_ptr()
+      names = opt.slot_names()
+      slots = m.stack_slots[si]
+      bp.slot0 = slots[names[0]].data_ptr() if len(names) > 0 else None
+      bp.slot1 = slots[names[1]].data_ptr() if len(names) > 1 else None
+      bp.dloc, bp.opt = m.plan.stacks[si].dim, OPT[opt.kind]
+      hp = opt.hyperparams(m.step_count)
+      for i in range(6):
+        bp.hp[i] = hp[i] if i < len(hp) else 0.0
+      bp.grad_scale = m.grad_scale
+      bp.scratch = info["scratch"].data_ptr()
+      bp.wait_flags = self._flag_ptr(m.rank, gchan, 0) if W > 1 else None
+      bp.W, bp.wait_seq, bp.status = W, seq, self.status.data_ptr()
+      if n > 0 or W > 1:
+        _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),
+                                                    st), "emb_bwd_update")

@@ -72,9 +72,13 @@ class _LookupFn(torch.autograd.Function):
   """Forward returns pooled activations; backward applies the table optimizer."""
 
   @staticmethod
-  def forward(ctx, anchor, module, kjt, training):
+  def forward(ctx, anchor, module, kjt, training, out, out_col):
     ctx.module = module
-    out, saved = module._backend.forward(kjt, training=training)
+    if out is not None:
+      res, saved = module._backend.forward(kjt, training=training, out=out, out_col=out_col)
+    else:
+      res, saved = module._backend.forward(kjt, training=training)
+    out = res
     ctx.saved = saved
     return out
 
@@ -83,7 +87,7 @@ class _LookupFn(torch.autograd.Function):
     if ctx.saved is not None:
       ctx.module._backend.backward(ctx.saved, grad_out)
       ctx.module.step_count += 1
-    return torch.zeros_like(ctx.module.anchor), None, None, None
+    return torch.zeros_like(ctx.module.anchor), None, None, None, None, None
 
 
 class ShardedEmbedding(nn.Module):
@@ -145,6 +149,10 @@ class ShardedEmbedding(nn.Module):
     self.anchor = nn.Parameter(torch.zeros((), device=self.device))
     self.anchor._recml_sharded = True
     self.step_count = 0
+    # Activation gradients arrive from `world` data-parallel ranks; like dense gradients they are
+    # averaged (each rank scales its loss by 1/local_batch), so the summed row gradient is divided
+    # by the world size before the row optimizer sees it.
+    self.grad_scale = 1.0 / self.world
     self.reset_parameters()
     self._backend = self._make_backend(config.backend)
 
@@ -204,7 +212,7 @@ class ShardedEmbedding(nn.Module):
     the same D, else a dict feature → `[B, D]` / `[B, L, D]`."""
     if tuple(kjt.keys) != self.feature_names:
       raise ValueError(f"Expected features {self.feature_names}, got {kjt.keys}")
-    out = _LookupFn.apply(self.anchor, self, kjt, torch.is_grad_enabled() and self.training)
+    out = _LookupFn.apply(self.anchor, self, kjt, torch.is_grad_enabled() and self.training, None, 0)
     from recml_b200.embedding import collective
     layout, _ = collective.feature_layout(self)
     has_rep = len(layout) != len(self.feature_names)

@@ -1,0 +1,150 @@
+"""DLRM-DCNv2 experiment: task, synthetic Criteo-shaped data and `experiment()` configs.
+
+Counterpart of `recml/examples/dlrm_experiment.py:238-405` (prediction task with BCE loss and the
+metrics loss / accuracy / auc (PR) / aucroc / label mean / prediction mean / batch size) using this
+framework's trainer, partitioners and sharded embeddings.  `tiny_experiment()` is the CPU
+configuration (8 tables × 1000 × 16, bottom 13-64-16, two full-rank cross layers on the 144-d
+concat, top 64-1, batch 256, Adagrad 0.01); `experiment()` is the full Criteo-1TB geometry.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Mapping, Sequence
+
+import torch
+import torch.distributed as dist
+
+from recml_b200 import config as cfg_lib
+from recml_b200 import embedding as emb
+from recml_b200 import metrics as M
+from recml_b200.data import iterator as iterator_lib
+from recml_b200.data import synthetic
+from recml_b200.models import dlrm
+from recml_b200.ops import bce
+from recml_b200.training import core, optim_factory, partitioning, state as state_lib, task as task_lib
+from recml_b200.training import trainer as trainer_lib
+from recml_b200.utils import types
+
+
+@dataclasses.dataclass
+class ModelConfig:
+  vocab_sizes: Sequence[int] = synthetic.CRITEO_VOCAB_SIZES
+  bag_sizes: Sequence[int] = synthetic.CRITEO_MULTI_HOT_SIZES
+  embedding_dim: int = 128
+  num_dense: int = 13
+  bottom_mlp_dims: Sequence[int] = (512, 256, 128)
+  top_mlp_dims: Sequence[int] = (1024, 1024, 512, 256, 1)
+  num_cross_layers: int = 3
+  cross_rank: int | None = 512
+  embedding_learning_rate: float = 0.01
+  embedding_init_scale: float | None = None
+  row_wise_min_bytes: int = 256 << 20
+  backend: str = "auto"
+
+
+class CriteoFactory(types.Factory[Any]):
+  """Synthetic Criteo-shaped batches (Zipf ids, log-normal dense, Bernoulli(0.25) labels)."""
+  model: ModelConfig
+  batch_size: int            # per process
+  num_batches: int = 4
+  steps: int | None = None
+  seed: int = 0
+  alpha: float = 1.05
+
+  def make(self):
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    ds = synthetic.SyntheticDLRMDataset(
+        self.batch_size, self.model.vocab_sizes, self.model.bag_sizes, num_batches=self.num_batches,
+        seed=self.seed, rank=rank, alpha=self.alpha, steps=self.steps, num_dense=self.model.num_dense,
+        pin=torch.cuda.is_available())
+    return iterator_lib.IterableIterator(ds)
+
+
+class PredictionTask(task_lib.Task):
+  def __init__(self, model: ModelConfig, train_data: CriteoFactory, eval_data: CriteoFactory | None,
+               optimizer: types.Factory, group=None):
+    self.cfg, self.train_data, self.eval_data, self.optimizer = model, train_data, eval_data, optimizer
+    self.group = group
+
+  def create_datasets(self):
+    train = self.train_data.make()
+    return train if self.eval_data is None else (train, self.eval_data.make())
+
+  def create_state(self, batch, rng) -> state_lib.State:
+    c = self.cfg
+    device = batch["dense"].device
+    torch.manual_seed(rng.initial_seed())
+    model = dlrm.DLRMDCNv2(
+        vocab_sizes=c.vocab_sizes, embedding_dim=c.embedding_dim, num_dense=c.num_dense,
+        bottom_mlp_dims=c.bottom_mlp_dims, top_mlp_dims=c.top_mlp_dims,
+        num_cross_layers=c.num_cross_layers, cross_rank=c.cross_rank, bag_sizes=c.bag_sizes,
+        embedding_optimizer=emb.RowWiseAdagradOptimizerSpec(learning_rate=c.embedding_learning_rate),
+        device=device, group=self.group, row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend,
+        init_scale=c.embedding_init_scale, seed=rng.initial_seed())
+    return state_lib.State.create(model=model, tx=self.optimizer.make())
+
+  def _metrics(self, r: bce.BCEResult, n: int) -> Mapping[str, M.Metric]:
+    out = {
+        "loss": M.Mean(total=r.loss_sum, count=r.weight_sum),
+        "accuracy": M.Mean(total=r.correct_sum, count=r.weight_sum),
+        "label/mean": M.Mean(total=r.label_sum, count=r.weight_sum),
+        "prediction/mean": M.Mean(total=r.pred_sum, count=r.weight_sum),
+        "common/batch_size": M.scalar(float(n)),
+    }
+    if r.hist_pos is not None:
+      out["auc"] = M.AUCPR.from_histograms(r.hist_pos, r.hist_neg)
+      out["aucroc"] = M.AUCROC.from_histograms(r.hist_pos, r.hist_neg)
+    return out
+
+  def train_step(self, batch, state, rng):
+    state.model.train()
+    logits = state.model(batch["dense"], batch["sparse"])
+    n = logits.numel()
+    r = bce.bce_with_logits(logits.detach(), batch["label"], grad_scale=1.0 / n)
+    logits.backward(r.dlogits.to(logits.dtype))
+    state.update()
+    return state, self._metrics(r, n)
+
+  def eval_step(self, batch, state):
+    state.model.eval()
+    logits = state.model(batch["dense"], batch["sparse"])
+    return self._metrics(bce.bce_with_logits(logits, batch["label"]), logits.numel())
+
+
+def features_summary(c: ModelConfig) -> str:
+  return f"{len(c.vocab_sizes)} tables, {sum(c.bag_sizes)} ids/sample, dim {c.embedding_dim}"
+
+
+def experiment(global_batch: int = 65536, train_steps: int = 1000, model_dir: str = "/tmp/dlrm") -> cfg_lib.Config:
+  """Full Criteo-1TB geometry (bottom 512-256-128, 3 low-rank-512 cross layers, top
+  1024-1024-512-256-1; the reference's `experiment()` uses batch 131 072 and Adagrad 0.01)."""
+  world = dist.get_world_size() if dist.is_initialized() else 1
+  model = cfg_lib.Config(ModelConfig)
+  return cfg_lib.Config(
+      core.Experiment,
+      task=cfg_lib.Config(
+          PredictionTask, model=model,
+          train_data=cfg_lib.Config(CriteoFactory, model=model, batch_size=global_batch // world),
+          eval_data=cfg_lib.Config(CriteoFactory, model=model, batch_size=global_batch // world, steps=8, seed=1),
+          optimizer=cfg_lib.Config(optim_factory.AdamFactory, learning_rate=1e-3)),
+      trainer=cfg_lib.Config(trainer_lib.Trainer, partitioner=cfg_lib.Config(partitioning.DataParallelPartitioner),
+                             model_dir=model_dir, train_steps=train_steps, steps_per_loop=100, steps_per_eval=8))
+
+
+def tiny_experiment(model_dir: str = "/tmp/dlrm_tiny", train_steps: int = 100, batch_size: int = 256,
+                    ) -> cfg_lib.Config:
+  model = cfg_lib.Config(
+      ModelConfig, vocab_sizes=(1000,) * 8, bag_sizes=(1,) * 8, embedding_dim=16, bottom_mlp_dims=(64, 16),
+      top_mlp_dims=(64, 1), num_cross_layers=2, cross_rank=None, embedding_learning_rate=0.01,
+      embedding_init_scale=0.01)
+  world = dist.get_world_size() if dist.is_initialized() else 1
+  return cfg_lib.Config(
+      core.Experiment,
+      task=cfg_lib.Config(
+          PredictionTask, model=model,
+          train_data=cfg_lib.Config(CriteoFactory, model=model, batch_size=batch_size // world, num_batches=8),
+          eval_data=cfg_lib.Config(CriteoFactory, model=model, batch_size=batch_size // world, steps=4, seed=1),
+          optimizer=cfg_lib.Config(optim_factory.AdagradFactory, learning_rate=0.01)),
+      trainer=cfg_lib.Config(trainer_lib.Trainer,
+                             partitioner=cfg_lib.Config(partitioning.DataParallelPartitioner),
+                             model_dir=model_dir, train_steps=train_steps, steps_per_loop=50, steps_per_eval=4))

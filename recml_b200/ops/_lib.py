@@ -19,12 +19,39 @@ class NativeError(RuntimeError):
   pass
 
 
+# Number of this library's kernels launched so far (benchmarks reset and read it).  Each launcher
+# call counts the kernels it launches; CUB's sort kernels are library code and count as zero.
+LAUNCHES = {"count": 0}
+_KERNELS_PER_CALL = {"recml_emb_bwd_update": 2, "recml_sort_pairs_u32": 0, "recml_sort_temp_bytes": 0,
+                     "recml_emb_struct_sizes": 0, "recml_optim_struct_sizes": 0}
+
+
+class _CountingLib:
+  def __init__(self, lib: ctypes.CDLL):
+    self._lib = lib
+    self._fns: dict[str, Any] = {}
+
+  def __getattr__(self, name: str):
+    fn = self._fns.get(name)
+    if fn is None:
+      raw = getattr(self._lib, name)
+      n = _KERNELS_PER_CALL.get(name, 1)
+      if name == "recml_sort_temp_bytes":
+        raw.restype = ctypes.c_longlong
+
+      def fn(*args, _raw=raw, _n=n):
+        LAUNCHES["count"] += _n
+        return _raw(*args)
+      self._fns[name] = fn
+    return fn
+
+
 @functools.lru_cache(maxsize=None)
-def cuda() -> ctypes.CDLL:
+def cuda() -> "_CountingLib":
   libs = _build.build()
   if "cuda" not in libs:
     raise NativeError("librecml_cuda.so could not be built (no CUDA sources / nvcc).")
-  return ctypes.CDLL(libs["cuda"])
+  return _CountingLib(ctypes.CDLL(libs["cuda"]))
 
 
 @functools.lru_cache(maxsize=None)

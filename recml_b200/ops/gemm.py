@@ -13,7 +13,7 @@ import torch
 
 from recml_b200.ops import _lib
 
-EPI_LINEAR, EPI_CROSS, EPI_MASK_RELU, EPI_MUL_ADD = 0, 1, 2, 3
+EPI_LINEAR, EPI_CROSS, EPI_MASK_RELU, EPI_MUL_ADD, EPI_ADD = 0, 1, 2, 3, 4
 
 
 def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, relu=False, epi=EPI_LINEAR,
@@ -33,6 +33,8 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, relu=False, epi=E
     x = aux0.to(torch.float32) * x + aux1.to(torch.float32)
   elif epi == EPI_MASK_RELU:
     x = torch.where(aux0 > 0, x, torch.zeros_like(x))
+  elif epi == EPI_ADD:
+    x = x + aux0.to(torch.float32)
   elif epi == EPI_MUL_ADD:
     x = x * aux0.to(torch.float32)
     if aux1 is not None:

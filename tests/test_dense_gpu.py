@@ -1,0 +1,116 @@
+"""MLP / DCNv2 autograd nodes and the memory-bound helpers on CUDA vs fp32 torch on CPU."""
+import pytest
+import torch
+
+from recml_b200.metrics import confusion
+from recml_b200.ops import _lib, bce, dense, elementwise as ew
+from recml_b200.training import optim_factory
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol=3e-2):
+  a, b = a.float().cpu(), b.float().cpu()
+  err = (a - b).abs().max().item()
+  scale = b.abs().max().item() + 1e-6
+  assert err / scale < tol, f"rel err {err / scale}"
+
+
+def test_mlp_forward_backward():
+  torch.manual_seed(0)
+  M, dims = 300, [13, 512, 256, 128]
+  ws = [torch.randn(dims[i + 1], dims[i]) * (1.0 / dims[i]) ** 0.5 for i in range(3)]
+  bs = [torch.randn(dims[i + 1]) * 0.1 for i in range(3)]
+  x = torch.randn(M, 13)
+  flags = [True, True, True]
+  pc = [t.clone().requires_grad_() for t in ws + bs]
+  pg = [t.clone().cuda().requires_grad_() for t in ws + bs]
+  yc = dense.mlp(x, pc[:3], pc[3:], flags)
+  yg = dense.mlp(x.cuda(), pg[:3], pg[3:], flags)
+  _close(yg, yc)
+  go = torch.randn_like(yc)
+  yc.backward(go)
+  yg.backward(go.cuda().to(yg.dtype))
+  torch.cuda.synchronize()
+  _lib.check_status()
+  for a, b in zip(pg, pc):
+    _close(a.grad, b.grad)
+
+
+def test_top_mlp_with_gemv_head():
+  torch.manual_seed(1)
+  M, dims = 260, [384, 256, 64, 1]
+  ws = [torch.randn(dims[i + 1], dims[i]) * (1.0 / dims[i]) ** 0.5 for i in range(3)]
+  bs = [torch.randn(dims[i + 1]) * 0.1 for i in range(3)]
+  x = (torch.randn(M, 384)).to(torch.bfloat16)
+  flags = [True, True, False]
+  pc = [t.clone().requires_grad_() for t in ws + bs]
+  pg = [t.clone().cuda().requires_grad_() for t in ws + bs]
+  xc, xg = x.float().requires_grad_(), x.cuda().requires_grad_()
+  yc, yg = dense.mlp(xc, pc[:3], pc[3:], flags), dense.mlp(xg, pg[:3], pg[3:], flags)
+  _close(yg, yc)
+  go = torch.randn_like(yc)
+  yc.backward(go)
+  yg.backward(go.cuda())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  for a, b in zip(pg + [xg], pc + [xc]):
+    _close(a.grad, b.grad)
+
+
+@pytest.mark.parametrize("rank", [64, None])
+def test_cross_network(rank):
+  torch.manual_seed(2)
+  M, d, L = 200, 384, 3
+  x0 = (torch.randn(M, d) * 0.5).to(torch.bfloat16)
+  us = [torch.randn(rank, d) * 0.05 for _ in range(L)] if rank else None
+  vs = [torch.randn(d, rank or d) * 0.05 for _ in range(L)]
+  bs = [torch.randn(d) * 0.1 for _ in range(L)]
+  def leaves(dev):
+    mk = lambda t: t.clone().to(dev).requires_grad_()
+    return ([mk(t) for t in us] if us else None), [mk(t) for t in vs], [mk(t) for t in bs]
+  uc, vc, bc = leaves("cpu")
+  ug, vg, bg = leaves("cuda")
+  xc, xg = x0.float().requires_grad_(), x0.cuda().requires_grad_()
+  yc, yg = dense.cross_network(xc, uc, vc, bc), dense.cross_network(xg, ug, vg, bg)
+  _close(yg, yc)
+  go = (torch.randn_like(yc) * 0.1)
+  yc.backward(go)
+  yg.backward(go.cuda().to(yg.dtype))
+  torch.cuda.synchronize()
+  _lib.check_status()
+  for a, b in zip((ug or []) + vg + bg + [xg], (uc or []) + vc + bc + [xc]):
+    _close(a.grad, b.grad, tol=5e-2)
+
+
+def test_bce_fused_matches_reference():
+  torch.manual_seed(3)
+  n = 10000
+  x, y = torch.randn(n) * 2, (torch.rand(n) < 0.25).float()
+  rc = bce.bce_with_logits(x, y, grad_scale=1.0 / n)
+  rg = bce.bce_with_logits(x.cuda(), y.cuda(), grad_scale=1.0 / n)
+  for f in ("loss_sum", "weight_sum", "label_sum", "pred_sum", "correct_sum", "dlogits", "hist_pos", "hist_neg"):
+    torch.testing.assert_close(getattr(rg, f).cpu(), getattr(rc, f), atol=1e-2, rtol=1e-4)
+  # histograms reproduce the thresholded confusion counts of the metric library exactly
+  tp, tn, fp, fn = confusion.estimate_confusion_matrix(torch.sigmoid(x), y, None, confusion.default_thresholds(200))
+  tp2, tn2, fp2, fn2 = confusion.confusion_from_histograms(rg.hist_pos.cpu(), rg.hist_neg.cpu())
+  torch.testing.assert_close(tp2, tp); torch.testing.assert_close(fp2, fp)
+
+
+@pytest.mark.parametrize("factory", [
+    optim_factory.AdamFactory(learning_rate=1e-2, weight_decay=1e-2, grad_clip_norm=1.0),
+    optim_factory.AdagradFactory(learning_rate=1e-2, grad_clip_norm=0.5),
+    optim_factory.SGDFactory(learning_rate=1e-2)], ids=["adamw", "adagrad", "sgd"])
+def test_fused_optimizer_matches_cpu(factory):
+  torch.manual_seed(4)
+  shapes = [(300, 70), (70,), (1, 9), (2049,)]
+  pc = {f"p{i}": torch.randn(s).requires_grad_() for i, s in enumerate(shapes)}
+  pg = {k: v.detach().clone().cuda().requires_grad_() for k, v in pc.items()}
+  oc, og = factory.make().init(pc), factory.make().init(pg)
+  for _ in range(4):
+    for k in pc:
+      g = torch.randn_like(pc[k])
+      pc[k].grad, pg[k].grad = g, g.cuda()
+    oc.step(); og.step()
+  for k in pc:
+    torch.testing.assert_close(pg[k].detach().cpu(), pc[k].detach(), atol=1e-5, rtol=1e-4)

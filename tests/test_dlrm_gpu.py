@@ -1,0 +1,38 @@
+"""Small DLRM-DCNv2 on one GPU: training reduces the loss and tracks the CPU run."""
+import pytest
+import torch
+
+from recml_b200.examples import dlrm_experiment as D
+from recml_b200.ops import _lib
+from recml_b200.training import optim_factory, partitioning
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(device, steps=30):
+  cfg = D.ModelConfig(vocab_sizes=(2000, 300, 17, 4096), bag_sizes=(3, 1, 2, 20), embedding_dim=128,
+                      bottom_mlp_dims=(64, 128), top_mlp_dims=(256, 64, 1), num_cross_layers=2, cross_rank=64,
+                      embedding_learning_rate=0.05, embedding_init_scale=0.05)
+  task = D.PredictionTask(cfg, D.CriteoFactory(model=cfg, batch_size=512, num_batches=2), None,
+                          optim_factory.AdamFactory(learning_rate=2e-3))
+  part = partitioning.NullPartitioner(device)
+  it = task.create_datasets()
+  batch = part.shard_inputs(next(it))
+  it.reset()
+  state = task.create_state(batch, torch.Generator().manual_seed(0))
+  rng = torch.Generator(device=device)
+  losses = []
+  for _ in range(steps):
+    state, m = task.train_step(part.shard_inputs(next(it)), state, rng)
+    losses.append(float(m["loss"].localize().compute()))
+  return losses
+
+
+def test_dlrm_trains_on_gpu():
+  lg = _run("cuda")
+  torch.cuda.synchronize()
+  _lib.check_status()
+  assert lg[-1] < lg[0] - 0.05, lg
+  lc = _run("cpu")
+  assert abs(lg[0] - lc[0]) < 0.05 and abs(lg[-1] - lc[-1]) < 0.1, (lg[::5], lc[::5])
+  assert _lib.LAUNCHES["count"] > 0
