@@ -82,7 +82,7 @@ class NullPartitioner(Partitioner):
     self._stager = _PinnedStager()
 
   def _put(self, x):
-    if hasattr(x, "to_device"):
+    if hasattr(x, "to_device") and not isinstance(x, (np.ndarray, torch.Tensor)):
       return x.to_device(self.device, self._stager if self.device.type == "cuda" else None)
     if isinstance(x, np.ndarray):
       x = torch.from_numpy(np.ascontiguousarray(x))

@@ -16,6 +16,27 @@ def _close(a, b, tol=3e-2):
   assert err / scale < tol, f"rel err {err / scale}"
 
 
+def _ref_mlp_bf16(x, ws, bs, flags, go):
+  """fp32 math on bf16-rounded operands and activations (what the kernels see), with the ReLU masks
+  taken from the rounded activations; returns output, weight grads, bias grads, input grad."""
+  r = lambda t: t.to(torch.bfloat16).float()
+  acts = [r(x)]
+  for w, b, f in zip(ws, bs, flags):
+    z = acts[-1] @ r(w).t() + b
+    z = torch.relu(z) if f else z
+    acts.append(r(z) if w.shape[0] > 1 else z)
+  g = go.float() if ws[-1].shape[0] == 1 else r(go)
+  dws, dbs = [], []
+  for i in range(len(ws) - 1, -1, -1):
+    if flags[i]:
+      g = g * (acts[i + 1] > 0)
+    dws.insert(0, g.t() @ acts[i])
+    dbs.insert(0, g.sum(0))
+    g = g @ (ws[i] if ws[i].shape[0] == 1 else r(ws[i]))
+    g = r(g)
+  return acts[-1], dws, dbs, g
+
+
 def test_mlp_forward_backward():
   torch.manual_seed(0)
   M, dims = 300, [13, 512, 256, 128]
@@ -23,18 +44,18 @@ def test_mlp_forward_backward():
   bs = [torch.randn(dims[i + 1]) * 0.1 for i in range(3)]
   x = torch.randn(M, 13)
   flags = [True, True, True]
-  pc = [t.clone().requires_grad_() for t in ws + bs]
+  go = torch.randn(M, dims[-1])
+  yr, dws, dbs, _ = _ref_mlp_bf16(x, ws, bs, flags, go)
   pg = [t.clone().cuda().requires_grad_() for t in ws + bs]
-  yc = dense.mlp(x, pc[:3], pc[3:], flags)
   yg = dense.mlp(x.cuda(), pg[:3], pg[3:], flags)
-  _close(yg, yc)
-  go = torch.randn_like(yc)
-  yc.backward(go)
+  _close(yg, yr, tol=1e-2)
   yg.backward(go.cuda().to(yg.dtype))
   torch.cuda.synchronize()
   _lib.check_status()
-  for a, b in zip(pg, pc):
-    _close(a.grad, b.grad)
+  for a, b in zip(pg, dws + dbs):
+    _close(a.grad, b, tol=2e-2)
+  # and the fp32 CPU path of the same function agrees in the forward direction
+  _close(yg, dense.mlp(x, ws, bs, flags), tol=2e-2)
 
 
 def test_top_mlp_with_gemv_head():
@@ -44,18 +65,17 @@ def test_top_mlp_with_gemv_head():
   bs = [torch.randn(dims[i + 1]) * 0.1 for i in range(3)]
   x = (torch.randn(M, 384)).to(torch.bfloat16)
   flags = [True, True, False]
-  pc = [t.clone().requires_grad_() for t in ws + bs]
+  go = torch.randn(M, 1)
+  yr, dws, dbs, dxr = _ref_mlp_bf16(x.float(), ws, bs, flags, go)
   pg = [t.clone().cuda().requires_grad_() for t in ws + bs]
-  xc, xg = x.float().requires_grad_(), x.cuda().requires_grad_()
-  yc, yg = dense.mlp(xc, pc[:3], pc[3:], flags), dense.mlp(xg, pg[:3], pg[3:], flags)
-  _close(yg, yc)
-  go = torch.randn_like(yc)
-  yc.backward(go)
+  xg = x.cuda().requires_grad_()
+  yg = dense.mlp(xg, pg[:3], pg[3:], flags)
+  _close(yg, yr, tol=1e-2)
   yg.backward(go.cuda())
   torch.cuda.synchronize()
   _lib.check_status()
-  for a, b in zip(pg + [xg], pc + [xc]):
-    _close(a.grad, b.grad)
+  for a, b in zip(pg + [xg], dws + dbs + [dxr]):
+    _close(a.grad, b.reshape(a.grad.shape), tol=2e-2)
 
 
 @pytest.mark.parametrize("rank", [64, None])
