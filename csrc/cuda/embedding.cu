@@ -40,7 +40,7 @@ struct FeatDesc {      // one sharded feature as seen by the rank running the ke
   long long slot_off;  // element offset of the feature's block in a destination pooled buffer
   long long grad_off;  // element offset of the feature's block in THIS rank's gradient buffer
   int seq_len;         // >0: sequence feature (no pooling), positions beyond seq_len dropped
-  int pad;
+  int dst_stride;      // elements between consecutive samples of this feature in the destination
 };
 
 struct IdPtrs {        // jagged ids of every source rank, in this rank's memory
@@ -135,7 +135,8 @@ __device__ __forceinline__ void grid_done_then_signal(unsigned int* done_counter
     if (prev == gridDim.x - 1) {
       *done_counter = 0;
       __threadfence_system();
-      for (int r = 0; r < W; ++r) st_release_sys(flags.p[r], seq);
+      for (int r = 0; r < W; ++r)
+        if (flags.p[r] != nullptr) st_release_sys(flags.p[r], seq);
     }
   }
 }
@@ -189,6 +190,8 @@ struct FwdParams {
   const float* table;
   PeerBf16 pooled;          // destination buffers (one per source rank of the ids)
   uint32_t* occ_key; uint32_t* occ_val; float* occ_gain; unsigned int* occ_count; unsigned int occ_cap;
+  long long grad_ld;        // >0: gradients will be read in place from a [B, grad_ld] matrix (1 rank):
+                            //     occurrence value = (b*grad_ld + grad_off)/8 instead of a buffer row
   const unsigned long long* wait_flags; unsigned long long wait_seq;   // ids channel (null: no wait)
   unsigned int* done_counter; PeerFlags flags; unsigned long long seq;  // pooled channel
   int* status;
@@ -222,7 +225,10 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
       if (f.combiner == kSqrtN) den = sqrtf(den);
       scale = den != 0.f ? 1.f / den : 0.f;
     }
-    const long long gv_base = f.grad_off / p.dloc + (static_cast<long long>(s) * p.B + b) * (f.seq_len > 0 ? f.seq_len : 1);
+    const long long gv_base = p.grad_ld > 0
+        ? (static_cast<long long>(b) * p.grad_ld + f.grad_off) / 8
+        : f.grad_off / p.dloc + (static_cast<long long>(s) * p.B + b) * (f.seq_len > 0 ? f.seq_len : 1);
+    const int gv_step = p.grad_ld > 0 ? f.dim / 8 : 1;   // per sequence position
     Vec<VPL> acc;
 #pragma unroll
     for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
@@ -255,7 +261,7 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
           if (owned) {
             const unsigned int at = pos + __popc(mask & ((1u << lane) - 1));
             p.occ_key[at] = lrow;
-            const unsigned int gv = static_cast<unsigned int>(gv_base + (f.seq_len > 0 ? i - o0 : 0));
+            const unsigned int gv = static_cast<unsigned int>(gv_base + (f.seq_len > 0 ? (i - o0) * gv_step : 0));
             if (GAINS) {
               p.occ_val[at] = at;                       // index into (occ_gv = occ_key slot of vals, gain)
               p.occ_gain[2 * static_cast<size_t>(at)] = __uint_as_float(gv);
@@ -269,17 +275,24 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         }
       }
       if (f.seq_len > 0) {
-        // sequence feature: every position is its own output vector
-        while (mask) {
-          const int j = __ffs(mask) - 1;
-          mask &= mask - 1;
+        // sequence feature: every position of this 32-wide window is its own output vector; positions
+        // this rank does not own (or that lie beyond the bag) are written as zeros so the slot is
+        // fully defined
+        const int npos = min(32, f.seq_len - (base - o0));
+        for (int j = 0; j < npos; ++j) {
+          const bool own_j = (mask >> j) & 1u;
           const unsigned int rj = __shfl_sync(0xffffffffu, lrow, j);
           const float wj = __shfl_sync(0xffffffffu, w, j);
           if (lane_on) {
-            Vec<VPL> r = load_f32<VPL>(p.table + static_cast<size_t>(rj) * p.dloc + lane * VPL);
+            Vec<VPL> r;
 #pragma unroll
-            for (int e = 0; e < VPL; ++e) r.v[e] *= wj;
-            store_bf16<VPL>(dst_base + (slot_row * f.seq_len + (base - o0 + j)) * f.dim, r);
+            for (int e = 0; e < VPL; ++e) r.v[e] = 0.f;
+            if (own_j) {
+              r = load_f32<VPL>(p.table + static_cast<size_t>(rj) * p.dloc + lane * VPL);
+#pragma unroll
+              for (int e = 0; e < VPL; ++e) r.v[e] *= wj;
+            }
+            store_bf16<VPL>(dst_base + slot_row * f.dst_stride + static_cast<long long>(base - o0 + j) * f.dim, r);
           }
         }
         continue;
@@ -309,7 +322,19 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         }
       }
     }
-    if (f.seq_len == 0 && lane_on) store_bf16<VPL>(dst_base + slot_row * f.dim, acc);
+    if (f.seq_len > 0) {
+      if (lane_on) {
+        Vec<VPL> z;
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) z.v[e] = 0.f;
+        // the id loop covered positions [0, 32*ceil(len/32)) ∩ [0, seq_len)
+        const int covered = min(f.seq_len, ((o1 - o0 + 31) / 32) * 32);
+        for (int pos = covered; pos < f.seq_len; ++pos)
+          store_bf16<VPL>(dst_base + slot_row * f.dst_stride + static_cast<long long>(pos) * f.dim, z);
+      }
+    } else if (lane_on) {
+      store_bf16<VPL>(dst_base + slot_row * f.dst_stride, acc);
+    }
   }
   grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
 }
@@ -324,25 +349,30 @@ struct CombineParams {
 
 __global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p) {
   if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 1, p.n_chan)) return;
-  const int lane = threadIdx.x & 31;
-  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const long long total = static_cast<long long>(p.n_feats) * p.B;
-  for (long long item = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; item < total;
-       item += warps) {
-    const int fi = static_cast<int>(item % p.n_feats);
-    const long long b = item / p.n_feats;
+  // one thread per 16-byte chunk (8 bf16) of one (sample, feature) vector
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int fi = 0; fi < p.n_feats; ++fi) {
     const CombineDesc f = p.feats[fi];
     const int width = f.dim * (f.seq_len > 0 ? f.seq_len : 1);
-    const __nv_bfloat16* src = p.pooled + f.slot_off + b * width;
-    __nv_bfloat16* dst = p.out + b * p.ld_out + f.out_col;
+    const int chunks = width / 8;
+    const long long total = static_cast<long long>(p.B) * chunks;
     const long long slot_stride = static_cast<long long>(p.B) * width;
-    for (int e = lane * 2; e < width; e += 64) {
-      float x = 0.f, y = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+      const long long b = i / chunks;
+      const int e = static_cast<int>(i - b * chunks) * 8;
+      const __nv_bfloat16* src = p.pooled + f.slot_off + b * width + e;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       for (int sl = 0; sl < f.nslots; ++sl) {
-        const uint32_t t = *reinterpret_cast<const uint32_t*>(src + sl * slot_stride + e);
-        x += bf16_lo(t); y += bf16_hi(t);
+        const uint4 t = *reinterpret_cast<const uint4*>(src + sl * slot_stride);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[2 * j] += bf16_lo(w[j]); acc[2 * j + 1] += bf16_hi(w[j]); }
       }
-      *reinterpret_cast<uint32_t*>(dst + e) = pack_bf16(x, y);
+      *reinterpret_cast<uint4*>(p.out + b * p.ld_out + f.out_col + e) =
+          make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                     pack_bf16(acc[6], acc[7]));
     }
   }
 }
@@ -392,7 +422,8 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
 // =================================== backward: segmented reduce + row optimizer ====================
 struct BwdParams {
   const uint32_t* keys; const uint32_t* vals; const float* occ_gain; const unsigned int* n_occ;
-  const __nv_bfloat16* grads;   // [*, dloc] gradient vectors
+  const __nv_bfloat16* grads;   // gradient vectors: vector v starts at grads + v * val_scale elements
+  long long val_scale;
   float* table; float* slot0; float* slot1; int dloc;
   int opt; float hp[6]; float grad_scale; int slot1_rowwise;
   float* scratch;               // [n_chunks, dloc] partial sums of runs that cross chunk boundaries (kept zero)
@@ -571,7 +602,7 @@ __global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) 
       kj[u] = __shfl_sync(0xffffffffu, key, j);
       const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
       gj[u] = __shfl_sync(0xffffffffu, gain, j);
-      if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.dloc + lane * VPL);
+      if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -681,7 +712,7 @@ extern "C" int recml_emb_fwd(const FwdParams* p, int train, int gains, cudaStrea
 }
 
 extern "C" int recml_emb_combine(const CombineParams* p, cudaStream_t stream) {
-  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 8);
+  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B * 4, 148 * 8);
   emb_combine_kernel<<<blocks, 256, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

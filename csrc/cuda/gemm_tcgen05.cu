@@ -46,6 +46,8 @@ struct Params {
   int ldd;
   int out_f32;        // 1: D is fp32
   int accumulate;     // 1: D += result (fp32 output only)
+  int split_k;        // >1: the K loop is cut into split_k ranges handled by different CTAs; partial
+                      //     results are added to the fp32 output with atomics (output pre-zeroed)
   const float* bias;  // [N] or null
   int relu;
   int epi;
@@ -170,8 +172,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int split_k = p.split_k > 1 ? p.split_k : 1;
+  const int num_tiles = m_tiles * n_tiles * split_k;   // work units
+  const int k_blocks_total = (p.K + BK - 1) / BK;
+  const int kb_per = (k_blocks_total + split_k - 1) / split_k;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -197,8 +201,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abortp; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int tl = tile / split_k, ks = tile % split_k;
+        const int m0 = (tl / n_tiles) * BM, n0 = (tl % n_tiles) * BN;
+        const int kb0 = ks * kb_per, kb1 = min(k_blocks_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::kStages;
           if (!mbar_wait(empty_bar(s), ((it / C::kStages) & 1) ^ 1, abortp, p.status, 10)) break;
           mbar_expect_tx(full_bar(s), C::kStageA + C::kStageB);
@@ -236,7 +242,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int ks = tile % split_k;
+        const int kb0 = ks * kb_per, kb1 = min(k_blocks_total, kb0 + kb_per);
+        if (kb0 >= kb1) {           // empty K range (cannot happen for kb_per >= 1 splits that exist)
+          tc_commit(tfull_bar(acc));
+          continue;
+        }
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::kStages;
           if (!mbar_wait(full_bar(s), (it / C::kStages) & 1, abortp, p.status, 21)) { ok = false; break; }
           tc_fence_after();
@@ -245,7 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t adesc = make_desc(sa + k * a_step, a_lbo, 1024);
             const uint64_t bdesc = make_desc(sb + k * b_step, b_lbo, 1024);
-            tc_mma_bf16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
+            tc_mma_bf16(tmem_d, adesc, bdesc, idesc, ((kb - kb0) | k) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
@@ -258,7 +270,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      const int tl = tile / split_k;
+      const int m0 = (tl / n_tiles) * BM, n0 = (tl % n_tiles) * BN;
       const int acc = t & 1;
       if (!mbar_wait(tfull_bar(acc), (t >> 1) & 1, abortp, p.status, 30)) break;
       tc_fence_after();
@@ -340,6 +353,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (p.out_f32) {
             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.d) + off + v * 8);
             float4 o0 = make_float4(x[0], x[1], x[2], x[3]), o1 = make_float4(x[4], x[5], x[6], x[7]);
+            if (split_k > 1) {
+              atomicAdd(dst, o0);
+              atomicAdd(dst + 1, o1);
+              continue;
+            }
             if (p.accumulate) {
               const float4 c0 = dst[0], c1 = dst[1];
               o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
@@ -430,7 +448,7 @@ static int launch(const void* a, int lda, const void* b, int ldb, const Params& 
       return -3;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.split_k > 1 ? p.split_k : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -445,7 +463,7 @@ static int launch(const void* a, int lda, const void* b, int ldb, const Params& 
 extern "C" int recml_gemm_bf16(const void* a, int lda, int a_mn, const void* b, int ldb, int b_mn, void* d,
                                int ldd, int out_f32, int accumulate, int M, int N, int K, const float* bias,
                                int relu, int epi, const void* aux0, const void* aux1, int ldaux, void* out2,
-                               int* status, cudaStream_t stream) {
+                               int split_k, int* status, cudaStream_t stream) {
   using namespace recml::gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (ldd % 4) || (!out_f32 && (ldd % 8))) return -10;
@@ -456,6 +474,14 @@ extern "C" int recml_gemm_bf16(const void* a, int lda, int a_mn, const void* b, 
   p.bias = bias; p.relu = relu; p.epi = epi;
   p.aux0 = static_cast<const __nv_bfloat16*>(aux0); p.aux1 = static_cast<const __nv_bfloat16*>(aux1);
   p.ldaux = ldaux; p.out2 = static_cast<__nv_bfloat16*>(out2); p.status = status;
+  {
+    const int kb = (K + BK - 1) / BK;
+    if (split_k > kb) split_k = kb;
+    if (split_k > 1 && (!out_f32 || epi != kEpiLinear || bias != nullptr || relu)) return -13;
+    // every split must own at least one k-block
+    while (split_k > 1 && ((kb + split_k - 1) / split_k) * (split_k - 1) >= kb) --split_k;
+    p.split_k = split_k > 1 ? split_k : 1;
+  }
   const bool wide = N > 128;
   if (!a_mn && !b_mn) return wide ? launch<256, false, false>(a, lda, b, ldb, p, stream)
                                   : launch<128, false, false>(a, lda, b, ldb, p, stream);

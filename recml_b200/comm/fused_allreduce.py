@@ -1,0 +1,119 @@
+"""Gradient averaging with the fused NVLink all-reduce (`csrc/cuda/allreduce.cu`).
+
+Gradients are grouped into buckets of ≤64 tensors / `bucket_elems` elements.  Each bucket runs
+pack (fp32→bf16 into symmetric memory) → two-shot reduce over peer pointers with the 1/W scale
+fused → unpack, on a side stream that starts as soon as the main stream has produced the
+gradients, so the exchange overlaps whatever the main stream does next.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from recml_b200.comm import symm
+from recml_b200.ops import _lib
+
+MAXW, MAXT = 8, 64
+c_ll, c_vp = ctypes.c_longlong, ctypes.c_void_p
+
+
+class _Bucket(ctypes.Structure):
+  _fields_ = [("grad", c_vp * MAXT), ("numel", c_ll * MAXT), ("offset", c_ll * MAXT),
+              ("block_start", c_ll * (MAXT + 1)), ("n", ctypes.c_int)]
+
+
+class _Comm(ctypes.Structure):
+  _fields_ = [("inp", c_vp * MAXW), ("out", c_vp * MAXW), ("flag_a", c_vp * MAXW), ("flag_b", c_vp * MAXW),
+              ("my_flag_a", c_vp), ("my_flag_b", c_vp), ("done_counter", c_vp), ("W", ctypes.c_int),
+              ("me", ctypes.c_int), ("seq", ctypes.c_ulonglong), ("total", c_ll), ("scale", ctypes.c_float),
+              ("status", c_vp)]
+
+
+class FusedNvlinkReducer:
+  def __init__(self, group, device: torch.device, bucket_elems: int = 8 << 20, average: bool = True):
+    self.group, self.device = group, device
+    self.world = dist.get_world_size(group)
+    self.rank = dist.get_rank(group)
+    if self.world > MAXW:
+      raise ValueError(f"at most {MAXW} ranks per node")
+    self.lib = _lib.cuda()
+    sizes = (ctypes.c_int * 2)()
+    self.lib.recml_ar_struct_sizes(sizes)
+    assert sizes[0] == ctypes.sizeof(_Bucket) and sizes[1] == ctypes.sizeof(_Comm), list(sizes)
+    self.bucket_elems = bucket_elems
+    self.average = average
+    self.cap = 0
+    self.buf = None
+    self.seq = 0
+    self.done = torch.zeros(4, dtype=torch.int32, device=device)
+    self.side = torch.cuda.Stream(device=device)
+    self.status = _lib.status_buffer(device)
+
+  def _ensure(self, elems: int):
+    unit = 8 * self.world
+    elems = (elems + unit - 1) // unit * unit
+    if self.buf is not None and elems <= self.cap:
+      return
+    cap = torch.tensor([elems], device=self.device, dtype=torch.int64)
+    dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=self.group)
+    self.cap = int(cap.item())
+    cv = symm.Carver()
+    self.flag_off = cv.take(2 * MAXW * 8)
+    self.in_off = [cv.take(self.cap * 2) for _ in range(2)]
+    self.out_off = [cv.take(self.cap * 2) for _ in range(2)]
+    self.buf = symm.SymmBuffer(cv.off, self.group, self.device)
+    self.seq = 0
+
+  def average_grads(self, params: Sequence[torch.Tensor]) -> None:
+    grads = []
+    for p in params:
+      g = p.grad
+      if g.dtype != torch.float32 or not g.is_contiguous():
+        g = g.to(torch.float32).contiguous()
+        p.grad = g
+      grads.append(g)
+    # bucket assignment
+    buckets, cur, n = [], [], 0
+    for g in grads:
+      sz = (g.numel() + 7) // 8 * 8
+      if cur and (n + sz > self.bucket_elems or len(cur) == MAXT):
+        buckets.append((cur, n)); cur, n = [], 0
+      cur.append((g, n)); n += sz
+    if cur:
+      buckets.append((cur, n))
+    self._ensure(max(n for _, n in buckets))
+    main = torch.cuda.current_stream(self.device)
+    self.side.wait_stream(main)
+    with torch.cuda.stream(self.side):
+      for items, n in buckets:
+        self.seq += 1
+        par = self.seq & 1
+        unit = 8 * self.world
+        total = (n + unit - 1) // unit * unit
+        b = _Bucket()
+        blocks = 0
+        for i, (g, off) in enumerate(items):
+          b.grad[i], b.numel[i], b.offset[i] = g.data_ptr(), g.numel(), off
+          b.block_start[i] = blocks
+          blocks += (g.numel() + 2047) // 2048
+        b.block_start[len(items)] = blocks
+        b.n = len(items)
+        c = _Comm()
+        for r in range(self.world):
+          c.inp[r] = self.buf.peer_ptr(r, self.in_off[par])
+          c.out[r] = self.buf.peer_ptr(r, self.out_off[par])
+          c.flag_a[r] = self.buf.peer_ptr(r, self.flag_off + self.rank * 8)
+          c.flag_b[r] = self.buf.peer_ptr(r, self.flag_off + (MAXW + self.rank) * 8)
+        c.my_flag_a = self.buf.peer_ptr(self.rank, self.flag_off)
+        c.my_flag_b = self.buf.peer_ptr(self.rank, self.flag_off + MAXW * 8)
+        c.done_counter = self.done.data_ptr()
+        c.W, c.me, c.seq, c.total = self.world, self.rank, self.seq, total
+        c.scale = 1.0 / self.world if self.average else 1.0
+        c.status = self.status.data_ptr()
+        # zero the bucket tail so padding never carries stale values into the sum
+        _lib.check_rc(self.lib.recml_allreduce_bucket(ctypes.byref(b), ctypes.byref(c),
+                                                      ctypes.c_void_p(self.side.cuda_stream)), "allreduce_bucket")
+    main.wait_stream(self.side)

@@ -36,7 +36,7 @@ OPT = {"sgd": 0, "adagrad": 1, "rowwise_adagrad": 2, "adam": 3, "rowwise_adam": 
 class FeatDesc(ctypes.Structure):
   _fields_ = [("feat_index", c_int), ("kind", c_int), ("owner", c_int), ("rot", c_int), ("row_base", c_int),
               ("combiner", c_int), ("dim", c_int), ("col_lo", c_int), ("slot_off", c_ll), ("grad_off", c_ll),
-              ("seq_len", c_int), ("pad", c_int)]
+              ("seq_len", c_int), ("dst_stride", c_int)]
 
 
 class IdPtrs(ctypes.Structure):
@@ -46,7 +46,7 @@ class IdPtrs(ctypes.Structure):
 class FwdParams(ctypes.Structure):
   _fields_ = [("ids", IdPtrs), ("feats", c_vp), ("n_feats", c_int), ("W", c_int), ("me", c_int), ("B", c_int),
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
-              ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("wait_flags", c_vp),
+              ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
               ("wait_seq", ctypes.c_ulonglong), ("done_counter", c_vp), ("flags", c_vp * MAXW),
               ("seq", ctypes.c_ulonglong), ("status", c_vp)]
 
@@ -73,7 +73,7 @@ class PushGradParams(ctypes.Structure):
 
 
 class BwdParams(ctypes.Structure):
-  _fields_ = [("keys", c_vp), ("vals", c_vp), ("occ_gain", c_vp), ("n_occ", c_vp), ("grads", c_vp),
+  _fields_ = [("keys", c_vp), ("vals", c_vp), ("occ_gain", c_vp), ("n_occ", c_vp), ("grads", c_vp), ("val_scale", c_ll),
               ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
               ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
               ("wait_flags", c_vp), ("W", c_int), ("wait_seq", ctypes.c_ulonglong), ("status", c_vp)]
@@ -167,35 +167,23 @@ class FusedBackend:
         self.grad_off[r][fname] = grad_elems[r]
         grad_elems[r] += W * B * wl
     grad_cap = max(grad_elems)
-    # ---- carve one symmetric allocation ----
-    cv = symm.Carver()
-    n_chan = 2 + len(m.plan.stacks)
-    self.flag_off = cv.take(n_chan * MAXW * 8)
-    self.ids_off = [[(cv.take(nnz_cap * 4), cv.take(self.n_offsets * 4), cv.take(nnz_cap * 4))
-                     for _ in range(W)] for _ in range(2)] if W > 1 else None
-    self.pooled_off = [cv.take(pooled_elems * 2) for _ in range(2 if W > 1 else 1)]
-    self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
-    self.buf = symm.SymmBuffer(cv.off, m.group, dev)
     self.pooled_elems, self.grad_cap = pooled_elems, grad_cap
+    self.buf = None
     # ---- per-stack work lists and occurrence storage ----
+    self.slot_off = slot_off
+    self.direct_ok = all(d.nslots == 1 for d in self.combine_descs) and all(
+        m.plan.tables[m.feature_to_table[f]].dim % 8 == 0 for f, _, _, _ in self.layout)
     self.stacks = []
     for si, st in enumerate(m.plan.stacks):
-      feats, occ_cap = [], 0
+      names = []
       for fname, col, width, L in self.layout:
         tp = m.plan.tables[m.feature_to_table[fname]]
-        if tp.stack != si:
+        if tp.stack != si or (tp.placement is Placement.TABLE_WISE and tp.owner != m.rank):
           continue
-        if tp.placement is Placement.TABLE_WISE and tp.owner != m.rank:
-          continue
-        spec = m.config.specs[fname]
-        feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
-                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot_off[fname],
-                              self.grad_off[m.rank][fname], L, 0))
-      info: dict[str, Any] = {"n_feats": len(feats), "feats": _device_struct_array(feats, dev),
-                              "feat_names": [m.feature_names[f.feat_index] for f in feats]}
+        names.append(fname)
+      info: dict[str, Any] = {"n_feats": len(names), "feat_names": names, "descs": {}}
       info["count"] = torch.zeros(1, dtype=torch.int32, device=dev)
       info["done"] = torch.zeros(4, dtype=torch.int32, device=dev)
-      info["count_host"] = torch.zeros(1, dtype=torch.int32).pin_memory()
       self.stacks.append(info)
     self.combine_dev = _device_struct_array(self.combine_descs, dev)
     push = []
@@ -209,6 +197,47 @@ class FusedBackend:
     self.done_ids = torch.zeros(4, dtype=torch.int32, device=dev)
     self.done_grads = torch.zeros(4, dtype=torch.int32, device=dev)
     self._occ_ready = False
+    if W > 1 or not self.direct_ok:
+      self._alloc_symm()
+
+  def _alloc_symm(self):
+    """One symmetric allocation holding flags, id copies, pooled slots and gradient blocks (the
+    single-GPU direct path needs none of them, so it is only made when first required)."""
+    if self.buf is not None:
+      return
+    m, W = self.m, self.m.world
+    nnz_cap, pooled_elems, grad_cap = self.nnz_cap, self.pooled_elems, self.grad_cap
+    cv = symm.Carver()
+    n_chan = 2 + len(m.plan.stacks)
+    self.flag_off = cv.take(n_chan * MAXW * 8)
+    self.ids_off = [[(cv.take(nnz_cap * 4), cv.take(self.n_offsets * 4), cv.take(nnz_cap * 4))
+                     for _ in range(W)] for _ in range(2)] if W > 1 else None
+    self.pooled_off = [cv.take(pooled_elems * 2) for _ in range(2 if W > 1 else 1)]
+    self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
+    self.buf = symm.SymmBuffer(cv.off, m.group, m.device)
+
+  def _feat_descs(self, si: int, direct: tuple[int, int] | None) -> torch.Tensor:
+    """Device array of FeatDesc for stack `si`.  `direct=(ld, out_col)` makes the forward kernel
+    store straight into a `[B, ld]` output matrix (and read gradients from a matrix of the same
+    geometry); None uses the symmetric pooled / gradient buffers."""
+    info = self.stacks[si]
+    if direct not in info["descs"]:
+      m = self.m
+      feats = []
+      for fname, col, width, L in self.layout:
+        if fname not in info["feat_names"]:
+          continue
+        tp = m.plan.tables[m.feature_to_table[fname]]
+        spec = m.config.specs[fname]
+        if direct is not None:
+          ld, out_col = direct
+          slot, goff, stride = out_col + col, out_col + col, ld
+        else:
+          slot, goff, stride = self.slot_off[fname], self.grad_off[m.rank][fname], width
+        feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
+                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot, goff, L, stride))
+      info["descs"][direct] = _device_struct_array(feats, m.device)
+    return info["descs"][direct]
 
   def _ensure_occ(self, kjt):
     """Occurrence / sort / scratch storage (training only), sized from the batch."""
@@ -237,10 +266,12 @@ class FusedBackend:
       nbytes = int(self.lib.recml_sort_temp_bytes(c_ll(cap)))
       info["sort_temp"] = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
       rows = m.plan.stacks[si].rows
-      info["end_bit"] = max(1, int(rows - 1).bit_length()) if rows > 1 else 1
+      info["end_bit"] = 32   # padding keys are 0xFFFFFFFF, so all 32 bits take part in the sort
     self._occ_ready = True
 
   def _flag_ptr(self, rank: int, chan: int, src: int) -> int:
+    if self.buf is None:
+      return 0
     return self.buf.peer_ptr(rank, self.flag_off + (chan * MAXW + src) * 8)
 
   # -- forward ---------------------------------------------------------------------------------------------
@@ -262,6 +293,15 @@ class FusedBackend:
     st = _lib.stream()
     gains = self.has_gains
     B = self.B
+    if out is None:
+      out = torch.empty(B, self.width, dtype=torch.bfloat16, device=dev)
+      out_col = 0
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    direct = None
+    if self.direct_ok and W == 1 and out.stride(0) % 8 == 0 and out_col % 8 == 0 and out.data_ptr() % 16 == 0:
+      direct = (out.stride(0), out_col)
+    if direct is None:
+      self._alloc_symm()
     ids = IdPtrs()
     if W > 1:
       p = PushIdsParams()
@@ -289,13 +329,15 @@ class FusedBackend:
         info["count"].zero_()
       fp = FwdParams()
       fp.ids = ids
-      fp.feats, fp.n_feats = info["feats"].data_ptr(), info["n_feats"]
+      fp.feats, fp.n_feats = self._feat_descs(si, direct).data_ptr(), info["n_feats"]
       fp.W, fp.me, fp.B, fp.dloc = W, m.rank, B, m.plan.stacks[si].dim
       fp.table = m.stack_weights[si].data_ptr()
       for r in range(W):
-        fp.pooled[r] = self.buf.peer_ptr(r, self.pooled_off[par])
+        fp.pooled[r] = out.data_ptr() if direct is not None else self.buf.peer_ptr(r, self.pooled_off[par])
         fp.flags[r] = self._flag_ptr(r, 1 + si, m.rank)
+      fp.grad_ld = direct[0] if direct is not None else 0
       if training:
+        info["keys"][0].fill_(-1)    # 0xFFFFFFFF padding sorts behind every real row
         fp.occ_key, fp.occ_val = info["keys"][0].data_ptr(), info["vals"][0].data_ptr()
         fp.occ_gain = info["gain"].data_ptr() if gains else None
         fp.occ_count, fp.occ_cap = info["count"].data_ptr(), info["occ_cap"]
@@ -305,16 +347,11 @@ class FusedBackend:
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
                       "emb_fwd")
-      if training:
-        info["count_host"].copy_(info["count"], non_blocking=True)
-    ev = None
-    if training:
-      ev = torch.cuda.Event()
-      ev.record()
     odt = m.config.output_dtype or torch.bfloat16
-    if out is None:
-      out = torch.empty(B, self.width, dtype=torch.bfloat16, device=dev)
-      out_col = 0
+    if direct is not None:
+      res = out[:, out_col:out_col + self.width]
+      res = res if odt == torch.bfloat16 else res.to(odt)
+      return res, ({"seq": seq, "par": par, "kjt": kjt, "direct": direct} if training else None)
     cp = CombineParams()
     cp.pooled = self.buf.peer_ptr(m.rank, self.pooled_off[par])
     cp.feats, cp.n_feats, cp.B = self.combine_dev.data_ptr(), len(self.combine_descs), B
@@ -323,8 +360,9 @@ class FusedBackend:
     cp.wait_flags = self._flag_ptr(m.rank, 1, 0) if W > 1 else None
     cp.W, cp.n_chan, cp.wait_seq, cp.status = W, len(self.stacks), seq, self.status.data_ptr()
     _lib.check_rc(self.lib.recml_emb_combine(ctypes.byref(cp), st), "emb_combine")
-    res = out if odt == torch.bfloat16 else out.to(odt)
-    saved = {"seq": seq, "par": par, "event": ev, "kjt": kjt} if training else None
+    res = out[:, out_col:out_col + self.width]
+    res = res if odt == torch.bfloat16 else res.to(odt)
+    saved = {"seq": seq, "par": par, "kjt": kjt, "direct": None} if training else None
     return res, saved
 
   # -- backward ----------------------------------------------------------------------------------------------
@@ -338,20 +376,30 @@ class FusedBackend:
       grad_out = grad_out.to(torch.bfloat16)
     if grad_out.stride(-1) != 1:
       grad_out = grad_out.contiguous()
-    pg = PushGradParams()
-    pg.grad, pg.ld = grad_out.data_ptr(), grad_out.stride(0)
-    pg.feats, pg.n_feats, pg.B, pg.W, pg.me = self.push_dev.data_ptr(), len(self.layout), B, W, m.rank
+    direct = saved["direct"]
     gchan = 1 + len(self.stacks)
-    for r in range(W):
-      pg.dst[r] = self.buf.peer_ptr(r, self.grad_buf_off[par])
-      pg.flags[r] = self._flag_ptr(r, gchan, m.rank)
-    pg.done_counter, pg.seq = self.done_grads.data_ptr(), seq
-    _lib.check_rc(self.lib.recml_emb_push_grads(ctypes.byref(pg), st), "emb_push_grads")
-    saved["event"].synchronize()   # occurrence counts (recorded long ago, during forward)
+    if direct is not None:
+      ld, out_col = direct
+      base = grad_out.data_ptr() - out_col * 2
+      if grad_out.stride(0) != ld or base % 16:
+        full = torch.empty(B, ld, dtype=torch.bfloat16, device=grad_out.device)
+        full[:, out_col:out_col + self.width] = grad_out
+        base, saved["_keep"] = full.data_ptr(), full
+      grads_ptr, val_scale = base, 8
+    else:
+      pg = PushGradParams()
+      pg.grad, pg.ld = grad_out.data_ptr(), grad_out.stride(0)
+      pg.feats, pg.n_feats, pg.B, pg.W, pg.me = self.push_dev.data_ptr(), len(self.layout), B, W, m.rank
+      for r in range(W):
+        pg.dst[r] = self.buf.peer_ptr(r, self.grad_buf_off[par])
+        pg.flags[r] = self._flag_ptr(r, gchan, m.rank)
+      pg.done_counter, pg.seq = self.done_grads.data_ptr(), seq
+      _lib.check_rc(self.lib.recml_emb_push_grads(ctypes.byref(pg), st), "emb_push_grads")
+      grads_ptr, val_scale = self.buf.peer_ptr(m.rank, self.grad_buf_off[par]), None
     for si, info in enumerate(self.stacks):
-      n = int(info["count_host"][0])
-      if n > info["occ_cap"]:
-        raise _lib.DeviceStatusError(f"occurrence list overflow: {n} > {info['occ_cap']}")
+      # The occurrence count stays on the device: the whole (0xFFFFFFFF-padded) capacity is sorted and
+      # the update kernel reads the count itself, so backward never synchronises with the host.
+      n = info["occ_cap"]
       opt = m.plan.stacks[si].optimizer
       if n > 0:
         _lib.check_rc(self.lib.recml_sort_pairs_u32(
@@ -362,7 +410,8 @@ class FusedBackend:
       bp.keys, bp.vals = info["keys"][1].data_ptr(), info["vals"][1].data_ptr()
       bp.occ_gain = info["gain"].data_ptr() if self.has_gains else None
       bp.n_occ = info["count"].data_ptr()
-      bp.grads = self.buf.peer_ptr(m.rank, self.grad_buf_off[par])
+      bp.grads = grads_ptr
+      bp.val_scale = val_scale if val_scale is not None else m.plan.stacks[si].dim
       bp.table = m.stack_weights[si].data_ptr()
       names = opt.slot_names()
       slots = m.stack_slots[si]
@@ -374,7 +423,7 @@ class FusedBackend:
         bp.hp[i] = hp[i] if i < len(hp) else 0.0
       bp.grad_scale = m.grad_scale
       bp.scratch = info["scratch"].data_ptr()
-      bp.wait_flags = self._flag_ptr(m.rank, gchan, 0) if W > 1 else None
+      bp.wait_flags = self._flag_ptr(m.rank, gchan, 0) if (W > 1 and direct is None) else None
       bp.W, bp.wait_seq, bp.status = W, seq, self.status.data_ptr()
       if n > 0 or W > 1:
         _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),

@@ -206,13 +206,15 @@ class ShardedEmbedding(nn.Module):
     return collective.CollectiveBackend(self)
 
   # -- forward -------------------------------------------------------------------------------
-  def forward(self, kjt: jagged_lib.KeyedJagged, *, flat: bool = False) -> Any:
+  def forward(self, kjt: jagged_lib.KeyedJagged, *, flat: bool = False, out: torch.Tensor | None = None,
+              out_col: int = 0) -> Any:
     """`flat=True` returns the `[B, ΣD]` concatenation of the sharded features in feature
     order (what DLRM consumes); otherwise `[B, F, D]` when every feature is pooled with
     the same D, else a dict feature → `[B, D]` / `[B, L, D]`."""
     if tuple(kjt.keys) != self.feature_names:
       raise ValueError(f"Expected features {self.feature_names}, got {kjt.keys}")
-    out = _LookupFn.apply(self.anchor, self, kjt, torch.is_grad_enabled() and self.training, None, 0)
+    out = _LookupFn.apply(self.anchor, self, kjt, torch.is_grad_enabled() and self.training,
+                          out if flat else None, out_col)
     from recml_b200.embedding import collective
     layout, _ = collective.feature_layout(self)
     has_rep = len(layout) != len(self.feature_names)

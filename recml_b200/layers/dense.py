@@ -52,6 +52,6 @@ class MLP(nn.Module):
     n = len(dims) - 1
     self.relu_flags = [True] * (n - 1) + [bool(activate_last)]
 
-  def forward(self, x):
+  def forward(self, x, out=None):
     biases = list(self.biases) if self.biases is not None else [None] * len(self.weights)
-    return dense_ops.mlp(x, list(self.weights), biases, self.relu_flags)
+    return dense_ops.mlp(x, list(self.weights), biases, self.relu_flags, out=out)

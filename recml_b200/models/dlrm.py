@@ -51,8 +51,17 @@ class DLRMDCNv2(nn.Module):
       self.bottom.to(device); self.cross.to(device); self.top.to(device)
 
   def forward(self, dense_x: torch.Tensor, sparse: emb.KeyedJagged) -> torch.Tensor:
-    bottom = self.bottom(dense_x)
-    pooled = self.embedding(sparse, flat=True)
-    x0 = torch.cat([bottom.to(pooled.dtype), pooled], dim=1)
+    if dense_x.is_cuda:
+      # bottom MLP and embedding kernels write their halves of the concat in place
+      from recml_b200.ops import dense as dense_ops
+      k = self.bottom.dims[-1]
+      full = torch.empty(dense_x.shape[0], self.concat_dim, dtype=torch.bfloat16, device=dense_x.device)
+      bottom = self.bottom(dense_x, out=full[:, :k])
+      pooled = self.embedding(sparse, flat=True, out=full, out_col=k)
+      x0 = dense_ops.JoinColumnsFn.apply(bottom, pooled, full)
+    else:
+      bottom = self.bottom(dense_x)
+      pooled = self.embedding(sparse, flat=True)
+      x0 = torch.cat([bottom.to(pooled.dtype), pooled], dim=1)
     y = self.top(self.cross(x0))
     return y.reshape(-1).to(torch.float32)

@@ -46,7 +46,7 @@ class MLPFn(torch.autograd.Function):
   output unit runs as a fused GEMV and returns fp32 `[M]`... as `[M, 1]`."""
 
   @staticmethod
-  def forward(ctx, x, relu_flags, *params):
+  def forward(ctx, x, relu_flags, out, *params):
     n = len(relu_flags)
     weights, biases = params[:n], params[n:]
     k0 = weights[0].shape[1]
@@ -67,7 +67,8 @@ class MLPFn(torch.autograd.Function):
           wp[:, :w16.shape[1]] = w16
           w16 = wp
         w16s.append(w16)
-        h = G.gemm(h, w16, bias=None if b is None else b.detach(), relu=bool(relu_flags[i]))
+        h = G.gemm(h, w16, bias=None if b is None else b.detach(), relu=bool(relu_flags[i]),
+                   out=out if i == n - 1 else None)
       acts.append(h)
     ctx.relu_flags, ctx.acts, ctx.w16s = relu_flags, acts, w16s
     ctx.weights, ctx.biases = weights, biases
@@ -111,11 +112,12 @@ class MLPFn(torch.autograd.Function):
     dx = None
     if ctx.need_dx:
       dx = g[:, :ctx.x_shape[1]].to(ctx.x_dtype)
-    return (dx, None, *dws, *dbs)
+    return (dx, None, None, *dws, *dbs)
 
 
-def mlp(x: torch.Tensor, weights, biases, relu_flags) -> torch.Tensor:
-  """Functional MLP.  weights[i]: `[out, in]`; biases[i]: `[out]` or None."""
+def mlp(x: torch.Tensor, weights, biases, relu_flags, out: torch.Tensor | None = None) -> torch.Tensor:
+  """Functional MLP.  weights[i]: `[out, in]`; biases[i]: `[out]` or None.  `out` (CUDA only): a bf16
+  `[M, out_features]` view, possibly strided, that receives the last layer's result."""
   if not x.is_cuda:
     h = x.to(torch.float32)
     for w, b, r in zip(weights, biases, relu_flags):
@@ -123,7 +125,7 @@ def mlp(x: torch.Tensor, weights, biases, relu_flags) -> torch.Tensor:
       if r:
         h = torch.relu(h)
     return h
-  return MLPFn.apply(x, tuple(bool(r) for r in relu_flags), *weights, *biases)
+  return MLPFn.apply(x, tuple(bool(r) for r in relu_flags), out, *weights, *biases)
 
 
 class CrossNetFn(torch.autograd.Function):
@@ -190,6 +192,20 @@ def cross_network(x0: torch.Tensor, us, vs, bs) -> torch.Tensor:
     return xl
   params = (*us, *vs, *bs) if low_rank else (*vs, *bs)
   return CrossNetFn.apply(x0, len(vs), low_rank, *params)
+
+
+class JoinColumnsFn(torch.autograd.Function):
+  """Declares that `full[:, :k]` was produced by `left` and `full[:, k:]` by `right` (both already
+  written in place), so the concat costs no copy and its gradient is two views."""
+
+  @staticmethod
+  def forward(ctx, left, right, full):
+    ctx.k = left.shape[1]
+    return full.detach()
+
+  @staticmethod
+  def backward(ctx, g):
+    return g[:, :ctx.k], g[:, ctx.k:], None
 
 
 class LinearFn(torch.autograd.Function):

@@ -50,7 +50,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bias: torch.Tensor | None = None, relu: bool = False, epi: int = EPI_LINEAR,
          aux0: torch.Tensor | None = None, aux1: torch.Tensor | None = None,
          out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None,
-         accumulate_into: torch.Tensor | None = None, want_out2: bool = False):
+         accumulate_into: torch.Tensor | None = None, want_out2: bool = False, split_k: int = 0):
+  """`split_k=0` picks a K split automatically for fp32-output products whose tile count would
+  leave most SMs idle (weight gradients: few output tiles, very long K)."""
   if not a.is_cuda:
     return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, relu=relu, epi=epi, aux0=aux0,
                           aux1=aux1, out_dtype=out_dtype, accumulate_into=accumulate_into,
@@ -67,6 +69,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     d = out if out is not None else torch.empty(M, N, dtype=out_dtype, device=a.device)
     out_f32, acc = int(d.dtype == torch.float32), 0
   out2 = torch.empty(M, N, dtype=torch.bfloat16, device=a.device) if want_out2 else None
+  if split_k == 0:
+    split_k = 1
+    if out_f32 and epi == EPI_LINEAR and bias is None and not relu:
+      tiles = ((M + 127) // 128) * ((N + 255) // 256 if N > 128 else 1)
+      kb = (K + 63) // 64
+      if tiles < 148 and kb >= 32:
+        split_k = max(1, min(296 // tiles, kb // 16, 16))
+  if split_k > 1 and not acc:
+    d.zero_()
   ldaux = aux0.stride(0) if aux0 is not None else 0
   rc = _lib.cuda().recml_gemm_bf16(
       _lib.ptr(a), ctypes.c_int(a.stride(0)), ctypes.c_int(int(a_mn)),
@@ -74,6 +85,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
       _lib.ptr(d), ctypes.c_int(d.stride(0)), ctypes.c_int(out_f32), ctypes.c_int(acc),
       ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), _lib.ptr(bias), ctypes.c_int(int(relu)),
       ctypes.c_int(epi), _lib.ptr(aux0), _lib.ptr(aux1), ctypes.c_int(ldaux), _lib.ptr(out2),
-      _lib.ptr(_lib.status_buffer(a.device)), _lib.stream())
+      ctypes.c_int(split_k), _lib.ptr(_lib.status_buffer(a.device)), _lib.stream())
   _lib.check_rc(rc, "recml_gemm_bf16")
   return (d, out2) if want_out2 else d
