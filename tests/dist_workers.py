@@ -1,0 +1,136 @@
+"""Worker functions executed by every rank of the multi-process tests (importable module so that
+`torch.multiprocessing.spawn` can pickle them)."""
+import os
+import sys
+import traceback
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _init(rank, world, backend, port):
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                    LOCAL_RANK=str(rank))
+  if backend == "nccl":
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+  else:
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def entry(rank, world, backend, port, fn_name, args, result_dir):
+  try:
+    _init(rank, world, backend, port)
+    out = globals()[fn_name](rank, world, *args)
+    torch.save(out, os.path.join(result_dir, f"rank{rank}.pt"))
+  except Exception:  # pylint: disable=broad-except
+    with open(os.path.join(result_dir, f"rank{rank}.err"), "w") as f:
+      f.write(traceback.format_exc())
+    raise
+  finally:
+    if dist.is_initialized():
+      try:
+        dist.barrier()
+        dist.destroy_process_group()
+      except Exception:  # pylint: disable=broad-except
+        pass
+
+
+# ---------------------------------------------------------------------------------------------------
+def _emb_specs():
+  from recml_b200 import embedding as emb
+  vocabs = [50, 3000, 7, 400]
+  combs = ["sum", "sum", "mean", "sqrtn"]
+  return vocabs, {f"f{i}": emb.EmbeddingSpec(v, 64, combiner=c) for i, (v, c) in enumerate(zip(vocabs, combs))}
+
+
+def _global_batch(seed, B_global, vocabs, bags):
+  from recml_b200 import embedding as emb
+  from recml_b200.data import synthetic
+  rng = np.random.default_rng(seed)
+  feats = {f"f{i}": [synthetic.zipf_ids(rng, v, (int(rng.integers(0, b + 1)),), 1.05).tolist()
+                     for _ in range(B_global)] for i, (v, b) in enumerate(zip(vocabs, bags))}
+  return feats
+
+
+def sharded_embedding_steps(rank, world, device_type, backend_name, placements, opt_kind, steps):
+  """Runs `steps` lookups + updates with the requested placements; returns this rank's outputs of
+  every step and the final un-sharded tables."""
+  from recml_b200 import embedding as emb
+  vocabs, specs = _emb_specs()
+  bags = [3, 9, 2, 5]
+  P = emb.Placement
+  overrides = {f"f{i}": P(p) for i, p in enumerate(placements)}
+  opt = {"rowwise_adagrad": emb.RowWiseAdagradOptimizerSpec(0.1), "adam": emb.AdamOptimizerSpec(0.02),
+         "sgd": emb.SGDOptimizerSpec(0.1)}[opt_kind]
+  device = torch.device("cuda", rank) if device_type == "cuda" else torch.device("cpu")
+  cfg = emb.ShardedEmbeddingConfig(specs, opt, placement_overrides=overrides, backend=backend_name, seed=5)
+  m = emb.ShardedEmbedding(cfg, device=device)
+  m.grad_scale = 1.0   # the test feeds identical per-sample gradients for every world size
+  outs = []
+  B_global = 32 * world if world > 1 else 64
+  if world == 1:
+    B_global = 64
+  for step in range(steps):
+    feats = _global_batch(100 + step, 64, vocabs, bags)     # same 64-sample global batch for any world
+    per = 64 // world
+    mine = {k: v[rank * per:(rank + 1) * per] for k, v in feats.items()}
+    kjt = emb.KeyedJagged.from_lists(mine).to_device(device)
+    out = m(kjt)
+    g = torch.from_numpy(np.random.default_rng(500 + step).normal(size=(64, len(specs), 64)).astype(np.float32))
+    g = (g * 0.1).to(torch.bfloat16).float()[rank * per:(rank + 1) * per]
+    out.backward(g.to(device).to(out.dtype))
+    outs.append(out.detach().float().cpu())
+  if device.type == "cuda":
+    torch.cuda.synchronize()
+    from recml_b200.ops import _lib
+    _lib.check_status(device)
+  tables = {n: m.gather_table(n).cpu() for n in m.plan.tables}
+  return {"outs": outs, "tables": tables}
+
+
+def allreduce_grads(rank, world, device_type, sizes):
+  """Fused NVLink reducer (CUDA) / flat-bucket reducer (CPU) vs a plain all_reduce mean."""
+  from recml_b200.comm import grad_reducer
+  device = torch.device("cuda", rank) if device_type == "cuda" else torch.device("cpu")
+  gen = torch.Generator().manual_seed(17 + rank)
+  params = [torch.zeros(s, device=device, requires_grad=True) for s in sizes]
+  results = []
+  red = grad_reducer.make_reducer(None, device)
+  for it in range(3):
+    for p in params:
+      p.grad = torch.randn(p.shape, generator=gen).to(device)
+    ref = []
+    for p in params:
+      t = p.grad.clone()
+      dist.all_reduce(t)
+      ref.append(t / world)
+    red.average_grads(params)
+    if device.type == "cuda":
+      torch.cuda.synchronize()
+    results.append(max(float((p.grad - r).abs().max() / (r.abs().max() + 1e-6)) for p, r in zip(params, ref)))
+  if device.type == "cuda":
+    from recml_b200.ops import _lib
+    _lib.check_status(device)
+  return {"max_rel_err": results, "reducer": type(red).__name__}
+
+
+def dlrm_tiny_training(rank, world, device_type, steps):
+  """BASELINE config 1 (tiny DLRM-DCNv2) as a data-parallel + sharded-embedding job."""
+  import tempfile
+  from recml_b200 import config as C, run_experiment
+  from recml_b200.examples import dlrm_experiment as D
+  d = tempfile.mkdtemp() if rank == 0 else None
+  box = [d]
+  dist.broadcast_object_list(box, src=0)
+  cfg = D.tiny_experiment(model_dir=box[0], train_steps=steps, batch_size=256)
+  if device_type == "cpu":
+    cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, device="cpu")
+  exp = C.build(cfg)
+  logs = run_experiment(exp, "train_and_eval")
+  import os as _os
+  return {"loss": float(logs["train"]["loss"]), "val_loss": float(logs["val"]["loss"]),
+          "ckpts": sorted(_os.listdir(_os.path.join(box[0], "checkpoints")))}

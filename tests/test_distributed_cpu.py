@@ -1,0 +1,39 @@
+"""Multi-process (gloo, world_size 2 and 3) tests of the sharded-embedding plumbing, gradient
+averaging and the tiny DLRM-DCNv2 job.  The reference has no multi-process test at all."""
+import pytest
+import torch
+
+from tests import dist_utils
+
+
+def _single(placements, opt, steps=3):
+  from tests import dist_workers
+  return dist_workers.sharded_embedding_steps(0, 1, "cpu", "collective", placements, opt, steps)
+
+
+@pytest.mark.parametrize("placements,opt", [
+    (["row_wise", "row_wise", "row_wise", "row_wise"], "rowwise_adagrad"),
+    (["table_wise", "row_wise", "table_wise", "column_wise"], "adam"),
+    (["column_wise", "table_wise", "row_wise", "table_wise"], "sgd")])
+@pytest.mark.parametrize("world", [2])
+def test_sharded_embedding_matches_single_process(world, placements, opt):
+  ref = _single(placements, opt)
+  res = dist_utils.run_ranks("sharded_embedding_steps", world, "gloo", "cpu", "collective", placements, opt, 3)
+  per = 64 // world
+  for step in range(3):
+    got = torch.cat([r["outs"][step] for r in res], dim=0)
+    torch.testing.assert_close(got, ref["outs"][step], atol=1e-5, rtol=1e-5)
+  for name, t in ref["tables"].items():
+    torch.testing.assert_close(res[0]["tables"][name], t, atol=2e-4, rtol=1e-4)
+    torch.testing.assert_close(res[1]["tables"][name], t, atol=2e-4, rtol=1e-4)
+
+
+def test_gradient_averaging_gloo():
+  res = dist_utils.run_ranks("allreduce_grads", 2, "gloo", "cpu", [(33, 7), (5,), (1000,)])
+  assert all(e < 1e-6 for r in res for e in r["max_rel_err"])
+
+
+def test_tiny_dlrm_two_ranks_matches_loss_trend():
+  res = dist_utils.run_ranks("dlrm_tiny_training", 2, "gloo", "cpu", 60)
+  assert res[0]["ckpts"] == ["49", "59"]
+  assert res[0]["loss"] < 0.62 and abs(res[0]["loss"] - res[1]["loss"]) < 0.1

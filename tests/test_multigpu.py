@@ -1,0 +1,38 @@
+"""2-GPU tests of the fused compute+collective kernels against single-process CPU references.
+Run on a box with two or more B200s; every peer wait in the kernels is bounded."""
+import pytest
+import torch
+
+from tests import dist_utils
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _single(placements, opt, steps=3):
+  from tests import dist_workers
+  return dist_workers.sharded_embedding_steps(0, 1, "cpu", "collective", placements, opt, steps)
+
+
+@pytest.mark.parametrize("placements,opt", [
+    (["row_wise", "row_wise", "row_wise", "row_wise"], "rowwise_adagrad"),
+    (["table_wise", "row_wise", "table_wise", "column_wise"], "adam"),
+    (["table_wise", "table_wise", "table_wise", "table_wise"], "sgd")])
+def test_fused_embedding_two_gpus(placements, opt):
+  ref = _single(placements, opt)
+  res = dist_utils.run_ranks("sharded_embedding_steps", 2, "nccl", "cuda", "fused", placements, opt, 3)
+  for step in range(3):
+    got = torch.cat([r["outs"][step] for r in res], dim=0)
+    torch.testing.assert_close(got, ref["outs"][step], atol=3e-2, rtol=3e-2)
+  for name, t in ref["tables"].items():
+    torch.testing.assert_close(res[0]["tables"][name], t, atol=5e-3, rtol=5e-3)
+
+
+def test_fused_allreduce_two_gpus():
+  res = dist_utils.run_ranks("allreduce_grads", 2, "nccl", "cuda", [(333, 77), (5,), (100000,), (1, 9)])
+  assert res[0]["reducer"] == "FusedNvlinkReducer"
+  assert all(e < 1e-2 for r in res for e in r["max_rel_err"]), res   # bf16 wire format
+
+
+def test_dlrm_tiny_two_gpus():
+  res = dist_utils.run_ranks("dlrm_tiny_training", 2, "nccl", "cuda", 60)
+  assert res[0]["loss"] < 0.62
