@@ -766,3 +766,71 @@ extern "C" int recml_emb_struct_sizes(int* out) {
   out[4] = sizeof(PushGradDesc); out[5] = sizeof(PushGradParams); out[6] = sizeof(BwdParams); out[7] = sizeof(PushIdsParams);
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward update (declared in embedding_static.h).
+// ---------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "embedding_static.h"
+
+namespace recml {
+namespace emb {
+// Scratch for the partial sums of row runs that cross 32-entry chunk boundaries: one line of
+// RECML_EMB_STATIC_MAX_DIM floats per chunk.  It lives in the library image, so every GPU that loads
+// the library holds these 4 MiB until the process exits.
+static __device__ __align__(256) float g_static_scratch[(RECML_EMB_STATIC_MAX_OCC / 32) * RECML_EMB_STATIC_MAX_DIM];
+}  // namespace emb
+}  // namespace recml
+
+static void static_fail(char* err, int err_len, const char* msg) {
+  if (err != nullptr && err_len > 0) snprintf(err, static_cast<size_t>(err_len), "%s", msg);
+}
+
+extern "C" int recml_emb_bwd_update_static(const BwdParams* p, long long max_occ, int gains, cudaStream_t stream,
+                                           char* err, int err_len) {
+  if (p == nullptr) { static_fail(err, err_len, "null parameter block"); return -20; }
+  if (max_occ > RECML_EMB_STATIC_MAX_OCC) {
+    static_fail(err, err_len, "max_occ exceeds RECML_EMB_STATIC_MAX_OCC (262144 occurrences per call)");
+    return -21;
+  }
+  if (p->dloc > RECML_EMB_STATIC_MAX_DIM) {
+    static_fail(err, err_len, "embedding dim exceeds RECML_EMB_STATIC_MAX_DIM (128 columns)");
+    return -22;
+  }
+  if (max_occ <= 0) return 0;
+  // In host code `g_static_scratch` is only a handle for the symbol; the device address has to be
+  // asked for, once per device, with that device current.
+  static std::mutex mu;
+  static float* dev_addr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    static_fail(err, err_len, "cudaGetDevice failed or device ordinal out of range");
+    return -23;
+  }
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_addr[dev] == nullptr) {
+      void* addr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&addr, recml::emb::g_static_scratch);
+      if (e != cudaSuccess || addr == nullptr) {
+        static_fail(err, err_len, cudaGetErrorString(e));
+        return -24;
+      }
+      dev_addr[dev] = static_cast<float*>(addr);
+    }
+    scratch = dev_addr[dev];
+  }
+  // The array keeps whatever the previous call left behind: clear the lines this call can touch.
+  const long long chunks = (max_occ + 31) / 32;
+  if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(chunks) * p->dloc * sizeof(float), stream) != cudaSuccess) {
+    static_fail(err, err_len, "cudaMemsetAsync on the static scratch failed");
+    return -25;
+  }
+  BwdParams q = *p;
+  q.scratch = scratch;
+  const int rc = recml_emb_bwd_update(&q, max_occ, gains, stream);
+  if (rc != 0) static_fail(err, err_len, "kernel launch failed");
+  return rc;
+}
