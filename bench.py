@@ -90,6 +90,7 @@ def main() -> None:
   ap.add_argument("--global-batch", type=int, default=65536)
   ap.add_argument("--vocab-scale", type=float, default=1.0, help="debug only: shrink table sizes")
   ap.add_argument("--backend", default="auto")
+  ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying CUDA graphs")
   args = ap.parse_args()
   if args.impl == "reference":
     if int(os.environ.get("RANK", "0")) == 0:
@@ -123,12 +124,15 @@ def main() -> None:
   n_pool = 4
   data = D.CriteoFactory(model=cfg, batch_size=B, num_batches=n_pool, seed=0)
   task = D.PredictionTask(cfg, data, None, optim_factory.AdamFactory(learning_rate=1e-3))
-  part = partitioning.DataParallelPartitioner()
+  use_graph = not args.no_graph and os.environ.get("RECML_BENCH_GRAPH", "1") != "0"
+  part = partitioning.DataParallelPartitioner(use_cuda_graph=use_graph, graph_warmup_steps=2)
   it = task.create_datasets()
   first = part.shard_inputs(next(it))
   gen = torch.Generator().manual_seed(0)
   state = part.partition_init(lambda b: task.create_state(b, gen))(first)
   step_rng = torch.Generator(device=device)
+  # the same wrapper the Trainer uses: eager warm-up steps, then CUDA-graph replay
+  train_step = part.partition_step(lambda inp, st: task.train_step(inp, st, step_rng), training=True)
 
   def barrier():
     if world > 1:
@@ -159,7 +163,7 @@ def main() -> None:
     hb = host_batches[cursor[0] % n_pool]
     cursor[0] += 1
     nonlocal state
-    state, metrics = task.train_step(part.shard_inputs(hb), state, step_rng)
+    state, metrics = train_step(part.shard_inputs(hb), state)
     last_loss[0] = float(metrics["loss"].localize().compute())   # D2H read of total and count
 
   for _ in range(args.warmup):
@@ -176,7 +180,7 @@ def main() -> None:
     db = dev_batches[cursor[0] % n_pool]
     cursor[0] += 1
     nonlocal state
-    state, _ = task.train_step(db, state, step_rng)
+    state, _ = train_step(db, state)
 
   for _ in range(args.warmup):
     dev_step()
@@ -198,7 +202,7 @@ def main() -> None:
                    "global_batch": args.global_batch, "per_gpu_batch": B, "ids_per_sample": sum(cfg.bag_sizes),
                    "parallelism": f"dp{W} + sharded embeddings (row-wise >=256MB tables, table-wise rest)",
                    "embedding_optimizer": "row-wise Adagrad (fp32 tables)", "dense_optimizer": "Adam",
-                   "vocab_scale": args.vocab_scale,
+                   "vocab_scale": args.vocab_scale, "cuda_graph": use_graph,
                    "l2": "inputs larger than L2: activations >= 450 MB per layer at batch 65536 and "
                          "embedding tables of 104 GB are streamed every step"},
         "clocks": clocks,

@@ -32,7 +32,7 @@ struct Comm {
   const unsigned long long* my_flag_b;
   unsigned int* done_counter;
   int W, me;
-  unsigned long long seq;
+  SeqRef seq;
   long long total;                     // bucket elements, multiple of 8*W
   float scale;
   int* status;
@@ -77,11 +77,12 @@ __global__ void __launch_bounds__(256) pack_kernel(const Bucket b, const Comm c)
     *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]),
                                                     pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
   }
-  signal_all(c.done_counter, c.flag_a, c.W, c.seq);
+  signal_all(c.done_counter, c.flag_a, c.W, seq_of(c.seq));
 }
 
 __global__ void __launch_bounds__(256) reduce_kernel(const Comm c) {
-  if (!wait_all(c.my_flag_a, c.W, c.seq, c.status, 8)) return;
+  const unsigned long long seq = seq_of(c.seq);
+  if (!wait_all(c.my_flag_a, c.W, seq, c.status, 8)) return;
   const long long slice = c.total / c.W;
   const long long lo = slice * c.me;
   const long long nvec = slice / 8;
@@ -105,11 +106,11 @@ __global__ void __launch_bounds__(256) reduce_kernel(const Comm c) {
       *reinterpret_cast<uint4*>(c.out[dst] + e) = o;
     }
   }
-  signal_all(c.done_counter + 1, c.flag_b, c.W, c.seq);
+  signal_all(c.done_counter + 1, c.flag_b, c.W, seq);
 }
 
 __global__ void __launch_bounds__(256) unpack_kernel(const Bucket b, const Comm c) {
-  if (!wait_all(c.my_flag_b, c.W, c.seq, c.status, 9)) return;
+  if (!wait_all(c.my_flag_b, c.W, seq_of(c.seq), c.status, 9)) return;
   int t = 0;
   while (t + 1 < b.n && static_cast<long long>(blockIdx.x) >= b.block_start[t + 1]) ++t;
   const long long base = (blockIdx.x - b.block_start[t]) * 2048LL;

@@ -63,6 +63,16 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, uns
   }
 }
 
+// Sequence numbers of peer flags can come from device memory (so that a captured CUDA graph sees a
+// new value on every replay): effective = *ptr * mul + add when ptr is set, else the literal.
+struct SeqRef {
+  const unsigned long long* ptr;
+  unsigned long long mul, add, literal;
+};
+__device__ __forceinline__ unsigned long long seq_of(const SeqRef& s) {
+  return s.ptr != nullptr ? (*s.ptr) * s.mul + s.add : s.literal;
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {

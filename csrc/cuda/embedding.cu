@@ -162,7 +162,7 @@ struct PushIdsParams {
   const int* values; const int* offsets; const float* weights;
   long long nnz; int n_offsets; int W; int me;
   int* dst_values[kMaxWorld]; int* dst_offsets[kMaxWorld]; float* dst_weights[kMaxWorld];
-  unsigned int* done_counter; PeerFlags flags; unsigned long long seq;
+  unsigned int* done_counter; PeerFlags flags; SeqRef seq;
 };
 
 __global__ void emb_push_ids_kernel(const PushIdsParams p) {
@@ -178,7 +178,7 @@ __global__ void emb_push_ids_kernel(const PushIdsParams p) {
       for (long long i = tid; i < p.nnz; i += stride) dw[i] = p.weights[i];
     }
   }
-  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+  grid_done_then_signal(p.done_counter, p.flags, p.W, seq_of(p.seq));
 }
 
 // =================================== forward: gather + pool + peer store ===========================
@@ -192,14 +192,15 @@ struct FwdParams {
   uint32_t* occ_key; uint32_t* occ_val; float* occ_gain; unsigned int* occ_count; unsigned int occ_cap;
   long long grad_ld;        // >0: gradients will be read in place from a [B, grad_ld] matrix (1 rank):
                             //     occurrence value = (b*grad_ld + grad_off)/8 instead of a buffer row
-  const unsigned long long* wait_flags; unsigned long long wait_seq;   // ids channel (null: no wait)
-  unsigned int* done_counter; PeerFlags flags; unsigned long long seq;  // pooled channel
+  const unsigned long long* wait_flags;   // ids channel (null: no wait)
+  unsigned int* done_counter; PeerFlags flags; SeqRef seq;  // pooled channel; the ids channel uses the same number
   int* status;
 };
 
 template <int VPL, bool TRAIN, bool GAINS>
 __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
-  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 0)) return;
+  const unsigned long long seq = seq_of(p.seq);
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq, p.status, 0)) return;
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long total = static_cast<long long>(p.n_feats) * p.W * p.B;
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
       store_bf16<VPL>(dst_base + slot_row * f.dst_stride, acc);
     }
   }
-  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+  grid_done_then_signal(p.done_counter, p.flags, p.W, seq);
 }
 
 // =================================== combine: sum source slots, write concat =======================
@@ -344,11 +345,11 @@ struct CombineDesc { long long slot_off; int nslots; int dim; int out_col; int s
 struct CombineParams {
   const __nv_bfloat16* pooled; const CombineDesc* feats; int n_feats; int B;
   __nv_bfloat16* out; long long ld_out;
-  const unsigned long long* wait_flags; int W; int n_chan; unsigned long long wait_seq; int* status;
+  const unsigned long long* wait_flags; int W; int n_chan; SeqRef seq; int* status;
 };
 
 __global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p) {
-  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 1, p.n_chan)) return;
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 1, p.n_chan)) return;
   // one thread per 16-byte chunk (8 bf16) of one (sample, feature) vector
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int fi = 0; fi < p.n_feats; ++fi) {
@@ -384,7 +385,7 @@ struct PushGradDesc {
 };
 struct PushGradParams {
   const __nv_bfloat16* grad; long long ld; const PushGradDesc* feats; int n_feats; int B; int W; int me;
-  PeerBf16 dst; unsigned int* done_counter; PeerFlags flags; unsigned long long seq;
+  PeerBf16 dst; unsigned int* done_counter; PeerFlags flags; SeqRef seq;
 };
 
 __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParams p) {
@@ -416,7 +417,7 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
       }
     }
   }
-  grid_done_then_signal(p.done_counter, p.flags, p.W, p.seq);
+  grid_done_then_signal(p.done_counter, p.flags, p.W, seq_of(p.seq));
 }
 
 // =================================== backward: segmented reduce + row optimizer ====================
@@ -427,7 +428,7 @@ struct BwdParams {
   float* table; float* slot0; float* slot1; int dloc;
   int opt; float hp[6]; float grad_scale; int slot1_rowwise;
   float* scratch;               // [n_chunks, dloc] partial sums of runs that cross chunk boundaries (kept zero)
-  const unsigned long long* wait_flags; int W; unsigned long long wait_seq; int* status;
+  const unsigned long long* wait_flags; int W; SeqRef seq; int* status;
 };
 
 template <int VPL>
@@ -571,7 +572,7 @@ __device__ __forceinline__ unsigned int lower_bound(const uint32_t* keys, unsign
 // thereby reduced by thousands of warps in parallel instead of one.
 template <int VPL, bool GAINS>
 __global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) {
-  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, p.wait_seq, p.status, 2)) return;
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 2)) return;
   const int lane = threadIdx.x & 31;
   const unsigned int n = *p.n_occ;
   const unsigned int chunk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -664,6 +665,8 @@ __global__ void __launch_bounds__(256) emb_bwd_finalize_kernel(const BwdParams p
   apply_row_update<VPL>(p, klast, acc, lane, lane_on);
 }
 
+__global__ void tick_kernel(unsigned long long* p) { *p += 1ull; }
+
 static int blocks_for(long long warps_needed, int max_blocks) {
   long long b = (warps_needed + 7) / 8;
   if (b < 1) b = 1;
@@ -674,6 +677,11 @@ static int blocks_for(long long warps_needed, int max_blocks) {
 }  // namespace recml
 
 using namespace recml::emb;
+
+extern "C" int recml_tick(unsigned long long* counter, cudaStream_t stream) {
+  tick_kernel<<<1, 1, 0, stream>>>(counter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 
 extern "C" int recml_emb_push_ids(const PushIdsParams* p, cudaStream_t stream) {
   long long work = p->nnz > p->n_offsets ? p->nnz : p->n_offsets;

@@ -48,7 +48,8 @@ __global__ void sqnorm_kernel(const TensorList tl, float* out) {
   }
 }
 
-__global__ void step_kernel(const TensorList tl, const Hyper h) {
+__global__ void step_kernel(const TensorList tl, const Hyper h_val, const Hyper* __restrict__ h_dev) {
+  const Hyper h = h_dev != nullptr ? *h_dev : h_val;   // device copy: refreshed per replay of a CUDA graph
   int t = 0;
   while (t + 1 < tl.n && static_cast<long long>(blockIdx.x) >= tl.block_start[t + 1]) ++t;
   const long long base = (blockIdx.x - tl.block_start[t]) * 1024LL;
@@ -97,9 +98,9 @@ extern "C" int recml_optim_sqnorm(const TensorList* tl, float* out, cudaStream_t
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-extern "C" int recml_optim_step(const TensorList* tl, const Hyper* h, cudaStream_t stream) {
+extern "C" int recml_optim_step(const TensorList* tl, const Hyper* h, const Hyper* h_dev, cudaStream_t stream) {
   const long long blocks = tl->block_start[tl->n];
   if (blocks <= 0) return 0;
-  step_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(*tl, *h);
+  step_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(*tl, *h, h_dev);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

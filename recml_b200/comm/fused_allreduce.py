@@ -25,10 +25,15 @@ class _Bucket(ctypes.Structure):
               ("block_start", c_ll * (MAXT + 1)), ("n", ctypes.c_int)]
 
 
+class _SeqRef(ctypes.Structure):
+  _fields_ = [("ptr", c_vp), ("mul", ctypes.c_ulonglong), ("add", ctypes.c_ulonglong),
+              ("literal", ctypes.c_ulonglong)]
+
+
 class _Comm(ctypes.Structure):
   _fields_ = [("inp", c_vp * MAXW), ("out", c_vp * MAXW), ("flag_a", c_vp * MAXW), ("flag_b", c_vp * MAXW),
               ("my_flag_a", c_vp), ("my_flag_b", c_vp), ("done_counter", c_vp), ("W", ctypes.c_int),
-              ("me", ctypes.c_int), ("seq", ctypes.c_ulonglong), ("total", c_ll), ("scale", ctypes.c_float),
+              ("me", ctypes.c_int), ("seq", _SeqRef), ("total", c_ll), ("scale", ctypes.c_float),
               ("status", c_vp)]
 
 
@@ -49,8 +54,24 @@ class FusedNvlinkReducer:
     self.buf = None
     self.seq = 0
     self.done = torch.zeros(4, dtype=torch.int32, device=device)
+    self.calls = 0                      # host mirror of `calls_dev`
+    self.calls_dev = torch.zeros(1, dtype=torch.int64, device=device)
+    self.buckets_done = 0               # buckets issued so far (buffer parity)
     self.side = torch.cuda.Stream(device=device)
     self.status = _lib.status_buffer(device)
+    self._last_buckets = 0
+    from recml_b200.utils import graphs
+    graphs.register(self)
+
+  def graph_snapshot(self):
+    return (self.calls, self.buckets_done)
+
+  def graph_restore(self, snap) -> None:
+    self.calls, self.buckets_done = snap
+
+  def graph_advance(self) -> None:
+    self.calls += 1
+    self.buckets_done += self._last_buckets
 
   def _ensure(self, elems: int):
     unit = 8 * self.world
@@ -84,13 +105,19 @@ class FusedNvlinkReducer:
       cur.append((g, n)); n += sz
     if cur:
       buckets.append((cur, n))
+    if len(buckets) > 64:
+      raise ValueError("more than 64 gradient buckets; raise bucket_elems")
     self._ensure(max(n for _, n in buckets))
     main = torch.cuda.current_stream(self.device)
     self.side.wait_stream(main)
+    self.calls += 1
+    self._last_buckets = len(buckets)
     with torch.cuda.stream(self.side):
-      for items, n in buckets:
-        self.seq += 1
-        par = self.seq & 1
+      _lib.check_rc(self.lib.recml_tick(_lib.ptr(self.calls_dev), ctypes.c_void_p(self.side.cuda_stream)), "tick")
+      for bi, (items, n) in enumerate(buckets):
+        # flag value of bucket bi in call c: c*64 + bi (monotonic for any bucket count <= 64)
+        par = self.buckets_done & 1
+        self.buckets_done += 1
         unit = 8 * self.world
         total = (n + unit - 1) // unit * unit
         b = _Bucket()
@@ -110,7 +137,8 @@ class FusedNvlinkReducer:
         c.my_flag_a = self.buf.peer_ptr(self.rank, self.flag_off)
         c.my_flag_b = self.buf.peer_ptr(self.rank, self.flag_off + MAXW * 8)
         c.done_counter = self.done.data_ptr()
-        c.W, c.me, c.seq, c.total = self.world, self.rank, self.seq, total
+        c.W, c.me, c.total = self.world, self.rank, total
+        c.seq = _SeqRef(self.calls_dev.data_ptr(), 64, bi, 0)
         c.scale = 1.0 / self.world if self.average else 1.0
         c.status = self.status.data_ptr()
         # zero the bucket tail so padding never carries stale values into the sum

@@ -33,6 +33,12 @@ OPT = {"sgd": 0, "adagrad": 1, "rowwise_adagrad": 2, "adam": 3, "rowwise_adam": 
        "adagrad_momentum": 5, "ftrl": 6, "laprop": 7}
 
 
+class SeqRef(ctypes.Structure):
+  """Sequence number of a flag exchange: `*ptr * mul + add` when ptr is set, else `literal`."""
+  _fields_ = [("ptr", c_vp), ("mul", ctypes.c_ulonglong), ("add", ctypes.c_ulonglong),
+              ("literal", ctypes.c_ulonglong)]
+
+
 class FeatDesc(ctypes.Structure):
   _fields_ = [("feat_index", c_int), ("kind", c_int), ("owner", c_int), ("rot", c_int), ("row_base", c_int),
               ("combiner", c_int), ("dim", c_int), ("col_lo", c_int), ("slot_off", c_ll), ("grad_off", c_ll),
@@ -47,8 +53,7 @@ class FwdParams(ctypes.Structure):
   _fields_ = [("ids", IdPtrs), ("feats", c_vp), ("n_feats", c_int), ("W", c_int), ("me", c_int), ("B", c_int),
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
               ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
-              ("wait_seq", ctypes.c_ulonglong), ("done_counter", c_vp), ("flags", c_vp * MAXW),
-              ("seq", ctypes.c_ulonglong), ("status", c_vp)]
+              ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp)]
 
 
 class CombineDesc(ctypes.Structure):
@@ -57,8 +62,7 @@ class CombineDesc(ctypes.Structure):
 
 class CombineParams(ctypes.Structure):
   _fields_ = [("pooled", c_vp), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("out", c_vp), ("ld_out", c_ll),
-              ("wait_flags", c_vp), ("W", c_int), ("n_chan", c_int), ("wait_seq", ctypes.c_ulonglong),
-              ("status", c_vp)]
+              ("wait_flags", c_vp), ("W", c_int), ("n_chan", c_int), ("seq", SeqRef), ("status", c_vp)]
 
 
 class PushGradDesc(ctypes.Structure):
@@ -69,21 +73,21 @@ class PushGradDesc(ctypes.Structure):
 class PushGradParams(ctypes.Structure):
   _fields_ = [("grad", c_vp), ("ld", c_ll), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("W", c_int),
               ("me", c_int), ("dst", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
-              ("seq", ctypes.c_ulonglong)]
+              ("seq", SeqRef)]
 
 
 class BwdParams(ctypes.Structure):
   _fields_ = [("keys", c_vp), ("vals", c_vp), ("occ_gain", c_vp), ("n_occ", c_vp), ("grads", c_vp), ("val_scale", c_ll),
               ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
               ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
-              ("wait_flags", c_vp), ("W", c_int), ("wait_seq", ctypes.c_ulonglong), ("status", c_vp)]
+              ("wait_flags", c_vp), ("W", c_int), ("seq", SeqRef), ("status", c_vp)]
 
 
 class PushIdsParams(ctypes.Structure):
   _fields_ = [("values", c_vp), ("offsets", c_vp), ("weights", c_vp), ("nnz", c_ll), ("n_offsets", c_int),
               ("W", c_int), ("me", c_int), ("dst_values", c_vp * MAXW), ("dst_offsets", c_vp * MAXW),
               ("dst_weights", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
-              ("seq", ctypes.c_ulonglong)]
+              ("seq", SeqRef)]
 
 
 _layout_checked = False
@@ -122,11 +126,25 @@ class FusedBackend:
     self.layout, self.width = collective.feature_layout(m)
     self.capacity_factor = capacity_factor
     self.seq = 0
+    self.seq_dev = torch.zeros(1, dtype=torch.int64, device=module.device)
     self.B = None
     self.status = _lib.status_buffer(m.device)
     self._sort_temp: dict[int, torch.Tensor] = {}
+    from recml_b200.utils import graphs
+    graphs.register(self)
     self.has_gains = any(s.combiner != "sum" or s.weight_name is not None
                          for s in m.config.specs.values())
+
+  # -- CUDA-graph protocol: host mirrors of device-side counters ----------------------------------------
+  def graph_snapshot(self):
+    return (self.seq, self.m.step_count)
+
+  def graph_restore(self, snap) -> None:
+    self.seq, self.m.step_count = snap
+
+  def graph_advance(self) -> None:
+    self.seq += 1
+    self.m.step_count += 1
 
   # -- one-time set-up for a batch geometry --------------------------------------------------------------
   def _setup(self, kjt: jagged_lib.KeyedJagged):
@@ -288,9 +306,13 @@ class FusedBackend:
     assert kjt.values.dtype == torch.int32 and kjt.offsets.dtype == torch.int32
     if training:
       self._ensure_occ(kjt)
+    # The step's sequence number lives on the device (ticked here, read by every kernel of the step),
+    # so a captured CUDA graph advances it on every replay; `self.seq` mirrors it for buffer parity.
     self.seq += 1
-    seq, par = self.seq, (self.seq & 1) if W > 1 else 0
+    par = (self.seq & 1) if W > 1 else 0
     st = _lib.stream()
+    _lib.check_rc(self.lib.recml_tick(_lib.ptr(self.seq_dev), st), "tick")
+    seq = SeqRef(self.seq_dev.data_ptr(), 1, 0, 0)
     gains = self.has_gains
     B = self.B
     if out is None:
@@ -342,7 +364,6 @@ class FusedBackend:
         fp.occ_gain = info["gain"].data_ptr() if gains else None
         fp.occ_count, fp.occ_cap = info["count"].data_ptr(), info["occ_cap"]
       fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
-      fp.wait_seq = seq
       fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
@@ -358,7 +379,7 @@ class FusedBackend:
     cp.out, cp.ld_out = out.data_ptr() + out_col * 2, out.stride(0)
     # wait on the pooled channels of every stack: channels 1..n_stacks are contiguous
     cp.wait_flags = self._flag_ptr(m.rank, 1, 0) if W > 1 else None
-    cp.W, cp.n_chan, cp.wait_seq, cp.status = W, len(self.stacks), seq, self.status.data_ptr()
+    cp.W, cp.n_chan, cp.seq, cp.status = W, len(self.stacks), seq, self.status.data_ptr()
     _lib.check_rc(self.lib.recml_emb_combine(ctypes.byref(cp), st), "emb_combine")
     res = out[:, out_col:out_col + self.width]
     res = res if odt == torch.bfloat16 else res.to(odt)
@@ -424,7 +445,7 @@ class FusedBackend:
       bp.grad_scale = m.grad_scale
       bp.scratch = info["scratch"].data_ptr()
       bp.wait_flags = self._flag_ptr(m.rank, gchan, 0) if (W > 1 and direct is None) else None
-      bp.W, bp.wait_seq, bp.status = W, seq, self.status.data_ptr()
+      bp.W, bp.seq, bp.status = W, seq, self.status.data_ptr()
       if n > 0 or W > 1:
         _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),
                                                     st), "emb_bwd_update")

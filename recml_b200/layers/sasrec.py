@@ -1,0 +1,46 @@
+"""SASRec: self-attentive sequential recommendation (`recml/layers/keras/sasrec.py:36-163`).
+Item embedding (tied reverse) + learned positions → final_norm → dropout → N causal pre-LN
+transformer blocks → final_norm → tied vocabulary logits."""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from recml_b200.layers import embeddings as emb_layers
+from recml_b200.layers import transformer
+from recml_b200.ops import norm as norm_ops
+
+
+class SASRec(nn.Module):
+  def __init__(self, *, vocab_size: int, max_positions: int, model_dim: int, mlp_dim: int, num_heads: int,
+               num_layers: int, dropout: float = 0.0, norm_eps: float = 1e-6, scale_by_sqrt_dim: bool = False,
+               add_head: bool = True):
+    super().__init__()
+    self.item_embedding = emb_layers.ReversibleEmbedding(vocab_size, model_dim, tie_weights=True)
+    self.position_embedding = emb_layers.PositionEmbedding(max_positions, model_dim)
+    self.embeddings_dropout = nn.Dropout(dropout)
+    self.decoder_blocks = nn.ModuleList(
+        transformer.TransformerBlock(model_dim, mlp_dim, num_heads, dropout, layer_norm_epsilon=norm_eps,
+                                     normalize_first=True, causal=True) for _ in range(num_layers))
+    self.final_norm_w, self.final_norm_b = nn.Parameter(torch.ones(model_dim)), nn.Parameter(torch.zeros(model_dim))
+    self.norm_eps, self.model_dim, self.scale_by_sqrt_dim, self.add_head = norm_eps, model_dim, \
+        scale_by_sqrt_dim, add_head
+
+  def _norm(self, x):
+    return norm_ops.layer_norm(x, self.final_norm_w, self.final_norm_b, self.norm_eps)
+
+  def encode(self, inputs, padding_mask=None, attention_mask=None):
+    """Sequence states `[B, L, D]` (what the sharded-vocabulary heads consume)."""
+    e = self.item_embedding(inputs)
+    if self.scale_by_sqrt_dim:
+      e = e * math.sqrt(self.model_dim)
+    e = self.embeddings_dropout(self._norm(e + self.position_embedding(e)))
+    for block in self.decoder_blocks:
+      e = block(e, padding_mask=padding_mask, attention_mask=attention_mask)
+    return self._norm(e)
+
+  def forward(self, inputs, padding_mask=None, attention_mask=None):
+    e = self.encode(inputs, padding_mask, attention_mask)
+    return e if not self.add_head else self.item_embedding(e, reverse=True)

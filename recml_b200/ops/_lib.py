@@ -22,7 +22,7 @@ class NativeError(RuntimeError):
 # Number of this library's kernels launched so far (benchmarks reset and read it).  Each launcher
 # call counts the kernels it launches; CUB's sort kernels are library code and count as zero.
 LAUNCHES = {"count": 0}
-_KERNELS_PER_CALL = {"recml_emb_bwd_update": 2, "recml_sort_pairs_u32": 0, "recml_sort_temp_bytes": 0,
+_KERNELS_PER_CALL = {"recml_emb_bwd_update": 2, "recml_allreduce_bucket": 3, "recml_sort_pairs_u32": 0, "recml_sort_temp_bytes": 0,
                      "recml_emb_struct_sizes": 0, "recml_optim_struct_sizes": 0}
 
 

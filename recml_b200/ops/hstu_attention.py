@@ -1,0 +1,146 @@
+"""HSTU pointwise (SiLU) attention.
+
+  O = mask( silu(Q·Kᵀ·scale + bias) / n ) · V
+
+Dense form `[B, L, H, Dh]` with an explicit `[B, L, L]` mask / bias is what the reference's model
+computes (`recml/layers/keras/hstu.py:356-390`); the reference also ships a block-sparse TPU kernel
+for the same math with causal / full / sliding-window masks and segment ids
+(`recml/core/ops/hstu_ops.py:196-270,829-1046`; dense oracle in `hstu_ops_test.py:45-58`).  The
+B200 path is JAGGED: sequences are packed back to back (`seq_offsets`), cost follows Σ Lᵢ² instead
+of B·L², and the learned relative-position / time-bucket bias (`hstu.py:91-113,190-237`) is
+computed inside the kernel from `pos_w[2N-1]`, `ts_w[buckets+1]` and the timestamps.  Its
+normaliser is the configured `max_seq_len` (the reference divides by the padded length).
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import math
+
+import torch
+
+from recml_b200.ops import _lib
+
+BUCKET_SIZE = 0.301
+
+
+class MaskType(enum.Enum):
+  CAUSAL = "causal"
+  FULL = "full"
+
+
+def time_buckets(delta: torch.Tensor, num_buckets: int) -> torch.Tensor:
+  """clip(int(log(clip(|Δt|, 1, 1e9)) / 0.301), 0, num_buckets)."""
+  v = delta.abs().clamp(min=1, max=int(1e9)).to(torch.float32)
+  return torch.clamp((torch.log(v) / BUCKET_SIZE).to(torch.int64), 0, num_buckets)
+
+
+def relative_bias_dense(L: int, pos_w: torch.Tensor | None, ts_w: torch.Tensor | None,
+                        timestamps: torch.Tensor | None) -> torch.Tensor | None:
+  """`[B or 1, L, L]` bias: pos_w[(j − i) + N − 1] + ts_w[bucket(t_ext[i+1] − t[j])] where
+  t_ext appends the last timestamp once more."""
+  bias = None
+  if pos_w is not None:
+    n = (pos_w.numel() + 1) // 2
+    i = torch.arange(L, device=pos_w.device)
+    bias = pos_w[(i[None, :] - i[:, None]) + n - 1][None]
+  if ts_w is not None and timestamps is not None:
+    ext = torch.cat([timestamps, timestamps[:, -1:]], dim=1)
+    delta = ext[:, 1:, None] - ext[:, None, :-1]
+    tb = ts_w[time_buckets(delta, ts_w.numel() - 1)]
+    bias = tb if bias is None else bias + tb
+  return bias
+
+
+def pointwise_attention_dense(q, k, v, attention_mask=None, attention_bias=None, *, scaled: bool = False,
+                              normalizer: float | None = None, dropout_p: float = 0.0, training: bool = False):
+  """q, k, v `[B, L, H, Dh]`; mask / bias `[B, L, L]` (bias broadcast over heads)."""
+  L = q.shape[1]
+  qf = q.float() / math.sqrt(q.shape[-1]) if scaled else q.float()
+  s = torch.einsum("bthd,bshd->bhts", qf, k.float())
+  if attention_bias is not None:
+    s = s + attention_bias[:, None].float()
+  p = torch.nn.functional.silu(s)
+  if not scaled:
+    p = p / (normalizer if normalizer is not None else L)
+  if attention_mask is not None:
+    p = torch.where(attention_mask[:, None].bool(), p, torch.zeros_like(p))
+  if training and dropout_p > 0:
+    p = torch.nn.functional.dropout(p, dropout_p)
+  return torch.einsum("bhts,bshd->bthd", p, v.float()).to(q.dtype)
+
+
+def pointwise_attention(mask_type: MaskType | str, q, k, v, *, q_segment_ids=None, kv_segment_ids=None,
+                        sliding_window_size: int | None = None, scale: float | None = None):
+  """API of the reference op on `[B, L, H, Dh]`: P = mask(silu(Q·Kᵀ·scale) / L_q); masks combine
+  causal / full, a sliding window (query i sees keys i−w+1..i) and equal segment ids."""
+  mask_type = MaskType(mask_type)
+  B, Lq, H, Dh = q.shape
+  Lk = k.shape[1]
+  i = torch.arange(Lq, device=q.device)[:, None]
+  j = torch.arange(Lk, device=q.device)[None, :]
+  m = (j <= i) if mask_type is MaskType.CAUSAL else torch.ones(Lq, Lk, dtype=torch.bool, device=q.device)
+  if sliding_window_size is not None:
+    m = m & (j > i - sliding_window_size) & (j < i + sliding_window_size)
+  m = m[None].expand(B, Lq, Lk)
+  if q_segment_ids is not None:
+    kv_seg = q_segment_ids if kv_segment_ids is None else kv_segment_ids
+    m = m & (q_segment_ids[:, :, None] == kv_seg[:, None, :])
+  s = torch.einsum("bthd,bshd->bhts", q.float(), k.float()) * (scale if scale is not None else 1.0)
+  p = torch.nn.functional.silu(s) / Lq
+  p = torch.where(m[:, None], p, torch.zeros_like(p))
+  return torch.einsum("bhts,bshd->bthd", p, v.float()).to(q.dtype)
+
+
+def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
+                               timestamps=None, causal: bool = True, scale: float = 1.0):
+  """fp32 torch oracle for the packed kernel: q, k, v `[T, H, Dh]`, `seq_offsets [B+1]`."""
+  out = torch.zeros_like(q, dtype=torch.float32)
+  offs = seq_offsets.tolist()
+  for b in range(len(offs) - 1):
+    a, e = offs[b], offs[b + 1]
+    L = e - a
+    if L == 0:
+      continue
+    ts = None if timestamps is None else timestamps[a:e][None]
+    bias = relative_bias_dense(L, pos_w, ts_w, ts)
+    s = torch.einsum("thd,shd->hts", q[a:e].float(), k[a:e].float()) * scale
+    if bias is not None:
+      s = s + bias.float()
+    p = torch.nn.functional.silu(s) / max_seq_len
+    if causal:
+      p = torch.tril(p)
+    out[a:e] = torch.einsum("hts,shd->thd", p, v[a:e].float())
+  return out.to(q.dtype)
+
+
+class _JaggedAttnFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, q, k, v, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale):
+    from recml_b200.ops import hstu_cuda
+    o = hstu_cuda.forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale)
+    ctx.save_for_backward(q, k, v, pos_w, ts_w, seq_offsets, timestamps)
+    ctx.meta = (max_seq_len, causal, scale)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    from recml_b200.ops import hstu_cuda
+    q, k, v, pos_w, ts_w, seq_offsets, timestamps = ctx.saved_tensors
+    max_seq_len, causal, scale = ctx.meta
+    dq, dk, dv, dpos, dts = hstu_cuda.backward(do.contiguous(), q, k, v, seq_offsets, timestamps, pos_w, ts_w,
+                                               max_seq_len, causal, scale)
+    return dq, dk, dv, dpos, dts, None, None, None, None, None
+
+
+def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
+                               timestamps=None, causal: bool = True, scale: float = 1.0):
+  """Packed HSTU attention.  CUDA bf16 inputs with head dim 64 or 128 run the sm_100a kernel;
+  everything else takes the torch oracle (differentiable through autograd)."""
+  if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
+    from recml_b200.ops import hstu_cuda
+    if hstu_cuda.available():
+      return _JaggedAttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), pos_w, ts_w,
+                                 seq_offsets.to(torch.int32), timestamps, max_seq_len, causal, scale)
+  return jagged_attention_reference(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
+                                    timestamps=timestamps, causal=causal, scale=scale)

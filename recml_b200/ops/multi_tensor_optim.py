@@ -39,14 +39,42 @@ def _check_layout(lib):
     _checked = True
 
 
+RING = 512
+
+
+def _hyper_for(opt, lr: float, t: int, sq_ptr) -> _Hyper:
+  kind = {"identity": 0, "adam": 1, "rss": 2}[opt.scaling.kind]
+  return _Hyper(kind, lr, opt.scaling.b1, opt.scaling.b2, opt.scaling.eps, 1.0 - opt.scaling.b1 ** t,
+                1.0 - opt.scaling.b2 ** t, opt.weight_decay or 0.0, opt.grad_clip_norm or 0.0, sq_ptr)
+
+
+def push_hyper(opt, lr: float, t: int) -> None:
+  """Writes the step's hyper-parameters into the optimizer's device struct (stream-ordered copy
+  from a ring of pinned slots, so the host may run ahead of the GPU)."""
+  if not hasattr(opt, "_hyper_dev"):
+    dev = opt.params[0].device
+    opt._hyper_dev = torch.zeros(ctypes.sizeof(_Hyper), dtype=torch.uint8, device=dev)
+    opt._hyper_ring = torch.zeros(RING, ctypes.sizeof(_Hyper), dtype=torch.uint8).pin_memory()
+    opt._hyper_slot = 0
+    opt._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+  h = _hyper_for(opt, lr, t, opt._sq.data_ptr() if opt.grad_clip_norm is not None else None)
+  slot = opt._hyper_ring[opt._hyper_slot % RING]
+  opt._hyper_slot += 1
+  ctypes.memmove(slot.data_ptr(), ctypes.addressof(h), ctypes.sizeof(_Hyper))
+  opt._hyper_dev.copy_(slot, non_blocking=True)
+
+
 def fused_step(opt, live: list[int], grads: list[torch.Tensor], lr: float):
   """Runs the update for `opt` (an `optim_factory.Optimizer`) on CUDA; returns the grad norm
-  tensor when clipping is on."""
+  tensor when clipping is on.  Hyper-parameters are read by the kernel from device memory, so the
+  same launch sequence is valid inside a captured CUDA graph."""
+  from recml_b200.utils import graphs
   lib = _lib.cuda()
   _check_layout(lib)
   kind = {"identity": 0, "adam": 1, "rss": 2}[opt.scaling.kind]
   t = opt.count + 1
-  dev = opt.params[live[0]].device
+  if not graphs.capturing():
+    push_hyper(opt, lr, t)       # during capture the copy is issued by graph_pre_replay instead
   grads = [g if (g.dtype == torch.float32 and g.is_contiguous()) else g.to(torch.float32).contiguous()
            for g in grads]
   lists = []
@@ -74,14 +102,14 @@ def fused_step(opt, live: list[int], grads: list[torch.Tensor], lr: float):
     lists.append(tl)
   sq = None
   if opt.grad_clip_norm is not None:
-    sq = torch.zeros(1, dtype=torch.float32, device=dev)
+    sq = opt._sq
+    sq.zero_()
     for tl in lists:
       _lib.check_rc(lib.recml_optim_sqnorm(ctypes.byref(tl), _lib.ptr(sq), _lib.stream()), "optim_sqnorm")
-  h = _Hyper(kind, lr, opt.scaling.b1, opt.scaling.b2, opt.scaling.eps, 1.0 - opt.scaling.b1 ** t,
-             1.0 - opt.scaling.b2 ** t, opt.weight_decay or 0.0, opt.grad_clip_norm or 0.0,
-             sq.data_ptr() if sq is not None else None)
+  h = _hyper_for(opt, lr, t, None)
   for tl in lists:
-    _lib.check_rc(lib.recml_optim_step(ctypes.byref(tl), ctypes.byref(h), _lib.stream()), "optim_step")
+    _lib.check_rc(lib.recml_optim_step(ctypes.byref(tl), ctypes.byref(h), _lib.ptr(opt._hyper_dev),
+                                       _lib.stream()), "optim_step")
   for i in live:
     p = opt.params[i]
     if getattr(p, "_recml_bf16", None) is not None:

@@ -106,6 +106,9 @@ class Optimizer:
           torch.full_like(p, scaling.initial_accumulator_value, dtype=torch.float32)
           for p in self.params]
     self.last_grad_norm: torch.Tensor | None = None
+    if self.params and self.params[0].is_cuda:
+      from recml_b200.utils import graphs
+      graphs.register(self)
 
   def _lr_at(self, step: int) -> float:
     return float(self.lr(step)) if callable(self.lr) else float(self.lr)
@@ -159,6 +162,22 @@ class Optimizer:
         u = u + self.weight_decay * p.to(torch.float32)
       p.add_(u.to(p.dtype), alpha=-lr)
     self.count += 1
+
+  # -- CUDA-graph protocol (`recml_b200.utils.graphs`) ---------------------------------------------
+  def graph_snapshot(self):
+    return self.count
+
+  def graph_restore(self, count) -> None:
+    self.count = count
+
+  def graph_advance(self) -> None:
+    self.count += 1
+
+  def graph_pre_replay(self) -> None:
+    from recml_b200.ops import multi_tensor_optim
+    lr = self._lr_at(self.count)
+    self.hyperparams["learning_rate"] = lr
+    multi_tensor_optim.push_hyper(self, lr, self.count + 1)
 
   def zero_grad(self) -> None:
     for p in self.params:

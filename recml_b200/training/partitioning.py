@@ -114,8 +114,11 @@ class DataParallelPartitioner(NullPartitioner):
   """
 
   def __init__(self, data_axis: str = "batch", *, group: Any = None,
-               inputs_are_global: bool = False, device=None, grad_dtype: torch.dtype | None = None):
+               inputs_are_global: bool = False, device=None, grad_dtype: torch.dtype | None = None,
+               use_cuda_graph: bool = False, graph_warmup_steps: int = 3):
     super().__init__(device)
+    self.use_cuda_graph = use_cuda_graph
+    self.graph_warmup_steps = graph_warmup_steps
     self.data_axis = data_axis
     self.group = group
     self.inputs_are_global = inputs_are_global
@@ -167,6 +170,15 @@ class DataParallelPartitioner(NullPartitioner):
     def wrapped(batch):
       return self._replicate(init_fn(batch))
     return wrapped
+
+
+  def partition_step(self, fn, *, training: bool = False):
+    """With `use_cuda_graph` the training step is recorded into CUDA graphs after a few eager
+    warm-up steps and replayed afterwards (fixed input shapes required)."""
+    if training and self.use_cuda_graph and self.device.type == "cuda":
+      from recml_b200.utils import graphs
+      return graphs.GraphedStep(fn, warmup=self.graph_warmup_steps)
+    return fn
 
 
 class ModelParallelPartitioner(DataParallelPartitioner):

@@ -118,7 +118,7 @@ def allreduce_grads(rank, world, device_type, sizes):
   return {"max_rel_err": results, "reducer": type(red).__name__}
 
 
-def dlrm_tiny_training(rank, world, device_type, steps):
+def dlrm_tiny_training(rank, world, device_type, steps, use_graph=False):
   """BASELINE config 1 (tiny DLRM-DCNv2) as a data-parallel + sharded-embedding job."""
   import tempfile
   from recml_b200 import config as C, run_experiment
@@ -129,6 +129,8 @@ def dlrm_tiny_training(rank, world, device_type, steps):
   cfg = D.tiny_experiment(model_dir=box[0], train_steps=steps, batch_size=256)
   if device_type == "cpu":
     cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, device="cpu")
+  if use_graph:
+    cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, use_cuda_graph=True)
   exp = C.build(cfg)
   logs = run_experiment(exp, "train_and_eval")
   import os as _os

@@ -36,3 +36,8 @@ def test_fused_allreduce_two_gpus():
 def test_dlrm_tiny_two_gpus():
   res = dist_utils.run_ranks("dlrm_tiny_training", 2, "nccl", "cuda", 60)
   assert res[0]["loss"] < 0.62
+
+
+def test_dlrm_tiny_two_gpus_cuda_graph():
+  res = dist_utils.run_ranks("dlrm_tiny_training", 2, "nccl", "cuda", 60, True)
+  assert res[0]["loss"] < 0.62

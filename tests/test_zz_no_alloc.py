@@ -43,7 +43,7 @@ def _params(fused, keys, vals, grads, count, table, slot, scratch, status, dim):
     bp.hp[i] = v
   bp.grad_scale = 1.0
   bp.scratch = None if scratch is None else scratch.data_ptr()
-  bp.wait_flags, bp.W, bp.wait_seq, bp.status = None, 1, 0, status.data_ptr()
+  bp.wait_flags, bp.W, bp.status = None, 1, status.data_ptr()
   return bp
 
 
