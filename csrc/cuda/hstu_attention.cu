@@ -1,0 +1,293 @@
+// Jagged HSTU attention for sm_100a:  O = mask( silu(Q·K^T·scale + bias) / n ) · V   per sequence,
+// with the learned relative-position and time-bucket bias evaluated in the kernel.
+//
+// Sequences are packed back to back ([T, H, Dh] bf16, seq_offsets[B+1]).  One CTA owns a 128-query
+// tile of one sequence and one head and walks over the key/value tiles it may see (causal: tiles up
+// to its own).  Per key tile:
+//   TMA (warp 0)        K_j, V_j -> shared memory (2 stages)
+//   tcgen05.mma (warp 1) S = Q·K_j^T into tensor memory
+//   warps 2..5           tcgen05.ld S; p = silu(s·scale + pos_w[kj-qi+N-1] + ts_w[bucket(Δt)]) / n;
+//                        causal / length mask; bf16 P written to shared memory in the 128-byte-swizzled
+//                        K-major layout the tensor core expects
+//   tcgen05.mma (warp 1) O += P·V_j    (V consumed as an MN-major operand straight from its [kv, Dh] tile)
+// The backward kernel (one CTA per key tile and head, walking over the query tiles that see it)
+// recomputes S and forms dV += P^T·dO, dK += dS^T·Q, dQ += dS·K on the tensor cores, with
+// dS = dP ⊙ d/ds[silu]/n and the bias gradients reduced through shared-memory histograms.
+// All waits are bounded; a CTA that gives up drains and frees its tensor memory.
+#include "tcgen05.cuh"
+
+namespace recml {
+namespace hstu {
+using namespace recml::tc;
+
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int kThreads = 192;
+constexpr float kBucketSize = 0.301f;
+
+struct Params {
+  int T, H, Dh, B, max_seq_len, num_buckets, causal;
+  float scale, inv_n;
+  const int* seq_offsets;
+  const int* tile_seq;        // [n_tiles] sequence of each 128-row tile (-1: unused slot)
+  const int* tile_row0;       // [n_tiles] first position (within the sequence) of the tile
+  const long long* timestamps;
+  const float* pos_w;
+  const float* ts_w;
+  __nv_bfloat16* out;         // fwd: O [T, H*Dh]
+  // backward only
+  float* dq;                  // [T, H*Dh] fp32, accumulated with atomics (pre-zeroed)
+  __nv_bfloat16* dk;          // [T, H*Dh]
+  __nv_bfloat16* dv;
+  float* dpos_w;              // [2N-1] (pre-zeroed) or null
+  float* dts_w;               // [num_buckets+1] (pre-zeroed) or null
+  int* status;
+};
+
+// Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
+// position tile_row0[t].  Slots beyond the real number of tiles keep -1.
+__global__ void tile_list_kernel(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int t = 0;
+  // longest-first within a sequence (late tiles see the most keys), sequences in order
+  for (int b = 0; b < B; ++b) {
+    const int L = seq_offsets[b + 1] - seq_offsets[b];
+    const int n = (L + BQ - 1) / BQ;
+    for (int i = n - 1; i >= 0 && t < cap; --i, ++t) { tile_seq[t] = b; tile_row0[t] = i * BQ; }
+  }
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ int time_bucket(long long dt, int num_buckets) {
+  long long a = dt < 0 ? -dt : dt;
+  a = a < 1 ? 1 : (a > 1000000000LL ? 1000000000LL : a);
+  const int b = static_cast<int>(logf(static_cast<float>(a)) / kBucketSize);
+  return b < 0 ? 0 : (b > num_buckets ? num_buckets : b);
+}
+
+template <int DH>
+struct Smem {
+  static constexpr int kSub = DH / 64;                 // 64-column sub-tiles per operand tile
+  static constexpr int kTile = BQ * 64 * 2 * kSub;     // bytes of one [128, DH] bf16 tile
+  static constexpr int kQ = 0;
+  static constexpr int kK = kTile;                     // 2 stages
+  static constexpr int kV = kK + 2 * kTile;            // 2 stages
+  static constexpr int kP = kV + 2 * kTile;            // [128, 128] bf16 = 32 KB
+  static constexpr int kBars = kP + BQ * BKV * 2;
+  static constexpr int kTs = kBars + 128;              // key timestamps of the current tile (2 x 128 x 8 B)
+  static constexpr int kTotal = kTs + 2 * BKV * 8 + 1024;
+  static constexpr int kTmemCols = 256;                // S: 128 columns, O: DH columns
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const Params p) {
+  using S = Smem<DH>;
+  const int seq = p.tile_seq[blockIdx.x];
+  if (seq < 0) return;   // whole CTA leaves before touching barriers or tensor memory
+  const int h = blockIdx.y;
+  const int q0 = p.tile_row0[blockIdx.x];
+  const int seq_start = p.seq_offsets[seq];
+  const int L = p.seq_offsets[seq + 1] - seq_start;
+  const int tok0 = seq_start + q0;
+  const int n_kv = p.causal ? (q0 / BKV + 1) : (L + BKV - 1) / BKV;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + S::kBars;
+  // barrier slots: 0 q_full, 1-2 kv_full, 3-4 kv_empty, 5 s_full, 6 s_empty, 7 p_full, 8 p_empty, 9 o_full
+  auto bar = [&](int i) { return bars + 8u * i; };
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(bar(0), 1);
+    mbar_init(bar(1), 1); mbar_init(bar(2), 1);
+    mbar_init(bar(3), 1); mbar_init(bar(4), 1);
+    mbar_init(bar(5), 1);
+    mbar_init(bar(6), 128);
+    mbar_init(bar(7), 128);
+    mbar_init(bar(8), 1);
+    mbar_init(bar(9), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 128;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(0), S::kTile);
+      for (int d = 0; d < S::kSub; ++d) tma_load_2d(base + S::kQ + d * 16384, &map_q, h * DH + 64 * d, tok0, bar(0));
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(bar(3 + s), ((j >> 1) & 1) ^ 1, abortp, p.status, 40)) break;
+        mbar_expect_tx(bar(1 + s), 2 * S::kTile);
+        const int row = seq_start + j * BKV;
+        for (int d = 0; d < S::kSub; ++d) {
+          tma_load_2d(base + S::kK + s * S::kTile + d * 16384, &map_k, h * DH + 64 * d, row, bar(1 + s));
+          tma_load_2d(base + S::kV + s * S::kTile + d * 16384, &map_v, h * DH + 64 * d, row, bar(1 + s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);
+      const uint32_t idesc_o = idesc_bf16(BQ, DH, false, true);
+      bool ok = mbar_wait(bar(0), 0, abortp, p.status, 41);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(bar(1 + s), (j >> 1) & 1, abortp, p.status, 42)) break;
+        if (j > 0 && !mbar_wait(bar(6), (j - 1) & 1, abortp, p.status, 43)) break;   // S of tile j-1 has been read
+        tc_fence_after();
+        const uint32_t sk = base + S::kK + s * S::kTile, sv = base + S::kV + s * S::kTile;
+#pragma unroll
+        for (int d = 0; d < S::kSub; ++d)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_bf16(tmem_s, make_desc(base + S::kQ + d * 16384 + k * 32, 16, 1024),
+                        make_desc(sk + d * 16384 + k * 32, 16, 1024), idesc_s, (d | k) ? 1u : 0u);
+        tc_commit(bar(5));
+        if (!mbar_wait(bar(7), j & 1, abortp, p.status, 44)) break;   // P_j written
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          tc_mma_bf16(tmem_o, make_desc(base + S::kP + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                      make_desc(sv + kk * 2048, 16384, 1024), idesc_o, (j | kk) ? 1u : 0u);
+        tc_commit(bar(3 + s));   // K_j / V_j stage free
+        tc_commit(bar(8));       // P buffer free
+      }
+      tc_commit(bar(9));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qi = q0 + r;
+    const bool row_ok = qi < L;
+    long long tq = 0;
+    if (p.timestamps != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int kv0 = j * BKV;
+      if (!mbar_wait(bar(5), j & 1, abortp, p.status, 45)) { ok = false; break; }
+      tc_fence_after();
+      if (j > 0 && !mbar_wait(bar(8), (j - 1) & 1, abortp, p.status, 46)) { ok = false; break; }
+      // key timestamps are read straight from global memory: all lanes of a warp ask for the same
+      // address at the same time, so each read is one broadcast transaction served by L1
+      const long long* tsk = p.timestamps != nullptr ? p.timestamps + seq_start + kv0 : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s + lane_off + c * 32, v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pr[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kj = kv0 + c * 32 + e + u;
+            float x = __uint_as_float(v[e + u]) * p.scale;
+            const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+            if (visible) {
+              if (p.pos_w != nullptr) x += __ldg(p.pos_w + (kj - qi) + p.max_seq_len - 1);
+              if (p.ts_w != nullptr) x += __ldg(p.ts_w + time_bucket(tq - __ldg(tsk + c * 32 + e + u), p.num_buckets));
+              pr[u] = silu(x) * p.inv_n;
+            } else {
+              pr[u] = 0.f;
+            }
+          }
+          packed[e >> 1] = pack_bf16(pr[0], pr[1]);
+        }
+        // 32 columns = 64 bytes = four 16-byte chunks of row r in sub-tile c/2
+        uint8_t* row_ptr = base_ptr + S::kP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
+              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(6));     // S may be overwritten
+      fence_async_smem();
+      mbar_arrive(bar(7));     // P is in shared memory
+    }
+    if (ok && mbar_wait(bar(9), 0, abortp, p.status, 47)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_off + c * 32, v);
+        if (row_ok) {
+          __nv_bfloat16* dst = p.out + static_cast<size_t>(tok0 + r) * p.H * DH + h * DH + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(dst + g * 8) =
+                make_uint4(pack_bf16(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                           pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                           pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                           pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+        }
+      }
+    }
+  }
+  if (*abortp) {
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_slot, S::kTmemCols);
+  }
+}
+
+}  // namespace hstu
+}  // namespace recml
+
+using namespace recml::hstu;
+
+extern "C" int recml_hstu_struct_size() { return static_cast<int>(sizeof(Params)); }
+
+extern "C" int recml_hstu_tile_list(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap,
+                                    cudaStream_t stream) {
+  cudaMemsetAsync(tile_seq, 0xFF, sizeof(int) * cap, stream);
+  tile_list_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, tile_seq, tile_row0, cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+template <int DH>
+static int launch_fwd(const void* q, const void* k, const void* v, const Params& p, int n_tiles, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  const long long cols = static_cast<long long>(p.H) * DH;
+  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, cols, BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, cols, BKV) ||
+      recml::tc::make_map_bf16(&mv, v, p.T, cols, cols, BKV))
+    return -2;
+  auto kern = hstu_fwd_kernel<DH>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<DH>::kTotal) != cudaSuccess) return -3;
+    configured = true;
+  }
+  dim3 grid(n_tiles, p.H);
+  kern<<<grid, kThreads, Smem<DH>::kTotal, stream>>>(mq, mk, mv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// q, k, v: [T, H, Dh] bf16 contiguous.  n_tiles: capacity of the tile list (>= number of real tiles).
+extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, const Params* p, int n_tiles,
+                                   cudaStream_t stream) {
+  if (p->T <= 0 || n_tiles <= 0) return 0;
+  if (p->Dh == 64) return launch_fwd<64>(q, k, v, *p, n_tiles, stream);
+  if (p->Dh == 128) return launch_fwd<128>(q, k, v, *p, n_tiles, stream);
+  return -10;
+}

@@ -1,0 +1,113 @@
+"""ctypes driver of the jagged HSTU attention kernels (`csrc/cuda/hstu_attention.cu`)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from recml_b200.ops import _lib
+
+c_int, c_float, c_vp = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+class _Params(ctypes.Structure):
+  _fields_ = [("T", c_int), ("H", c_int), ("Dh", c_int), ("B", c_int), ("max_seq_len", c_int),
+              ("num_buckets", c_int), ("causal", c_int), ("scale", c_float), ("inv_n", c_float),
+              ("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("timestamps", c_vp),
+              ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
+              ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp)]
+
+
+_ok: bool | None = None
+
+
+def available() -> bool:
+  global _ok
+  if _ok is None:
+    try:
+      _ok = int(_lib.cuda().recml_hstu_struct_size()) == ctypes.sizeof(_Params)
+    except Exception:  # pylint: disable=broad-except
+      _ok = False
+  return _ok
+
+
+def _tiles(seq_offsets: torch.Tensor, T: int):
+  B = seq_offsets.numel() - 1
+  cap = (T + 127) // 128 + B
+  tile_seq = torch.empty(cap, dtype=torch.int32, device=seq_offsets.device)
+  tile_row0 = torch.zeros(cap, dtype=torch.int32, device=seq_offsets.device)
+  _lib.check_rc(_lib.cuda().recml_hstu_tile_list(_lib.ptr(seq_offsets), c_int(B), _lib.ptr(tile_seq),
+                                                 _lib.ptr(tile_row0), c_int(cap), _lib.stream()), "hstu_tile_list")
+  return tile_seq, tile_row0, cap
+
+
+def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles):
+  T, H, Dh = q.shape
+  p = _Params()
+  p.T, p.H, p.Dh, p.B, p.max_seq_len = T, H, Dh, seq_offsets.numel() - 1, max_seq_len
+  p.num_buckets = ts_w.numel() - 1 if ts_w is not None else 0
+  p.causal, p.scale, p.inv_n = int(causal), scale, 1.0 / max_seq_len
+  p.seq_offsets, p.tile_seq, p.tile_row0 = seq_offsets.data_ptr(), tiles[0].data_ptr(), tiles[1].data_ptr()
+  p.timestamps = timestamps.data_ptr() if (timestamps is not None and ts_w is not None) else None
+  p.pos_w = pos_w.data_ptr() if pos_w is not None else None
+  p.ts_w = ts_w.data_ptr() if (ts_w is not None and timestamps is not None) else None
+  p.status = _lib.status_buffer(q.device).data_ptr()
+  return p
+
+
+def forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
+  assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.bfloat16
+  if timestamps is not None:
+    timestamps = timestamps.to(torch.int64).contiguous()
+  pos_w = None if pos_w is None else pos_w.detach().float().contiguous()
+  ts_w = None if ts_w is None else ts_w.detach().float().contiguous()
+  tiles = _tiles(seq_offsets, q.shape[0])
+  out = torch.empty_like(q)
+  p = _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles)
+  p.out = out.data_ptr()
+  keep = (timestamps, pos_w, ts_w, tiles)  # referenced until the launch is enqueued
+  _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
+                                                c_int(tiles[2]), _lib.stream()), "hstu_attn_fwd")
+  del keep
+  return out
+
+
+def backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
+  """Gradients w.r.t. q, k, v, pos_w, ts_w."""
+  lib = _lib.cuda()
+  if not hasattr(lib._lib, "recml_hstu_attn_bwd"):
+    return _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale)
+  if timestamps is not None:
+    timestamps = timestamps.to(torch.int64).contiguous()
+  pw = None if pos_w is None else pos_w.detach().float().contiguous()
+  tw = None if ts_w is None else ts_w.detach().float().contiguous()
+  tiles = _tiles(seq_offsets, q.shape[0])
+  dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+  dk, dv = torch.empty_like(k), torch.empty_like(v)
+  dpos = torch.zeros_like(pw) if pw is not None else None
+  dts = torch.zeros_like(tw) if (tw is not None and timestamps is not None) else None
+  p = _params(q, seq_offsets, timestamps, pw, tw, max_seq_len, causal, scale, tiles)
+  p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+  p.dpos_w = dpos.data_ptr() if dpos is not None else None
+  p.dts_w = dts.data_ptr() if dts is not None else None
+  _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do.contiguous()),
+                                        ctypes.byref(p), c_int(tiles[2]), _lib.stream()), "hstu_attn_bwd")
+  return (dq.to(q.dtype), dk, dv, None if dpos is None else dpos.to(pos_w.dtype),
+          None if ts_w is None else (dts.to(ts_w.dtype) if dts is not None else torch.zeros_like(ts_w)))
+
+
+def _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
+  from recml_b200.ops import hstu_attention as A
+  with torch.enable_grad():
+    leaves = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    pw = None if pos_w is None else pos_w.detach().float().requires_grad_()
+    tw = None if ts_w is None else ts_w.detach().float().requires_grad_()
+    o = A.jagged_attention_reference(*leaves, seq_offsets, max_seq_len, pos_w=pw, ts_w=tw, timestamps=timestamps,
+                                     causal=causal, scale=scale)
+    params = leaves + [t for t in (pw, tw) if t is not None]
+    grads = list(torch.autograd.grad(o, params, do.float(), allow_unused=True))
+  dq, dk, dv = (g.to(q.dtype) for g in grads[:3])
+  rest = grads[3:]
+  dpos = rest.pop(0) if pw is not None else None
+  dts = rest.pop(0) if tw is not None else None
+  return dq, dk, dv, dpos, dts

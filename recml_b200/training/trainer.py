@@ -236,7 +236,9 @@ class Trainer(core.Trainer[task_lib.Task]):
       state = self._maybe_restore_checkpoint(state)
 
     def _train(inputs, st):
-      step_rng.manual_seed(self._rng_seed + 1 + st.step)  # fold the step into the stream
+      from recml_b200.utils import graphs
+      if not graphs.capturing():   # reseeding a CUDA generator is not allowed while a graph records
+        step_rng.manual_seed(self._rng_seed + 1 + st.step)  # fold the step into the stream
       return task.train_step(inputs, st, step_rng)
 
     train_step = self._partitioner.partition_step(_train, training=True)

@@ -1,0 +1,56 @@
+"""Jagged HSTU attention kernels vs the fp32 torch formula (the reference's own kernel test compares
+against the dense formula with atol = rtol = 5e-3, `recml/core/ops/hstu_ops_test.py:45-70`)."""
+import numpy as np
+import pytest
+import torch
+
+from recml_b200.ops import _lib, hstu_attention as A
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(lengths, H, Dh, seed=0, with_bias=True, N=None):
+  g = torch.Generator().manual_seed(seed)
+  T = int(sum(lengths))
+  q, k, v = (torch.randn(T, H, Dh, generator=g).mul(0.5).to(torch.bfloat16) for _ in range(3))
+  offs = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32)
+  N = N or max(lengths)
+  pos_w = torch.randn(2 * N - 1, generator=g) * 0.3 if with_bias else None
+  ts_w = torch.randn(129, generator=g) * 0.3 if with_bias else None
+  rng = np.random.default_rng(seed)
+  ts = torch.from_numpy(np.concatenate([1_600_000_000 + np.cumsum(rng.exponential(3600.0, L)).astype(np.int64)
+                                        for L in lengths])) if with_bias else None
+  return q, k, v, offs, N, pos_w, ts_w, ts
+
+
+@pytest.mark.parametrize("lengths,H,Dh,bias", [([128], 1, 64, False), ([5, 128, 300, 1, 77], 2, 64, True),
+                                               ([700, 33], 4, 64, True), ([260, 130], 2, 128, True)])
+def test_forward_matches_reference(lengths, H, Dh, bias):
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, with_bias=bias)
+  ref = A.jagged_attention_reference(q.float(), k.float(), v.float(), offs, N, pos_w=pos_w, ts_w=ts_w, timestamps=ts)
+  cu = lambda t: None if t is None else t.cuda()
+  out = A.jagged_pointwise_attention(q.cuda(), k.cuda(), v.cuda(), offs.cuda(), N, pos_w=cu(pos_w), ts_w=cu(ts_w),
+                                     timestamps=cu(ts))
+  torch.cuda.synchronize()
+  _lib.check_status()
+  err = (out.float().cpu() - ref).abs().max().item()
+  scale = ref.abs().max().item() + 1e-6
+  assert err / scale < 2e-2, (err, scale)
+
+
+def test_backward_matches_reference():
+  lengths, H, Dh = [200, 64, 391], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=3)
+  leaves = [t.float().requires_grad_() for t in (q, k, v)] + [pos_w.clone().requires_grad_(), ts_w.clone().requires_grad_()]
+  ref = A.jagged_attention_reference(leaves[0], leaves[1], leaves[2], offs, N, pos_w=leaves[3], ts_w=leaves[4], timestamps=ts)
+  go = torch.randn(ref.shape, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+  ref.backward(go.float())
+  gl = [t.cuda().requires_grad_() for t in (q, k, v)] + [pos_w.cuda().requires_grad_(), ts_w.cuda().requires_grad_()]
+  out = A.jagged_pointwise_attention(gl[0], gl[1], gl[2], offs.cuda(), N, pos_w=gl[3], ts_w=gl[4], timestamps=ts.cuda())
+  out.backward(go.cuda())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  for name, a, b in zip("q k v pos_w ts_w".split(), gl, leaves):
+    err = (a.grad.float().cpu() - b.grad).abs().max().item()
+    scale = b.grad.abs().max().item() + 1e-6
+    assert err / scale < 3e-2, (name, err, scale)
