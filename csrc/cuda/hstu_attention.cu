@@ -251,6 +251,267 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
+// =============================================== backward ===============================================
+template <int DH>
+struct SmemB {
+  static constexpr int kSub = DH / 64;
+  static constexpr int kTile = BQ * 64 * 2 * kSub;
+  static constexpr int kStages = DH == 64 ? 2 : 1;      // Q_i / dO_i ring
+  static constexpr int kK = 0;
+  static constexpr int kV = kTile;
+  static constexpr int kQ = 2 * kTile;
+  static constexpr int kDO = kQ + kStages * kTile;
+  static constexpr int kP = kDO + kStages * kTile;      // [128 q, 128 kv] bf16
+  static constexpr int kDS = kP + BQ * BKV * 2;
+  static constexpr int kBars = kDS + BQ * BKV * 2;
+  static constexpr int kHist = kBars + 128;             // 2 x 256 diagonal bins (by step parity) + 256 time bins, fp32
+  static constexpr int kTotal = kHist + 768 * 4 + 1024;
+  // tensor memory columns: [0,128) S then dQ, [128,256) dP, [256,256+DH) dV, [256+DH,256+2DH) dK
+  static constexpr int kTmemCols = 512;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const Params p) {
+  using S = SmemB<DH>;
+  const int seq = p.tile_seq[blockIdx.x];
+  if (seq < 0) return;
+  const int h = blockIdx.y;
+  const int kv0 = p.tile_row0[blockIdx.x];
+  const int seq_start = p.seq_offsets[seq];
+  const int L = p.seq_offsets[seq + 1] - seq_start;
+  const int n_q_total = (L + BQ - 1) / BQ;
+  const int i_first = p.causal ? kv0 / BQ : 0;
+  const int n_it = n_q_total - i_first;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + S::kBars;
+  // 0 kv_full, 1-2 qdo_full, 3-4 qdo_empty, 5 sp_full, 6 pds_full, 7 dq_full, 8 dq_empty, 9 final
+  auto bar = [&](int i) { return bars + 8u * i; };
+  float* hist = reinterpret_cast<float*>(base_ptr + S::kHist);   // [0,512) diagonals x2, [512,768) time buckets
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(bar(0), 1);
+    mbar_init(bar(1), 1); mbar_init(bar(2), 1);
+    mbar_init(bar(3), 1); mbar_init(bar(4), 1);
+    mbar_init(bar(5), 1);
+    mbar_init(bar(6), 128);
+    mbar_init(bar(7), 1);
+    mbar_init(bar(8), 128);
+    mbar_init(bar(9), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < 768; i += kThreads) hist[i] = 0.f;
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = tmem_slot, tmem_dp = tmem_slot + 128, tmem_dv = tmem_slot + 256,
+                 tmem_dk = tmem_slot + 256 + DH;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(0), 2 * S::kTile);
+      for (int d = 0; d < S::kSub; ++d) {
+        tma_load_2d(base + S::kK + d * 16384, &map_k, h * DH + 64 * d, seq_start + kv0, bar(0));
+        tma_load_2d(base + S::kV + d * 16384, &map_v, h * DH + 64 * d, seq_start + kv0, bar(0));
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % S::kStages;
+        if (!mbar_wait(bar(3 + st), ((it / S::kStages) & 1) ^ 1, abortp, p.status, 50)) break;
+        mbar_expect_tx(bar(1 + st), 2 * S::kTile);
+        const int row = seq_start + (i_first + it) * BQ;
+        for (int d = 0; d < S::kSub; ++d) {
+          tma_load_2d(base + S::kQ + st * S::kTile + d * 16384, &map_q, h * DH + 64 * d, row, bar(1 + st));
+          tma_load_2d(base + S::kDO + st * S::kTile + d * 16384, &map_do, h * DH + 64 * d, row, bar(1 + st));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);     // S = Q·K^T, dP = dO·V^T
+      const uint32_t idesc_t = idesc_bf16(BKV, DH, true, true);       // dV = P^T·dO, dK = dS^T·Q
+      const uint32_t idesc_q = idesc_bf16(BQ, DH, false, true);       // dQ = dS·K
+      bool ok = mbar_wait(bar(0), 0, abortp, p.status, 51);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % S::kStages;
+        if (!mbar_wait(bar(1 + st), (it / S::kStages) & 1, abortp, p.status, 52)) break;
+        if (it > 0 && !mbar_wait(bar(8), (it - 1) & 1, abortp, p.status, 53)) break;   // dQ of tile it-1 read out
+        tc_fence_after();
+        const uint32_t sq = base + S::kQ + st * S::kTile, sdo = base + S::kDO + st * S::kTile;
+#pragma unroll
+        for (int d = 0; d < S::kSub; ++d)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tc_mma_bf16(tmem_s, make_desc(sq + d * 16384 + k * 32, 16, 1024),
+                        make_desc(base + S::kK + d * 16384 + k * 32, 16, 1024), idesc_s, (d | k) ? 1u : 0u);
+            tc_mma_bf16(tmem_dp, make_desc(sdo + d * 16384 + k * 32, 16, 1024),
+                        make_desc(base + S::kV + d * 16384 + k * 32, 16, 1024), idesc_s, (d | k) ? 1u : 0u);
+          }
+        tc_commit(bar(5));
+        if (!mbar_wait(bar(6), it & 1, abortp, p.status, 54)) break;   // P and dS are in shared memory
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {   // contraction over the 128 query rows
+          tc_mma_bf16(tmem_dv, make_desc(base + S::kP + kk * 2048, 16384, 1024), make_desc(sdo + kk * 2048, 16384, 1024),
+                      idesc_t, (it | kk) ? 1u : 0u);
+          tc_mma_bf16(tmem_dk, make_desc(base + S::kDS + kk * 2048, 16384, 1024), make_desc(sq + kk * 2048, 16384, 1024),
+                      idesc_t, (it | kk) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)    // contraction over the 128 keys; dQ reuses S's columns
+          tc_mma_bf16(tmem_s, make_desc(base + S::kDS + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                      make_desc(base + S::kK + kk * 2048, 16384, 1024), idesc_q, kk ? 1u : 0u);
+        tc_commit(bar(7));           // dQ ready; P / dS / this Q,dO stage no longer read
+        tc_commit(bar(3 + st));
+      }
+      tc_commit(bar(9));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const long long* tsk = p.timestamps != nullptr ? p.timestamps + seq_start + kv0 : nullptr;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int q0 = (i_first + it) * BQ;
+      const int qi = q0 + r;
+      const bool row_ok = qi < L;
+      long long tq = 0;
+      if (p.timestamps != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+      if (!mbar_wait(bar(5), it & 1, abortp, p.status, 55)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dpv[32];
+        tmem_ld32(tmem_s + lane_off + c * 32, sv);
+        tmem_ld32(tmem_dp + lane_off + c * 32, dpv);
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pr[2], dr[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + e + u;
+            const int kj = kv0 + col;
+            pr[u] = 0.f; dr[u] = 0.f;
+            const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+            if (visible) {
+              float x = __uint_as_float(sv[e + u]) * p.scale;
+              int bucket = 0;
+              if (p.pos_w != nullptr) x += __ldg(p.pos_w + (kj - qi) + p.max_seq_len - 1);
+              if (p.ts_w != nullptr) {
+                bucket = time_bucket(tq - __ldg(tsk + col), p.num_buckets);
+                x += __ldg(p.ts_w + bucket);
+              }
+              const float sig = 1.f / (1.f + __expf(-x));
+              pr[u] = x * sig * p.inv_n;
+              const float ds = __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n;
+              dr[u] = ds;
+              // bias gradients: diagonal bin (kj - qi) - (kv0 - q0) + 127 in [0, 255); lanes of a warp hit
+              // distinct diagonals, so the shared-memory atomics do not collide inside a warp
+              if (p.dpos_w != nullptr) atomicAdd(hist + (it & 1) * 256 + (col - r + 127), ds);
+              if (p.dts_w != nullptr) atomicAdd(hist + 512 + bucket, ds);
+            }
+          }
+          pp[e >> 1] = pack_bf16(pr[0], pr[1]);
+          dd[e >> 1] = pack_bf16(dr[0], dr[1]);
+        }
+        uint8_t* prow = base_ptr + S::kP + (c >> 1) * 16384 + r * 128;
+        uint8_t* drow = base_ptr + S::kDS + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
+          *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(bar(6));
+      // dQ tile: wait for the three products of this step, then add it into the fp32 gradient
+      if (!mbar_wait(bar(7), it & 1, abortp, p.status, 56)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s + lane_off + c * 32, v);
+        if (row_ok) {
+          float* dst = p.dq + static_cast<size_t>(seq_start + qi) * p.H * DH + h * DH + c * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            atomicAdd(reinterpret_cast<float4*>(dst) + g,
+                      make_float4(__uint_as_float(v[4 * g]) * p.scale, __uint_as_float(v[4 * g + 1]) * p.scale,
+                                  __uint_as_float(v[4 * g + 2]) * p.scale, __uint_as_float(v[4 * g + 3]) * p.scale));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(8));
+      // flush the diagonal bins of this (q tile, kv tile) pair: 128 compute threads, 255 bins
+      if (p.dpos_w != nullptr) {
+        // every compute thread must be past its last histogram atomic: they all arrived on bar(6) before the
+        // dQ commit could complete, and this thread observed that commit
+        const int tid = threadIdx.x - 64;
+        for (int b = tid; b < 255; b += 128) {
+          const float val = atomicExch(hist + (it & 1) * 256 + b, 0.f);   // the other parity is being filled by step it+1
+          if (val != 0.f) atomicAdd(p.dpos_w + (kv0 - q0) + (b - 127) + p.max_seq_len - 1, val);
+        }
+      }
+    }
+    if (ok && mbar_wait(bar(9), 0, abortp, p.status, 57)) {
+      tc_fence_after();
+      const int kj = kv0 + r;
+      const bool kv_ok = kj < L;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32], w[32];
+        tmem_ld32(tmem_dv + lane_off + c * 32, v);
+        tmem_ld32(tmem_dk + lane_off + c * 32, w);
+        if (kv_ok) {
+          const size_t off = static_cast<size_t>(seq_start + kj) * p.H * DH + h * DH + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            *reinterpret_cast<uint4*>(p.dv + off + g * 8) =
+                make_uint4(pack_bf16(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                           pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                           pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                           pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+            *reinterpret_cast<uint4*>(p.dk + off + g * 8) =
+                make_uint4(pack_bf16(__uint_as_float(w[8 * g]) * p.scale, __uint_as_float(w[8 * g + 1]) * p.scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 2]) * p.scale, __uint_as_float(w[8 * g + 3]) * p.scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 4]) * p.scale, __uint_as_float(w[8 * g + 5]) * p.scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 6]) * p.scale, __uint_as_float(w[8 * g + 7]) * p.scale));
+          }
+        }
+      }
+    }
+  }
+  if (*abortp) {
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (p.dts_w != nullptr) {
+    for (int b = threadIdx.x; b <= p.num_buckets && b < 256; b += kThreads) {
+      const float val = hist[512 + b];
+      if (val != 0.f) atomicAdd(p.dts_w + b, val);
+    }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_slot, S::kTmemCols);
+  }
+}
+
 }  // namespace hstu
 }  // namespace recml
 
@@ -289,5 +550,36 @@ extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, 
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->Dh == 64) return launch_fwd<64>(q, k, v, *p, n_tiles, stream);
   if (p->Dh == 128) return launch_fwd<128>(q, k, v, *p, n_tiles, stream);
+  return -10;
+}
+
+template <int DH>
+static int launch_bwd(const void* q, const void* k, const void* v, const void* d_o, const Params& p, int n_tiles,
+                      cudaStream_t stream) {
+  CUtensorMap mq, mk, mv, mdo;
+  const long long cols = static_cast<long long>(p.H) * DH;
+  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, cols, BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, cols, BKV) ||
+      recml::tc::make_map_bf16(&mv, v, p.T, cols, cols, BKV) || recml::tc::make_map_bf16(&mdo, d_o, p.T, cols, cols, BQ))
+    return -2;
+  auto kern = hstu_bwd_kernel<DH>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB<DH>::kTotal) != cudaSuccess) return -3;
+    configured = true;
+  }
+  dim3 grid(n_tiles, p.H);
+  kern<<<grid, kThreads, SmemB<DH>::kTotal, stream>>>(mq, mk, mv, mdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// dq (fp32), dpos_w, dts_w must be zero on entry; dk / dv are fully written for every token.
+// Rows whose key tile contains no query that sees them still get written (with zeros) because every
+// key tile of every sequence has a CTA.
+extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const Params* p,
+                                   int n_tiles, cudaStream_t stream) {
+  if (p->T <= 0 || n_tiles <= 0) return 0;
+  if (p->num_buckets + 1 > 256) return -11;
+  if (p->Dh == 64) return launch_bwd<64>(q, k, v, d_o, *p, n_tiles, stream);
+  if (p->Dh == 128) return launch_bwd<128>(q, k, v, d_o, *p, n_tiles, stream);
   return -10;
 }
