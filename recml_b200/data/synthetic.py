@@ -99,3 +99,27 @@ class SyntheticDLRMDataset:
     while self.steps is None or i < self.steps:
       yield self.batches[i % len(self.batches)]
       i += 1
+
+
+def make_hstu_batch(rng: np.random.Generator, num_sequences: int, vocab: int, *, min_len: int = 16,
+                    max_len: int = 4096, mean_target: int = 512, alpha_len: float = 1.2, alpha_ids: float = 1.05,
+                    num_negatives: int = 512, token_capacity: int | None = None) -> dict:
+    """Packed next-item batch: power-law lengths, Zipf item ids, Exponential(1 h) timestamp gaps,
+    shared uniform negatives.  Lengths are rescaled so their mean is close to `mean_target` and the
+    total fits `token_capacity`."""
+    lens = powerlaw_lengths(rng, num_sequences, min_len, max_len, alpha_len).astype(np.float64)
+    lens = np.clip(np.round(lens * mean_target / max(lens.mean(), 1.0)), min_len, max_len).astype(np.int64)
+    if token_capacity is not None:
+        while lens.sum() > token_capacity:
+            lens[np.argmax(lens)] = max(min_len, lens.max() // 2)
+    T = int(lens.sum())
+    ids = zipf_ids(rng, vocab, (T + 1,), alpha_ids)
+    offs = np.zeros(num_sequences + 1, dtype=np.int32)
+    offs[1:] = np.cumsum(lens)
+    targets = ids[1:T + 1].copy()
+    weights = np.ones(T, dtype=np.float32)
+    weights[offs[1:] - 1] = 0.0                      # the last position of a sequence has no next item
+    return {"input_ids": torch.from_numpy(ids[:T].copy()), "target_ids": torch.from_numpy(targets),
+            "negative_ids": torch.from_numpy(rng.integers(0, vocab, num_negatives).astype(np.int32)),
+            "seq_offsets": torch.from_numpy(offs), "timestamps": torch.from_numpy(exponential_timestamps(rng, lens)),
+            "target_weights": torch.from_numpy(weights)}

@@ -141,7 +141,9 @@ class HSTU(nn.Module):
                add_head: bool = True, use_relative_bias: bool = False, num_time_buckets: int = 128,
                max_seq_len: int | None = None):
     super().__init__()
-    self.item_embedding = emb_layers.ReversibleEmbedding(vocab_size, model_dim, tie_weights=False)
+    # vocab_size None: the caller owns the item table (e.g. a sharded embedding) and feeds embeddings
+    self.item_embedding = (emb_layers.ReversibleEmbedding(vocab_size, model_dim, tie_weights=False)
+                           if vocab_size is not None else None)
     self.position_embedding = (emb_layers.PositionEmbedding(max_positions, model_dim)
                                if max_positions is not None else None)
     self.embeddings_dropout = nn.Dropout(dropout)
@@ -192,6 +194,13 @@ class HSTU(nn.Module):
     lens = seq_offsets[1:] - seq_offsets[:-1]
     positions = torch.arange(ids.numel(), device=ids.device) - torch.repeat_interleave(seq_offsets[:-1], lens)
     e = self._embed(ids, positions if self.position_embedding is not None else None)
+    return self.encode_jagged(e, seq_offsets, timestamps)
+
+  def encode_jagged(self, e: torch.Tensor, seq_offsets: torch.Tensor, timestamps: torch.Tensor | None = None,
+                    normalize_input: bool = False):
+    """Packed token embeddings `[T, D]` (already looked up) → token states `[T, D]`."""
+    if normalize_input:
+      e = self.embeddings_dropout(self._final_norm(e))
     pos_w = ts_w = None
     if self.relative_bias is not None:
       pos_w, ts_w = self.relative_bias.positional_bias.pos_biases, self.relative_bias.ts_w

@@ -221,7 +221,7 @@ class LinearFn(torch.autograd.Function):
     w16 = bf16_weight(w)
     y = G.gemm(x2, w16, bias=None if b is None else b.detach(), relu=relu)
     ctx.save = (x2, w16, y if relu else None)
-    ctx.has_bias, ctx.shape, ctx.dtype = b is not None, shp, x.dtype
+    ctx.has_bias, ctx.shape, ctx.dtype, ctx.w_dtype = b is not None, shp, x.dtype, w.dtype
     return y.view(*shp[:-1], w.shape[0])
 
   @staticmethod
@@ -235,7 +235,7 @@ class LinearFn(torch.autograd.Function):
     dw = G.gemm(g, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
     db = ew.colsum(g) if ctx.has_bias else None
     dx = G.gemm(g, w16, b_mn=True).view(ctx.shape).to(ctx.dtype)
-    return dx, dw, db, None
+    return dx, dw.to(ctx.w_dtype), db, None
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, relu: bool = False):
