@@ -22,7 +22,8 @@ using namespace recml::tc;
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // TMA warp, MMA warp, 8 element-wise warps (two per tensor-memory lane quarter)
+constexpr int kCompute = 256;
 constexpr float kBucketSize = 0.301f;
 
 struct Params {
@@ -31,7 +32,7 @@ struct Params {
   const int* seq_offsets;
   const int* tile_seq;        // [n_tiles] sequence of each 128-row tile (-1: unused slot)
   const int* tile_row0;       // [n_tiles] first position (within the sequence) of the tile
-  const long long* timestamps;
+  const int* timestamps;      // seconds relative to the earliest timestamp of the batch (int32)
   const float* pos_w;
   const float* ts_w;
   __nv_bfloat16* out;         // fwd: O [T, H*Dh]
@@ -57,13 +58,57 @@ __global__ void tile_list_kernel(const int* seq_offsets, int B, int* tile_seq, i
   }
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+// sigmoid through the single-instruction tanh approximation: one special-function op instead of exp + rcp
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
+__device__ __forceinline__ float silu(float x) { return x * sigmoid_fast(x); }
 
-__device__ __forceinline__ int time_bucket(long long dt, int num_buckets) {
-  long long a = dt < 0 ? -dt : dt;
-  a = a < 1 ? 1 : (a > 1000000000LL ? 1000000000LL : a);
-  const int b = static_cast<int>(logf(static_cast<float>(a)) / kBucketSize);
-  return b < 0 ? 0 : (b > num_buckets ? num_buckets : b);
+// bucket = clip(int(ln(clip(|dt|, 1, 1e9)) / 0.301), 0, num_buckets), with ln taken as log2 * ln(2)
+__device__ __forceinline__ int time_bucket(int dt, int num_buckets) {
+  int a = dt < 0 ? -dt : dt;
+  a = a < 1 ? 1 : (a > 1000000000 ? 1000000000 : a);
+  const int b = static_cast<int>(__log2f(static_cast<float>(a)) * (0.69314718f / kBucketSize));
+  return b > num_buckets ? num_buckets : b;
+}
+
+// Per-warp scratch in shared memory for the bias terms of one (query tile, key tile) pair: the 128 key
+// timestamps, the 160-entry window of the relative-position table the warp's 32 rows touch, and a copy
+// of the time-bucket table.  Only __syncwarp is needed to publish it.
+struct WarpBias {      // a warp covers 32 rows x 64 columns of the score tile
+  int ts_k[64];
+  float pos[96];
+  float tsw[260];
+};
+
+// One lane polls the mbarrier, the result is broadcast: the whole warp takes the same branch, so warp-level
+// synchronisation after it can never be left waiting for a lane that gave up.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int where, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status, where) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
+// `kv0` here is the first key of the warp's 64-column half.
+__device__ __forceinline__ void stage_bias(WarpBias& wb, const Params& p, int lane, int seq_start, int L, int kv0,
+                                           int q0, int quarter) {
+  __syncwarp();
+  if (p.ts_w != nullptr) {
+    for (int i = lane; i < 64; i += 32) wb.ts_k[i] = (kv0 + i < L) ? __ldg(p.timestamps + seq_start + kv0 + i) : 0;
+  }
+  if (p.pos_w != nullptr) {
+    // rows r = quarter*32 + lane, columns c: index (kv0 + c) - (q0 + r) + N - 1 = base + c - lane, lane in [0,32)
+    const int base = kv0 - q0 - quarter * 32 + p.max_seq_len - 1 - 31;
+    for (int i = lane; i < 96; i += 32) {
+      const int idx = base + i;
+      wb.pos[i] = (idx >= 0 && idx < 2 * p.max_seq_len - 1) ? __ldg(p.pos_w + idx) : 0.f;
+    }
+  }
+  __syncwarp();
 }
 
 template <int DH>
@@ -75,9 +120,9 @@ struct Smem {
   static constexpr int kV = kK + 2 * kTile;            // 2 stages
   static constexpr int kP = kV + 2 * kTile;            // [128, 128] bf16 = 32 KB
   static constexpr int kBars = kP + BQ * BKV * 2;
-  static constexpr int kTs = kBars + 128;              // key timestamps of the current tile (2 x 128 x 8 B)
-  static constexpr int kTotal = kTs + 2 * BKV * 8 + 1024;
-  static constexpr int kTmemCols = 256;                // S: 128 columns, O: DH columns
+  static constexpr int kBias = kBars + 128;            // 4 x WarpBias
+  static constexpr int kTotal = kBias + 8 * static_cast<int>(sizeof(WarpBias)) + 1024;
+  static constexpr int kTmemCols = 512;                // S: 2 x 128 columns, O: DH columns
 };
 
 template <int DH>
@@ -98,7 +143,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bars = base + S::kBars;
-  // barrier slots: 0 q_full, 1-2 kv_full, 3-4 kv_empty, 5 s_full, 6 s_empty, 7 p_full, 8 p_empty, 9 o_full
+  // barrier slots: 0 q_full, 1-2 kv_full, 3-4 kv_empty, 5-6 s_full, 7-8 s_empty, 9 p_full, 10 p_empty, 11 o_full
   auto bar = [&](int i) { return bars + 8u * i; };
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -106,21 +151,20 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(bar(0), 1);
-    mbar_init(bar(1), 1); mbar_init(bar(2), 1);
-    mbar_init(bar(3), 1); mbar_init(bar(4), 1);
-    mbar_init(bar(5), 1);
-    mbar_init(bar(6), 128);
-    mbar_init(bar(7), 128);
-    mbar_init(bar(8), 1);
-    mbar_init(bar(9), 1);
+    for (int i = 0; i <= 6; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(7), kCompute);
+    mbar_init(bar(8), kCompute);
+    mbar_init(bar(9), kCompute);
+    mbar_init(bar(10), 1);
+    mbar_init(bar(11), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 128;
+  // tensor memory: S buffers at columns [0,128) and [128,256), O at [256, 256+DH)
+  const uint32_t tmem_o = tmem_slot + 256;
   volatile int* abortp = &abort_flag;
 
   if (warp == 0) {
@@ -143,88 +187,98 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);
       const uint32_t idesc_o = idesc_bf16(BQ, DH, false, true);
       bool ok = mbar_wait(bar(0), 0, abortp, p.status, 41);
-      for (int j = 0; j < n_kv && ok; ++j) {
+      // S_j = Q·K_j^T goes to S buffer j&1, so the scores of tile j+1 are produced while the element-wise
+      // warps still work on tile j
+      auto issue_qk = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(bar(1 + s), (j >> 1) & 1, abortp, p.status, 42)) break;
-        if (j > 0 && !mbar_wait(bar(6), (j - 1) & 1, abortp, p.status, 43)) break;   // S of tile j-1 has been read
+        if (!mbar_wait(bar(1 + s), (j >> 1) & 1, abortp, p.status, 42)) return false;
+        if (j >= 2 && !mbar_wait(bar(7 + s), ((j >> 1) - 1) & 1, abortp, p.status, 43)) return false;
         tc_fence_after();
-        const uint32_t sk = base + S::kK + s * S::kTile, sv = base + S::kV + s * S::kTile;
+        const uint32_t sk = base + S::kK + s * S::kTile;
 #pragma unroll
         for (int d = 0; d < S::kSub; ++d)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_bf16(tmem_s, make_desc(base + S::kQ + d * 16384 + k * 32, 16, 1024),
+            tc_mma_bf16(tmem_slot + s * 128, make_desc(base + S::kQ + d * 16384 + k * 32, 16, 1024),
                         make_desc(sk + d * 16384 + k * 32, 16, 1024), idesc_s, (d | k) ? 1u : 0u);
-        tc_commit(bar(5));
-        if (!mbar_wait(bar(7), j & 1, abortp, p.status, 44)) break;   // P_j written
+        tc_commit(bar(5 + s));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < n_kv && !issue_qk(j + 1)) break;
+        if (!mbar_wait(bar(9), j & 1, abortp, p.status, 44)) break;   // P_j written
         tc_fence_after();
+        const uint32_t sv = base + S::kV + s * S::kTile;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
           tc_mma_bf16(tmem_o, make_desc(base + S::kP + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                       make_desc(sv + kk * 2048, 16384, 1024), idesc_o, (j | kk) ? 1u : 0u);
         tc_commit(bar(3 + s));   // K_j / V_j stage free
-        tc_commit(bar(8));       // P buffer free
+        tc_commit(bar(10));      // P buffer free
       }
-      tc_commit(bar(9));
+      tc_commit(bar(11));
     }
   } else {
-    const int quarter = warp & 3;
+    const int cw = warp - 2;              // 0..7
+    const int quarter = warp & 3;         // tensor-memory lane quarter this warp may read
+    const int half = cw >> 2;             // which 64 key columns of the tile this warp handles
     const int r = quarter * 32 + lane;
     const int qi = q0 + r;
     const bool row_ok = qi < L;
-    long long tq = 0;
-    if (p.timestamps != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+    WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
+    if (p.ts_w != nullptr)
+      for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
+    int tq = 0;
+    if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      const int kv0 = j * BKV;
-      if (!mbar_wait(bar(5), j & 1, abortp, p.status, 45)) { ok = false; break; }
+      const int kv0 = j * BKV + half * 64;
+      const int sb = j & 1;
+      stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter);
+      if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
       tc_fence_after();
-      if (j > 0 && !mbar_wait(bar(8), (j - 1) & 1, abortp, p.status, 46)) { ok = false; break; }
-      // key timestamps are read straight from global memory: all lanes of a warp ask for the same
-      // address at the same time, so each read is one broadcast transaction served by L1
-      const long long* tsk = p.timestamps != nullptr ? p.timestamps + seq_start + kv0 : nullptr;
+      if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_s + lane_off + c * 32, v);
+        tmem_ld32(tmem_slot + sb * 128 + lane_off + half * 64 + c * 32, v);
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pr[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int kj = kv0 + c * 32 + e + u;
+            const int col = c * 32 + e + u;       // within the warp's 64 columns
+            const int kj = kv0 + col;
             float x = __uint_as_float(v[e + u]) * p.scale;
             const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-            if (visible) {
-              if (p.pos_w != nullptr) x += __ldg(p.pos_w + (kj - qi) + p.max_seq_len - 1);
-              if (p.ts_w != nullptr) x += __ldg(p.ts_w + time_bucket(tq - __ldg(tsk + c * 32 + e + u), p.num_buckets));
-              pr[u] = silu(x) * p.inv_n;
-            } else {
-              pr[u] = 0.f;
-            }
+            if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
+            if (p.ts_w != nullptr) x += wb.tsw[time_bucket(tq - wb.ts_k[col], p.num_buckets)];
+            pr[u] = visible ? silu(x) * p.inv_n : 0.f;
           }
           packed[e >> 1] = pack_bf16(pr[0], pr[1]);
         }
-        // 32 columns = 64 bytes = four 16-byte chunks of row r in sub-tile c/2
-        uint8_t* row_ptr = base_ptr + S::kP + (c >> 1) * 16384 + r * 128;
+        // 32 columns = 64 bytes = four 16-byte chunks of row r in the 64-column sub-tile `half`
+        uint8_t* row_ptr = base_ptr + S::kP + half * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          const int chunk = (c * 4 + g) ^ (r & 7);
           *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
       }
       tc_fence_before();
-      mbar_arrive(bar(6));     // S may be overwritten
+      mbar_arrive(bar(7 + sb));   // this S buffer may be overwritten
       fence_async_smem();
-      mbar_arrive(bar(7));     // P is in shared memory
+      mbar_arrive(bar(9));        // P is in shared memory
     }
-    if (ok && mbar_wait(bar(9), 0, abortp, p.status, 47)) {
+    if (ok && warp_wait(bar(11), 0, abortp, p.status, 47, lane)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = half; c < DH / 32; c += 2) {
         uint32_t v[32];
         tmem_ld32(tmem_o + lane_off + c * 32, v);
         if (row_ok) {
@@ -265,7 +319,8 @@ struct SmemB {
   static constexpr int kDS = kP + BQ * BKV * 2;
   static constexpr int kBars = kDS + BQ * BKV * 2;
   static constexpr int kHist = kBars + 128;             // 2 x 256 diagonal bins (by step parity) + 256 time bins, fp32
-  static constexpr int kTotal = kHist + 768 * 4 + 1024;
+  static constexpr int kBias = kHist + 768 * 4;
+  static constexpr int kTotal = kBias + 8 * static_cast<int>(sizeof(WarpBias)) + 1024;
   // tensor memory columns: [0,128) S then dQ, [128,256) dP, [256,256+DH) dV, [256+DH,256+2DH) dK
   static constexpr int kTmemCols = 512;
 };
@@ -303,9 +358,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar(1), 1); mbar_init(bar(2), 1);
     mbar_init(bar(3), 1); mbar_init(bar(4), 1);
     mbar_init(bar(5), 1);
-    mbar_init(bar(6), 128);
+    mbar_init(bar(6), kCompute);
     mbar_init(bar(7), 1);
-    mbar_init(bar(8), 128);
+    mbar_init(bar(8), kCompute);
     mbar_init(bar(9), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -377,72 +432,85 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_commit(bar(9));
     }
   } else {
+    const int cw = warp - 2;
     const int quarter = warp & 3;
+    const int half = cw >> 2;             // which 64 key columns of the tile this warp handles
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const long long* tsk = p.timestamps != nullptr ? p.timestamps + seq_start + kv0 : nullptr;
+    WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
+    if (p.ts_w != nullptr)
+      for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int q0 = (i_first + it) * BQ;
       const int qi = q0 + r;
       const bool row_ok = qi < L;
-      long long tq = 0;
-      if (p.timestamps != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
-      if (!mbar_wait(bar(5), it & 1, abortp, p.status, 55)) { ok = false; break; }
+      int tq = 0;
+      if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+      stage_bias(wb, p, lane, seq_start, L, kv0 + half * 64, q0, quarter);
+      if (!warp_wait(bar(5), it & 1, abortp, p.status, 55, lane)) { ok = false; break; }
       tc_fence_after();
+      // time-bucket gradient: along a row the bucket changes rarely (log-spaced buckets, increasing
+      // timestamps), so equal-bucket runs are summed in a register and flushed with one atomic
+      int run_bucket = -1;
+      float run_sum = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dpv[32];
-        tmem_ld32(tmem_s + lane_off + c * 32, sv);
-        tmem_ld32(tmem_dp + lane_off + c * 32, dpv);
+        tmem_ld32(tmem_s + lane_off + half * 64 + c * 32, sv);
+        tmem_ld32(tmem_dp + lane_off + half * 64 + c * 32, dpv);
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pr[2], dr[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            const int kj = kv0 + col;
-            pr[u] = 0.f; dr[u] = 0.f;
+            const int col = c * 32 + e + u;              // within the warp's 64 columns
+            const int kj = kv0 + half * 64 + col;
             const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-            if (visible) {
-              float x = __uint_as_float(sv[e + u]) * p.scale;
-              int bucket = 0;
-              if (p.pos_w != nullptr) x += __ldg(p.pos_w + (kj - qi) + p.max_seq_len - 1);
-              if (p.ts_w != nullptr) {
-                bucket = time_bucket(tq - __ldg(tsk + col), p.num_buckets);
-                x += __ldg(p.ts_w + bucket);
+            float x = __uint_as_float(sv[e + u]) * p.scale;
+            int bucket = 0;
+            if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
+            if (p.ts_w != nullptr) {
+              bucket = time_bucket(tq - wb.ts_k[col], p.num_buckets);
+              x += wb.tsw[bucket];
+            }
+            const float sig = sigmoid_fast(x);
+            const float ds = visible ? __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n : 0.f;
+            pr[u] = visible ? x * sig * p.inv_n : 0.f;
+            dr[u] = ds;
+            // diagonal bin (kj - qi) - (kv0 - q0) + 127: lanes of a warp hit distinct bins
+            if (p.dpos_w != nullptr && visible) atomicAdd(hist + (it & 1) * 256 + (half * 64 + col - r + 127), ds);
+            if (p.dts_w != nullptr && visible) {
+              if (bucket != run_bucket) {
+                if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
+                run_bucket = bucket;
+                run_sum = 0.f;
               }
-              const float sig = 1.f / (1.f + __expf(-x));
-              pr[u] = x * sig * p.inv_n;
-              const float ds = __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n;
-              dr[u] = ds;
-              // bias gradients: diagonal bin (kj - qi) - (kv0 - q0) + 127 in [0, 255); lanes of a warp hit
-              // distinct diagonals, so the shared-memory atomics do not collide inside a warp
-              if (p.dpos_w != nullptr) atomicAdd(hist + (it & 1) * 256 + (col - r + 127), ds);
-              if (p.dts_w != nullptr) atomicAdd(hist + 512 + bucket, ds);
+              run_sum += ds;
             }
           }
           pp[e >> 1] = pack_bf16(pr[0], pr[1]);
           dd[e >> 1] = pack_bf16(dr[0], dr[1]);
         }
-        uint8_t* prow = base_ptr + S::kP + (c >> 1) * 16384 + r * 128;
-        uint8_t* drow = base_ptr + S::kDS + (c >> 1) * 16384 + r * 128;
+        uint8_t* prow = base_ptr + S::kP + half * 16384 + r * 128;
+        uint8_t* drow = base_ptr + S::kDS + half * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          const int chunk = (c * 4 + g) ^ (r & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
         }
       }
+      if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(bar(6));
       // dQ tile: wait for the three products of this step, then add it into the fp32 gradient
-      if (!mbar_wait(bar(7), it & 1, abortp, p.status, 56)) { ok = false; break; }
+      if (!warp_wait(bar(7), it & 1, abortp, p.status, 56, lane)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = half; c < DH / 32; c += 2) {
         uint32_t v[32];
         tmem_ld32(tmem_s + lane_off + c * 32, v);
         if (row_ok) {
@@ -461,18 +529,18 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // every compute thread must be past its last histogram atomic: they all arrived on bar(6) before the
         // dQ commit could complete, and this thread observed that commit
         const int tid = threadIdx.x - 64;
-        for (int b = tid; b < 255; b += 128) {
+        for (int b = tid; b < 255; b += kCompute) {
           const float val = atomicExch(hist + (it & 1) * 256 + b, 0.f);   // the other parity is being filled by step it+1
           if (val != 0.f) atomicAdd(p.dpos_w + (kv0 - q0) + (b - 127) + p.max_seq_len - 1, val);
         }
       }
     }
-    if (ok && mbar_wait(bar(9), 0, abortp, p.status, 57)) {
+    if (ok && warp_wait(bar(9), 0, abortp, p.status, 57, lane)) {
       tc_fence_after();
       const int kj = kv0 + r;
       const bool kv_ok = kj < L;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = half; c < DH / 32; c += 2) {
         uint32_t v[32], w[32];
         tmem_ld32(tmem_dv + lane_off + c * 32, v);
         tmem_ld32(tmem_dk + lane_off + c * 32, w);

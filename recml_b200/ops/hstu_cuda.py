@@ -31,6 +31,15 @@ def available() -> bool:
   return _ok
 
 
+def _ts32(timestamps):
+  """Seconds relative to the earliest timestamp of the batch as int32 (the kernels only use differences)."""
+  if timestamps is None:
+    return None
+  if timestamps.dtype == torch.int32:
+    return timestamps.contiguous()
+  return (timestamps - timestamps.min()).to(torch.int32).contiguous()
+
+
 def _tiles(seq_offsets: torch.Tensor, T: int):
   B = seq_offsets.numel() - 1
   cap = (T + 127) // 128 + B
@@ -57,8 +66,7 @@ def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale,
 
 def forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
   assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.bfloat16
-  if timestamps is not None:
-    timestamps = timestamps.to(torch.int64).contiguous()
+  timestamps = _ts32(timestamps)
   pos_w = None if pos_w is None else pos_w.detach().float().contiguous()
   ts_w = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0])
@@ -77,8 +85,7 @@ def backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, cau
   lib = _lib.cuda()
   if not hasattr(lib._lib, "recml_hstu_attn_bwd"):
     return _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale)
-  if timestamps is not None:
-    timestamps = timestamps.to(torch.int64).contiguous()
+  timestamps = _ts32(timestamps)
   pw = None if pos_w is None else pos_w.detach().float().contiguous()
   tw = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0])
