@@ -1,0 +1,219 @@
+// TFRecord files and tf.train.Example / SequenceExample records without TensorFlow: framing with
+// masked CRC-32C, a protobuf wire-format walker for the Features message, and a multi-threaded batch
+// parser that fills dense int64 / float32 arrays (fixed-length features) or jagged values + row lengths
+// (variable-length features).  This is the native input pipeline that replaces the tf.data runtime
+// the reference relies on.
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "host/thread_pool.h"
+
+namespace {
+
+uint32_t g_crc_table[8][256];
+bool g_crc_ready = false;
+
+void crc_init() {
+  if (g_crc_ready) return;
+  for (uint32_t i = 0; i < 256; ++i) {
+    uint32_t c = i;
+    for (int k = 0; k < 8; ++k) c = (c & 1) ? (c >> 1) ^ 0x82F63B78u : (c >> 1);
+    g_crc_table[0][i] = c;
+  }
+  for (uint32_t i = 0; i < 256; ++i)
+    for (int t = 1; t < 8; ++t) g_crc_table[t][i] = (g_crc_table[t - 1][i] >> 8) ^ g_crc_table[0][g_crc_table[t - 1][i] & 0xff];
+  g_crc_ready = true;
+}
+
+uint32_t crc32c(const uint8_t* p, size_t n) {
+  crc_init();
+  uint32_t c = 0xffffffffu;
+  while (n >= 8) {
+    uint32_t lo, hi;
+    memcpy(&lo, p, 4);
+    memcpy(&hi, p + 4, 4);
+    lo ^= c;
+    c = g_crc_table[7][lo & 0xff] ^ g_crc_table[6][(lo >> 8) & 0xff] ^ g_crc_table[5][(lo >> 16) & 0xff] ^
+        g_crc_table[4][lo >> 24] ^ g_crc_table[3][hi & 0xff] ^ g_crc_table[2][(hi >> 8) & 0xff] ^
+        g_crc_table[1][(hi >> 16) & 0xff] ^ g_crc_table[0][hi >> 24];
+    p += 8;
+    n -= 8;
+  }
+  while (n--) c = g_crc_table[0][(c ^ *p++) & 0xff] ^ (c >> 8);
+  return c ^ 0xffffffffu;
+}
+
+uint32_t masked(uint32_t crc) { return ((crc >> 15) | (crc << 17)) + 0xa282ead8u; }
+
+struct Slice { const uint8_t* p; size_t n; };
+
+bool varint(Slice& s, uint64_t& v) {
+  v = 0;
+  for (int shift = 0; shift < 64 && s.n > 0; shift += 7) {
+    const uint8_t b = *s.p++;
+    --s.n;
+    v |= static_cast<uint64_t>(b & 0x7f) << shift;
+    if (!(b & 0x80)) return true;
+  }
+  return false;
+}
+
+bool field(Slice& s, uint32_t& num, uint32_t& wire, Slice& payload, uint64_t& scalar) {
+  uint64_t key;
+  if (!varint(s, key)) return false;
+  num = static_cast<uint32_t>(key >> 3);
+  wire = static_cast<uint32_t>(key & 7);
+  payload = Slice{nullptr, 0};
+  scalar = 0;
+  if (wire == 0) return varint(s, scalar);
+  if (wire == 2) {
+    uint64_t len;
+    if (!varint(s, len) || len > s.n) return false;
+    payload = Slice{s.p, static_cast<size_t>(len)};
+    s.p += len;
+    s.n -= len;
+    return true;
+  }
+  const size_t w = wire == 1 ? 8 : (wire == 5 ? 4 : 0);
+  if (w == 0 || w > s.n) return false;
+  payload = Slice{s.p, w};
+  s.p += w;
+  s.n -= w;
+  return true;
+}
+
+// Feature { bytes_list = 1; float_list = 2; int64_list = 3 }, each list has `repeated value = 1`.
+void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floats, std::vector<std::string>* bytes) {
+  uint32_t kind, wire, num;
+  Slice pl;
+  uint64_t sc;
+  while (f.n > 0 && field(f, kind, wire, pl, sc)) {
+    if (wire != 2) continue;   // kind: 1 bytes_list, 2 float_list, 3 int64_list
+    Slice list = pl;
+    while (list.n > 0 && field(list, num, wire, pl, sc)) {
+      if (num != 1) continue;
+      if (kind == 3 && ints != nullptr) {
+        if (wire == 2) {         // packed varints
+          Slice pk = pl;
+          uint64_t v;
+          while (pk.n > 0 && varint(pk, v)) ints->push_back(static_cast<int64_t>(v));
+        } else if (wire == 0) {
+          ints->push_back(static_cast<int64_t>(sc));
+        }
+      } else if (kind == 2 && floats != nullptr) {
+        if (wire == 2) {         // packed floats
+          for (size_t i = 0; i + 4 <= pl.n; i += 4) { float v; memcpy(&v, pl.p + i, 4); floats->push_back(v); }
+        } else if (wire == 5) {
+          float v; memcpy(&v, pl.p, 4); floats->push_back(v);
+        }
+      } else if (kind == 1 && bytes != nullptr && wire == 2) {
+        bytes->emplace_back(reinterpret_cast<const char*>(pl.p), pl.n);
+      }
+    }
+  }
+}
+
+// Example { Features features = 1 }; Features { map<string, Feature> feature = 1 } (map entry: key = 1, value = 2)
+bool find_feature(Slice example, const char* name, Slice& out) {
+  const size_t name_len = strlen(name);
+  uint32_t num, wire;
+  Slice pl;
+  uint64_t sc;
+  while (example.n > 0 && field(example, num, wire, pl, sc)) {
+    if (num != 1 || wire != 2) continue;
+    Slice feats = pl;
+    while (feats.n > 0 && field(feats, num, wire, pl, sc)) {
+      if (num != 1 || wire != 2) continue;
+      Slice entry = pl, key{nullptr, 0}, val{nullptr, 0};
+      while (entry.n > 0 && field(entry, num, wire, pl, sc)) {
+        if (num == 1) key = pl;
+        if (num == 2) val = pl;
+      }
+      if (key.n == name_len && memcmp(key.p, name, name_len) == 0) { out = val; return true; }
+    }
+  }
+  return false;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t recml_crc32c(const uint8_t* p, long long n) { return crc32c(p, static_cast<size_t>(n)); }
+
+// Scans a TFRecord file image: fills offsets[i] / lengths[i] of each record payload (up to cap).
+// Returns the record count, or -(1+index) of the first corrupt record when verify != 0.
+long long recml_tfrecord_index(const uint8_t* data, long long size, long long* offsets, long long* lengths,
+                               long long cap, int verify) {
+  long long pos = 0, n = 0;
+  while (pos + 12 <= size) {
+    uint64_t len;
+    uint32_t len_crc;
+    memcpy(&len, data + pos, 8);
+    memcpy(&len_crc, data + pos + 8, 4);
+    if (verify && masked(crc32c(data + pos, 8)) != len_crc) return -(1 + n);
+    if (pos + 12 + static_cast<long long>(len) + 4 > size) return -(1 + n);
+    if (verify) {
+      uint32_t data_crc;
+      memcpy(&data_crc, data + pos + 12 + len, 4);
+      if (masked(crc32c(data + pos + 12, len)) != data_crc) return -(1 + n);
+    }
+    if (n < cap) { offsets[n] = pos + 12; lengths[n] = static_cast<long long>(len); }
+    ++n;
+    pos += 12 + static_cast<long long>(len) + 4;
+  }
+  return n;
+}
+
+// Frames one payload as a TFRecord into out (capacity >= len + 16); returns bytes written.
+long long recml_tfrecord_frame(const uint8_t* payload, long long len, uint8_t* out) {
+  const uint64_t l = static_cast<uint64_t>(len);
+  memcpy(out, &l, 8);
+  const uint32_t c1 = masked(crc32c(out, 8));
+  memcpy(out + 8, &c1, 4);
+  memcpy(out + 12, payload, static_cast<size_t>(len));
+  const uint32_t c2 = masked(crc32c(payload, static_cast<size_t>(len)));
+  memcpy(out + 12 + len, &c2, 4);
+  return len + 16;
+}
+
+// Parses one named feature from `count` serialized Examples in parallel.
+//   kind 0: int64, 1: float.   fixed_len > 0: dense output [count, fixed_len] (missing / short values
+//   are filled with `default_*`, long ones truncated); fixed_len == 0: only row_lengths are filled on the first
+//   pass (values == nullptr) and values are written at the offsets given by `row_starts` on the second.
+int recml_parse_examples(const uint8_t* data, const long long* offsets, const long long* lengths, long long count,
+                         const char* name, int kind, int fixed_len, long long default_int, float default_float,
+                         void* values, long long* row_lengths, const long long* row_starts) {
+  int status = 0;
+  recml::ThreadPool::global().parallel_for(count, [&](long long r0, long long r1, int) {
+    std::vector<int64_t> ints;
+    std::vector<float> floats;
+    for (long long r = r0; r < r1; ++r) {
+      ints.clear();
+      floats.clear();
+      Slice feat;
+      if (find_feature(Slice{data + offsets[r], static_cast<size_t>(lengths[r])}, name, feat))
+        parse_feature(feat, kind == 0 ? &ints : nullptr, kind == 1 ? &floats : nullptr, nullptr);
+      const long long n = kind == 0 ? static_cast<long long>(ints.size()) : static_cast<long long>(floats.size());
+      if (row_lengths != nullptr) row_lengths[r] = n;
+      if (values == nullptr) continue;
+      if (fixed_len > 0) {
+        for (int i = 0; i < fixed_len; ++i) {
+          if (kind == 0) static_cast<int64_t*>(values)[r * fixed_len + i] = i < n ? ints[i] : default_int;
+          else static_cast<float*>(values)[r * fixed_len + i] = i < n ? floats[i] : default_float;
+        }
+      } else if (row_starts != nullptr) {
+        for (long long i = 0; i < n; ++i) {
+          if (kind == 0) static_cast<int64_t*>(values)[row_starts[r] + i] = ints[i];
+          else static_cast<float*>(values)[row_starts[r] + i] = floats[i];
+        }
+      }
+    }
+  }, 64);
+  return status;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// Host-side id preprocessing: the C++ counterpart of the reference's native input-preprocessing
+// module (sample ids -> per-partition CSR with duplicate ids merged, id dropping and per-partition
+// statistics), re-targeted at GPU shards.
+//
+// Two services, both multi-threaded over features / samples:
+//   recml_pack_jagged      per-feature id lists -> one KeyedJagged (values / offsets / weights)
+//   recml_partition_csr    jagged ids of one table -> ids grouped by owning shard, duplicates of the
+//                          same (sample, row) merged by adding their gains, optional dropping beyond a
+//                          per-partition cap, and the statistics the embedding planner sizes buffers
+//                          with (max ids / max unique ids per partition, drop count).
+// Row -> shard follows the MOD layout: shard = (id % shards + rotation) % shards, local row = id / shards.
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <numeric>
+#include <vector>
+
+#include "host/thread_pool.h"
+
+namespace {
+
+struct Entry {
+  int32_t shard, row, sample;
+  float gain;
+};
+
+}  // namespace
+
+extern "C" {
+
+// features[f] points at the ids of feature f (concatenated bags), lengths[f] at its per-sample bag
+// sizes (batch entries).  Output buffers are caller-allocated: values[total], offsets[F*batch+1],
+// weights_out[total] (may be null, as may weights_in / weights_in[f]).
+int recml_pack_jagged(int num_features, int batch, const int64_t* const* features, const int32_t* const* lengths,
+                      const float* const* weights_in, int32_t* values, int32_t* offsets, float* weights_out) {
+  std::vector<long long> feat_total(num_features + 1, 0);
+  for (int f = 0; f < num_features; ++f) {
+    long long t = 0;
+    for (int b = 0; b < batch; ++b) t += lengths[f][b];
+    feat_total[f + 1] = feat_total[f] + t;
+  }
+  if (feat_total[num_features] > INT32_MAX) return -1;
+  recml::ThreadPool::global().parallel_for(num_features, [&](long long f0, long long f1, int) {
+    for (long long f = f0; f < f1; ++f) {
+      long long pos = feat_total[f];
+      for (int b = 0; b < batch; ++b) {
+        offsets[f * batch + b] = static_cast<int32_t>(pos);
+        pos += lengths[f][b];
+      }
+      const long long n = feat_total[f + 1] - feat_total[f];
+      for (long long i = 0; i < n; ++i) values[feat_total[f] + i] = static_cast<int32_t>(features[f][i]);
+      if (weights_out != nullptr) {
+        const float* w = (weights_in != nullptr) ? weights_in[f] : nullptr;
+        for (long long i = 0; i < n; ++i) weights_out[feat_total[f] + i] = w ? w[i] : 1.0f;
+      }
+    }
+  });
+  offsets[static_cast<long long>(num_features) * batch] = static_cast<int32_t>(feat_total[num_features]);
+  return 0;
+}
+
+// ids[nnz] with offsets[batch+1] (bag b = ids[offsets[b]:offsets[b+1]]), optional gains[nnz].
+// Outputs (caller-allocated, capacity nnz): out_rows / out_samples / out_gains sorted by (shard, row, sample);
+// shard_ptr[shards+1] delimits each shard's slice; stats[0..2] = max ids per shard, max unique rows
+// per shard, dropped ids.  max_ids_per_shard <= 0 disables dropping.  Returns the number of entries kept.
+long long recml_partition_csr(const int32_t* ids, const int32_t* offsets, const float* gains, int batch, int shards,
+                              int rotation, int max_ids_per_shard, int32_t* out_rows, int32_t* out_samples,
+                              float* out_gains, int64_t* shard_ptr, int64_t* stats) {
+  const long long nnz = offsets[batch];
+  std::vector<Entry> e(static_cast<size_t>(nnz));
+  recml::ThreadPool::global().parallel_for(batch, [&](long long b0, long long b1, int) {
+    for (long long b = b0; b < b1; ++b)
+      for (int i = offsets[b]; i < offsets[b + 1]; ++i) {
+        const int32_t id = ids[i];
+        e[i] = Entry{static_cast<int32_t>((id % shards + rotation) % shards), id / shards, static_cast<int32_t>(b),
+                     gains ? gains[i] : 1.0f};
+      }
+  }, 1024);
+  std::sort(e.begin(), e.end(), [](const Entry& a, const Entry& b) {
+    if (a.shard != b.shard) return a.shard < b.shard;
+    if (a.row != b.row) return a.row < b.row;
+    return a.sample < b.sample;
+  });
+  long long kept = 0, dropped = 0, max_ids = 0, max_unique = 0;
+  long long i = 0;
+  for (int s = 0; s < shards; ++s) {
+    shard_ptr[s] = kept;
+    long long in_shard = 0, unique = 0;
+    int32_t last_row = -1;
+    while (i < nnz && e[i].shard == s) {
+      // merge duplicates of the same (row, sample)
+      Entry cur = e[i++];
+      while (i < nnz && e[i].shard == s && e[i].row == cur.row && e[i].sample == cur.sample) cur.gain += e[i++].gain;
+      if (max_ids_per_shard > 0 && in_shard >= max_ids_per_shard) {
+        ++dropped;
+        continue;
+      }
+      if (cur.row != last_row) { ++unique; last_row = cur.row; }
+      out_rows[kept] = cur.row;
+      out_samples[kept] = cur.sample;
+      out_gains[kept] = cur.gain;
+      ++kept;
+      ++in_shard;
+    }
+    max_ids = std::max(max_ids, in_shard);
+    max_unique = std::max(max_unique, unique);
+  }
+  shard_ptr[shards] = kept;
+  stats[0] = max_ids;
+  stats[1] = max_unique;
+  stats[2] = dropped;
+  return kept;
+}
+
+int recml_host_threads() { return recml::ThreadPool::global().size(); }
+
+}  // extern "C"

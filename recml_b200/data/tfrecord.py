@@ -1,0 +1,116 @@
+"""TFRecord / tf.Example I/O on the native reader (`csrc/data/tfrecord.cpp`), with a pure-Python
+serializer for writing test and export files.  No TensorFlow involved."""
+from __future__ import annotations
+
+import ctypes
+import struct
+from typing import Iterable, Mapping, Sequence
+
+import numpy as np
+
+from recml_b200.ops import _lib
+
+c_ll = ctypes.c_longlong
+
+
+def _lib_host():
+  lib = _lib.host()
+  lib.recml_tfrecord_index.restype = c_ll
+  lib.recml_tfrecord_frame.restype = c_ll
+  lib.recml_crc32c.restype = ctypes.c_uint32
+  return lib
+
+
+def crc32c(data: bytes) -> int:
+  return int(_lib_host().recml_crc32c(data, c_ll(len(data))))
+
+
+# ---- protobuf wire-format writer for tf.train.Example -------------------------------------------------
+def _varint(v: int) -> bytes:
+  v &= (1 << 64) - 1
+  out = bytearray()
+  while True:
+    b = v & 0x7F
+    v >>= 7
+    out.append(b | (0x80 if v else 0))
+    if not v:
+      return bytes(out)
+
+
+def _ld(num: int, payload: bytes) -> bytes:
+  return _varint((num << 3) | 2) + _varint(len(payload)) + payload
+
+
+def encode_example(features: Mapping[str, Sequence]) -> bytes:
+  """Serialises {name: list of ints | floats | bytes} as a tf.train.Example."""
+  entries = b""
+  for name, vals in features.items():
+    vals = list(vals) if not isinstance(vals, (bytes, str)) else [vals]
+    if vals and isinstance(vals[0], (bytes, str)):
+      body = b"".join(_ld(1, v if isinstance(v, bytes) else v.encode()) for v in vals)
+      feat = _ld(1, body)
+    elif vals and isinstance(vals[0], (float, np.floating)):
+      feat = _ld(2, _ld(1, struct.pack(f"<{len(vals)}f", *vals)))
+    else:
+      feat = _ld(3, _ld(1, b"".join(_varint(int(v)) for v in vals)))
+    entries += _ld(1, _ld(1, name.encode()) + _ld(2, feat))
+  return _ld(1, entries)
+
+
+def write_tfrecord(path: str, records: Iterable[bytes]) -> int:
+  lib = _lib_host()
+  n = 0
+  with open(path, "wb") as f:
+    for rec in records:
+      buf = ctypes.create_string_buffer(len(rec) + 16)
+      w = lib.recml_tfrecord_frame(rec, c_ll(len(rec)), buf)
+      f.write(buf.raw[:w])
+      n += 1
+  return n
+
+
+class RecordFile:
+  """A TFRecord file mapped into memory and indexed (payload offsets / lengths); CRCs verified."""
+
+  def __init__(self, path: str, verify: bool = True):
+    self.data = np.fromfile(path, dtype=np.uint8)
+    lib = _lib_host()
+    ptr = self.data.ctypes.data_as(ctypes.c_void_p)
+    n = lib.recml_tfrecord_index(ptr, c_ll(self.data.size), None, None, c_ll(0), ctypes.c_int(int(verify)))
+    if n < 0:
+      raise IOError(f"{path}: corrupt TFRecord at record {-n - 1}")
+    self.offsets = np.zeros(n, dtype=np.int64)
+    self.lengths = np.zeros(n, dtype=np.int64)
+    lib.recml_tfrecord_index(ptr, c_ll(self.data.size), self.offsets.ctypes.data_as(ctypes.c_void_p),
+                             self.lengths.ctypes.data_as(ctypes.c_void_p), c_ll(n), ctypes.c_int(0))
+
+  def __len__(self) -> int:
+    return int(self.offsets.size)
+
+  def record(self, i: int) -> bytes:
+    return self.data[self.offsets[i]:self.offsets[i] + self.lengths[i]].tobytes()
+
+  def parse(self, rows: np.ndarray, name: str, dtype: str, fixed_len: int = 0, default=0):
+    """Parses feature `name` of the given record indices with all host threads.
+    fixed_len > 0 → dense `[len(rows), fixed_len]`; else (values, row_lengths) jagged."""
+    lib = _lib_host()
+    kind = 0 if dtype in ("int64", "int") else 1
+    np_dt = np.int64 if kind == 0 else np.float32
+    offs = np.ascontiguousarray(self.offsets[rows])
+    lens = np.ascontiguousarray(self.lengths[rows])
+    n = len(rows)
+    args = (self.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
+            lens.ctypes.data_as(ctypes.c_void_p), c_ll(n), name.encode(), ctypes.c_int(kind))
+    di, df = c_ll(int(default) if kind == 0 else 0), ctypes.c_float(float(default) if kind == 1 else 0.0)
+    if fixed_len > 0:
+      out = np.empty((n, fixed_len), dtype=np_dt)
+      lib.recml_parse_examples(*args, ctypes.c_int(fixed_len), di, df, out.ctypes.data_as(ctypes.c_void_p), None, None)
+      return out
+    row_len = np.zeros(n, dtype=np.int64)
+    lib.recml_parse_examples(*args, ctypes.c_int(0), di, df, None, row_len.ctypes.data_as(ctypes.c_void_p), None)
+    starts = np.zeros(n, dtype=np.int64)
+    np.cumsum(row_len[:-1], out=starts[1:])
+    vals = np.empty(int(row_len.sum()), dtype=np_dt)
+    lib.recml_parse_examples(*args, ctypes.c_int(0), di, df, vals.ctypes.data_as(ctypes.c_void_p), None,
+                             starts.ctypes.data_as(ctypes.c_void_p))
+    return vals, row_len

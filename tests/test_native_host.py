@@ -1,0 +1,123 @@
+"""Native host library: id packing / partitioning vs numpy, TFRecord + tf.Example round trips, the
+TFRecord dataset factory, CRC-32C vectors, parallel chunk I/O."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from recml_b200.data import tfrecord, tfrecord_factory as tff
+from recml_b200.embedding import id_pipeline as ip
+from recml_b200.embedding.jagged import KeyedJagged
+from recml_b200.ops import _lib
+
+
+def test_crc32c_known_vectors():
+  assert tfrecord.crc32c(b"123456789") == 0xE3069283
+  assert tfrecord.crc32c(b"") == 0
+  assert tfrecord.crc32c(bytes(32)) == 0x8A9136AA
+
+
+def test_pack_jagged_matches_python():
+  rng = np.random.default_rng(0)
+  B = 37
+  feats, lists = {}, {}
+  for f in range(5):
+    lens = rng.integers(0, 6, B).astype(np.int32)
+    ids = rng.integers(0, 1000, int(lens.sum()))
+    feats[f"f{f}"] = (ids, lens)
+    offs = np.concatenate([[0], np.cumsum(lens)])
+    lists[f"f{f}"] = [ids[offs[b]:offs[b + 1]].tolist() for b in range(B)]
+  a, b = ip.pack_jagged(feats), KeyedJagged.from_lists(lists)
+  assert torch.equal(a.values, b.values) and torch.equal(a.offsets, b.offsets) and a.batch_size() == B
+
+
+def test_partition_csr_merges_duplicates_and_counts():
+  ids = np.array([5, 5, 2, 9, 4, 4, 4, 13], np.int32)      # bags: [5,5,2] [9] [4,4,4,13]
+  offs = np.array([0, 3, 4, 8], np.int32)
+  rows, samples, gains, ptr, st = ip.partition_csr(ids, offs, shards=4)
+  # shard = id % 4: 5,9,13 -> 1 ; 2 -> 2 ; 4 -> 0 ; local row = id // 4
+  got = sorted(zip(np.repeat(np.arange(4), np.diff(ptr)).tolist(), rows.tolist(), samples.tolist(), gains.tolist()))
+  assert got == [(0, 1, 2, 3.0), (1, 1, 0, 2.0), (1, 2, 1, 1.0), (1, 3, 2, 1.0), (2, 0, 0, 1.0)]
+  assert (st.max_ids_per_partition, st.max_unique_ids_per_partition, st.dropped_ids) == (3, 3, 0)
+  *_, st2 = ip.partition_csr(ids, offs, shards=4, max_ids_per_partition=2)
+  assert st2.dropped_ids == 1 and st2.max_ids_per_partition == 2
+
+
+def test_stats_recorder_roundtrip(tmp_path):
+  r = ip.StatsRecorder(str(tmp_path), 0)
+  r.record("t", ip.PartitionStats(5, 3, 0)); r.record("t", ip.PartitionStats(4, 9, 2))
+  r.publish()
+  r1 = ip.StatsRecorder(str(tmp_path), 1)
+  r1.record("t", ip.PartitionStats(8, 1, 1)); r1.publish()
+  s = r.load()["t"]
+  assert (s.max_ids_per_partition, s.max_unique_ids_per_partition, s.dropped_ids) == (8, 9, 3)
+
+
+def _write(path, n, seed=0):
+  rng = np.random.default_rng(seed)
+  recs, truth = [], []
+  for i in range(n):
+    seq = rng.integers(1, 10**12, int(rng.integers(0, 7))).tolist()
+    dense = rng.normal(size=3).astype(np.float32).tolist()
+    truth.append((seq, dense, i % 2))
+    recs.append(tfrecord.encode_example({"sequence": seq, "dense": dense, "label": [i % 2], "tag": [b"x"]}))
+  tfrecord.write_tfrecord(path, recs)
+  return truth
+
+
+def test_tfrecord_roundtrip_and_corruption(tmp_path):
+  p = str(tmp_path / "a.tfrecord")
+  truth = _write(p, 50)
+  rf = tfrecord.RecordFile(p)
+  assert len(rf) == 50
+  rows = np.arange(50)
+  vals, lens = rf.parse(rows, "sequence", "int64")
+  assert lens.tolist() == [len(t[0]) for t in truth] and vals.tolist() == [v for t in truth for v in t[0]]
+  np.testing.assert_allclose(rf.parse(rows, "dense", "float32", 3), np.array([t[1] for t in truth], np.float32))
+  assert rf.parse(rows, "label", "int64", 1)[:, 0].tolist() == [t[2] for t in truth]
+  assert rf.parse(rows[:3], "missing", "int64", 2, default=-1).tolist() == [[-1, -1]] * 3
+  raw = bytearray(open(p, "rb").read())
+  raw[40] ^= 0xFF
+  open(p, "wb").write(raw)
+  with pytest.raises(IOError):
+    tfrecord.RecordFile(p)
+
+
+def test_tfrecord_factory_batches_labels_and_sharding(tmp_path):
+  for k in range(4):
+    _write(str(tmp_path / f"part-{k}.tfrecord"), 20, seed=k)
+  spec = {"sequence": tff.VarLenFeature("int64"), "dense": tff.FixedLenFeature((3,), "float32"),
+          "label": tff.FixedLenFeature((1,), "int64")}
+  fac = tff.TFDatasetFactory(input_path=str(tmp_path / "part-*.tfrecord"), feature_spec=spec, global_batch_size=8,
+                             label_name="label", sharding_info=tff.DatasetShardingInfo(2, 1))
+  it = fac.make()
+  batches = list(it)
+  assert len(batches) == 2 * (20 // 4)           # files 1 and 3, per-process batch 8 / 2 = 4
+  feats, label = batches[0]
+  assert feats["dense"].shape == (4, 3) and label.shape == (4, 1) and feats["sequence"]["lengths"].shape == (4,)
+  assert tff.DatasetShardingInfo(4, 0).per_process_batch_size(64) == 16
+  dbg = tff.TFDatasetFactory(input_path=str(tmp_path / "part-0.tfrecord"), feature_spec=spec, global_batch_size=4,
+                             debug=True).make()
+  a, b = next(dbg), next(dbg)
+  assert a is b
+
+
+def test_parallel_chunk_io(tmp_path):
+  lib = _lib.host()
+  n = 12
+  bufs = [np.random.default_rng(i).integers(0, 255, 1000 + i, dtype=np.uint8) for i in range(n)]
+  paths = [str(tmp_path / f"c{i}").encode() for i in range(n)]
+  P = ctypes.c_void_p
+  cp = (ctypes.c_char_p * n)(*paths)
+  bp = (P * n)(*[b.ctypes.data for b in bufs])
+  sz = (ctypes.c_longlong * n)(*[b.size for b in bufs])
+  crcs = (ctypes.c_uint32 * n)()
+  assert lib.recml_write_chunks(n, cp, bp, sz, crcs, 0) == 0
+  outs = [np.empty_like(b) for b in bufs]
+  op = (P * n)(*[o.ctypes.data for o in outs])
+  assert lib.recml_read_chunks(n, cp, op, sz) == 0
+  for a, b, c in zip(bufs, outs, crcs):
+    assert np.array_equal(a, b) and c == tfrecord.crc32c(a.tobytes())
+  assert not any(f.endswith(".partial") for f in os.listdir(tmp_path))
