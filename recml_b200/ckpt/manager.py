@@ -164,13 +164,14 @@ class CheckpointManager:
   def _write(self, tmp, staged, kinds, metrics, rank, world):
     item = os.path.join(tmp, self.item_name)
     meta_tree, sharding = {}, {}
+    pending = []     # (array dir, chunk index, array): written together by the native chunk writer
     for path, rec in staged:
       key = ".".join(path)
       leaf_dir = os.path.join(item, key)
       if rec[0] == "full":
         _, arr, dt = rec
         zarr_io.write_zarray(leaf_dir, arr.shape, arr.shape, dt, self.compressor)
-        zarr_io.write_chunk(leaf_dir, [0] * arr.ndim, arr, self.compressor)
+        pending.append((leaf_dir, [0] * arr.ndim, arr))
         meta_tree[key] = {"key_path": list(path), "shape": list(arr.shape), "dtype": dt,
                           "value_type": "array"}
         sharding[key] = {"sharding_type": "replicated"}
@@ -186,10 +187,11 @@ class CheckpointManager:
             full = np.zeros(leaf.chunk_shape, dtype=arr.dtype)
             full[tuple(slice(0, s) for s in arr.shape)] = arr
             arr = full
-          zarr_io.write_chunk(leaf_dir, leaf.grid_index, arr, self.compressor)
+          pending.append((leaf_dir, leaf.grid_index, arr))
         meta_tree[key] = {"key_path": list(path), "shape": list(leaf.global_shape),
                           "dtype": dt_all, "value_type": "array"}
         sharding[key] = {"sharding_type": "block", "chunk_shape": list(leaf.chunk_shape)}
+    zarr_io.write_chunks_parallel(pending, self.compressor)
     if rank == 0:
       with open(os.path.join(item, TREE_METADATA), "w") as f:
         json.dump({"tree_metadata": meta_tree,

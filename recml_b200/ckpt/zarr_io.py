@@ -182,3 +182,34 @@ def _read_chunk(path, cidx, chunks, dt, comp) -> np.ndarray:
     return arr.reshape(chunks)
   return np.frombuffer(blob, dtype=dt, count=n).reshape(chunks) if len(chunks) else \
       np.frombuffer(blob, dtype=dt, count=1)
+
+
+def write_chunks_parallel(items, compressor: str | None = None) -> None:
+  """`items`: list of (array dir, chunk index, numpy array).  Chunks are written concurrently by the
+  native chunk writer (`csrc/ckpt/chunk_io.cpp`: temp name + rename per chunk); falls back to the
+  serial Python writer when the native library is unavailable."""
+  if not items:
+    return
+  try:
+    from recml_b200.ops import _lib
+    lib = _lib.host()
+  except Exception:  # pylint: disable=broad-except
+    lib = None
+  if lib is None:
+    for path, index, arr in items:
+      write_chunk(path, index, arr, compressor)
+    return
+  blobs = []
+  for path, index, arr in items:
+    raw = arr.tobytes(order="C")
+    if compressor == "zstd":
+      raw = zstd_compress(raw)
+    blobs.append((os.path.join(path, chunk_name(index)).encode(), raw))
+  n = len(blobs)
+  paths = (ctypes.c_char_p * n)(*[b[0] for b in blobs])
+  bufs = (ctypes.c_char_p * n)(*[b[1] for b in blobs])
+  sizes = (ctypes.c_longlong * n)(*[len(b[1]) for b in blobs])
+  rc = lib.recml_write_chunks(ctypes.c_int(n), paths, ctypes.cast(bufs, ctypes.POINTER(ctypes.c_void_p)), sizes, None,
+                              ctypes.c_int(0))
+  if rc != 0:
+    raise IOError(f"native chunk write failed for {blobs[-rc - 1][0].decode()}")

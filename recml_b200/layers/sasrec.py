@@ -18,7 +18,9 @@ class SASRec(nn.Module):
                num_layers: int, dropout: float = 0.0, norm_eps: float = 1e-6, scale_by_sqrt_dim: bool = False,
                add_head: bool = True):
     super().__init__()
-    self.item_embedding = emb_layers.ReversibleEmbedding(vocab_size, model_dim, tie_weights=True)
+    # vocab_size None: the caller owns the (sharded) item table and feeds embeddings to `encode_embeddings`
+    self.item_embedding = (emb_layers.ReversibleEmbedding(vocab_size, model_dim, tie_weights=True)
+                           if vocab_size is not None else None)
     self.position_embedding = emb_layers.PositionEmbedding(max_positions, model_dim)
     self.embeddings_dropout = nn.Dropout(dropout)
     self.decoder_blocks = nn.ModuleList(
@@ -33,7 +35,10 @@ class SASRec(nn.Module):
 
   def encode(self, inputs, padding_mask=None, attention_mask=None):
     """Sequence states `[B, L, D]` (what the sharded-vocabulary heads consume)."""
-    e = self.item_embedding(inputs)
+    return self.encode_embeddings(self.item_embedding(inputs), padding_mask, attention_mask)
+
+  def encode_embeddings(self, e, padding_mask=None, attention_mask=None):
+    """Same as `encode` for item embeddings `[B, L, D]` that were looked up elsewhere."""
     if self.scale_by_sqrt_dim:
       e = e * math.sqrt(self.model_dim)
     e = self.embeddings_dropout(self._norm(e + self.position_embedding(e)))

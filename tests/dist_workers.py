@@ -136,3 +136,46 @@ def dlrm_tiny_training(rank, world, device_type, steps, use_graph=False):
   import os as _os
   return {"loss": float(logs["train"]["loss"]), "val_loss": float(logs["val"]["loss"]),
           "ckpts": sorted(_os.listdir(_os.path.join(box[0], "checkpoints")))}
+
+
+def vocab_rank_sharded(rank, world, device_type, rows, D, V):
+  """Ranks over a MOD-row-sharded item matrix vs the single-process fp32 ranks."""
+  from recml_b200.ops import vocab_rank as VR
+  device = torch.device("cuda", rank) if device_type == "cuda" else torch.device("cpu")
+  g = torch.Generator().manual_seed(0)
+  x_all = (torch.randn(rows * world, D, generator=g) * 0.3).to(torch.bfloat16)
+  items = (torch.randn(V, D, generator=g) * 0.3).to(torch.bfloat16)
+  target_all = torch.randint(0, V, (rows * world,), generator=g)
+  pos_all = (x_all.float() * items[target_all].float()).sum(-1)
+  sl = slice(rank * rows, (rank + 1) * rows)
+  shard = items[rank::world].contiguous().to(device)        # local row i <-> global id i*world + rank
+  ranker = VR.VocabRanker(rows, D, None, device)
+  out = None
+  for _ in range(2):
+    out = ranker.ranks(x_all[sl].to(device), pos_all[sl].to(device), target_all[sl].to(device), shard, world, rank)
+  if device.type == "cuda":
+    torch.cuda.synchronize()
+    from recml_b200.ops import _lib
+    _lib.check_status(device)
+  s = x_all[sl].float() @ items.float().t()
+  ref = 1 + ((s > pos_all[sl][:, None]) & (torch.arange(V)[None] != target_all[sl][:, None])).sum(1)
+  near = ((s - pos_all[sl][:, None]).abs() < 2e-3 * s.abs().max()).sum(1)
+  return {"max_excess": int(((out.cpu() - ref).abs() - near).max()), "exact": float((out.cpu() == ref).float().mean())}
+
+
+def sequence_experiment(rank, world, device_type, which, steps):
+  import tempfile
+  from recml_b200 import config as C, run_experiment
+  d = tempfile.mkdtemp() if rank == 0 else None
+  box = [d]
+  dist.broadcast_object_list(box, src=0)
+  if which == "sasrec":
+    from recml_b200.examples import sasrec_experiment as E
+  else:
+    from recml_b200.examples import hstu_experiment as E
+  cfg = E.tiny_experiment(model_dir=box[0], train_steps=steps)
+  if device_type == "cpu":
+    cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, device="cpu")
+  logs = run_experiment(C.build(cfg), "train_and_eval")
+  return {k: {kk: float(vv) for kk, vv in v.items() if not kk.startswith(("perf", "model", "optimizer"))}
+          for k, v in logs.items()}

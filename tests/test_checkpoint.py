@@ -1,0 +1,98 @@
+"""Checkpoint manager: layout, round trips (dense, bf16, sharded leaves restored under a different
+sharding), retention, save policy, async completion, zstd chunks, the checkpoints iterator."""
+import json
+import os
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from recml_b200 import ckpt
+from recml_b200.ckpt import zarr_io
+
+
+def _tree():
+  return {"step": torch.tensor(7), "params": {"w": torch.randn(5, 3), "b": torch.randn(3).to(torch.bfloat16)},
+          "opt_state": {"count": torch.tensor(3), "mu": [torch.zeros(2), torch.ones(2, 2)]}}
+
+
+def test_layout_and_roundtrip(tmp_path):
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  t = _tree()
+  assert m.save(11, t, metrics={"train": {"loss": 0.5}})
+  d = tmp_path / "11"
+  assert (d / "_CHECKPOINT_METADATA").exists() and (d / "state" / "_METADATA").exists()
+  assert (d / "state" / "_sharding").exists() and (d / "commit_success.txt").exists()
+  assert (d / "state" / "params.w" / ".zarray").exists() and (d / "state" / "params.w" / "0.0").exists()
+  z = json.load(open(d / "state" / "params.w" / ".zarray"))
+  assert z["shape"] == [5, 3] and z["dtype"] == "<f4" and z["zarr_format"] == 2
+  assert json.load(open(d / "state" / "params.b" / ".zarray"))["dtype"] == "bfloat16"
+  assert m.metrics(11)["train"]["loss"] == 0.5
+  back = m.restore(11)
+  torch.testing.assert_close(back["params"]["w"], t["params"]["w"])
+  assert back["params"]["b"].dtype == torch.bfloat16 and torch.equal(back["params"]["b"], t["params"]["b"])
+  assert isinstance(back["opt_state"]["mu"], list) and back["opt_state"]["mu"][1].shape == (2, 2)
+  tgt = m.restore(11, target={"params": {"w": torch.zeros(5, 3)}})
+  torch.testing.assert_close(tgt["params"]["w"], t["params"]["w"])
+  with pytest.raises(KeyError):
+    m.restore(11, target={"params": {"nope": torch.zeros(1)}})
+  with pytest.raises(FileNotFoundError):
+    ckpt.restore_tree(str(tmp_path / "11" / "missing"))
+
+
+def test_retention_policy_and_async(tmp_path):
+  keep = {3, 7, 11}
+  m = ckpt.CheckpointManager(str(tmp_path), max_to_keep=2, should_save_fn=lambda s, _: s in keep)
+  for s in range(12):
+    m.save(s, {"x": torch.full((4,), float(s))})
+  m.wait_until_finished()
+  assert m.all_steps() == [7, 11] and m.latest_step() == 11
+  assert float(m.restore()["x"][0]) == 11.0
+  assert not [n for n in os.listdir(tmp_path) if "tmp" in n]
+  assert m.save(5, {"x": torch.zeros(1)}, force=True)
+  m.close()
+
+
+def test_sharded_leaf_resharding(tmp_path):
+  """A table saved as two row blocks is read back whole, and as three uneven blocks."""
+  full = torch.arange(40, dtype=torch.float32).reshape(10, 4)
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  # one process plays both ranks: write block 0, then block 1 into the same step directory
+  a = ckpt.ShardedLeaf(full[:5], (10, 4), (0, 0), (5, 4))
+  m.save(0, {"t": a})
+  zarr_io.write_chunk(str(tmp_path / "0" / "state" / "t"), (1, 0), full[5:].numpy(), None)
+  torch.testing.assert_close(m.restore(0)["t"], full)
+  for lo, hi in [(0, 4), (4, 8), (8, 10)]:
+    got = zarr_io.read_region(str(tmp_path / "0" / "state" / "t"), [lo, 0], [hi, 4])
+    torch.testing.assert_close(got, full[lo:hi])
+  tgt = ckpt.ShardedLeaf(torch.zeros(4, 4), (10, 4), (1, 0), (4, 4))
+  torch.testing.assert_close(m.restore(0, target={"t": tgt})["t"], full[4:8])
+
+
+@pytest.mark.skipif(not zarr_io.zstd_available(), reason="libzstd not loadable")
+def test_zstd_chunks(tmp_path):
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False, compressor="zstd")
+  x = torch.zeros(1000, 16)
+  m.save(1, {"x": x})
+  assert os.path.getsize(tmp_path / "1" / "state" / "x" / "0.0") < x.numel()
+  assert json.load(open(tmp_path / "1" / "state" / "x" / ".zarray"))["compressor"]["id"] == "zstd"
+  torch.testing.assert_close(m.restore(1)["x"], x)
+
+
+def test_checkpoints_iterator_sees_new_steps_and_stops_on_marker(tmp_path):
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  m.save(1, {"x": torch.zeros(1)})
+  done = threading.Event()
+
+  def writer():
+    time.sleep(0.3)
+    m.save(2, {"x": torch.zeros(1)})
+    time.sleep(0.3)
+    done.set()
+
+  th = threading.Thread(target=writer); th.start()
+  seen = list(ckpt.checkpoints_iterator(str(tmp_path), timeout=0.5, timeout_fn=done.is_set, poll_secs=0.05))
+  th.join()
+  assert seen == [1, 2]

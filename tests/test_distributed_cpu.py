@@ -37,3 +37,13 @@ def test_tiny_dlrm_two_ranks_matches_loss_trend():
   res = dist_utils.run_ranks("dlrm_tiny_training", 2, "gloo", "cpu", 60)
   assert res[0]["ckpts"] == ["49", "59"]
   assert res[0]["loss"] < 0.62 and abs(res[0]["loss"] - res[1]["loss"]) < 0.1
+
+
+def test_vocab_rank_sharded_gloo():
+  res = dist_utils.run_ranks("vocab_rank_sharded", 2, "gloo", "cpu", 24, 32, 501)
+  assert all(r["max_excess"] <= 0 for r in res), res
+
+
+def test_sasrec_tiny_two_ranks():
+  res = dist_utils.run_ranks("sequence_experiment", 2, "gloo", "cpu", "sasrec", 30)
+  assert res[0]["train"]["loss"] < 1.45 and 0.0 <= res[0]["val"]["ndcg@10"] <= 1.0

@@ -41,3 +41,14 @@ def test_dlrm_tiny_two_gpus():
 def test_dlrm_tiny_two_gpus_cuda_graph():
   res = dist_utils.run_ranks("dlrm_tiny_training", 2, "nccl", "cuda", 60, True)
   assert res[0]["loss"] < 0.62
+
+
+def test_vocab_rank_two_gpus():
+  res = dist_utils.run_ranks("vocab_rank_sharded", 2, "nccl", "cuda", 256, 256, 30011)
+  assert all(r["max_excess"] <= 0 and r["exact"] > 0.9 for r in res), res
+
+
+@pytest.mark.parametrize("which", ["sasrec", "hstu"])
+def test_sequence_experiments_two_gpus(which):
+  res = dist_utils.run_ranks("sequence_experiment", 2, "nccl", "cuda", which, 30)
+  assert res[0]["train"]["loss"] == res[0]["train"]["loss"]   # finite
