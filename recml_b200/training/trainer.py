@@ -93,7 +93,8 @@ class Trainer(core.Trainer[task_lib.Task]):
                steps_per_eval: int | None = None, checkpoint_interval: int | None = None,
                max_checkpoints_to_keep: int = 5, continuous_eval_timeout: int = 30,
                rng_seed: int = core.DEFAULT_RNG_SEED, rng_impl: str | None = None,
-               enable_checkpointing: bool = True, check_for_checkpoints: bool = True):
+               enable_checkpointing: bool = True, check_for_checkpoints: bool = True,
+               failure_detection: bool = False, heartbeat_timeout_s: float = 30.0):
     if not isinstance(steps_per_loop, int) or steps_per_loop < 1:
       raise ValueError(f"`steps_per_loop` ({steps_per_loop}) must be a positive integer.")
     self._partitioner = partitioner or partitioning.NullPartitioner()
@@ -109,6 +110,9 @@ class Trainer(core.Trainer[task_lib.Task]):
     self._enable_checkpointing = enable_checkpointing
     self._check_for_checkpoints = check_for_checkpoints
     self._progress = profiling.ReportProgress()
+    self._failure_detection = failure_detection
+    self._heartbeat_timeout_s = heartbeat_timeout_s
+    self._health = None
 
   # -- lazily created helpers ---------------------------------------------------------
   @functools.cached_property
@@ -159,13 +163,33 @@ class Trainer(core.Trainer[task_lib.Task]):
     with open(os.path.join(self._model_dir, core.TRAINING_COMPLETE_MARKER_FILE), "w") as f:
       f.write("COMPLETED")
 
+  # -- failure detection: host heartbeats between steps, device status words once per loop ---------------
+  def _start_health(self):
+    if not self._failure_detection or self._health is not None:
+      return
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+      return
+    from recml_b200.comm import health
+    store = dist.distributed_c10d._get_default_store()   # pylint: disable=protected-access
+    self._health = health.HealthMonitor(store, dist.get_rank(), dist.get_world_size(),
+                                        timeout_s=self._heartbeat_timeout_s).start()
+
+  def _check_health(self, step: int, end_of_loop: bool = False) -> None:
+    if self._health is not None:
+      self._health.check(step)
+    if end_of_loop and torch.cuda.is_available():
+      from recml_b200.ops import _lib
+      _lib.check_status()
+
   # -- the hot loop ----------------------------------------------------------------------
   def _train_n_steps(self, *, train_iter, train_step, state, start_step: int, num_steps: int,
                      summary_writer) -> tuple[state_lib.State, Mapping[str, Any]]:
     accum = metrics_tools.MetricAccumulator(summary_writer)
     timer = profiling.DeviceStepTimer(enabled=torch.cuda.is_available())
     t0, examples, timed_steps = None, 0, 0
+    self._start_health()
     for step in range(start_step, start_step + num_steps):
+      self._check_health(step)
       if step - start_step == WARMUP_STEPS:
         timer.start()
         t0 = time.time()
@@ -181,6 +205,7 @@ class Trainer(core.Trainer[task_lib.Task]):
       if step != start_step + num_steps - 1:
         self._maybe_save_checkpoint(step, state)
     device_ms = timer.stop()
+    self._check_health(start_step + num_steps - 1, end_of_loop=True)
     scalars = dict(accum.compute_and_log_scalars(start_step + num_steps - 1))
     if t0 is not None and timed_steps:
       if torch.cuda.is_available():

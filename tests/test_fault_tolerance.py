@@ -1,0 +1,73 @@
+"""Failure detection without faulting a GPU: missed heartbeats, an injected rank exception, loader
+errors surfacing in the consumer, and (GPU) a bounded device-side wait that expires and reports."""
+import ctypes
+import time
+
+import pytest
+import torch
+
+from recml_b200.comm import health
+from recml_b200.data import tfrecord_factory as tff
+
+
+def test_heartbeat_detects_a_silent_rank():
+  store = health.DictStore()
+  t = [0.0]
+  a = health.HealthMonitor(store, 0, 2, interval_s=0.05, timeout_s=1.0, clock=lambda: t[0]).start()
+  b = health.HealthMonitor(store, 1, 2, interval_s=0.05, timeout_s=1.0, clock=lambda: t[0],
+                           injector=health.FaultInjector("stop_heartbeat:rank=1:step=3")).start()
+  time.sleep(0.2)
+  t[0] = 0.5
+  a.check(step=1); b.check(step=1)
+  b.check(step=3)                      # rank 1 stops beating from step 3 on
+  time.sleep(0.2)
+  a.check(step=3)                      # records the last value it saw
+  t[0] = 5.0
+  time.sleep(0.2)
+  with pytest.raises(health.PeerFailure) as e:
+    a.check(step=4)
+  assert e.value.ranks == [1]
+  b.check(step=4)                      # rank 0 is still alive from rank 1's point of view
+  a.stop(); b.stop()
+
+
+def test_injected_exception_and_parsing():
+  inj = health.FaultInjector("raise:rank=0:step=2")
+  m = health.HealthMonitor(health.DictStore(), 0, 1, injector=inj).start()
+  m.check(step=1)
+  with pytest.raises(RuntimeError, match="injected failure"):
+    m.check(step=2)
+  m.stop()
+  assert not health.FaultInjector("").fires("raise", 0, 0)
+
+
+def test_loader_thread_exception_reaches_the_consumer(tmp_path):
+  p = tmp_path / "bad.tfrecord"
+  p.write_bytes(b"\x05\x00\x00\x00\x00\x00\x00\x00garbage-garbage-garbage")
+  fac = tff.TFDatasetFactory(input_path=str(p), feature_spec={"x": tff.FixedLenFeature((1,))}, global_batch_size=2,
+                             prefetch_buffer_size=2)
+  with pytest.raises(IOError):
+    next(fac.make())
+
+
+@pytest.mark.gpu
+def test_device_wait_expires_and_reports_status():
+  from recml_b200.ops import _lib
+  lib = _lib.cuda()
+  flag = torch.zeros(1, dtype=torch.int64, device="cuda")          # nobody raises it
+  status = torch.zeros(4, dtype=torch.int32, device="cuda")
+  result = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+  t0 = time.time()
+  rc = lib.recml_wait_probe(_lib.ptr(flag), ctypes.c_ulonglong(1), ctypes.c_ulonglong(20_000_000), _lib.ptr(status),
+                            ctypes.c_int(7), _lib.ptr(result), _lib.stream())
+  assert rc == 0
+  torch.cuda.synchronize()
+  assert time.time() - t0 < 5.0
+  assert result.item() == 0 and status.tolist()[:2] == [2, 7]      # kPeerTimeout, detail
+  # the context is still usable, and a raised flag is seen at once
+  flag.fill_(3)
+  status.zero_()
+  lib.recml_wait_probe(_lib.ptr(flag), ctypes.c_ulonglong(3), ctypes.c_ulonglong(20_000_000), _lib.ptr(status),
+                       ctypes.c_int(7), _lib.ptr(result), _lib.stream())
+  torch.cuda.synchronize()
+  assert result.item() == 1 and status.tolist()[0] == 0
