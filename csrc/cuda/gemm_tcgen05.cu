@@ -61,22 +61,28 @@ template <int BN>
 struct Cfg {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kSmem = kStages * (kStageA + kStageB) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kStages = (BN == 256) ? 3 : 4;
+  // per epilogue warp: four 4 KB buffers (out, out2, aux0, aux1), each a [32 rows, 64 cols] bf16 box
+  static constexpr int kEpi = 4 * 4 * 4096;
+  static constexpr int kSmem = kStages * (kStageA + kStageB) + kEpi + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_d2,
+            const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
             const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a = base;
   const uint32_t smem_b = base + C::kStages * C::kStageA;
-  const uint32_t bars = smem_b + C::kStages * C::kStageB;
-  // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]
+  const uint32_t epi_smem = smem_b + C::kStages * C::kStageB;
+  uint8_t* epi_ptr = smem_raw + (epi_smem - smem_u32(smem_raw));
+  const uint32_t bars = epi_smem + C::kEpi;
+  // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], aux_full[4 warps]
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
   auto tfull_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
@@ -101,6 +107,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(tfull_bar(s), 1);
       mbar_init(tempty_bar(s), 128);
     }
+    for (int w = 0; w < 4; ++w) mbar_init(bars + 8u * (2 * C::kStages + 4 + w), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
@@ -181,114 +188,235 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------ epilogue ------------------------------
+    // bf16 outputs: every warp owns 32 rows of the tile.  Per 64-column slab it (1) TMA-loads the 32 x 64
+    // boxes of the auxiliary operands into its private shared-memory buffers, (2) reads the accumulator
+    // from tensor memory, applies the epilogue and writes bf16 into a swizzled staging box, (3) hands the
+    // box to a TMA store.  All global traffic of the epilogue is therefore full 128-byte lines, and only
+    // __syncwarp is needed.  fp32 outputs (weight gradients) are written directly: a thread's 32 floats
+    // already are one full line.
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const uint32_t my_smem = epi_smem + quarter * 16384;
+    uint8_t* my_ptr = epi_ptr + quarter * 16384;
+    const uint32_t aux_bar = bars + 8u * (2 * C::kStages + 4 + quarter);
+    const int n_aux = p.epi == kEpiLinear ? 0 : ((p.epi == kEpiCross || (p.epi == kEpiMulAdd && p.aux1 != nullptr)) ? 2 : 1);
+    uint32_t aux_uses = 0;
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int tl = tile / split_k;
       const int m0 = (tl / n_tiles) * BM, n0 = (tl % n_tiles) * BN;
       const int acc = t & 1;
-      if (!mbar_wait(tfull_bar(acc), (t >> 1) & 1, abortp, p.status, 30)) break;
+      {
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(tfull_bar(acc), (t >> 1) & 1, abortp, p.status, 30) ? 1 : 0;
+        if (!__shfl_sync(0xffffffffu, okw, 0)) break;
+      }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (!p.out_f32) {
+        const int row0 = m0 + quarter * 32;
+        bool ok = true;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        if (!row_ok) continue;
-        const size_t off = static_cast<size_t>(row) * p.ldd + col0;
-        const size_t aoff = static_cast<size_t>(row) * p.ldaux + col0;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {  // 4 groups of 8 columns
-          if (col0 + v * 8 >= p.N) break;
-          float x[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]);
-          if (p.bias != nullptr) {
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8 + 4));
-            x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
-            x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
-          }
-          if (p.epi == kEpiLinear) {
-            if (p.relu) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+        for (int sl = 0; sl < BN / 64 && ok; ++sl) {
+          const int col0 = n0 + sl * 64;
+          if (col0 >= p.N) break;  // warp-uniform
+          if (lane == 0) {
+            // the staging boxes may still be read by the previous slab's stores
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (n_aux > 0) {
+              mbar_expect_tx(aux_bar, 4096u * n_aux);
+              tma_load_2d(my_smem + 8192, &map_x0, col0, row0, aux_bar);
+              if (n_aux == 2) tma_load_2d(my_smem + 12288, &map_x1, col0, row0, aux_bar);
             }
-          } else {
-            const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(p.aux0 + aoff + v * 8));
-            const uint32_t a0w[4] = {a0.x, a0.y, a0.z, a0.w};
-            if (p.epi == kEpiCross) {
-              if (p.out2 != nullptr) {
-                uint4 o;
-                o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
-                o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
-                *reinterpret_cast<uint4*>(p.out2 + off + v * 8) = o;
-              }
-              const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
-              const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+          }
+          __syncwarp();
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t r[32];
+            tmem_ld32(taddr + sl * 64 + hh * 32, r);
+            if (hh == 0 && n_aux > 0) {
+              int okw = 1;
+              if (lane == 0) okw = mbar_wait(aux_bar, aux_uses & 1, abortp, p.status, 31) ? 1 : 0;
+              ++aux_uses;
+              if (!__shfl_sync(0xffffffffu, okw, 0)) { ok = false; break; }
+            }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x[2 * j] = bf16_lo(a0w[j]) * x[2 * j] + bf16_lo(a1w[j]);
-                x[2 * j + 1] = bf16_hi(a0w[j]) * x[2 * j + 1] + bf16_hi(a1w[j]);
-              }
-            } else if (p.epi == kEpiMaskRelu) {
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + hh * 32 + g * 8;
+              const int chunk = ((hh * 4 + g) ^ (lane & 7)) * 16 + lane * 128;
+              float x[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x[2 * j] = bf16_lo(a0w[j]) > 0.f ? x[2 * j] : 0.f;
-                x[2 * j + 1] = bf16_hi(a0w[j]) > 0.f ? x[2 * j + 1] : 0.f;
+              for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[g * 8 + j]);
+              if (p.bias != nullptr && col < p.N) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
+                x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+                x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
               }
-            } else if (p.epi == kEpiAdd) {
+              if (p.epi == kEpiLinear) {
+                if (p.relu) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x[2 * j] += bf16_lo(a0w[j]);
-                x[2 * j + 1] += bf16_hi(a0w[j]);
-              }
-            } else {  // kEpiMulAdd
+                  for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+                }
+              } else {
+                const uint4 a0 = *reinterpret_cast<const uint4*>(my_ptr + 8192 + chunk);
+                const uint32_t a0w[4] = {a0.x, a0.y, a0.z, a0.w};
+                if (p.epi == kEpiCross) {
+                  if (p.out2 != nullptr)
+                    *reinterpret_cast<uint4*>(my_ptr + 4096 + chunk) =
+                        make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+                  const uint4 a1 = *reinterpret_cast<const uint4*>(my_ptr + 12288 + chunk);
+                  const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x[2 * j] *= bf16_lo(a0w[j]);
-                x[2 * j + 1] *= bf16_hi(a0w[j]);
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] = bf16_lo(a0w[j]) * x[2 * j] + bf16_lo(a1w[j]);
+                    x[2 * j + 1] = bf16_hi(a0w[j]) * x[2 * j + 1] + bf16_hi(a1w[j]);
+                  }
+                } else if (p.epi == kEpiMaskRelu) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] = bf16_lo(a0w[j]) > 0.f ? x[2 * j] : 0.f;
+                    x[2 * j + 1] = bf16_hi(a0w[j]) > 0.f ? x[2 * j + 1] : 0.f;
+                  }
+                } else if (p.epi == kEpiAdd) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] += bf16_lo(a0w[j]);
+                    x[2 * j + 1] += bf16_hi(a0w[j]);
+                  }
+                } else {  // kEpiMulAdd
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] *= bf16_lo(a0w[j]);
+                    x[2 * j + 1] *= bf16_hi(a0w[j]);
+                  }
+                  if (n_aux == 2) {
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(my_ptr + 12288 + chunk);
+                    const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      x[2 * j] += bf16_lo(a1w[j]);
+                      x[2 * j + 1] += bf16_hi(a1w[j]);
+                    }
+                  }
+                }
               }
-              if (p.aux1 != nullptr) {
+              *reinterpret_cast<uint4*>(my_ptr + chunk) =
+                  make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+            }
+          }
+          if (!ok) break;
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_d, col0, row0, my_smem);
+            if (p.epi == kEpiCross && p.out2 != nullptr) tma_store_2d(&map_d2, col0, row0, my_smem + 4096);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        if (!ok) break;
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          if (!row_ok) continue;
+          const size_t off = static_cast<size_t>(row) * p.ldd + col0;
+          const size_t aoff = static_cast<size_t>(row) * p.ldaux + col0;
+  #pragma unroll
+          for (int v = 0; v < 4; ++v) {  // 4 groups of 8 columns
+            if (col0 + v * 8 >= p.N) break;
+            float x[8];
+  #pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(r[v * 8 + j]);
+            if (p.bias != nullptr) {
+              const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8));
+              const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + v * 8 + 4));
+              x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+              x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+            }
+            if (p.epi == kEpiLinear) {
+              if (p.relu) {
+  #pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+              }
+            } else {
+              const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(p.aux0 + aoff + v * 8));
+              const uint32_t a0w[4] = {a0.x, a0.y, a0.z, a0.w};
+              if (p.epi == kEpiCross) {
+                if (p.out2 != nullptr) {
+                  uint4 o;
+                  o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+                  o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+                  *reinterpret_cast<uint4*>(p.out2 + off + v * 8) = o;
+                }
                 const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
                 const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
+  #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  x[2 * j] += bf16_lo(a1w[j]);
-                  x[2 * j + 1] += bf16_hi(a1w[j]);
+                  x[2 * j] = bf16_lo(a0w[j]) * x[2 * j] + bf16_lo(a1w[j]);
+                  x[2 * j + 1] = bf16_hi(a0w[j]) * x[2 * j + 1] + bf16_hi(a1w[j]);
+                }
+              } else if (p.epi == kEpiMaskRelu) {
+  #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  x[2 * j] = bf16_lo(a0w[j]) > 0.f ? x[2 * j] : 0.f;
+                  x[2 * j + 1] = bf16_hi(a0w[j]) > 0.f ? x[2 * j + 1] : 0.f;
+                }
+              } else if (p.epi == kEpiAdd) {
+  #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  x[2 * j] += bf16_lo(a0w[j]);
+                  x[2 * j + 1] += bf16_hi(a0w[j]);
+                }
+              } else {  // kEpiMulAdd
+  #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  x[2 * j] *= bf16_lo(a0w[j]);
+                  x[2 * j + 1] *= bf16_hi(a0w[j]);
+                }
+                if (p.aux1 != nullptr) {
+                  const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
+                  const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+  #pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] += bf16_lo(a1w[j]);
+                    x[2 * j + 1] += bf16_hi(a1w[j]);
+                  }
                 }
               }
             }
-          }
-          if (p.out_f32) {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.d) + off + v * 8);
-            float4 o0 = make_float4(x[0], x[1], x[2], x[3]), o1 = make_float4(x[4], x[5], x[6], x[7]);
-            if (split_k > 1) {
-              atomicAdd(dst, o0);
-              atomicAdd(dst + 1, o1);
-              continue;
+            if (p.out_f32) {
+              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.d) + off + v * 8);
+              float4 o0 = make_float4(x[0], x[1], x[2], x[3]), o1 = make_float4(x[4], x[5], x[6], x[7]);
+              if (split_k > 1) {
+                atomicAdd(dst, o0);
+                atomicAdd(dst + 1, o1);
+                continue;
+              }
+              if (p.accumulate) {
+                const float4 c0 = dst[0], c1 = dst[1];
+                o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
+                o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
+              }
+              dst[0] = o0; dst[1] = o1;
+            } else {
+              uint4 o;
+              o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+              o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + off + v * 8) = o;
             }
-            if (p.accumulate) {
-              const float4 c0 = dst[0], c1 = dst[1];
-              o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
-              o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
-            }
-            dst[0] = o0; dst[1] = o1;
-          } else {
-            uint4 o;
-            o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
-            o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + off + v * 8) = o;
           }
         }
+  
       }
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------ teardown ------------------------------
@@ -318,6 +446,17 @@ static int launch(const void* a, int lda, const void* b, int ldb, const Params& 
   if (rc) return rc;
   rc = B_MN ? make_map(&mb, b, p.K, p.N, ldb, 64) : make_map(&mb, b, p.N, p.K, ldb, BN);
   if (rc) return rc;
+  // bf16 outputs / auxiliary operands move through [32 rows, 64 cols] boxes (one per epilogue warp)
+  CUtensorMap md, md2, mx0, mx1;
+  if (!p.out_f32) {
+    if (make_map(&md, p.d, p.M, p.N, p.ldd, 32)) return -5;
+  } else {
+    md = ma;
+  }
+  md2 = md; mx0 = md; mx1 = md;
+  if (!p.out_f32 && p.out2 != nullptr && make_map(&md2, p.out2, p.M, p.N, p.ldd, 32)) return -5;
+  if (!p.out_f32 && p.aux0 != nullptr && make_map(&mx0, p.aux0, p.M, p.N, p.ldaux, 32)) return -5;
+  if (!p.out_f32 && p.aux1 != nullptr && make_map(&mx1, p.aux1, p.M, p.N, p.ldaux, 32)) return -5;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -327,7 +466,7 @@ static int launch(const void* a, int lda, const void* b, int ldb, const Params& 
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.split_k > 1 ? p.split_k : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mb, p);
+  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mb, md, md2, mx0, mx1, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -345,6 +484,8 @@ extern "C" int recml_gemm_bf16(const void* a, int lda, int a_mn, const void* b, 
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (ldd % 4) || (!out_f32 && (ldd % 8))) return -10;
   if (epi != kEpiLinear && (aux0 == nullptr || (ldaux % 8))) return -11;
+  if (epi != kEpiLinear && out_f32) return -14;   // fused epilogues produce bf16
+  if ((reinterpret_cast<uintptr_t>(aux0) | reinterpret_cast<uintptr_t>(aux1) | reinterpret_cast<uintptr_t>(out2)) & 15) return -12;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return -12;
   Params p;
   p.M = M; p.N = N; p.K = K; p.d = d; p.ldd = ldd; p.out_f32 = out_f32; p.accumulate = accumulate;
