@@ -163,19 +163,41 @@ struct PushIdsParams {
   long long nnz; int n_offsets; int W; int me;
   int* dst_values[kMaxWorld]; int* dst_offsets[kMaxWorld]; float* dst_weights[kMaxWorld];
   unsigned int* done_counter; PeerFlags flags; SeqRef seq;
+  const unsigned char* need;   // per feature: bit r set when rank r holds part of its table (null: all)
+  int n_feats; int B;          // offsets[f*B] is the first id of feature f
 };
 
+// The offsets go to every rank; the ids of a feature only to the ranks that own rows of its table
+// (one rank for a table-wise feature).  Each id is read once and stored to its destinations.
 __global__ void emb_push_ids_kernel(const PushIdsParams p) {
+  extern __shared__ int bounds[];   // n_feats + 1 feature boundaries in `values`
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (int r = 0; r < p.W; ++r) {
-    int* dv = p.dst_values[r];
-    for (long long i = tid; i < p.nnz; i += stride) dv[i] = p.values[i];
-    int* dof = p.dst_offsets[r];
-    for (long long i = tid; i < p.n_offsets; i += stride) dof[i] = p.offsets[i];
-    if (p.weights != nullptr) {
-      float* dw = p.dst_weights[r];
-      for (long long i = tid; i < p.nnz; i += stride) dw[i] = p.weights[i];
+  for (long long i = tid; i < p.n_offsets; i += stride) {
+    const int o = p.offsets[i];
+    for (int r = 0; r < p.W; ++r) p.dst_offsets[r][i] = o;
+  }
+  if (p.need != nullptr) {
+    for (int f = threadIdx.x; f <= p.n_feats; f += blockDim.x) bounds[f] = p.offsets[static_cast<long long>(f) * p.B];
+    __syncthreads();
+  }
+  for (long long i = tid; i < p.nnz; i += stride) {
+    unsigned int mask = 0xffu;
+    if (p.need != nullptr) {
+      int lo = 0, hi = p.n_feats;     // bounds[lo] <= i < bounds[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (bounds[mid] <= i) lo = mid; else hi = mid;
+      }
+      mask = p.need[lo];
+    }
+    const int v = p.values[i];
+    const float w = p.weights != nullptr ? p.weights[i] : 0.f;
+    for (int r = 0; r < p.W; ++r) {
+      if ((mask >> r) & 1u) {
+        p.dst_values[r][i] = v;
+        if (p.weights != nullptr) p.dst_weights[r][i] = w;
+      }
     }
   }
   grid_done_then_signal(p.done_counter, p.flags, p.W, seq_of(p.seq));
@@ -686,8 +708,11 @@ extern "C" int recml_tick(unsigned long long* counter, cudaStream_t stream) {
 extern "C" int recml_emb_push_ids(const PushIdsParams* p, cudaStream_t stream) {
   long long work = p->nnz > p->n_offsets ? p->nnz : p->n_offsets;
   int blocks = static_cast<int>((work + 1023) / 1024);
-  blocks = blocks < 1 ? 1 : (blocks > 296 ? 296 : blocks);
-  emb_push_ids_kernel<<<blocks, 256, 0, stream>>>(*p);
+  const int cap = 148 * 8;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  const size_t smem = p->need != nullptr ? (static_cast<size_t>(p->n_feats) + 1) * sizeof(int) : 0;
+  if (smem > 40 * 1024) return -2;
+  emb_push_ids_kernel<<<blocks, 256, smem, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -60,6 +60,8 @@ class FusedNvlinkReducer:
     self.side = torch.cuda.Stream(device=device)
     self.status = _lib.status_buffer(device)
     self._last_buckets = 0
+    self._issued = 0
+    self._attached = None
     from recml_b200.utils import graphs
     graphs.register(self)
 
@@ -88,60 +90,145 @@ class FusedNvlinkReducer:
     self.buf = symm.SymmBuffer(cv.off, self.group, self.device)
     self.seq = 0
 
-  def average_grads(self, params: Sequence[torch.Tensor]) -> None:
-    grads = []
-    for p in params:
-      g = p.grad
-      if g.dtype != torch.float32 or not g.is_contiguous():
-        g = g.to(torch.float32).contiguous()
-        p.grad = g
-      grads.append(g)
-    # bucket assignment
+  # ---- bucket layout ------------------------------------------------------------------------
+  def _layout(self, tensors) -> list[tuple[list, int]]:
+    """Greedy buckets of (tensor, element offset) in the given order; offsets are 8-aligned."""
     buckets, cur, n = [], [], 0
-    for g in grads:
-      sz = (g.numel() + 7) // 8 * 8
+    for t in tensors:
+      sz = (t.numel() + 7) // 8 * 8
       if cur and (n + sz > self.bucket_elems or len(cur) == MAXT):
         buckets.append((cur, n)); cur, n = [], 0
-      cur.append((g, n)); n += sz
+      cur.append((t, n)); n += sz
     if cur:
       buckets.append((cur, n))
     if len(buckets) > 64:
       raise ValueError("more than 64 gradient buckets; raise bucket_elems")
-    self._ensure(max(n for _, n in buckets))
-    main = torch.cuda.current_stream(self.device)
-    self.side.wait_stream(main)
+    return buckets
+
+  def _begin(self, producer: torch.cuda.Stream) -> None:
+    """First bucket of a step: fork the side stream off `producer` and advance the call counter."""
+    self.side.wait_stream(producer)
     self.calls += 1
-    self._last_buckets = len(buckets)
+    self._issued = 0
     with torch.cuda.stream(self.side):
       _lib.check_rc(self.lib.recml_tick(_lib.ptr(self.calls_dev), ctypes.c_void_p(self.side.cuda_stream)), "tick")
-      for bi, (items, n) in enumerate(buckets):
-        # flag value of bucket bi in call c: c*64 + bi (monotonic for any bucket count <= 64)
-        par = self.buckets_done & 1
-        self.buckets_done += 1
-        unit = 8 * self.world
-        total = (n + unit - 1) // unit * unit
-        b = _Bucket()
-        blocks = 0
-        for i, (g, off) in enumerate(items):
-          b.grad[i], b.numel[i], b.offset[i] = g.data_ptr(), g.numel(), off
-          b.block_start[i] = blocks
-          blocks += (g.numel() + 2047) // 2048
-        b.block_start[len(items)] = blocks
-        b.n = len(items)
-        c = _Comm()
-        for r in range(self.world):
-          c.inp[r] = self.buf.peer_ptr(r, self.in_off[par])
-          c.out[r] = self.buf.peer_ptr(r, self.out_off[par])
-          c.flag_a[r] = self.buf.peer_ptr(r, self.flag_off + self.rank * 8)
-          c.flag_b[r] = self.buf.peer_ptr(r, self.flag_off + (MAXW + self.rank) * 8)
-        c.my_flag_a = self.buf.peer_ptr(self.rank, self.flag_off)
-        c.my_flag_b = self.buf.peer_ptr(self.rank, self.flag_off + MAXW * 8)
-        c.done_counter = self.done.data_ptr()
-        c.W, c.me, c.total = self.world, self.rank, total
-        c.seq = _SeqRef(self.calls_dev.data_ptr(), 64, bi, 0)
-        c.scale = 1.0 / self.world if self.average else 1.0
-        c.status = self.status.data_ptr()
-        # zero the bucket tail so padding never carries stale values into the sum
-        _lib.check_rc(self.lib.recml_allreduce_bucket(ctypes.byref(b), ctypes.byref(c),
-                                                      ctypes.c_void_p(self.side.cuda_stream)), "allreduce_bucket")
+
+  def _issue(self, items, n: int) -> None:
+    """Launches pack + two-shot reduce + unpack of one bucket on the side stream.  `items` is a list
+    of (fp32 gradient, element offset); the k-th bucket issued in call c signals c*64 + k, which is
+    monotonic because every rank issues its buckets in the same order."""
+    k = self._issued
+    self._issued += 1
+    par = self.buckets_done & 1
+    self.buckets_done += 1
+    unit = 8 * self.world
+    total = (n + unit - 1) // unit * unit
+    b = _Bucket()
+    blocks = 0
+    for i, (g, off) in enumerate(items):
+      b.grad[i], b.numel[i], b.offset[i] = g.data_ptr(), g.numel(), off
+      b.block_start[i] = blocks
+      blocks += (g.numel() + 2047) // 2048
+    b.block_start[len(items)] = blocks
+    b.n = len(items)
+    c = _Comm()
+    for r in range(self.world):
+      c.inp[r] = self.buf.peer_ptr(r, self.in_off[par])
+      c.out[r] = self.buf.peer_ptr(r, self.out_off[par])
+      c.flag_a[r] = self.buf.peer_ptr(r, self.flag_off + self.rank * 8)
+      c.flag_b[r] = self.buf.peer_ptr(r, self.flag_off + (MAXW + self.rank) * 8)
+    c.my_flag_a = self.buf.peer_ptr(self.rank, self.flag_off)
+    c.my_flag_b = self.buf.peer_ptr(self.rank, self.flag_off + MAXW * 8)
+    c.done_counter = self.done.data_ptr()
+    c.W, c.me, c.total = self.world, self.rank, total
+    c.seq = _SeqRef(self.calls_dev.data_ptr(), 64, k, 0)
+    c.scale = 1.0 / self.world if self.average else 1.0
+    c.status = self.status.data_ptr()
+    with torch.cuda.stream(self.side):
+      _lib.check_rc(self.lib.recml_allreduce_bucket(ctypes.byref(b), ctypes.byref(c),
+                                                    ctypes.c_void_p(self.side.cuda_stream)), "allreduce_bucket")
+
+  @staticmethod
+  def _fp32_grad(p: torch.Tensor) -> torch.Tensor:
+    g = p.grad
+    if g.dtype != torch.float32 or not g.is_contiguous():
+      g = g.to(torch.float32).contiguous()
+      p.grad = g
+    return g
+
+  # ---- overlapped mode: reduce a bucket as soon as backward has produced it ------------------
+  def attach(self, params: Sequence[torch.Tensor]) -> None:
+    """Fixes the bucket layout over `params` (filled in reverse order, the order in which backward
+    produces gradients) and hooks every parameter so that a bucket is reduced on the side stream
+    the moment its last gradient has been accumulated; `average_grads` then only launches what is
+    left and joins the side stream.  Collective: every rank attaches the same parameters.  One
+    backward pass per `average_grads` call (no gradient accumulation across backward passes)."""
+    if self._attached is not None:
+      if [id(p) for p in self._attached] == [id(p) for p in reversed(list(params))]:
+        return
+      for h in self._hooks:       # a new state replaces the old one
+        h.remove()
+    order = [p for p in reversed(list(params))]
+    self._attached = order
+    self._abuckets = self._layout(order)
+    self._bucket_of = {}
+    for bi, (items, _) in enumerate(self._abuckets):
+      for p, _off in items:
+        self._bucket_of[id(p)] = bi
+    self._ensure(max(n for _, n in self._abuckets))
+    self._reset_step()
+    self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in order]
+
+  def _reset_step(self) -> None:
+    self._ready = [0] * len(self._abuckets)
+    self._launched = [False] * len(self._abuckets)
+    self._began = False
+
+  def _launch_attached(self, bi: int) -> None:
+    cur = torch.cuda.current_stream(self.device)
+    if not self._began:
+      self._began = True
+      self._begin(cur)
+    else:
+      self.side.wait_stream(cur)
+    items, n = self._abuckets[bi]
+    live = [(self._fp32_grad(p), off) for p, off in items if p.grad is not None]
+    self._launched[bi] = True
+    if live:
+      self._issue(live, n)
+
+  def _on_grad(self, p: torch.Tensor) -> None:
+    bi = self._bucket_of[id(p)]
+    if self._launched[bi]:
+      raise RuntimeError("a gradient arrived for a bucket that was already reduced: overlapped gradient "
+                         "reduction supports one backward pass per optimizer step")
+    self._ready[bi] += 1
+    if self._ready[bi] == len(self._abuckets[bi][0]):
+      self._launch_attached(bi)
+
+  def _finish_attached(self, params: Sequence[torch.Tensor]) -> None:
+    known = self._bucket_of
+    extra = [p for p in params if id(p) not in known]
+    if extra:
+      raise ValueError(f"{len(extra)} parameters were not attached to the overlapped reducer")
+    for bi in range(len(self._abuckets)):
+      if not self._launched[bi] and any(p.grad is not None for p, _ in self._abuckets[bi][0]):
+        self._launch_attached(bi)
+    if self._began:
+      torch.cuda.current_stream(self.device).wait_stream(self.side)
+    self._last_buckets = self._issued if self._began else 0
+    self._reset_step()
+
+  def average_grads(self, params: Sequence[torch.Tensor]) -> None:
+    if self._attached is not None:
+      self._finish_attached(params)
+      return
+    grads = [self._fp32_grad(p) for p in params]
+    buckets = self._layout(grads)
+    self._ensure(max(n for _, n in buckets))
+    main = torch.cuda.current_stream(self.device)
+    self._begin(main)
+    self._last_buckets = len(buckets)
+    for items, n in buckets:
+      self._issue(items, n)
     main.wait_stream(self.side)

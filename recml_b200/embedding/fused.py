@@ -87,7 +87,7 @@ class PushIdsParams(ctypes.Structure):
   _fields_ = [("values", c_vp), ("offsets", c_vp), ("weights", c_vp), ("nnz", c_ll), ("n_offsets", c_int),
               ("W", c_int), ("me", c_int), ("dst_values", c_vp * MAXW), ("dst_offsets", c_vp * MAXW),
               ("dst_weights", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
-              ("seq", SeqRef)]
+              ("seq", SeqRef), ("need", c_vp), ("n_feats", c_int), ("B", c_int)]
 
 
 _layout_checked = False
@@ -126,6 +126,7 @@ class FusedBackend:
     self.layout, self.width = collective.feature_layout(m)
     self.capacity_factor = capacity_factor
     self.seq = 0
+    self._need = None
     self.seq_dev = torch.zeros(1, dtype=torch.int64, device=module.device)
     self.B = None
     self.status = _lib.status_buffer(m.device)
@@ -234,6 +235,18 @@ class FusedBackend:
     self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
     self.buf = symm.SymmBuffer(cv.off, m.group, m.device)
 
+  def _need_mask(self) -> torch.Tensor:
+    """uint8 per feature: bit r set when rank r holds rows (or columns) of the feature's table, i.e.
+    needs its ids."""
+    if self._need is None:
+      m = self.m
+      bits = []
+      for fname in m.feature_names:
+        tp = m.plan.tables[m.feature_to_table[fname]]
+        bits.append(1 << tp.owner if tp.placement is Placement.TABLE_WISE else (1 << m.world) - 1)
+      self._need = torch.tensor(bits, dtype=torch.uint8, device=m.device)
+    return self._need
+
   def _feat_descs(self, si: int, direct: tuple[int, int] | None) -> torch.Tensor:
     """Device array of FeatDesc for stack `si`.  `direct=(ld, out_col)` makes the forward kernel
     store straight into a `[B, ld]` output matrix (and read gradients from a matrix of the same
@@ -337,6 +350,7 @@ class FusedBackend:
         p.dst_weights[r] = self.buf.peer_ptr(r, wo)
         p.flags[r] = self._flag_ptr(r, 0, m.rank)
       p.done_counter, p.seq = self.done_ids.data_ptr(), seq
+      p.need, p.n_feats, p.B = self._need_mask().data_ptr(), len(m.feature_names), B
       _lib.check_rc(self.lib.recml_emb_push_ids(ctypes.byref(p), st), "emb_push_ids")
       for s in range(W):
         vo, oo, wo = self.ids_off[par][s]

@@ -91,8 +91,9 @@ class KeyedJagged:
       if t is None:
         return None
       if device.type == "cuda" and not t.is_cuda:
-        src = stager.stage(t) if stager is not None else t.pin_memory()
-        return src.to(device, non_blocking=True)
+        if stager is not None:
+          return stager.put(t, device)
+        return t.pin_memory().to(device, non_blocking=True)
       return t.to(device)
     return KeyedJagged(self.keys, put(self.values), put(self.offsets), put(self.weights), self._batch)
 

@@ -36,7 +36,7 @@ class ShardedEmbeddingConfig:
   optimizer: specs_lib.OptimizerSpec
   sharding_strategy: str = "auto"          # "auto" | "MOD" (all row-wise) | "table" | "column"
   placement_overrides: Mapping[str, Placement] | None = None
-  row_wise_min_bytes: int = 256 << 20
+  row_wise_min_bytes: int | None = None   # None: cost-balanced placement (see planner)
   replicate_max_rows: int = 0
   allow_id_dropping: bool = False
   ids_per_sample: Mapping[str, float] | None = None

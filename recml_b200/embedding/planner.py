@@ -4,11 +4,15 @@ The reference has one strategy — MOD row sharding of stacked tables over all
 SparseCores, row i on shard (i % S + rotation) % S at local row i // S — plus a manual
 vocabulary threshold below which a table is a replicated dense layer
 (`recml/inference/models/jax/DLRM_DCNv2/dlrm_main.py:129-131`).  On an NVSwitch box all
-peers are equidistant, so placement only has to balance (a) HBM bytes and (b) gather
-work per rank:
+peers are equidistant and one GPU holds 180 GB, so placement is driven by traffic and
+gather balance, not by fitting a table:
 
-  ROW_WISE     rows MOD-sharded over all ranks (large tables; spreads hot rows)
-  TABLE_WISE   whole table on one rank (medium tables; one pooled vector per bag moves)
+  TABLE_WISE   whole table on one rank: ONE pooled vector per bag crosses NVLink in the
+               forward and one gradient vector in the backward (the default)
+  ROW_WISE     rows MOD-sharded over all ranks: every rank sends a partial per bag, W times
+               the traffic, so only tables whose gather work would unbalance the ranks
+               (cost above `hot_fraction` of the per-rank mean) or that exceed
+               `table_wise_max_bytes` are split
   COLUMN_WISE  every rank holds a slice of the embedding dim (few-row, very hot tables)
   REPLICATED   every rank holds the table; its gradient joins the dense all-reduce
 
@@ -77,45 +81,73 @@ def _local_rows(vocab: int, world: int, rank: int, rotation: int) -> int:
 
 def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
                 ids_per_sample: Mapping[str, float] | None = None,
-                row_wise_min_bytes: int = 256 << 20, replicate_max_rows: int = 0,
+                row_wise_min_bytes: int | None = None, replicate_max_rows: int = 0,
                 column_wise: Sequence[str] = (), overrides: Mapping[str, Placement] | None = None,
-                default: Placement | None = None) -> ShardingPlan:
-  """Greedy plan.  Large tables are row-sharded; the rest go table-wise to the rank with
-  the least accumulated gather cost (ids per sample × dim), largest first."""
+                default: Placement | None = None, hot_fraction: float = 0.75,
+                table_wise_max_bytes: int = 48 << 30, rank_budget_bytes: int = 140 << 30
+                ) -> ShardingPlan:
+  """Greedy plan.  Cost of a table = ids per sample × dim (its gather work and its wire
+  bytes).  Tables hotter than `hot_fraction` × (total cost / world), or larger than
+  `table_wise_max_bytes`, are row-sharded; the rest go table-wise, largest cost first, to
+  the rank with the least accumulated cost that still has `rank_budget_bytes` of room.
+  `row_wise_min_bytes`, when given, replaces the cost rule with a plain size threshold."""
   overrides = dict(overrides or {})
   ids_per_sample = ids_per_sample or {}
   plans: dict[str, TablePlan] = {}
   load = [0.0] * world
+  used = [0] * world
   rot = 0
-  rw_cost = 0.0
-  order = sorted(tables, key=lambda t: -(ids_per_sample.get(t.name, 1.0) * t.embedding_dim))
+  cost_of = lambda t: ids_per_sample.get(t.name, 1.0) * t.embedding_dim
+  mean_cost = sum(cost_of(t) for t in tables) / max(world, 1)
+  order = sorted(tables, key=lambda t: -cost_of(t))
+
+  def row_bytes(t):
+    return t.embedding_dim * 4 + t.optimizer.slot_bytes_per_row(t.embedding_dim)
+
+  def auto(t):
+    size = t.vocabulary_size * row_bytes(t)
+    if world == 1:
+      return Placement.TABLE_WISE
+    if t.name in column_wise:
+      return Placement.COLUMN_WISE
+    if default is not None:
+      return default
+    if t.vocabulary_size <= replicate_max_rows:
+      return Placement.REPLICATED
+    if row_wise_min_bytes is not None:
+      return Placement.ROW_WISE if size >= row_wise_min_bytes else Placement.TABLE_WISE
+    if size > table_wise_max_bytes or (cost_of(t) > hot_fraction * mean_cost and t.vocabulary_size >= world):
+      return Placement.ROW_WISE
+    return Placement.TABLE_WISE
+
+  chosen = {t.name: overrides.get(t.name) or auto(t) for t in tables}
+  # row-/column-wise tables load every rank equally: account for them before the greedy pass
+  for t in tables:
+    if chosen[t.name] in (Placement.ROW_WISE, Placement.COLUMN_WISE):
+      for r in range(world):
+        load[r] += cost_of(t) / world
+        used[r] += t.vocabulary_size * row_bytes(t) // world
   for t in order:
-    size = t.vocabulary_size * t.embedding_dim * 4
-    p = overrides.get(t.name)
-    if p is None:
-      if world == 1:
-        p = Placement.TABLE_WISE
-      elif t.name in column_wise:
-        p = Placement.COLUMN_WISE
-      elif default is not None:
-        p = default
-      elif t.vocabulary_size <= replicate_max_rows:
-        p = Placement.REPLICATED
-      elif size >= row_wise_min_bytes:
-        p = Placement.ROW_WISE
-      else:
-        p = Placement.TABLE_WISE
-    cost = ids_per_sample.get(t.name, 1.0) * t.embedding_dim
+    p = chosen[t.name]
+    size = t.vocabulary_size * row_bytes(t)
+    if p is Placement.TABLE_WISE and world > 1 and t.name not in overrides:
+      if not any(used[r] + size <= rank_budget_bytes for r in range(world)):
+        p = Placement.ROW_WISE      # no rank has room for the whole table
+        for r in range(world):
+          load[r] += cost_of(t) / world
+          used[r] += size // world
+    cost = cost_of(t)
     tp = TablePlan(t.name, t.vocabulary_size, t.embedding_dim, p)
     if p is Placement.ROW_WISE:
       tp.rotation = rot % world
       rot += 1
       tp.local_rows = _local_rows(t.vocabulary_size, world, rank, tp.rotation)
       tp.local_dim = t.embedding_dim
-      rw_cost += cost / world
     elif p is Placement.TABLE_WISE:
-      tp.owner = min(range(world), key=lambda r: load[r])
+      fits = [r for r in range(world) if used[r] + size <= rank_budget_bytes] or list(range(world))
+      tp.owner = min(fits, key=lambda r: load[r])
       load[tp.owner] += cost
+      used[tp.owner] += size
       tp.local_rows = t.vocabulary_size if tp.owner == rank else 0
       tp.local_dim = t.embedding_dim
     elif p is Placement.COLUMN_WISE:

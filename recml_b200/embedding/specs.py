@@ -36,6 +36,10 @@ class OptimizerSpec:
   def slot_init(self, slot: str) -> float:
     return 0.0
 
+  def slot_bytes_per_row(self, dim: int) -> int:
+    """Optimizer-state bytes stored beside each table row (fp32 slots)."""
+    return sum(4 if self.slot_is_rowwise(s) else 4 * dim for s in self.slot_names())
+
   def hyperparams(self, step: int) -> tuple[float, ...]:
     """Scalars handed to the update kernel for this step (first one is the step size)."""
     return (self.lr(step),)

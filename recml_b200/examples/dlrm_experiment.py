@@ -38,7 +38,7 @@ class ModelConfig:
   cross_rank: int | None = 512
   embedding_learning_rate: float = 0.01
   embedding_init_scale: float | None = None
-  row_wise_min_bytes: int = 256 << 20
+  row_wise_min_bytes: int | None = None
   backend: str = "auto"
 
 
@@ -92,8 +92,11 @@ class PredictionTask(task_lib.Task):
         "common/batch_size": M.scalar(float(n)),
     }
     if r.hist_pos is not None:
-      out["auc"] = M.AUCPR.from_histograms(r.hist_pos, r.hist_neg)
-      out["aucroc"] = M.AUCROC.from_histograms(r.hist_pos, r.hist_neg)
+      # one pass over the histograms feeds both curves
+      tp, tn, fp, fn = M.confusion_from_histograms(r.hist_pos, r.hist_neg)
+      counts = dict(true_positives=tp, true_negatives=tn, false_positives=fp, false_negatives=fn)
+      out["auc"] = M.AUCPR(**counts)
+      out["aucroc"] = M.AUCROC(**counts)
     return out
 
   def train_step(self, batch, state, rng):

@@ -3,7 +3,8 @@ metrics the reference README promises)."""
 from recml_b200.metrics.base import Metric, ScalarMetric, scalar
 from recml_b200.metrics.confusion import (AUCPR, AUCROC, FBeta, Precision, PrecisionAtRecall,
                                           Recall, aucpr, aucroc, default_thresholds,
-                                          estimate_confusion_matrix, f1_score, fbeta_score,
+                                          confusion_from_histograms, estimate_confusion_matrix, f1_score,
+                                          fbeta_score,
                                           precision, precision_at_recall, recall)
 from recml_b200.metrics.mean import (accuracy, binary_accuracy, mean_squared_error,
                                      top_k_accuracy)

@@ -24,7 +24,7 @@ class DLRMDCNv2(nn.Module):
                cross_rank: int | None = 512, bag_sizes: Sequence[int] | None = None,
                embedding_optimizer: emb.OptimizerSpec | None = None, combiner: str = "sum",
                feature_names: Sequence[str] | None = None, device=None, group=None,
-               sharding_strategy: str = "auto", row_wise_min_bytes: int = 256 << 20,
+               sharding_strategy: str = "auto", row_wise_min_bytes: int | None = None,
                backend: str = "auto", seed: int = 0, init_scale: float | None = None):
     super().__init__()
     if bottom_mlp_dims[-1] != embedding_dim:

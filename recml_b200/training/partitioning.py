@@ -36,27 +36,40 @@ def default_device() -> torch.device:
 
 
 class _PinnedStager:
-  """Reusable pinned host buffers so every H2D copy is asynchronous."""
+  """Reusable pinned host buffers so every H2D copy is asynchronous.
 
-  def __init__(self):
-    self._bufs: dict[tuple, list[torch.Tensor]] = {}
-    self._turn = 0
+  A buffer is handed out again only after the copy that last read it has finished: `put` records
+  an event behind the copy, and a buffer whose event is still pending is skipped (a new one is
+  allocated, up to `max_per_key` per shape; beyond that the host waits for the oldest copy).
+  Tensors of equal shape inside one batch therefore never share a buffer, however far the host
+  runs ahead of the device.
+  """
 
-  def stage(self, t: torch.Tensor) -> torch.Tensor:
+  def __init__(self, max_per_key: int = 16):
+    self._bufs: dict[tuple, list[list]] = {}
+    self.max_per_key = max_per_key
+
+  def put(self, t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """Pageable host tensor → device tensor through a pinned buffer (pinned inputs go directly)."""
     if t.is_pinned():
-      return t
+      return t.to(device, non_blocking=True)
     key = (tuple(t.shape), t.dtype)
     ring = self._bufs.setdefault(key, [])
-    if len(ring) < 3:  # triple buffering: a buffer is reused two steps later
-      ring.append(torch.empty(t.shape, dtype=t.dtype, pin_memory=True))
-      buf = ring[-1]
-    else:
-      buf = ring[self._turn % 3]
-    buf.copy_(t)
-    return buf
-
-  def advance(self):
-    self._turn += 1
+    slot = next((s for s in ring if s[1] is None or s[1].query()), None)
+    if slot is None:
+      if len(ring) < self.max_per_key:
+        slot = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True), None]
+        ring.append(slot)
+      else:
+        slot = ring.pop(0)          # oldest copy: wait for it, then recycle its buffer
+        slot[1].synchronize()
+        ring.append(slot)
+    slot[0].copy_(t)
+    out = slot[0].to(device, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(device))
+    slot[1] = ev
+    return out
 
 
 class Partitioner(abc.ABC):
@@ -89,13 +102,11 @@ class NullPartitioner(Partitioner):
     if not isinstance(x, torch.Tensor):
       return x
     if self.device.type == "cuda" and not x.is_cuda:
-      return self._stager.stage(x).to(self.device, non_blocking=True)
+      return self._stager.put(x, self.device)
     return x.to(self.device)
 
   def shard_inputs(self, inputs: Any) -> Any:
-    out = _tree_map(self._put, inputs)
-    self._stager.advance()
-    return out
+    return _tree_map(self._put, inputs)
 
   def partition_init(self, init_fn, *, abstract_batch=None):
     return init_fn
@@ -115,8 +126,10 @@ class DataParallelPartitioner(NullPartitioner):
 
   def __init__(self, data_axis: str = "batch", *, group: Any = None,
                inputs_are_global: bool = False, device=None, grad_dtype: torch.dtype | None = None,
-               use_cuda_graph: bool = False, graph_warmup_steps: int = 3):
+               use_cuda_graph: bool = False, graph_warmup_steps: int = 3,
+               overlap_grad_reduce: bool = True):
     super().__init__(device)
+    self.overlap_grad_reduce = overlap_grad_reduce
     self.use_cuda_graph = use_cuda_graph
     self.graph_warmup_steps = graph_warmup_steps
     self.data_axis = data_axis
@@ -148,13 +161,26 @@ class DataParallelPartitioner(NullPartitioner):
       inputs = _tree_map(cut, inputs)
     return super().shard_inputs(inputs)
 
-  def all_reduce_grads(self, params: Sequence[torch.Tensor]) -> None:
-    if self.world == 1 or not params:
-      return
+  def _get_reducer(self):
     if self._reducer is None:
       from recml_b200.comm import grad_reducer
       self._reducer = grad_reducer.make_reducer(self.group, self.device)
-    self._reducer.average_grads(params)
+    return self._reducer
+
+  def all_reduce_grads(self, params: Sequence[torch.Tensor]) -> None:
+    if self.world == 1 or not params:
+      return
+    self._get_reducer().average_grads(params)
+
+  def _attach_overlap(self, state: state_lib.State) -> None:
+    """Lets the fused reducer start each gradient bucket from a hook inside backward, so the
+    exchange runs under the rest of the backward pass (the embedding update above all)."""
+    if self.world == 1 or not self.overlap_grad_reduce or state.optimizer is None:
+      return
+    reducer = self._get_reducer()
+    params = [p for p in state.optimizer.params if p.requires_grad]
+    if hasattr(reducer, "attach") and params:
+      reducer.attach(params)
 
   def _replicate(self, state: state_lib.State) -> state_lib.State:
     if self.world > 1:
@@ -164,6 +190,7 @@ class DataParallelPartitioner(NullPartitioner):
             dist.broadcast(t, src=dist.get_global_rank(self.group, 0) if self.group else 0,
                            group=self.group)
     state.grad_sync = self.all_reduce_grads
+    self._attach_overlap(state)
     return state
 
   def partition_init(self, init_fn, *, abstract_batch=None):

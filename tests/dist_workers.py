@@ -179,3 +179,4 @@ def sequence_experiment(rank, world, device_type, which, steps):
   logs = run_experiment(C.build(cfg), "train_and_eval")
   return {k: {kk: float(vv) for kk, vv in v.items() if not kk.startswith(("perf", "model", "optimizer"))}
           for k, v in logs.items()}
+
