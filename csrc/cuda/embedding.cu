@@ -449,7 +449,7 @@ struct BwdParams {
   long long val_scale;
   float* table; float* slot0; float* slot1; int dloc;
   int opt; float hp[6]; float grad_scale; int slot1_rowwise;
-  float* scratch;               // [n_chunks, dloc] partial sums of runs that cross chunk boundaries (kept zero)
+  float* scratch;               // [>= ceil(n / kRange), dloc] partial sums of runs that cross range boundaries (kept zero)
   const unsigned long long* wait_flags; int W; SeqRef seq; int* status;
 };
 
@@ -587,76 +587,86 @@ __device__ __forceinline__ unsigned int lower_bound(const uint32_t* keys, unsign
   return lo;
 }
 
-// One warp per chunk of 32 sorted occurrences.  Runs of equal rows that lie inside the chunk are
-// reduced in registers and applied at once; the pieces of a run that crosses chunk boundaries are
-// added (fp32 atomics) into the scratch line of the chunk where the run STARTS, and
-// emb_bwd_finalize applies those afterwards.  Hot rows (Zipf heads with 10^5 occurrences) are
-// thereby reduced by thousands of warps in parallel instead of one.
+// One warp per RANGE of kRange sorted occurrences, walked in 32-wide windows with the running sum
+// carried across windows.  A run of equal rows that lies inside the range is reduced in registers
+// and applied at once; the pieces of a run that crosses range boundaries are added (fp32 atomics)
+// into the scratch line of the range where the run STARTS, and emb_bwd_finalize applies those
+// afterwards.  Hot rows (Zipf heads with 10^5 occurrences) are thereby reduced by thousands of
+// warps in parallel, with one atomic line update per kRange occurrences.
+constexpr unsigned int kRange = 128;
+
 template <int VPL, bool GAINS>
 __global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) {
   if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 2)) return;
   const int lane = threadIdx.x & 31;
   const unsigned int n = *p.n_occ;
-  const unsigned int chunk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const unsigned int start = chunk * 32u;
+  const unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned int start = range * kRange;
   if (start >= n) return;
-  const int cnt = min(32u, n - start);
+  const unsigned int end = min(start + kRange, n);
   const bool lane_on = lane * VPL < p.dloc;
-  uint32_t key = 0xffffffffu, val = 0;
-  if (lane < cnt) { key = p.keys[start + lane]; val = p.vals[start + lane]; }
-  unsigned int gv = val;
-  float gain = 1.f;
-  if (GAINS && lane < cnt) {
-    gv = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
-    gain = p.occ_gain[2 * static_cast<size_t>(val) + 1];
-  }
-  const bool has_prev = start > 0, has_next = start + cnt < n;
+  const bool has_prev = start > 0, has_next = end < n;
   const uint32_t prev_key = has_prev ? p.keys[start - 1] : 0;
-  const uint32_t next_key = has_next ? p.keys[start + cnt] : 0;
+  const uint32_t next_key = has_next ? p.keys[end] : 0;
   Vec<VPL> acc;
 #pragma unroll
   for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-  int seg_start = 0;
-  for (int j0 = 0; j0 < cnt; j0 += 4) {
-    Vec<VPL> g[4]; uint32_t kj[4]; float gj[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = min(j0 + u, cnt - 1);
-      kj[u] = __shfl_sync(0xffffffffu, key, j);
-      const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
-      gj[u] = __shfl_sync(0xffffffffu, gain, j);
-      if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
+  bool first_run = true;      // no run has been closed yet: the open one may have begun before `start`
+  for (unsigned int w0 = start; w0 < end; w0 += 32u) {
+    const int cnt = static_cast<int>(min(32u, end - w0));
+    uint32_t key = 0xffffffffu, val = 0;
+    if (lane < cnt) { key = p.keys[w0 + lane]; val = p.vals[w0 + lane]; }
+    unsigned int gv = val;
+    float gain = 1.f;
+    if (GAINS && lane < cnt) {
+      gv = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
+      gain = p.occ_gain[2 * static_cast<size_t>(val) + 1];
     }
+    const bool window_is_last = w0 + cnt >= end;
+    // key that follows this window inside the range (only read when there is one)
+    const uint32_t after = window_is_last ? 0u : p.keys[w0 + cnt];
+    for (int j0 = 0; j0 < cnt; j0 += 4) {
+      Vec<VPL> g[4]; uint32_t kj[4]; float gj[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u;
-      if (j >= cnt) break;
-      if (lane_on) {
-#pragma unroll
-        for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? gj[u] : 1.f, g[u].v[e], acc.v[e]);
+      for (int u = 0; u < 4; ++u) {
+        const int j = min(j0 + u, cnt - 1);
+        kj[u] = __shfl_sync(0xffffffffu, key, j);
+        const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
+        gj[u] = __shfl_sync(0xffffffffu, gain, j);
+        if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
       }
-      const uint32_t knext = __shfl_sync(0xffffffffu, key, min(j + 1, 31));
-      const bool last = (j == cnt - 1) || (knext != kj[u]);
-      if (!last) continue;
-      const bool begins = (seg_start > 0) || !has_prev || (prev_key != kj[u]);
-      const bool ends = (j < cnt - 1) || !has_next || (next_key != kj[u]);
-      if (begins && ends) {
-        apply_row_update<VPL>(p, kj[u], acc, lane, lane_on);
-      } else {
-        unsigned int slot = chunk;
-        if (!begins) {
-          if (lane == 0) slot = lower_bound(p.keys, start, kj[u]) >> 5;
-          slot = __shfl_sync(0xffffffffu, slot, 0);
-        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u;
+        if (j >= cnt) break;
         if (lane_on) {
-          float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
 #pragma unroll
-          for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
+          for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? gj[u] : 1.f, g[u].v[e], acc.v[e]);
         }
-      }
+        const uint32_t knext = __shfl_sync(0xffffffffu, key, min(j + 1, 31));
+        const bool at_range_end = window_is_last && j == cnt - 1;
+        const bool last = at_range_end || ((j == cnt - 1) ? (after != kj[u]) : (knext != kj[u]));
+        if (!last) continue;
+        const bool begins = !first_run || !has_prev || (prev_key != kj[u]);
+        const bool ends = !at_range_end || !has_next || (next_key != kj[u]);
+        if (begins && ends) {
+          apply_row_update<VPL>(p, kj[u], acc, lane, lane_on);
+        } else {
+          unsigned int slot = range;
+          if (!begins) {
+            if (lane == 0) slot = lower_bound(p.keys, start, kj[u]) / kRange;
+            slot = __shfl_sync(0xffffffffu, slot, 0);
+          }
+          if (lane_on) {
+            float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
 #pragma unroll
-      for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-      seg_start = j + 1;
+            for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+        first_run = false;
+      }
     }
   }
 }
@@ -665,15 +675,15 @@ template <int VPL>
 __global__ void __launch_bounds__(256) emb_bwd_finalize_kernel(const BwdParams p) {
   const int lane = threadIdx.x & 31;
   const unsigned int n = *p.n_occ;
-  const unsigned int chunk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const unsigned int start = chunk * 32u;
+  const unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned int start = range * kRange;
   if (start >= n) return;
-  const unsigned int last = min(start + 32u, n) - 1;
+  const unsigned int last = min(start + kRange, n) - 1;
   const uint32_t klast = p.keys[last];
-  if (!(last + 1 < n && p.keys[last + 1] == klast)) return;            // run does not cross into the next chunk
+  if (!(last + 1 < n && p.keys[last + 1] == klast)) return;            // run does not cross into the next range
   if (p.keys[start] == klast && start > 0 && p.keys[start - 1] == klast) return;  // run started earlier
   const bool lane_on = lane * VPL < p.dloc;
-  float* sp = p.scratch + static_cast<size_t>(chunk) * p.dloc + lane * VPL;
+  float* sp = p.scratch + static_cast<size_t>(range) * p.dloc + lane * VPL;
   Vec<VPL> acc;
 #pragma unroll
   for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
@@ -771,13 +781,13 @@ extern "C" int recml_sort_pairs_u32(const uint32_t* keys_in, uint32_t* keys_out,
   return e == cudaSuccess ? 0 : -1;
 }
 
-// max_occ: host-side upper bound of *n_occ used to size the grid (chunks beyond n exit at once).
+// max_occ: host-side upper bound of *n_occ used to size the grid (ranges beyond n exit at once).
 extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int gains, cudaStream_t stream) {
   const int vpl = vpl_for(p->dloc);
   if (vpl == 0 || (p->dloc % vpl) != 0) return -10;
   if (max_occ <= 0) return 0;
-  const long long chunks = (max_occ + 31) / 32;
-  const int blocks = static_cast<int>((chunks + 7) / 8);
+  const long long ranges = (max_occ + kRange - 1) / kRange;
+  const int blocks = static_cast<int>((ranges + 7) / 8);
 #define RECML_BWD(V)                                                                      \
   do {                                                                                    \
     if (gains) emb_bwd_update_kernel<V, true><<<blocks, 256, 0, stream>>>(*p);            \
