@@ -15,7 +15,7 @@ import gc
 import logging as pylogging
 import os
 import time
-from typing import Any, Callable, Mapping
+from typing import Any, Callable, Mapping, Sequence
 
 import numpy as np
 import torch
@@ -24,6 +24,7 @@ from torch import nn
 from recml_b200 import ckpt as ckpt_lib
 from recml_b200.metrics import reduction
 from recml_b200.metrics import tools as metrics_tools
+from recml_b200.training import callbacks as callbacks_lib
 from recml_b200.training import core
 from recml_b200.training import optim_factory
 from recml_b200.training import partitioning
@@ -61,7 +62,8 @@ class ModuleTrainer(core.Trainer[ModuleTask]):
                model_dir: str | None = None, train_steps: int = 0, steps_per_loop: int | None = None,
                steps_per_eval: int | None = None, continuous_eval_timeout: int = 30,
                max_checkpoints_to_keep: int = 5, checkpoint_save_interval_epochs: int = 1,
-               rng_seed: int = core.DEFAULT_RNG_SEED, enable_checkpointing: bool = True):
+               rng_seed: int = core.DEFAULT_RNG_SEED, enable_checkpointing: bool = True,
+               callbacks: Sequence["callbacks_lib.Callback"] = ()):
     self._partitioner = distribution or partitioning.NullPartitioner()
     self._model_dir = model_dir or "/tmp"
     self._steps_per_epoch = steps_per_loop if steps_per_loop is not None else max(train_steps, 1)
@@ -73,6 +75,7 @@ class ModuleTrainer(core.Trainer[ModuleTask]):
     self._ckpt_dir = os.path.join(self._model_dir, core.CHECKPOINT_DIR)
     self._max_keep = max_checkpoints_to_keep
     self._interval = checkpoint_save_interval_epochs
+    self._callbacks = list(callbacks)
 
   def _manager(self) -> ckpt_lib.CheckpointManager:
     return ckpt_lib.CheckpointManager(self._ckpt_dir, max_to_keep=self._max_keep,
@@ -129,7 +132,14 @@ class ModuleTrainer(core.Trainer[ModuleTask]):
         log_dir=os.path.join(self._model_dir, core.LOG_DIR), name=core.EVAL_LOG_DIRNAME)
     history: dict[str, list[float]] = {}
     it = iter(train_ds)
+    for cb in self._callbacks:
+      cb.set_state(state)
+      begin = cb.on_train_begin({})
+      if begin is not None:
+        first_epoch = max(first_epoch, begin)
     for epoch in range(first_epoch, self._num_epochs):
+      for cb in self._callbacks:
+        cb.on_epoch_begin(epoch, {})
       cm.module.train()
       totals: dict[str, Any] = {}
       t0 = time.time()
@@ -164,8 +174,12 @@ class ModuleTrainer(core.Trainer[ModuleTask]):
         history.setdefault(k, []).append(v)
       if mgr is not None:
         mgr.save(epoch, state.state_dict())
+      for cb in self._callbacks:
+        cb.on_epoch_end(epoch, logs)
     if mgr is not None:
       mgr.wait_until_finished()
+    for cb in self._callbacks:
+      cb.on_train_end({k: v[-1] for k, v in history.items()})
     rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
     if rank == 0:
       os.makedirs(self._model_dir, exist_ok=True)

@@ -183,6 +183,12 @@ class Optimizer:
     for p in self.params:
       p.grad = None
 
+  def reset_step_count(self) -> None:
+    """Restarts the schedule / bias-correction clock while keeping the slots (the
+    `restore_iterations=False` case of `recml/core/utils/keras_utils.py:293-294`)."""
+    self.count = 0
+    self.hyperparams["learning_rate"] = self._lr_at(0)
+
   # -- checkpointing -----------------------------------------------------------
   def state_dict(self) -> dict[str, Any]:
     out: dict[str, Any] = {"count": torch.tensor(self.count, dtype=torch.int64)}

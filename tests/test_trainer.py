@@ -152,3 +152,50 @@ def test_module_trainer_modes(tmp_path, mode):
     assert "val_loss" in hist and "val_mse" in hist
   if mode == "eval":
     assert "loss" in hist
+
+
+def test_callbacks_and_selective_restore(tmp_path):
+  from recml_b200.training import callbacks
+  seen = []
+
+  class _Spy(callbacks.Callback):
+    def on_train_begin(self, logs=None):
+      seen.append("begin")
+
+    def on_epoch_end(self, epoch, logs=None):
+      seen.append(("epoch", epoch, "loss" in logs))
+
+    def on_train_end(self, logs=None):
+      seen.append("end")
+
+  side = os.path.join(tmp_path, "side")
+  mgr = ckpt.CheckpointManager(os.path.join(side, "checkpoints"), item_name="default")
+  cbs = [_Spy(), callbacks.EpochCheckpointAndRestoreCallback(mgr, marker_path=os.path.join(side, "marker.txt")),
+         callbacks.EpochSummaryCallback(os.path.join(side, "logs"), steps_per_epoch=10)]
+  trainer = recml.KerasTrainer(model_dir=str(tmp_path), train_steps=20, steps_per_loop=10, callbacks=cbs,
+                               enable_checkpointing=False)
+  trainer.train(_ModTask())
+  assert seen == ["begin", ("epoch", 0, True), ("epoch", 1, True), "end"]
+  assert open(os.path.join(side, "marker.txt")).read() == "COMPLETED"
+  assert ckpt.all_steps(os.path.join(side, "checkpoints")) == [0, 1]
+  assert os.path.isdir(os.path.join(side, "logs", "train"))
+
+  # selective restore into a fresh state
+  def fresh():
+    torch.manual_seed(1)
+    return recml.State.create(model=nn.Linear(4, 1, bias=False), tx=recml.AdamFactory(learning_rate=0.05).make())
+  ckdir = os.path.join(side, "checkpoints")
+  full = fresh()
+  assert callbacks.restore_state(full, ckdir) == 1
+  assert full.optimizer.count == 20 and float(full.optimizer.slots["nu"][0].abs().sum()) > 0
+  no_opt = fresh()
+  callbacks.restore_state(no_opt, ckdir, restore_optimizer_vars=False, restore_steps=False)
+  assert torch.equal(no_opt.params["weight"], full.params["weight"])
+  assert no_opt.optimizer.count == 0 and float(no_opt.optimizer.slots["nu"][0].abs().sum()) == 0 and no_opt.step == 0
+  no_iter = fresh()
+  callbacks.restore_state(no_iter, ckdir, step=0, restore_iterations=False)
+  assert no_iter.optimizer.count == 0 and float(no_iter.optimizer.slots["nu"][0].abs().sum()) > 0
+  with pytest.raises(ValueError):
+    callbacks.restore_state(fresh(), ckdir, step=7)
+  with pytest.raises(FileNotFoundError):
+    callbacks.restore_state(fresh(), os.path.join(tmp_path, "nothing"))
