@@ -5,6 +5,7 @@
 // the reference relies on.
 #include <cstdint>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -214,6 +215,37 @@ int recml_parse_examples(const uint8_t* data, const long long* offsets, const lo
     }
   }, 64);
   return status;
+}
+
+// Decodes a bytes-list feature whose strings are raw little-endian buffers (the `decode_raw` idiom of
+// pre-batched Criteo records: one string per sample holding its multi-hot int64 ids).  All strings of
+// record r are concatenated into out[r * fixed_bytes ..]; returns the number of records whose total
+// length differed from fixed_bytes (those rows are zero-filled past their data).
+int recml_parse_raw_bytes(const uint8_t* data, const long long* offsets, const long long* lengths, long long count,
+                          const char* name, long long fixed_bytes, uint8_t* out) {
+  std::atomic<int> bad{0};
+  recml::ThreadPool::global().parallel_for(count, [&](long long r0, long long r1, int) {
+    std::vector<std::string> strs;
+    for (long long r = r0; r < r1; ++r) {
+      strs.clear();
+      Slice feat;
+      if (find_feature(Slice{data + offsets[r], static_cast<size_t>(lengths[r])}, name, feat))
+        parse_feature(feat, nullptr, nullptr, &strs);
+      uint8_t* dst = out + r * fixed_bytes;
+      long long at = 0;
+      for (const std::string& b : strs) {
+        const long long n = static_cast<long long>(b.size());
+        const long long take = at + n <= fixed_bytes ? n : (fixed_bytes > at ? fixed_bytes - at : 0);
+        if (take > 0) memcpy(dst + at, b.data(), static_cast<size_t>(take));
+        at += n;
+      }
+      if (at != fixed_bytes) {
+        bad.fetch_add(1);
+        if (at < fixed_bytes) memset(dst + at, 0, static_cast<size_t>(fixed_bytes - at));
+      }
+    }
+  }, 8);
+  return bad.load();
 }
 
 }  // extern "C"

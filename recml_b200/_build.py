@@ -87,7 +87,12 @@ def _compile_all(srcs, hdrs, compiler_cmd, tag) -> tuple[list[str], bool]:
   return objs, bool(jobs)
 
 
-def build(verbose: bool = False, force: bool = False) -> dict[str, str]:
+def build_host(verbose: bool = False, force: bool = False) -> dict[str, str]:
+  """Builds only the C++ host library (machines without nvcc: CI, CPU-only test runs)."""
+  return build(verbose=verbose, force=force, only=("host",))
+
+
+def build(verbose: bool = False, force: bool = False, only: tuple[str, ...] = ("cuda", "host")) -> dict[str, str]:
   """Builds whatever is out of date and returns the library paths."""
   os.makedirs(LIB_DIR, exist_ok=True)
   cu, cu_hdr, cpp, cpp_hdr = _sources()
@@ -99,7 +104,7 @@ def build(verbose: bool = False, force: bool = False) -> dict[str, str]:
       ("host", cpp, cpp_hdr, host_lib_path(),
        lambda s, o: ["g++", *CXX_FLAGS, "-I", CSRC, "-c", s, "-o", o],
        lambda objs, lib: ["g++", "-shared", "-pthread", "-o", lib, *objs, "-lz", "-ldl"])):
-    if not srcs:
+    if not srcs or name not in only:
       continue
     want = _digest(srcs + hdrs, name)
     stamp = lib + ".sha"
