@@ -64,19 +64,13 @@ class Mamba2(nn.Module):
     z = dense_ops.linear(inputs, self.z_proj, self.z_bias)
     xbc = dense_ops.linear(inputs, self.xbc_proj, self.xbc_bias)
     dt = torch.nn.functional.softplus(dense_ops.linear(inputs, self.dt_proj, self.dt_proj_bias).float() + self.dt_bias)
-    xbc = ssd_ops.causal_depthwise_conv1d_silu(xbc, self.conv_weight, self.conv_bias)
+    xbc = ssd_ops.conv1d_silu(xbc, self.conv_weight, self.conv_bias)
     x, b, c = torch.split(xbc.float(), [self.d_inner, self.d_state, self.d_state], dim=-1)
     x = x.reshape(B, L, self.nheads, self.headdim)
     b = b.reshape(B, L, 1, self.d_state)
     c = c.reshape(B, L, 1, self.d_state)
-    pad = (-L) % self.chunk_size
-    xs, as_, bs, cs = x * dt[..., None], a * dt, b, c
-    if pad:
-      f = torch.nn.functional.pad
-      xs, as_, bs, cs = f(xs, (0, 0, 0, 0, 0, pad)), f(as_, (0, 0, 0, pad)), f(bs, (0, 0, 0, 0, 0, pad)), \
-          f(cs, (0, 0, 0, 0, 0, pad))
-    init = None if self.init_states is None else self.init_states[None].expand(B, -1, -1, -1)
-    y = ssd_ops.ssd_chunked(xs, as_, bs, cs, self.chunk_size, init)[:, :L]
+    xs, as_ = x * dt[..., None], a * dt
+    y = ssd_ops.ssd_scan(xs, as_, b, c, self.chunk_size, self.init_states)
     y = y.reshape(B, L, self.d_inner)
     y = norm_ops.layer_norm((y * torch.nn.functional.silu(z.float())).to(inputs.dtype), self.norm_w, self.norm_b,
                             1e-5, rms=True)

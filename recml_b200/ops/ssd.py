@@ -9,6 +9,8 @@ plain O(L) recurrence used as the oracle.  On CUDA the chunk kernels are `csrc/c
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 
@@ -70,3 +72,130 @@ def causal_depthwise_conv1d_silu(x, weight, bias=None):
   y = torch.nn.functional.conv1d(xp, weight.float()[:, None, :], None if bias is None else bias.float(),
                                  groups=weight.shape[0])
   return torch.nn.functional.silu(y).transpose(1, 2).to(x.dtype)
+
+
+# ---- CUDA path (`csrc/cuda/ssd.cu`) -----------------------------------------------------------------------
+class _ScanParams(ctypes.Structure):
+  _fields_ = [("x", ctypes.c_void_p), ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("c", ctypes.c_void_p),
+              ("init", ctypes.c_void_p), ("init_batch_stride", ctypes.c_longlong), ("y", ctypes.c_void_p),
+              ("ckpt", ctypes.c_void_p), ("B", ctypes.c_int), ("L", ctypes.c_int), ("H", ctypes.c_int),
+              ("P", ctypes.c_int), ("N", ctypes.c_int), ("n_ckpt", ctypes.c_int), ("dy", ctypes.c_void_p),
+              ("dx", ctypes.c_void_p), ("da", ctypes.c_void_p), ("db", ctypes.c_void_p), ("dc", ctypes.c_void_p),
+              ("dinit", ctypes.c_void_p)]
+
+
+def _cuda_supported(x, b) -> bool:
+  P, N = x.shape[-1], b.shape[-1]
+  # the backward keeps 9 state matrices of a (batch, head) pair in shared memory
+  return x.is_cuda and b.shape[-2] == 1 and P in (8, 16, 32, 64) and N in (16, 32, 64) and 9 * P * (N + 4) * 4 < 200_000
+
+
+class _ScanFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, x, a, b, c, init):
+    from recml_b200.ops import _lib
+    lib = _lib.cuda()
+    assert lib.recml_ssd_struct_size() == ctypes.sizeof(_ScanParams)
+    B, L, H, P = x.shape
+    N = b.shape[-1]
+    xf, af = x.float().contiguous(), a.float().contiguous()
+    bf, cf = b.float().reshape(B, L, N).contiguous(), c.float().reshape(B, L, N).contiguous()
+    initf = None if init is None else init.float().contiguous()
+    interval = lib.recml_ssd_ckpt_interval()
+    n_ckpt = (L + interval - 1) // interval
+    y = torch.empty_like(xf)
+    ckpt = torch.empty(B, H, n_ckpt, P, N, dtype=torch.float32, device=x.device)
+    p = _ScanParams()
+    p.x, p.a, p.b, p.c = xf.data_ptr(), af.data_ptr(), bf.data_ptr(), cf.data_ptr()
+    p.init = None if initf is None else initf.data_ptr()
+    p.init_batch_stride = 0 if initf is None or initf.dim() == 3 else H * P * N
+    p.y, p.ckpt = y.data_ptr(), ckpt.data_ptr()
+    p.B, p.L, p.H, p.P, p.N, p.n_ckpt = B, L, H, P, N, n_ckpt
+    _lib.check_rc(lib.recml_ssd_scan(ctypes.byref(p), ctypes.c_int(0), _lib.stream()), "ssd_scan_fwd")
+    ctx.save_for_backward(xf, af, bf, cf, ckpt)
+    ctx.meta = (x.dtype, a.dtype, b.dtype, c.dtype, b.shape, None if init is None else (init.dtype, init.dim()))
+    return y.to(x.dtype)
+
+  @staticmethod
+  def backward(ctx, dy):
+    from recml_b200.ops import _lib
+    lib = _lib.cuda()
+    xf, af, bf, cf, ckpt = ctx.saved_tensors
+    xdt, adt, bdt, cdt, bshape, init_meta = ctx.meta
+    B, L, H, P = xf.shape
+    N = bf.shape[-1]
+    dyf = dy.float().contiguous()
+    dx, da = torch.empty_like(xf), torch.empty_like(af)
+    db = torch.empty(B, L, H, N, dtype=torch.float32, device=xf.device)
+    dc = torch.empty_like(db)
+    dinit = torch.empty(B, H, P, N, dtype=torch.float32, device=xf.device) if init_meta is not None else None
+    p = _ScanParams()
+    p.x, p.a, p.b, p.c = xf.data_ptr(), af.data_ptr(), bf.data_ptr(), cf.data_ptr()
+    p.ckpt = ckpt.data_ptr()
+    p.B, p.L, p.H, p.P, p.N, p.n_ckpt = B, L, H, P, N, ckpt.shape[2]
+    p.dy, p.dx, p.da, p.db, p.dc = dyf.data_ptr(), dx.data_ptr(), da.data_ptr(), db.data_ptr(), dc.data_ptr()
+    p.dinit = None if dinit is None else dinit.data_ptr()
+    _lib.check_rc(lib.recml_ssd_scan(ctypes.byref(p), ctypes.c_int(1), _lib.stream()), "ssd_scan_bwd")
+    gi = None
+    if dinit is not None:
+      gi = (dinit.sum(0) if init_meta[1] == 3 else dinit).to(init_meta[0])
+    return (dx.to(xdt), da.to(adt), db.sum(2).reshape(bshape).to(bdt), dc.sum(2).reshape(bshape).to(cdt), gi)
+
+
+def ssd_scan(x, a, b, c, block_len: int = 64, initial_states=None):
+  """The SSD recurrence over the whole sequence: x `[B, L, H, P]`, a `[B, L, H]`, b / c `[B, L, G, N]`,
+  initial state `[H, P, N]` or `[B, H, P, N]`.  On CUDA (one group, P in {8..64}, N in {16, 32, 64})
+  this is the register-resident scan kernel; elsewhere the chunked formulation with zero padding to
+  a multiple of `block_len`."""
+  if _cuda_supported(x, b):
+    return _ScanFn.apply(x, a, b, c, initial_states)
+  L = x.shape[1]
+  pad = (-L) % block_len
+  if pad:
+    f = torch.nn.functional.pad
+    x, a = f(x, (0, 0, 0, 0, 0, pad)), f(a, (0, 0, 0, pad))
+    b, c = f(b, (0, 0, 0, 0, 0, pad)), f(c, (0, 0, 0, 0, 0, pad))
+  init = initial_states
+  if init is not None and init.dim() == 3:
+    init = init[None].expand(x.shape[0], -1, -1, -1)
+  return ssd_chunked(x, a, b, c, block_len, init)[:, :L]
+
+
+class _ConvFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, x, weight, bias):
+    from recml_b200.ops import _lib
+    lib = _lib.cuda()
+    B, L, C = x.shape
+    xf, wf = x.float().contiguous(), weight.float().contiguous()
+    bf = None if bias is None else bias.float().contiguous()
+    y = torch.empty_like(xf)
+    _lib.check_rc(lib.recml_conv1d_silu_fwd(_lib.ptr(xf), _lib.ptr(wf), None if bf is None else _lib.ptr(bf), _lib.ptr(y),
+                                            ctypes.c_int(B), ctypes.c_int(L), ctypes.c_int(C),
+                                            ctypes.c_int(weight.shape[1]), _lib.stream()), "conv1d_silu_fwd")
+    ctx.save_for_backward(xf, wf, bf if bf is not None else torch.empty(0, device=x.device))
+    ctx.meta = (x.dtype, weight.dtype, None if bias is None else bias.dtype)
+    return y.to(x.dtype)
+
+  @staticmethod
+  def backward(ctx, dy):
+    from recml_b200.ops import _lib
+    lib = _lib.cuda()
+    xf, wf, bf = ctx.saved_tensors
+    xdt, wdt, bdt = ctx.meta
+    B, L, C = xf.shape
+    dyf = dy.float().contiguous()
+    dx, du, dw = torch.empty_like(xf), torch.empty_like(xf), torch.empty_like(wf)
+    dbias = torch.empty(C, dtype=torch.float32, device=xf.device) if bdt is not None else None
+    _lib.check_rc(lib.recml_conv1d_silu_bwd(
+        _lib.ptr(xf), _lib.ptr(wf), _lib.ptr(bf) if bdt is not None else None, _lib.ptr(dyf), _lib.ptr(dx), _lib.ptr(du),
+        _lib.ptr(dw), None if dbias is None else _lib.ptr(dbias), ctypes.c_int(B), ctypes.c_int(L), ctypes.c_int(C),
+        ctypes.c_int(wf.shape[1]), _lib.stream()), "conv1d_silu_bwd")
+    return dx.to(xdt), dw.to(wdt), None if dbias is None else dbias.to(bdt)
+
+
+def conv1d_silu(x, weight, bias=None):
+  """Depthwise causal conv + SiLU: the CUDA kernels for 2..4 taps on a GPU, the torch formulation elsewhere."""
+  if x.is_cuda and 2 <= weight.shape[1] <= 4:
+    return _ConvFn.apply(x, weight, bias)
+  return causal_depthwise_conv1d_silu(x, weight, bias)
