@@ -91,6 +91,7 @@ def main() -> None:
   ap.add_argument("--vocab-scale", type=float, default=1.0, help="debug only: shrink table sizes")
   ap.add_argument("--backend", default="auto")
   ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying CUDA graphs")
+  ap.add_argument("--no-hstu", action="store_true", help="skip the second metric (HSTU tokens/s) reported under \"hstu\"")
   args = ap.parse_args()
   if args.impl == "reference":
     if int(os.environ.get("RANK", "0")) == 0:
@@ -190,6 +191,19 @@ def main() -> None:
   clocks = sampler.stop() if sampler is not None else None
   _lib.check_status(device)
 
+  # ---- second headline metric: HSTU generative-retrieval training tokens/s (same launch, after DLRM) ----
+  hstu = None
+  if not args.no_hstu:
+    try:
+      del train_step, state, task, dev_batches, host_batches, first, it, data
+      import gc
+      gc.collect()
+      torch.cuda.empty_cache()
+      from recml_b200.benchmarks import hstu_bench
+      hstu = hstu_bench.run(steps=max(3, min(args.steps, 10)), warmup=3)
+    except Exception as e:  # pylint: disable=broad-except
+      hstu = {"error": f"{type(e).__name__}: {e}"[:300]}
+
   if rank == 0:
     ms_step = dev_ms / args.steps
     value = args.global_batch / (ms_step * 1e-3)
@@ -208,7 +222,7 @@ def main() -> None:
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8, "last_loss": last_loss[0]},
-        "gpu_launches": launches, "impl": "ours"}))
+        "gpu_launches": launches, "impl": "ours", "hstu": hstu}))
   if world > 1:
     dist.destroy_process_group()
 
