@@ -23,7 +23,9 @@ class NativeError(RuntimeError):
 # call counts the kernels it launches; CUB's sort kernels are library code and count as zero.
 LAUNCHES = {"count": 0}
 _KERNELS_PER_CALL = {"recml_emb_bwd_update": 2, "recml_allreduce_bucket": 3, "recml_sort_pairs_u32": 0, "recml_sort_temp_bytes": 0,
-                     "recml_emb_struct_sizes": 0, "recml_optim_struct_sizes": 0}
+                     "recml_emb_struct_sizes": 0, "recml_optim_struct_sizes": 0, "recml_ar_struct_sizes": 0,
+                     "recml_ssd_struct_size": 0, "recml_ssd_ckpt_interval": 0, "recml_conv1d_silu_bwd": 2,
+                     "recml_hstu_struct_size": 0, "recml_vocab_rank_struct_size": 0}
 
 
 class _CountingLib:
