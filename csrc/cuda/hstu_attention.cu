@@ -43,6 +43,12 @@ struct Params {
   float* dpos_w;              // [2N-1] (pre-zeroed) or null
   float* dts_w;               // [num_buckets+1] (pre-zeroed) or null
   int* status;
+  // softmax mode (SASRec / BERT4Rec blocks): P = softmax over the visible keys instead of SiLU / n.
+  // The forward needs the whole key row in tensor memory (max_seq_len <= 256: two score tiles) and
+  // writes the row log-sum-exp; the backward reads it back together with delta = rowsum(dO * O).
+  int softmax;
+  float* lse;                 // [T, H]
+  const float* delta;         // [T, H] (backward)
 };
 
 // Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
@@ -234,7 +240,69 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
+    float out_scale = 1.f;
+    if (p.softmax) {
+      // Exact softmax over at most two score tiles that are both resident in tensor memory: every warp
+      // scans the whole row (all 128 columns of each tile) for the maximum and the sum, then writes
+      // only its own 64-column half of P.
+      for (int j = 0; j < n_kv && ok; ++j)
+        if (!warp_wait(bar(5 + j), 0, abortp, p.status, 45, lane)) ok = false;
+      float m = -INFINITY, l = 0.f;
+      if (ok) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass)
+#pragma unroll 1
+          for (int jc = 0; jc < n_kv * 4; ++jc) {
+            uint32_t v[32];
+            tmem_ld32(tmem_slot + (jc >> 2) * 128 + lane_off + (jc & 3) * 32, v);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int kj = jc * 32 + e;
+              const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+              const float x = __uint_as_float(v[e]) * p.scale;
+              if (visible) {
+                if (pass == 0) m = fmaxf(m, x); else l += __expf(x - m);
+              }
+            }
+          }
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_slot + j * 128 + lane_off + half * 64 + c * 32, v);
+          uint32_t packed[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float pr[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int kj = j * BKV + half * 64 + c * 32 + e + u;
+              const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+              pr[u] = visible ? __expf(__uint_as_float(v[e + u]) * p.scale - m) : 0.f;
+            }
+            packed[e >> 1] = pack_bf16(pr[0], pr[1]);
+          }
+          uint8_t* row_ptr = base_ptr + S::kP + half * 16384 + r * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = (c * 4 + g) ^ (r & 7);
+            *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
+                make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar(7 + j));
+        fence_async_smem();
+        mbar_arrive(bar(9));
+      }
+      out_scale = l > 0.f ? 1.f / l : 0.f;
+      if (ok && half == 0 && row_ok && p.lse != nullptr)
+        p.lse[static_cast<size_t>(tok0 + r) * p.H + h] = l > 0.f ? m + logf(l) : 0.f;
+    }
+    for (int j = 0; j < n_kv && ok && !p.softmax; ++j) {
       const int kv0 = j * BKV + half * 64;
       const int sb = j & 1;
       stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter);
@@ -286,10 +354,10 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int g = 0; g < 4; ++g)
             *reinterpret_cast<uint4*>(dst + g * 8) =
-                make_uint4(pack_bf16(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                           pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                           pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                           pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+                make_uint4(pack_bf16(__uint_as_float(v[8 * g]) * out_scale, __uint_as_float(v[8 * g + 1]) * out_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 2]) * out_scale, __uint_as_float(v[8 * g + 3]) * out_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 4]) * out_scale, __uint_as_float(v[8 * g + 5]) * out_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 6]) * out_scale, __uint_as_float(v[8 * g + 7]) * out_scale));
         }
       }
     }
@@ -447,6 +515,11 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const bool row_ok = qi < L;
       int tq = 0;
       if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+      float lse_r = 0.f, delta_r = 0.f;
+      if (p.softmax && row_ok) {
+        lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
+        delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
+      }
       stage_bias(wb, p, lane, seq_start, L, kv0 + half * 64, q0, quarter);
       if (!warp_wait(bar(5), it & 1, abortp, p.status, 55, lane)) { ok = false; break; }
       tc_fence_after();
@@ -475,9 +548,17 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               bucket = time_bucket(tq - wb.ts_k[col], p.num_buckets);
               x += wb.tsw[bucket];
             }
-            const float sig = sigmoid_fast(x);
-            const float ds = visible ? __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n : 0.f;
-            pr[u] = visible ? x * sig * p.inv_n : 0.f;
+            float ds;
+            if (p.softmax) {
+              // P = exp(x - lse);  dS = P * (dP - delta)
+              const float pv = visible ? __expf(x - lse_r) : 0.f;
+              ds = pv * (__uint_as_float(dpv[e + u]) - delta_r);
+              pr[u] = pv;
+            } else {
+              const float sig = sigmoid_fast(x);
+              ds = visible ? __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n : 0.f;
+              pr[u] = visible ? x * sig * p.inv_n : 0.f;
+            }
             dr[u] = ds;
             // diagonal bin (kj - qi) - (kv0 - q0) + 127: lanes of a warp hit distinct bins
             if (p.dpos_w != nullptr && visible) atomicAdd(hist + (it & 1) * 256 + (half * 64 + col - r + 127), ds);
@@ -616,6 +697,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
 extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, const Params* p, int n_tiles,
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
+  if (p->softmax && p->max_seq_len > 2 * BKV) return -11;   // the softmax forward keeps the whole key row in tensor memory
   if (p->Dh == 64) return launch_fwd<64>(q, k, v, *p, n_tiles, stream);
   if (p->Dh == 128) return launch_fwd<128>(q, k, v, *p, n_tiles, stream);
   return -10;

@@ -33,12 +33,18 @@ class MultiHeadAttention(nn.Module):
     init(self.out)
     self.out_bias = nn.Parameter(torch.zeros(model_dim))
 
-  def forward(self, x: torch.Tensor, mask: torch.Tensor | None) -> torch.Tensor:
+  def forward(self, x: torch.Tensor, mask: torch.Tensor | None, *, padding_mask: torch.Tensor | None = None,
+              causal: bool = False, structured: bool = False) -> torch.Tensor:
+    """`structured` says that `mask` is exactly padding ∧ causality (no explicit attention mask), which
+    lets the op use the packed-sequence kernels instead of a dense `[B, L, L]` mask."""
     B, L, D = x.shape
     qkv = dense_ops.linear(x, self.qkv, self.qkv_bias).reshape(B, L, 3, self.num_heads, self.head_dim)
     q, k, v = qkv.unbind(dim=2)
-    a = sm_ops.softmax_attention(q, k, v, mask, self.dropout_p, self.training).reshape(B, L, D)
-    return dense_ops.linear(a, self.out, self.out_bias)
+    if structured:
+      a = sm_ops.structured_attention(q, k, v, padding_mask, causal, self.dropout_p, self.training)
+    else:
+      a = sm_ops.softmax_attention(q, k, v, mask, self.dropout_p, self.training)
+    return dense_ops.linear(a.reshape(B, L, D), self.out, self.out_bias)
 
 
 class TransformerBlock(nn.Module):
@@ -63,12 +69,13 @@ class TransformerBlock(nn.Module):
     mask = sm_ops.merge_masks(B, L, x.device, padding_mask=padding_mask, attention_mask=attention_mask,
                               causal=self.causal)
     ln = norm_ops.layer_norm
+    kw = dict(padding_mask=padding_mask, causal=self.causal, structured=attention_mask is None)
     if self.normalize_first:
-      x = x + self.attn_dropout(self.attn(ln(x, self.attn_norm_w, self.attn_norm_b, self.eps), mask)).to(x.dtype)
+      x = x + self.attn_dropout(self.attn(ln(x, self.attn_norm_w, self.attn_norm_b, self.eps), mask, **kw)).to(x.dtype)
       h = self.activation(dense_ops.linear(ln(x, self.ffn_norm_w, self.ffn_norm_b, self.eps), self.ffn_in,
                                            self.ffn_in_bias))
       return x + self.ffn_dropout(dense_ops.linear(h, self.ffn_out, self.ffn_out_bias)).to(x.dtype)
-    x = ln(x + self.attn_dropout(self.attn(x, mask)).to(x.dtype), self.attn_norm_w, self.attn_norm_b, self.eps)
+    x = ln(x + self.attn_dropout(self.attn(x, mask, **kw)).to(x.dtype), self.attn_norm_w, self.attn_norm_b, self.eps)
     h = self.activation(dense_ops.linear(x, self.ffn_in, self.ffn_in_bias))
     return ln(x + self.ffn_dropout(dense_ops.linear(h, self.ffn_out, self.ffn_out_bias)).to(x.dtype),
               self.ffn_norm_w, self.ffn_norm_b, self.eps)

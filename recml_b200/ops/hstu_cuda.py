@@ -15,7 +15,8 @@ class _Params(ctypes.Structure):
               ("num_buckets", c_int), ("causal", c_int), ("scale", c_float), ("inv_n", c_float),
               ("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("timestamps", c_vp),
               ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
-              ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp)]
+              ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("softmax", c_int), ("lse", c_vp),
+              ("delta", c_vp)]
 
 
 _ok: bool | None = None
@@ -118,3 +119,35 @@ def _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_s
   dpos = rest.pop(0) if pw is not None else None
   dts = rest.pop(0) if tw is not None else None
   return dq, dk, dv, dpos, dts
+
+
+# ---- softmax mode: the same kernels with P = softmax(scale * QK^T) over the visible keys ----------------------
+SOFTMAX_MAX_LEN = 256
+
+
+def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
+  """Jagged softmax attention; returns (out `[T, H, Dh]` bf16, row log-sum-exp `[T, H]` fp32)."""
+  assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.bfloat16
+  assert max_seq_len <= SOFTMAX_MAX_LEN
+  tiles = _tiles(seq_offsets, q.shape[0])
+  out = torch.empty_like(q)
+  lse = torch.empty(q.shape[0], q.shape[1], dtype=torch.float32, device=q.device)
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles)
+  p.out, p.softmax, p.lse = out.data_ptr(), 1, lse.data_ptr()
+  _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
+                                                c_int(tiles[2]), _lib.stream()), "softmax_attn_fwd")
+  return out, lse
+
+
+def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, scale):
+  tiles = _tiles(seq_offsets, q.shape[0])
+  do = do.contiguous()
+  delta = (do.float() * out.float()).sum(-1).contiguous()          # [T, H]
+  dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+  dk, dv = torch.empty_like(k), torch.empty_like(v)
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles)
+  p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+  p.softmax, p.lse, p.delta = 1, lse.data_ptr(), delta.data_ptr()
+  _lib.check_rc(_lib.cuda().recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do), ctypes.byref(p),
+                                                c_int(tiles[2]), _lib.stream()), "softmax_attn_bwd")
+  return dq.to(q.dtype), dk, dv

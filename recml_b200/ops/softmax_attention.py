@@ -34,3 +34,63 @@ def softmax_attention(q, k, v, mask: torch.Tensor | None, dropout_p: float = 0.0
   if training and dropout_p > 0:
     p = torch.nn.functional.dropout(p, dropout_p)
   return torch.einsum("bhts,bshd->bthd", p, v.float()).to(q.dtype)
+
+
+# ---- structured masks (padding ∧ optional causality) on the tcgen05 attention kernels ----------------------
+class _JaggedSoftmaxFn(torch.autograd.Function):
+  """Softmax attention over packed sequences: q, k, v `[T, H, Dh]` bf16, `seq_offsets [B+1]`."""
+
+  @staticmethod
+  def forward(ctx, q, k, v, seq_offsets, max_seq_len, causal, scale):
+    from recml_b200.ops import hstu_cuda
+    out, lse = hstu_cuda.softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale)
+    ctx.save_for_backward(q, k, v, out, lse, seq_offsets)
+    ctx.meta = (max_seq_len, causal, scale)
+    return out
+
+  @staticmethod
+  def backward(ctx, do):
+    from recml_b200.ops import hstu_cuda
+    q, k, v, out, lse, seq_offsets = ctx.saved_tensors
+    dq, dk, dv = hstu_cuda.softmax_backward(do, out, lse, q, k, v, seq_offsets, *ctx.meta)
+    return dq, dk, dv, None, None, None, None
+
+
+def jagged_softmax_attention(q, k, v, seq_offsets, max_seq_len: int, causal: bool, scale: float | None = None):
+  scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+  return _JaggedSoftmaxFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), seq_offsets, max_seq_len, causal, scale)
+
+
+def _kernel_ok(q, L: int) -> bool:
+  if not q.is_cuda or q.shape[-1] not in (64, 128) or L > 256:
+    return False
+  from recml_b200.ops import hstu_cuda
+  return hstu_cuda.available()
+
+
+def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: bool, dropout_p: float = 0.0,
+                         training: bool = False):
+  """Attention whose mask is `key is not padding` ∧ (`key <= query` when causal): q, k, v `[B, L, H, Dh]`,
+  `padding_mask [B, L]` (True = real token).  On a GPU (head dim 64 / 128, L ≤ 256, no attention
+  dropout) the valid tokens are packed and run through the jagged tcgen05 kernels in softmax mode, so
+  no `[B, H, L, L]` score tensor is ever written; rows of padded queries come back as zeros (the
+  dense formulation gives them the average of the visible values; nothing downstream reads them).
+  Everywhere else this is `softmax_attention` with the merged mask."""
+  B, L, H, Dh = q.shape
+  if not _kernel_ok(q, L) or (training and dropout_p > 0):
+    mask = merge_masks(B, L, q.device, padding_mask=padding_mask, causal=causal)
+    return softmax_attention(q, k, v, mask, dropout_p, training)
+  dt = q.dtype
+  flat = lambda t: t.reshape(B * L, H, Dh).to(torch.bfloat16)
+  if padding_mask is None:
+    offs = torch.arange(B + 1, device=q.device, dtype=torch.int32) * L
+    out = jagged_softmax_attention(flat(q), flat(k), flat(v), offs, L, causal)
+    return out.reshape(B, L, H, Dh).to(dt)
+  valid = padding_mask.bool()
+  idx = valid.reshape(-1).nonzero().squeeze(1)          # packs the real tokens (one host sync for the count)
+  offs = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
+  offs[1:] = valid.sum(1).cumsum(0)
+  pick = lambda t: flat(t).index_select(0, idx)
+  packed = jagged_softmax_attention(pick(q), pick(k), pick(v), offs, L, causal)
+  out = torch.zeros(B * L, H, Dh, dtype=packed.dtype, device=q.device).index_copy(0, idx, packed)
+  return out.reshape(B, L, H, Dh).to(dt)
