@@ -6,7 +6,7 @@ Each case builds inputs larger than L2 (126 MB) but only a few GB in total, warm
 kernel with CUDA events and prints achieved bandwidth / FLOP rate against the measured peaks of this
 machine (MEASURED_PEAKS.json when present).  The same command line is what `ncu` captures.
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, gemm_cross, emb_fwd, emb_bwd, hstu_fwd, hstu_bwd, vocab_rank,
-layernorm, allreduce (needs torchrun with 2+ ranks).
+layernorm, ssd_fwd, ssd_bwd, mha_fwd, mha_bwd, sampled_softmax.
 """
 from __future__ import annotations
 
@@ -139,6 +139,50 @@ def main():
     w, b = torch.ones(256, device="cuda", requires_grad=True), torch.zeros(256, device="cuda", requires_grad=True)
     ms = timed(lambda: norm.layer_norm(x.detach(), w, b, 1e-6), args.iters, flush)
     bytes_ = x.numel() * 4
+    out.update(ms=ms, gbs=bytes_ / ms / 1e6, frac=bytes_ / ms / 1e6 / hbm, of=tag)
+  elif c in ("ssd_fwd", "ssd_bwd"):
+    from recml_b200.ops import ssd
+    B, L, H, P, N = 512, 200, 8, 64, 64            # Mamba4Rec block at d_model 256: d_inner 512 = 8 heads x 64
+    x = (torch.randn(B, L, H, P, device="cuda") * 0.3).requires_grad_()
+    a = (-torch.rand(B, L, H, device="cuda") * 0.5).requires_grad_()
+    b = (torch.randn(B, L, 1, N, device="cuda") * 0.3).requires_grad_()
+    cc = (torch.randn(B, L, 1, N, device="cuda") * 0.3).requires_grad_()
+    if c == "ssd_fwd":
+      fn = lambda: ssd.ssd_scan(x.detach(), a.detach(), b.detach(), cc.detach())
+      bytes_ = (2 * x.numel() + a.numel() + 2 * b.numel() * 1) * 4 + B * H * ((L + 31) // 32) * P * N * 4
+    else:
+      go = torch.randn(B, L, H, P, device="cuda")
+      def fn():
+        ssd.ssd_scan(x, a, b, cc).backward(go)
+      bytes_ = (4 * x.numel() + 2 * a.numel() + 2 * b.numel() + 2 * B * L * H * N * 2) * 4 + 2 * B * H * ((L + 31) // 32) * P * N * 4
+    ms = timed(fn, args.iters, flush)
+    steps = float(B) * L * H
+    out.update(ms=ms, gbs=bytes_ / ms / 1e6, frac=bytes_ / ms / 1e6 / hbm, of=tag, state_updates_per_s=steps * P * N / ms * 1e3)
+  elif c in ("mha_fwd", "mha_bwd"):
+    from recml_b200.ops import softmax_attention as sm
+    B, L, H, Dh = 512, 200, 4, 64                   # SASRec block: batch 512 per GPU, 200 positions, 4 x 64
+    q, k, v = (rnd(B * L, H, Dh).requires_grad_() for _ in range(3))
+    offs = torch.arange(B + 1, device="cuda", dtype=torch.int32) * L
+    pairs = float(B) * L * (L + 1) / 2
+    if c == "mha_fwd":
+      fn = lambda: sm.jagged_softmax_attention(q.detach(), k.detach(), v.detach(), offs, L, True)
+      flops = 4.0 * pairs * Dh * H
+    else:
+      go = rnd(B * L, H, Dh)
+      def fn():
+        sm.jagged_softmax_attention(q, k, v, offs, L, True).backward(go)
+      flops = 14.0 * pairs * Dh * H
+    ms = timed(fn, args.iters)
+    out.update(ms=ms, tflops_causal=flops / ms / 1e9, tokens=B * L)
+  elif c == "sampled_softmax":
+    from recml_b200.ops import sampled_softmax as S
+    T, C = 65536, 1024
+    pos = torch.randn(T, device="cuda")
+    neg = rnd(T, C)
+    cand, tgt = torch.randint(0, 10_000_000, (C,), device="cuda"), torch.randint(0, 10_000_000, (T,), device="cuda")
+    w = torch.ones(T, device="cuda")
+    ms = timed(lambda: S.sampled_softmax_loss(pos, neg, cand, tgt, w, 0.05), args.iters, flush)
+    bytes_ = T * C * 2 * 2                            # logits read (second pass hits L1/L2) + gradient written
     out.update(ms=ms, gbs=bytes_ / ms / 1e6, frac=bytes_ / ms / 1e6 / hbm, of=tag)
   else:
     raise SystemExit(f"unknown case {c}")

@@ -14,6 +14,7 @@ from torch import nn
 from recml_b200 import embedding as emb
 from recml_b200.layers import hstu as hstu_layers
 from recml_b200.ops import dense as dense_ops
+from recml_b200.ops import sampled_softmax
 
 
 class HSTURetrieval(nn.Module):
@@ -63,12 +64,7 @@ class HSTURetrieval(nn.Module):
     cand = torch.cat([e_ng, e_tg[inb_idx]], dim=0)
     cand = torch.nn.functional.normalize(cand.float(), dim=-1).to(h.dtype)
     cand_ids = torch.cat([negative_ids, target_ids[inb_idx]])
-    pos = (h.float() * torch.nn.functional.normalize(e_tg.float(), dim=-1)).sum(-1, keepdim=True)
-    neg = dense_ops.linear(h, cand).float()                                               # [T, C]
-    neg = neg.masked_fill(cand_ids[None, :] == target_ids[:, None], -1e4)                 # accidental hits
-    logits = torch.cat([pos, neg], dim=1) / self.temperature
-    nll = torch.logsumexp(logits, dim=1) - logits[:, 0]
-    w = target_weights.float()
-    loss = (nll * w).sum() / w.sum().clamp_min(1.0)
-    hit = ((logits.argmax(dim=1) == 0).float() * w).sum() / w.sum().clamp_min(1.0)
+    pos = (h.float() * torch.nn.functional.normalize(e_tg.float(), dim=-1)).sum(-1)
+    neg = dense_ops.linear(h, cand)                                                       # [T, C] bf16 on CUDA
+    loss, hit = sampled_softmax.sampled_softmax_loss(pos, neg, cand_ids, target_ids, target_weights, self.temperature)
     return loss, hit.detach()

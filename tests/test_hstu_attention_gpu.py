@@ -86,3 +86,26 @@ def test_hstu_retrieval_trains_on_gpu():
   lc = run("cpu", 1)
   assert abs(lg[0] - lc[0]) < 0.15, (lg[0], lc[0])
   assert lg[-1] < lg[0] * 0.7, lg
+
+
+def test_sampled_softmax_kernel_matches_torch():
+  import torch
+  from recml_b200.ops import sampled_softmax as S
+  torch.manual_seed(0)
+  T, C = 777, 1000
+  pos = torch.randn(T, device="cuda") * 0.5
+  neg = (torch.randn(T, C, device="cuda") * 0.5).to(torch.bfloat16)
+  cand = torch.randint(0, 3000, (C,), device="cuda")
+  tgt = torch.randint(0, 3000, (T,), device="cuda")
+  tgt[:50] = cand[:50]                      # accidental hits
+  w = (torch.rand(T, device="cuda") > 0.2).float()
+  a = [pos.clone().requires_grad_(), neg.clone().requires_grad_()]
+  r = [pos.clone().requires_grad_(), neg.float().clone().requires_grad_()]
+  loss, hit = S.sampled_softmax_loss(a[0], a[1], cand, tgt, w, 0.05)
+  loss_r, hit_r = S.reference(r[0], r[1], cand, tgt, w, 0.05)
+  torch.testing.assert_close(loss, loss_r, rtol=1e-4, atol=1e-4)
+  torch.testing.assert_close(hit, hit_r, rtol=1e-5, atol=1e-5)
+  (loss * 3.0).backward()
+  (loss_r * 3.0).backward()
+  torch.testing.assert_close(a[0].grad, r[0].grad, rtol=1e-3, atol=1e-5)
+  torch.testing.assert_close(a[1].grad.float(), r[1].grad, rtol=2e-2, atol=1e-5)
