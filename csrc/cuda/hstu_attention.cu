@@ -22,8 +22,10 @@ using namespace recml::tc;
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kThreads = 320;        // TMA warp, MMA warp, 8 element-wise warps (two per tensor-memory lane quarter)
+constexpr int kThreads = 320;        // backward: TMA warp, MMA warp, 8 element-wise warps (two per tensor-memory lane quarter)
 constexpr int kCompute = 256;
+constexpr int kFwdThreads = 576;     // forward: TMA warp, MMA warp, 16 element-wise warps (four per lane quarter, 32 columns each)
+constexpr int kFwdCompute = 512;
 constexpr float kBucketSize = 0.301f;
 
 struct Params {
@@ -127,12 +129,12 @@ struct Smem {
   static constexpr int kP = kV + 2 * kTile;            // [128, 128] bf16 = 32 KB
   static constexpr int kBars = kP + BQ * BKV * 2;
   static constexpr int kBias = kBars + 128;            // 4 x WarpBias
-  static constexpr int kTotal = kBias + 8 * static_cast<int>(sizeof(WarpBias)) + 1024;
+  static constexpr int kTotal = kBias + 16 * static_cast<int>(sizeof(WarpBias)) + 1024;
   static constexpr int kTmemCols = 512;                // S: 2 x 128 columns, O: DH columns
 };
 
 template <int DH>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
   using S = Smem<DH>;
@@ -158,9 +160,9 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int i = 0; i <= 6; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(7), kCompute);
-    mbar_init(bar(8), kCompute);
-    mbar_init(bar(9), kCompute);
+    mbar_init(bar(7), kFwdCompute);
+    mbar_init(bar(8), kFwdCompute);
+    mbar_init(bar(9), kFwdCompute);
     mbar_init(bar(10), 1);
     mbar_init(bar(11), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -227,9 +229,9 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_commit(bar(11));
     }
   } else {
-    const int cw = warp - 2;              // 0..7
+    const int cw = warp - 2;              // 0..15
     const int quarter = warp & 3;         // tensor-memory lane quarter this warp may read
-    const int half = cw >> 2;             // which 64 key columns of the tile this warp handles
+    const int cb = cw >> 2;               // which 32 key columns of the tile this warp handles
     const int r = quarter * 32 + lane;
     const int qi = q0 + r;
     const bool row_ok = qi < L;
@@ -244,7 +246,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (p.softmax) {
       // Exact softmax over at most two score tiles that are both resident in tensor memory: every warp
       // scans the whole row (all 128 columns of each tile) for the maximum and the sum, then writes
-      // only its own 64-column half of P.
+      // only its own 32 columns of P.
       for (int j = 0; j < n_kv && ok; ++j)
         if (!warp_wait(bar(5 + j), 0, abortp, p.status, 45, lane)) ok = false;
       float m = -INFINITY, l = 0.f;
@@ -269,26 +271,25 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        {
           uint32_t v[32];
-          tmem_ld32(tmem_slot + j * 128 + lane_off + half * 64 + c * 32, v);
+          tmem_ld32(tmem_slot + j * 128 + lane_off + cb * 32, v);
           uint32_t packed[16];
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             float pr[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              const int kj = j * BKV + half * 64 + c * 32 + e + u;
+              const int kj = j * BKV + cb * 32 + e + u;
               const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
               pr[u] = visible ? __expf(__uint_as_float(v[e + u]) * p.scale - m) : 0.f;
             }
             packed[e >> 1] = pack_bf16(pr[0], pr[1]);
           }
-          uint8_t* row_ptr = base_ptr + S::kP + half * 16384 + r * 128;
+          uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int chunk = (c * 4 + g) ^ (r & 7);
+            const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
             *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
                 make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
           }
@@ -299,27 +300,26 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(bar(9));
       }
       out_scale = l > 0.f ? 1.f / l : 0.f;
-      if (ok && half == 0 && row_ok && p.lse != nullptr)
+      if (ok && cb == 0 && row_ok && p.lse != nullptr)
         p.lse[static_cast<size_t>(tok0 + r) * p.H + h] = l > 0.f ? m + logf(l) : 0.f;
     }
     for (int j = 0; j < n_kv && ok && !p.softmax; ++j) {
-      const int kv0 = j * BKV + half * 64;
+      const int kv0 = j * BKV + cb * 32;
       const int sb = j & 1;
       stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter);
       if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
       tc_fence_after();
       if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t v[32];
-        tmem_ld32(tmem_slot + sb * 128 + lane_off + half * 64 + c * 32, v);
+        tmem_ld32(tmem_slot + sb * 128 + lane_off + cb * 32, v);
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pr[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;       // within the warp's 64 columns
+            const int col = e + u;                // within the warp's 32 columns
             const int kj = kv0 + col;
             float x = __uint_as_float(v[e + u]) * p.scale;
             const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
@@ -329,11 +329,11 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           packed[e >> 1] = pack_bf16(pr[0], pr[1]);
         }
-        // 32 columns = 64 bytes = four 16-byte chunks of row r in the 64-column sub-tile `half`
-        uint8_t* row_ptr = base_ptr + S::kP + half * 16384 + r * 128;
+        // 32 columns = 64 bytes = four 16-byte chunks of row r in 64-column sub-tile cb / 2
+        uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = (c * 4 + g) ^ (r & 7);
+          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
           *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
@@ -346,7 +346,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (ok && warp_wait(bar(11), 0, abortp, p.status, 47, lane)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = half; c < DH / 32; c += 2) {
+      for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32];
         tmem_ld32(tmem_o + lane_off + c * 32, v);
         if (row_ok) {
@@ -689,7 +689,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
     configured = true;
   }
   dim3 grid(n_tiles, p.H);
-  kern<<<grid, kThreads, Smem<DH>::kTotal, stream>>>(mq, mk, mv, p);
+  kern<<<grid, kFwdThreads, Smem<DH>::kTotal, stream>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
