@@ -22,10 +22,8 @@ using namespace recml::tc;
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kThreads = 320;        // backward: TMA warp, MMA warp, 8 element-wise warps (two per tensor-memory lane quarter)
-constexpr int kCompute = 256;
-constexpr int kFwdThreads = 576;     // forward: TMA warp, MMA warp, 16 element-wise warps (four per lane quarter, 32 columns each)
-constexpr int kFwdCompute = 512;
+constexpr int kThreads = 576;        // TMA warp, MMA warp, 16 element-wise warps (four per tensor-memory lane quarter,
+constexpr int kCompute = 512;        // each covering 32 rows x 32 columns of a score tile)
 constexpr float kBucketSize = 0.301f;
 
 struct Params {
@@ -85,7 +83,7 @@ __device__ __forceinline__ int time_bucket(int dt, int num_buckets) {
 // Per-warp scratch in shared memory for the bias terms of one (query tile, key tile) pair: the 128 key
 // timestamps, the 160-entry window of the relative-position table the warp's 32 rows touch, and a copy
 // of the time-bucket table.  Only __syncwarp is needed to publish it.
-struct WarpBias {      // a warp covers 32 rows x 64 columns of the score tile
+struct WarpBias {      // a warp covers 32 rows x 32 columns of the score tile (the staging covers 64 columns)
   int ts_k[64];
   float pos[96];
   float tsw[260];
@@ -101,7 +99,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
   return ok != 0;
 }
 
-// `kv0` here is the first key of the warp's 64-column half.
+// `kv0` here is the first key of the warp's columns.
 __device__ __forceinline__ void stage_bias(WarpBias& wb, const Params& p, int lane, int seq_start, int L, int kv0,
                                            int q0, int quarter) {
   __syncwarp();
@@ -134,7 +132,7 @@ struct Smem {
 };
 
 template <int DH>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
   using S = Smem<DH>;
@@ -160,9 +158,9 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int i = 0; i <= 6; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(7), kFwdCompute);
-    mbar_init(bar(8), kFwdCompute);
-    mbar_init(bar(9), kFwdCompute);
+    mbar_init(bar(7), kCompute);
+    mbar_init(bar(8), kCompute);
+    mbar_init(bar(9), kCompute);
     mbar_init(bar(10), 1);
     mbar_init(bar(11), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -388,7 +386,7 @@ struct SmemB {
   static constexpr int kBars = kDS + BQ * BKV * 2;
   static constexpr int kHist = kBars + 128;             // 2 x 256 diagonal bins (by step parity) + 256 time bins, fp32
   static constexpr int kBias = kHist + 768 * 4;
-  static constexpr int kTotal = kBias + 8 * static_cast<int>(sizeof(WarpBias)) + 1024;
+  static constexpr int kTotal = kBias + 16 * static_cast<int>(sizeof(WarpBias)) + 1024;
   // tensor memory columns: [0,128) S then dQ, [128,256) dP, [256,256+DH) dV, [256+DH,256+2DH) dK
   static constexpr int kTmemCols = 512;
 };
@@ -502,7 +500,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else {
     const int cw = warp - 2;
     const int quarter = warp & 3;
-    const int half = cw >> 2;             // which 64 key columns of the tile this warp handles
+    const int cb = cw >> 2;               // which 32 key columns of the tile this warp handles
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
@@ -520,26 +518,25 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
         delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
       }
-      stage_bias(wb, p, lane, seq_start, L, kv0 + half * 64, q0, quarter);
+      stage_bias(wb, p, lane, seq_start, L, kv0 + cb * 32, q0, quarter);
       if (!warp_wait(bar(5), it & 1, abortp, p.status, 55, lane)) { ok = false; break; }
       tc_fence_after();
       // time-bucket gradient: along a row the bucket changes rarely (log-spaced buckets, increasing
       // timestamps), so equal-bucket runs are summed in a register and flushed with one atomic
       int run_bucket = -1;
       float run_sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t sv[32], dpv[32];
-        tmem_ld32(tmem_s + lane_off + half * 64 + c * 32, sv);
-        tmem_ld32(tmem_dp + lane_off + half * 64 + c * 32, dpv);
+        tmem_ld32(tmem_s + lane_off + cb * 32, sv);
+        tmem_ld32(tmem_dp + lane_off + cb * 32, dpv);
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pr[2], dr[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;              // within the warp's 64 columns
-            const int kj = kv0 + half * 64 + col;
+            const int col = e + u;                       // within the warp's 32 columns
+            const int kj = kv0 + cb * 32 + col;
             const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
             float x = __uint_as_float(sv[e + u]) * p.scale;
             int bucket = 0;
@@ -561,7 +558,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             dr[u] = ds;
             // diagonal bin (kj - qi) - (kv0 - q0) + 127: lanes of a warp hit distinct bins
-            if (p.dpos_w != nullptr && visible) atomicAdd(hist + (it & 1) * 256 + (half * 64 + col - r + 127), ds);
+            if (p.dpos_w != nullptr && visible) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + col - r + 127), ds);
             if (p.dts_w != nullptr && visible) {
               if (bucket != run_bucket) {
                 if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
@@ -574,11 +571,11 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pp[e >> 1] = pack_bf16(pr[0], pr[1]);
           dd[e >> 1] = pack_bf16(dr[0], dr[1]);
         }
-        uint8_t* prow = base_ptr + S::kP + half * 16384 + r * 128;
-        uint8_t* drow = base_ptr + S::kDS + half * 16384 + r * 128;
+        uint8_t* prow = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
+        uint8_t* drow = base_ptr + S::kDS + (cb >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = (c * 4 + g) ^ (r & 7);
+          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
         }
@@ -591,7 +588,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!warp_wait(bar(7), it & 1, abortp, p.status, 56, lane)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = half; c < DH / 32; c += 2) {
+      for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32];
         tmem_ld32(tmem_s + lane_off + c * 32, v);
         if (row_ok) {
@@ -621,7 +618,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int kj = kv0 + r;
       const bool kv_ok = kj < L;
 #pragma unroll 1
-      for (int c = half; c < DH / 32; c += 2) {
+      for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32], w[32];
         tmem_ld32(tmem_dv + lane_off + c * 32, v);
         tmem_ld32(tmem_dk + lane_off + c * 32, w);
@@ -689,7 +686,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
     configured = true;
   }
   dim3 grid(n_tiles, p.H);
-  kern<<<grid, kFwdThreads, Smem<DH>::kTotal, stream>>>(mq, mk, mv, p);
+  kern<<<grid, kThreads, Smem<DH>::kTotal, stream>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
