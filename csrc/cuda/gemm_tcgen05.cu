@@ -62,7 +62,8 @@ struct Cfg {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStages = (BN == 256) ? 3 : 4;
-  // per epilogue warp: four 4 KB buffers (out, out2, aux0, aux1), each a [32 rows, 64 cols] bf16 box
+  // per epilogue warp: two staging sets of two 4 KB [32 rows, 64 cols] bf16 boxes (auxiliary operands come in,
+  // results are written over them and go out)
   static constexpr int kEpi = 4 * 4 * 4096;
   static constexpr int kSmem = kStages * (kStageA + kStageB) + kEpi + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
@@ -107,7 +108,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(tfull_bar(s), 1);
       mbar_init(tempty_bar(s), 128);
     }
-    for (int w = 0; w < 4; ++w) mbar_init(bars + 8u * (2 * C::kStages + 4 + w), 1);
+    for (int w = 0; w < 8; ++w) mbar_init(bars + 8u * (2 * C::kStages + 4 + w), 1);   // 4 epilogue warps x 2 staging sets
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
@@ -188,18 +189,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    // bf16 outputs: every warp owns 32 rows of the tile.  Per 64-column slab it (1) TMA-loads the 32 x 64
-    // boxes of the auxiliary operands into its private shared-memory buffers, (2) reads the accumulator
-    // from tensor memory, applies the epilogue and writes bf16 into a swizzled staging box, (3) hands the
-    // box to a TMA store.  All global traffic of the epilogue is therefore full 128-byte lines, and only
-    // __syncwarp is needed.  fp32 outputs (weight gradients) are written directly: a thread's 32 floats
-    // already are one full line.
+    // bf16 outputs: every warp owns 32 rows of the tile and walks it in 64-column slabs.  Per slab it
+    // (1) waits for the 32 x 64 boxes of the auxiliary operands that a TMA load brought into one of its
+    // two private staging sets, (2) reads the accumulator from tensor memory, applies the epilogue and
+    // writes the bf16 results OVER the auxiliary boxes (same thread, same 16-byte chunk), (3) hands the
+    // boxes to TMA stores.  The loads of the NEXT slab (of this tile or of the warp's next tile) are
+    // issued into the other set before step (1), so their latency hides behind this slab's work.  All
+    // global traffic of the epilogue is full 128-byte lines and only __syncwarp is needed.  fp32
+    // outputs (weight gradients) are written directly: a thread's 32 floats already are one full line.
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     const uint32_t my_smem = epi_smem + quarter * 16384;
     uint8_t* my_ptr = epi_ptr + quarter * 16384;
-    const uint32_t aux_bar = bars + 8u * (2 * C::kStages + 4 + quarter);
+    auto aux_bar = [&](uint32_t set) { return bars + 8u * (2 * C::kStages + 4 + quarter * 2 + set); };
     const int n_aux = p.epi == kEpiLinear ? 0 : ((p.epi == kEpiCross || (p.epi == kEpiMulAdd && p.aux1 != nullptr)) ? 2 : 1);
-    uint32_t aux_uses = 0;
+    const bool cross = p.epi == kEpiCross;
+    auto slabs_of = [&](int tl) {
+      const int rem = p.N - (tl % n_tiles) * BN;
+      return rem >= BN ? BN / 64 : (rem + 63) / 64;
+    };
+    auto issue_aux = [&](int tl, int sl, uint32_t set) {   // one lane calls this
+      const int r0 = (tl / n_tiles) * BM + quarter * 32, c0 = (tl % n_tiles) * BN + sl * 64;
+      mbar_expect_tx(aux_bar(set), 4096u * n_aux);
+      tma_load_2d(my_smem + set * 8192, &map_x0, c0, r0, aux_bar(set));
+      if (n_aux == 2) tma_load_2d(my_smem + set * 8192 + 4096, &map_x1, c0, r0, aux_bar(set));
+    };
+    uint32_t item = 0;          // slabs processed so far: staging set = item & 1, barrier parity = (item >> 1) & 1
+    if (!p.out_f32 && n_aux > 0 && lane == 0 && static_cast<int>(blockIdx.x) < num_tiles) issue_aux(blockIdx.x / split_k, 0, 0);
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int tl = tile / split_k;
@@ -217,17 +232,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if (!p.out_f32) {
         const int row0 = m0 + quarter * 32;
         bool ok = true;
+        const int n_slabs = slabs_of(tl);
 #pragma unroll 1
-        for (int sl = 0; sl < BN / 64 && ok; ++sl) {
+        for (int sl = 0; sl < n_slabs && ok; ++sl, ++item) {
           const int col0 = n0 + sl * 64;
-          if (col0 >= p.N) break;  // warp-uniform
+          const uint32_t set = item & 1u;
+          uint8_t* st = my_ptr + set * 8192;
           if (lane == 0) {
-            // the staging boxes may still be read by the previous slab's stores
+            // every earlier store has finished reading its boxes: both sets may be overwritten
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             if (n_aux > 0) {
-              mbar_expect_tx(aux_bar, 4096u * n_aux);
-              tma_load_2d(my_smem + 8192, &map_x0, col0, row0, aux_bar);
-              if (n_aux == 2) tma_load_2d(my_smem + 12288, &map_x1, col0, row0, aux_bar);
+              if (sl + 1 < n_slabs) issue_aux(tl, sl + 1, set ^ 1u);
+              else if (tile + static_cast<int>(gridDim.x) < num_tiles) issue_aux((tile + gridDim.x) / split_k, 0, set ^ 1u);
             }
           }
           __syncwarp();
@@ -237,8 +253,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tmem_ld32(taddr + sl * 64 + hh * 32, r);
             if (hh == 0 && n_aux > 0) {
               int okw = 1;
-              if (lane == 0) okw = mbar_wait(aux_bar, aux_uses & 1, abortp, p.status, 31) ? 1 : 0;
-              ++aux_uses;
+              if (lane == 0) okw = mbar_wait(aux_bar(set), (item >> 1) & 1u, abortp, p.status, 31) ? 1 : 0;
               if (!__shfl_sync(0xffffffffu, okw, 0)) { ok = false; break; }
             }
 #pragma unroll
@@ -254,25 +269,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
                 x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
               }
+              int out_off = 0;      // where the result goes inside the set: over aux0, or over aux1 for the cross epilogue
               if (p.epi == kEpiLinear) {
                 if (p.relu) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
                 }
               } else {
-                const uint4 a0 = *reinterpret_cast<const uint4*>(my_ptr + 8192 + chunk);
+                const uint4 a0 = *reinterpret_cast<const uint4*>(st + chunk);
                 const uint32_t a0w[4] = {a0.x, a0.y, a0.z, a0.w};
-                if (p.epi == kEpiCross) {
-                  if (p.out2 != nullptr)
-                    *reinterpret_cast<uint4*>(my_ptr + 4096 + chunk) =
-                        make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
-                  const uint4 a1 = *reinterpret_cast<const uint4*>(my_ptr + 12288 + chunk);
+                if (cross) {
+                  const uint4 a1 = *reinterpret_cast<const uint4*>(st + 4096 + chunk);
                   const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+                  // second output V = acc + bias replaces the x0 chunk this thread has just read
+                  *reinterpret_cast<uint4*>(st + chunk) =
+                      make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     x[2 * j] = bf16_lo(a0w[j]) * x[2 * j] + bf16_lo(a1w[j]);
                     x[2 * j + 1] = bf16_hi(a0w[j]) * x[2 * j + 1] + bf16_hi(a1w[j]);
                   }
+                  out_off = 4096;
                 } else if (p.epi == kEpiMaskRelu) {
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
@@ -292,7 +309,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     x[2 * j + 1] *= bf16_hi(a0w[j]);
                   }
                   if (n_aux == 2) {
-                    const uint4 a1 = *reinterpret_cast<const uint4*>(my_ptr + 12288 + chunk);
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(st + 4096 + chunk);
                     const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -302,7 +319,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   }
                 }
               }
-              *reinterpret_cast<uint4*>(my_ptr + chunk) =
+              *reinterpret_cast<uint4*>(st + out_off + chunk) =
                   make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
             }
           }
@@ -310,8 +327,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_d, col0, row0, my_smem);
-            if (p.epi == kEpiCross && p.out2 != nullptr) tma_store_2d(&map_d2, col0, row0, my_smem + 4096);
+            tma_store_2d(&map_d, col0, row0, my_smem + set * 8192 + (cross ? 4096u : 0u));
+            if (cross && p.out2 != nullptr) tma_store_2d(&map_d2, col0, row0, my_smem + set * 8192);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
