@@ -214,7 +214,7 @@ def main() -> None:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"model": "DLRM-DCNv2 (Criteo-1TB geometry, 26 tables, dim 128, 3x rank-512 cross)",
                    "global_batch": args.global_batch, "per_gpu_batch": B, "ids_per_sample": sum(cfg.bag_sizes),
-                   "parallelism": f"dp{W} + sharded embeddings (row-wise >=256MB tables, table-wise rest)",
+                   "parallelism": f"dp{W} + sharded embeddings (cost-balanced placement: table-wise, hottest tables row-wise)",
                    "embedding_optimizer": "row-wise Adagrad (fp32 tables)", "dense_optimizer": "Adam",
                    "vocab_scale": args.vocab_scale, "cuda_graph": use_graph,
                    "l2": "inputs larger than L2: activations >= 450 MB per layer at batch 65536 and "
