@@ -18,6 +18,7 @@ roofline: the slower of (HBM bytes the busiest rank must move / measured copy ba
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 
@@ -169,7 +170,8 @@ def main():
         row.update({"fwd_floor_ms": round(ff * 1e3, 4), "bwd_floor_ms": round(bf * 1e3, 4),
                     "fwd_frac_of_roofline": round(ff * 1e3 / f, 3), "bwd_frac_of_roofline": round(bf * 1e3 / b, 3),
                     "placements": placements, **{k: round(v, 3) for k, v in det.items()}})
-      del module
+      del module, gathered
+      gc.collect()                 # module and backend reference each other: without this the tables stay allocated
       torch.cuda.empty_cache()
     if "fused_fwd_ms" in row and "collective_fwd_ms" in row:
       row["fwd_speedup_vs_nccl"] = round(row["collective_fwd_ms"] / row["fused_fwd_ms"], 2)

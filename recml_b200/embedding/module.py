@@ -220,17 +220,24 @@ class ShardedEmbedding(nn.Module):
     has_rep = len(layout) != len(self.feature_names)
     if flat and not has_rep:
       return out
+    d = self.uniform_dim()
+    if (not has_rep and not flat and d is not None and all(L == 0 for _, _, _, L in layout)
+        and out.is_contiguous() and out.shape[1] == len(layout) * d):
+      return out.view(out.shape[0], len(layout), d)      # a view: nothing is copied, forward or backward
     feats = {}
-    for f, col, width, L in layout:
+    # one split (whose backward is one concatenation) instead of a slice per feature, whose backward
+    # would allocate and add a full-width gradient per feature
+    contiguous_cols = all(col == sum(w for _, _, w, _ in layout[:i]) for i, (_, col, _, _) in enumerate(layout))
+    pieces = (torch.split(out, [w for _, _, w, _ in layout], dim=1) if contiguous_cols and
+              sum(w for _, _, w, _ in layout) == out.shape[1] else [out[:, c:c + w] for _, c, w, _ in layout])
+    for (f, col, width, L), x in zip(layout, pieces):
       D = self.config.specs[f].embedding_dim
-      x = out[:, col:col + width]
       feats[f] = x.reshape(x.shape[0], L, D) if L else x
     for f in self.feature_names:
       if f not in feats:
         feats[f] = self._replicated_lookup(kjt, f).to(out.dtype)
     if flat:
       return torch.cat([feats[f].reshape(feats[f].shape[0], -1) for f in self.feature_names], dim=1)
-    d = self.uniform_dim()
     if d is not None:
       return torch.stack([feats[f] for f in self.feature_names], dim=1)
     return feats
