@@ -4,6 +4,8 @@ Public surface (the names exported by the reference's `recml/__init__.py:19-40`)
 """
 from recml_b200 import config
 from recml_b200 import data
+from recml_b200 import embedding
+from recml_b200 import layers
 from recml_b200 import metrics
 from recml_b200 import utils
 from recml_b200.metrics.base import Metric
