@@ -31,7 +31,7 @@ METRIC = "dlrm_dcnv2_train_samples_per_sec"
 
 
 def reference_arm() -> None:
-  # The reference has no setup.py / pyproject, so `pip install /root/reference` is refused; its
+  # The reference tree has no setup.py / pyproject, so pip refuses to install it; its
   # bundled wheel installs into baseline/_ref but imports jax / flax, which are not in this image,
   # and its embedding and attention ops only lower to TPU custom calls.
   print(json.dumps({"impl": "reference", "unavailable":
