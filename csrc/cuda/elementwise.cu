@@ -113,30 +113,53 @@ __global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, long long M, 
 
 // ---- DCN cross backward, element-wise part ----------------------------------------------------------
 // dv = g * x0 ; dx0 (+)= g * v        (all [M, N] bf16 with leading dim ld; dx0 fp32 accumulate or bf16)
-__global__ void cross_bwd_ew_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x0,
-                                    const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ dv,
-                                    __nv_bfloat16* __restrict__ dx0, int accumulate, long long M, int N,
-                                    long long ld) {
-  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8;
-  const long long per_row = N;  // N % 8 == 0
-  if (i >= M * per_row) return;
-  const long long r = i / per_row;
-  const long long off = r * ld + (i - r * per_row);
-  const uint4 G = *reinterpret_cast<const uint4*>(g + off);
-  const uint4 X = *reinterpret_cast<const uint4*>(x0 + off);
-  const uint4 V = *reinterpret_cast<const uint4*>(v + off);
-  uint4 D = make_uint4(0, 0, 0, 0);
-  if (accumulate) D = *reinterpret_cast<const uint4*>(dx0 + off);
-  const uint32_t gw[4] = {G.x, G.y, G.z, G.w}, xw[4] = {X.x, X.y, X.z, X.w}, vw[4] = {V.x, V.y, V.z, V.w};
-  uint32_t dw[4] = {D.x, D.y, D.z, D.w}, ow[4];
+// A block covers 256 columns (32 lanes x 8 bf16) x rows_per_block rows, its 8 warps striding the rows, and also
+// reduces the column sums of dv (= the gradient of the layer's bias) so that dv is not read again for them.
+__global__ void __launch_bounds__(256) cross_bwd_ew_kernel(
+    const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ v,
+    __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ dx0, int accumulate, long long M, int N, long long ld,
+    float* __restrict__ colsum_dv, int rows_per_block) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r1 = min(M, r0 + rows_per_block);
+  float cs[8];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
-    ow[j] = pack_bf16(g0 * bf16_lo(xw[j]), g1 * bf16_hi(xw[j]));
-    dw[j] = pack_bf16(bf16_lo(dw[j]) + g0 * bf16_lo(vw[j]), bf16_hi(dw[j]) + g1 * bf16_hi(vw[j]));
+  for (int j = 0; j < 8; ++j) cs[j] = 0.f;
+  if (col < N) {        // N % 8 == 0
+    for (long long r = r0 + warp; r < r1; r += 8) {
+      const long long off = r * ld + col;
+      const uint4 G = *reinterpret_cast<const uint4*>(g + off);
+      const uint4 X = *reinterpret_cast<const uint4*>(x0 + off);
+      const uint4 V = *reinterpret_cast<const uint4*>(v + off);
+      uint4 D = make_uint4(0, 0, 0, 0);
+      if (accumulate) D = *reinterpret_cast<const uint4*>(dx0 + off);
+      const uint32_t gw[4] = {G.x, G.y, G.z, G.w}, xw[4] = {X.x, X.y, X.z, X.w}, vw[4] = {V.x, V.y, V.z, V.w};
+      uint32_t dw[4] = {D.x, D.y, D.z, D.w}, ow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
+        ow[j] = pack_bf16(g0 * bf16_lo(xw[j]), g1 * bf16_hi(xw[j]));
+        cs[2 * j] += bf16_lo(ow[j]);          // sums of the ROUNDED values, i.e. exactly what a later pass over dv would add
+        cs[2 * j + 1] += bf16_hi(ow[j]);
+        dw[j] = pack_bf16(bf16_lo(dw[j]) + g0 * bf16_lo(vw[j]), bf16_hi(dw[j]) + g1 * bf16_hi(vw[j]));
+      }
+      *reinterpret_cast<uint4*>(dv + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      *reinterpret_cast<uint4*>(dx0 + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+    }
   }
-  *reinterpret_cast<uint4*>(dv + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-  *reinterpret_cast<uint4*>(dx0 + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+  if (colsum_dv == nullptr) return;
+  __shared__ float sh[8][256];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sh[warp][lane * 8 + j] = cs[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.x * 256 + c < N) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) acc += sh[w][c];
+    atomicAdd(colsum_dv + blockIdx.x * 256 + c, acc);
+  }
 }
 
 // out = a + b (bf16, [M,N] with leading dims)
@@ -266,13 +289,15 @@ extern "C" int recml_colsum_bf16(const void* x, long long M, int N, long long ld
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// colsum_dv: optional fp32 [N], pre-zeroed; receives the column sums of dv.
 extern "C" int recml_cross_bwd_ew(const void* g, const void* x0, const void* v, void* dv, void* dx0, int accumulate,
-                                  long long M, int N, long long ld, cudaStream_t stream) {
-  const long long n = M * N / 8;
-  if (n <= 0) return 0;
-  cross_bwd_ew_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, stream>>>(
+                                  long long M, int N, long long ld, float* colsum_dv, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const int rows_per_block = 128;
+  dim3 grid((N + 255) / 256, static_cast<unsigned>((M + rows_per_block - 1) / rows_per_block));
+  cross_bwd_ew_kernel<<<grid, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(x0), static_cast<const __nv_bfloat16*>(v),
-      static_cast<__nv_bfloat16*>(dv), static_cast<__nv_bfloat16*>(dx0), accumulate, M, N, ld);
+      static_cast<__nv_bfloat16*>(dv), static_cast<__nv_bfloat16*>(dx0), accumulate, M, N, ld, colsum_dv, rows_per_block);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -164,8 +164,8 @@ class CrossNetFn(torch.autograd.Function):
     dus, dvs, dbs = [None] * n, [None] * n, [None] * n
     for i in range(n - 1, -1, -1):
       xl, u, v, u16, v16 = ctx.saved[i]
-      dv = ew.cross_bwd_ew(g, x0, v, dx0, accumulate=i != n - 1)   # dv = g⊙x0 ; dx0 (+)= g⊙v
-      dbs[i] = ew.colsum(dv)
+      # dv = g⊙x0 ; dx0 (+)= g⊙v ; db = column sums of dv, all in one pass
+      dv, dbs[i] = ew.cross_bwd_ew(g, x0, v, dx0, accumulate=i != n - 1, want_colsum=True)
       if ctx.low_rank:
         dvs[i] = G.gemm(dv, u, a_mn=True, b_mn=True, out_dtype=torch.float32)       # [d, r]
         du = G.gemm(dv, v16, b_mn=True)                                             # [M, r]

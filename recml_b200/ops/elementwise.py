@@ -47,20 +47,22 @@ def colsum(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
   return out
 
 
-def cross_bwd_ew(g, x0, v, dx0, accumulate: bool):
-  """dv = g⊙x0 (returned); dx0 (+)= g⊙v, in place."""
+def cross_bwd_ew(g, x0, v, dx0, accumulate: bool, want_colsum: bool = False):
+  """dv = g⊙x0 (returned); dx0 (+)= g⊙v, in place.  With `want_colsum` also returns the fp32 column
+  sums of dv (the cross layer's bias gradient), computed in the same pass."""
   if not g.is_cuda:
     dv = (g.float() * x0.float()).to(g.dtype)
     upd = g.float() * v.float()
     dx0.copy_((dx0.float() + upd if accumulate else upd).to(dx0.dtype))
-    return dv
+    return (dv, dv.float().sum(0)) if want_colsum else dv
   M, N = g.shape
   assert g.stride(0) == x0.stride(0) == v.stride(0) == dx0.stride(0)
   dv = torch.empty_strided(g.shape, g.stride(), dtype=g.dtype, device=g.device)
+  cs = torch.zeros(N, dtype=torch.float32, device=g.device) if want_colsum else None
   _lib.check_rc(_lib.cuda().recml_cross_bwd_ew(_lib.ptr(g), _lib.ptr(x0), _lib.ptr(v), _lib.ptr(dv), _lib.ptr(dx0),
                                                c_int(int(accumulate)), c_ll(M), c_int(N), c_ll(g.stride(0)),
-                                               _lib.stream()), "cross_bwd_ew")
-  return dv
+                                               _lib.ptr(cs), _lib.stream()), "cross_bwd_ew")
+  return (dv, cs) if want_colsum else dv
 
 
 def add_bf16(a, b, out=None):
