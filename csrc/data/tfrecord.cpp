@@ -139,6 +139,29 @@ bool find_feature(Slice example, const char* name, Slice& out) {
   return false;
 }
 
+// SequenceExample { Features context = 1; FeatureLists feature_lists = 2 };
+// FeatureLists { map<string, FeatureList> feature_list = 1 };  FeatureList { repeated Feature feature = 1 }
+bool find_feature_list(Slice example, const char* name, Slice& out) {
+  const size_t name_len = strlen(name);
+  uint32_t num, wire;
+  Slice pl;
+  uint64_t sc;
+  while (example.n > 0 && field(example, num, wire, pl, sc)) {
+    if (num != 2 || wire != 2) continue;
+    Slice lists = pl;
+    while (lists.n > 0 && field(lists, num, wire, pl, sc)) {
+      if (num != 1 || wire != 2) continue;
+      Slice entry = pl, key{nullptr, 0}, val{nullptr, 0};
+      while (entry.n > 0 && field(entry, num, wire, pl, sc)) {
+        if (num == 1) key = pl;
+        if (num == 2) val = pl;
+      }
+      if (key.n == name_len && memcmp(key.p, name, name_len) == 0) { out = val; return true; }
+    }
+  }
+  return false;
+}
+
 }  // namespace
 
 extern "C" {
@@ -215,6 +238,44 @@ int recml_parse_examples(const uint8_t* data, const long long* offsets, const lo
     }
   }, 64);
   return status;
+}
+
+// Parses one named feature LIST of `count` serialized SequenceExamples: the values of all steps of a
+// record are concatenated.  Pass 1 (values == nullptr): row_lengths[r] = number of values, steps[r] =
+// number of steps.  Pass 2: values written at row_starts[r].  kind 0: int64, 1: float.
+int recml_parse_sequence_examples(const uint8_t* data, const long long* offsets, const long long* lengths,
+                                  long long count, const char* name, int kind, void* values, long long* row_lengths,
+                                  long long* steps, const long long* row_starts) {
+  recml::ThreadPool::global().parallel_for(count, [&](long long r0, long long r1, int) {
+    std::vector<int64_t> ints;
+    std::vector<float> floats;
+    for (long long r = r0; r < r1; ++r) {
+      ints.clear();
+      floats.clear();
+      long long n_steps = 0;
+      Slice list;
+      if (find_feature_list(Slice{data + offsets[r], static_cast<size_t>(lengths[r])}, name, list)) {
+        uint32_t num, wire;
+        Slice pl;
+        uint64_t sc;
+        while (list.n > 0 && field(list, num, wire, pl, sc)) {
+          if (num != 1 || wire != 2) continue;
+          parse_feature(pl, kind == 0 ? &ints : nullptr, kind == 1 ? &floats : nullptr, nullptr);
+          ++n_steps;
+        }
+      }
+      const long long n = kind == 0 ? static_cast<long long>(ints.size()) : static_cast<long long>(floats.size());
+      if (row_lengths != nullptr) row_lengths[r] = n;
+      if (steps != nullptr) steps[r] = n_steps;
+      if (values != nullptr && row_starts != nullptr) {
+        for (long long i = 0; i < n; ++i) {
+          if (kind == 0) static_cast<int64_t*>(values)[row_starts[r] + i] = ints[i];
+          else static_cast<float*>(values)[row_starts[r] + i] = floats[i];
+        }
+      }
+    }
+  }, 64);
+  return 0;
 }
 
 // Decodes a bytes-list feature whose strings are raw little-endian buffers (the `decode_raw` idiom of

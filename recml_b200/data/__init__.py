@@ -1,2 +1,3 @@
 """Data: iterator protocol, synthetic generators, TFRecord input pipeline."""
 from recml_b200.data.iterator import ArraySpec, IterableIterator, Iterator, TFDatasetIterator
+from recml_b200.data.preprocessing import PreprocessingMode

@@ -114,3 +114,41 @@ class RecordFile:
     lib.recml_parse_examples(*args, ctypes.c_int(0), di, df, vals.ctypes.data_as(ctypes.c_void_p), None,
                              starts.ctypes.data_as(ctypes.c_void_p))
     return vals, row_len
+
+
+  def parse_sequence(self, rows: np.ndarray, name: str, dtype: str):
+    """Feature list `name` of tf.SequenceExample records: (values, values per record, steps per record);
+    the values of a record's steps are concatenated in step order."""
+    lib = _lib_host()
+    kind = 0 if dtype in ("int64", "int") else 1
+    np_dt = np.int64 if kind == 0 else np.float32
+    offs = np.ascontiguousarray(self.offsets[rows])
+    lens = np.ascontiguousarray(self.lengths[rows])
+    n = len(rows)
+    args = (self.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
+            lens.ctypes.data_as(ctypes.c_void_p), c_ll(n), name.encode(), ctypes.c_int(kind))
+    row_len, steps = np.zeros(n, dtype=np.int64), np.zeros(n, dtype=np.int64)
+    lib.recml_parse_sequence_examples(*args, None, row_len.ctypes.data_as(ctypes.c_void_p),
+                                      steps.ctypes.data_as(ctypes.c_void_p), None)
+    starts = np.zeros(n, dtype=np.int64)
+    np.cumsum(row_len[:-1], out=starts[1:])
+    vals = np.empty(int(row_len.sum()), dtype=np_dt)
+    lib.recml_parse_sequence_examples(*args, vals.ctypes.data_as(ctypes.c_void_p), None, None,
+                                      starts.ctypes.data_as(ctypes.c_void_p))
+    return vals, row_len, steps
+
+
+def encode_sequence_example(context: Mapping[str, Sequence], feature_lists: Mapping[str, Sequence[Sequence]]) -> bytes:
+  """Serialises a tf.train.SequenceExample: `context` like `encode_example`, `feature_lists` maps a name
+  to a list of steps, each a list of ints or floats."""
+  def feature(vals):
+    vals = list(vals)
+    if vals and isinstance(vals[0], (float, np.floating)):
+      return _ld(2, _ld(1, struct.pack(f"<{len(vals)}f", *vals)))
+    return _ld(3, _ld(1, b"".join(_varint(int(v)) for v in vals)))
+  ctx = encode_example(context)        # Example{features=1} has the same wire shape as SequenceExample.context
+  lists = b""
+  for name, steps in feature_lists.items():
+    fl = b"".join(_ld(1, feature(st)) for st in steps)
+    lists += _ld(1, _ld(1, name.encode()) + _ld(2, fl))
+  return ctx + _ld(2, lists)

@@ -62,6 +62,39 @@ def get_file_groups(input_path: str | Sequence[str], sharding: DatasetShardingIn
   return files
 
 
+def _take(features: dict, idx: np.ndarray) -> dict:
+  """Rows `idx` of a parsed feature dict (dense arrays and {"values", "lengths"[, "steps"]} jagged ones)."""
+  out = {}
+  for k, v in features.items():
+    if isinstance(v, dict):
+      lens = v["lengths"]
+      starts = np.zeros(len(lens) + 1, dtype=np.int64)
+      np.cumsum(lens, out=starts[1:])
+      pieces = [v["values"][starts[i]:starts[i + 1]] for i in idx]
+      item = {"values": np.concatenate(pieces) if pieces else v["values"][:0], "lengths": lens[idx]}
+      if "steps" in v:
+        item["steps"] = v["steps"][idx]
+      out[k] = item
+    else:
+      out[k] = v[idx]
+  return out
+
+
+def _concat(parts: list[dict]) -> dict:
+  out = {}
+  for k, v in parts[0].items():
+    if isinstance(v, dict):
+      out[k] = {kk: np.concatenate([p[k][kk] for p in parts]) for kk in v}
+    else:
+      out[k] = np.concatenate([p[k] for p in parts])
+  return out
+
+
+def _rows_of(features: dict) -> int:
+  v = next(iter(features.values()))
+  return len(v["lengths"]) if isinstance(v, dict) else len(v)
+
+
 class _RecordDataset:
   def __init__(self, fac: "TFDatasetFactory"):
     self.fac = fac
@@ -73,7 +106,7 @@ class _RecordDataset:
     self.batch = self.sharding.per_process_batch_size(fac.global_batch_size)
     self._cached = None
 
-  def _parse(self, rf: tfrecord.RecordFile, rows: np.ndarray) -> dict:
+  def _parse_features(self, rf: tfrecord.RecordFile, rows: np.ndarray) -> dict:
     out = {}
     for name, spec in self.fac.feature_spec.items():
       if isinstance(spec, FixedLenFeature):
@@ -83,6 +116,12 @@ class _RecordDataset:
       else:
         vals, lens = rf.parse(rows, name, spec.dtype)
         out[name] = {"values": vals, "lengths": lens}
+    for name, spec in (self.fac.sequence_feature_spec or {}).items():     # tf.SequenceExample feature lists
+      vals, lens, steps = rf.parse_sequence(rows, name, spec.dtype)
+      out[name] = {"values": vals, "lengths": lens, "steps": steps}
+    return out
+
+  def _finish(self, out: dict):
     for fn in self.fac.preprocessors:
       out = fn(out)
     if self.fac.label_name is not None:
@@ -92,28 +131,116 @@ class _RecordDataset:
       out = fn(out)
     return out
 
+  def _record_stream(self, rng):
+    """(file index, record index) in reading order: `cycle_length` files are open at a time and
+    `block_length` records are taken from each in turn (tf.data `interleave`); then an optional
+    shuffle window."""
+    fac = self.fac
+    files = list(range(len(self.files)))
+    if fac.file_shuffle:
+      rng.shuffle(files)
+
+    def rows_of(fi):
+      n = len(self._open(fi))
+      rows = np.arange(n)
+      if self.shard_records:
+        rows = rows[self.sharding.process_index::self.sharding.num_processes]
+      if fac.shuffle and not fac.shuffle_buffer_size:
+        rng.shuffle(rows)
+      return rows
+
+    def interleaved():
+      cycle = max(1, fac.cycle_length or 1)
+      pending = list(files)
+      active: list[tuple[int, np.ndarray, int]] = []
+      while pending or active:
+        while pending and len(active) < cycle:
+          fi = pending.pop(0)
+          active.append((fi, rows_of(fi), 0))
+        nxt = []
+        for fi, rows, at in active:
+          hi = min(at + max(1, fac.block_length), len(rows))
+          for r in rows[at:hi]:
+            yield fi, int(r)
+          if hi < len(rows):
+            nxt.append((fi, rows, hi))
+        active = nxt
+
+    if fac.shuffle and fac.shuffle_buffer_size:
+      window: list = []
+      for item in interleaved():
+        window.append(item)
+        if len(window) >= fac.shuffle_buffer_size:
+          yield window.pop(int(rng.integers(len(window))))
+      while window:
+        yield window.pop(int(rng.integers(len(window))))
+    else:
+      yield from interleaved()
+
+  def _open(self, fi: int) -> tfrecord.RecordFile:
+    if fi not in self._open_cache:
+      if len(self._open_cache) > 2 * max(1, self.fac.cycle_length or 1) + 2:
+        self._open_cache.clear()
+      self._open_cache[fi] = tfrecord.RecordFile(self.files[fi], verify=self.fac.verify_checksums)
+    return self._open_cache[fi]
+
+  def _parse_mixed(self, items: list[tuple[int, int]]) -> dict:
+    """Parses records that may come from several files, keeping the order of `items`."""
+    fis = np.array([fi for fi, _ in items])
+    rows = np.array([r for _, r in items], dtype=np.int64)
+    uniq = list(dict.fromkeys(fis.tolist()))
+    if len(uniq) == 1:
+      return self._parse_features(self._open(uniq[0]), rows)
+    parts, order = [], []
+    for fi in uniq:
+      sel = np.nonzero(fis == fi)[0]
+      parts.append(self._parse_features(self._open(fi), rows[sel]))
+      order.append(sel)
+    merged = _concat(parts)
+    inv = np.argsort(np.concatenate(order), kind="stable")
+    return _take(merged, inv)
+
   def _generate(self):
     fac = self.fac
     rng = np.random.default_rng(fac.seed)
+    self._open_cache: dict = {}
     epoch = 0
+    carry: list[dict] = []          # rows that passed the filter but do not fill a batch yet
+    carried = 0
     while True:
-      files = list(self.files)
-      if fac.file_shuffle:
-        rng.shuffle(files)
-      for path in files:
-        rf = tfrecord.RecordFile(path, verify=fac.verify_checksums)
-        rows = np.arange(len(rf))
-        if self.shard_records:
-          rows = rows[self.sharding.process_index::self.sharding.num_processes]
-        if fac.shuffle:
-          rng.shuffle(rows)
-        for a in range(0, len(rows), self.batch):
-          chunk = rows[a:a + self.batch]
-          if len(chunk) < self.batch and fac.drop_remainder:
-            continue
-          yield self._parse(rf, chunk)
+      items: list[tuple[int, int]] = []
+      stream = self._record_stream(rng)
+      done = False
+      while not done:
+        items.clear()
+        for it in stream:
+          items.append(it)
+          if len(items) == self.batch:
+            break
+        else:
+          done = True
+        if not items:
+          break
+        if len(items) < self.batch and fac.drop_remainder and fac.filter_fn is None:
+          break
+        feats = self._parse_mixed(items)
+        if fac.filter_fn is None:
+          yield self._finish(feats)
+          continue
+        keep = np.nonzero(np.asarray(fac.filter_fn(feats), dtype=bool))[0]   # vectorised filter, then re-batch
+        if len(keep):
+          carry.append(_take(feats, keep))
+          carried += len(keep)
+        while carried >= self.batch:
+          merged = _concat(carry)
+          yield self._finish(_take(merged, np.arange(self.batch)))
+          rest = _rows_of(merged) - self.batch
+          carry = [_take(merged, np.arange(self.batch, self.batch + rest))] if rest else []
+          carried = rest
       epoch += 1
       if not fac.repeat or (fac.num_epochs is not None and epoch >= fac.num_epochs):
+        if carried and not fac.drop_remainder:
+          yield self._finish(_concat(carry))
         return
 
   def __iter__(self):
@@ -170,6 +297,11 @@ class TFDatasetFactory(types.Factory[iterator_lib.Iterator]):
   verify_checksums: bool = True
   debug: bool = False
   sharding_info: DatasetShardingInfo | None = None
+  sequence_feature_spec: Mapping[str, VarLenFeature] | None = None   # feature lists of tf.SequenceExample records
+  filter_fn: Callable[[dict], Any] | None = None   # parsed batch -> boolean keep mask; survivors are re-batched
+  shuffle_buffer_size: int = 0                     # > 0: shuffle records in a window instead of per file
+  cycle_length: int | None = None                  # files read concurrently (interleave)
+  block_length: int = 1                            # consecutive records taken from a file per turn
 
   def make(self) -> iterator_lib.Iterator:
     return iterator_lib.IterableIterator(_RecordDataset(self))

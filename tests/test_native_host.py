@@ -121,3 +121,43 @@ def test_parallel_chunk_io(tmp_path):
   for a, b, c in zip(bufs, outs, crcs):
     assert np.array_equal(a, b) and c == tfrecord.crc32c(a.tobytes())
   assert not any(f.endswith(".partial") for f in os.listdir(tmp_path))
+
+
+def test_factory_filter_rebatch_interleave_and_sequence_examples(tmp_path):
+  import numpy as np
+  from recml_b200.data import tfrecord, tfrecord_factory as F
+  # three files of 10 records each; record id = file * 100 + index
+  for f in range(3):
+    recs = [tfrecord.encode_sequence_example({"id": [f * 100 + i], "w": [float(i)]},
+                                             {"hist": [[i, i + 1]] * (i % 3), "score": [[0.5 * s] for s in range(i % 2 + 1)]})
+            for i in range(10)]
+    tfrecord.write_tfrecord(str(tmp_path / f"part-{f}.tfrecord"), recs)
+  spec = {"id": F.FixedLenFeature((), "int64"), "w": F.FixedLenFeature((), "float")}
+  seq = {"hist": F.VarLenFeature("int64"), "score": F.VarLenFeature("float")}
+  sharding = F.DatasetShardingInfo(num_processes=1, process_index=0)
+  fac = F.TFDatasetFactory(input_path=str(tmp_path / "part-*.tfrecord"), feature_spec=spec, sequence_feature_spec=seq,
+                           global_batch_size=4, cycle_length=3, block_length=2, prefetch_buffer_size=0,
+                           sharding_info=sharding, drop_remainder=False)
+  batches = list(fac.make())
+  ids = np.concatenate([b["id"] for b in batches])
+  # interleave: two records from each of the three files in turn
+  assert ids[:8].tolist() == [0, 1, 100, 101, 200, 201, 2, 3] and sorted(ids.tolist()) == sorted(
+      f * 100 + i for f in range(3) for i in range(10))
+  b0 = batches[0]                       # records 0, 1, 100, 101
+  assert b0["hist"]["steps"].tolist() == [0, 1, 0, 1] and b0["hist"]["lengths"].tolist() == [0, 2, 0, 2]
+  assert b0["hist"]["values"].tolist() == [1, 2, 1, 2]
+  assert b0["score"]["steps"].tolist() == [1, 2, 1, 2] and np.allclose(b0["score"]["values"], [0, 0, 0.5, 0, 0, 0.5])
+  # vectorised filter keeps even ids and re-batches the survivors into full batches
+  fac2 = F.TFDatasetFactory(input_path=str(tmp_path / "part-*.tfrecord"), feature_spec=spec, sequence_feature_spec=seq,
+                            global_batch_size=4, prefetch_buffer_size=0, sharding_info=sharding,
+                            filter_fn=lambda feats: feats["id"] % 2 == 0)
+  out = list(fac2.make())
+  assert all(len(b["id"]) == 4 for b in out) and len(out) == 3        # 15 survivors -> 3 full batches, remainder dropped
+  kept = np.concatenate([b["id"] for b in out])
+  assert (kept % 2 == 0).all() and kept.tolist() == [0, 2, 4, 6, 8, 100, 102, 104, 106, 108, 200, 202]
+  assert sum(int(b["hist"]["lengths"].sum()) for b in out) == sum(2 * (i % 3) for i in (0, 2, 4, 6, 8)) * 2 + 2 * (0 + 2)
+  # shuffle window: a permutation of the same records
+  fac3 = F.TFDatasetFactory(input_path=str(tmp_path / "part-*.tfrecord"), feature_spec=spec, global_batch_size=5,
+                            shuffle=True, shuffle_buffer_size=7, prefetch_buffer_size=0, sharding_info=sharding)
+  got = np.concatenate([b["id"] for b in fac3.make()])
+  assert sorted(got.tolist()) == sorted(ids.tolist()) and got.tolist() != sorted(got.tolist())
