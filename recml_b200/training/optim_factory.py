@@ -269,3 +269,17 @@ class SGDFactory(types.Factory[OptimizerBuilder]):
   def make(self) -> OptimizerBuilder:
     return OptimizerFactory(learning_rate=self.learning_rate, weight_decay=self.weight_decay,
                             grad_clip_norm=self.grad_clip_norm, freeze_mask=self.freeze_mask).make()
+
+
+def create_optimizer_for_sharded_model(model, factory: types.Factory[OptimizerBuilder] | OptimizerBuilder) -> Optimizer:
+  """Dense optimizer for a model that contains sharded embeddings.
+
+  The reference needs `create_optimizer_for_sc_model` (`jax_tpu_embedding/sparsecore/lib/flax/linen/
+  embed_optimizer.py:77-97`) to route the embedding variables — whose "gradients" are already updated
+  tables — around the dense optimizer with an optax `multi_transform`.  Here the tables are buffers of
+  `ShardedEmbedding`, updated inside its backward kernel, so the split is structural: this returns
+  `factory`'s optimizer over every trainable parameter that is not part of a sharded table."""
+  builder = factory.make() if hasattr(factory, "make") else factory
+  named = {n: p for n, p in model.named_parameters()
+           if p.requires_grad and not getattr(p, "_recml_sharded", False)}
+  return builder.init(named)
