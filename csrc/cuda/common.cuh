@@ -18,6 +18,7 @@ enum StatusCode : int {
   kPeerTimeout = 2,      // a peer rank never raised its flag
   kBadArgument = 3,
   kCapacity = 4,         // a fixed-capacity buffer overflowed
+  kBadIndex = 5,         // an input id lies outside its table (the access is skipped)
 };
 
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // 2 s

@@ -41,6 +41,8 @@ struct FeatDesc {      // one sharded feature as seen by the rank running the ke
   long long grad_off;  // element offset of the feature's block in THIS rank's gradient buffer
   int seq_len;         // >0: sequence feature (no pooling), positions beyond seq_len dropped
   int dst_stride;      // elements between consecutive samples of this feature in the destination
+  int vocab;           // rows of the feature's table: ids outside [0, vocab) are reported and ignored
+  int pad;
 };
 
 struct IdPtrs {        // jagged ids of every source rank, in this rank's memory
@@ -266,6 +268,10 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         if (GAINS) w = (wts != nullptr ? wts[i] : 1.f) * scale;
       }
       bool owned = id >= 0;
+      if (owned && id >= f.vocab) {      // never form an address from an id the table does not have
+        report(p.status, kBadIndex, id);
+        owned = false;
+      }
       unsigned int lrow = 0;
       if (f.kind == kRowWise) {
         owned = owned && ((id % p.W + f.rot) % p.W == p.me);

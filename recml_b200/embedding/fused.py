@@ -42,7 +42,7 @@ class SeqRef(ctypes.Structure):
 class FeatDesc(ctypes.Structure):
   _fields_ = [("feat_index", c_int), ("kind", c_int), ("owner", c_int), ("rot", c_int), ("row_base", c_int),
               ("combiner", c_int), ("dim", c_int), ("col_lo", c_int), ("slot_off", c_ll), ("grad_off", c_ll),
-              ("seq_len", c_int), ("dst_stride", c_int)]
+              ("seq_len", c_int), ("dst_stride", c_int), ("vocab", c_int), ("pad", c_int)]
 
 
 class IdPtrs(ctypes.Structure):
@@ -266,7 +266,7 @@ class FusedBackend:
         else:
           slot, goff, stride = self.slot_off[fname], self.grad_off[m.rank][fname], width
         feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
-                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot, goff, L, stride))
+                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot, goff, L, stride, tp.vocab, 0))
       info["descs"][direct] = _device_struct_array(feats, m.device)
     return info["descs"][direct]
 

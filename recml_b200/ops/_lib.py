@@ -85,7 +85,7 @@ def status_buffer(device: torch.device | None = None) -> torch.Tensor:
 
 
 STATUS_NAMES = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument",
-                4: "buffer capacity exceeded"}
+                4: "buffer capacity exceeded", 5: "input id outside its table (detail = the id)"}
 
 
 class DeviceStatusError(RuntimeError):

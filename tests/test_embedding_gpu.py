@@ -104,3 +104,27 @@ def test_sequence_feature_no_pooling():
   og, oc = g(kjt.to_device(torch.device("cuda"))), c(kjt)
   for k in oc:
     torch.testing.assert_close(og[k].float().cpu(), oc[k], atol=2e-2, rtol=2e-2)
+
+
+def test_out_of_range_ids_are_reported_not_dereferenced():
+  """An id beyond the vocabulary must neither be read nor update anything: the kernel records it and the
+  host raises at the next status check."""
+  import numpy as np
+  import torch
+  from recml_b200 import embedding as emb
+  from recml_b200.ops import _lib
+  spec = {"f": emb.EmbeddingSpec(100, 64, combiner="sum")}
+  m = emb.ShardedEmbedding(emb.ShardedEmbeddingConfig(spec, emb.SGDOptimizerSpec(0.1)), device="cuda")
+  _lib.check_status(torch.device("cuda"))
+  values = torch.tensor([3, 5, 100_000, 7], dtype=torch.int32)
+  offsets = torch.tensor([0, 2, 4], dtype=torch.int32)
+  kjt = emb.KeyedJagged(("f",), values, offsets, None, 2).to_device(torch.device("cuda"))
+  out = m(kjt)
+  table = m.gather_table("f")
+  ref1 = table[5] + table[3]
+  ref2 = table[7]                         # the bad id contributes nothing
+  torch.testing.assert_close(out.reshape(2, 64).float()[0], ref1.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+  torch.testing.assert_close(out.reshape(2, 64).float()[1], ref2.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+  with pytest.raises(_lib.DeviceStatusError, match="outside its table"):
+    _lib.check_status(torch.device("cuda"))
+  _lib.check_status(torch.device("cuda"))  # the status word was cleared
