@@ -7,8 +7,8 @@
 //               broadcast) fills a ring of shared-memory stages and signals "full" mbarriers
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16) and
 //               releases stages / publishes accumulators with tcgen05.commit
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), apply
-//               the fused epilogue, store bf16 / fp32 rows
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (two warps per 32-lane quarter, taking
+//               alternate 64-column slabs), apply the fused epilogue, store bf16 / fp32 rows
 // Two accumulator buffers (2 x BN columns of tensor memory) let the epilogue of tile i
 // overlap the main loop of tile i+1.
 //
@@ -29,7 +29,7 @@ using namespace recml::tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 
 enum Epilogue : int {
   kEpiLinear = 0,    // D = act(acc + bias)
@@ -62,7 +62,7 @@ struct Cfg {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStages = (BN == 256) ? 3 : 4;
-  // per epilogue warp: two staging sets of two 4 KB [32 rows, 64 cols] bf16 boxes (auxiliary operands come in,
+  // per epilogue warp: one staging set of two 4 KB [32 rows, 64 cols] bf16 boxes (auxiliary operands come in,
   // results are written over them and go out)
   static constexpr int kEpi = 4 * 4 * 4096;
   static constexpr int kSmem = kStages * (kStageA + kStageB) + kEpi + 1024 /*align*/ + 256 /*barriers*/;
@@ -106,7 +106,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 128);
+      mbar_init(tempty_bar(s), 256);
     }
     for (int w = 0; w < 8; ++w) mbar_init(bars + 8u * (2 * C::kStages + 4 + w), 1);   // 4 epilogue warps x 2 staging sets
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -189,32 +189,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    // bf16 outputs: every warp owns 32 rows of the tile and walks it in 64-column slabs.  Per slab it
-    // (1) waits for the 32 x 64 boxes of the auxiliary operands that a TMA load brought into one of its
-    // two private staging sets, (2) reads the accumulator from tensor memory, applies the epilogue and
+    // bf16 outputs: the two warps of a lane quarter own the same 32 rows of the tile and take alternate
+    // 64-column slabs.  Per slab a warp (1) TMA-loads the 32 x 64 boxes of the auxiliary operands into
+    // its private staging set, (2) reads the accumulator from tensor memory, applies the epilogue and
     // writes the bf16 results OVER the auxiliary boxes (same thread, same 16-byte chunk), (3) hands the
-    // boxes to TMA stores.  The loads of the NEXT slab (of this tile or of the warp's next tile) are
-    // issued into the other set before step (1), so their latency hides behind this slab's work.  All
-    // global traffic of the epilogue is full 128-byte lines and only __syncwarp is needed.  fp32
-    // outputs (weight gradients) are written directly: a thread's 32 floats already are one full line.
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
-    const uint32_t my_smem = epi_smem + quarter * 16384;
-    uint8_t* my_ptr = epi_ptr + quarter * 16384;
-    auto aux_bar = [&](uint32_t set) { return bars + 8u * (2 * C::kStages + 4 + quarter * 2 + set); };
+    // boxes to TMA stores.  While one warp waits for its loads or for its store to drain, its sibling
+    // computes, so the quarter keeps a slab in flight at every stage.  All global traffic of the
+    // epilogue is full 128-byte lines and only __syncwarp is needed.  fp32 outputs (weight gradients)
+    // are written directly: a thread's 32 floats already are one full line.
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+    const int sub = (warp - 2) >> 2;         // which of the quarter's two warps
+    const uint32_t my_smem = epi_smem + quarter * 16384 + sub * 8192;
+    uint8_t* st = epi_ptr + quarter * 16384 + sub * 8192;
+    const uint32_t aux_bar = bars + 8u * (2 * C::kStages + 4 + quarter * 2 + sub);
     const int n_aux = p.epi == kEpiLinear ? 0 : ((p.epi == kEpiCross || (p.epi == kEpiMulAdd && p.aux1 != nullptr)) ? 2 : 1);
     const bool cross = p.epi == kEpiCross;
     auto slabs_of = [&](int tl) {
       const int rem = p.N - (tl % n_tiles) * BN;
       return rem >= BN ? BN / 64 : (rem + 63) / 64;
     };
-    auto issue_aux = [&](int tl, int sl, uint32_t set) {   // one lane calls this
-      const int r0 = (tl / n_tiles) * BM + quarter * 32, c0 = (tl % n_tiles) * BN + sl * 64;
-      mbar_expect_tx(aux_bar(set), 4096u * n_aux);
-      tma_load_2d(my_smem + set * 8192, &map_x0, c0, r0, aux_bar(set));
-      if (n_aux == 2) tma_load_2d(my_smem + set * 8192 + 4096, &map_x1, c0, r0, aux_bar(set));
-    };
-    uint32_t item = 0;          // slabs processed so far: staging set = item & 1, barrier parity = (item >> 1) & 1
-    if (!p.out_f32 && n_aux > 0 && lane == 0 && static_cast<int>(blockIdx.x) < num_tiles) issue_aux(blockIdx.x / split_k, 0, 0);
+    uint32_t aux_uses = 0;      // completed phases of this warp's aux barrier
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int tl = tile / split_k;
@@ -234,16 +228,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool ok = true;
         const int n_slabs = slabs_of(tl);
 #pragma unroll 1
-        for (int sl = 0; sl < n_slabs && ok; ++sl, ++item) {
+        for (int sl = sub; sl < n_slabs && ok; sl += 2) {
           const int col0 = n0 + sl * 64;
-          const uint32_t set = item & 1u;
-          uint8_t* st = my_ptr + set * 8192;
           if (lane == 0) {
-            // every earlier store has finished reading its boxes: both sets may be overwritten
+            // this warp's previous store has finished reading the staging set
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             if (n_aux > 0) {
-              if (sl + 1 < n_slabs) issue_aux(tl, sl + 1, set ^ 1u);
-              else if (tile + static_cast<int>(gridDim.x) < num_tiles) issue_aux((tile + gridDim.x) / split_k, 0, set ^ 1u);
+              mbar_expect_tx(aux_bar, 4096u * n_aux);
+              tma_load_2d(my_smem, &map_x0, col0, row0, aux_bar);
+              if (n_aux == 2) tma_load_2d(my_smem + 4096, &map_x1, col0, row0, aux_bar);
             }
           }
           __syncwarp();
@@ -253,7 +246,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tmem_ld32(taddr + sl * 64 + hh * 32, r);
             if (hh == 0 && n_aux > 0) {
               int okw = 1;
-              if (lane == 0) okw = mbar_wait(aux_bar(set), (item >> 1) & 1u, abortp, p.status, 31) ? 1 : 0;
+              if (lane == 0) okw = mbar_wait(aux_bar, aux_uses & 1u, abortp, p.status, 31) ? 1 : 0;
+              ++aux_uses;
               if (!__shfl_sync(0xffffffffu, okw, 0)) { ok = false; break; }
             }
 #pragma unroll
@@ -327,15 +321,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_d, col0, row0, my_smem + set * 8192 + (cross ? 4096u : 0u));
-            if (cross && p.out2 != nullptr) tma_store_2d(&map_d2, col0, row0, my_smem + set * 8192);
+            tma_store_2d(&map_d, col0, row0, my_smem + (cross ? 4096u : 0u));
+            if (cross && p.out2 != nullptr) tma_store_2d(&map_d2, col0, row0, my_smem);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
         if (!ok) break;
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = sub; c < BN / 32; c += 2) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;  // warp-uniform
           uint32_t r[32];
