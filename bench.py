@@ -160,11 +160,18 @@ def main() -> None:
   cursor = [0]
   last_loss = [0.0]
 
+  def host_stream():
+    while True:
+      yield host_batches[cursor[0] % n_pool]
+      cursor[0] += 1
+
+  # the framework's input path: pinned host batch -> copy stream -> device, one batch ahead of the step
+  from recml_b200.data import prefetch
+  feeder = prefetch.DevicePrefetcher(host_stream(), part, depth=1)
+
   def e2e_step():
-    hb = host_batches[cursor[0] % n_pool]
-    cursor[0] += 1
     nonlocal state
-    state, metrics = train_step(part.shard_inputs(hb), state)
+    state, metrics = train_step(next(feeder), state)              # issues the H2D copy of the NEXT batch
     last_loss[0] = float(metrics["loss"].localize().compute())   # D2H read of total and count
 
   for _ in range(args.warmup):
@@ -195,7 +202,7 @@ def main() -> None:
   hstu = None
   if not args.no_hstu:
     try:
-      del train_step, state, task, dev_batches, host_batches, first, it, data
+      del train_step, state, task, dev_batches, host_batches, first, it, data, feeder
       import gc
       gc.collect()
       torch.cuda.empty_cache()

@@ -94,10 +94,12 @@ class Trainer(core.Trainer[task_lib.Task]):
                max_checkpoints_to_keep: int = 5, continuous_eval_timeout: int = 30,
                rng_seed: int = core.DEFAULT_RNG_SEED, rng_impl: str | None = None,
                enable_checkpointing: bool = True, check_for_checkpoints: bool = True,
-               failure_detection: bool = False, heartbeat_timeout_s: float = 30.0):
+               failure_detection: bool = False, heartbeat_timeout_s: float = 30.0,
+               prefetch_to_device: int = 1):
     if not isinstance(steps_per_loop, int) or steps_per_loop < 1:
       raise ValueError(f"`steps_per_loop` ({steps_per_loop}) must be a positive integer.")
     self._partitioner = partitioner or partitioning.NullPartitioner()
+    self._prefetch_depth = prefetch_to_device      # batches copied to the device ahead of the step that uses them
     self._model_dir = model_dir or "/tmp"
     self._train_steps = train_steps
     self._steps_per_loop = steps_per_loop
@@ -188,14 +190,17 @@ class Trainer(core.Trainer[task_lib.Task]):
     timer = profiling.DeviceStepTimer(enabled=torch.cuda.is_available())
     t0, examples, timed_steps = None, 0, 0
     self._start_health()
+    if getattr(self, "_prefetcher_src", None) is not train_iter:       # one prefetcher per iterator, kept across loops
+      from recml_b200.data import prefetch
+      self._prefetcher = prefetch.DevicePrefetcher(train_iter, self._partitioner, depth=self._prefetch_depth)
+      self._prefetcher_src = train_iter
     for step in range(start_step, start_step + num_steps):
       self._check_health(step)
       if step - start_step == WARMUP_STEPS:
         timer.start()
         t0 = time.time()
       with profiling.step_annotation("train", step):
-        host_batch = next(train_iter)
-        inputs = self._partitioner.shard_inputs(host_batch)
+        inputs, host_batch = self._prefetcher.next_with_host()
         state, metrics = train_step(inputs, state)
       if t0 is not None:
         examples += _batch_size_of(host_batch)
