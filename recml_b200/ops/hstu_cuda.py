@@ -32,16 +32,36 @@ def available() -> bool:
   return _ok
 
 
+# Every layer of a model (and its backward) passes the SAME seq_offsets / timestamps tensors: what is
+# derived from them is computed once per batch and remembered for the tensor object it came from.
+_memo: dict[str, tuple] = {}
+
+
+def _remember(kind: str, src: torch.Tensor, make):
+  key = (id(src), src.data_ptr(), src._version, tuple(src.shape))
+  hit = _memo.get(kind)
+  if hit is not None and hit[0] == key and hit[1]() is src:
+    return hit[2]
+  import weakref
+  val = make()
+  _memo[kind] = (key, weakref.ref(src), val)
+  return val
+
+
 def _ts32(timestamps):
   """Seconds relative to the earliest timestamp of the batch as int32 (the kernels only use differences)."""
   if timestamps is None:
     return None
   if timestamps.dtype == torch.int32:
     return timestamps.contiguous()
-  return (timestamps - timestamps.min()).to(torch.int32).contiguous()
+  return _remember("ts32", timestamps, lambda: (timestamps - timestamps.min()).to(torch.int32).contiguous())
 
 
 def _tiles(seq_offsets: torch.Tensor, T: int):
+  return _remember(f"tiles{T}", seq_offsets, lambda: _make_tiles(seq_offsets, T))
+
+
+def _make_tiles(seq_offsets: torch.Tensor, T: int):
   B = seq_offsets.numel() - 1
   cap = (T + 127) // 128 + B
   tile_seq = torch.empty(cap, dtype=torch.int32, device=seq_offsets.device)
