@@ -49,6 +49,8 @@ struct Params {
   int softmax;
   float* lse;                 // [T, H]
   const float* delta;         // [T, H] (backward)
+  // row pitch in elements of q / k / v / dO when they are column slices of a wider matrix (0: H * Dh)
+  int ld_q, ld_k, ld_v, ld_do;
 };
 
 // Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
@@ -676,8 +678,9 @@ template <int DH>
 static int launch_fwd(const void* q, const void* k, const void* v, const Params& p, int n_tiles, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   const long long cols = static_cast<long long>(p.H) * DH;
-  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, cols, BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, cols, BKV) ||
-      recml::tc::make_map_bf16(&mv, v, p.T, cols, cols, BKV))
+  auto pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : cols; };
+  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
+      recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV))
     return -2;
   auto kern = hstu_fwd_kernel<DH>;
   static bool configured = false;
@@ -705,8 +708,9 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
                       cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo;
   const long long cols = static_cast<long long>(p.H) * DH;
-  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, cols, BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, cols, BKV) ||
-      recml::tc::make_map_bf16(&mv, v, p.T, cols, cols, BKV) || recml::tc::make_map_bf16(&mdo, d_o, p.T, cols, cols, BQ))
+  auto pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : cols; };
+  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
+      recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV) || recml::tc::make_map_bf16(&mdo, d_o, p.T, cols, pitch(p.ld_do), BQ))
     return -2;
   auto kern = hstu_bwd_kernel<DH>;
   static bool configured = false;

@@ -128,7 +128,7 @@ class _JaggedAttnFn(torch.autograd.Function):
     from recml_b200.ops import hstu_cuda
     q, k, v, pos_w, ts_w, seq_offsets, timestamps = ctx.saved_tensors
     max_seq_len, causal, scale = ctx.meta
-    dq, dk, dv, dpos, dts = hstu_cuda.backward(do.contiguous(), q, k, v, seq_offsets, timestamps, pos_w, ts_w,
+    dq, dk, dv, dpos, dts = hstu_cuda.backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w,
                                                max_seq_len, causal, scale)
     return dq, dk, dv, dpos, dts, None, None, None, None, None
 
@@ -140,7 +140,7 @@ def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=
   if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
     from recml_b200.ops import hstu_cuda
     if hstu_cuda.available():
-      return _JaggedAttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), pos_w, ts_w,
+      return _JaggedAttnFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), pos_w, ts_w,
                                  seq_offsets.to(torch.int32), timestamps, max_seq_len, causal, scale)
   return jagged_attention_reference(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
                                     timestamps=timestamps, causal=causal, scale=scale)

@@ -16,7 +16,7 @@ class _Params(ctypes.Structure):
               ("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("timestamps", c_vp),
               ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
               ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("softmax", c_int), ("lse", c_vp),
-              ("delta", c_vp)]
+              ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int)]
 
 
 _ok: bool | None = None
@@ -71,9 +71,25 @@ def _make_tiles(seq_offsets: torch.Tensor, T: int):
   return tile_seq, tile_row0, cap
 
 
-def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles):
+def rows_ok(t: torch.Tensor) -> bool:
+  """`[T, H, Dh]` bf16 whose heads are contiguous and whose rows start on 16-byte boundaries: a plain tensor
+  or a column slice of a wider matrix (e.g. one of the u|q|k|v blocks of a fused projection)."""
+  H, Dh = t.shape[1], t.shape[2]
+  return (t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == Dh and t.stride(0) >= H * Dh
+          and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0)
+
+
+def as_rows(t: torch.Tensor) -> torch.Tensor:
+  return t if rows_ok(t) else t.contiguous()
+
+
+def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles, k=None, v=None, do=None):
   T, H, Dh = q.shape
   p = _Params()
+  p.ld_q = q.stride(0)
+  p.ld_k = k.stride(0) if k is not None else 0
+  p.ld_v = v.stride(0) if v is not None else 0
+  p.ld_do = do.stride(0) if do is not None else 0
   p.T, p.H, p.Dh, p.B, p.max_seq_len = T, H, Dh, seq_offsets.numel() - 1, max_seq_len
   p.num_buckets = ts_w.numel() - 1 if ts_w is not None else 0
   p.causal, p.scale, p.inv_n = int(causal), scale, 1.0 / max_seq_len
@@ -86,13 +102,13 @@ def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale,
 
 
 def forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
-  assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.bfloat16
+  assert rows_ok(q) and rows_ok(k) and rows_ok(v)
   timestamps = _ts32(timestamps)
   pos_w = None if pos_w is None else pos_w.detach().float().contiguous()
   ts_w = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0])
-  out = torch.empty_like(q)
-  p = _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles)
+  out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+  p = _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles, k, v)
   p.out = out.data_ptr()
   keep = (timestamps, pos_w, ts_w, tiles)  # referenced until the launch is enqueued
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
@@ -110,15 +126,16 @@ def backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, cau
   pw = None if pos_w is None else pos_w.detach().float().contiguous()
   tw = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0])
+  do = as_rows(do)
   dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-  dk, dv = torch.empty_like(k), torch.empty_like(v)
+  dk, dv = (torch.empty(k.shape, dtype=k.dtype, device=k.device) for _ in range(2))
   dpos = torch.zeros_like(pw) if pw is not None else None
   dts = torch.zeros_like(tw) if (tw is not None and timestamps is not None) else None
-  p = _params(q, seq_offsets, timestamps, pw, tw, max_seq_len, causal, scale, tiles)
+  p = _params(q, seq_offsets, timestamps, pw, tw, max_seq_len, causal, scale, tiles, k, v, do)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
   p.dpos_w = dpos.data_ptr() if dpos is not None else None
   p.dts_w = dts.data_ptr() if dts is not None else None
-  _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do.contiguous()),
+  _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do),
                                         ctypes.byref(p), c_int(tiles[2]), _lib.stream()), "hstu_attn_bwd")
   return (dq.to(q.dtype), dk, dv, None if dpos is None else dpos.to(pos_w.dtype),
           None if ts_w is None else (dts.to(ts_w.dtype) if dts is not None else torch.zeros_like(ts_w)))
@@ -147,12 +164,12 @@ SOFTMAX_MAX_LEN = 256
 
 def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
   """Jagged softmax attention; returns (out `[T, H, Dh]` bf16, row log-sum-exp `[T, H]` fp32)."""
-  assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.bfloat16
+  assert rows_ok(q) and rows_ok(k) and rows_ok(v)
   assert max_seq_len <= SOFTMAX_MAX_LEN
   tiles = _tiles(seq_offsets, q.shape[0])
-  out = torch.empty_like(q)
+  out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
   lse = torch.empty(q.shape[0], q.shape[1], dtype=torch.float32, device=q.device)
-  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles)
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v)
   p.out, p.softmax, p.lse = out.data_ptr(), 1, lse.data_ptr()
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "softmax_attn_fwd")
@@ -161,11 +178,11 @@ def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
 
 def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, scale):
   tiles = _tiles(seq_offsets, q.shape[0])
-  do = do.contiguous()
+  do = as_rows(do)
   delta = (do.float() * out.float()).sum(-1).contiguous()          # [T, H]
   dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-  dk, dv = torch.empty_like(k), torch.empty_like(v)
-  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles)
+  dk, dv = (torch.empty(k.shape, dtype=k.dtype, device=k.device) for _ in range(2))
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v, do)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
   p.softmax, p.lse, p.delta = 1, lse.data_ptr(), delta.data_ptr()
   _lib.check_rc(_lib.cuda().recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do), ctypes.byref(p),

@@ -58,7 +58,9 @@ class _JaggedSoftmaxFn(torch.autograd.Function):
 
 def jagged_softmax_attention(q, k, v, seq_offsets, max_seq_len: int, causal: bool, scale: float | None = None):
   scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
-  return _JaggedSoftmaxFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), seq_offsets, max_seq_len, causal, scale)
+  from recml_b200.ops import hstu_cuda
+  return _JaggedSoftmaxFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), seq_offsets, max_seq_len,
+                                causal, scale)
 
 
 def _kernel_ok(q, L: int) -> bool:

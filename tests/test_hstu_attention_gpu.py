@@ -109,3 +109,24 @@ def test_sampled_softmax_kernel_matches_torch():
   (loss_r * 3.0).backward()
   torch.testing.assert_close(a[0].grad, r[0].grad, rtol=1e-3, atol=1e-5)
   torch.testing.assert_close(a[1].grad.float(), r[1].grad, rtol=2e-2, atol=1e-5)
+
+
+def test_attention_accepts_column_slices_of_a_fused_projection():
+  """q, k, v handed over as views into one [T, 4, H, Dh] buffer give the same output and gradients."""
+  import torch
+  from recml_b200.ops import hstu_attention as A
+  torch.manual_seed(0)
+  T, H, Dh, N = 300, 2, 64, 256
+  offs = torch.tensor([0, 130, 300], dtype=torch.int32, device="cuda")
+  fused = (torch.randn(T, 4, H, Dh, device="cuda") * 0.5).to(torch.bfloat16)
+  outs = []
+  for strided in (True, False):
+    leaf = fused.clone().requires_grad_()
+    _, q, k, v = leaf.unbind(dim=1)
+    if not strided:
+      q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = A.jagged_pointwise_attention(q, k, v, offs, N, causal=True, scale=0.125)
+    o.backward(torch.ones_like(o) * 0.01)
+    outs.append((o.detach().float(), leaf.grad.float()))
+  torch.testing.assert_close(outs[0][0], outs[1][0], rtol=0, atol=0)
+  torch.testing.assert_close(outs[0][1], outs[1][1], rtol=1e-2, atol=1e-4)
