@@ -7,6 +7,10 @@
 //   unpack  waits for flag B from every peer, converts `out` back into the fp32 gradient tensors
 // Traffic per rank: (W-1)/W of the bucket in and the same out — the two-shot optimum, at full
 // NVSwitch bandwidth to all peers at once.  Flags are sequence numbers; waits are bounded.
+// When the symmetric buffers are bound to an NVLink multicast object the reduce step instead issues
+// `multimem.ld_reduce` (the switch sums the W copies of the slice, fp32 accumulation) and
+// `multimem.st` (the switch stores the result into every rank's `out`), so each rank moves only
+// 1/W of the bucket in and out over its own links.
 #include "common.cuh"
 
 namespace recml {
@@ -36,6 +40,8 @@ struct Comm {
   long long total;                     // bucket elements, multiple of 8*W
   float scale;
   int* status;
+  __nv_bfloat16* mc_in;                // multicast address of `in` (nullptr: plain peer loads / stores)
+  __nv_bfloat16* mc_out;
 };
 
 __device__ __forceinline__ void signal_all(unsigned int* done_counter, unsigned long long* const* flags, int W,
@@ -78,6 +84,38 @@ __global__ void __launch_bounds__(256) pack_kernel(const Bucket b, const Comm c)
                                                     pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
   }
   signal_all(c.done_counter, c.flag_a, c.W, seq_of(c.seq));
+}
+
+// In-switch reduction of one 16-byte vector of bf16 pairs over all ranks bound to the multicast object.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+// One 16-byte store that the switch replicates into every bound rank's copy.
+__device__ __forceinline__ void multimem_st_16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               :: "l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__global__ void __launch_bounds__(256) reduce_nvls_kernel(const Comm c) {
+  const unsigned long long seq = seq_of(c.seq);
+  if (!wait_all(c.my_flag_a, c.W, seq, c.status, 8)) return;
+  const long long slice = c.total / c.W;
+  const long long lo = slice * c.me;
+  const long long nvec = slice / 8;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = lo + v * 8;
+    const uint4 t = multimem_ld_reduce_bf16x8(c.mc_in + e);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16(bf16_lo(w[j]) * c.scale, bf16_hi(w[j]) * c.scale);
+    multimem_st_16(c.mc_out + e, make_uint4(o[0], o[1], o[2], o[3]));
+  }
+  signal_all(c.done_counter + 1, c.flag_b, c.W, seq);
 }
 
 __global__ void __launch_bounds__(256) reduce_kernel(const Comm c) {
@@ -145,7 +183,10 @@ extern "C" int recml_allreduce_bucket(const Bucket* b, const Comm* c, cudaStream
   const long long nvec = c->total / c->W / 8;
   int rb = static_cast<int>((nvec + 255) / 256);
   rb = rb < 1 ? 1 : (rb > 592 ? 592 : rb);
-  reduce_kernel<<<rb, 256, 0, stream>>>(*c);
+  if (c->mc_in != nullptr && c->mc_out != nullptr && c->W > 1)
+    reduce_nvls_kernel<<<rb, 256, 0, stream>>>(*c);
+  else
+    reduce_kernel<<<rb, 256, 0, stream>>>(*c);
   unpack_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(*b, *c);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

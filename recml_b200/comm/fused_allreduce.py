@@ -34,12 +34,16 @@ class _Comm(ctypes.Structure):
   _fields_ = [("inp", c_vp * MAXW), ("out", c_vp * MAXW), ("flag_a", c_vp * MAXW), ("flag_b", c_vp * MAXW),
               ("my_flag_a", c_vp), ("my_flag_b", c_vp), ("done_counter", c_vp), ("W", ctypes.c_int),
               ("me", ctypes.c_int), ("seq", _SeqRef), ("total", c_ll), ("scale", ctypes.c_float),
-              ("status", c_vp)]
+              ("status", c_vp), ("mc_in", c_vp), ("mc_out", c_vp)]
 
 
 class FusedNvlinkReducer:
-  def __init__(self, group, device: torch.device, bucket_elems: int = 8 << 20, average: bool = True):
+  def __init__(self, group, device: torch.device, bucket_elems: int = 8 << 20, average: bool = True,
+               use_nvls: bool | None = None):
     self.group, self.device = group, device
+    # in-switch reduction whenever the symmetric buffer has a multicast mapping, unless switched off
+    # (RECML_NVLS=0, or NCCL_NVLS_ENABLE=0 so that one variable turns NVLS off in every library of a job)
+    self.use_nvls = symm.nvls_enabled() if use_nvls is None else bool(use_nvls)
     self.world = dist.get_world_size(group)
     self.rank = dist.get_rank(group)
     if self.world > MAXW:
@@ -144,6 +148,9 @@ class FusedNvlinkReducer:
     c.seq = _SeqRef(self.calls_dev.data_ptr(), 64, k, 0)
     c.scale = 1.0 / self.world if self.average else 1.0
     c.status = self.status.data_ptr()
+    if self.use_nvls and self.buf.multicast_ptr:
+      c.mc_in = self.buf.multicast_ptr + self.in_off[par]
+      c.mc_out = self.buf.multicast_ptr + self.out_off[par]
     with torch.cuda.stream(self.side):
       _lib.check_rc(self.lib.recml_allreduce_bucket(ctypes.byref(b), ctypes.byref(c),
                                                     ctypes.c_void_p(self.side.cuda_stream)), "allreduce_bucket")

@@ -37,6 +37,11 @@ def available(group=None) -> bool:
   return _symm_module() is not None and os.environ.get("RECML_DISABLE_SYMM", "0") != "1"
 
 
+def nvls_enabled() -> bool:
+  """Whether kernels may use `multimem` instructions on buffers that have a multicast mapping."""
+  return os.environ.get("RECML_NVLS", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+
+
 class SymmBuffer:
   """`nbytes` of device memory on every rank, addressable from every rank.
 
@@ -69,11 +74,15 @@ class SymmBuffer:
     self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
     self.local.zero_()
     self.handle = symm_mem.rendezvous(self.local, name)
-    self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+    ptrs = [int(p) for p in self.handle.buffer_ptrs]
+    # the handle reports the bases of the exported blocks; the tensor normally starts at its block's base
+    shift = self.local.data_ptr() - ptrs[self.rank]
+    self.ptrs = [p + shift for p in ptrs]
     try:
-      self.multicast_ptr = int(self.handle.multicast_ptr or 0)
+      mc = int(self.handle.multicast_ptr or 0)
     except Exception:  # pylint: disable=broad-except
-      self.multicast_ptr = 0
+      mc = 0
+    self.multicast_ptr = mc + shift if mc else 0
     torch.cuda.synchronize()
     dist.barrier(group=group)
 

@@ -92,14 +92,17 @@ def sharded_embedding_steps(rank, world, device_type, backend_name, placements, 
   return {"outs": outs, "tables": tables}
 
 
-def allreduce_grads(rank, world, device_type, sizes):
-  """Fused NVLink reducer (CUDA) / flat-bucket reducer (CPU) vs a plain all_reduce mean."""
+def allreduce_grads(rank, world, device_type, sizes, nvls=None):
+  """Fused NVLink reducer (CUDA) / flat-bucket reducer (CPU) vs a plain all_reduce mean.  `nvls`
+  forces the in-switch (`multimem`) reduce step on or off; None keeps the default."""
   from recml_b200.comm import grad_reducer
   device = torch.device("cuda", rank) if device_type == "cuda" else torch.device("cpu")
   gen = torch.Generator().manual_seed(17 + rank)
   params = [torch.zeros(s, device=device, requires_grad=True) for s in sizes]
   results = []
   red = grad_reducer.make_reducer(None, device)
+  if nvls is not None and hasattr(red, "use_nvls"):
+    red.use_nvls = bool(nvls)
   for it in range(3):
     for p in params:
       p.grad = torch.randn(p.shape, generator=gen).to(device)
@@ -112,10 +115,23 @@ def allreduce_grads(rank, world, device_type, sizes):
     if device.type == "cuda":
       torch.cuda.synchronize()
     results.append(max(float((p.grad - r).abs().max() / (r.abs().max() + 1e-6)) for p, r in zip(params, ref)))
+  ms = None
   if device.type == "cuda":
     from recml_b200.ops import _lib
     _lib.check_status(device)
-  return {"max_rel_err": results, "reducer": type(red).__name__}
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(10):
+      red.average_grads(params)
+    ev[1].record()
+    torch.cuda.synchronize()
+    _lib.check_status(device)
+    ms = ev[0].elapsed_time(ev[1]) / 10
+  buf = getattr(red, "buf", None)
+  return {"max_rel_err": results, "reducer": type(red).__name__, "ms": ms,
+          "multicast": bool(buf is not None and buf.multicast_ptr), "nvls": getattr(red, "use_nvls", False)}
 
 
 def dlrm_tiny_training(rank, world, device_type, steps, use_graph=False):

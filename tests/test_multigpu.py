@@ -27,10 +27,14 @@ def test_fused_embedding_two_gpus(placements, opt):
     torch.testing.assert_close(res[0]["tables"][name], t, atol=5e-3, rtol=5e-3)
 
 
-def test_fused_allreduce_two_gpus():
-  res = dist_utils.run_ranks("allreduce_grads", 2, "nccl", "cuda", [(333, 77), (5,), (100000,), (1, 9)])
+@pytest.mark.parametrize("nvls", [False, True])
+def test_fused_allreduce_two_gpus(nvls):
+  """Peer-load two-shot reduce and the in-switch `multimem` reduce (taken only when the symmetric
+  buffer has a multicast mapping) against NCCL's all-reduce."""
+  res = dist_utils.run_ranks("allreduce_grads", 2, "nccl", "cuda", [(333, 77), (5,), (100000,), (1, 9), (2048, 2048)], nvls)
   assert res[0]["reducer"] == "FusedNvlinkReducer"
   assert all(e < 1e-2 for r in res for e in r["max_rel_err"]), res   # bf16 wire format
+  print("fused all-reduce", {k: res[0][k] for k in ("nvls", "multicast", "ms")})
 
 
 def test_dlrm_tiny_two_gpus():
