@@ -527,6 +527,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // timestamps), so equal-bucket runs are summed in a register and flushed with one atomic
       int run_bucket = -1;
       float run_sum = 0.f;
+      float dacc = 0.f;
       {
         uint32_t sv[32], dpv[32];
         tmem_ld32(tmem_s + lane_off + cb * 32, sv);
@@ -551,7 +552,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             if (p.softmax) {
               // P = exp(x - lse);  dS = P * (dP - delta)
               const float pv = visible ? __expf(x - lse_r) : 0.f;
-              ds = pv * (__uint_as_float(dpv[e + u]) - delta_r);
+              ds = visible ? pv * (__uint_as_float(dpv[e + u]) - delta_r) : 0.f;
               pr[u] = pv;
             } else {
               const float sig = sigmoid_fast(x);
@@ -559,8 +560,19 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               pr[u] = visible ? x * sig * p.inv_n : 0.f;
             }
             dr[u] = ds;
-            // diagonal bin (kj - qi) - (kv0 - q0) + 127: lanes of a warp hit distinct bins
-            if (p.dpos_w != nullptr && visible) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + col - r + 127), ds);
+            // Position-bias gradient.  This lane's element lies on diagonal (col - lane) of the warp's
+            // 32x32 block; the partial sum of a diagonal travels one lane up per column, so every lane
+            // adds its element to the sum that is passing through it.  The diagonal leaving lane 31 is
+            // complete and goes to the shared histogram (bin = (kj - qi) - (kv0 - q0) + 127); the 32
+            // diagonals still in flight after the last column are flushed below.
+            if (p.dpos_w != nullptr) {
+              dacc += ds;
+              if (col < 31) {
+                if (lane == 31) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + col - r + 127), dacc);
+                const float below = __shfl_sync(0xffffffffu, dacc, (lane + 31) & 31);
+                dacc = lane == 0 ? 0.f : below;
+              }
+            }
             if (p.dts_w != nullptr && visible) {
               if (bucket != run_bucket) {
                 if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
@@ -582,7 +594,19 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
         }
       }
-      if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
+      if (p.dpos_w != nullptr) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + 31 - r + 127), dacc);
+      if (p.dts_w != nullptr) {
+        // far from the diagonal a whole 32x32 block usually falls into one bucket: one atomic per warp
+        const int b0 = __shfl_sync(0xffffffffu, run_bucket, 0);
+        if (__all_sync(0xffffffffu, run_bucket == b0)) {
+          float s = run_sum;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (lane == 0 && b0 >= 0) atomicAdd(hist + 512 + b0, s);
+        } else if (run_bucket >= 0) {
+          atomicAdd(hist + 512 + run_bucket, run_sum);
+        }
+      }
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(bar(6));
