@@ -134,3 +134,19 @@ def test_fused_optimizer_matches_cpu(factory):
     oc.step(); og.step()
   for k in pc:
     torch.testing.assert_close(pg[k].detach().cpu(), pc[k].detach(), atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("shape,ld", [((1000, 1024), 1024), ((777, 128), 384), ((513, 72), 72), ((300, 50), 50),
+                                      ((4100, 264), 520)])
+def test_colsum_matches_fp32_sum(shape, ld):
+  """Bias-gradient column sums: the 16-byte path (N % 8 == 0) and the generic one, dense and row-strided."""
+  M, N = shape
+  torch.manual_seed(3)
+  full = torch.randn(M, ld, device="cuda").to(torch.bfloat16)
+  x = full[:, :N]
+  got = ew.colsum(x)
+  want = x.float().sum(0)
+  torch.testing.assert_close(got, want, atol=2e-3 * M ** 0.5, rtol=1e-4)
+  # accumulation into an existing vector
+  again = ew.colsum(x, out=got.clone())
+  torch.testing.assert_close(again, 2 * want, atol=4e-3 * M ** 0.5, rtol=1e-4)
