@@ -36,7 +36,7 @@ enum Epilogue : int {
   kEpiCross = 1,     // V = acc + bias (optional store to out2); D = aux0 * V + aux1
   kEpiMaskRelu = 2,  // D = acc * (aux0 > 0)              (ReLU backward fused in dgrad)
   kEpiMulAdd = 3,    // D = acc * aux0 (+ aux1)           (DCN input-gradient paths)
-  kEpiAdd = 4,       // D = acc + aux0                    (residual / skip gradients)
+  kEpiAdd = 4,       // D = acc + aux0 (+ aux1)           (residual / skip gradients)
 };
 
 struct Params {
@@ -202,7 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t my_smem = epi_smem + quarter * 16384 + sub * 8192;
     uint8_t* st = epi_ptr + quarter * 16384 + sub * 8192;
     const uint32_t aux_bar = bars + 8u * (2 * C::kStages + 4 + quarter * 2 + sub);
-    const int n_aux = p.epi == kEpiLinear ? 0 : ((p.epi == kEpiCross || (p.epi == kEpiMulAdd && p.aux1 != nullptr)) ? 2 : 1);
+    const int n_aux = p.epi == kEpiLinear ? 0 : ((p.epi == kEpiCross || ((p.epi == kEpiMulAdd || p.epi == kEpiAdd) && p.aux1 != nullptr)) ? 2 : 1);
     const bool cross = p.epi == kEpiCross;
     auto slabs_of = [&](int tl) {
       const int rem = p.N - (tl % n_tiles) * BN;
@@ -296,6 +296,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     x[2 * j] += bf16_lo(a0w[j]);
                     x[2 * j + 1] += bf16_hi(a0w[j]);
                   }
+                  if (n_aux == 2) {
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(st + 4096 + chunk);
+                    const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      x[2 * j] += bf16_lo(a1w[j]);
+                      x[2 * j + 1] += bf16_hi(a1w[j]);
+                    }
+                  }
                 } else {  // kEpiMulAdd
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
@@ -382,6 +391,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int j = 0; j < 4; ++j) {
                   x[2 * j] += bf16_lo(a0w[j]);
                   x[2 * j + 1] += bf16_hi(a0w[j]);
+                }
+                if (p.aux1 != nullptr) {
+                  const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(p.aux1 + aoff + v * 8));
+                  const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w};
+  #pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    x[2 * j] += bf16_lo(a1w[j]);
+                    x[2 * j + 1] += bf16_hi(a1w[j]);
+                  }
                 }
               } else {  // kEpiMulAdd
   #pragma unroll

@@ -170,11 +170,12 @@ class CrossNetFn(torch.autograd.Function):
         dvs[i] = G.gemm(dv, u, a_mn=True, b_mn=True, out_dtype=torch.float32)       # [d, r]
         du = G.gemm(dv, v16, b_mn=True)                                             # [M, r]
         dus[i] = G.gemm(du, xl, a_mn=True, b_mn=True, out_dtype=torch.float32)      # [r, d]
-        g = G.gemm(du, u16, b_mn=True, epi=G.EPI_ADD, aux0=g)                       # dxl = du·U + g
+        # dxl = du·U + g; layer 0's xl IS x0, so its product also takes the accumulated dx0
+        g = G.gemm(du, u16, b_mn=True, epi=G.EPI_ADD, aux0=g, aux1=dx0 if i == 0 else None)
       else:
         dvs[i] = G.gemm(dv, xl, a_mn=True, b_mn=True, out_dtype=torch.float32)      # [d, d]
-        g = G.gemm(dv, v16, b_mn=True, epi=G.EPI_ADD, aux0=g)
-    dx0 = ew.add_bf16(dx0, g)   # layer 0's xl IS x0
+        g = G.gemm(dv, v16, b_mn=True, epi=G.EPI_ADD, aux0=g, aux1=dx0 if i == 0 else None)
+    dx0 = g
     if ctx.low_rank:
       return (dx0, None, None, *dus, *dvs, *dbs)
     return (dx0, None, None, *dvs, *dbs)

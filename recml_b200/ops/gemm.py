@@ -35,6 +35,8 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, relu=False, epi=E
     x = torch.where(aux0 > 0, x, torch.zeros_like(x))
   elif epi == EPI_ADD:
     x = x + aux0.to(torch.float32)
+    if aux1 is not None:
+      x = x + aux1.to(torch.float32)
   elif epi == EPI_MUL_ADD:
     x = x * aux0.to(torch.float32)
     if aux1 is not None:

@@ -60,3 +60,7 @@ def test_bias_relu_and_epilogues():
          G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_MASK_RELU, aux0=x0.cpu()).cuda())
   _check(G.gemm(a, b, epi=G.EPI_MUL_ADD, aux0=x0, aux1=xl),
          G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_MUL_ADD, aux0=x0.cpu(), aux1=xl.cpu()).cuda())
+  _check(G.gemm(a, b, epi=G.EPI_ADD, aux0=x0),
+         G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_ADD, aux0=x0.cpu()).cuda())
+  _check(G.gemm(a, b, epi=G.EPI_ADD, aux0=x0, aux1=xl),
+         G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_ADD, aux0=x0.cpu(), aux1=xl.cpu()).cuda())
