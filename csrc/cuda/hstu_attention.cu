@@ -54,15 +54,28 @@ struct Params {
 };
 
 // Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
-// position tile_row0[t].  Slots beyond the real number of tiles keep -1.
-__global__ void tile_list_kernel(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap) {
-  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+// position tile_row0[t].  Slots beyond the real number of tiles keep -1.  The list is ordered by
+// decreasing work so that the CTAs dispatched last are the short ones (under causal masking the
+// forward's query tile i visits i + 1 key tiles, the backward's key tile i visits n - i query
+// tiles): level w = max_n .. 1 lists, for every sequence with at least w tiles, the tile with w steps.
+__global__ void tile_list_kernel(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap, int backward) {
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  int max_n = 0;
+  for (int b = lane; b < B; b += 32) max_n = max(max_n, (seq_offsets[b + 1] - seq_offsets[b] + BQ - 1) / BQ);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) max_n = max(max_n, __shfl_xor_sync(0xffffffffu, max_n, o));
   int t = 0;
-  // longest-first within a sequence (late tiles see the most keys), sequences in order
-  for (int b = 0; b < B; ++b) {
-    const int L = seq_offsets[b + 1] - seq_offsets[b];
-    const int n = (L + BQ - 1) / BQ;
-    for (int i = n - 1; i >= 0 && t < cap; --i, ++t) { tile_seq[t] = b; tile_row0[t] = i * BQ; }
+  for (int w = max_n; w >= 1; --w) {
+    for (int b0 = 0; b0 < B; b0 += 32) {
+      const int b = b0 + lane;
+      const int n = b < B ? (seq_offsets[b + 1] - seq_offsets[b] + BQ - 1) / BQ : 0;
+      const bool has = n >= w;
+      const unsigned mask = __ballot_sync(0xffffffffu, has);
+      const int at = t + __popc(mask & ((1u << lane) - 1u));
+      if (has && at < cap) { tile_seq[at] = b; tile_row0[at] = (backward ? n - w : w - 1) * BQ; }
+      t += __popc(mask);
+    }
   }
 }
 
@@ -138,10 +151,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
   using S = Smem<DH>;
-  const int seq = p.tile_seq[blockIdx.x];
+  // CTAs are dispatched in linear block order; heads vary fastest so that this order follows the work-sorted list
+  const int lin = blockIdx.x + gridDim.x * blockIdx.y;
+  const int tile_id = lin / p.H;
+  const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;   // whole CTA leaves before touching barriers or tensor memory
-  const int h = blockIdx.y;
-  const int q0 = p.tile_row0[blockIdx.x];
+  const int h = lin % p.H;
+  const int q0 = p.tile_row0[tile_id];
   const int seq_start = p.seq_offsets[seq];
   const int L = p.seq_offsets[seq + 1] - seq_start;
   const int tok0 = seq_start + q0;
@@ -399,10 +415,12 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const Params p) {
   using S = SmemB<DH>;
-  const int seq = p.tile_seq[blockIdx.x];
+  const int lin = blockIdx.x + gridDim.x * blockIdx.y;   // heads fastest: dispatch order = work-sorted list order
+  const int tile_id = lin / p.H;
+  const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;
-  const int h = blockIdx.y;
-  const int kv0 = p.tile_row0[blockIdx.x];
+  const int h = lin % p.H;
+  const int kv0 = p.tile_row0[tile_id];
   const int seq_start = p.seq_offsets[seq];
   const int L = p.seq_offsets[seq + 1] - seq_start;
   const int n_q_total = (L + BQ - 1) / BQ;
@@ -691,10 +709,10 @@ using namespace recml::hstu;
 
 extern "C" int recml_hstu_struct_size() { return static_cast<int>(sizeof(Params)); }
 
-extern "C" int recml_hstu_tile_list(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap,
+extern "C" int recml_hstu_tile_list(const int* seq_offsets, int B, int* tile_seq, int* tile_row0, int cap, int backward,
                                     cudaStream_t stream) {
   cudaMemsetAsync(tile_seq, 0xFF, sizeof(int) * cap, stream);
-  tile_list_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, tile_seq, tile_row0, cap);
+  tile_list_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, tile_seq, tile_row0, cap, backward);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

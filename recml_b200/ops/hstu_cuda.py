@@ -57,17 +57,20 @@ def _ts32(timestamps):
   return _remember("ts32", timestamps, lambda: (timestamps - timestamps.min()).to(torch.int32).contiguous())
 
 
-def _tiles(seq_offsets: torch.Tensor, T: int):
-  return _remember(f"tiles{T}", seq_offsets, lambda: _make_tiles(seq_offsets, T))
+def _tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
+  """Work-sorted tile list of the batch (heaviest tiles first); the backward kernel, which walks key
+  tiles, has its own order."""
+  return _remember(f"tiles{T}{'b' if backward else 'f'}", seq_offsets, lambda: _make_tiles(seq_offsets, T, backward))
 
 
-def _make_tiles(seq_offsets: torch.Tensor, T: int):
+def _make_tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
   B = seq_offsets.numel() - 1
   cap = (T + 127) // 128 + B
   tile_seq = torch.empty(cap, dtype=torch.int32, device=seq_offsets.device)
   tile_row0 = torch.zeros(cap, dtype=torch.int32, device=seq_offsets.device)
   _lib.check_rc(_lib.cuda().recml_hstu_tile_list(_lib.ptr(seq_offsets), c_int(B), _lib.ptr(tile_seq),
-                                                 _lib.ptr(tile_row0), c_int(cap), _lib.stream()), "hstu_tile_list")
+                                                 _lib.ptr(tile_row0), c_int(cap), c_int(int(backward)),
+                                                 _lib.stream()), "hstu_tile_list")
   return tile_seq, tile_row0, cap
 
 
@@ -125,7 +128,7 @@ def backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, cau
   timestamps = _ts32(timestamps)
   pw = None if pos_w is None else pos_w.detach().float().contiguous()
   tw = None if ts_w is None else ts_w.detach().float().contiguous()
-  tiles = _tiles(seq_offsets, q.shape[0])
+  tiles = _tiles(seq_offsets, q.shape[0], backward=True)
   do = as_rows(do)
   dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
   dk, dv = (torch.empty(k.shape, dtype=k.dtype, device=k.device) for _ in range(2))
@@ -177,7 +180,7 @@ def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
 
 
 def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, scale):
-  tiles = _tiles(seq_offsets, q.shape[0])
+  tiles = _tiles(seq_offsets, q.shape[0], backward=True)
   do = as_rows(do)
   delta = (do.float() * out.float()).sum(-1).contiguous()          # [T, H]
   dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
