@@ -51,6 +51,12 @@ struct Params {
   const float* delta;         // [T, H] (backward)
   // row pitch in elements of q / k / v / dO when they are column slices of a wider matrix (0: H * Dh)
   int ld_q, ld_k, ld_v, ld_do;
+  // Time buckets of every (query tile, key tile) pair, computed once per batch because all heads, layers
+  // and both passes use the same ones: pair (qt, kt) of sequence s is the 128 x 128 uint8 block number
+  // pair_base[s] + (causal ? qt (qt + 1) / 2 + kt : qt * n_tiles(s) + kt).  Null: buckets are computed inline.
+  const unsigned char* bucket_cache;
+  const int* pair_base;       // [B + 1]
+  int cap_pairs;              // blocks the cache can hold; a sequence whose blocks would not fit computes inline
 };
 
 // Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
@@ -95,6 +101,59 @@ __device__ __forceinline__ int time_bucket(int dt, int num_buckets) {
   return b > num_buckets ? num_buckets : b;
 }
 
+__device__ __forceinline__ int pair_index(const Params& p, int seq, int n_tiles, int qt, int kt) {
+  return p.pair_base[seq] + (p.causal ? qt * (qt + 1) / 2 + kt : qt * n_tiles + kt);
+}
+// byte `col` of the 32 bucket bytes a thread holds for its row (col is a compile-time constant after unrolling)
+__device__ __forceinline__ int bucket_byte(const uint32_t (&w)[8], int col) { return (w[col >> 2] >> ((col & 3) * 8)) & 0xff; }
+
+// pair_base[s] = number of cached tile pairs of the sequences before s.
+__global__ void pair_base_kernel(const int* seq_offsets, int B, int causal, int* pair_base) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int acc = 0;
+  for (int b = 0; b < B; ++b) {
+    pair_base[b] = acc;
+    const int n = (seq_offsets[b + 1] - seq_offsets[b] + BQ - 1) / BQ;
+    acc += causal ? n * (n + 1) / 2 : n * n;
+  }
+  pair_base[B] = acc;
+}
+
+// One block per (query tile of the forward list, key tile): 256 threads, thread = (row, 64-column half).
+__global__ void __launch_bounds__(256) bucket_cache_kernel(const int* seq_offsets, const int* tile_seq, const int* tile_row0,
+                                                           const int* timestamps, const int* pair_base, int num_buckets,
+                                                           int causal, int cap_pairs, unsigned char* cache) {
+  const int seq = tile_seq[blockIdx.x];
+  if (seq < 0) return;
+  const int q0 = tile_row0[blockIdx.x], qt = q0 / BQ, kt = blockIdx.y;
+  const int seq_start = seq_offsets[seq];
+  const int L = seq_offsets[seq + 1] - seq_start;
+  const int nt = (L + BQ - 1) / BQ;
+  if (kt >= nt || (causal && kt > qt)) return;
+  const int pair = pair_base[seq] + (causal ? qt * (qt + 1) / 2 + kt : qt * nt + kt);
+  if (pair >= cap_pairs) return;
+  __shared__ int ts_k[BKV];
+  const int kv0 = kt * BKV;
+  if (threadIdx.x < BKV) ts_k[threadIdx.x] = (kv0 + threadIdx.x < L) ? timestamps[seq_start + kv0 + threadIdx.x] : 0;
+  __syncthreads();
+  const int r = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * 64;
+  const int qi = q0 + r;
+  const int tq = qi < L ? timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)] : 0;
+  unsigned char* dst = cache + (static_cast<size_t>(pair) << 14) + r * BKV + c0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t v = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) v |= static_cast<uint32_t>(time_bucket(tq - ts_k[c0 + g * 16 + j * 4 + b], num_buckets)) << (8 * b);
+      w[j] = v;
+    }
+    *reinterpret_cast<uint4*>(dst + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // Per-warp scratch in shared memory for the bias terms of one (query tile, key tile) pair: the 128 key
 // timestamps, the 160-entry window of the relative-position table the warp's 32 rows touch, and a copy
 // of the time-bucket table.  Only __syncwarp is needed to publish it.
@@ -102,6 +161,7 @@ struct WarpBias {      // a warp covers 32 rows x 32 columns of the score tile (
   int ts_k[64];
   float pos[96];
   float tsw[260];
+  float diag[32];      // backward: diagonals of the position-bias gradient completed by lane 31, one per column
 };
 
 // One lane polls the mbarrier, the result is broadcast: the whole warp takes the same branch, so warp-level
@@ -116,9 +176,9 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 
 // `kv0` here is the first key of the warp's columns.
 __device__ __forceinline__ void stage_bias(WarpBias& wb, const Params& p, int lane, int seq_start, int L, int kv0,
-                                           int q0, int quarter) {
+                                           int q0, int quarter, bool cached) {
   __syncwarp();
-  if (p.ts_w != nullptr) {
+  if (p.ts_w != nullptr && !cached) {
     for (int i = lane; i < 64; i += 32) wb.ts_k[i] = (kv0 + i < L) ? __ldg(p.timestamps + seq_start + kv0 + i) : 0;
   }
   if (p.pos_w != nullptr) {
@@ -256,6 +316,9 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
     int tq = 0;
     if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
+    const bool cached = p.ts_w != nullptr && p.bucket_cache != nullptr && L <= p.max_seq_len &&
+                        p.pair_base[seq + 1] <= p.cap_pairs;
+    const int n_tiles_seq = (L + BQ - 1) / BQ;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     float out_scale = 1.f;
@@ -322,7 +385,14 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int j = 0; j < n_kv && ok && !p.softmax; ++j) {
       const int kv0 = j * BKV + cb * 32;
       const int sb = j & 1;
-      stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter);
+      stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter, cached);
+      uint32_t bk[8];
+      if (cached) {
+        const uint4* bc = reinterpret_cast<const uint4*>(
+            p.bucket_cache + (static_cast<size_t>(pair_index(p, seq, n_tiles_seq, q0 / BQ, j)) << 14) + r * BKV + cb * 32);
+        const uint4 b0 = __ldg(bc), b1 = __ldg(bc + 1);
+        bk[0] = b0.x; bk[1] = b0.y; bk[2] = b0.z; bk[3] = b0.w; bk[4] = b1.x; bk[5] = b1.y; bk[6] = b1.z; bk[7] = b1.w;
+      }
       if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
       tc_fence_after();
       if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
@@ -340,7 +410,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             float x = __uint_as_float(v[e + u]) * p.scale;
             const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
             if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
-            if (p.ts_w != nullptr) x += wb.tsw[time_bucket(tq - wb.ts_k[col], p.num_buckets)];
+            if (p.ts_w != nullptr) x += wb.tsw[cached ? bucket_byte(bk, col) : time_bucket(tq - wb.ts_k[col], p.num_buckets)];
             pr[u] = visible ? silu(x) * p.inv_n : 0.f;
           }
           packed[e >> 1] = pack_bf16(pr[0], pr[1]);
@@ -526,6 +596,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
     if (p.ts_w != nullptr)
       for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
+    const bool cached = p.ts_w != nullptr && p.bucket_cache != nullptr && L <= p.max_seq_len &&
+                        p.pair_base[seq + 1] <= p.cap_pairs;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int q0 = (i_first + it) * BQ;
@@ -538,7 +610,14 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
         delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
       }
-      stage_bias(wb, p, lane, seq_start, L, kv0 + cb * 32, q0, quarter);
+      stage_bias(wb, p, lane, seq_start, L, kv0 + cb * 32, q0, quarter, cached);
+      uint32_t bk[8];
+      if (cached) {
+        const uint4* bc = reinterpret_cast<const uint4*>(
+            p.bucket_cache + (static_cast<size_t>(pair_index(p, seq, n_q_total, i_first + it, kv0 / BKV)) << 14) + r * BKV + cb * 32);
+        const uint4 b0 = __ldg(bc), b1 = __ldg(bc + 1);
+        bk[0] = b0.x; bk[1] = b0.y; bk[2] = b0.z; bk[3] = b0.w; bk[4] = b1.x; bk[5] = b1.y; bk[6] = b1.z; bk[7] = b1.w;
+      }
       if (!warp_wait(bar(5), it & 1, abortp, p.status, 55, lane)) { ok = false; break; }
       tc_fence_after();
       // time-bucket gradient: along a row the bucket changes rarely (log-spaced buckets, increasing
@@ -563,7 +642,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             int bucket = 0;
             if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
             if (p.ts_w != nullptr) {
-              bucket = time_bucket(tq - wb.ts_k[col], p.num_buckets);
+              bucket = cached ? bucket_byte(bk, col) : time_bucket(tq - wb.ts_k[col], p.num_buckets);
               x += wb.tsw[bucket];
             }
             float ds;
@@ -581,12 +660,12 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             // Position-bias gradient.  This lane's element lies on diagonal (col - lane) of the warp's
             // 32x32 block; the partial sum of a diagonal travels one lane up per column, so every lane
             // adds its element to the sum that is passing through it.  The diagonal leaving lane 31 is
-            // complete and goes to the shared histogram (bin = (kj - qi) - (kv0 - q0) + 127); the 32
-            // diagonals still in flight after the last column are flushed below.
+            // complete and is parked in the warp's scratch; after the last column those 31 and the 32
+            // diagonals still in flight go to the shared histogram (bin = (kj - qi) - (kv0 - q0) + 127).
             if (p.dpos_w != nullptr) {
               dacc += ds;
               if (col < 31) {
-                if (lane == 31) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + col - r + 127), dacc);
+                if (lane == 31) wb.diag[col] = dacc;
                 const float below = __shfl_sync(0xffffffffu, dacc, (lane + 31) & 31);
                 dacc = lane == 0 ? 0.f : below;
               }
@@ -612,7 +691,12 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
         }
       }
-      if (p.dpos_w != nullptr) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + 31 - r + 127), dacc);
+      if (p.dpos_w != nullptr) {
+        atomicAdd(hist + (it & 1) * 256 + (cb * 32 + 31 - r + 127), dacc);
+        __syncwarp();
+        // the diagonals that left lane 31 at columns 0..30 (row quarter * 32 + 31)
+        if (lane < 31) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + lane - (quarter * 32 + 31) + 127), wb.diag[lane]);
+      }
       if (p.dts_w != nullptr) {
         // far from the diagonal a whole 32x32 block usually falls into one bucket: one atomic per warp
         const int b0 = __shfl_sync(0xffffffffu, run_bucket, 0);
@@ -713,6 +797,20 @@ extern "C" int recml_hstu_tile_list(const int* seq_offsets, int B, int* tile_seq
                                     cudaStream_t stream) {
   cudaMemsetAsync(tile_seq, 0xFF, sizeof(int) * cap, stream);
   tile_list_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, tile_seq, tile_row0, cap, backward);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Fills pair_base [B + 1] and the bucket blocks of every tile pair the kernels will visit.  `tile_seq` /
+// `tile_row0` are the forward tile list (capacity n_tiles); cap_pairs bounds the blocks `cache` can hold.
+extern "C" int recml_hstu_bucket_cache(const int* seq_offsets, int B, const int* tile_seq, const int* tile_row0, int n_tiles,
+                                       const int* timestamps, int num_buckets, int causal, int max_tiles_per_seq,
+                                       int* pair_base, unsigned char* cache, int cap_pairs, cudaStream_t stream) {
+  if (B <= 0 || n_tiles <= 0 || max_tiles_per_seq <= 0) return 0;
+  if (num_buckets + 1 > 256) return -11;
+  pair_base_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, causal, pair_base);
+  dim3 grid(n_tiles, max_tiles_per_seq);
+  bucket_cache_kernel<<<grid, 256, 0, stream>>>(seq_offsets, tile_seq, tile_row0, timestamps, pair_base, num_buckets, causal,
+                                                cap_pairs, cache);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -16,7 +16,8 @@ class _Params(ctypes.Structure):
               ("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("timestamps", c_vp),
               ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
               ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("softmax", c_int), ("lse", c_vp),
-              ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int)]
+              ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int),
+              ("bucket_cache", c_vp), ("pair_base", c_vp), ("cap_pairs", c_int)]
 
 
 _ok: bool | None = None
@@ -38,13 +39,16 @@ _memo: dict[str, tuple] = {}
 
 
 def _remember(kind: str, src: torch.Tensor, make):
-  key = (id(src), src.data_ptr(), src._version, tuple(src.shape))
+  """One remembered value per kind, valid while `src` keeps its storage, shape and version.  The entry
+  holds `src` itself, so its storage cannot be handed to another tensor in the meantime: a tensor object
+  with the same address, layout and version counter is an alias of it (autograd hands the backward pass
+  such aliases of what the forward saved)."""
+  key = (src.data_ptr(), src._version, tuple(src.shape), tuple(src.stride()), src.dtype)
   hit = _memo.get(kind)
-  if hit is not None and hit[0] == key and hit[1]() is src:
+  if hit is not None and hit[0] == key:
     return hit[2]
-  import weakref
   val = make()
-  _memo[kind] = (key, weakref.ref(src), val)
+  _memo[kind] = (key, src, val)
   return val
 
 
@@ -74,6 +78,38 @@ def _make_tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
   return tile_seq, tile_row0, cap
 
 
+BUCKET_CACHE_MAX_BYTES = 1 << 30
+
+
+def _bucket_cache(seq_offsets, ts32, T: int, max_seq_len: int, num_buckets: int, causal: bool):
+  """Time-bucket indices of every (query tile, key tile) pair of the batch as uint8 blocks of 128 x 128,
+  computed once per batch: all heads, all layers and both passes read the same ones.  Returns
+  (cache, pair_base, cap_pairs) or None when the blocks would not fit the size limit (the kernels then
+  compute the buckets inline)."""
+  if ts32 is None or num_buckets + 1 > 256:
+    return None
+  B = seq_offsets.numel() - 1
+  cap = (T + 127) // 128 + B
+  max_nt = (max_seq_len + 127) // 128
+  cap_pairs = cap * ((max_nt + 2) // 2 if causal else max_nt)
+  if cap_pairs * 16384 > BUCKET_CACHE_MAX_BYTES:
+    return None
+
+  def make():
+    tiles = _tiles(seq_offsets, T)
+    cache = torch.empty(cap_pairs * 16384, dtype=torch.uint8, device=seq_offsets.device)
+    pair_base = torch.empty(B + 1, dtype=torch.int32, device=seq_offsets.device)
+    _lib.check_rc(_lib.cuda().recml_hstu_bucket_cache(
+        _lib.ptr(seq_offsets), c_int(B), _lib.ptr(tiles[0]), _lib.ptr(tiles[1]), c_int(tiles[2]), _lib.ptr(ts32),
+        c_int(num_buckets), c_int(int(causal)), c_int(max_nt), _lib.ptr(pair_base), _lib.ptr(cache), c_int(cap_pairs),
+        _lib.stream()), "hstu_bucket_cache")
+    return cache, pair_base, cap_pairs, seq_offsets   # the offsets the blocks were made for stay alive with them
+
+  hit = _remember(f"buckets{T}_{max_seq_len}_{num_buckets}_{int(causal)}", ts32, make)
+  same = hit[3] is seq_offsets or (hit[3].data_ptr() == seq_offsets.data_ptr() and hit[3]._version == seq_offsets._version)
+  return hit if same else None
+
+
 def rows_ok(t: torch.Tensor) -> bool:
   """`[T, H, Dh]` bf16 whose heads are contiguous and whose rows start on 16-byte boundaries: a plain tensor
   or a column slice of a wider matrix (e.g. one of the u|q|k|v blocks of a fused projection)."""
@@ -101,6 +137,10 @@ def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale,
   p.pos_w = pos_w.data_ptr() if pos_w is not None else None
   p.ts_w = ts_w.data_ptr() if (ts_w is not None and timestamps is not None) else None
   p.status = _lib.status_buffer(q.device).data_ptr()
+  if p.ts_w is not None:
+    bc = _bucket_cache(seq_offsets, timestamps, T, max_seq_len, p.num_buckets, bool(causal))
+    if bc is not None:
+      p.bucket_cache, p.pair_base, p.cap_pairs = bc[0].data_ptr(), bc[1].data_ptr(), bc[2]
   return p
 
 
