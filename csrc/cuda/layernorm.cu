@@ -104,6 +104,105 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ dy, c
   }
 }
 
+// bf16 backward with 16-byte accesses for D % 8 == 0, D <= 256 * NCH: lane l owns columns
+// [c * 256 + 8 l, c * 256 + 8 l + 8) of chunk c.  The dw / db partial sums of a block's 8 warps meet in
+// shared memory, so the global atomics are one per column per block.
+template <int NCH>
+__global__ void __launch_bounds__(256) ln_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ gate, const float* __restrict__ w,
+                                                         const float* __restrict__ b, const float* __restrict__ stats,
+                                                         __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dgate,
+                                                         float* __restrict__ dw, float* __restrict__ db, long long M, int D,
+                                                         int rms, int rows_per_warp) {
+  __shared__ float red[8][2][NCH * 256];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long r0 = warp * rows_per_warp;
+  float aw[NCH][8], ab[NCH][8], wv[NCH][8], bv[NCH][8];
+  bool act[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    act[c] = col < D;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      aw[c][j] = 0.f; ab[c][j] = 0.f;
+      wv[c][j] = act[c] ? w[col + j] : 0.f;
+      bv[c][j] = (act[c] && b != nullptr) ? b[col + j] : 0.f;
+    }
+  }
+  const float inv_d = 1.f / D;
+  for (long long row = r0; row < min(M, r0 + rows_per_warp); ++row) {
+    const float mean = stats[2 * row], rstd = stats[2 * row + 1];
+    float xh[NCH][8], d[NCH][8], d0[NCH][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (!act[c]) continue;
+      const long long off = row * D + c * 256 + lane * 8;
+      const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + off));
+      const uint4 dv = __ldg(reinterpret_cast<const uint4*>(dy + off));
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, dwv[4] = {dv.x, dv.y, dv.z, dv.w};
+      uint32_t gw[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};   // bf16 ones
+      if (gate != nullptr) {
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate + off));
+        gw[0] = gv.x; gw[1] = gv.y; gw[2] = gv.z; gw[3] = gv.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xh[c][2 * j] = (bf16_lo(xw[j]) - mean) * rstd;
+        xh[c][2 * j + 1] = (bf16_hi(xw[j]) - mean) * rstd;
+        d0[c][2 * j] = bf16_lo(dwv[j]);
+        d0[c][2 * j + 1] = bf16_hi(dwv[j]);
+        d[c][2 * j] = d0[c][2 * j] * bf16_lo(gw[j]);
+        d[c][2 * j + 1] = d0[c][2 * j + 1] * bf16_hi(gw[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float dyh = d[c][j] * wv[c][j];
+        s1 += dyh; s2 += dyh * xh[c][j];
+      }
+    }
+    s1 = wsum(s1) * inv_d; s2 = wsum(s2) * inv_d;
+    if (rms) s1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (!act[c]) continue;
+      const long long off = row * D + c * 256 + lane * 8;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = rstd * (d[c][j] * wv[c][j] - s1 - xh[c][j] * s2);
+        aw[c][j] += d[c][j] * xh[c][j];
+        ab[c][j] += d[c][j];
+      }
+      *reinterpret_cast<uint4*>(dx + off) =
+          make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+      if (dgate != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = d0[c][j] * (xh[c][j] * wv[c][j] + bv[c][j]);
+        *reinterpret_cast<uint4*>(dgate + off) =
+            make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      red[wib][0][c * 256 + lane * 8 + j] = aw[c][j];
+      red[wib][1][c * 256 + lane * 8 + j] = ab[c][j];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float sw = 0.f, sb = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { sw += red[q][0][i]; sb += red[q][1][i]; }
+    atomicAdd(dw + i, sw);
+    atomicAdd(db + i, sb);
+  }
+}
+
 }  // namespace ln
 }  // namespace recml
 
@@ -145,6 +244,23 @@ extern "C" int recml_layernorm_bwd(const void* dy, const void* x, const void* ga
                                    int D, int rms, int is_bf16, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (D > 1024) return -10;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) |
+                         reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dgate)) & 15) == 0;
+  if (is_bf16 && D % 8 == 0 && D <= 512 && aligned) {
+    using B = __nv_bfloat16;
+    const int rows_per_warp = M > 148LL * 64 * 4 ? 8 : 2;
+    const long long warps = (M + rows_per_warp - 1) / rows_per_warp;
+    const int blocks = static_cast<int>((warps + 7) / 8);
+    if (D <= 256)
+      ln_bwd_vec_kernel<1><<<blocks, 256, 0, stream>>>(static_cast<const B*>(dy), static_cast<const B*>(x), static_cast<const B*>(gate),
+                                                       w, b, stats, static_cast<B*>(dx), static_cast<B*>(dgate), dw, db, M, D, rms,
+                                                       rows_per_warp);
+    else
+      ln_bwd_vec_kernel<2><<<blocks, 256, 0, stream>>>(static_cast<const B*>(dy), static_cast<const B*>(x), static_cast<const B*>(gate),
+                                                       w, b, stats, static_cast<B*>(dx), static_cast<B*>(dgate), dw, db, M, D, rms,
+                                                       rows_per_warp);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   if (is_bf16) launch_bwd<__nv_bfloat16>(dy, x, gate, w, b, stats, dx, dgate, dw, db, M, D, rms, stream);
   else launch_bwd<float>(dy, x, gate, w, b, stats, dx, dgate, dw, db, M, D, rms, stream);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
