@@ -45,6 +45,60 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, co
   }
 }
 
+// bf16 forward with 16-byte accesses for D % 8 == 0, D <= 256 * NCH: the row stays in registers between the
+// statistics and the output, lane l owning columns [c * 256 + 8 l, + 8) of chunk c.
+template <int NCH>
+__global__ void __launch_bounds__(256) ln_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                                                         const float* __restrict__ w, const float* __restrict__ b,
+                                                         __nv_bfloat16* __restrict__ y, float* __restrict__ stats, long long M,
+                                                         int D, float eps, int rms) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float v[NCH][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    if (col < D) {
+      const uint4 t = __ldg(reinterpret_cast<const uint4*>(x + row * D + col));
+      const uint32_t tw[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { v[c][2 * j] = bf16_lo(tw[j]); v[c][2 * j + 1] = bf16_hi(tw[j]); }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[c][j]; ss += v[c][j] * v[c][j]; }
+    }
+  }
+  s = wsum(s); ss = wsum(ss);
+  const float mean = rms ? 0.f : s / D;
+  const float var = rms ? ss / D : fmaxf(ss / D - mean * mean, 0.f);
+  const float rstd = rsqrtf(var + eps);
+  if (lane == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    if (col < D) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + col)), w1 = __ldg(reinterpret_cast<const float4*>(w + col + 4));
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[c][j] - mean) * rstd * wv[j];
+      if (b != nullptr) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + col)), b1 = __ldg(reinterpret_cast<const float4*>(b + col + 4));
+        o[0] += b0.x; o[1] += b0.y; o[2] += b0.z; o[3] += b0.w; o[4] += b1.x; o[5] += b1.y; o[6] += b1.z; o[7] += b1.w;
+      }
+      if (gate != nullptr) {
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gate + row * D + col));
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { o[2 * j] *= bf16_lo(gw[j]); o[2 * j + 1] *= bf16_hi(gw[j]); }
+      }
+      *reinterpret_cast<uint4*>(y + row * D + col) =
+          make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+    }
+  }
+}
+
 // dx for y = g * (xhat * w + b):  let dyh = dy * g * w ;  dx = rstd * (dyh - mean(dyh) - xhat * mean(dyh * xhat))
 // (rms: the mean(dyh) term drops).  dgate = dy * (xhat * w + b).  Each warp walks `rows_per_warp`
 // rows and keeps its dw / db partial sums in registers (NPL columns per lane), so the global
@@ -213,6 +267,18 @@ extern "C" int recml_layernorm_fwd(const void* x, const void* gate, const float*
                                    cudaStream_t stream) {
   if (M <= 0) return 0;
   const int blocks = static_cast<int>((M * 32 + 255) / 256);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(y) |
+                         reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+  if (is_bf16 && D % 8 == 0 && D <= 1024 && aligned) {
+    using B = __nv_bfloat16;
+#define RECML_LNF(N) ln_fwd_vec_kernel<N><<<blocks, 256, 0, stream>>>(static_cast<const B*>(x), static_cast<const B*>(gate), w, b, \
+                                                                      static_cast<B*>(y), stats, M, D, eps, rms)
+    if (D <= 256) RECML_LNF(1);
+    else if (D <= 512) RECML_LNF(2);
+    else RECML_LNF(4);
+#undef RECML_LNF
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   if (is_bf16)
     ln_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
         static_cast<const __nv_bfloat16*>(gate), w, b, static_cast<__nv_bfloat16*>(y), stats, M, D, eps, rms);
