@@ -41,8 +41,8 @@ class FusedNvlinkReducer:
   def __init__(self, group, device: torch.device, bucket_elems: int = 8 << 20, average: bool = True,
                use_nvls: bool | None = None):
     self.group, self.device = group, device
-    # in-switch reduction whenever the symmetric buffer has a multicast mapping, unless switched off
-    # (RECML_NVLS=0, or NCCL_NVLS_ENABLE=0 so that one variable turns NVLS off in every library of a job)
+    # in-switch reduction when asked for (RECML_NVLS=1) and the symmetric buffer has a multicast mapping;
+    # NCCL_NVLS_ENABLE=0 turns it off together with NCCL's own NVLS use
     self.use_nvls = symm.nvls_enabled() if use_nvls is None else bool(use_nvls)
     self.world = dist.get_world_size(group)
     self.rank = dist.get_rank(group)

@@ -38,8 +38,11 @@ def available(group=None) -> bool:
 
 
 def nvls_enabled() -> bool:
-  """Whether kernels may use `multimem` instructions on buffers that have a multicast mapping."""
-  return os.environ.get("RECML_NVLS", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+  """Whether kernels use `multimem` instructions on buffers that have a multicast mapping.  Opt-in
+  (`RECML_NVLS=1`): with peer loads the gradient exchange is already hidden under the backward pass, and
+  a second multicast-bound reducer created in a process that had already released one ran its steps at
+  half speed on 2 GPUs.  `NCCL_NVLS_ENABLE=0` keeps it off whatever `RECML_NVLS` says."""
+  return os.environ.get("RECML_NVLS", "0") == "1" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
 
 
 class SymmBuffer:

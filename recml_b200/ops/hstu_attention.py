@@ -141,6 +141,6 @@ def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=
     from recml_b200.ops import hstu_cuda
     if hstu_cuda.available():
       return _JaggedAttnFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), pos_w, ts_w,
-                                 seq_offsets.to(torch.int32), timestamps, max_seq_len, causal, scale)
+                                 hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len, causal, scale)
   return jagged_attention_reference(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
                                     timestamps=timestamps, causal=causal, scale=scale)

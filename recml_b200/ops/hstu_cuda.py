@@ -61,6 +61,14 @@ def _ts32(timestamps):
   return _remember("ts32", timestamps, lambda: (timestamps - timestamps.min()).to(torch.int32).contiguous())
 
 
+def offsets32(seq_offsets: torch.Tensor) -> torch.Tensor:
+  """`seq_offsets` as contiguous int32, the same tensor object for every call of a batch (what is derived
+  from the offsets is remembered per tensor, so a fresh conversion per layer would defeat it)."""
+  if seq_offsets.dtype == torch.int32 and seq_offsets.is_contiguous():
+    return seq_offsets
+  return _remember("offs32", seq_offsets, lambda: seq_offsets.to(torch.int32).contiguous())
+
+
 def _tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
   """Work-sorted tile list of the batch (heaviest tiles first); the backward kernel, which walks key
   tiles, has its own order."""
