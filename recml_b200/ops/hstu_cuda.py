@@ -38,12 +38,13 @@ def available() -> bool:
 _memo: dict[str, tuple] = {}
 
 
-def _remember(kind: str, src: torch.Tensor, make):
-  """One remembered value per kind, valid while `src` keeps its storage, shape and version.  The entry
+def _remember(kind: str, src: torch.Tensor, make, extra: tuple = ()):
+  """One remembered value per kind (a fixed set of kinds, so the table cannot grow with the batches seen),
+  valid while `src` keeps its storage, shape and version and `extra` is unchanged.  The entry
   holds `src` itself, so its storage cannot be handed to another tensor in the meantime: a tensor object
   with the same address, layout and version counter is an alias of it (autograd hands the backward pass
   such aliases of what the forward saved)."""
-  key = (src.data_ptr(), src._version, tuple(src.shape), tuple(src.stride()), src.dtype)
+  key = (src.data_ptr(), src._version, tuple(src.shape), tuple(src.stride()), src.dtype, extra)
   hit = _memo.get(kind)
   if hit is not None and hit[0] == key:
     return hit[2]
@@ -72,7 +73,7 @@ def offsets32(seq_offsets: torch.Tensor) -> torch.Tensor:
 def _tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
   """Work-sorted tile list of the batch (heaviest tiles first); the backward kernel, which walks key
   tiles, has its own order."""
-  return _remember(f"tiles{T}{'b' if backward else 'f'}", seq_offsets, lambda: _make_tiles(seq_offsets, T, backward))
+  return _remember("tiles_b" if backward else "tiles_f", seq_offsets, lambda: _make_tiles(seq_offsets, T, backward), (T,))
 
 
 def _make_tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
@@ -113,7 +114,7 @@ def _bucket_cache(seq_offsets, ts32, T: int, max_seq_len: int, num_buckets: int,
         _lib.stream()), "hstu_bucket_cache")
     return cache, pair_base, cap_pairs, seq_offsets   # the offsets the blocks were made for stay alive with them
 
-  hit = _remember(f"buckets{T}_{max_seq_len}_{num_buckets}_{int(causal)}", ts32, make)
+  hit = _remember("buckets", ts32, make, (T, max_seq_len, num_buckets, bool(causal)))
   same = hit[3] is seq_offsets or (hit[3].data_ptr() == seq_offsets.data_ptr() and hit[3]._version == seq_offsets._version)
   return hit if same else None
 
