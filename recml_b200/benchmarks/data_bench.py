@@ -1,0 +1,68 @@
+"""Host input pipeline throughput (CPU only): TFRecord indexing + CRC check and `tf.Example` parsing of
+Criteo-shaped per-example records (1 label, 13 float features, 26 variable-length id features) by the
+native parser, one call per feature versus one pass for all features.
+
+  python -m recml_b200.benchmarks.data_bench [--examples N] [--threads T]
+
+Prints one JSON line.  The file is written to a temporary directory and removed afterwards.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import tempfile
+import time
+
+
+def run(examples: int = 20000, seed: int = 0) -> dict:
+  import numpy as np
+  from recml_b200.data import tfrecord
+  rng = np.random.default_rng(seed)
+  specs = ([("label", "int64", 1, 0)] + [(f"dense_{j}", "float", 1, 0.0) for j in range(13)] +
+           [(f"cat_{j}", "int64", 0, 0) for j in range(26)])
+  with tempfile.TemporaryDirectory() as d:
+    path = os.path.join(d, "examples.tfrecord")
+    recs = []
+    for _ in range(examples):
+      f = {"label": [int(rng.integers(0, 2))]}
+      for j in range(13):
+        f[f"dense_{j}"] = [float(rng.normal())]
+      for j in range(26):
+        f[f"cat_{j}"] = [int(x) for x in rng.integers(0, 1 << 30, int(rng.integers(1, 16)))]
+      recs.append(tfrecord.encode_example(f))
+    tfrecord.write_tfrecord(path, recs)
+    size = os.path.getsize(path)
+    t = time.perf_counter()
+    rf = tfrecord.RecordFile(path, verify=True)
+    t_index = time.perf_counter() - t
+    rows = np.arange(len(rf))
+    rf.parse_many(rows[:64], specs)                      # start the thread pool
+    t = time.perf_counter()
+    for name, dtype, fixed, default in specs:
+      rf.parse(rows, name, dtype, fixed, default)
+    t_each = time.perf_counter() - t
+    best = float("inf")
+    for _ in range(3):
+      t = time.perf_counter()
+      rf.parse_many(rows, specs)
+      best = min(best, time.perf_counter() - t)
+  return {"examples": examples, "file_mb": size / 1e6, "features": len(specs),
+          "index_crc_ms": t_index * 1e3, "index_crc_mb_per_s": size / 1e6 / t_index,
+          "per_feature_parse_examples_per_s": examples / t_each,
+          "one_pass_parse_examples_per_s": examples / best, "one_pass_mb_per_s": size / 1e6 / best,
+          "host_threads": int(os.environ.get("RECML_HOST_THREADS", os.cpu_count() or 1))}
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--examples", type=int, default=20000)
+  ap.add_argument("--threads", type=int, default=0, help="host threads of the native pool (0: all cores)")
+  args = ap.parse_args()
+  if args.threads > 0:
+    os.environ["RECML_HOST_THREADS"] = str(args.threads)
+  print(json.dumps(run(args.examples)))
+
+
+if __name__ == "__main__":
+  main()

@@ -116,6 +116,49 @@ class RecordFile:
     return vals, row_len
 
 
+  def parse_many(self, rows: np.ndarray, specs: Sequence[tuple]) -> dict:
+    """Parses several features of the given records in ONE pass over each record (the per-feature
+    `parse` walks a record's feature map once per call).  `specs`: (name, dtype, fixed_len, default)
+    tuples, fixed_len 0 for variable length.  Returns name -> dense `[n, fixed_len]` array, or
+    (values, row_lengths) for variable-length features."""
+    lib = _lib_host()
+    n, F = len(rows), len(specs)
+    offs = np.ascontiguousarray(self.offsets[rows])
+    lens = np.ascontiguousarray(self.lengths[rows])
+    kinds = [0 if dt in ("int64", "int") else 1 for _, dt, _, _ in specs]
+    names = (ctypes.c_char_p * F)(*[nm.encode() for nm, _, _, _ in specs])
+    c_kinds = (ctypes.c_int * F)(*kinds)
+    c_fixed = (ctypes.c_int * F)(*[int(fl) for _, _, fl, _ in specs])
+    c_di = (c_ll * F)(*[int(d) if k == 0 else 0 for (_, _, _, d), k in zip(specs, kinds)])
+    c_df = (ctypes.c_float * F)(*[float(d) if k == 1 else 0.0 for (_, _, _, d), k in zip(specs, kinds)])
+    dense, rowlen = {}, {}
+    c_dense, c_rows = (ctypes.c_void_p * F)(), (ctypes.c_void_p * F)()
+    for f, ((nm, _, fl, _), k) in enumerate(zip(specs, kinds)):
+      if fl > 0:
+        dense[f] = np.empty((n, fl), dtype=np.int64 if k == 0 else np.float32)
+        c_dense[f] = dense[f].ctypes.data
+      else:
+        rowlen[f] = np.zeros(n, dtype=np.int64)
+        c_rows[f] = rowlen[f].ctypes.data
+    lib.recml_parse_multi.restype = ctypes.c_void_p
+    lib.recml_parse_multi_size.restype = c_ll
+    handle = ctypes.c_void_p(lib.recml_parse_multi(
+        self.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
+        lens.ctypes.data_as(ctypes.c_void_p), c_ll(n), ctypes.c_int(F), names, c_kinds, c_fixed, c_di, c_df,
+        c_dense, c_rows))
+    out = {}
+    try:
+      for f, ((nm, _, fl, _), k) in enumerate(zip(specs, kinds)):
+        if fl > 0:
+          out[nm] = dense[f]
+          continue
+        vals = np.empty(int(lib.recml_parse_multi_size(handle, ctypes.c_int(f))), dtype=np.int64 if k == 0 else np.float32)
+        lib.recml_parse_multi_fetch(handle, ctypes.c_int(f), vals.ctypes.data_as(ctypes.c_void_p))
+        out[nm] = (vals, rowlen[f])
+    finally:
+      lib.recml_parse_multi_free(handle)
+    return out
+
   def parse_sequence(self, rows: np.ndarray, name: str, dtype: str):
     """Feature list `name` of tf.SequenceExample records: (values, values per record, steps per record);
     the values of a record's steps are concatenated in step order."""

@@ -108,13 +108,19 @@ class _RecordDataset:
 
   def _parse_features(self, rf: tfrecord.RecordFile, rows: np.ndarray) -> dict:
     out = {}
+    # every tf.Example feature in one pass over each record
+    specs = []
     for name, spec in self.fac.feature_spec.items():
       if isinstance(spec, FixedLenFeature):
-        n = int(np.prod(spec.shape)) if spec.shape else 1
-        arr = rf.parse(rows, name, spec.dtype, n, spec.default_value).reshape((len(rows),) + tuple(spec.shape))
-        out[name] = arr
+        specs.append((name, spec.dtype, int(np.prod(spec.shape)) if spec.shape else 1, spec.default_value))
       else:
-        vals, lens = rf.parse(rows, name, spec.dtype)
+        specs.append((name, spec.dtype, 0, 0))
+    parsed = rf.parse_many(rows, specs) if specs else {}
+    for name, spec in self.fac.feature_spec.items():
+      if isinstance(spec, FixedLenFeature):
+        out[name] = parsed[name].reshape((len(rows),) + tuple(spec.shape))
+      else:
+        vals, lens = parsed[name]
         out[name] = {"values": vals, "lengths": lens}
     for name, spec in (self.fac.sequence_feature_spec or {}).items():     # tf.SequenceExample feature lists
       vals, lens, steps = rf.parse_sequence(rows, name, spec.dtype)

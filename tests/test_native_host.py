@@ -161,3 +161,34 @@ def test_factory_filter_rebatch_interleave_and_sequence_examples(tmp_path):
                             shuffle=True, shuffle_buffer_size=7, prefetch_buffer_size=0, sharding_info=sharding)
   got = np.concatenate([b["id"] for b in fac3.make()])
   assert sorted(got.tolist()) == sorted(ids.tolist()) and got.tolist() != sorted(got.tolist())
+
+
+def test_parse_many_matches_per_feature_parse(tmp_path):
+  """One pass over each record for all features gives what one call per feature gives: fixed-length with
+  defaults and truncation, variable-length, features missing from some records, any request order."""
+  from recml_b200.data import tfrecord
+  rng = np.random.default_rng(5)
+  recs = []
+  for i in range(700):
+    f = {"label": [int(rng.integers(0, 2))], "d0": [float(rng.normal())], "d1": [float(x) for x in rng.normal(size=3)]}
+    if i % 3:
+      f["ids_a"] = [int(x) for x in rng.integers(0, 1 << 40, int(rng.integers(0, 9)))]
+    if i % 5:
+      f["ids_b"] = [int(x) for x in rng.integers(0, 100, int(rng.integers(1, 4)))]
+    f["w"] = [float(x) for x in rng.random(int(rng.integers(0, 5)))]
+    recs.append(tfrecord.encode_example(f))
+  path = str(tmp_path / "many.tfrecord")
+  tfrecord.write_tfrecord(path, recs)
+  rf = tfrecord.RecordFile(path)
+  rows = rng.permutation(len(rf))[:650]
+  specs = [("ids_b", "int64", 2, -1), ("w", "float", 0, 0), ("label", "int64", 1, 0), ("absent", "int64", 2, 7),
+           ("d1", "float", 2, 0.5), ("ids_a", "int64", 0, 0), ("d0", "float", 1, 0.0), ("gone", "float", 0, 0)]
+  many = rf.parse_many(rows, specs)
+  for name, dtype, fixed, default in specs:
+    if fixed:
+      np.testing.assert_array_equal(many[name], rf.parse(rows, name, dtype, fixed, default))
+    else:
+      vals, lens = rf.parse(rows, name, dtype)
+      np.testing.assert_array_equal(many[name][0], vals)
+      np.testing.assert_array_equal(many[name][1], lens)
+  assert (many["absent"] == 7).all() and many["gone"][0].size == 0
