@@ -79,4 +79,56 @@ int recml_read_chunks(int count, const char* const* paths, uint8_t* const* bufs,
   return failed.load();
 }
 
+// Writes bufs[i][0:sizes[i]] at file_offsets[i] of the EXISTING file paths[i] (the caller creates the
+// temporary files, splits large chunks into segments so that many threads write one file, and renames the
+// files once every segment is in).  Returns 0, or -(1+i) for the first item that failed.
+int recml_write_ranges(int count, const char* const* paths, const long long* file_offsets, const uint8_t* const* bufs,
+                       const long long* sizes) {
+  std::atomic<int> failed{0};
+  recml::ThreadPool::global().parallel_for(count, [&](long long i0, long long i1, int) {
+    for (long long i = i0; i < i1; ++i) {
+      const int fd = ::open(paths[i], O_WRONLY);
+      bool ok = fd >= 0;
+      long long put = 0;
+      while (ok && put < sizes[i]) {
+        const ssize_t r = ::pwrite(fd, bufs[i] + put, static_cast<size_t>(sizes[i] - put), file_offsets[i] + put);
+        if (r <= 0) ok = false; else put += r;
+      }
+      if (fd >= 0) ::close(fd);
+      if (!ok) {
+        int expected = 0;
+        failed.compare_exchange_strong(expected, static_cast<int>(-(1 + i)));
+      }
+    }
+  }, 1);
+  return failed.load();
+}
+
+// Reads sizes[i] bytes at file_offsets[i] of paths[i] into bufs[i]; a large chunk is read by several
+// items (one per segment) so that one file is read by many threads.  A short file fails, except that
+// allow_short lets an item end at the end of its file (the rest of the buffer is left as it is).
+int recml_read_ranges(int count, const char* const* paths, const long long* file_offsets, uint8_t* const* bufs,
+                      const long long* sizes, int allow_short) {
+  std::atomic<int> failed{0};
+  recml::ThreadPool::global().parallel_for(count, [&](long long i0, long long i1, int) {
+    for (long long i = i0; i < i1; ++i) {
+      const int fd = ::open(paths[i], O_RDONLY);
+      bool ok = fd >= 0;
+      long long got = 0;
+      while (ok && got < sizes[i]) {
+        const ssize_t r = ::pread(fd, bufs[i] + got, static_cast<size_t>(sizes[i] - got), file_offsets[i] + got);
+        if (r < 0) ok = false;
+        else if (r == 0) { ok = allow_short != 0; break; }
+        else got += r;
+      }
+      if (fd >= 0) ::close(fd);
+      if (!ok) {
+        int expected = 0;
+        failed.compare_exchange_strong(expected, static_cast<int>(-(1 + i)));
+      }
+    }
+  }, 1);
+  return failed.load();
+}
+
 }  // extern "C"

@@ -147,6 +147,9 @@ def read_region(path: str, start: Sequence[int] | None = None,
   start = [0] * nd if start is None else list(start)
   stop = list(shape) if stop is None else list(stop)
   out = np.empty([b - a for a, b in zip(start, stop)], dtype=dt)
+  if nd >= 1 and comp is None and _read_rows_native(path, shape, chunks, dt, start, stop, out):
+    t = torch.from_numpy(out)
+    return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd == 0:
     out = _read_chunk(path, [], [], dt, comp).reshape(())
   else:
@@ -164,6 +167,74 @@ def read_region(path: str, start: Sequence[int] | None = None,
       out[dst] = data[src]
   t = torch.from_numpy(np.ascontiguousarray(out))
   return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
+
+
+_SEGMENT_BYTES = 16 << 20
+
+
+def _write_raw_native(lib, items) -> None:
+  """Uncompressed chunks straight from the arrays' memory (no intermediate copy): each chunk goes to a
+  `.partial` file created at its final size, written in 16 MB segments by all host threads, then renamed."""
+  arrays = [np.ascontiguousarray(arr) for _, _, arr in items]       # kept alive until the write returns
+  finals = [os.path.join(path, chunk_name(index)) for path, index, _ in items]
+  segs = []
+  for arr, final in zip(arrays, finals):
+    tmp = final + ".partial"
+    with open(tmp, "wb") as f:
+      f.truncate(arr.nbytes)
+    base = arr.ctypes.data
+    for off in range(0, arr.nbytes, _SEGMENT_BYTES):
+      segs.append((tmp.encode(), off, base + off, min(_SEGMENT_BYTES, arr.nbytes - off)))
+  n = len(segs)
+  if n:
+    paths = (ctypes.c_char_p * n)(*[s[0] for s in segs])
+    offs = (ctypes.c_longlong * n)(*[s[1] for s in segs])
+    bufs = (ctypes.c_void_p * n)(*[s[2] for s in segs])
+    sizes = (ctypes.c_longlong * n)(*[s[3] for s in segs])
+    rc = lib.recml_write_ranges(ctypes.c_int(n), paths, offs, bufs, sizes)
+    if rc != 0:
+      raise IOError(f"native chunk write failed for {segs[-rc - 1][0].decode()}")
+  for final in finals:
+    os.rename(final + ".partial", final)
+
+
+def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> bool:
+  """Uncompressed arrays chunked along the first dimension only, whole rows requested: every chunk maps
+  to one contiguous piece of `out`, so the native reader fills `out` directly, many threads at once and
+  in segments of 16 MB (a table shard is one large chunk).  False: the caller takes the general path."""
+  nd = len(shape)
+  if any(chunks[d] != shape[d] or start[d] != 0 or stop[d] != shape[d] for d in range(1, nd)) or out.size == 0:
+    return False
+  try:
+    from recml_b200.ops import _lib
+    lib = _lib.host()
+  except Exception:  # pylint: disable=broad-except
+    return False
+  if lib is None or not hasattr(lib, "recml_read_ranges"):
+    return False
+  row_bytes = int(np.prod(shape[1:], dtype=np.int64)) * dt.itemsize if nd > 1 else dt.itemsize
+  a, b, c = start[0], stop[0], chunks[0]
+  items = []
+  for ci in range(a // c, (b - 1) // c + 1):
+    fpath = os.path.join(path, chunk_name([ci] + [0] * (nd - 1)))
+    if not os.path.exists(fpath):
+      raise FileNotFoundError(fpath)
+    lo, hi = max(a, ci * c), min(b, (ci + 1) * c, shape[0])
+    f_off, d_off, size = (lo - ci * c) * row_bytes, (lo - a) * row_bytes, (hi - lo) * row_bytes
+    if os.path.getsize(fpath) < f_off + size:
+      return False                      # clipped or foreign chunk layout
+    for seg in range(0, size, _SEGMENT_BYTES):
+      items.append((fpath.encode(), f_off + seg, d_off + seg, min(_SEGMENT_BYTES, size - seg)))
+  n = len(items)
+  base = out.ctypes.data
+  paths = (ctypes.c_char_p * n)(*[it[0] for it in items])
+  offs = (ctypes.c_longlong * n)(*[it[1] for it in items])
+  bufs = (ctypes.c_void_p * n)(*[base + it[2] for it in items])
+  sizes = (ctypes.c_longlong * n)(*[it[3] for it in items])
+  rc = lib.recml_read_ranges(ctypes.c_int(n), paths, offs, bufs, sizes, ctypes.c_int(0))
+  if rc != 0:
+    raise IOError(f"native chunk read failed for {items[-rc - 1][0].decode()}")
+  return True
 
 
 def _read_chunk(path, cidx, chunks, dt, comp) -> np.ndarray:
@@ -198,6 +269,9 @@ def write_chunks_parallel(items, compressor: str | None = None) -> None:
   if lib is None:
     for path, index, arr in items:
       write_chunk(path, index, arr, compressor)
+    return
+  if compressor is None and hasattr(lib, "recml_write_ranges"):
+    _write_raw_native(lib, items)
     return
   blobs = []
   for path, index, arr in items:

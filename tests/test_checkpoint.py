@@ -96,3 +96,27 @@ def test_checkpoints_iterator_sees_new_steps_and_stops_on_marker(tmp_path):
   seen = list(ckpt.checkpoints_iterator(str(tmp_path), timeout=0.5, timeout_fn=done.is_set, poll_secs=0.05))
   th.join()
   assert seen == [1, 2]
+
+
+def test_row_range_reads_match_general_path(tmp_path):
+  """The native reader (uncompressed arrays chunked along rows) returns what the chunk-by-chunk reader
+  returns for whole arrays and for row ranges that start and end inside chunks; a missing chunk file
+  still raises FileNotFoundError."""
+  import numpy as np
+  import pytest
+  from recml_b200.ckpt import zarr_io
+  rng = np.random.default_rng(0)
+  full = rng.normal(size=(1000, 24)).astype(np.float32)
+  path = str(tmp_path / "arr")
+  os.makedirs(path)
+  zarr_io.write_zarray(path, full.shape, (256, 24), "<f4", None)
+  items = [(path, [ci, 0], full[ci * 256:(ci + 1) * 256]) for ci in range(4)]
+  zarr_io.write_chunks_parallel(items)
+  for lo, hi in [(0, 1000), (100, 700), (255, 257), (512, 1000), (999, 1000)]:
+    got = zarr_io.read_region(path, [lo, 0], [hi, 24]).numpy()
+    np.testing.assert_array_equal(got, full[lo:hi])
+  cols = zarr_io.read_region(path, [10, 3], [20, 9]).numpy()      # not whole rows: general path
+  np.testing.assert_array_equal(cols, full[10:20, 3:9])
+  os.remove(os.path.join(path, "2.0"))
+  with pytest.raises(FileNotFoundError):
+    zarr_io.read_region(path, [0, 0], [1000, 24])
