@@ -73,7 +73,12 @@ uint32_t masked(uint32_t crc) { return ((crc >> 15) | (crc << 17)) + 0xa282ead8u
 
 struct Slice { const uint8_t* p; size_t n; };
 
-bool varint(Slice& s, uint64_t& v) {
+inline bool varint(Slice& s, uint64_t& v) {
+  if (s.n > 0 && !(*s.p & 0x80)) {      // keys and most lengths fit one byte
+    v = *s.p++;
+    --s.n;
+    return true;
+  }
   v = 0;
   for (int shift = 0; shift < 64 && s.n > 0; shift += 7) {
     const uint8_t b = *s.p++;
@@ -84,7 +89,7 @@ bool varint(Slice& s, uint64_t& v) {
   return false;
 }
 
-bool field(Slice& s, uint32_t& num, uint32_t& wire, Slice& payload, uint64_t& scalar) {
+inline bool field(Slice& s, uint32_t& num, uint32_t& wire, Slice& payload, uint64_t& scalar) {
   uint64_t key;
   if (!varint(s, key)) return false;
   num = static_cast<uint32_t>(key >> 3);
@@ -367,6 +372,11 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
     std::vector<char> seen(n_feat);
     for (long long c = c0; c < c1; ++c) {
       const long long r0 = c * mp->chunk, r1 = std::min(count, r0 + mp->chunk);
+      for (int f = 0; f < n_feat; ++f) {     // a first guess of 8 values per record saves most regrowth
+        if (fixed_lens[f] > 0) continue;
+        if (kinds[f] == 0) mp->ints[c][f].reserve(static_cast<size_t>(r1 - r0) * 8);
+        else mp->floats[c][f].reserve(static_cast<size_t>(r1 - r0) * 8);
+      }
       for (long long r = r0; r < r1; ++r) {
         std::fill(seen.begin(), seen.end(), 0);
         Slice example{data + offsets[r], static_cast<size_t>(lengths[r])};
