@@ -3,6 +3,7 @@ serializer for writing test and export files.  No TensorFlow involved."""
 from __future__ import annotations
 
 import ctypes
+import os
 import struct
 from typing import Iterable, Mapping, Sequence
 
@@ -73,7 +74,9 @@ class RecordFile:
   """A TFRecord file mapped into memory and indexed (payload offsets / lengths); CRCs verified."""
 
   def __init__(self, path: str, verify: bool = True):
-    self.data = np.fromfile(path, dtype=np.uint8)
+    # mapped, not read: only the pages of the records a process parses are brought in
+    self.data = (np.memmap(path, dtype=np.uint8, mode="r") if os.path.getsize(path) > 0
+                 else np.zeros(0, dtype=np.uint8))
     lib = _lib_host()
     ptr = self.data.ctypes.data_as(ctypes.c_void_p)
     n = lib.recml_tfrecord_index(ptr, c_ll(self.data.size), None, None, c_ll(0), ctypes.c_int(int(verify)))
