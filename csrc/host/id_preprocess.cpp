@@ -24,6 +24,40 @@ struct Entry {
   float gain;
 };
 
+// Sorts one shard's entries by (row, sample): LSD radix sort, 11 bits per pass, over only as many bits as
+// the largest row and the batch size need (rows and samples are non-negative).
+void radix_sort_entries(Entry* lo, Entry* hi, int batch) {
+  const size_t n = static_cast<size_t>(hi - lo);
+  if (n < 2048) {
+    std::sort(lo, hi, [](const Entry& a, const Entry& b) { return a.row != b.row ? a.row < b.row : a.sample < b.sample; });
+    return;
+  }
+  int sample_bits = 1;
+  while ((1LL << sample_bits) < batch) ++sample_bits;
+  int32_t max_row = 0;
+  for (const Entry* p = lo; p < hi; ++p) max_row = std::max(max_row, p->row);
+  int row_bits = 1;
+  while ((1LL << row_bits) <= max_row) ++row_bits;
+  const int total_bits = sample_bits + row_bits;
+  auto key = [sample_bits](const Entry& x) {
+    return (static_cast<uint64_t>(static_cast<uint32_t>(x.row)) << sample_bits) | static_cast<uint32_t>(x.sample);
+  };
+  std::vector<Entry> tmp(n);
+  Entry* src = lo;
+  Entry* dst = tmp.data();
+  constexpr int kBits = 11;
+  std::vector<size_t> count(1u << kBits);
+  for (int shift = 0; shift < total_bits; shift += kBits) {
+    std::fill(count.begin(), count.end(), 0);
+    for (size_t i = 0; i < n; ++i) ++count[(key(src[i]) >> shift) & ((1u << kBits) - 1)];
+    size_t run = 0;
+    for (size_t& c : count) { const size_t t = c; c = run; run += t; }
+    for (size_t i = 0; i < n; ++i) dst[count[(key(src[i]) >> shift) & ((1u << kBits) - 1)]++] = src[i];
+    std::swap(src, dst);
+  }
+  if (src != lo) std::copy(src, src + n, lo);
+}
+
 }  // namespace
 
 extern "C" {
@@ -76,35 +110,55 @@ long long recml_partition_csr(const int32_t* ids, const int32_t* offsets, const 
                      gains ? gains[i] : 1.0f};
       }
   }, 1024);
-  std::sort(e.begin(), e.end(), [](const Entry& a, const Entry& b) {
-    if (a.shard != b.shard) return a.shard < b.shard;
-    if (a.row != b.row) return a.row < b.row;
-    return a.sample < b.sample;
-  });
+  // bucket by shard (counting sort), then every shard is sorted by (row, sample), merged and capped on its
+  // own thread; the shards' survivors are laid end to end afterwards
+  std::vector<long long> start(shards + 1, 0);
+  for (long long k = 0; k < nnz; ++k) ++start[e[k].shard + 1];
+  for (int s = 0; s < shards; ++s) start[s + 1] += start[s];
+  std::vector<Entry> by(static_cast<size_t>(nnz));
+  {
+    std::vector<long long> at(start.begin(), start.end() - 1);
+    for (long long k = 0; k < nnz; ++k) by[at[e[k].shard]++] = e[k];
+  }
+  std::vector<long long> kept_s(shards, 0), unique_s(shards, 0), dropped_s(shards, 0);
+  recml::ThreadPool::global().parallel_for(shards, [&](long long s0, long long s1, int) {
+    for (long long s = s0; s < s1; ++s) {
+      Entry* lo = by.data() + start[s];
+      Entry* hi = by.data() + start[s + 1];
+      radix_sort_entries(lo, hi, batch);
+      long long in_shard = 0, unique = 0, dropped = 0;
+      int32_t last_row = -1;
+      Entry* out = lo;
+      for (Entry* p = lo; p < hi;) {
+        Entry cur = *p++;      // merge duplicates of the same (row, sample)
+        while (p < hi && p->row == cur.row && p->sample == cur.sample) cur.gain += (p++)->gain;
+        if (max_ids_per_shard > 0 && in_shard >= max_ids_per_shard) { ++dropped; continue; }
+        if (cur.row != last_row) { ++unique; last_row = cur.row; }
+        *out++ = cur;
+        ++in_shard;
+      }
+      kept_s[s] = in_shard; unique_s[s] = unique; dropped_s[s] = dropped;
+    }
+  }, 1);
   long long kept = 0, dropped = 0, max_ids = 0, max_unique = 0;
-  long long i = 0;
   for (int s = 0; s < shards; ++s) {
     shard_ptr[s] = kept;
-    long long in_shard = 0, unique = 0;
-    int32_t last_row = -1;
-    while (i < nnz && e[i].shard == s) {
-      // merge duplicates of the same (row, sample)
-      Entry cur = e[i++];
-      while (i < nnz && e[i].shard == s && e[i].row == cur.row && e[i].sample == cur.sample) cur.gain += e[i++].gain;
-      if (max_ids_per_shard > 0 && in_shard >= max_ids_per_shard) {
-        ++dropped;
-        continue;
-      }
-      if (cur.row != last_row) { ++unique; last_row = cur.row; }
-      out_rows[kept] = cur.row;
-      out_samples[kept] = cur.sample;
-      out_gains[kept] = cur.gain;
-      ++kept;
-      ++in_shard;
-    }
-    max_ids = std::max(max_ids, in_shard);
-    max_unique = std::max(max_unique, unique);
+    kept += kept_s[s];
+    dropped += dropped_s[s];
+    max_ids = std::max(max_ids, kept_s[s]);
+    max_unique = std::max(max_unique, unique_s[s]);
   }
+  recml::ThreadPool::global().parallel_for(shards, [&](long long s0, long long s1, int) {
+    for (long long s = s0; s < s1; ++s) {
+      const Entry* src = by.data() + start[s];
+      const long long base = shard_ptr[s];
+      for (long long k = 0; k < kept_s[s]; ++k) {
+        out_rows[base + k] = src[k].row;
+        out_samples[base + k] = src[k].sample;
+        out_gains[base + k] = src[k].gain;
+      }
+    }
+  }, 1);
   shard_ptr[shards] = kept;
   stats[0] = max_ids;
   stats[1] = max_unique;

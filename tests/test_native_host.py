@@ -192,3 +192,34 @@ def test_parse_many_matches_per_feature_parse(tmp_path):
       np.testing.assert_array_equal(many[name][0], vals)
       np.testing.assert_array_equal(many[name][1], lens)
   assert (many["absent"] == 7).all() and many["gone"][0].size == 0
+
+
+@pytest.mark.parametrize("shards,rotation,cap", [(8, 0, 0), (3, 2, 0), (4, 1, 5000)])
+def test_partition_csr_large_batch_matches_numpy(shards, rotation, cap):
+  """Large batches take the per-shard radix sort: order, merged gains, shard pointers, statistics and
+  dropping beyond the cap must equal a numpy restatement."""
+  rng = np.random.default_rng(shards)
+  B, bag = 4096, 12
+  ids = (rng.zipf(1.2, B * bag) % 300000).astype(np.int32)
+  offs = np.arange(0, B * bag + 1, bag, dtype=np.int32)
+  gains = rng.random(B * bag).astype(np.float32)
+  rows, samples, g, ptr, st = ip.partition_csr(ids, offs, shards, rotation=rotation, gains=gains, max_ids_per_partition=cap)
+  shard = (ids % shards + rotation) % shards
+  row = ids // shards
+  sample = np.repeat(np.arange(B), bag)
+  order = np.lexsort((sample, row, shard))
+  key = np.stack([shard[order], row[order], sample[order]], 1)
+  first = np.r_[True, (key[1:] != key[:-1]).any(1)]
+  grp = np.cumsum(first) - 1
+  merged = np.bincount(grp, weights=gains[order].astype(np.float64))
+  ks, kr, km = key[first, 0], key[first, 1], key[first, 2]
+  keep = np.ones(ks.size, bool)
+  if cap:
+    rank_in_shard = np.arange(ks.size) - np.searchsorted(ks, ks, side="left")
+    keep = rank_in_shard < cap
+  np.testing.assert_array_equal(rows, kr[keep])
+  np.testing.assert_array_equal(samples, km[keep])
+  np.testing.assert_allclose(g, merged[keep], rtol=1e-5)
+  np.testing.assert_array_equal(ptr, np.r_[0, np.cumsum(np.bincount(ks[keep], minlength=shards))])
+  assert st.dropped_ids == int((~keep).sum())
+  assert st.max_ids_per_partition == int(np.bincount(ks[keep], minlength=shards).max())
