@@ -354,7 +354,10 @@ struct MultiParse {
 void* recml_parse_multi(const uint8_t* data, const long long* offsets, const long long* lengths, long long count,
                         int n_feat, const char* const* names, const int* kinds, const int* fixed_lens,
                         const long long* default_int, const float* default_float, void* const* dense_out,
-                        long long* const* row_lengths) {
+                        long long* const* row_lengths, const int* sources, long long* const* steps_out) {
+  // sources (may be null: all 0): 0 = feature of an Example / context feature of a SequenceExample,
+  // 1 = feature list of a SequenceExample (variable length only: the values of all its steps are
+  // concatenated and steps_out[f][r] receives the number of steps).
   auto* mp = new MultiParse();
   mp->n_feat = n_feat;
   mp->count = count;
@@ -385,7 +388,8 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
         uint64_t sc;
         int guess = 0;      // records usually list their features in the same order: try the next one first
         while (example.n > 0 && field(example, num, wire, pl, sc)) {
-          if (num != 1 || wire != 2) continue;
+          if (wire != 2 || (num != 1 && num != 2)) continue;
+          const int src = num == 2 ? 1 : 0;
           Slice feats = pl;
           while (feats.n > 0 && field(feats, num, wire, pl, sc)) {
             if (num != 1 || wire != 2) continue;
@@ -397,11 +401,27 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
             int f = -1;
             for (int t = 0; t < n_feat; ++t) {
               const int cand = guess + t < n_feat ? guess + t : guess + t - n_feat;
-              if (name_len[cand] == key.n && memcmp(key.p, names[cand], key.n) == 0) { f = cand; break; }
+              if (name_len[cand] == key.n && (sources != nullptr ? sources[cand] : 0) == src &&
+                  memcmp(key.p, names[cand], key.n) == 0) { f = cand; break; }
             }
             if (f < 0 || seen[f]) continue;
             seen[f] = 1;
             guess = f + 1 < n_feat ? f + 1 : 0;
+            if (src == 1) {       // FeatureList { repeated Feature feature = 1 }
+              std::vector<int64_t>* di = kinds[f] == 0 ? &mp->ints[c][f] : nullptr;
+              std::vector<float>* df = kinds[f] == 0 ? nullptr : &mp->floats[c][f];
+              const size_t before = di != nullptr ? di->size() : df->size();
+              long long n_steps = 0;
+              Slice list = val;
+              while (list.n > 0 && field(list, num, wire, pl, sc)) {
+                if (num != 1 || wire != 2) continue;
+                parse_feature(pl, di, df, nullptr);
+                ++n_steps;
+              }
+              row_lengths[f][r] = static_cast<long long>((di != nullptr ? di->size() : df->size()) - before);
+              if (steps_out != nullptr && steps_out[f] != nullptr) steps_out[f][r] = n_steps;
+              continue;
+            }
             const int fl = fixed_lens[f];
             if (kinds[f] == 0) {
               std::vector<int64_t>& dst = fl > 0 ? iv : mp->ints[c][f];
@@ -431,7 +451,11 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
         for (int f = 0; f < n_feat; ++f) {      // features the record does not have
           if (seen[f]) continue;
           const int fl = fixed_lens[f];
-          if (fl == 0) { row_lengths[f][r] = 0; continue; }
+          if (fl == 0) {
+            row_lengths[f][r] = 0;
+            if (steps_out != nullptr && steps_out[f] != nullptr) steps_out[f][r] = 0;
+            continue;
+          }
           for (int i = 0; i < fl; ++i) {
             if (kinds[f] == 0) static_cast<int64_t*>(dense_out[f])[r * fl + i] = default_int[f];
             else static_cast<float*>(dense_out[f])[r * fl + i] = default_float[f];

@@ -122,9 +122,12 @@ class RecordFile:
   def parse_many(self, rows: np.ndarray, specs: Sequence[tuple]) -> dict:
     """Parses several features of the given records in ONE pass over each record (the per-feature
     `parse` walks a record's feature map once per call).  `specs`: (name, dtype, fixed_len, default)
-    tuples, fixed_len 0 for variable length.  Returns name -> dense `[n, fixed_len]` array, or
-    (values, row_lengths) for variable-length features."""
+    tuples, fixed_len 0 for variable length; a fifth element "list" marks a feature LIST of a
+    tf.SequenceExample (variable length).  Returns name -> dense `[n, fixed_len]` array,
+    (values, row_lengths) for variable-length features, (values, row_lengths, steps) for feature lists."""
     lib = _lib_host()
+    is_list = [len(sp) > 4 and sp[4] == "list" for sp in specs]
+    specs = [tuple(sp[:4]) for sp in specs]
     n, F = len(rows), len(specs)
     offs = np.ascontiguousarray(self.offsets[rows])
     lens = np.ascontiguousarray(self.lengths[rows])
@@ -134,9 +137,15 @@ class RecordFile:
     c_fixed = (ctypes.c_int * F)(*[int(fl) for _, _, fl, _ in specs])
     c_di = (c_ll * F)(*[int(d) if k == 0 else 0 for (_, _, _, d), k in zip(specs, kinds)])
     c_df = (ctypes.c_float * F)(*[float(d) if k == 1 else 0.0 for (_, _, _, d), k in zip(specs, kinds)])
-    dense, rowlen = {}, {}
-    c_dense, c_rows = (ctypes.c_void_p * F)(), (ctypes.c_void_p * F)()
+    dense, rowlen, steps = {}, {}, {}
+    c_dense, c_rows, c_steps = (ctypes.c_void_p * F)(), (ctypes.c_void_p * F)(), (ctypes.c_void_p * F)()
+    c_src = (ctypes.c_int * F)(*[int(x) for x in is_list])
     for f, ((nm, _, fl, _), k) in enumerate(zip(specs, kinds)):
+      if is_list[f]:
+        if fl > 0:
+          raise ValueError(f"feature list {nm!r} must be variable length")
+        steps[f] = np.zeros(n, dtype=np.int64)
+        c_steps[f] = steps[f].ctypes.data
       if fl > 0:
         dense[f] = np.empty((n, fl), dtype=np.int64 if k == 0 else np.float32)
         c_dense[f] = dense[f].ctypes.data
@@ -148,7 +157,7 @@ class RecordFile:
     handle = ctypes.c_void_p(lib.recml_parse_multi(
         self.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
         lens.ctypes.data_as(ctypes.c_void_p), c_ll(n), ctypes.c_int(F), names, c_kinds, c_fixed, c_di, c_df,
-        c_dense, c_rows))
+        c_dense, c_rows, c_src, c_steps))
     out = {}
     try:
       for f, ((nm, _, fl, _), k) in enumerate(zip(specs, kinds)):
@@ -157,7 +166,7 @@ class RecordFile:
           continue
         vals = np.empty(int(lib.recml_parse_multi_size(handle, ctypes.c_int(f))), dtype=np.int64 if k == 0 else np.float32)
         lib.recml_parse_multi_fetch(handle, ctypes.c_int(f), vals.ctypes.data_as(ctypes.c_void_p))
-        out[nm] = (vals, rowlen[f])
+        out[nm] = (vals, rowlen[f], steps[f]) if is_list[f] else (vals, rowlen[f])
     finally:
       lib.recml_parse_multi_free(handle)
     return out

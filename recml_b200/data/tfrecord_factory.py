@@ -115,6 +115,10 @@ class _RecordDataset:
         specs.append((name, spec.dtype, int(np.prod(spec.shape)) if spec.shape else 1, spec.default_value))
       else:
         specs.append((name, spec.dtype, 0, 0))
+    seq = self.fac.sequence_feature_spec or {}
+    one_call = not (set(seq) & set(self.fac.feature_spec))       # results are keyed by name
+    if one_call:
+      specs += [(name, spec.dtype, 0, 0, "list") for name, spec in seq.items()]   # tf.SequenceExample feature lists
     parsed = rf.parse_many(rows, specs) if specs else {}
     for name, spec in self.fac.feature_spec.items():
       if isinstance(spec, FixedLenFeature):
@@ -122,8 +126,8 @@ class _RecordDataset:
       else:
         vals, lens = parsed[name]
         out[name] = {"values": vals, "lengths": lens}
-    for name, spec in (self.fac.sequence_feature_spec or {}).items():     # tf.SequenceExample feature lists
-      vals, lens, steps = rf.parse_sequence(rows, name, spec.dtype)
+    for name, spec in seq.items():
+      vals, lens, steps = parsed[name] if one_call else rf.parse_sequence(rows, name, spec.dtype)
       out[name] = {"values": vals, "lengths": lens, "steps": steps}
     return out
 

@@ -223,3 +223,28 @@ def test_partition_csr_large_batch_matches_numpy(shards, rotation, cap):
   np.testing.assert_array_equal(ptr, np.r_[0, np.cumsum(np.bincount(ks[keep], minlength=shards))])
   assert st.dropped_ids == int((~keep).sum())
   assert st.max_ids_per_partition == int(np.bincount(ks[keep], minlength=shards).max())
+
+
+def test_parse_many_feature_lists_match_parse_sequence(tmp_path):
+  from recml_b200.data import tfrecord
+  rng = np.random.default_rng(9)
+  recs = []
+  for i in range(300):
+    steps = int(rng.integers(0, 12))
+    ctx = {"user": [int(rng.integers(0, 1000))]}
+    lists = {"item": [[int(rng.integers(0, 5000))] for _ in range(steps)],
+             "ts": [[float(rng.random()), float(rng.random())] for _ in range(steps)]}
+    if i % 4 == 0:
+      lists.pop("ts")
+    recs.append(tfrecord.encode_sequence_example(ctx, lists))
+  path = str(tmp_path / "seq.tfrecord")
+  tfrecord.write_tfrecord(path, recs)
+  rf = tfrecord.RecordFile(path)
+  rows = np.arange(len(rf))
+  many = rf.parse_many(rows, [("item", "int64", 0, 0, "list"), ("user", "int64", 1, 0), ("ts", "float", 0, 0, "list")])
+  np.testing.assert_array_equal(many["user"], rf.parse(rows, "user", "int64", 1))
+  for name, dtype in (("item", "int64"), ("ts", "float")):
+    vals, lens, steps = rf.parse_sequence(rows, name, dtype)
+    np.testing.assert_array_equal(many[name][0], vals)
+    np.testing.assert_array_equal(many[name][1], lens)
+    np.testing.assert_array_equal(many[name][2], steps)
