@@ -336,6 +336,59 @@ int recml_parse_raw_bytes(const uint8_t* data, const long long* offsets, const l
   return bad.load();
 }
 
+// Pre-batched multi-hot id features (the Criteo records of the reference's loader: feature f of a record is
+// a bytes list with one string per sample, each holding multi_hot[f] little-endian int64 ids).  Decodes
+// features [0, n_feat) of `count` records into out[r * total + batch * sum(multi_hot[0..f)) + b * multi_hot[f] + j]
+// as int32 ids taken modulo vocab[f]: the feature-major value layout the embedding input uses, with no
+// intermediate int64 arrays.  One task per (record, feature).  Returns the number of (record, feature)
+// pairs whose payload was not exactly batch strings of multi_hot[f] ids (their slots are zero-filled).
+int recml_decode_multihot_records(const uint8_t* data, const long long* offsets, const long long* lengths, long long count,
+                                  int n_feat, const char* const* names, const int* multi_hot, const long long* vocab,
+                                  int batch, int32_t* out) {
+  std::vector<long long> start(n_feat + 1, 0);
+  for (int f = 0; f < n_feat; ++f) start[f + 1] = start[f] + static_cast<long long>(batch) * multi_hot[f];
+  const long long total = start[n_feat];
+  std::atomic<int> bad{0};
+  recml::ThreadPool::global().parallel_for(count * n_feat, [&](long long t0, long long t1, int) {
+    for (long long t = t0; t < t1; ++t) {
+      const long long r = t / n_feat;
+      const int f = static_cast<int>(t % n_feat);
+      const int m = multi_hot[f];
+      const long long v = vocab[f] > 0 ? vocab[f] : 1;
+      int32_t* dst = out + r * total + start[f];
+      long long got = 0;           // samples decoded
+      bool ok = true;
+      Slice feat;
+      if (find_feature(Slice{data + offsets[r], static_cast<size_t>(lengths[r])}, names[f], feat)) {
+        uint32_t kind, wire, num;
+        Slice pl;
+        uint64_t sc;
+        while (feat.n > 0 && field(feat, kind, wire, pl, sc)) {
+          if (kind != 1 || wire != 2) continue;          // bytes_list
+          Slice list = pl;
+          while (list.n > 0 && field(list, num, wire, pl, sc)) {
+            if (num != 1 || wire != 2) continue;
+            if (pl.n != static_cast<size_t>(m) * 8 || got >= batch) { ok = false; continue; }
+            for (int j = 0; j < m; ++j) {
+              int64_t id;
+              memcpy(&id, pl.p + 8 * j, 8);
+              long long q = id % v;
+              if (q < 0) q += v;                         // numpy's modulo is non-negative
+              dst[got * m + j] = static_cast<int32_t>(q);
+            }
+            ++got;
+          }
+        }
+      }
+      if (got != batch || !ok) {
+        bad.fetch_add(1);
+        if (got < batch) memset(dst + got * m, 0, sizeof(int32_t) * static_cast<size_t>(batch - got) * m);
+      }
+    }
+  }, 1);
+  return bad.load();
+}
+
 // ---- one pass over every record for many features ---------------------------------------------------
 // The per-feature entry point above walks a record's feature map once per requested feature; a batch of
 // small Examples with tens of features is parsed an order of magnitude faster by visiting every map entry

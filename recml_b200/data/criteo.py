@@ -94,28 +94,44 @@ class CriteoDataLoader:
     self.is_training, self.shuffle_buffer, self.eval_steps = is_training, shuffle_buffer, eval_steps
     self.verify_crc = verify_crc
     self._rng = np.random.default_rng(seed + process_index)
+    self._offsets = None
 
   def _parse(self, rf: tfrecord.RecordFile, rows: np.ndarray) -> list[dict]:
-    B = self.batch_size
-    labels = rf.parse(rows, LABEL, "int64", fixed_len=B, default=-1)
+    """Label and the 13 dense features in one pass over each record; the id features are decoded by the
+    native library straight into the int32 feature-major value layout (modulo the vocabulary included)."""
+    B, R, F = self.batch_size, len(rows), len(self.multi_hot)
+    fixed = rf.parse_many(rows, [(LABEL, "int64", B, -1)] + [(n, "float", B, 0.0) for n in DENSE])
+    labels = fixed[LABEL]
     if (labels[:, -1] < 0).any():
       raise ValueError(f"a record holds fewer than batch_size={B} samples")
-    dense = np.stack([rf.parse(rows, n, "float", fixed_len=B) for n in DENSE], axis=-1)      # [R, B, 13]
+    dense = np.stack([fixed[n] for n in DENSE], axis=-1)      # [R, B, 13]
     lib = tfrecord._lib_host()
     offs = np.ascontiguousarray(rf.offsets[rows])
     lens = np.ascontiguousarray(rf.lengths[rows])
-    ids = []
-    for f, name in enumerate(SPARSE[:len(self.multi_hot)]):
-      m = self.multi_hot[f]
-      buf = np.empty((len(rows), B, m), dtype="<i8")
-      bad = lib.recml_parse_raw_bytes(rf.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
-                                      lens.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(len(rows)), name.encode(),
-                                      ctypes.c_longlong(B * m * 8), buf.ctypes.data_as(ctypes.c_void_p))
-      if bad:
-        raise ValueError(f"{name}: {bad} records do not hold {B} bags of {m} int64 ids")
-      ids.append(np.mod(buf, self.vocab_sizes[f]))
-    return [assemble(labels[r].astype(np.float32), dense[r], [a[r] for a in ids],
-                     weight=None if self.is_training else np.ones(B, np.float32)) for r in range(len(rows))]
+    names = SPARSE[:F]
+    total = B * int(sum(self.multi_hot))
+    values = np.empty((R, total), dtype=np.int32)
+    bad = lib.recml_decode_multihot_records(
+        rf.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p), lens.ctypes.data_as(ctypes.c_void_p),
+        ctypes.c_longlong(R), ctypes.c_int(F), (ctypes.c_char_p * F)(*[n.encode() for n in names]),
+        (ctypes.c_int * F)(*self.multi_hot), (ctypes.c_longlong * F)(*self.vocab_sizes[:F]), ctypes.c_int(B),
+        values.ctypes.data_as(ctypes.c_void_p))
+    if bad:
+      raise ValueError(f"{bad} (record, feature) pairs do not hold {B} bags of the configured multi-hot sizes")
+    if self._offsets is None:       # the bag sizes are fixed, so every batch has the same offsets
+      lens_all = np.concatenate([np.full(B, m, dtype=np.int64) for m in self.multi_hot])
+      self._offsets = np.zeros(lens_all.size + 1, dtype=np.int32)
+      self._offsets[1:] = np.cumsum(lens_all)
+    keys = tuple(f"cat_{i}" for i in range(F))      # the names `assemble` gives the features
+    out = []
+    for r in range(R):
+      item = {"dense": torch.from_numpy(np.ascontiguousarray(dense[r], dtype=np.float32)),
+              "sparse": KeyedJagged(keys, torch.from_numpy(values[r]), torch.from_numpy(self._offsets), None, B),
+              "label": torch.from_numpy(labels[r].astype(np.float32))}
+      if not self.is_training:
+        item["weight"] = torch.ones(B, dtype=torch.float32)
+      out.append(item)
+    return out
 
   def _records(self) -> Iterator[dict]:
     while True:
