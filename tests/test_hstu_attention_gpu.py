@@ -130,3 +130,51 @@ def test_attention_accepts_column_slices_of_a_fused_projection():
     outs.append((o.detach().float(), leaf.grad.float()))
   torch.testing.assert_close(outs[0][0], outs[1][0], rtol=0, atol=0)
   torch.testing.assert_close(outs[0][1], outs[1][1], rtol=1e-2, atol=1e-4)
+
+
+def _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, causal, go):
+  gl = [t.cuda().requires_grad_() for t in (q, k, v)] + [pos_w.cuda().requires_grad_(), ts_w.cuda().requires_grad_()]
+  out = A.jagged_pointwise_attention(gl[0], gl[1], gl[2], offs.cuda(), N, pos_w=gl[3], ts_w=gl[4], timestamps=ts.cuda(),
+                                     causal=causal)
+  out.backward(go.cuda())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  return out.detach(), [t.grad.detach() for t in gl]
+
+
+def test_non_causal_with_bias_matches_reference():
+  """Full (non-causal) attention with both bias terms: the per-batch time-bucket blocks are then indexed by
+  the square (query tile, key tile) grid instead of the causal triangle."""
+  lengths, H, Dh = [200, 64, 391], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=5)
+  leaves = [t.float().requires_grad_() for t in (q, k, v)] + [pos_w.clone().requires_grad_(), ts_w.clone().requires_grad_()]
+  ref = A.jagged_attention_reference(leaves[0], leaves[1], leaves[2], offs, N, pos_w=leaves[3], ts_w=leaves[4],
+                                     timestamps=ts, causal=False)
+  go = torch.randn(ref.shape, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+  ref.backward(go.float())
+  out, grads = _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, False, go)
+  assert (out.float().cpu() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6) < 2e-2
+  for name, a, b in zip("q k v pos_w ts_w".split(), grads, leaves):
+    err = (a.float().cpu() - b.grad).abs().max().item()
+    assert err / (b.grad.abs().max().item() + 1e-6) < 3e-2, (name, err)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_bucket_cache_equals_inline_buckets(causal, monkeypatch):
+  """Cached bucket indices and buckets computed in the kernel come from the same function: forward outputs
+  and dk / dv agree exactly, the atomically accumulated gradients to rounding."""
+  from recml_b200.ops import hstu_cuda
+  lengths, H, Dh = [300, 17, 260], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=7)
+  go = torch.randn(sum(lengths), H, Dh, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+  hstu_cuda._memo.clear()
+  out_c, g_c = _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, causal, go)
+  assert "buckets" in hstu_cuda._memo
+  monkeypatch.setattr(hstu_cuda, "BUCKET_CACHE_MAX_BYTES", 0)
+  hstu_cuda._memo.clear()
+  out_i, g_i = _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, causal, go)
+  assert "buckets" not in hstu_cuda._memo
+  assert torch.equal(out_c, out_i)
+  assert torch.equal(g_c[1], g_i[1]) and torch.equal(g_c[2], g_i[2])
+  for a, b in zip(g_c, g_i):
+    torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
