@@ -416,7 +416,11 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
   mp->count = count;
   mp->kind.assign(kinds, kinds + n_feat);
   const int threads = recml::ThreadPool::global().size();
-  mp->chunk = std::max<long long>(64, (count + threads * 4 - 1) / (threads * 4));
+  long long bytes = 0;
+  for (long long r = 0; r < count; ++r) bytes += lengths[r];
+  // small records are grouped by at least 64 per task; pre-batched records (tens of KB each) go one per task
+  const long long min_chunk = count > 0 && bytes / count > 16384 ? 1 : 64;
+  mp->chunk = std::max<long long>(min_chunk, (count + threads * 4 - 1) / (threads * 4));
   mp->n_chunks = static_cast<int>((count + mp->chunk - 1) / mp->chunk);
   mp->ints.assign(mp->n_chunks, std::vector<std::vector<int64_t>>(n_feat));
   mp->floats.assign(mp->n_chunks, std::vector<std::vector<float>>(n_feat));
