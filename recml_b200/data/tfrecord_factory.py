@@ -142,9 +142,9 @@ class _RecordDataset:
     return out
 
   def _record_stream(self, rng):
-    """(file index, record index) in reading order: `cycle_length` files are open at a time and
-    `block_length` records are taken from each in turn (tf.data `interleave`); then an optional
-    shuffle window."""
+    """(file indices, record indices) array pairs in reading order: `cycle_length` files are open at a time
+    and `block_length` records are taken from each in turn (tf.data `interleave`); then an optional shuffle
+    window.  The order is produced in blocks with numpy, not record by record."""
     fac = self.fac
     files = list(range(len(self.files)))
     if fac.file_shuffle:
@@ -152,7 +152,7 @@ class _RecordDataset:
 
     def rows_of(fi):
       n = len(self._open(fi))
-      rows = np.arange(n)
+      rows = np.arange(n, dtype=np.int64)
       if self.shard_records:
         rows = rows[self.sharding.process_index::self.sharding.num_processes]
       if fac.shuffle and not fac.shuffle_buffer_size:
@@ -161,31 +161,54 @@ class _RecordDataset:
 
     def interleaved():
       cycle = max(1, fac.cycle_length or 1)
+      blk = max(1, fac.block_length)
       pending = list(files)
       active: list[tuple[int, np.ndarray, int]] = []
       while pending or active:
         while pending and len(active) < cycle:
           fi = pending.pop(0)
           active.append((fi, rows_of(fi), 0))
-        nxt = []
+        active = [a for a in active if a[2] < len(a[1])]
+        if not active:
+          continue
+        if len(active) == 1 and (cycle == 1 or not pending):
+          fi, rows, at = active[0]                  # one open file: its blocks follow one another anyway
+          yield np.full(len(rows) - at, fi, dtype=np.int64), rows[at:]
+          active = []
+          continue
+        # whole rounds (one block from every open file) until the first file runs short of a full block
+        k = min((len(rows) - at) // blk for _, rows, at in active)
+        if k >= 1:
+          parts_r = np.stack([rows[at:at + k * blk].reshape(k, blk) for _, rows, at in active], axis=1)
+          parts_f = np.broadcast_to(np.array([fi for fi, _, _ in active], dtype=np.int64)[None, :, None], parts_r.shape)
+          yield parts_f.reshape(-1), parts_r.reshape(-1)
+          active = [(fi, rows, at + k * blk) for fi, rows, at in active]
+          continue
+        nxt = []                                   # a round with a short last block
         for fi, rows, at in active:
-          hi = min(at + max(1, fac.block_length), len(rows))
-          for r in rows[at:hi]:
-            yield fi, int(r)
+          hi = min(at + blk, len(rows))
+          yield np.full(hi - at, fi, dtype=np.int64), rows[at:hi]
           if hi < len(rows):
             nxt.append((fi, rows, hi))
         active = nxt
 
-    if fac.shuffle and fac.shuffle_buffer_size:
-      window: list = []
-      for item in interleaved():
-        window.append(item)
-        if len(window) >= fac.shuffle_buffer_size:
-          yield window.pop(int(rng.integers(len(window))))
-      while window:
-        yield window.pop(int(rng.integers(len(window))))
-    else:
+    if not (fac.shuffle and fac.shuffle_buffer_size):
       yield from interleaved()
+      return
+    # shuffle window: keep up to shuffle_buffer_size - 1 records back, emit the surplus in random order
+    keep = max(0, int(fac.shuffle_buffer_size) - 1)
+    win_f, win_r = np.zeros(0, np.int64), np.zeros(0, np.int64)
+    for bf, br in interleaved():
+      win_f, win_r = np.concatenate([win_f, bf]), np.concatenate([win_r, br])
+      n_out = len(win_r) - keep
+      if n_out > 0:
+        perm = rng.permutation(len(win_r))
+        out, rest = perm[:n_out], perm[n_out:]
+        yield win_f[out], win_r[out]
+        win_f, win_r = win_f[rest], win_r[rest]
+    if len(win_r):
+      perm = rng.permutation(len(win_r))
+      yield win_f[perm], win_r[perm]
 
   def _open(self, fi: int) -> tfrecord.RecordFile:
     if fi not in self._open_cache:
@@ -194,11 +217,9 @@ class _RecordDataset:
       self._open_cache[fi] = tfrecord.RecordFile(self.files[fi], verify=self.fac.verify_checksums)
     return self._open_cache[fi]
 
-  def _parse_mixed(self, items: list[tuple[int, int]]) -> dict:
-    """Parses records that may come from several files, keeping the order of `items`."""
-    fis = np.array([fi for fi, _ in items])
-    rows = np.array([r for _, r in items], dtype=np.int64)
-    uniq = list(dict.fromkeys(fis.tolist()))
+  def _parse_mixed(self, fis: np.ndarray, rows: np.ndarray) -> dict:
+    """Parses records that may come from several files, keeping the given order."""
+    uniq = list(dict.fromkeys(fis.tolist())) if len(fis) and (fis != fis[0]).any() else [int(fis[0])]
     if len(uniq) == 1:
       return self._parse_features(self._open(uniq[0]), rows)
     parts, order = [], []
@@ -210,6 +231,23 @@ class _RecordDataset:
     inv = np.argsort(np.concatenate(order), kind="stable")
     return _take(merged, inv)
 
+  def _batches_of(self, stream):
+    """Cuts the stream of (file indices, record indices) blocks into pieces of the batch size; the last
+    piece of an epoch may be shorter."""
+    pend_f, pend_r, n = [], [], 0
+    for bf, br in stream:
+      pend_f.append(bf); pend_r.append(br); n += len(br)
+      if n < self.batch:
+        continue
+      f, r = np.concatenate(pend_f), np.concatenate(pend_r)
+      at = 0
+      while n - at >= self.batch:
+        yield f[at:at + self.batch], r[at:at + self.batch]
+        at += self.batch
+      pend_f, pend_r, n = ([f[at:]], [r[at:]], n - at) if at < n else ([], [], 0)
+    if n:
+      yield np.concatenate(pend_f), np.concatenate(pend_r)
+
   def _generate(self):
     fac = self.fac
     rng = np.random.default_rng(fac.seed)
@@ -218,22 +256,10 @@ class _RecordDataset:
     carry: list[dict] = []          # rows that passed the filter but do not fill a batch yet
     carried = 0
     while True:
-      items: list[tuple[int, int]] = []
-      stream = self._record_stream(rng)
-      done = False
-      while not done:
-        items.clear()
-        for it in stream:
-          items.append(it)
-          if len(items) == self.batch:
-            break
-        else:
-          done = True
-        if not items:
+      for fis, rows in self._batches_of(self._record_stream(rng)):
+        if len(rows) < self.batch and fac.drop_remainder and fac.filter_fn is None:
           break
-        if len(items) < self.batch and fac.drop_remainder and fac.filter_fn is None:
-          break
-        feats = self._parse_mixed(items)
+        feats = self._parse_mixed(fis, rows)
         if fac.filter_fn is None:
           yield self._finish(feats)
           continue

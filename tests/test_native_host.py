@@ -248,3 +248,30 @@ def test_parse_many_feature_lists_match_parse_sequence(tmp_path):
     np.testing.assert_array_equal(many[name][0], vals)
     np.testing.assert_array_equal(many[name][1], lens)
     np.testing.assert_array_equal(many[name][2], steps)
+
+
+@pytest.mark.parametrize("sizes,cycle,block", [([7, 3, 10], 2, 2), ([5, 5, 5, 5], 4, 1), ([9], 3, 4), ([4, 11, 2, 6, 1], 3, 3),
+                                               ([6, 6], 1, 5)])
+def test_interleave_order_matches_record_by_record_definition(tmp_path, sizes, cycle, block):
+  """The block-wise (numpy) interleave must give the order of the plain definition: `cycle_length` files open,
+  `block_length` records from each in turn, a finished file replaced by the next pending one."""
+  from recml_b200.data import tfrecord, tfrecord_factory as F
+  for fi, n in enumerate(sizes):
+    tfrecord.write_tfrecord(str(tmp_path / f"part-{fi:02d}.tfrecord"),
+                            [tfrecord.encode_example({"x": [fi * 1000 + r]}) for r in range(n)])
+  fac = F.TFDatasetFactory(input_path=str(tmp_path / "part-*.tfrecord"), global_batch_size=1,
+                           feature_spec={"x": F.FixedLenFeature((1,), "int64")}, cycle_length=cycle, block_length=block,
+                           prefetch_buffer_size=0, sharding_info=F.DatasetShardingInfo(1, 0))
+  got = [int(b["x"][0, 0]) for b in fac.make()]
+  pending = [(fi, list(range(n))) for fi, n in enumerate(sizes)]
+  active, want = [], []
+  while pending or active:
+    while pending and len(active) < cycle:
+      active.append(pending.pop(0))
+    nxt = []
+    for fi, rows in active:
+      want += [fi * 1000 + r for r in rows[:block]]
+      if rows[block:]:
+        nxt.append((fi, rows[block:]))
+    active = nxt
+  assert got == want
