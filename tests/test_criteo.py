@@ -107,3 +107,21 @@ def test_experiment_launcher_runs_tiny_dlrm(tmp_path):
                       "--mode=train"], capture_output=True, text=True, env=env, timeout=600)
   assert r.returncode == 0, r.stderr[-2000:]
   assert os.path.isdir(tmp_path / "checkpoints")
+
+
+def test_loader_takes_ids_modulo_vocab_like_numpy_and_rejects_wrong_bag_sizes(tmp_path):
+  """Negative ids wrap the way numpy's modulo does; a record whose bags do not have the configured
+  multi-hot size is refused."""
+  B = 4
+  rng = np.random.default_rng(1)
+  labels, dense = rng.integers(0, 2, B), rng.normal(size=(B, 13)).astype(np.float32)
+  ids = [rng.integers(-10_000, 10_000, size=(B, m)) for m in HOT] + [np.zeros((B, 1), np.int64)] * 23
+  tfrecord.write_tfrecord(str(tmp_path / "neg.tfrecord"), [criteo.encode_record(labels, dense, ids)])
+  b = next(iter(criteo.CriteoDataLoader(str(tmp_path / "neg.tfrecord"), B, vocab_sizes=VOCAB, multi_hot_sizes=HOT,
+                                        is_training=False)))
+  want = np.concatenate([np.mod(a, v).reshape(-1) for a, v in zip(ids[:3], VOCAB)])
+  np.testing.assert_array_equal(b["sparse"].values.numpy(), want.astype(np.int32))
+  wrong = criteo.CriteoDataLoader(str(tmp_path / "neg.tfrecord"), B, vocab_sizes=VOCAB, multi_hot_sizes=[3, 2, 5],
+                                  is_training=False)
+  with pytest.raises(ValueError):
+    next(iter(wrong))
