@@ -124,10 +124,17 @@ void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floa
     while (list.n > 0 && field(list, num, wire, pl, sc)) {
       if (num != 1) continue;
       if (kind == 3 && ints != nullptr) {
-        if (wire == 2) {         // packed varints
+        if (wire == 2) {         // packed varints: one terminating byte (high bit clear) per value
+          size_t n_vals = 0;
+          for (size_t i = 0; i < pl.n; ++i) n_vals += !(pl.p[i] & 0x80);
+          const size_t at = ints->size();
+          ints->resize(at + n_vals);
+          int64_t* out = ints->data() + at;
           Slice pk = pl;
           uint64_t v;
-          while (pk.n > 0 && varint(pk, v)) ints->push_back(static_cast<int64_t>(v));
+          size_t k = 0;
+          while (k < n_vals && pk.n > 0 && varint(pk, v)) out[k++] = static_cast<int64_t>(v);
+          if (k < n_vals) ints->resize(at + k);      // truncated payload
         } else if (wire == 0) {
           ints->push_back(static_cast<int64_t>(sc));
         }
