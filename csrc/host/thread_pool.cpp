@@ -1,6 +1,7 @@
 #include "host/thread_pool.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 namespace recml {
@@ -58,14 +59,21 @@ void ThreadPool::parallel_for(long long n, const std::function<void(long long, l
     fn(0, n, 0);
     return;
   }
-  // A private completion latch, so nested / concurrent parallel_for calls do not wait on each other.
+  // Work is handed out in grains from a shared counter, so uneven items (a long file, a wide feature) do
+  // not leave the other workers idle.  A private completion latch, so nested / concurrent parallel_for
+  // calls do not wait on each other.
+  const long long grain = std::max<long long>(std::max<long long>(1, min_chunk), (n + parts * 8LL - 1) / (parts * 8LL));
+  std::atomic<long long> next{0};
   std::mutex mu;
   std::condition_variable cv;
   int left = parts;
   for (int p = 0; p < parts; ++p) {
-    const long long b = n * p / parts, e = n * (p + 1) / parts;
-    submit([&, b, e, p] {
-      fn(b, e, p);
+    submit([&, p] {
+      for (;;) {
+        const long long b = next.fetch_add(grain);
+        if (b >= n) break;
+        fn(b, std::min(n, b + grain), p);
+      }
       std::lock_guard<std::mutex> lock(mu);
       if (--left == 0) cv.notify_all();
     });

@@ -1,5 +1,5 @@
 // Fixed-size worker pool shared by the host-side native components (id preprocessing, record
-// parsing, checkpoint chunk I/O).  parallel_for splits [0, n) into contiguous ranges.
+// parsing, checkpoint chunk I/O).  parallel_for hands [0, n) out in contiguous grains from a shared counter.
 #pragma once
 #include <condition_variable>
 #include <functional>
