@@ -252,32 +252,42 @@ class _RecordDataset:
     fac = self.fac
     rng = np.random.default_rng(fac.seed)
     self._open_cache: dict = {}
-    epoch = 0
     carry: list[dict] = []          # rows that passed the filter but do not fill a batch yet
     carried = 0
-    while True:
-      for fis, rows in self._batches_of(self._record_stream(rng)):
-        if len(rows) < self.batch and fac.drop_remainder and fac.filter_fn is None:
-          break
-        feats = self._parse_mixed(fis, rows)
-        if fac.filter_fn is None:
-          yield self._finish(feats)
-          continue
-        keep = np.nonzero(np.asarray(fac.filter_fn(feats), dtype=bool))[0]   # vectorised filter, then re-batch
-        if len(keep):
-          carry.append(_take(feats, keep))
-          carried += len(keep)
-        while carried >= self.batch:
-          merged = _concat(carry)
-          yield self._finish(_take(merged, np.arange(self.batch)))
-          rest = _rows_of(merged) - self.batch
-          carry = [_take(merged, np.arange(self.batch, self.batch + rest))] if rest else []
-          carried = rest
-      epoch += 1
-      if not fac.repeat or (fac.num_epochs is not None and epoch >= fac.num_epochs):
-        if carried and not fac.drop_remainder:
-          yield self._finish(_concat(carry))
-        return
+
+    def epochs():
+      """The record stream of every epoch, one after the other: with `repeat` the records are repeated
+      BEFORE batching (the reference repeats its file list), so batches run across epoch boundaries and
+      an input smaller than one batch still fills batches."""
+      epoch = 0
+      while True:
+        seen = 0
+        for bf, br in self._record_stream(rng):
+          seen += len(br)
+          yield bf, br
+        epoch += 1
+        if seen == 0 or not fac.repeat or (fac.num_epochs is not None and epoch >= fac.num_epochs):
+          return
+
+    for fis, rows in self._batches_of(epochs()):
+      if len(rows) < self.batch and fac.drop_remainder and fac.filter_fn is None:
+        break
+      feats = self._parse_mixed(fis, rows)
+      if fac.filter_fn is None:
+        yield self._finish(feats)
+        continue
+      keep = np.nonzero(np.asarray(fac.filter_fn(feats), dtype=bool))[0]   # vectorised filter, then re-batch
+      if len(keep):
+        carry.append(_take(feats, keep))
+        carried += len(keep)
+      while carried >= self.batch:
+        merged = _concat(carry)
+        yield self._finish(_take(merged, np.arange(self.batch)))
+        rest = _rows_of(merged) - self.batch
+        carry = [_take(merged, np.arange(self.batch, self.batch + rest))] if rest else []
+        carried = rest
+    if carried and not fac.drop_remainder:
+      yield self._finish(_concat(carry))
 
   def __iter__(self):
     fac = self.fac

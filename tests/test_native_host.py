@@ -275,3 +275,26 @@ def test_interleave_order_matches_record_by_record_definition(tmp_path, sizes, c
         nxt.append((fi, rows[block:]))
     active = nxt
   assert got == want
+
+
+def test_data_benchmark_runs_on_a_small_file():
+  from recml_b200.benchmarks import data_bench
+  out = data_bench.run(examples=300)
+  assert out["features"] == 40 and out["one_pass_parse_examples_per_s"] > 0 and out["factory_examples_per_s"] > 0
+
+
+def test_repeat_fills_batches_across_epochs(tmp_path):
+  """`repeat` repeats the records before batching: an input of 5 records gives batches of 4 that run
+  across epoch boundaries, and `num_epochs` bounds the total."""
+  from recml_b200.data import tfrecord, tfrecord_factory as F
+  tfrecord.write_tfrecord(str(tmp_path / "five.tfrecord"), [tfrecord.encode_example({"x": [r]}) for r in range(5)])
+  fac = F.TFDatasetFactory(input_path=str(tmp_path / "five.tfrecord"), global_batch_size=4, repeat=True, num_epochs=3,
+                           feature_spec={"x": F.FixedLenFeature((1,), "int64")}, prefetch_buffer_size=0,
+                           sharding_info=F.DatasetShardingInfo(1, 0))
+  got = [b["x"][:, 0].tolist() for b in fac.make()]
+  assert got == [[0, 1, 2, 3], [4, 0, 1, 2], [3, 4, 0, 1]]           # 15 records, the last 3 dropped
+  big = F.TFDatasetFactory(input_path=str(tmp_path / "five.tfrecord"), global_batch_size=8, repeat=True,
+                           feature_spec={"x": F.FixedLenFeature((1,), "int64")}, prefetch_buffer_size=0,
+                           sharding_info=F.DatasetShardingInfo(1, 0))
+  it = iter(big.make())
+  assert next(it)["x"][:, 0].tolist() == [0, 1, 2, 3, 4, 0, 1, 2]
