@@ -136,13 +136,17 @@ class CriteoDataLoader:
   def _records(self) -> Iterator[dict]:
     while True:
       order = self._rng.permutation(len(self.files)) if self.is_training else np.arange(len(self.files))
+      seen = 0
       for fi in order:
         rf = tfrecord.RecordFile(self.files[fi], verify=self.verify_crc)
         n = len(rf)
+        seen += n
         for lo in range(0, n, 16):
           yield from self._parse(rf, np.arange(lo, min(lo + 16, n)))
       if not self.is_training:
         return
+      if seen == 0:
+        raise ValueError(f"no records in {self.files}: a training loader would repeat nothing for ever")
 
   def __iter__(self) -> Iterator[dict]:
     if self.is_training:
