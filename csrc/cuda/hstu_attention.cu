@@ -6,13 +6,18 @@
 // to its own).  Per key tile:
 //   TMA (warp 0)        K_j, V_j -> shared memory (2 stages)
 //   tcgen05.mma (warp 1) S = Q·K_j^T into tensor memory
-//   warps 2..5           tcgen05.ld S; p = silu(s·scale + pos_w[kj-qi+N-1] + ts_w[bucket(Δt)]) / n;
+//   warps 2..17          (each 32 rows x 32 columns of the score tile) tcgen05.ld S;
+//                        p = silu(s·scale + pos_w[kj-qi+N-1] + ts_w[bucket(Δt)]) / n;
 //                        causal / length mask; bf16 P written to shared memory in the 128-byte-swizzled
 //                        K-major layout the tensor core expects
 //   tcgen05.mma (warp 1) O += P·V_j    (V consumed as an MN-major operand straight from its [kv, Dh] tile)
 // The backward kernel (one CTA per key tile and head, walking over the query tiles that see it)
 // recomputes S and forms dV += P^T·dO, dK += dS^T·Q, dQ += dS·K on the tensor cores, with
-// dS = dP ⊙ d/ds[silu]/n and the bias gradients reduced through shared-memory histograms.
+// dS = dP ⊙ d/ds[silu]/n.  The position-bias gradient is summed along the diagonals of each warp's block in
+// registers (a partial sum per diagonal moves one lane per column) before it reaches a shared-memory
+// histogram; the time-bucket gradient is summed per run of equal buckets.
+// CTAs take their tiles from a list sorted by decreasing work (the backward has its own order) with the
+// heads varying fastest, and read the time-bucket indices from blocks computed once per batch.
 // All waits are bounded; a CTA that gives up drains and frees its tensor memory.
 #include "tcgen05.cuh"
 
