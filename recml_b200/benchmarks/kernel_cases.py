@@ -6,7 +6,7 @@ Each case builds inputs larger than L2 (126 MB) but only a few GB in total, warm
 kernel with CUDA events and prints achieved bandwidth / FLOP rate against the measured peaks of this
 machine (MEASURED_PEAKS.json when present).  The same command line is what `ncu` captures.
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, gemm_cross, emb_fwd, emb_bwd, hstu_fwd, hstu_bwd, vocab_rank,
-layernorm, ssd_fwd, ssd_bwd, mha_fwd, mha_bwd, sampled_softmax.
+layernorm, layernorm_bwd, ssd_fwd, ssd_bwd, mha_fwd, mha_bwd, sampled_softmax.
 """
 from __future__ import annotations
 
@@ -133,12 +133,21 @@ def main():
     ms = timed(lambda: r.ranks(x, pos, tgt, shard, 1, 0), args.iters, flush)
     flops = 2.0 * rows * V * D
     out.update(ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tf, of=tag)
-  elif c == "layernorm":
+  elif c in ("layernorm", "layernorm_bwd"):
     from recml_b200.ops import norm
     x = rnd(1 << 19, 256).requires_grad_()
     w, b = torch.ones(256, device="cuda", requires_grad=True), torch.zeros(256, device="cuda", requires_grad=True)
-    ms = timed(lambda: norm.layer_norm(x.detach(), w, b, 1e-6), args.iters, flush)
-    bytes_ = x.numel() * 4
+    if c == "layernorm":
+      ms = timed(lambda: norm.layer_norm(x.detach(), w, b, 1e-6), args.iters, flush)
+      bytes_ = x.numel() * 4                  # bf16 in + bf16 out
+    else:                                     # forward + backward: x, dy in; y, dx out (+ statistics)
+      dy = rnd(1 << 19, 256)
+
+      def fb():
+        x.grad = w.grad = b.grad = None
+        norm.layer_norm(x, w, b, 1e-6).backward(dy)
+      ms = timed(fb, args.iters, flush)
+      bytes_ = x.numel() * 2 * 5              # forward: x in, y out; backward: x, dy in, dx out
     out.update(ms=ms, gbs=bytes_ / ms / 1e6, frac=bytes_ / ms / 1e6 / hbm, of=tag)
   elif c in ("ssd_fwd", "ssd_bwd"):
     from recml_b200.ops import ssd
