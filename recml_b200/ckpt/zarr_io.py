@@ -147,11 +147,14 @@ def read_region(path: str, start: Sequence[int] | None = None,
   start = [0] * nd if start is None else list(start)
   stop = list(shape) if stop is None else list(stop)
   out = np.empty([b - a for a, b in zip(start, stop)], dtype=dt)
+  if out.size == 0:                      # an empty leaf (or an empty request) has no chunk to read
+    t = torch.from_numpy(out)
+    return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd >= 1 and comp is None and _read_rows_native(path, shape, chunks, dt, start, stop, out):
     t = torch.from_numpy(out)
     return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd == 0:
-    out = _read_chunk(path, [], [], dt, comp).reshape(())
+    out = np.array(_read_chunk(path, [], [], dt, comp).reshape(()))      # a writable 0-d copy
   else:
     lo = [a // c for a, c in zip(start, chunks)]
     hi = [(b - 1) // c for b, c in zip(stop, chunks)]
@@ -165,7 +168,7 @@ def read_region(path: str, start: Sequence[int] | None = None,
       dst = tuple(slice(max(a, o) - a, min(b, o + c, s) - a)
                   for a, b, o, c, s in zip(start, stop, c0, chunks, shape))
       out[dst] = data[src]
-  t = torch.from_numpy(np.ascontiguousarray(out))
+  t = torch.from_numpy(out)            # `out` is contiguous and owned here (ascontiguousarray would turn 0-d into 1-d)
   return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
 
 

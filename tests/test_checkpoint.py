@@ -120,3 +120,16 @@ def test_row_range_reads_match_general_path(tmp_path):
   os.remove(os.path.join(path, "2.0"))
   with pytest.raises(FileNotFoundError):
     zarr_io.read_region(path, [0, 0], [1000, 24])
+
+
+def test_edge_case_leaves_round_trip(tmp_path):
+  """Empty arrays, 0-d scalars (they stay 0-d), bf16 and integer leaves, nested containers."""
+  state = {"empty": torch.zeros(0, 4), "half": torch.randn(5, 3).to(torch.bfloat16), "count": torch.tensor(7),
+           "grid": torch.arange(10).view(2, 5), "nested": {"v": torch.randn(3), "rate": torch.tensor(2.5)}}
+  m = ckpt.CheckpointManager(str(tmp_path))
+  m.save(1, state)
+  m.wait_until_finished()
+  out = m.restore(1)
+  for got, want in ((out[k], state[k]) for k in ("empty", "half", "count", "grid")):
+    assert got.dtype == want.dtype and got.shape == want.shape and torch.equal(got, want)
+  assert torch.equal(out["nested"]["v"], state["nested"]["v"]) and out["nested"]["rate"].shape == ()
