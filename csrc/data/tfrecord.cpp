@@ -140,7 +140,9 @@ void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floa
         }
       } else if (kind == 2 && floats != nullptr) {
         if (wire == 2) {         // packed floats
-          for (size_t i = 0; i + 4 <= pl.n; i += 4) { float v; memcpy(&v, pl.p + i, 4); floats->push_back(v); }
+          const size_t at = floats->size(), n_vals = pl.n / 4;
+          floats->resize(at + n_vals);
+          if (n_vals) memcpy(floats->data() + at, pl.p, n_vals * 4);
         } else if (wire == 5) {
           float v; memcpy(&v, pl.p, 4); floats->push_back(v);
         }
