@@ -90,8 +90,10 @@ def _loader(pattern, per_rank_batch, cfg, rank, world, training, steps=None):
   else:
     src = criteo.synthetic_loader(per_rank_batch, cfg.vocab_sizes, cfg.bag_sizes, steps=steps, rank=rank,
                                   seed=0 if training else 1)
-  return criteo.ThreadedProducer(src, num_workers=FLAGS.producer_workers, depth=FLAGS.producer_depth,
-                                 pin=torch.cuda.is_available())
+  # queued batches sit in pinned memory: keep the queue under 4 GiB whatever the batch size
+  batch_bytes = per_rank_batch * (4 * sum(cfg.bag_sizes) + 4 * 13 + 8)
+  depth = max(4, min(FLAGS.producer_depth, (4 << 30) // max(1, batch_bytes)))
+  return criteo.ThreadedProducer(src, num_workers=FLAGS.producer_workers, depth=depth, pin=torch.cuda.is_available())
 
 
 def evaluate(task, part, state, loader, max_steps: int) -> dict[str, float]:
