@@ -55,6 +55,11 @@ def cuda_lib_path() -> str:
   return os.path.join(LIB_DIR, "librecml_cuda.so")
 
 
+def _read_text(path: str) -> str:
+  with open(path) as f:
+    return f.read()
+
+
 def host_lib_path() -> str:
   return os.path.join(LIB_DIR, "librecml_host.so")
 
@@ -108,7 +113,7 @@ def build(verbose: bool = False, force: bool = False, only: tuple[str, ...] = ("
       continue
     want = _digest(srcs + hdrs, name)
     stamp = lib + ".sha"
-    if not force and os.path.exists(lib) and os.path.exists(stamp) and open(stamp).read() == want:
+    if not force and os.path.exists(lib) and os.path.exists(stamp) and _read_text(stamp) == want:
       out[name] = lib
       continue
     if name == "cuda" and not os.path.exists(_nvcc()):
