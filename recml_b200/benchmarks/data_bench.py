@@ -1,6 +1,7 @@
 """Host input pipeline throughput (CPU only): TFRecord indexing + CRC check and `tf.Example` parsing of
 Criteo-shaped per-example records (1 label, 13 float features, 26 variable-length id features) by the
-native parser, one call per feature versus one pass for all features.
+native parser, one call per feature versus one pass for all features, the dataset factory end to end, and the
+loader of pre-batched Criteo records.
 
   python -m recml_b200.benchmarks.data_bench [--examples N] [--threads T]
 
@@ -59,7 +60,20 @@ def run(examples: int = 20000, seed: int = 0) -> dict:
     for _ in range(n_batches):
       next(it)
     t_fac = time.perf_counter() - t
-  return {"examples": examples, "factory_examples_per_s": n_batches * 4096 / t_fac, "file_mb": size / 1e6, "features": len(specs),
+    # pre-batched Criteo records (one record = one batch of 4096 samples, 214 ids per sample) through the loader
+    from recml_b200.data import criteo
+    hot = [3, 2, 1, 2, 6, 1, 1, 1, 1, 7, 3, 8, 1, 6, 9, 5, 1, 1, 1, 12, 100, 27, 10, 3, 1, 1]
+    cpath, B = os.path.join(d, "criteo.tfrecord"), 4096
+    tfrecord.write_tfrecord(cpath, [criteo.encode_record(rng.integers(0, 2, B), rng.normal(size=(B, 13)).astype(np.float32),
+                                                         [rng.integers(0, 1000, (B, m)) for m in hot]) for _ in range(4)])
+    it = iter(criteo.CriteoDataLoader(cpath, B, vocab_sizes=[1000] * 26, multi_hot_sizes=hot, is_training=True, shuffle_buffer=1))
+    next(it)
+    t = time.perf_counter()
+    for _ in range(16):
+      next(it)
+    t_criteo = time.perf_counter() - t
+  return {"examples": examples, "factory_examples_per_s": n_batches * 4096 / t_fac,
+          "criteo_prebatched_samples_per_s": 16 * B / t_criteo, "file_mb": size / 1e6, "features": len(specs),
           "index_crc_ms": t_index * 1e3, "index_crc_mb_per_s": size / 1e6 / t_index,
           "per_feature_parse_examples_per_s": examples / t_each,
           "one_pass_parse_examples_per_s": examples / best, "one_pass_mb_per_s": size / 1e6 / best,
