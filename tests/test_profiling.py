@@ -30,7 +30,7 @@ def test_report_progress_rates_and_shares():
     time.sleep(0.03)
   time.sleep(0.04)
   rp(10)
-  assert rp.steps_per_sec is not None and 50 < rp.steps_per_sec < 400
+  assert rp.steps_per_sec is not None and 1 < rp.steps_per_sec < 400
 
 
 def test_trace_writes_a_chrome_trace(tmp_path):
