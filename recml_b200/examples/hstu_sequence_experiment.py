@@ -24,7 +24,10 @@ from recml_b200 import config as C
 from recml_b200 import metrics as metrics_lib
 from recml_b200.data import tfrecord, tfrecord_factory as F
 from recml_b200.layers import hstu as hstu_layers
-from recml_b200.training import core, module_trainer, optim_factory
+from recml_b200.training import core, module_trainer, optim_factory, partitioning
+from recml_b200.training import state as state_lib
+from recml_b200.training import task as task_lib
+from recml_b200.training import trainer as trainer_lib
 
 
 @dataclasses.dataclass
@@ -110,6 +113,58 @@ class HSTUSequenceTask(module_trainer.ModuleTask):
         optim_factory.AdamFactory(learning_rate=self.config.learning_rate).make(),
         {"accuracy": lambda y, logits: metrics_lib.accuracy(y.long(), logits.float()),
          "top_10_accuracy": lambda y, logits: metrics_lib.top_k_accuracy(y.long(), logits.float(), k=10)})
+
+
+class HSTUSequenceStepTask(task_lib.Task):
+  """The same model and data under the step-function trainer (`recml/examples/train_hstu_jax.py:60-200`):
+  explicit `create_state` / `train_step` / `eval_step` instead of compile-and-fit."""
+
+  def __init__(self, model_config: HSTUModelConfig, train_data: SequenceDataFactory, eval_data: SequenceDataFactory):
+    self.config, self.train_data, self.eval_data = model_config, train_data, eval_data
+
+  def create_datasets(self):
+    return self.train_data.make(), self.eval_data.make()
+
+  def create_state(self, batch, rng):
+    torch.manual_seed(rng.initial_seed())
+    model = LastPositionHSTU(self.config).to(batch[1].device)
+    return state_lib.State.create(model=model, tx=optim_factory.AdamFactory(learning_rate=self.config.learning_rate).make())
+
+  @staticmethod
+  def _metrics(logits, y):
+    loss = nn.functional.cross_entropy(logits.float(), y.long())
+    n = torch.tensor(float(y.numel()), device=y.device)
+    return loss, {"loss": metrics_lib.Mean(total=loss.detach() * n, count=n),
+                  "accuracy": metrics_lib.accuracy(y.long(), logits.detach().float())}
+
+  def train_step(self, batch, state, rng):
+    state.model.train()
+    x, y = batch
+    loss, ms = self._metrics(state.model(x), y)
+    loss.backward()
+    state.update()
+    return state, ms
+
+  def eval_step(self, batch, state):
+    state.model.eval()
+    x, y = batch
+    with torch.no_grad():
+      return self._metrics(state.model(x), y)[1]
+
+
+def step_experiment(train_path: str = "/tmp/hstu_train-*.tfrecord", eval_path: str = "/tmp/hstu_eval-*.tfrecord",
+                    model_dir: str = "/tmp/hstu_sequence_steps", vocab_size: int = 5_000_000, batch_size: int = 128,
+                    train_steps: int = 2000) -> C.Config:
+  max_len = 50
+  model = C.Config(HSTUModelConfig, vocab_size=vocab_size, max_sequence_length=max_len, model_dim=64, num_layers=4)
+  task = C.Config(HSTUSequenceStepTask, model_config=model,
+                  train_data=C.Config(SequenceDataFactory, input_path=train_path, batch_size=batch_size,
+                                      max_sequence_length=max_len, is_training=True),
+                  eval_data=C.Config(SequenceDataFactory, input_path=eval_path, batch_size=batch_size,
+                                     max_sequence_length=max_len, is_training=False))
+  trainer = C.Config(trainer_lib.Trainer, partitioner=C.Config(partitioning.DataParallelPartitioner), model_dir=model_dir,
+                     train_steps=train_steps, steps_per_loop=100, steps_per_eval=10)
+  return C.Config(core.Experiment, task=task, trainer=trainer)
 
 
 def write_synthetic_tfrecords(path: str, num_examples: int, vocab_size: int, max_len: int = 60, seed: int = 0) -> None:

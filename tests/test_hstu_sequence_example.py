@@ -51,3 +51,20 @@ def test_experiment_trains_and_evaluates(tmp_path):
   assert "val_loss" in hist and "val_accuracy" in hist
   assert hist["loss"][-1] < np.log(vocab)                  # better than the uniform guess
   assert os.path.isdir(os.path.join(tmp_path, "model", "checkpoints"))
+
+
+def test_step_trainer_variant_trains(tmp_path):
+  vocab = 40
+  E.write_synthetic_tfrecords(str(tmp_path / "data" / "train-0.tfrecord"), 600, vocab, max_len=12, seed=0)
+  E.write_synthetic_tfrecords(str(tmp_path / "data" / "eval-0.tfrecord"), 128, vocab, max_len=12, seed=1)
+  cfg = E.step_experiment(train_path=str(tmp_path / "data" / "train-*.tfrecord"),
+                          eval_path=str(tmp_path / "data" / "eval-*.tfrecord"), model_dir=str(tmp_path / "model"),
+                          vocab_size=vocab, batch_size=32, train_steps=90)
+  for part in (cfg.task.model_config, cfg.task.train_data, cfg.task.eval_data):
+    part.max_sequence_length = 10
+  cfg.task.model_config.model_dim, cfg.task.model_config.num_layers = 32, 1
+  cfg.task.model_config.dropout, cfg.task.model_config.learning_rate = 0.0, 5e-3
+  cfg.trainer.steps_per_loop, cfg.trainer.steps_per_eval = 30, 4
+  cfg.trainer.partitioner = C.Config(recml.DataParallelPartitioner, device="cpu")
+  logs = recml.run_experiment(C.build(cfg), "train_and_eval")
+  assert logs["train"]["loss"] < np.log(vocab) and "accuracy" in logs["val"]
