@@ -81,4 +81,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Kernels meant to share the SMs with a tensor-core GEMM of another stream ask for the largest shared-memory
+// carve-out although they need little of it: an SM keeps one L1 / shared-memory split for all the blocks
+// resident on it, so a kernel that configured it for a large L1 would keep the GEMM's CTAs (which need
+// ~210 KB of shared memory) off that SM until it has drained.
+template <typename Kernel>
+inline void prefer_max_shared_carveout(Kernel kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 }  // namespace recml

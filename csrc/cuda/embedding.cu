@@ -12,10 +12,11 @@
 //            concat input (emb_combine)
 //   backward rank s pushes each feature's activation gradient to the rank(s) owning that
 //            feature (emb_push_grads)                                                   flag chan 2
-//            owners radix-sort the occurrence list by row, reduce each run of equal rows in
+//            owners radix-sort the occurrence list by row (radix_sort.cu; it only needs the forward's
+//            output, so it runs beside the dense forward pass), reduce each run of equal rows in
 //            fp32 and apply the row optimizer in the same kernel (emb_bwd_update/finalize).
 // Peer flags are monotonically increasing sequence numbers; all waits are bounded.
-#include <cub/device/device_radix_sort.cuh>
+#include <cstdio>
 
 #include "common.cuh"
 
@@ -109,6 +110,29 @@ __device__ __forceinline__ Vec<VPL> load_bf16(const __nv_bfloat16* p) {
   }
   return r;
 }
+// Raw (still packed) bf16 elements of one lane: kept packed while several loads are in flight, so a batch of
+// loads costs half the registers of converted floats.
+template <int VPL> struct RawBf16 { uint32_t w[(VPL + 1) / 2]; };
+template <int VPL>
+__device__ __forceinline__ RawBf16<VPL> load_raw_bf16(const __nv_bfloat16* p) {
+  RawBf16<VPL> r;
+  if constexpr (VPL == 1) { r.w[0] = *reinterpret_cast<const unsigned short*>(p); }
+  else if constexpr (VPL == 2) { r.w[0] = *reinterpret_cast<const uint32_t*>(p); }
+  else if constexpr (VPL == 4) { const uint2 t = *reinterpret_cast<const uint2*>(p); r.w[0] = t.x; r.w[1] = t.y; }
+  else { const uint4 t = *reinterpret_cast<const uint4*>(p); r.w[0] = t.x; r.w[1] = t.y; r.w[2] = t.z; r.w[3] = t.w; }
+  return r;
+}
+template <int VPL>
+__device__ __forceinline__ void fma_raw_bf16(Vec<VPL>& acc, float gain, const RawBf16<VPL>& r) {
+  if constexpr (VPL == 1) { acc.v[0] = fmaf(gain, bf16_lo(r.w[0]), acc.v[0]); }
+  else {
+#pragma unroll
+    for (int i = 0; i < VPL / 2; ++i) {
+      acc.v[2 * i] = fmaf(gain, bf16_lo(r.w[i]), acc.v[2 * i]);
+      acc.v[2 * i + 1] = fmaf(gain, bf16_hi(r.w[i]), acc.v[2 * i + 1]);
+    }
+  }
+}
 template <int VPL>
 __device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const Vec<VPL>& r) {
   if constexpr (VPL == 1) { *p = __float2bfloat16(r.v[0]); }
@@ -125,6 +149,13 @@ __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
   return x;
+}
+
+// Asks L2 for the 128-byte lines of [ptr, ptr + bytes): issued a window ahead of the loads that need them, so
+// those loads pay the L2 latency instead of the DRAM one.
+__device__ __forceinline__ void prefetch_l2(const void* ptr, int bytes) {
+  const char* c = static_cast<const char*>(ptr);
+  for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
 }
 
 // Raises flag[chan][me] = seq on every rank once ALL blocks of the grid have finished their stores.
@@ -219,6 +250,10 @@ struct FwdParams {
   const unsigned long long* wait_flags;   // ids channel (null: no wait)
   unsigned int* done_counter; PeerFlags flags; SeqRef seq;  // pooled channel; the ids channel uses the same number
   int* status;
+  unsigned int* dropped;    // non-null: ids that do not fit the occurrence list are dropped from the lookup and
+                            // counted here (allow_id_dropping); null: an overflow is a kCapacity error
+  int prefetch;             // 1: ask L2 for a bag's rows as soon as their ids are known
+  int pad;
 };
 
 template <int VPL, bool TRAIN, bool GAINS>
@@ -280,27 +315,36 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         lrow = f.row_base + id;
       }
       if (f.seq_len > 0 && i - o0 >= f.seq_len) owned = false;
+      if (owned && p.prefetch) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
       unsigned int mask = __ballot_sync(0xffffffffu, owned);
       if (TRAIN && mask != 0) {
+        // claim room in the occurrence list; the count may run past the capacity (readers clamp it), and
+        // exactly the entries below the capacity get written
         const int n_own = __popc(mask);
         unsigned int pos = 0;
         if (lane == 0) pos = atomicAdd(p.occ_count, static_cast<unsigned int>(n_own));
         pos = __shfl_sync(0xffffffffu, pos, 0);
-        if (pos + n_own <= p.occ_cap) {
-          if (owned) {
-            const unsigned int at = pos + __popc(mask & ((1u << lane) - 1));
-            p.occ_key[at] = lrow;
-            const unsigned int gv = static_cast<unsigned int>(gv_base + (f.seq_len > 0 ? (i - o0) * gv_step : 0));
-            if (GAINS) {
-              p.occ_val[at] = at;                       // index into (occ_gv = occ_key slot of vals, gain)
-              p.occ_gain[2 * static_cast<size_t>(at)] = __uint_as_float(gv);
-              p.occ_gain[2 * static_cast<size_t>(at) + 1] = w;
-            } else {
-              p.occ_val[at] = gv;
-            }
+        const unsigned int at = pos + __popc(mask & ((1u << lane) - 1));
+        const bool fits = owned && at < p.occ_cap;
+        if (fits) {
+          p.occ_key[at] = lrow;
+          const unsigned int gv = static_cast<unsigned int>(gv_base + (f.seq_len > 0 ? (i - o0) * gv_step : 0));
+          if (GAINS) {
+            p.occ_val[at] = at;                       // index into (occ_gv = occ_key slot of vals, gain)
+            p.occ_gain[2 * static_cast<size_t>(at)] = __uint_as_float(gv);
+            p.occ_gain[2 * static_cast<size_t>(at) + 1] = w;
+          } else {
+            p.occ_val[at] = gv;
           }
-        } else {
-          report(p.status, kCapacity, 1);
+        }
+        const unsigned int over = __ballot_sync(0xffffffffu, owned && !fits);
+        if (over != 0) {
+          if (p.dropped != nullptr) {
+            if (lane == 0) atomicAdd(p.dropped, static_cast<unsigned int>(__popc(over)));
+            mask &= ~over;      // dropped ids take no part in the lookup either
+          } else {
+            report(p.status, kCapacity, 1);
+          }
         }
       }
       if (f.seq_len > 0) {
@@ -326,24 +370,25 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         }
         continue;
       }
-      // gather owned rows, four at a time so several loads are in flight
+      // gather owned rows, several at a time so that many loads are in flight
+      constexpr int kDepth = VPL <= 4 ? 8 : 4;
       while (mask) {
-        int j[4]; unsigned int rj[4]; float wj[4];
+        int j[kDepth]; unsigned int rj[kDepth]; float wj[kDepth];
         int n = 0;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kDepth; ++u) {
           j[u] = mask ? __ffs(mask) - 1 : 0;
           if (mask) { mask &= mask - 1; n = u + 1; }
           rj[u] = __shfl_sync(0xffffffffu, lrow, j[u]);
           wj[u] = __shfl_sync(0xffffffffu, w, j[u]);
         }
         if (lane_on) {
-          Vec<VPL> r[4];
+          Vec<VPL> r[kDepth];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < kDepth; ++u)
             if (u < n) r[u] = load_f32<VPL>(p.table + static_cast<size_t>(rj[u]) * p.dloc + lane * VPL);
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < kDepth; ++u)
             if (u < n) {
 #pragma unroll
               for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? wj[u] : 1.f, r[u].v[e], acc.v[e]);
@@ -457,7 +502,19 @@ struct BwdParams {
   int opt; float hp[6]; float grad_scale; int slot1_rowwise;
   float* scratch;               // [>= ceil(n / kRange), dloc] partial sums of runs that cross range boundaries (kept zero)
   const unsigned long long* wait_flags; int W; SeqRef seq; int* status;
+  const float* hp_dev;          // non-null: the six hyper-parameters are read from device memory (so that a
+                                // captured CUDA graph follows a learning-rate schedule) instead of `hp`
+  unsigned int n_cap;           // >0: *n_occ is clamped to this (capacity of the occurrence list)
+  int pad;
 };
+
+__device__ __forceinline__ float hpv(const BwdParams& p, int i) {
+  return p.hp_dev != nullptr ? __ldg(p.hp_dev + i) : p.hp[i];
+}
+__device__ __forceinline__ unsigned int occ_count_of(const BwdParams& p) {
+  const unsigned int n = *p.n_occ;
+  return p.n_cap > 0 && n > p.n_cap ? p.n_cap : n;
+}
 
 template <int VPL>
 __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned int row, Vec<VPL> g, int lane,
@@ -472,7 +529,7 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
 #pragma unroll
     for (int e = 0; e < VPL; ++e) sq += g.v[e] * g.v[e];
   }
-  const float lr = p.hp[0];
+  const float lr = hpv(p, 0);
   switch (p.opt) {
     case kSGD:
       if (lane_on) {
@@ -485,7 +542,7 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
       const float s = p.slot0[row] + msq;
       __syncwarp();
       if (lane == 0) p.slot0[row] = s;
-      const float inv = lr / (sqrtf(s) + p.hp[1]);
+      const float inv = lr / (sqrtf(s) + hpv(p, 1));
       if (lane_on) {
 #pragma unroll
         for (int e = 0; e < VPL; ++e) w.v[e] -= inv * g.v[e];
@@ -502,7 +559,7 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
       break;
     case kAdam:
     case kRowAdam: {
-      const float b1 = p.hp[1], b2 = p.hp[2], eps = p.hp[3];
+      const float b1 = hpv(p, 1), b2 = hpv(p, 2), eps = hpv(p, 3);
       float vrow = 0.f;
       if (p.opt == kRowAdam) {
         const float msq = warp_sum(sq) / p.dloc;
@@ -529,8 +586,8 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
     }
     case kAdagradMomentum:
       if (lane_on) {
-        const float k = p.hp[1], beta2 = p.hp[2], eps = p.hp[3], expo = p.hp[4];
-        const bool nesterov = p.hp[5] != 0.f;
+        const float k = hpv(p, 1), beta2 = hpv(p, 2), eps = hpv(p, 3), expo = hpv(p, 4);
+        const bool nesterov = hpv(p, 5) != 0.f;
         Vec<VPL> a = load_f32_rw<VPL>(p.slot0 + off), mo = load_f32_rw<VPL>(p.slot1 + off);
 #pragma unroll
         for (int e = 0; e < VPL; ++e) {
@@ -546,8 +603,8 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
       break;
     case kFTRL:
       if (lane_on) {
-        const float lrp = p.hp[1], l1 = p.hp[2], l2 = p.hp[3], beta = p.hp[4];
-        const bool mult = p.hp[5] != 0.f;
+        const float lrp = hpv(p, 1), l1 = hpv(p, 2), l2 = hpv(p, 3), beta = hpv(p, 4);
+        const bool mult = hpv(p, 5) != 0.f;
         Vec<VPL> a = load_f32_rw<VPL>(p.slot0 + off), li = load_f32_rw<VPL>(p.slot1 + off);
 #pragma unroll
         for (int e = 0; e < VPL; ++e) {
@@ -566,7 +623,7 @@ __device__ __forceinline__ void apply_row_update(const BwdParams& p, unsigned in
       break;
     case kLaProp:
       if (lane_on) {
-        const float b1 = p.hp[1], decay = p.hp[2], eps = p.hp[3];
+        const float b1 = hpv(p, 1), decay = hpv(p, 2), eps = hpv(p, 3);
         Vec<VPL> mu = load_f32_rw<VPL>(p.slot0 + off), nu = load_f32_rw<VPL>(p.slot1 + off);
 #pragma unroll
         for (int e = 0; e < VPL; ++e) {
@@ -594,85 +651,119 @@ __device__ __forceinline__ unsigned int lower_bound(const uint32_t* keys, unsign
 }
 
 // One warp per RANGE of kRange sorted occurrences, walked in 32-wide windows with the running sum
-// carried across windows.  A run of equal rows that lies inside the range is reduced in registers
-// and applied at once; the pieces of a run that crosses range boundaries are added (fp32 atomics)
-// into the scratch line of the range where the run STARTS, and emb_bwd_finalize applies those
-// afterwards.  Hot rows (Zipf heads with 10^5 occurrences) are thereby reduced by thousands of
-// warps in parallel, with one atomic line update per kRange occurrences.
+// carried across windows; a persistent grid strides over the ranges.  A run of equal rows that lies
+// inside the range is reduced in registers and applied at once; the pieces of a run that crosses
+// range boundaries are added (fp32 atomics) into the scratch line of the range where the run STARTS,
+// and emb_bwd_finalize applies those afterwards.  Hot rows (Zipf heads with 10^5 occurrences) are
+// thereby reduced by thousands of warps in parallel, with one atomic line update per kRange
+// occurrences.
+//
+// The kernel is bound by memory latency (random 256-byte gradient vectors, random table rows), so
+// every window first asks L2 for what the NEXT window will read (its gradient vectors) and for the
+// table rows and optimizer slots of the runs that end in THIS window; the loads that follow then wait
+// for L2, not DRAM.  It uses no shared memory and at most 64 registers so that it can share the SMs with a
+// tensor-core GEMM running on another stream: beside this library's GEMM CTA (320 threads x 104 registers,
+// ~210 KB of shared memory) an SM was measured to take three 128-thread blocks of 64 registers, but not
+// three of 80 (`blocks_per_sm` caps the grid accordingly).
 constexpr unsigned int kRange = 128;
+constexpr int kBwdThreads = 128;
 
 template <int VPL, bool GAINS>
-__global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 8) emb_bwd_update_kernel(const BwdParams p) {
   if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 2)) return;
   const int lane = threadIdx.x & 31;
-  const unsigned int n = *p.n_occ;
-  const unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const unsigned int start = range * kRange;
-  if (start >= n) return;
-  const unsigned int end = min(start + kRange, n);
+  const unsigned int n = occ_count_of(p);
+  const unsigned int warps = (gridDim.x * blockDim.x) >> 5;
   const bool lane_on = lane * VPL < p.dloc;
-  const bool has_prev = start > 0, has_next = end < n;
-  const uint32_t prev_key = has_prev ? p.keys[start - 1] : 0;
-  const uint32_t next_key = has_next ? p.keys[end] : 0;
-  Vec<VPL> acc;
+  const int grad_bytes = p.dloc * 2, row_bytes = p.dloc * 4;
+  const bool slot0_row = p.opt == kRowAdagrad, slot1_row = p.opt == kRowAdam;
+  constexpr int kBatch = VPL <= 4 ? 8 : 4;
+  for (unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; range * kRange < n; range += warps) {
+    const unsigned int start = range * kRange;
+    const unsigned int end = min(start + kRange, n);
+    const bool has_prev = start > 0, has_next = end < n;
+    const uint32_t prev_key = has_prev ? p.keys[start - 1] : 0;
+    const uint32_t next_key = has_next ? p.keys[end] : 0;
+    Vec<VPL> acc;
 #pragma unroll
-  for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-  bool first_run = true;      // no run has been closed yet: the open one may have begun before `start`
-  for (unsigned int w0 = start; w0 < end; w0 += 32u) {
-    const int cnt = static_cast<int>(min(32u, end - w0));
-    uint32_t key = 0xffffffffu, val = 0;
-    if (lane < cnt) { key = p.keys[w0 + lane]; val = p.vals[w0 + lane]; }
-    unsigned int gv = val;
-    float gain = 1.f;
-    if (GAINS && lane < cnt) {
-      gv = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
-      gain = p.occ_gain[2 * static_cast<size_t>(val) + 1];
-    }
-    const bool window_is_last = w0 + cnt >= end;
-    // key that follows this window inside the range (only read when there is one)
-    const uint32_t after = window_is_last ? 0u : p.keys[w0 + cnt];
-    for (int j0 = 0; j0 < cnt; j0 += 4) {
-      Vec<VPL> g[4]; uint32_t kj[4]; float gj[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int j = min(j0 + u, cnt - 1);
-        kj[u] = __shfl_sync(0xffffffffu, key, j);
-        const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
-        gj[u] = __shfl_sync(0xffffffffu, gain, j);
-        if (lane_on && j0 + u < cnt) g[u] = load_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int j = j0 + u;
-        if (j >= cnt) break;
-        if (lane_on) {
-#pragma unroll
-          for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(GAINS ? gj[u] : 1.f, g[u].v[e], acc.v[e]);
+    for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+    bool first_run = true;      // no run has been closed yet: the open one may have begun before `start`
+    // this window's entries; the next window's are fetched one window ahead
+    uint32_t key = 0xffffffffu; unsigned int gv = 0; float gain = 1.f;
+    auto fetch = [&](unsigned int w0, uint32_t& k, unsigned int& g, float& gn) {
+      k = 0xffffffffu; g = 0; gn = 1.f;
+      if (w0 + lane < end) {
+        k = p.keys[w0 + lane];
+        const uint32_t val = p.vals[w0 + lane];
+        g = val;
+        if (GAINS) {
+          g = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
+          gn = p.occ_gain[2 * static_cast<size_t>(val) + 1];
         }
-        const uint32_t knext = __shfl_sync(0xffffffffu, key, min(j + 1, 31));
-        const bool at_range_end = window_is_last && j == cnt - 1;
-        const bool last = at_range_end || ((j == cnt - 1) ? (after != kj[u]) : (knext != kj[u]));
-        if (!last) continue;
-        const bool begins = !first_run || !has_prev || (prev_key != kj[u]);
-        const bool ends = !at_range_end || !has_next || (next_key != kj[u]);
-        if (begins && ends) {
-          apply_row_update<VPL>(p, kj[u], acc, lane, lane_on);
-        } else {
-          unsigned int slot = range;
-          if (!begins) {
-            if (lane == 0) slot = lower_bound(p.keys, start, kj[u]) / kRange;
-            slot = __shfl_sync(0xffffffffu, slot, 0);
-          }
-          if (lane_on) {
-            float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
+        prefetch_l2(p.grads + static_cast<size_t>(g) * p.val_scale, grad_bytes);
+      }
+    };
+    fetch(start, key, gv, gain);
+    for (unsigned int w0 = start; w0 < end; w0 += 32u) {
+      const int cnt = static_cast<int>(min(32u, end - w0));
+      const bool window_is_last = w0 + cnt >= end;
+      uint32_t nkey = 0xffffffffu; unsigned int ngv = 0; float ngain = 1.f;
+      if (!window_is_last) fetch(w0 + 32u, nkey, ngv, ngain);
+      // which entries end a run (inside the range; the range's last entry always closes the open piece)
+      const uint32_t after = __shfl_sync(0xffffffffu, nkey, 0);
+      uint32_t knext = __shfl_down_sync(0xffffffffu, key, 1);
+      if (lane == cnt - 1) knext = after;
+      const bool ends_run = lane < cnt && ((window_is_last && lane == cnt - 1) || knext != key);
+      const unsigned int last_mask = __ballot_sync(0xffffffffu, ends_run);
+      if (ends_run) {
+        prefetch_l2(p.table + static_cast<size_t>(key) * p.dloc, row_bytes);
+        if (p.slot0 != nullptr) {
+          if (slot0_row) prefetch_l2(p.slot0 + key, 4); else prefetch_l2(p.slot0 + static_cast<size_t>(key) * p.dloc, row_bytes);
+        }
+        if (p.slot1 != nullptr) {
+          if (slot1_row) prefetch_l2(p.slot1 + key, 4); else prefetch_l2(p.slot1 + static_cast<size_t>(key) * p.dloc, row_bytes);
+        }
+      }
+      for (int j0 = 0; j0 < cnt; j0 += kBatch) {
+        RawBf16<VPL> g[kBatch]; float gj[kBatch];
 #pragma unroll
-            for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
-          }
+        for (int u = 0; u < kBatch; ++u) {
+          const int j = min(j0 + u, cnt - 1);
+          const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
+          gj[u] = GAINS ? __shfl_sync(0xffffffffu, gain, j) : 1.f;
+          if (lane_on && j0 + u < cnt)
+            g[u] = load_raw_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
         }
 #pragma unroll
-        for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-        first_run = false;
+        for (int u = 0; u < kBatch; ++u) {
+          const int j = j0 + u;
+          if (j >= cnt) break;
+          if (lane_on) fma_raw_bf16<VPL>(acc, gj[u], g[u]);
+          if (!((last_mask >> j) & 1u)) continue;
+          const uint32_t kj = __shfl_sync(0xffffffffu, key, j);
+          const bool at_range_end = window_is_last && j == cnt - 1;
+          const bool begins = !first_run || !has_prev || (prev_key != kj);
+          const bool ends = !at_range_end || !has_next || (next_key != kj);
+          if (begins && ends) {
+            apply_row_update<VPL>(p, kj, acc, lane, lane_on);
+          } else {
+            unsigned int slot = range;
+            if (!begins) {
+              if (lane == 0) slot = lower_bound(p.keys, start, kj) / kRange;
+              slot = __shfl_sync(0xffffffffu, slot, 0);
+            }
+            if (lane_on) {
+              float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
+#pragma unroll
+              for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+          first_run = false;
+        }
       }
+      key = nkey; gv = ngv; gain = ngain;
     }
   }
 }
@@ -680,7 +771,7 @@ __global__ void __launch_bounds__(256) emb_bwd_update_kernel(const BwdParams p) 
 template <int VPL>
 __global__ void __launch_bounds__(256) emb_bwd_finalize_kernel(const BwdParams p) {
   const int lane = threadIdx.x & 31;
-  const unsigned int n = *p.n_occ;
+  const unsigned int n = occ_count_of(p);
   const unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const unsigned int start = range * kRange;
   if (start >= n) return;
@@ -767,38 +858,45 @@ extern "C" int recml_emb_combine(const CombineParams* p, cudaStream_t stream) {
 }
 
 extern "C" int recml_emb_push_grads(const PushGradParams* p, cudaStream_t stream) {
-  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 8);
+  static bool configured = false;
+  if (!configured) { recml::prefer_max_shared_carveout(emb_push_grads_kernel); configured = true; }
+  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 4);
   emb_push_grads_kernel<<<blocks, 256, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-extern "C" long long recml_sort_temp_bytes(long long n) {
-  size_t bytes = 0;
-  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
-                                  static_cast<const uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr), n);
-  return static_cast<long long>(bytes);
-}
-
-extern "C" int recml_sort_pairs_u32(const uint32_t* keys_in, uint32_t* keys_out, const uint32_t* vals_in,
-                                    uint32_t* vals_out, long long n, int end_bit, void* temp,
-                                    long long temp_bytes, cudaStream_t stream) {
-  size_t bytes = static_cast<size_t>(temp_bytes);
-  cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, bytes, keys_in, keys_out, vals_in, vals_out, n, 0, end_bit, stream);
-  return e == cudaSuccess ? 0 : -1;
-}
-
-// max_occ: host-side upper bound of *n_occ used to size the grid (ranges beyond n exit at once).
-extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int gains, cudaStream_t stream) {
+// max_occ: host-side upper bound of *n_occ used to size the grid (the persistent grid strides over the ranges
+// that exist).  blocks_per_sm: resident 128-thread blocks per SM (0 = default 12); a small value (3) leaves
+// room for a GEMM CTA of another stream on every SM.
+extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int gains, int blocks_per_sm,
+                                    cudaStream_t stream) {
   const int vpl = vpl_for(p->dloc);
   if (vpl == 0 || (p->dloc % vpl) != 0) return -10;
   if (max_occ <= 0) return 0;
   const long long ranges = (max_occ + kRange - 1) / kRange;
-  const int blocks = static_cast<int>((ranges + 7) / 8);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (blocks_per_sm <= 0) blocks_per_sm = 12;
+  long long want = (ranges + (kBwdThreads / 32) - 1) / (kBwdThreads / 32);
+  const long long cap = static_cast<long long>(sms) * blocks_per_sm;
+  const int blocks = static_cast<int>(want < cap ? want : cap);
+  const int fin_blocks = static_cast<int>((ranges + 7) / 8);
 #define RECML_BWD(V)                                                                      \
   do {                                                                                    \
-    if (gains) emb_bwd_update_kernel<V, true><<<blocks, 256, 0, stream>>>(*p);            \
-    else emb_bwd_update_kernel<V, false><<<blocks, 256, 0, stream>>>(*p);                 \
-    emb_bwd_finalize_kernel<V><<<blocks, 256, 0, stream>>>(*p);                           \
+    static bool configured = false;                                                       \
+    if (!configured) {                                                                    \
+      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, true>);                  \
+      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, false>);                 \
+      recml::prefer_max_shared_carveout(emb_bwd_finalize_kernel<V>);                      \
+      configured = true;                                                                  \
+    }                                                                                     \
+    if (gains) emb_bwd_update_kernel<V, true><<<blocks, kBwdThreads, 0, stream>>>(*p);    \
+    else emb_bwd_update_kernel<V, false><<<blocks, kBwdThreads, 0, stream>>>(*p);         \
+    emb_bwd_finalize_kernel<V><<<fin_blocks, 256, 0, stream>>>(*p);                       \
   } while (0)
   switch (vpl) {
     case 1: RECML_BWD(1); break;
@@ -825,10 +923,12 @@ extern "C" int recml_emb_struct_sizes(int* out) {
 
 namespace recml {
 namespace emb {
-// Scratch for the partial sums of row runs that cross 32-entry chunk boundaries: one line of
-// RECML_EMB_STATIC_MAX_DIM floats per chunk.  It lives in the library image, so every GPU that loads
-// the library holds these 4 MiB until the process exits.
-static __device__ __align__(256) float g_static_scratch[(RECML_EMB_STATIC_MAX_OCC / 32) * RECML_EMB_STATIC_MAX_DIM];
+// Scratch for the partial sums of row runs that cross range boundaries: one line of
+// RECML_EMB_STATIC_MAX_DIM floats per range of RECML_EMB_STATIC_RANGE (= kRange) sorted occurrences.  It
+// lives in the library image, so every GPU that loads the library holds this 1 MiB until the process exits.
+static_assert(RECML_EMB_STATIC_RANGE == kRange, "the static scratch is sized in ranges of kRange occurrences");
+static __device__ __align__(256) float
+    g_static_scratch[(RECML_EMB_STATIC_MAX_OCC / RECML_EMB_STATIC_RANGE) * RECML_EMB_STATIC_MAX_DIM];
 }  // namespace emb
 }  // namespace recml
 
@@ -872,14 +972,14 @@ extern "C" int recml_emb_bwd_update_static(const BwdParams* p, long long max_occ
     scratch = dev_addr[dev];
   }
   // The array keeps whatever the previous call left behind: clear the lines this call can touch.
-  const long long chunks = (max_occ + 31) / 32;
+  const long long chunks = (max_occ + RECML_EMB_STATIC_RANGE - 1) / RECML_EMB_STATIC_RANGE;
   if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(chunks) * p->dloc * sizeof(float), stream) != cudaSuccess) {
     static_fail(err, err_len, "cudaMemsetAsync on the static scratch failed");
     return -25;
   }
   BwdParams q = *p;
   q.scratch = scratch;
-  const int rc = recml_emb_bwd_update(&q, max_occ, gains, stream);
+  const int rc = recml_emb_bwd_update(&q, max_occ, gains, 0, stream);
   if (rc != 0) static_fail(err, err_len, "kernel launch failed");
   return rc;
 }

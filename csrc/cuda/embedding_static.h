@@ -13,10 +13,10 @@
 //
 // Same contract as recml_emb_bwd_update (sorted occurrence keys / values, gradient vectors, table
 // and optimizer slots are passed in by the caller; `p->scratch` is ignored), with these differences:
-//   * The scratch for runs of equal rows that cross 32-entry chunk boundaries is a file-scope
-//     `static __device__` array of RECML_EMB_STATIC_MAX_OCC/32 x RECML_EMB_STATIC_MAX_DIM floats
-//     (4 MiB).  It is part of the library image: every GPU that loads the library holds it until
-//     the process exits.
+//   * The kernel walks the sorted occurrences in ranges of RECML_EMB_STATIC_RANGE (128) entries.  The
+//     scratch for runs of equal rows that cross range boundaries is a file-scope `static __device__`
+//     array of RECML_EMB_STATIC_MAX_OCC/128 x RECML_EMB_STATIC_MAX_DIM floats (1 MiB).  It is part of
+//     the library image: every GPU that loads the library holds it until the process exits.
 //   * Limits: max_occ <= RECML_EMB_STATIC_MAX_OCC and p->dloc <= RECML_EMB_STATIC_MAX_DIM.  Larger
 //     requests are refused with a negative return code and a message in `err` (when given).
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine.  The first call
@@ -34,6 +34,7 @@
 
 #define RECML_EMB_STATIC_MAX_OCC 262144LL
 #define RECML_EMB_STATIC_MAX_DIM 128
+#define RECML_EMB_STATIC_RANGE 128
 
 #ifdef __cplusplus
 namespace recml { namespace emb { struct BwdParams; } }

@@ -1,19 +1,22 @@
 """Fused sharded-embedding backend: sm_100a kernels over NVLink peer memory
-(`csrc/cuda/embedding.cu`).
+(`csrc/cuda/embedding.cu`, `csrc/cuda/radix_sort.cu`).
 
 Per step:  ids are pushed to every peer (one kernel, peer stores + flag) → one forward kernel per
 table stack gathers / pools the rows this rank owns for EVERY rank's samples and stores each
 pooled bf16 vector straight into the requesting rank's buffer (the all-to-all is the store) →
 the combine kernel waits for all sources' flags, sums the per-source slots of row-sharded
-features and writes the concatenated dense input.  Backward: one kernel pushes each feature's
-activation gradient into its owner's buffer, the owner radix-sorts the (row, gradient index)
-occurrences recorded during forward, reduces runs of equal rows and applies the row optimizer
-inside the same kernel.  All buffers that peers write are double-buffered by step parity; flags
-are monotonically increasing step sequence numbers, and every wait is bounded.
+features and writes the concatenated dense input.  The (row, gradient index) occurrences recorded
+by the forward are radix-sorted by row on a side stream while the dense forward runs.  Backward
+(on its own side stream, beside the dense weight-gradient GEMMs): one kernel pushes each feature's
+activation gradient into its owner's buffer, the owner reduces runs of equal rows of the sorted
+occurrences and applies the row optimizer inside the same kernel.  All buffers that peers write
+are double-buffered by step parity; flags are monotonically increasing step sequence numbers, and
+every wait is bounded.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any
 
 import torch
@@ -23,6 +26,7 @@ from recml_b200.embedding import collective
 from recml_b200.embedding import jagged as jagged_lib
 from recml_b200.embedding.planner import Placement
 from recml_b200.ops import _lib
+from recml_b200.utils import streams
 
 MAXW = 8
 c_ll, c_int, c_uint, c_float, c_vp = (ctypes.c_longlong, ctypes.c_int, ctypes.c_uint, ctypes.c_float,
@@ -53,7 +57,8 @@ class FwdParams(ctypes.Structure):
   _fields_ = [("ids", IdPtrs), ("feats", c_vp), ("n_feats", c_int), ("W", c_int), ("me", c_int), ("B", c_int),
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
               ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
-              ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp)]
+              ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp), ("dropped", c_vp),
+              ("prefetch", c_int), ("pad", c_int)]
 
 
 class CombineDesc(ctypes.Structure):
@@ -80,7 +85,8 @@ class BwdParams(ctypes.Structure):
   _fields_ = [("keys", c_vp), ("vals", c_vp), ("occ_gain", c_vp), ("n_occ", c_vp), ("grads", c_vp), ("val_scale", c_ll),
               ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
               ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
-              ("wait_flags", c_vp), ("W", c_int), ("seq", SeqRef), ("status", c_vp)]
+              ("wait_flags", c_vp), ("W", c_int), ("seq", SeqRef), ("status", c_vp), ("hp_dev", c_vp),
+              ("n_cap", c_uint), ("pad", c_int)]
 
 
 class PushIdsParams(ctypes.Structure):
@@ -130,7 +136,13 @@ class FusedBackend:
     self.seq_dev = torch.zeros(1, dtype=torch.int64, device=module.device)
     self.B = None
     self.status = _lib.status_buffer(m.device)
-    self._sort_temp: dict[int, torch.Tensor] = {}
+    # resident 128-thread blocks per SM of the backward update kernel: 0 = fill the GPU; a model that runs
+    # weight-gradient GEMMs beside the embedding backward sets 3 so that a GEMM CTA fits on every SM
+    self.bwd_blocks_per_sm = int(os.environ.get("RECML_EMB_BWD_BLOCKS", "0"))
+    self.side_streams = os.environ.get("RECML_EMB_STREAMS", "1") != "0"
+    self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
+    self.dropped = torch.zeros(1, dtype=torch.int32, device=module.device) if module.config.allow_id_dropping else None
+    self._hp_slot = 0
     from recml_b200.utils import graphs
     graphs.register(self)
     self.has_gains = any(s.combiner != "sum" or s.weight_name is not None
@@ -146,6 +158,34 @@ class FusedBackend:
   def graph_advance(self) -> None:
     self.seq += 1
     self.m.step_count += 1
+
+  def graph_pre_replay(self) -> None:
+    self._push_hyper()
+
+  # -- row-optimizer hyper-parameters live on the device (a replayed graph follows a schedule) -----------
+  HP_RING = 256
+
+  def _push_hyper(self) -> None:
+    """Copies this step's hyper-parameters of every stack into device memory through a ring of pinned
+    slots (stream-ordered, so the host may run ahead of the device)."""
+    m = self.m
+    if not getattr(self, "_occ_ready", False):
+      return
+    n = len(self.stacks)
+    if not hasattr(self, "_hp_ring"):
+      self._hp_ring = torch.zeros(self.HP_RING, n, 8, dtype=torch.float32).pin_memory()
+      self._hp_dev = torch.zeros(n, 8, dtype=torch.float32, device=m.device)
+    slot = self._hp_ring[self._hp_slot % self.HP_RING]
+    self._hp_slot += 1
+    for si in range(n):
+      hp = m.plan.stacks[si].optimizer.hyperparams(m.step_count)
+      for i in range(6):
+        slot[si, i] = float(hp[i]) if i < len(hp) else 0.0
+    self._hp_dev.copy_(slot, non_blocking=True)
+
+  def dropped_ids(self) -> int:
+    """Ids dropped so far because an occurrence list was full (`allow_id_dropping`); synchronises."""
+    return 0 if self.dropped is None else int(self.dropped.item())
 
   # -- one-time set-up for a batch geometry --------------------------------------------------------------
   def _setup(self, kjt: jagged_lib.KeyedJagged):
@@ -293,12 +333,13 @@ class FusedBackend:
       info["vals"] = torch.empty(2, cap, dtype=torch.int32, device=dev)
       info["gain"] = torch.empty(cap, 2, dtype=torch.float32, device=dev) if self.has_gains else None
       dloc = m.plan.stacks[si].dim
-      info["scratch"] = torch.zeros((cap + 31) // 32, dloc, dtype=torch.float32, device=dev)
-      nbytes = int(self.lib.recml_sort_temp_bytes(c_ll(cap)))
-      info["sort_temp"] = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
-      rows = m.plan.stacks[si].rows
-      info["end_bit"] = 32   # padding keys are 0xFFFFFFFF, so all 32 bits take part in the sort
+      info["scratch"] = torch.zeros((cap + 127) // 128, dloc, dtype=torch.float32, device=dev)
+      words = int(self.lib.recml_radix_sort_scratch_words(c_ll(cap)))
+      info["sort_scratch"] = torch.empty(words, dtype=torch.int32, device=dev)
+      info["key_bits"] = max(1, int(max(m.plan.stacks[si].rows, 1) - 1).bit_length())
+      info["sorted"] = 0     # which of the two (keys, vals) buffers holds the sorted list
     self._occ_ready = True
+    self._push_hyper()
 
   def _flag_ptr(self, rank: int, chan: int, src: int) -> int:
     if self.buf is None:
@@ -314,6 +355,7 @@ class FusedBackend:
       self._setup(kjt)
     if kjt.batch_size() != self.B:
       raise ValueError(f"fused backend was set up for batch {self.B}, got {kjt.batch_size()}")
+    streams.join("emb_bwd", "emb_sort", device=dev)    # the previous step's table update comes first
     if kjt.values.numel() > self.nnz_cap:
       raise ValueError(f"batch has {kjt.values.numel()} ids, capacity is {self.nnz_cap}")
     assert kjt.values.dtype == torch.int32 and kjt.offsets.dtype == torch.int32
@@ -373,15 +415,18 @@ class FusedBackend:
         fp.flags[r] = self._flag_ptr(r, 1 + si, m.rank)
       fp.grad_ld = direct[0] if direct is not None else 0
       if training:
-        info["keys"][0].fill_(-1)    # 0xFFFFFFFF padding sorts behind every real row
         fp.occ_key, fp.occ_val = info["keys"][0].data_ptr(), info["vals"][0].data_ptr()
         fp.occ_gain = info["gain"].data_ptr() if gains else None
         fp.occ_count, fp.occ_cap = info["count"].data_ptr(), info["occ_cap"]
+        fp.dropped = self.dropped.data_ptr() if self.dropped is not None else None
       fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
+      fp.prefetch = self.fwd_prefetch
       fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
                       "emb_fwd")
+    if training:
+      self._sort_occurrences()
     odt = m.config.output_dtype or torch.bfloat16
     if direct is not None:
       res = out[:, out_col:out_col + self.width]
@@ -400,17 +445,56 @@ class FusedBackend:
     saved = {"seq": seq, "par": par, "kjt": kjt, "direct": None} if training else None
     return res, saved
 
+  def _sort_occurrences(self) -> None:
+    """Groups the step's occurrence list by row.  The list is complete once the forward kernels have run
+    and nothing else of the forward pass needs the result, so the sort goes to a side stream and runs
+    beside the dense forward; the backward waits for it."""
+    use_side = self.side_streams
+    s = streams.fork("emb_sort", self.m.device) if use_side else torch.cuda.current_stream(self.m.device)
+    with torch.cuda.stream(s):
+      st = _lib.stream()
+      for info in self.stacks:
+        n = info["occ_cap"]
+        if n <= 0 or info["n_feats"] == 0:
+          continue
+        rc = self.lib.recml_radix_sort_pairs(
+            _lib.ptr(info["keys"][0]), _lib.ptr(info["vals"][0]), _lib.ptr(info["keys"][1]),
+            _lib.ptr(info["vals"][1]), _lib.ptr(info["count"]), c_ll(n), c_int(info["key_bits"]),
+            _lib.ptr(info["sort_scratch"]), _lib.ptr(self.status), st)
+        if rc < 0:
+          raise _lib.NativeError(f"radix sort failed with code {rc}")
+        _lib.LAUNCHES["count"] += 4 * ((info["key_bits"] + 8) // 9) - 1    # four kernels per pass
+        info["sorted"] = rc
+
   # -- backward ----------------------------------------------------------------------------------------------
   @torch.no_grad()
   def backward(self, saved: Any, grad_out: torch.Tensor) -> None:
+    """Launches the gradient push and the table update.  With side streams on, they are issued on the
+    "emb_bwd" stream (after everything issued so far on the current stream and after the sort), so the
+    caller's stream is free to go on with work that does not touch the tables; `streams.join("emb_bwd")`
+    (done by the next forward and by `State.update`) orders later work behind the update."""
     m = self.m
-    W, B = m.world, self.B
-    st = _lib.stream()
-    seq, par = saved["seq"], saved["par"]
     if grad_out.dtype != torch.bfloat16:
       grad_out = grad_out.to(torch.bfloat16)
     if grad_out.stride(-1) != 1:
       grad_out = grad_out.contiguous()
+    from recml_b200.utils import graphs
+    if not graphs.capturing():
+      self._push_hyper()
+    if not self.side_streams:
+      self._backward_on_current(saved, grad_out)
+      return
+    s = streams.fork("emb_bwd", m.device)
+    streams.chain("emb_bwd", "emb_sort", m.device)
+    streams.keep_alive_on(s, grad_out)
+    with torch.cuda.stream(s):
+      self._backward_on_current(saved, grad_out)
+
+  def _backward_on_current(self, saved: Any, grad_out: torch.Tensor) -> None:
+    m = self.m
+    W, B = m.world, self.B
+    st = _lib.stream()
+    seq, par = saved["seq"], saved["par"]
     direct = saved["direct"]
     gchan = 1 + len(self.stacks)
     if direct is not None:
@@ -432,17 +516,13 @@ class FusedBackend:
       _lib.check_rc(self.lib.recml_emb_push_grads(ctypes.byref(pg), st), "emb_push_grads")
       grads_ptr, val_scale = self.buf.peer_ptr(m.rank, self.grad_buf_off[par]), None
     for si, info in enumerate(self.stacks):
-      # The occurrence count stays on the device: the whole (0xFFFFFFFF-padded) capacity is sorted and
-      # the update kernel reads the count itself, so backward never synchronises with the host.
+      # The occurrence count stays on the device: every kernel reads it there, so backward never
+      # synchronises with the host.
       n = info["occ_cap"]
       opt = m.plan.stacks[si].optimizer
-      if n > 0:
-        _lib.check_rc(self.lib.recml_sort_pairs_u32(
-            _lib.ptr(info["keys"][0]), _lib.ptr(info["keys"][1]), _lib.ptr(info["vals"][0]),
-            _lib.ptr(info["vals"][1]), c_ll(n), c_int(info["end_bit"]), _lib.ptr(info["sort_temp"]),
-            c_ll(info["sort_temp"].numel()), st), "sort_pairs")
+      srt = info["sorted"]
       bp = BwdParams()
-      bp.keys, bp.vals = info["keys"][1].data_ptr(), info["vals"][1].data_ptr()
+      bp.keys, bp.vals = info["keys"][srt].data_ptr(), info["vals"][srt].data_ptr()
       bp.occ_gain = info["gain"].data_ptr() if self.has_gains else None
       bp.n_occ = info["count"].data_ptr()
       bp.grads = grads_ptr
@@ -460,6 +540,8 @@ class FusedBackend:
       bp.scratch = info["scratch"].data_ptr()
       bp.wait_flags = self._flag_ptr(m.rank, gchan, 0) if (W > 1 and direct is None) else None
       bp.W, bp.seq, bp.status = W, seq, self.status.data_ptr()
+      bp.hp_dev = self._hp_dev[si].data_ptr()
+      bp.n_cap = n
       if n > 0 or W > 1:
         _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),
-                                                    st), "emb_bwd_update")
+                                                    c_int(self.bwd_blocks_per_sm), st), "emb_bwd_update")

@@ -28,6 +28,8 @@ class CrossNetwork(nn.Module):
         nn.init.xavier_normal_(v)
       self.v.append(nn.Parameter(v))
       self.b.append(nn.Parameter(torch.zeros(dim)))
+    self.defer_wgrad = False   # see `MLP.defer_wgrad`
 
   def forward(self, x0):
-    return dense_ops.cross_network(x0, list(self.u) if self.u is not None else None, list(self.v), list(self.b))
+    return dense_ops.cross_network(x0, list(self.u) if self.u is not None else None, list(self.v), list(self.b),
+                                   defer_wgrad=self.defer_wgrad and x0.is_cuda and torch.is_grad_enabled())

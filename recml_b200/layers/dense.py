@@ -51,7 +51,10 @@ class MLP(nn.Module):
         self.biases.append(nn.Parameter(torch.zeros(dims[i + 1])))
     n = len(dims) - 1
     self.relu_flags = [True] * (n - 1) + [bool(activate_last)]
+    # set by a model that flushes `ops.dense` deferred weight gradients itself (see `ops/dense.py`)
+    self.defer_wgrad = False
 
   def forward(self, x, out=None):
     biases = list(self.biases) if self.biases is not None else [None] * len(self.weights)
-    return dense_ops.mlp(x, list(self.weights), biases, self.relu_flags, out=out)
+    return dense_ops.mlp(x, list(self.weights), biases, self.relu_flags, out=out,
+                         defer_wgrad=self.defer_wgrad and x.is_cuda and torch.is_grad_enabled())

@@ -25,7 +25,8 @@ class DLRMDCNv2(nn.Module):
                embedding_optimizer: emb.OptimizerSpec | None = None, combiner: str = "sum",
                feature_names: Sequence[str] | None = None, device=None, group=None,
                sharding_strategy: str = "auto", row_wise_min_bytes: int | None = None,
-               backend: str = "auto", seed: int = 0, init_scale: float | None = None):
+               backend: str = "auto", seed: int = 0, init_scale: float | None = None,
+               overlap_backward: bool = True):
     super().__init__()
     if bottom_mlp_dims[-1] != embedding_dim:
       raise ValueError("bottom MLP must end in embedding_dim so it can join the feature concat")
@@ -49,6 +50,15 @@ class DLRMDCNv2(nn.Module):
     self.concat_dim = d
     if device is not None:
       self.bottom.to(device); self.cross.to(device); self.top.to(device)
+    # Backward schedule on CUDA: the data-gradient chain of the top MLP and the cross network runs first;
+    # its end feeds the embedding backward (its own stream, memory-latency bound), beside which the queued
+    # weight-gradient GEMMs (tensor-core bound) run on a third stream.
+    if overlap_backward and device is not None and torch.device(device).type == "cuda":
+      self.cross.defer_wgrad = True
+      self.top.defer_wgrad = True
+      backend_obj = getattr(self.embedding, "_backend", None)
+      if hasattr(backend_obj, "bwd_blocks_per_sm") and backend_obj.bwd_blocks_per_sm == 0:
+        backend_obj.bwd_blocks_per_sm = 3
 
   def forward(self, dense_x: torch.Tensor, sparse: emb.KeyedJagged) -> torch.Tensor:
     if dense_x.is_cuda:

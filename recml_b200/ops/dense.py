@@ -12,6 +12,55 @@ import torch
 
 from recml_b200.ops import elementwise as ew
 from recml_b200.ops import gemm as G
+from recml_b200.utils import streams
+
+# ---- deferred weight gradients ------------------------------------------------------------------------
+# A backward pass is a chain of data-gradient GEMMs (each needs the previous one) with a weight-gradient
+# GEMM hanging off every link.  Only the chain is on the critical path: what consumes its end (the
+# embedding backward, which is bound by memory latency, not by the tensor cores) can start as soon as
+# the chain is done if the weight gradients are computed afterwards, beside it, on another stream.
+# Nodes created with `defer=True` therefore queue their weight-gradient work instead of running it;
+# `flush_deferred()` runs the queue on the "wgrad" side stream (ordered after everything issued so far
+# on the current stream), stores the results in `.grad` and fires the parameters' post-accumulate hooks
+# (the bucketed gradient all-reduce); `State.update` flushes what is left and joins the stream before
+# the optimizer step.
+_pending: list = []
+
+
+def _deliver(p: torch.Tensor, g: torch.Tensor) -> None:
+  """What autograd's AccumulateGrad node does for a gradient returned by backward()."""
+  if g.shape != p.shape:
+    g = g.reshape(p.shape)
+  if g.dtype != p.dtype:
+    g = g.to(p.dtype)
+  if p.grad is None:
+    p.grad = g
+  else:
+    p.grad.add_(g)
+  hooks = getattr(p, "_post_accumulate_grad_hooks", None)
+  if hooks:
+    for h in list(hooks.values()):
+      h(p)
+
+
+def flush_deferred() -> None:
+  """Runs the queued weight-gradient work on the "wgrad" side stream."""
+  if not _pending:
+    return
+  work = list(_pending)
+  _pending.clear()
+  s = streams.fork("wgrad", priority=-1)
+  with torch.cuda.stream(s):
+    for tensors, fn in work:
+      streams.keep_alive_on(s, *tensors)
+      fn()
+
+
+def join_deferred() -> None:
+  """Flushes the queue and makes the current stream wait for the weight gradients."""
+  flush_deferred()
+  streams.join("wgrad")
+
 
 
 def bf16_weight(p: torch.Tensor) -> torch.Tensor:
@@ -46,8 +95,9 @@ class MLPFn(torch.autograd.Function):
   output unit runs as a fused GEMV and returns fp32 `[M]`... as `[M, 1]`."""
 
   @staticmethod
-  def forward(ctx, x, relu_flags, out, *params):
+  def forward(ctx, x, relu_flags, out, defer, *params):
     n = len(relu_flags)
+    ctx.defer = bool(defer)
     weights, biases = params[:n], params[n:]
     k0 = weights[0].shape[1]
     k_pad = (k0 + 7) // 8 * 8
@@ -82,6 +132,26 @@ class MLPFn(torch.autograd.Function):
     n = len(relu)
     dws, dbs = [None] * n, [None] * n
     g = dy
+    defer = ctx.defer
+
+    def wgrad(i, g, x_i):
+      """Weight and bias gradient of layer i from its output gradient `g` (bf16) and input `x_i`."""
+      w = weights[i]
+      dw = G.gemm(g, x_i, a_mn=True, b_mn=True, out_dtype=torch.float32)
+      dw = dw if dw.shape[1] == w.shape[1] else dw[:, :w.shape[1]].contiguous()
+      db = ew.colsum(g) if biases[i] is not None else None
+      return dw, db
+
+    def queue(i, g, x_i):
+      def run(i=i, g=g, x_i=x_i):
+        dw, db = wgrad(i, g, x_i)
+        # the bias first: gradients reach the hooks in the order autograd would deliver them (reverse
+        # parameter order), which is the order the all-reduce buckets are laid out in
+        if db is not None:
+          _deliver(biases[i], db)
+        _deliver(weights[i], dw)
+      _pending.append(((g, x_i), run))
+
     for i in range(n - 1, -1, -1):
       x_i, y_i, w = acts[i], acts[i + 1], weights[i]
       prev_relu = i > 0 and relu[i - 1]
@@ -99,11 +169,10 @@ class MLPFn(torch.autograd.Function):
         g = g.to(torch.bfloat16)
       if i == n - 1 and relu[i]:
         g = ew.relu_mask(g, y_i)       # hidden layers get their mask from the GEMM epilogue below
-      k_in = w.shape[1]
-      dw = G.gemm(g, x_i, a_mn=True, b_mn=True, out_dtype=torch.float32)
-      dws[i] = dw if dw.shape[1] == k_in else dw[:, :k_in].contiguous()
-      if biases[i] is not None:
-        dbs[i] = ew.colsum(g)
+      if defer:
+        queue(i, g, x_i)
+      else:
+        dws[i], dbs[i] = wgrad(i, g, x_i)
       if need_dx:
         if prev_relu:
           g = G.gemm(g, w16s[i], b_mn=True, epi=G.EPI_MASK_RELU, aux0=x_i)
@@ -112,12 +181,14 @@ class MLPFn(torch.autograd.Function):
     dx = None
     if ctx.need_dx:
       dx = g[:, :ctx.x_shape[1]].to(ctx.x_dtype)
-    return (dx, None, None, *dws, *dbs)
+    return (dx, None, None, None, *dws, *dbs)
 
 
-def mlp(x: torch.Tensor, weights, biases, relu_flags, out: torch.Tensor | None = None) -> torch.Tensor:
+def mlp(x: torch.Tensor, weights, biases, relu_flags, out: torch.Tensor | None = None,
+        defer_wgrad: bool = False) -> torch.Tensor:
   """Functional MLP.  weights[i]: `[out, in]`; biases[i]: `[out]` or None.  `out` (CUDA only): a bf16
-  `[M, out_features]` view, possibly strided, that receives the last layer's result."""
+  `[M, out_features]` view, possibly strided, that receives the last layer's result.  `defer_wgrad`
+  (CUDA only): weight gradients are queued during backward and computed by `flush_deferred()`."""
   if not x.is_cuda:
     h = x.to(torch.float32)
     for w, b, r in zip(weights, biases, relu_flags):
@@ -125,7 +196,7 @@ def mlp(x: torch.Tensor, weights, biases, relu_flags, out: torch.Tensor | None =
       if r:
         h = torch.relu(h)
     return h
-  return MLPFn.apply(x, tuple(bool(r) for r in relu_flags), out, *weights, *biases)
+  return MLPFn.apply(x, tuple(bool(r) for r in relu_flags), out, defer_wgrad, *weights, *biases)
 
 
 class CrossNetFn(torch.autograd.Function):
@@ -133,7 +204,8 @@ class CrossNetFn(torch.autograd.Function):
   v = (xl·Uᵀ)·Vᵀ + b; full-rank layer params: (None, W `[d, d]`, b)."""
 
   @staticmethod
-  def forward(ctx, x0, n_layers, low_rank, *params):
+  def forward(ctx, x0, n_layers, low_rank, defer, *params):
+    ctx.defer = bool(defer)
     x0 = x0.detach()
     if x0.dtype != torch.bfloat16 or x0.stride(-1) != 1:
       x0 = x0.to(torch.bfloat16).contiguous()
@@ -153,6 +225,7 @@ class CrossNetFn(torch.autograd.Function):
         saved.append((xl, None, v, None, v16))
       xl = out
     ctx.saved, ctx.x0, ctx.low_rank, ctx.n = saved, x0, low_rank, n_layers
+    ctx.us, ctx.vs = us, vs
     return xl
 
   @staticmethod
@@ -166,23 +239,35 @@ class CrossNetFn(torch.autograd.Function):
       xl, u, v, u16, v16 = ctx.saved[i]
       # dv = g⊙x0 ; dx0 (+)= g⊙v ; db = column sums of dv, all in one pass
       dv, dbs[i] = ew.cross_bwd_ew(g, x0, v, dx0, accumulate=i != n - 1, want_colsum=True)
+      wg = lambda a, b: G.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
       if ctx.low_rank:
-        dvs[i] = G.gemm(dv, u, a_mn=True, b_mn=True, out_dtype=torch.float32)       # [d, r]
         du = G.gemm(dv, v16, b_mn=True)                                             # [M, r]
-        dus[i] = G.gemm(du, xl, a_mn=True, b_mn=True, out_dtype=torch.float32)      # [r, d]
+        if ctx.defer:
+          def run(i=i, dv=dv, u=u, du=du, xl=xl):
+            _deliver(ctx.vs[i], wg(dv, u))
+            _deliver(ctx.us[i], wg(du, xl))
+          _pending.append(((dv, u, du, xl), run))
+        else:
+          dvs[i] = wg(dv, u)                                                        # [d, r]
+          dus[i] = wg(du, xl)                                                       # [r, d]
         # dxl = du·U + g; layer 0's xl IS x0, so its product also takes the accumulated dx0
         g = G.gemm(du, u16, b_mn=True, epi=G.EPI_ADD, aux0=g, aux1=dx0 if i == 0 else None)
       else:
-        dvs[i] = G.gemm(dv, xl, a_mn=True, b_mn=True, out_dtype=torch.float32)      # [d, d]
+        if ctx.defer:
+          def run(i=i, dv=dv, xl=xl):
+            _deliver(ctx.vs[i], wg(dv, xl))
+          _pending.append(((dv, xl), run))
+        else:
+          dvs[i] = wg(dv, xl)                                                       # [d, d]
         g = G.gemm(dv, v16, b_mn=True, epi=G.EPI_ADD, aux0=g, aux1=dx0 if i == 0 else None)
     dx0 = g
     if ctx.low_rank:
-      return (dx0, None, None, *dus, *dvs, *dbs)
-    return (dx0, None, None, *dvs, *dbs)
+      return (dx0, None, None, None, *dus, *dvs, *dbs)
+    return (dx0, None, None, None, *dvs, *dbs)
 
 
-def cross_network(x0: torch.Tensor, us, vs, bs) -> torch.Tensor:
-  """`us` None → full-rank layers (`vs[i]` is `[d, d]`)."""
+def cross_network(x0: torch.Tensor, us, vs, bs, defer_wgrad: bool = False) -> torch.Tensor:
+  """`us` None → full-rank layers (`vs[i]` is `[d, d]`).  `defer_wgrad` as in `mlp`."""
   low_rank = us is not None
   if not x0.is_cuda:
     x0f = x0.to(torch.float32)
@@ -192,12 +277,13 @@ def cross_network(x0: torch.Tensor, us, vs, bs) -> torch.Tensor:
       xl = x0f * torch.nn.functional.linear(h, vs[i], bs[i]) + xl
     return xl
   params = (*us, *vs, *bs) if low_rank else (*vs, *bs)
-  return CrossNetFn.apply(x0, len(vs), low_rank, *params)
+  return CrossNetFn.apply(x0, len(vs), low_rank, defer_wgrad, *params)
 
 
 class JoinColumnsFn(torch.autograd.Function):
   """Declares that `full[:, :k]` was produced by `left` and `full[:, k:]` by `right` (both already
-  written in place), so the concat costs no copy and its gradient is two views."""
+  written in place), so the concat costs no copy and its gradient is two views.  Its backward is where
+  the data-gradient chain of the layers above ends, so queued weight-gradient work is started here."""
 
   @staticmethod
   def forward(ctx, left, right, full):
@@ -206,6 +292,7 @@ class JoinColumnsFn(torch.autograd.Function):
 
   @staticmethod
   def backward(ctx, g):
+    flush_deferred()
     return g[:, :ctx.k], g[:, ctx.k:], None
 
 

@@ -64,10 +64,21 @@ class State:
     if grads is not None:
       for n, g in grads.items():
         self.params[n].grad = g
+    on_cuda = any(p.is_cuda for p in self.optimizer.params[:1])
+    if on_cuda:
+      # weight gradients queued during backward (`ops.dense`) run on their own stream; they must be in
+      # `.grad` before the gradients are synchronised and applied
+      from recml_b200.ops import dense as dense_ops
+      dense_ops.join_deferred()
     if self.grad_sync is not None:
       self.grad_sync([p for p in self.optimizer.params if p.grad is not None])
     self.optimizer.step()
     self.optimizer.zero_grad()
+    if on_cuda:
+      # side streams of the step (embedding backward, occurrence sort) end here, so the step is one unit
+      # for whoever comes next on this stream (the next step, a checkpoint, a CUDA-graph capture)
+      from recml_b200.utils import streams
+      streams.join()
     if mutable is not None:
       self.mutable.update(mutable)
     self.step += 1

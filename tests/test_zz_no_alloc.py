@@ -7,7 +7,7 @@ occurrence lists and gradients as usual; the scratch that the ordinary entry poi
 the caller is a fixed array inside the library here.
 
 The test drives both entry points through their exported C symbols on identical inputs — row-wise
-Adagrad over occurrence lists with hot rows whose runs span many 32-entry chunks, which is exactly
+Adagrad over occurrence lists with hot rows whose runs span many 128-entry ranges, which is exactly
 what the scratch is for — twice in a row with different data, and requires the updated tables and
 optimizer state to agree within the tolerance of the other embedding tests.  The second round
 proves that leftovers of the first call in the shared array do not leak into the next one.
@@ -65,9 +65,9 @@ def test_static_scratch_entry_matches_regular_entry_twice():
   for rnd, n_occ in enumerate((60000, 35001)):
     keys, vals, grads = _inputs(10 + rnd, n_occ, rows, dim, n_vec)
     count = torch.tensor([n_occ], dtype=torch.int32, device=dev)
-    scratch = torch.zeros((n_occ + 31) // 32, dim, device=dev)
+    scratch = torch.zeros((n_occ + 127) // 128, dim, device=dev)
     pa = _params(fused, keys, vals, grads, count, table_a, slot_a, scratch, status, dim)
-    assert regular(ctypes.byref(pa), ctypes.c_longlong(n_occ), ctypes.c_int(0), stream) == 0
+    assert regular(ctypes.byref(pa), ctypes.c_longlong(n_occ), ctypes.c_int(0), ctypes.c_int(0), stream) == 0
     pb = _params(fused, keys, vals, grads, count, table_b, slot_b, None, status, dim)
     rc = static(ctypes.byref(pb), ctypes.c_longlong(n_occ), ctypes.c_int(0), stream, err, ctypes.c_int(256))
     assert rc == 0, err.value
