@@ -9,7 +9,11 @@ decides which steps are kept, and at most `max_to_keep` steps stay on disk.
 
 A checkpoint is staged in `<step>.orbax-checkpoint-tmp-<n>` and renamed to `<step>`
 once every rank finished writing, so a reader never sees a partial step directory;
-`commit_success.txt` is written last inside it as the completion marker.
+`commit_success.txt` is written last inside it as the completion marker.  In a multi-rank job
+the ranks agree on success before the rename: if any rank failed to write its shards the
+staging directory is removed, nothing is committed or rotated out, and every rank raises.
+`async_save` moves the file writes of a single-process job to a background thread; a
+multi-rank save returns once it is committed (the agreement is a collective).
 """
 from __future__ import annotations
 
@@ -151,15 +155,28 @@ class CheckpointManager:
       self._thread.start()
     else:
       work()
-      _barrier(self.group)
+      ok = self._all_ranks_ok(self._error is None)
       if rank == 0:
-        self._finalize(step, tmp, final)
+        if ok:
+          self._finalize(step, tmp, final)
+        else:
+          shutil.rmtree(tmp, ignore_errors=True)
       _barrier(self.group)
-      if self._error:
-        err, self._error = self._error, None
-        raise err
+      err, self._error = self._error, None
+      if not ok:
+        if err is not None:
+          raise err
+        raise RuntimeError(f"checkpoint {step}: another rank failed to write its shards; nothing was committed")
     self._last_saved = step
     return True
+
+  def _all_ranks_ok(self, ok: bool) -> bool:
+    """True when every rank of the group reports success (also a barrier)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self.group) == 1:
+      return ok
+    flags: list[Any] = [None] * dist.get_world_size(self.group)
+    dist.all_gather_object(flags, bool(ok), group=self.group)
+    return all(flags)
 
   def _write(self, tmp, staged, kinds, metrics, rank, world):
     item = os.path.join(tmp, self.item_name)

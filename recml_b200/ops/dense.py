@@ -19,11 +19,13 @@ from recml_b200.utils import streams
 # GEMM hanging off every link.  Only the chain is on the critical path: what consumes its end (the
 # embedding backward, which is bound by memory latency, not by the tensor cores) can start as soon as
 # the chain is done if the weight gradients are computed afterwards, beside it, on another stream.
-# Nodes created with `defer=True` therefore queue their weight-gradient work instead of running it;
+# Nodes created with deferral therefore queue their weight-gradient work instead of running it;
 # `flush_deferred()` runs the queue on the "wgrad" side stream (ordered after everything issued so far
 # on the current stream), stores the results in `.grad` and fires the parameters' post-accumulate hooks
 # (the bucketed gradient all-reduce); `State.update` flushes what is left and joins the stream before
-# the optimizer step.
+# the optimizer step.  Such a node receives DETACHED views of its parameters and delivers every one of
+# their gradients itself: autograd runs a parameter's accumulation node (and its hooks) even when
+# backward() returns no gradient for it, which would announce a gradient that does not exist yet.
 _pending: list = []
 
 
@@ -95,9 +97,10 @@ class MLPFn(torch.autograd.Function):
   output unit runs as a fused GEMV and returns fp32 `[M]`... as `[M, 1]`."""
 
   @staticmethod
-  def forward(ctx, x, relu_flags, out, defer, *params):
+  def forward(ctx, x, relu_flags, out, targets, *params):
     n = len(relu_flags)
-    ctx.defer = bool(defer)
+    # targets = (weights, biases): the real parameters when `params` are detached stand-ins (deferral)
+    ctx.defer, ctx.targets = targets is not None, targets
     weights, biases = params[:n], params[n:]
     k0 = weights[0].shape[1]
     k_pad = (k0 + 7) // 8 * 8
@@ -111,7 +114,8 @@ class MLPFn(torch.autograd.Function):
           y = torch.relu(y)
         h = y[:, None]
       else:
-        w16 = bf16_weight(w)
+        # the bf16 compute copy hangs on the real parameter (the optimizer refreshes it there)
+        w16 = bf16_weight(targets[0][i] if targets is not None else w)
         if w16.shape[1] != h.shape[1]:   # first layer: pad K to the input's padded width
           wp = torch.zeros(w16.shape[0], h.shape[1], dtype=torch.bfloat16, device=w16.device)
           wp[:, :w16.shape[1]] = w16
@@ -133,6 +137,7 @@ class MLPFn(torch.autograd.Function):
     dws, dbs = [None] * n, [None] * n
     g = dy
     defer = ctx.defer
+    tw, tb = ctx.targets if defer else (weights, biases)
 
     def wgrad(i, g, x_i):
       """Weight and bias gradient of layer i from its output gradient `g` (bf16) and input `x_i`."""
@@ -148,8 +153,8 @@ class MLPFn(torch.autograd.Function):
         # the bias first: gradients reach the hooks in the order autograd would deliver them (reverse
         # parameter order), which is the order the all-reduce buckets are laid out in
         if db is not None:
-          _deliver(biases[i], db)
-        _deliver(weights[i], dw)
+          _deliver(tb[i], db)
+        _deliver(tw[i], dw)
       _pending.append(((g, x_i), run))
 
     for i in range(n - 1, -1, -1):
@@ -163,7 +168,12 @@ class MLPFn(torch.autograd.Function):
         dw = torch.zeros(w.numel(), dtype=torch.float32, device=w.device)
         db = torch.zeros(1, dtype=torch.float32, device=w.device) if biases[i] is not None else None
         g = ew.gemv_bwd(x_i, w.detach().reshape(-1), gv.contiguous(), prev_relu, dw, db)
-        dws[i], dbs[i] = dw.view_as(w), db
+        if defer:    # computed on the chain anyway: delivered at once
+          if db is not None:
+            _deliver(tb[i], db)
+          _deliver(tw[i], dw.view_as(w))
+        else:
+          dws[i], dbs[i] = dw.view_as(w), db
         continue
       if g.dtype != torch.bfloat16:
         g = g.to(torch.bfloat16)
@@ -196,7 +206,12 @@ def mlp(x: torch.Tensor, weights, biases, relu_flags, out: torch.Tensor | None =
       if r:
         h = torch.relu(h)
     return h
-  return MLPFn.apply(x, tuple(bool(r) for r in relu_flags), out, defer_wgrad, *weights, *biases)
+  flags = tuple(bool(r) for r in relu_flags)
+  if defer_wgrad and x.requires_grad and torch.is_grad_enabled():
+    det = lambda t: None if t is None else t.detach()
+    return MLPFn.apply(x, flags, out, (tuple(weights), tuple(biases)), *[det(w) for w in weights],
+                       *[det(b) for b in biases])
+  return MLPFn.apply(x, flags, out, None, *weights, *biases)
 
 
 class CrossNetFn(torch.autograd.Function):
@@ -204,8 +219,9 @@ class CrossNetFn(torch.autograd.Function):
   v = (xl·Uᵀ)·Vᵀ + b; full-rank layer params: (None, W `[d, d]`, b)."""
 
   @staticmethod
-  def forward(ctx, x0, n_layers, low_rank, defer, *params):
-    ctx.defer = bool(defer)
+  def forward(ctx, x0, n_layers, low_rank, targets, *params):
+    # targets = (us, vs, bs): the real parameters when `params` are detached stand-ins (deferral)
+    ctx.defer, ctx.targets = targets is not None, targets
     x0 = x0.detach()
     if x0.dtype != torch.bfloat16 or x0.stride(-1) != 1:
       x0 = x0.to(torch.bfloat16).contiguous()
@@ -214,9 +230,9 @@ class CrossNetFn(torch.autograd.Function):
     bs = params[2 * n_layers:] if low_rank else params[n_layers:]
     xl, saved = x0, []
     for i in range(n_layers):
-      v16 = bf16_weight(vs[i])
+      v16 = bf16_weight(targets[1][i] if targets is not None else vs[i])
       if low_rank:
-        u16 = bf16_weight(us[i])
+        u16 = bf16_weight(targets[0][i] if targets is not None else us[i])
         u = G.gemm(xl, u16)
         out, v = G.gemm(u, v16, bias=bs[i].detach(), epi=G.EPI_CROSS, aux0=x0, aux1=xl, want_out2=True)
         saved.append((xl, u, v, u16, v16))
@@ -225,7 +241,6 @@ class CrossNetFn(torch.autograd.Function):
         saved.append((xl, None, v, None, v16))
       xl = out
     ctx.saved, ctx.x0, ctx.low_rank, ctx.n = saved, x0, low_rank, n_layers
-    ctx.us, ctx.vs = us, vs
     return xl
 
   @staticmethod
@@ -235,17 +250,21 @@ class CrossNetFn(torch.autograd.Function):
       g = g.to(torch.bfloat16).contiguous()
     dx0 = torch.empty_like(x0)
     dus, dvs, dbs = [None] * n, [None] * n, [None] * n
+    tus, tvs, tbs = ctx.targets if ctx.defer else (None, None, None)
     for i in range(n - 1, -1, -1):
       xl, u, v, u16, v16 = ctx.saved[i]
       # dv = g⊙x0 ; dx0 (+)= g⊙v ; db = column sums of dv, all in one pass
       dv, dbs[i] = ew.cross_bwd_ew(g, x0, v, dx0, accumulate=i != n - 1, want_colsum=True)
+      if ctx.defer:
+        _deliver(tbs[i], dbs[i])
+        dbs[i] = None
       wg = lambda a, b: G.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
       if ctx.low_rank:
         du = G.gemm(dv, v16, b_mn=True)                                             # [M, r]
         if ctx.defer:
           def run(i=i, dv=dv, u=u, du=du, xl=xl):
-            _deliver(ctx.vs[i], wg(dv, u))
-            _deliver(ctx.us[i], wg(du, xl))
+            _deliver(tvs[i], wg(dv, u))
+            _deliver(tus[i], wg(du, xl))
           _pending.append(((dv, u, du, xl), run))
         else:
           dvs[i] = wg(dv, u)                                                        # [d, r]
@@ -255,7 +274,7 @@ class CrossNetFn(torch.autograd.Function):
       else:
         if ctx.defer:
           def run(i=i, dv=dv, xl=xl):
-            _deliver(ctx.vs[i], wg(dv, xl))
+            _deliver(tvs[i], wg(dv, xl))
           _pending.append(((dv, xl), run))
         else:
           dvs[i] = wg(dv, xl)                                                       # [d, d]
@@ -277,7 +296,10 @@ def cross_network(x0: torch.Tensor, us, vs, bs, defer_wgrad: bool = False) -> to
       xl = x0f * torch.nn.functional.linear(h, vs[i], bs[i]) + xl
     return xl
   params = (*us, *vs, *bs) if low_rank else (*vs, *bs)
-  return CrossNetFn.apply(x0, len(vs), low_rank, defer_wgrad, *params)
+  if defer_wgrad and x0.requires_grad and torch.is_grad_enabled():
+    targets = (tuple(us) if low_rank else None, tuple(vs), tuple(bs))
+    return CrossNetFn.apply(x0, len(vs), low_rank, targets, *[t.detach() for t in params])
+  return CrossNetFn.apply(x0, len(vs), low_rank, None, *params)
 
 
 class JoinColumnsFn(torch.autograd.Function):
