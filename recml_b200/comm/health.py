@@ -83,6 +83,19 @@ class HealthMonitor:
     if self._thread is not None:
       self._thread.join(timeout=2 * self.interval_s + 1)
 
+  @staticmethod
+  def _left_key(rank: int) -> str:
+    return f"recml/left/{rank}"
+
+  def leave(self) -> None:
+    """Announces that this rank leaves the job (between steps, with none of its kernels or collectives in
+    flight) and stops its heartbeat; the peers' next `check()` raises `PeerFailure` naming it, before they
+    launch anything that would wait for this rank."""
+    try:
+      self.store.set(self._left_key(self.rank), b"1")
+    finally:
+      self.stop()
+
   def _get(self, rank: int) -> bytes | None:
     try:
       if hasattr(self.store, "check") and not self.store.check([self._key(rank)]):
@@ -101,6 +114,14 @@ class HealthMonitor:
     late, ages = [], []
     for r in range(self.world):
       if r == self.rank:
+        continue
+      try:
+        gone = bool(self.store.check([self._left_key(r)])) if hasattr(self.store, "check") else False
+      except Exception:  # pylint: disable=broad-except
+        gone = False
+      if gone:
+        late.append(r)
+        ages.append(0.0)
         continue
       val = self._get(r)
       prev_val, prev_t = self._seen.get(r, (b"", now))

@@ -107,6 +107,51 @@ def check_status(device: torch.device | None = None, sync: bool = True) -> None:
     raise cls(f"device status {vals[0]} ({STATUS_NAMES.get(vals[0], '?')}), detail {vals[1]}")
 
 
+class _StatusPoller:
+  """Looks at the status word without stalling the host: every call issues an asynchronous copy of
+  the word into pinned memory and examines the copy issued by the previous call once its event has
+  completed, so an error reported by a kernel surfaces one or two steps later instead of at the next
+  synchronisation point."""
+
+  def __init__(self, device: torch.device):
+    self.device = device
+    self.pinned = torch.zeros(2, 4, dtype=torch.int32).pin_memory()
+    self.events: list[Any] = [None, None]
+    self.turn = 0
+
+  def poll(self) -> None:
+    buf = status_buffer(self.device)
+    prev = self.turn ^ 1
+    ev = self.events[prev]
+    if ev is not None and ev.query():
+      vals = self.pinned[prev].tolist()
+      self.events[prev] = None
+      if vals[0] != 0:
+        buf.zero_()
+        cls = PeerTimeoutError if vals[0] == 2 else DeviceStatusError
+        raise cls(f"device status {vals[0]} ({STATUS_NAMES.get(vals[0], '?')}), detail {vals[1]}")
+    cur = self.turn
+    if self.events[cur] is None:
+      self.pinned[cur].copy_(buf, non_blocking=True)
+      ev = torch.cuda.Event()
+      ev.record(torch.cuda.current_stream(self.device))
+      self.events[cur] = ev
+      self.turn ^= 1
+
+
+_pollers: dict[int, _StatusPoller] = {}
+
+
+def poll_status(device: torch.device | None = None) -> None:
+  """Non-blocking status check for hot loops (see `_StatusPoller`); `check_status` is the blocking one."""
+  idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+  if idx not in _status:
+    return          # no kernel of this library has run on the device yet
+  if idx not in _pollers:
+    _pollers[idx] = _StatusPoller(torch.device("cuda", idx))
+  _pollers[idx].poll()
+
+
 def check_rc(rc: int, what: str) -> None:
   if rc != 0:
     raise NativeError(f"{what} failed with code {rc}")

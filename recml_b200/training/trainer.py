@@ -143,6 +143,9 @@ class Trainer(core.Trainer[task_lib.Task]):
     mgr = self.checkpoint_manager
     if mgr is None or not mgr.should_save(step):
       return
+    if torch.cuda.is_available():
+      from recml_b200.ops import _lib
+      _lib.check_status()      # raises before anything is written if a kernel reported an error
     with self._progress.timed("checkpointing"):
       mgr.save(step, state.state_dict(), metrics=metrics)
 
@@ -165,7 +168,9 @@ class Trainer(core.Trainer[task_lib.Task]):
     with open(os.path.join(self._model_dir, core.TRAINING_COMPLETE_MARKER_FILE), "w") as f:
       f.write("COMPLETED")
 
-  # -- failure detection: host heartbeats between steps, device status words once per loop ---------------
+  # -- failure detection: host heartbeats and a non-blocking look at the device status word between steps;
+  #    a blocking check at the end of a loop and before every checkpoint, so that a step whose kernels
+  #    reported a timeout, a capacity overflow or a bad index is never saved ---------------------------
   def _start_health(self):
     if not self._failure_detection or self._health is not None:
       return
@@ -179,9 +184,12 @@ class Trainer(core.Trainer[task_lib.Task]):
   def _check_health(self, step: int, end_of_loop: bool = False) -> None:
     if self._health is not None:
       self._health.check(step)
-    if end_of_loop and torch.cuda.is_available():
+    if torch.cuda.is_available():
       from recml_b200.ops import _lib
-      _lib.check_status()
+      if end_of_loop:
+        _lib.check_status()
+      else:
+        _lib.poll_status()
 
   # -- the hot loop ----------------------------------------------------------------------
   def _train_n_steps(self, *, train_iter, train_step, state, start_step: int, num_steps: int,

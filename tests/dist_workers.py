@@ -39,6 +39,54 @@ def entry(rank, world, backend, port, fn_name, args, result_dir):
         pass
 
 
+def leave_entry(rank, world, port, result_dir, announce):
+  """A job whose last rank leaves between steps (host-side failure: no GPU involved).  With `announce`
+  it tells the store first; without, it just exits.  Every rank exits through os._exit so that nobody
+  waits in a barrier for a rank that is gone."""
+  import datetime
+  import time
+  from recml_b200.comm import health
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+  dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+  store = dist.distributed_c10d._get_default_store()   # pylint: disable=protected-access
+  mon = health.HealthMonitor(store, rank, world, interval_s=0.05, timeout_s=1.0).start()
+  out = {"steps_done": 0, "detected": None, "collective_error": None, "seconds": None}
+  t = torch.ones(4)
+  leave_step = 3
+  t0 = time.time()
+  try:
+    for step in range(200):
+      mon.check(step)                       # host check BEFORE anything that waits for peers
+      leaving = rank == world - 1 and step == leave_step
+      if leaving and announce:
+        # announced one step ahead: the leaver still takes part in this step's collective, which no peer can
+        # finish before the announcement is in the store, so every peer sees it at its next check
+        mon.leave()
+      elif leaving:
+        torch.save({"left_at": step}, os.path.join(result_dir, f"rank{rank}.pt"))
+        os._exit(0)
+      try:
+        dist.all_reduce(t)
+        if leaving:
+          torch.save({"left_at": step}, os.path.join(result_dir, f"rank{rank}.pt"))
+          os._exit(0)
+      except Exception as e:  # the peer's socket closed or the process-group timeout ran out
+        out["collective_error"] = type(e).__name__
+        t0 = time.time()
+        while True:                         # the heartbeat names the culprit once it has been silent long enough
+          mon.check(step)
+          time.sleep(0.05)
+          if time.time() - t0 > 10:
+            break
+        break
+      out["steps_done"] += 1
+      time.sleep(0.02)
+  except health.PeerFailure as e:
+    out["detected"], out["seconds"] = list(e.ranks), time.time() - t0
+  torch.save(out, os.path.join(result_dir, f"rank{rank}.pt"))
+  os._exit(0)
+
+
 # ---------------------------------------------------------------------------------------------------
 def _emb_specs():
   from recml_b200 import embedding as emb

@@ -50,6 +50,42 @@ def test_loader_thread_exception_reaches_the_consumer(tmp_path):
     next(fac.make())
 
 
+def _run_leave_job(world, announce, tmp_path):
+  import os
+  import torch.multiprocessing as mp
+  from tests import dist_utils, dist_workers
+  ctx = mp.spawn(dist_workers.leave_entry, args=(world, dist_utils._free_port(), str(tmp_path), announce),
+                 nprocs=world, join=False, start_method="spawn")
+  deadline = time.time() + 60
+  while time.time() < deadline and not ctx.join(timeout=1.0):
+    pass
+  for p in ctx.processes:
+    assert not p.is_alive(), "a rank is still waiting for the one that left"
+  return [torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def test_announced_leave_is_seen_before_the_next_collective(tmp_path):
+  """gloo ranks: the last rank tells the store that it leaves, takes part in one more step and goes; the
+  survivors' host check raises `PeerFailure` naming it before they launch another collective."""
+  res = _run_leave_job(3, True, tmp_path)
+  assert res[2] == {"left_at": 3}
+  for r in res[:2]:
+    assert r["detected"] == [2] and r["collective_error"] is None
+    assert r["steps_done"] == 4          # exactly the steps all ranks took part in (the leaver's last one included)
+
+
+def test_silent_exit_ends_the_collective_and_the_heartbeat_names_the_rank(tmp_path):
+  """gloo ranks: the last rank exits without a word.  The survivor's next collective ends with an error (closed
+  socket or the short process-group timeout) instead of hanging, and the heartbeat check then raises
+  `PeerFailure` for that rank within the heartbeat timeout."""
+  res = _run_leave_job(2, False, tmp_path)
+  assert res[1] == {"left_at": 3}
+  assert res[0]["detected"] == [1]
+  assert res[0]["steps_done"] == 3
+  if res[0]["collective_error"] is not None:      # otherwise the heartbeat fired before the collective was tried
+    assert res[0]["seconds"] < 9.0
+
+
 @pytest.mark.gpu
 def test_device_wait_expires_and_reports_status():
   from recml_b200.ops import _lib
