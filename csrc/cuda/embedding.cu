@@ -253,7 +253,7 @@ struct FwdParams {
   unsigned int* dropped;    // non-null: ids that do not fit the occurrence list are dropped from the lookup and
                             // counted here (allow_id_dropping); null: an overflow is a kCapacity error
   int prefetch;             // 1: ask L2 for a bag's rows as soon as their ids are known
-  int pad;
+  int tiled;                // 1: no sequence feature in this launch -> the 32-bags-per-warp kernel
 };
 
 template <int VPL, bool TRAIN, bool GAINS>
@@ -409,6 +409,161 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
     } else if (lane_on) {
       store_bf16<VPL>(dst_base + slot_row * f.dst_stride, acc);
     }
+  }
+  grid_done_then_signal(p.done_counter, p.flags, p.W, seq);
+}
+
+// ---- forward, tiled: 32 consecutive bags of one (feature, source rank) per warp ----------------------
+// The kernel above gives every bag its own chain of dependent memory latencies (offsets -> ids -> claim of
+// occurrence entries -> rows), which dominates when bags hold one to three ids, as most recommender features
+// do.  Here a warp takes 32 bags at once: one coalesced load brings their 33 offsets, the ids of all of them
+// are contiguous and come in 32-wide chunks, occurrence entries are claimed once per chunk, and the owned
+// rows are gathered eight at a time ACROSS bag boundaries, each bag's sum being stored when its last row
+// has been added.  Pooled features only (a launch with a sequence feature takes the per-bag kernel).
+template <int VPL, bool TRAIN, bool GAINS>
+__global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
+  const unsigned long long seq = seq_of(p.seq);
+  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq, p.status, 0)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int blocks_per = (p.B + 31) / 32;
+  const long long total = static_cast<long long>(p.n_feats) * p.W * blocks_per;
+  const bool lane_on = lane * VPL < p.dloc;
+  constexpr int kDepth = VPL <= 4 ? 8 : 4;
+  for (long long tile = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; tile < total;
+       tile += warps) {
+    const int b0 = static_cast<int>(tile % blocks_per) * 32;
+    const int s = static_cast<int>((tile / blocks_per) % p.W);
+    const FeatDesc f = p.feats[tile / (static_cast<long long>(blocks_per) * p.W)];
+    const int nb = min(32, p.B - b0);                      // bags of this tile
+    const int* offs = p.ids.offsets[s] + static_cast<long long>(f.feat_index) * p.B + b0;
+    const int o_mine = offs[min(lane, nb)];               // lane l: first id of bag l (lanes >= nb: the end)
+    const int p0 = __shfl_sync(0xffffffffu, o_mine, 0);
+    const int p1 = offs[nb];
+    const int* vals = p.ids.values[s];
+    const float* wts = GAINS ? p.ids.weights[s] : nullptr;
+    // combiner denominator of this lane's bag (over the WHOLE bag, not only the rows this rank owns)
+    float scale_mine = 1.f;
+    if (GAINS && f.combiner != kSum) {
+      const int o1 = __shfl_down_sync(0xffffffffu, o_mine, 1);
+      const int e = lane == 31 ? p1 : o1;
+      float den = 0.f;
+      if (lane < nb) {
+        for (int i = o_mine; i < e; ++i) {
+          const float w = wts != nullptr ? wts[i] : 1.f;
+          den += f.combiner == kMean ? w : w * w;
+        }
+      }
+      if (f.combiner == kSqrtN) den = sqrtf(den);
+      scale_mine = den != 0.f ? 1.f / den : 0.f;
+    }
+    __nv_bfloat16* dst_base = p.pooled.p[s] + f.slot_off + (f.kind == kColumnWise ? f.col_lo : 0) + lane * VPL;
+    const long long slot_row0 = (f.kind == kRowWise ? static_cast<long long>(p.me) * p.B : 0) + b0;
+    Vec<VPL> acc;
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+    int cur = 0;          // bag whose sum is being built; bags below it have been stored
+    auto store_upto = [&](int bag) {      // stores bag `cur` (acc) and zeros for the bags between, then cur = bag
+      while (cur < bag) {
+        if (lane_on) store_bf16<VPL>(dst_base + (slot_row0 + cur) * f.dst_stride, acc);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
+        ++cur;
+      }
+    };
+    for (int base = p0; base < p1; base += 32) {
+      const int i = base + lane;
+      int id = -1;
+      float w = 1.f;
+      if (i < p1) id = vals[i];
+      // bag of this id: the last lane whose first id is <= i (offsets are non-decreasing; lanes >= nb hold
+      // the end of the tile).  Every lane runs the five shuffle steps, whatever it holds.
+      int lo = 0, hi = nb;          // o[lo] <= i < o[hi]
+#pragma unroll
+      for (int step = 0; step < 5; ++step) {
+        const int mid = (lo + hi) >> 1;
+        const int om = __shfl_sync(0xffffffffu, o_mine, mid);
+        if (hi - lo > 1) { if (om <= i) lo = mid; else hi = mid; }
+      }
+      const int bag = lo;
+      if (GAINS) {
+        const float sc = __shfl_sync(0xffffffffu, scale_mine, bag);
+        if (i < p1) w = (wts != nullptr ? wts[i] : 1.f) * sc;
+      }
+      bool owned = id >= 0;
+      if (owned && id >= f.vocab) {
+        report(p.status, kBadIndex, id);
+        owned = false;
+      }
+      unsigned int lrow = 0;
+      if (f.kind == kRowWise) {
+        owned = owned && ((id % p.W + f.rot) % p.W == p.me);
+        lrow = f.row_base + id / p.W;
+      } else {
+        lrow = f.row_base + id;
+      }
+      if (owned && p.prefetch) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
+      unsigned int mask = __ballot_sync(0xffffffffu, owned);
+      if (TRAIN && mask != 0) {
+        const int n_own = __popc(mask);
+        unsigned int pos = 0;
+        if (lane == 0) pos = atomicAdd(p.occ_count, static_cast<unsigned int>(n_own));
+        pos = __shfl_sync(0xffffffffu, pos, 0);
+        const unsigned int at = pos + __popc(mask & ((1u << lane) - 1));
+        const bool fits = owned && at < p.occ_cap;
+        if (fits) {
+          const int b = b0 + bag;
+          const long long gvl = p.grad_ld > 0 ? (static_cast<long long>(b) * p.grad_ld + f.grad_off) / 8
+                                              : f.grad_off / p.dloc + (static_cast<long long>(s) * p.B + b);
+          const unsigned int gv = static_cast<unsigned int>(gvl);
+          p.occ_key[at] = lrow;
+          if (GAINS) {
+            p.occ_val[at] = at;
+            p.occ_gain[2 * static_cast<size_t>(at)] = __uint_as_float(gv);
+            p.occ_gain[2 * static_cast<size_t>(at) + 1] = w;
+          } else {
+            p.occ_val[at] = gv;
+          }
+        }
+        const unsigned int over = __ballot_sync(0xffffffffu, owned && !fits);
+        if (over != 0) {
+          if (p.dropped != nullptr) {
+            if (lane == 0) atomicAdd(p.dropped, static_cast<unsigned int>(__popc(over)));
+            mask &= ~over;
+          } else {
+            report(p.status, kCapacity, 1);
+          }
+        }
+      }
+      while (mask) {
+        unsigned int rj[kDepth]; float wj[kDepth]; int bj[kDepth];
+        int n = 0;
+#pragma unroll
+        for (int u = 0; u < kDepth; ++u) {
+          const int j = mask ? __ffs(mask) - 1 : 0;
+          if (mask) { mask &= mask - 1; n = u + 1; }
+          rj[u] = __shfl_sync(0xffffffffu, lrow, j);
+          wj[u] = GAINS ? __shfl_sync(0xffffffffu, w, j) : 1.f;
+          bj[u] = __shfl_sync(0xffffffffu, bag, j);
+        }
+        Vec<VPL> r[kDepth];
+        if (lane_on) {
+#pragma unroll
+          for (int u = 0; u < kDepth; ++u)
+            if (u < n) r[u] = load_f32<VPL>(p.table + static_cast<size_t>(rj[u]) * p.dloc + lane * VPL);
+        }
+#pragma unroll
+        for (int u = 0; u < kDepth; ++u) {
+          if (u >= n) break;
+          if (bj[u] != cur) store_upto(bj[u]);
+          if (lane_on) {
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(wj[u], r[u].v[e], acc.v[e]);
+          }
+        }
+      }
+    }
+    store_upto(nb);       // the open bag and the (empty or un-owned) bags after it
   }
   grid_done_then_signal(p.done_counter, p.flags, p.W, seq);
 }
@@ -825,6 +980,16 @@ extern "C" int recml_emb_push_ids(const PushIdsParams* p, cudaStream_t stream) {
 
 template <int VPL>
 static void launch_fwd(const FwdParams& p, bool train, bool gains, int blocks, cudaStream_t stream) {
+  if (p.tiled) {
+    if (train) {
+      if (gains) emb_fwd_tiled_kernel<VPL, true, true><<<blocks, 256, 0, stream>>>(p);
+      else emb_fwd_tiled_kernel<VPL, true, false><<<blocks, 256, 0, stream>>>(p);
+    } else {
+      if (gains) emb_fwd_tiled_kernel<VPL, false, true><<<blocks, 256, 0, stream>>>(p);
+      else emb_fwd_tiled_kernel<VPL, false, false><<<blocks, 256, 0, stream>>>(p);
+    }
+    return;
+  }
   if (train) {
     if (gains) emb_fwd_kernel<VPL, true, true><<<blocks, 256, 0, stream>>>(p);
     else emb_fwd_kernel<VPL, true, false><<<blocks, 256, 0, stream>>>(p);
@@ -840,7 +1005,7 @@ static int vpl_for(int dloc) { return dloc <= 32 ? 1 : dloc <= 64 ? 2 : dloc <= 
 extern "C" int recml_emb_fwd(const FwdParams* p, int train, int gains, cudaStream_t stream) {
   const int vpl = vpl_for(p->dloc);
   if (vpl == 0 || (p->dloc % vpl) != 0) return -10;
-  const long long items = static_cast<long long>(p->n_feats) * p->W * p->B;
+  const long long items = static_cast<long long>(p->n_feats) * p->W * (p->tiled ? (p->B + 31) / 32 : p->B);
   const int blocks = blocks_for(items, 148 * 8);
   switch (vpl) {
     case 1: launch_fwd<1>(*p, train, gains, blocks, stream); break;

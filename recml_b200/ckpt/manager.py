@@ -46,12 +46,16 @@ class ShardedLeaf:
   chunk grid.  `write` is False on ranks that hold a replica which another rank saves.
   """
 
-  def __init__(self, local: torch.Tensor, global_shape, grid_index, chunk_shape=None, write=True):
+  def __init__(self, local: torch.Tensor, global_shape, grid_index, chunk_shape=None, write=True, mod=None):
     self.local = local
     self.global_shape = tuple(int(s) for s in global_shape)
     self.grid_index = tuple(int(i) for i in grid_index)
     self.chunk_shape = tuple(int(s) for s in (chunk_shape or local.shape))
     self.write = write
+    # Row-sharded embedding tables are stored in MOD layout, `[W, ceil(V / W), ...]` with block r holding the
+    # rows whose id is r modulo W.  `mod = {"vocab": V, "world": W}` records that, so that a job with another
+    # world size can pick its own residue class out of the stored blocks (`_read_mod_resharded`).
+    self.mod = dict(mod) if mod else None
 
 
 def _rank_world(group=None) -> tuple[int, int]:
@@ -208,6 +212,8 @@ class CheckpointManager:
         meta_tree[key] = {"key_path": list(path), "shape": list(leaf.global_shape),
                           "dtype": dt_all, "value_type": "array"}
         sharding[key] = {"sharding_type": "block", "chunk_shape": list(leaf.chunk_shape)}
+        if leaf.mod:
+          sharding[key]["mod"] = leaf.mod
     zarr_io.write_chunks_parallel(pending, self.compressor)
     if rank == 0:
       with open(os.path.join(item, TREE_METADATA), "w") as f:
@@ -283,18 +289,78 @@ def restore_tree(item: str, target: Mapping[str, Any] | None = None) -> Any:
     kinds = {tuple(k.split(".")) if k else (): v for k, v in meta.get("containers", {}).items()}
     return tree_lib.restore_containers(tree_lib.unflatten(leaves), kinds)
   out = {}
+  sharding_meta = {}
+  if os.path.exists(os.path.join(item, SHARDING_FILE)):
+    with open(os.path.join(item, SHARDING_FILE)) as f:
+      sharding_meta = json.load(f)
   for path, leaf in tree_lib.flatten(target):
     key = ".".join(path)
     if key not in meta["tree_metadata"]:
       raise KeyError(f"Checkpoint has no leaf {key!r}")
     leaf_dir = os.path.join(item, key)
     if isinstance(leaf, ShardedLeaf):
+      stored_shape = tuple(zarr_io.read_meta(leaf_dir)["shape"])
+      stored_mod = (sharding_meta.get(key) or {}).get("mod")
+      if stored_shape != leaf.global_shape or (stored_mod is None) != (leaf.mod is None):
+        out[path] = _read_resharded(leaf_dir, stored_shape, stored_mod, leaf)
+        continue
       start = [i * c for i, c in zip(leaf.grid_index, leaf.chunk_shape)]
       stop = [min(s + c, g) for s, c, g in zip(start, leaf.chunk_shape, leaf.global_shape)]
       out[path] = zarr_io.read_region(leaf_dir, start, stop)
     else:
       out[path] = zarr_io.read_region(leaf_dir)
   return tree_lib.restore_containers(tree_lib.unflatten(out), tree_lib.key_types(target))
+
+
+def _read_resharded(leaf_dir: str, stored_shape, stored_mod, leaf: ShardedLeaf) -> torch.Tensor:
+  """This rank's block of a row-sharded array whose layout on disk differs from the target's.
+
+  MOD layout is `[W, ceil(V / W), ...]`, block b = rows with id % W == b at position id // W; the logical
+  layout is `[V, ...]`.  Handled: MOD(W) -> MOD(W'), MOD(W) -> logical row block, logical -> MOD(W').  An id
+  lies in stored block b and in wanted residue class r of W' iff id = b (mod W) and id = r (mod W'), which
+  has solutions only when b = r modulo gcd(W, W'), so only those blocks are read."""
+  import math
+  nd = len(stored_shape)
+  dtype = zarr_io.read_region(leaf_dir, [0] * nd, [0] * nd).dtype
+  if stored_mod is not None:
+    vocab, w_old = int(stored_mod["vocab"]), int(stored_shape[0])
+    tail = tuple(stored_shape[2:])
+
+    def blocks(keep_block):
+      for b in range(w_old):
+        n_b = (vocab - b + w_old - 1) // w_old if vocab > b else 0      # rows of block b that exist
+        if n_b == 0 or not keep_block(b):
+          continue
+        block = zarr_io.read_region(leaf_dir, [b, 0] + [0] * len(tail), [b + 1, n_b] + list(tail))[0]
+        yield b + torch.arange(n_b, dtype=torch.int64) * w_old, block
+
+    if leaf.mod is not None:                                   # MOD(W) -> MOD(W')
+      w_new, rows_new, r = leaf.global_shape[0], leaf.global_shape[1], leaf.grid_index[0]
+      out = torch.zeros((1, rows_new) + tail, dtype=dtype)
+      g = math.gcd(w_old, w_new)
+      for ids, block in blocks(lambda b: (b - r) % g == 0):
+        keep = (ids % w_new) == r
+        out[0, ids[keep] // w_new] = block[keep]
+      return out
+    if leaf.global_shape != (vocab,) + tail:
+      raise ValueError(f"{leaf_dir}: stored MOD layout of a [{vocab}, ...] table does not fit target "
+                       f"{leaf.global_shape}")
+    start = leaf.grid_index[0] * leaf.chunk_shape[0]            # MOD(W) -> rows [start, stop) of the table
+    stop = min(start + leaf.chunk_shape[0], vocab)
+    out = torch.zeros((stop - start,) + tail, dtype=dtype)
+    for ids, block in blocks(lambda b: True):
+      keep = (ids >= start) & (ids < stop)
+      out[ids[keep] - start] = block[keep]
+    return out
+  if leaf.mod is None or tuple(stored_shape[1:]) != tuple(leaf.global_shape[2:]):
+    raise ValueError(f"{leaf_dir} was stored with global shape {tuple(stored_shape)}, the target expects "
+                     f"{leaf.global_shape}; only row-sharded (MOD) leaves can change their world size")
+  w_new, rows_new, r = leaf.global_shape[0], leaf.global_shape[1], leaf.grid_index[0]   # logical -> MOD(W')
+  full = zarr_io.read_region(leaf_dir)
+  mine = full[r::w_new]
+  out = torch.zeros((1, rows_new) + tuple(stored_shape[1:]), dtype=dtype)
+  out[0, :mine.shape[0]] = mine
+  return out
 
 
 def _jsonable(x: Any) -> Any:

@@ -58,7 +58,7 @@ class FwdParams(ctypes.Structure):
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
               ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
               ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp), ("dropped", c_vp),
-              ("prefetch", c_int), ("pad", c_int)]
+              ("prefetch", c_int), ("tiled", c_int)]
 
 
 class CombineDesc(ctypes.Structure):
@@ -141,6 +141,7 @@ class FusedBackend:
     self.bwd_blocks_per_sm = int(os.environ.get("RECML_EMB_BWD_BLOCKS", "0"))
     self.side_streams = os.environ.get("RECML_EMB_STREAMS", "1") != "0"
     self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
+    self.fwd_tiled = os.environ.get("RECML_EMB_FWD_TILED", "1") != "0"
     self.dropped = torch.zeros(1, dtype=torch.int32, device=module.device) if module.config.allow_id_dropping else None
     self._hp_slot = 0
     from recml_b200.utils import graphs
@@ -421,6 +422,7 @@ class FusedBackend:
         fp.dropped = self.dropped.data_ptr() if self.dropped is not None else None
       fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
       fp.prefetch = self.fwd_prefetch
+      fp.tiled = int(self.fwd_tiled and all(L == 0 for f_, _, _, L in self.layout if f_ in info["feat_names"]))
       fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),

@@ -349,7 +349,7 @@ class ShardedEmbedding(nn.Module):
       gshape = (W, rows) if rowwise else (W, rows, tp.dim)
       chunk = (1, rows) if rowwise else (1, rows, tp.dim)
       idx = (res, 0) if rowwise else (res, 0, 0)
-      return ShardedLeaf(local[None], gshape, idx, chunk)
+      return ShardedLeaf(local[None], gshape, idx, chunk, mod={"vocab": tp.vocab, "world": W})
     if tp.placement is Placement.COLUMN_WISE:
       if rowwise:
         return ShardedLeaf(local, (tp.vocab,), (0,), (tp.vocab,), write=self.rank == 0)

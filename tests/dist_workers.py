@@ -39,6 +39,40 @@ def entry(rank, world, backend, port, fn_name, args, result_dir):
         pass
 
 
+def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank):
+  """Trains a row-sharded (MOD) embedding for two steps and checkpoints it.  With `fail_rank` >= 0 that
+  rank's chunk writer raises, and the save must commit nothing on any rank."""
+  from recml_b200 import ckpt, embedding as emb
+  from recml_b200.ckpt import zarr_io
+  specs = {"a": emb.EmbeddingSpec(37, 8, combiner="sum"), "b": emb.EmbeddingSpec(10, 8, combiner="sum")}
+  cfg = emb.ShardedEmbeddingConfig(specs, emb.AdagradOptimizerSpec(learning_rate=0.1), sharding_strategy="MOD",
+                                   backend="collective")
+  m = emb.ShardedEmbedding(cfg, device="cpu")
+  gen = np.random.default_rng(rank)
+  for _ in range(2):
+    feats = {k: [gen.integers(0, s.input_dim, size=3).tolist() for _ in range(4)] for k, s in specs.items()}
+    out = m(emb.KeyedJagged.from_lists(feats))
+    (out if isinstance(out, torch.Tensor) else sum(o.sum() for o in out.values())).sum().backward()
+  mgr = ckpt.CheckpointManager(ckpt_dir, async_save=False)
+  mgr.save(1, {"sharded": m.sharded_state_dict()})           # a good checkpoint first
+  raised = None
+  if fail_rank >= 0:
+    real = zarr_io.write_chunks_parallel
+    if rank == fail_rank:
+      def boom(*a, **k):
+        raise IOError("disk full (injected)")
+      zarr_io.write_chunks_parallel = boom
+    try:
+      mgr.save(2, {"sharded": m.sharded_state_dict()})
+    except Exception as e:  # pylint: disable=broad-except
+      raised = type(e).__name__
+    zarr_io.write_chunks_parallel = real
+  tables = {n: m.gather_table(n) for n in specs}
+  slots = {n: m.gather_table(n, "accumulator") for n in specs}
+  return {"tables": tables, "slots": slots, "raised": raised, "steps": mgr.all_steps(),
+          "listing": sorted(os.listdir(ckpt_dir))}
+
+
 def leave_entry(rank, world, port, result_dir, announce):
   """A job whose last rank leaves between steps (host-side failure: no GPU involved).  With `announce`
   it tells the store first; without, it just exits.  Every rank exits through os._exit so that nobody

@@ -71,6 +71,33 @@ def test_sharded_leaf_resharding(tmp_path):
   torch.testing.assert_close(m.restore(0, target={"t": tgt})["t"], full[4:8])
 
 
+@pytest.mark.parametrize("new_world", [1, 3, 4])
+def test_mod_sharded_leaf_restores_on_another_world_size(tmp_path, new_world):
+  """A row-sharded table saved by 2 ranks in MOD layout (block b = ids with id % 2 == b) is read back by
+  jobs of 1, 3 and 4 ranks, each rank getting exactly its residue class; a plain block leaf whose global
+  shape changed is refused."""
+  V, D, W = 11, 3, 2
+  full = torch.arange(V * D, dtype=torch.float32).reshape(V, D)
+  rows = (V + W - 1) // W
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  mod = {"vocab": V, "world": W}
+  blocks = [full[b::W] for b in range(W)]
+  m.save(0, {"t": ckpt.ShardedLeaf(blocks[0][None], (W, rows, D), (0, 0, 0), (1, rows, D), mod=mod)})
+  pad = torch.zeros(rows, D)
+  pad[:blocks[1].shape[0]] = blocks[1]
+  zarr_io.write_chunk(str(tmp_path / "0" / "state" / "t"), (1, 0, 0), pad[None].numpy(), None)
+  rows_new = (V + new_world - 1) // new_world
+  for r in range(new_world):
+    want = full[r::new_world]
+    tgt = ckpt.ShardedLeaf(torch.zeros(1, want.shape[0], D), (new_world, rows_new, D), (r, 0, 0), (1, rows_new, D),
+                           mod={"vocab": V, "world": new_world})
+    got = m.restore(0, target={"t": tgt})["t"]
+    torch.testing.assert_close(got[0][:want.shape[0]], want)
+  plain = ckpt.ShardedLeaf(torch.zeros(1, rows_new, D), (new_world + 5, rows_new, D), (0, 0, 0), (1, rows_new, D))
+  with pytest.raises(ValueError, match="does not fit target"):
+    m.restore(0, target={"t": plain})
+
+
 @pytest.mark.skipif(not zarr_io.zstd_available(), reason="libzstd not loadable")
 def test_zstd_chunks(tmp_path):
   m = ckpt.CheckpointManager(str(tmp_path), async_save=False, compressor="zstd")

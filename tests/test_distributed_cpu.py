@@ -47,3 +47,28 @@ def test_vocab_rank_sharded_gloo():
 def test_sasrec_tiny_two_ranks():
   res = dist_utils.run_ranks("sequence_experiment", 2, "gloo", "cpu", "sasrec", 30)
   assert res[0]["train"]["loss"] < 1.45 and 0.0 <= res[0]["val"]["ndcg@10"] <= 1.0
+
+
+def test_row_wise_table_saved_by_two_ranks_restores_on_one(tmp_path):
+  """MOD-sharded tables and their optimizer slots written by a 2-rank job are restored by a 1-rank job."""
+  from recml_b200 import ckpt, embedding as emb
+  d = str(tmp_path / "ck")
+  res = dist_utils.run_ranks("save_row_wise_tables", 2, "gloo", "cpu", d, -1)
+  specs = {"a": emb.EmbeddingSpec(37, 8, combiner="sum"), "b": emb.EmbeddingSpec(10, 8, combiner="sum")}
+  cfg = emb.ShardedEmbeddingConfig(specs, emb.AdagradOptimizerSpec(learning_rate=0.1), sharding_strategy="MOD",
+                                   backend="collective")
+  m = emb.ShardedEmbedding(cfg, device="cpu")
+  got = ckpt.CheckpointManager(d, async_save=False).restore(1, target={"sharded": m.sharded_state_dict()})
+  m.load_sharded_state_dict(got["sharded"])
+  for n in specs:
+    torch.testing.assert_close(m.gather_table(n), res[0]["tables"][n])
+    torch.testing.assert_close(m.gather_table(n, "accumulator"), res[0]["slots"][n])
+
+
+def test_failed_shard_write_commits_nothing_on_any_rank(tmp_path):
+  d = str(tmp_path / "ck")
+  res = dist_utils.run_ranks("save_row_wise_tables", 2, "gloo", "cpu", d, 1)
+  assert res[0]["raised"] == "RuntimeError" and res[1]["raised"] == "OSError"
+  for r in res:
+    assert r["steps"] == [1]                           # the good checkpoint survives, step 2 does not exist
+    assert not any(".orbax-checkpoint-tmp-" in n for n in r["listing"])
