@@ -84,6 +84,12 @@ class Optimizer:
                *, learning_rate: float | Schedule, scaling: Scaling, weight_decay: float | None,
                grad_clip_norm: float | None, weight_decay_mask: Mask, freeze_mask: Mask | None):
     items = list(named_params.items()) if isinstance(named_params, Mapping) else list(named_params)
+    # kept so that a partitioner can bind the same update rule to the shards of the parameters
+    self._config = dict(learning_rate=learning_rate, scaling=scaling, weight_decay=weight_decay,
+                        grad_clip_norm=grad_clip_norm, weight_decay_mask=weight_decay_mask, freeze_mask=freeze_mask)
+    # set by a partitioner whose parameters are sharded: sums a squared-norm over the ranks that hold the
+    # other shards, so that global-norm clipping sees the whole gradient
+    self.sq_norm_sync = None
     freeze = _as_mask(freeze_mask)
     wd_mask = _as_mask(weight_decay_mask) or default_weight_decay_mask
     self.names = [n for n, p in items if not (freeze and freeze(n, p))]
@@ -137,7 +143,10 @@ class Optimizer:
       return
     gs = [g.to(torch.float32) for g in gs]
     if self.grad_clip_norm is not None:
-      norm = torch.sqrt(sum((g * g).sum() for g in gs))
+      sq = sum((g * g).sum() for g in gs)
+      if self.sq_norm_sync is not None:
+        sq = self.sq_norm_sync(params, gs, sq)
+      norm = torch.sqrt(sq)
       self.last_grad_norm = norm
       # optax.clip_by_global_norm: g * (clip / max(norm, clip))
       factor = self.grad_clip_norm / torch.clamp(norm, min=self.grad_clip_norm)
@@ -182,6 +191,12 @@ class Optimizer:
   def zero_grad(self) -> None:
     for p in self.params:
       p.grad = None
+
+  def rebind(self, named_params) -> "Optimizer":
+    """A fresh optimizer with this one's configuration over other tensors (slots start from scratch)."""
+    new = Optimizer(named_params, **self._config)
+    new.count = self.count
+    return new
 
   def reset_step_count(self) -> None:
     """Restarts the schedule / bias-correction clock while keeping the slots (the

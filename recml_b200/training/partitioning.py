@@ -209,12 +209,20 @@ class DataParallelPartitioner(NullPartitioner):
 
 
 class ModelParallelPartitioner(DataParallelPartitioner):
-  """N-D mesh: `axes=[("data", -1), ("model", 2)]`; the batch is split over `dp_axes`
-  and parameters are sharded according to `rules`, a list of `(regex over the dotted
-  parameter name, spec)` where `spec` has one mesh-axis name or None per tensor dim
-  (the torch rendering of `nn.with_partitioning` + logical→mesh rules,
-  `partitioning.py:148-288`).  Sharded parameters are cut in place at init and tagged
-  `_recml_partitioned`; their gradients are reduced over the data axes only.
+  """N-D mesh: `axes=[("data", -1), ("model", 2)]`; the batch is split over the first `dp_axes` axes and
+  parameters are sharded according to `rules`, a list of `(regex over the dotted parameter name, spec)`
+  where `spec` has one mesh-axis name or None per tensor dim (the torch rendering of
+  `nn.with_partitioning` + logical→mesh rules, `recml/core/training/partitioning.py:148-288`).
+
+  What the reference leaves to the compiler happens explicitly here.  A sharded parameter exists twice:
+  the SHARD (`[out / n, in]` for a spec `("model", None)`) is what the state, the optimizer (so its slots
+  are shard-sized) and the checkpoints hold; the model keeps computing with a FULL tensor that is
+  re-assembled from the shards (all-gather over the spec's mesh axes) at the start of every step.  After
+  backward the full gradient is cut back onto the shard: sliced when the ranks along the axis saw the
+  same batch (axis outside the data axes), reduce-scattered when they saw different batches (axis among
+  the data axes: fully-sharded data parallelism); the data axes the parameter is not sharded over are
+  then averaged.  Layers that are tensor-parallel by construction (`recml_b200.layers.parallel`) own
+  their shards already: they are tagged by the layer and only get their mesh placement here.
   """
 
   def __init__(self, axes: Sequence[tuple[str, int]], dp_axes: int = 1,
@@ -237,6 +245,7 @@ class ModelParallelPartitioner(DataParallelPartitioner):
     me = dist.get_rank() if dist.is_initialized() else 0
     self.coords = dict(zip(names, (int(c[0]) for c in np.where(self.mesh == me))))
     self._axis_groups: dict[str, Any] = {}
+    self._sharded: dict[str, tuple[torch.Tensor, torch.Tensor, tuple]] = {}
     if dist.is_initialized() and world > 1:
       for ai, name in enumerate(names):
         moved = np.moveaxis(self.mesh, ai, -1).reshape(-1, sizes[ai])
@@ -257,6 +266,13 @@ class ModelParallelPartitioner(DataParallelPartitioner):
   def axis_group(self, name: str):
     return self._axis_groups.get(name)
 
+  def axis_size(self, name: str) -> int:
+    return self.axis_sizes[self.axis_names.index(name)]
+
+  @property
+  def dp_size(self) -> int:
+    return int(np.prod([self.axis_size(a) for a in self.dp_axis_names])) if self.dp_axis_names else 1
+
   def spec_for(self, name: str, ndim: int) -> tuple[str | None, ...] | None:
     for pat, spec in self.rules:
       if pat.search(name):
@@ -265,34 +281,147 @@ class ModelParallelPartitioner(DataParallelPartitioner):
         return spec
     return None
 
+  # -- placement ---------------------------------------------------------------------------------------
+  def _grid(self, spec, shard_shape):
+    """(global shape, block index, write?) of a shard with mesh spec `spec`; one replica writes it."""
+    gshape, index = [], []
+    for dim, axis in enumerate(spec):
+      n = self.axis_size(axis) if axis is not None else 1
+      gshape.append(shard_shape[dim] * n)
+      index.append(self.coords[axis] if axis is not None else 0)
+    used = {a for a in spec if a is not None}
+    write = all(self.coords[a] == 0 for a in self.axis_names if a not in used)
+    return tuple(gshape), tuple(index), write
+
   def _shard_state(self, state: state_lib.State) -> state_lib.State:
+    new_params: dict[str, torch.Tensor] = {}
+    self._sharded = {}
     with torch.no_grad():
       for name, p in state.params.items():
-        spec = getattr(p, "_recml_spec", None) or self.spec_for(name, p.ndim)
-        if spec is None:
+        tp_spec = getattr(p, "_recml_tp_spec", None)
+        if tp_spec is not None:              # a tensor-parallel layer's own shard: placement only
+          spec = tuple(tp_spec)
+          p._recml_partitioned, p._recml_spec = True, spec
+          p._recml_grid = self._grid(spec, tuple(p.shape))
+          new_params[name] = p
+          continue
+        spec = self.spec_for(name, p.ndim)
+        if spec is None or all(a is None for a in spec):
+          new_params[name] = p
           continue
         piece = p.data
         for dim, axis in enumerate(spec):
           if axis is None:
             continue
-          n, i = self.axis_sizes[self.axis_names.index(axis)], self.coords[axis]
+          n, i = self.axis_size(axis), self.coords[axis]
           if piece.shape[dim] % n:
             raise ValueError(f"{name} dim {dim} ({piece.shape[dim]}) not divisible by {n}.")
           piece = piece.chunk(n, dim=dim)[i]
-        p.data = piece.contiguous()
-        p._recml_partitioned = True
-        p._recml_spec = tuple(spec)
+        shard = torch.nn.Parameter(piece.contiguous().clone(), requires_grad=p.requires_grad)
+        shard._recml_partitioned, shard._recml_spec = True, tuple(spec)
+        shard._recml_grid = self._grid(spec, tuple(shard.shape))
+        self._sharded[name] = (p, shard, tuple(spec))
+        new_params[name] = shard
+    state.params = new_params
+    if state.optimizer is not None and (self._sharded or any(
+        getattr(p, "_recml_partitioned", False) for p in new_params.values())):
+      # slots must have the shards' shapes: bind the same update rule to the new parameter set
+      state.optimizer = state.optimizer.rebind({n: p for n, p in new_params.items() if p.requires_grad})
+      state.optimizer.sq_norm_sync = self._sq_norm_sync
+    state.pre_sync = self._scatter_grads
     return state
+
+  # -- per step: shards -> full tensors before compute, full gradients -> shards after backward ----------
+  @torch.no_grad()
+  def gather_params(self) -> None:
+    for full, shard, spec in self._sharded.values():
+      piece = shard.data
+      for dim in range(len(spec) - 1, -1, -1):
+        axis = spec[dim]
+        if axis is None or self.axis_size(axis) == 1:
+          continue
+        parts = [torch.empty_like(piece) for _ in range(self.axis_size(axis))]
+        dist.all_gather(parts, piece.contiguous(), group=self._axis_groups[axis])
+        piece = torch.cat(parts, dim=dim)
+      full.copy_(piece)        # in place and counted: cached bf16 compute copies of `full` notice the change
+
+  @torch.no_grad()
+  def _scatter_grads(self, state: state_lib.State) -> None:
+    for full, shard, spec in self._sharded.values():
+      g = full.grad
+      full.grad = None
+      if g is None:
+        continue
+      g = g.to(torch.float32)
+      for dim, axis in enumerate(spec):
+        if axis is None:
+          continue
+        n, i = self.axis_size(axis), self.coords[axis]
+        if n == 1:
+          continue
+        if axis in self.dp_axis_names:          # ranks along this axis saw different batches: sum, keep own block
+          parts = [c.contiguous() for c in g.chunk(n, dim=dim)]
+          out = torch.empty_like(parts[i])
+          if dist.get_backend(self._axis_groups[axis]) == "gloo":
+            for r in range(n):                 # gloo has no reduce_scatter: n reductions, one kept
+              dist.reduce(parts[r], dst=dist.get_global_rank(self._axis_groups[axis], r), group=self._axis_groups[axis])
+            out = parts[i]
+          else:
+            dist.reduce_scatter(out, parts, group=self._axis_groups[axis])
+          g = out
+        else:                                   # same batch on every rank of the axis: the block is complete
+          g = g.chunk(n, dim=dim)[i].contiguous()
+      for axis in self.dp_axis_names:           # data axes the parameter is not sharded over
+        if axis not in spec and self.axis_size(axis) > 1:
+          dist.all_reduce(g, group=self._axis_groups[axis])
+      if self.dp_size > 1:
+        g = g / self.dp_size
+      shard.grad = g.to(shard.dtype)
+
+  def _sq_norm_sync(self, params, grads, sq):
+    """Squared gradient norm over ALL shards: the part of `sq` that comes from sharded parameters is summed
+    over the mesh axes they are sharded over."""
+    by_axes: dict[tuple, torch.Tensor] = {}
+    rest = sq.clone()
+    for p, g in zip(params, grads):
+      spec = getattr(p, "_recml_spec", None)
+      axes = tuple(sorted({a for a in (spec or ()) if a is not None and self.axis_size(a) > 1}))
+      if not axes:
+        continue
+      part = (g * g).sum()
+      rest = rest - part
+      by_axes[axes] = by_axes.get(axes, torch.zeros_like(part)) + part
+    for axes, part in by_axes.items():
+      for a in axes:
+        dist.all_reduce(part, group=self._axis_groups[a])
+      rest = rest + part
+    return rest
+
+  def all_reduce_grads(self, params: Sequence[torch.Tensor]) -> None:
+    """Replicated parameters are averaged over the data group; shards cut from full tensors were averaged
+    when their gradients were scattered; a tensor-parallel layer's shards see the same batch along their
+    own axis and are averaged over the data group like replicated ones."""
+    own = {id(s) for _, s, _ in self._sharded.values()}
+    super().all_reduce_grads([p for p in params if id(p) not in own])
 
   def partition_init(self, init_fn, *, abstract_batch=None):
     def wrapped(batch):
       st = init_fn(batch)
-      if self.world > 1 or (dist.is_initialized() and dist.get_world_size() > 1):
-        src = 0
+      if dist.is_initialized() and dist.get_world_size() > 1:
         with torch.no_grad():
           for t in list(st.params.values()) + list(st.mutable.values()):
-            dist.broadcast(t, src=src)
+            if getattr(t, "_recml_tp_spec", None) is None:     # a TP layer's shards differ by construction
+              dist.broadcast(t, src=0)
       st = self._shard_state(st)
       st.grad_sync = self.all_reduce_grads
       return st
     return wrapped
+
+  def partition_step(self, fn, *, training: bool = False):
+    inner = super().partition_step(fn, training=training)
+
+    def step(inputs, state):
+      if self._sharded:
+        self.gather_params()
+      return inner(inputs, state)
+    return step

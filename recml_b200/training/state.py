@@ -45,6 +45,9 @@ class State:
     # Installed by a partitioner: called with the list of params between backward and the
     # optimizer step (data-parallel gradient all-reduce).
     self.grad_sync: Callable[[list[torch.Tensor]], None] | None = None
+    # Installed by a partitioner with sharded parameters: moves the gradients of the gathered (full)
+    # tensors the model computed with onto the shards the optimizer owns.
+    self.pre_sync: Callable[["State"], None] | None = None
 
   @classmethod
   def create(cls, *, model: nn.Module | None = None, params=None,
@@ -64,6 +67,8 @@ class State:
     if grads is not None:
       for n, g in grads.items():
         self.params[n].grad = g
+    if self.pre_sync is not None:
+      self.pre_sync(self)
     on_cuda = any(p.is_cuda for p in self.optimizer.params[:1])
     if on_cuda:
       # weight gradients queued during backward (`ops.dense`) run on their own stream; they must be in
@@ -104,11 +109,15 @@ class State:
   def state_dict(self) -> dict[str, Any]:
     sd: dict[str, Any] = {
         "step": torch.tensor(self.step, dtype=torch.int64),
-        "params": {n: p.detach() for n, p in self.params.items()},
+        "params": {n: _leaf_of(p, p.detach()) for n, p in self.params.items()},
         "mutable": {n: b.detach() for n, b in self.mutable.items()},
     }
     if self.optimizer is not None:
       sd["opt_state"] = self.optimizer.state_dict()
+      by_name = dict(zip(self.optimizer.names, self.optimizer.params))
+      for slot, entries in sd["opt_state"].items():
+        if isinstance(entries, dict):
+          sd["opt_state"][slot] = {n: _leaf_of(by_name.get(n), t) for n, t in entries.items()}
     sharded = {n or "root": m.sharded_state_dict() for n, m in self.sharded_modules().items()}
     if sharded:
       sd["sharded"] = sharded
@@ -129,6 +138,17 @@ class State:
     if restore_step:
       self.step = int(sd["step"])
     return self
+
+
+def _leaf_of(param, tensor):
+  """Checkpoint leaf for `tensor` (a parameter or one of its optimizer slots): a block of a global array
+  when the parameter is a shard placed by a partitioner, the tensor itself otherwise."""
+  grid = getattr(param, "_recml_grid", None)
+  if grid is None or tensor.shape != param.shape:
+    return tensor
+  from recml_b200.ckpt.manager import ShardedLeaf
+  global_shape, index, write = grid
+  return ShardedLeaf(tensor.detach(), global_shape, index, tuple(tensor.shape), write=write)
 
 
 # Names of the reference API (`recml/__init__.py:19-40`).

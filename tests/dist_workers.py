@@ -73,6 +73,83 @@ def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank):
           "listing": sorted(os.listdir(ckpt_dir))}
 
 
+class _ToyNet(torch.nn.Module):
+  def __init__(self, tp_group=None):
+    super().__init__()
+    from recml_b200.layers import dense, parallel
+    torch.manual_seed(0)
+    self.a = dense.Linear(8, 16, activation="relu")
+    self.b = dense.Linear(16, 16, activation="relu")
+    self.tp = parallel.TensorParallelMLP(16, 32, 16, group=tp_group) if tp_group != "none" else None
+    self.c = dense.Linear(16, 1)
+
+  def forward(self, x):
+    h = self.b(self.a(x))
+    if self.tp is not None:
+      h = h + self.tp(h)
+    return self.c(h).reshape(-1)
+
+
+def _toy_batches(steps, n):
+  g = torch.Generator().manual_seed(7)
+  return [(torch.randn(n, 8, generator=g), torch.randn(n, generator=g)) for _ in range(steps)]
+
+
+def sharded_state_training(rank, world, device_type, axes, dp_axes, rules, steps, ckpt_dir, with_tp):
+  """Trains a small MLP whose parameters are sharded by `rules` over the mesh `axes`; returns the final
+  FULL parameters (gathered) and the loss history, for comparison with a replicated single-process run."""
+  from recml_b200 import ckpt
+  from recml_b200.training import optim_factory, partitioning, state as state_lib
+  part = partitioning.ModelParallelPartitioner(axes, dp_axes=dp_axes, rules=rules, device="cpu") if world > 1 or axes \
+      else partitioning.NullPartitioner("cpu")
+  tp_group = part.axis_group("model") if (with_tp and hasattr(part, "axis_group")) else (None if with_tp else "none")
+  factory = optim_factory.AdamFactory(learning_rate=1e-2, grad_clip_norm=1.0)
+  state = part.partition_init(lambda b: state_lib.State.create(model=_ToyNet(tp_group), tx=factory.make()))(None)
+  dp = getattr(part, "dp_size", 1)
+  # data-parallel rank = position along the data axes (ranks along "model" see the same slice)
+  dp_rank = 0
+  if hasattr(part, "coords"):
+    for a in part.dp_axis_names:
+      dp_rank = dp_rank * part.axis_size(a) + part.coords[a]
+  losses = []
+
+  def train_step(batch, st):
+    x, y = batch
+    loss = ((st.model(x) - y) ** 2).mean()
+    loss.backward()
+    st.update()
+    return st, loss.detach()
+
+  step = part.partition_step(train_step, training=True)
+  n = 16
+  for x, y in _toy_batches(steps, n):
+    sl = slice(dp_rank * n // dp, (dp_rank + 1) * n // dp)
+    state, loss = step((x[sl], y[sl]), state)
+    losses.append(float(loss))
+  shapes = {k: tuple(p.shape) for k, p in state.params.items()}
+  slot_shapes = {k: tuple(t.shape) for k, t in zip(state.optimizer.names, state.optimizer.slots["mu"])}
+  restored_ok = None
+  if ckpt_dir:
+    mgr = ckpt.CheckpointManager(ckpt_dir, async_save=False)
+    mgr.save(steps, state.state_dict())
+    before = {k: p.detach().clone() for k, p in state.params.items()}
+    with torch.no_grad():
+      for p in state.params.values():
+        p.zero_()
+    state.load_state_dict(mgr.restore(steps, target=state.state_dict()))
+    # shards come back bit-exact; replicated leaves are rank 0's copy, equal up to float reassociation
+    restored_ok = all(torch.allclose(before[k], p, rtol=1e-5, atol=1e-7) for k, p in state.params.items()) and all(
+        torch.equal(before[k], p) for k, p in state.params.items() if getattr(p, "_recml_partitioned", False))
+    stored = {k: tuple(v.shape) for k, v in mgr.restore(steps)["params"].items()} if rank == 0 else None
+  else:
+    stored = None
+  if hasattr(part, "gather_params"):
+    part.gather_params()
+  full = {k: p.detach().clone() for k, p in state.model.named_parameters() if "tp." not in k}
+  return {"losses": losses, "full": full, "shapes": shapes, "slot_shapes": slot_shapes, "restored_ok": restored_ok,
+          "stored": stored}
+
+
 def leave_entry(rank, world, port, result_dir, announce):
   """A job whose last rank leaves between steps (host-side failure: no GPU involved).  With `announce`
   it tells the store first; without, it just exits.  Every rank exits through os._exit so that nobody
