@@ -368,6 +368,8 @@ class ShardedEmbedding(nn.Module):
         continue
       for key, buf in [("table", self.stack_weights[tp.stack])] + list(
           self.stack_slots[tp.stack].items()):
+        if key not in sd[name]:          # an export without optimizer slots: keep the initial ones
+          continue
         dst = buf[tp.row_base:tp.row_base + tp.local_rows]
         src = torch.as_tensor(sd[name][key])
         if tp.placement is Placement.ROW_WISE:

@@ -113,6 +113,22 @@ class PredictionTask(task_lib.Task):
     logits = state.model(batch["dense"], batch["sparse"])
     return self._metrics(bce.bce_with_logits(logits, batch["label"]), logits.numel())
 
+  def model_kwargs(self) -> dict[str, Any]:
+    """Keyword arguments that rebuild the module (`serving.load` adds device and group)."""
+    c = self.cfg
+    return dict(vocab_sizes=list(c.vocab_sizes), embedding_dim=c.embedding_dim, num_dense=c.num_dense,
+                bottom_mlp_dims=list(c.bottom_mlp_dims), top_mlp_dims=list(c.top_mlp_dims),
+                num_cross_layers=c.num_cross_layers, cross_rank=c.cross_rank, bag_sizes=list(c.bag_sizes),
+                row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend, init_scale=c.embedding_init_scale)
+
+  def export_model(self, state, model_dir: str) -> None:
+    """Writes `<model_dir>/export`: the module's weights (tables shard by shard) and the recipe to rebuild
+    it for serving (`recml_b200.serving.load`).  Collective: every rank of the job calls it."""
+    import os
+    from recml_b200 import serving
+    serving.export(state.model, os.path.join(model_dir, "export"), builder="recml_b200.models.dlrm:DLRMDCNv2",
+                   kwargs=self.model_kwargs(), step=state.step)
+
 
 def features_summary(c: ModelConfig) -> str:
   return f"{len(c.vocab_sizes)} tables, {sum(c.bag_sizes)} ids/sample, dim {c.embedding_dim}"

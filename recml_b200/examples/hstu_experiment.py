@@ -94,6 +94,18 @@ class HSTUTask(task_lib.Task):
     return (batch["input_ids"], batch["target_ids"], batch["negative_ids"], batch["seq_offsets"],
             batch["timestamps"], batch["target_weights"])
 
+  def export_model(self, state, model_dir: str) -> None:
+    """`<model_dir>/export` for `recml_b200.serving.load` (collective: every rank writes its table shards)."""
+    import os
+    from recml_b200 import serving
+    c = self.cfg
+    serving.export(state.model, os.path.join(model_dir, "export"),
+                   builder="recml_b200.models.hstu_retrieval:HSTURetrieval",
+                   kwargs=dict(vocab_size=c.vocab_size, model_dim=c.model_dim, num_heads=c.num_heads,
+                               num_layers=c.num_layers, max_seq_len=c.max_seq_len, token_capacity=c.token_capacity,
+                               num_negatives=c.num_negatives, num_in_batch=c.num_in_batch, backend=c.backend),
+                   step=state.step)
+
   def train_step(self, batch, state, rng):
     state.model.train()
     loss, hit = state.model(*self._args(batch))

@@ -97,6 +97,17 @@ class SASRecTask(task_lib.Task):
     n = batch["padding_mask"].sum().float()
     return state, {"loss": M.Mean(total=loss.detach() * n, count=n)}
 
+  def export_model(self, state, model_dir: str) -> None:
+    """`<model_dir>/export` for `recml_b200.serving.load` (collective: every rank writes its table shards)."""
+    import os
+    from recml_b200 import serving
+    c = self.cfg
+    serving.export(state.model, os.path.join(model_dir, "export"),
+                   builder="recml_b200.models.sasrec_retrieval:SASRecRetrieval",
+                   kwargs=dict(vocab_size=c.vocab_size, max_positions=c.max_positions, model_dim=c.model_dim,
+                               mlp_dim=c.mlp_dim, num_heads=c.num_heads, num_layers=c.num_layers,
+                               batch_size=c.batch_size, backend=c.backend), step=state.step)
+
   def eval_step(self, batch, state):
     """Leave-last-out: the history is everything but the final item, the target is the final item."""
     state.model.eval()

@@ -35,7 +35,9 @@ class Task(abc.ABC):
     return state
 
   def export_model(self, state: state_lib.State, model_dir: str) -> None:
-    """Hook called by rank 0 once training completes."""
+    """Hook called once training completes, on EVERY rank (exporting sharded embedding tables is a
+    collective: see `recml_b200.serving.export`); an override that only writes files should do so on
+    rank 0."""
     del state, model_dir
 
 

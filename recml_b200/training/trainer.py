@@ -290,7 +290,9 @@ class Trainer(core.Trainer[task_lib.Task]):
       mgr.wait_until_finished()
     if _process_index() == 0:
       self._write_marker_file()
-      task.export_model(state, self._model_dir)
+    # The reference calls the hook on process 0 only; here every rank calls it, because an export of
+    # sharded tables is collective (each rank writes its shards).  Hooks that only write files guard on rank.
+    task.export_model(state, self._model_dir)
     if mgr is not None:
       mgr.close()
       del self.checkpoint_manager

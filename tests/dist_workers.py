@@ -313,6 +313,26 @@ def dlrm_tiny_training(rank, world, device_type, steps, use_graph=False):
           "ckpts": sorted(_os.listdir(_os.path.join(box[0], "checkpoints")))}
 
 
+def dlrm_tiny_export(rank, world, device_type, model_dir):
+  """Trains the tiny DLRM on `world` ranks with row-sharded tables; the trainer's final export is collective."""
+  from recml_b200 import config as C, run_experiment
+  from recml_b200.examples import dlrm_experiment as D
+  cfg = D.tiny_experiment(model_dir=model_dir, train_steps=4, batch_size=64)
+  cfg.task.model.row_wise_min_bytes = 0          # every table row-wise: shards on both ranks
+  cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, device="cpu")
+  exp = C.build(cfg)
+  run_experiment(exp, "train")
+  # the trained module is not returned by the trainer: rebuild it from the last checkpoint
+  from recml_b200 import ckpt
+  it = exp.task.create_datasets()[0]
+  state = exp.task.create_state(next(it), torch.Generator().manual_seed(0))
+  mgr = ckpt.CheckpointManager(os.path.join(model_dir, "checkpoints"), async_save=False)
+  state.load_state_dict(mgr.restore(mgr.latest_step(), target=state.state_dict()))
+  emb_mod = state.model.embedding
+  return {"tables": {n: emb_mod.gather_table(n) for n in emb_mod.plan.tables},
+          "placements": {n: str(tp.placement) for n, tp in emb_mod.plan.tables.items()}}
+
+
 def vocab_rank_sharded(rank, world, device_type, rows, D, V):
   """Ranks over a MOD-row-sharded item matrix vs the single-process fp32 ranks."""
   from recml_b200.ops import vocab_rank as VR
