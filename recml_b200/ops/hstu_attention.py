@@ -70,26 +70,84 @@ def pointwise_attention_dense(q, k, v, attention_mask=None, attention_bias=None,
   return torch.einsum("bhts,bshd->bthd", p, v.float()).to(q.dtype)
 
 
-def pointwise_attention(mask_type: MaskType | str, q, k, v, *, q_segment_ids=None, kv_segment_ids=None,
-                        sliding_window_size: int | None = None, scale: float | None = None):
-  """API of the reference op on `[B, L, H, Dh]`: P = mask(silu(Q·Kᵀ·scale) / L_q); masks combine
-  causal / full, a sliding window (query i sees keys i−w+1..i) and equal segment ids."""
+def attention_mask(mask_type: MaskType | str, Lq: int, Lk: int, *, sliding_window_size: int | None = None,
+                   q_offset: int = 0, device=None) -> torch.Tensor:
+  """`[Lq, Lk]` bool mask of the reference op: causal (key j visible to query i when j <= i) or full,
+  intersected with a window that is INCLUSIVE on both sides, i - w <= j <= i + w (the reference builds it
+  as `LocalMask(window_size=(w, w), offset=0)`, `recml/core/ops/hstu_ops.py:940-945`), so a causal window
+  of size w sees w + 1 keys.  `q_offset` is the position of query row 0 (queries sharded along the sequence)."""
   mask_type = MaskType(mask_type)
+  i = torch.arange(Lq, device=device)[:, None] + q_offset
+  j = torch.arange(Lk, device=device)[None, :]
+  m = (j <= i) if mask_type is MaskType.CAUSAL else torch.ones(Lq, Lk, dtype=torch.bool, device=device)
+  if sliding_window_size is not None:
+    m = m & (j >= i - sliding_window_size) & (j <= i + sliding_window_size)
+  return m
+
+
+def pointwise_attention(mask_type: MaskType | str, q, k, v, *, q_segment_ids=None, kv_segment_ids=None,
+                        sliding_window_size: int | None = None, scale: float | None = None, q_offset: int = 0,
+                        normalizer: float | None = None):
+  """API of the reference op on `[B, L, H, Dh]`: P = mask(silu(Q·Kᵀ·scale) / L_q); masks combine
+  causal / full, a sliding window (inclusive: query i sees keys i−w..i+w) and equal segment ids.
+  `q_offset` / `normalizer` serve the sequence-sharded mode, where a rank holds a slice of the queries."""
   B, Lq, H, Dh = q.shape
   Lk = k.shape[1]
-  i = torch.arange(Lq, device=q.device)[:, None]
-  j = torch.arange(Lk, device=q.device)[None, :]
-  m = (j <= i) if mask_type is MaskType.CAUSAL else torch.ones(Lq, Lk, dtype=torch.bool, device=q.device)
-  if sliding_window_size is not None:
-    m = m & (j > i - sliding_window_size) & (j < i + sliding_window_size)
+  m = attention_mask(mask_type, Lq, Lk, sliding_window_size=sliding_window_size, q_offset=q_offset, device=q.device)
   m = m[None].expand(B, Lq, Lk)
   if q_segment_ids is not None:
     kv_seg = q_segment_ids if kv_segment_ids is None else kv_segment_ids
     m = m & (q_segment_ids[:, :, None] == kv_seg[:, None, :])
   s = torch.einsum("bthd,bshd->bhts", q.float(), k.float()) * (scale if scale is not None else 1.0)
-  p = torch.nn.functional.silu(s) / Lq
+  p = torch.nn.functional.silu(s) / (normalizer if normalizer is not None else Lq)
   p = torch.where(m[:, None], p, torch.zeros_like(p))
   return torch.einsum("bhts,bshd->bthd", p, v.float()).to(q.dtype)
+
+
+class _AllGatherSeq(torch.autograd.Function):
+  """Concatenates the ranks' `[B, L/W, ...]` slices along dim 1; backward sums the gradients of every
+  rank's copy and keeps the own slice (a reduce-scatter)."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    import torch.distributed as dist
+    ctx.group = group
+    n = dist.get_world_size(group)
+    parts = [torch.empty_like(x) for _ in range(n)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
+
+  @staticmethod
+  def backward(ctx, g):
+    import torch.distributed as dist
+    n, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+    g = g.contiguous()
+    dist.all_reduce(g, group=ctx.group)
+    return g.chunk(n, dim=1)[r].contiguous(), None
+
+
+def q_sharded_pointwise_attention(mask_type: MaskType | str, q, k, v, *, group=None, segment_ids=None,
+                                  sliding_window_size: int | None = None, scale: float | None = None):
+  """The reference op's `q_seq_shards` mode (`recml/core/ops/hstu_ops.py:847-848,1018-1040`): every rank of
+  `group` holds a contiguous slice of the SEQUENCE (`[B, L / W, H, Dh]` of q, k, v and `[B, L / W]` segment
+  ids).  Keys and values are all-gathered (their gradients reduce-scattered in backward), the queries stay
+  where they are, and each rank computes its rows of the output with the mask shifted to its position;
+  the normaliser is the full length, so the concatenation of the ranks' outputs equals the unsharded op."""
+  import torch.distributed as dist
+  if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+    return pointwise_attention(mask_type, q, k, v, q_segment_ids=segment_ids,
+                               sliding_window_size=sliding_window_size, scale=scale)
+  n, r = dist.get_world_size(group), dist.get_rank(group)
+  Lq = q.shape[1]
+  k_all, v_all = _AllGatherSeq.apply(k, group), _AllGatherSeq.apply(v, group)
+  kv_seg = None
+  if segment_ids is not None:
+    parts = [torch.empty_like(segment_ids) for _ in range(n)]
+    dist.all_gather(parts, segment_ids.contiguous(), group=group)
+    kv_seg = torch.cat(parts, dim=1)
+  return pointwise_attention(mask_type, q, k_all, v_all, q_segment_ids=segment_ids, kv_segment_ids=kv_seg,
+                             sliding_window_size=sliding_window_size, scale=scale, q_offset=r * Lq,
+                             normalizer=float(Lq * n))
 
 
 def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,

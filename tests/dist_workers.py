@@ -313,6 +313,22 @@ def dlrm_tiny_training(rank, world, device_type, steps, use_graph=False):
           "ckpts": sorted(_os.listdir(_os.path.join(box[0], "checkpoints")))}
 
 
+def q_sharded_attention(rank, world, device_type):
+  """Sequence-sharded HSTU attention on `world` ranks: this rank's output rows and input gradients."""
+  from recml_b200.ops import hstu_attention as A
+  g = torch.Generator().manual_seed(3)
+  B, L, H, Dh = 2, 24, 2, 8
+  q, k, v = (torch.randn(B, L, H, Dh, generator=g) for _ in range(3))
+  seg = torch.tensor([[0] * 10 + [1] * 14, [0] * 24])
+  go = torch.randn(B, L, H, Dh, generator=g)
+  n = L // world
+  sl = slice(rank * n, (rank + 1) * n)
+  leaves = [t[:, sl].clone().requires_grad_() for t in (q, k, v)]
+  out = A.q_sharded_pointwise_attention("causal", *leaves, segment_ids=seg[:, sl], sliding_window_size=6, scale=0.3)
+  out.backward(go[:, sl])
+  return {"out": out.detach(), "grads": [t.grad for t in leaves]}
+
+
 def dlrm_tiny_export(rank, world, device_type, model_dir):
   """Trains the tiny DLRM on `world` ranks with row-sharded tables; the trainer's final export is collective."""
   from recml_b200 import config as C, run_experiment

@@ -128,3 +128,28 @@ def test_tensor_parallel_mlp_matches_dense_two_ranks():
     torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=1e-5, atol=1e-6)
     for k, v in ref["full"].items():
       torch.testing.assert_close(r["full"][k], v, rtol=1e-4, atol=1e-6)
+
+
+def test_q_sequence_sharded_attention_matches_unsharded():
+  """The op's sequence-sharded mode on 2 gloo ranks (causal, inclusive window, segment ids) equals the
+  single-process op in outputs and in the gradients of q, k and v."""
+  from recml_b200.ops import hstu_attention as A
+  g = torch.Generator().manual_seed(3)
+  B, L, H, Dh = 2, 24, 2, 8
+  q, k, v = (torch.randn(B, L, H, Dh, generator=g).requires_grad_() for _ in range(3))
+  seg = torch.tensor([[0] * 10 + [1] * 14, [0] * 24])
+  go = torch.randn(B, L, H, Dh, generator=g)
+  ref = A.pointwise_attention("causal", q, k, v, q_segment_ids=seg, sliding_window_size=6, scale=0.3)
+  ref.backward(go)
+  res = dist_utils.run_ranks("q_sharded_attention", 2, "gloo", "cpu")
+  torch.testing.assert_close(torch.cat([r["out"] for r in res], dim=1), ref.detach())
+  for i, t in enumerate((q, k, v)):
+    torch.testing.assert_close(torch.cat([r["grads"][i] for r in res], dim=1), t.grad, rtol=1e-4, atol=1e-6)
+
+
+def test_sliding_window_is_inclusive_like_the_reference_local_mask():
+  from recml_b200.ops import hstu_attention as A
+  m = A.attention_mask("causal", 8, 8, sliding_window_size=2)
+  assert m[5].tolist() == [False, False, False, True, True, True, False, False]      # keys 3, 4, 5: w + 1 of them
+  f = A.attention_mask("full", 8, 8, sliding_window_size=1)
+  assert f[4].tolist() == [False, False, False, True, True, True, False, False]

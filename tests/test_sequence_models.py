@@ -124,7 +124,8 @@ def test_pointwise_attention_api_masks():
   ref = torch.einsum("bhts,bshd->bthd", p * m, v)
   torch.testing.assert_close(out, ref)
   w = A.pointwise_attention(A.MaskType.CAUSAL, q, k, v, sliding_window_size=2)
-  m2 = torch.tril(torch.ones(5, 5)).bool() & (torch.arange(5)[None, :] > torch.arange(5)[:, None] - 2)
+  # inclusive window, as the reference's LocalMask(window_size=(2, 2)): query i sees keys i-2 .. i
+  m2 = torch.tril(torch.ones(5, 5)).bool() & (torch.arange(5)[None, :] >= torch.arange(5)[:, None] - 2)
   torch.testing.assert_close(w, torch.einsum("bhts,bshd->bthd", p * m2, v))
 
 
