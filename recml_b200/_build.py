@@ -27,6 +27,21 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-pthread", "-Wall"]
 
+# Checked builds (separate object and library names, so they never mix with the optimised ones):
+#   RECML_DEBUG=1                       kernels and host code compiled with -DRECML_DEBUG: buffers handed to
+#                                       kernels carry canary words that are verified after the launch, and
+#                                       device-side index checks that the optimised build leaves out are on
+#   RECML_SANITIZE=address,undefined    host library built with the named compiler sanitizers (run Python with
+#                                       LD_PRELOAD=$(gcc -print-file-name=libasan.so))
+DEBUG = os.environ.get("RECML_DEBUG", "0") not in ("", "0")
+SANITIZE = os.environ.get("RECML_SANITIZE", "")
+_SUFFIX = ("_dbg" if DEBUG else "") + ("_san" if SANITIZE else "")
+if DEBUG:
+  NVCC_FLAGS = NVCC_FLAGS + ["-DRECML_DEBUG=1"]
+  CXX_FLAGS = CXX_FLAGS + ["-DRECML_DEBUG=1"]
+if SANITIZE:
+  CXX_FLAGS = [f for f in CXX_FLAGS if f != "-O3"] + ["-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={SANITIZE}"]
+
 
 def _nvcc() -> str:
   return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
@@ -52,7 +67,7 @@ def _sources():
 
 
 def cuda_lib_path() -> str:
-  return os.path.join(LIB_DIR, "librecml_cuda.so")
+  return os.path.join(LIB_DIR, f"librecml_cuda{'_dbg' if DEBUG else ''}.so")
 
 
 def _read_text(path: str) -> str:
@@ -61,7 +76,7 @@ def _read_text(path: str) -> str:
 
 
 def host_lib_path() -> str:
-  return os.path.join(LIB_DIR, "librecml_host.so")
+  return os.path.join(LIB_DIR, f"librecml_host{_SUFFIX}.so")
 
 
 def _run(cmd: list[str]) -> None:
@@ -75,7 +90,7 @@ def _compile_all(srcs, hdrs, compiler_cmd, tag) -> tuple[list[str], bool]:
   hdr_digest = _digest(hdrs, tag)
   jobs, objs = [], []
   for src in srcs:
-    obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
+    obj = os.path.join(OBJ_DIR, os.path.basename(src) + (_SUFFIX if tag == "host" else ("_dbg" if DEBUG else "")) + ".o")
     stamp = obj + ".sha"
     want = _digest([src], hdr_digest)
     objs.append(obj)
@@ -108,7 +123,8 @@ def build(verbose: bool = False, force: bool = False, only: tuple[str, ...] = ("
        lambda objs, lib: [_nvcc(), "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]),
       ("host", cpp, cpp_hdr, host_lib_path(),
        lambda s, o: ["g++", *CXX_FLAGS, "-I", CSRC, "-c", s, "-o", o],
-       lambda objs, lib: ["g++", "-shared", "-pthread", "-o", lib, *objs, "-lz", "-ldl"])):
+       lambda objs, lib: ["g++", "-shared", "-pthread", "-o", lib, *objs, "-lz", "-ldl",
+                          *([f"-fsanitize={SANITIZE}"] if SANITIZE else [])])):
     if not srcs or name not in only:
       continue
     want = _digest(srcs + hdrs, name)

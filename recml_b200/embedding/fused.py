@@ -372,7 +372,7 @@ class FusedBackend:
     gains = self.has_gains
     B = self.B
     if out is None:
-      out = torch.empty(B, self.width, dtype=torch.bfloat16, device=dev)
+      out = _lib.debug_empty((B, self.width), torch.bfloat16, dev, "pooled embedding output")
       out_col = 0
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     direct = None

@@ -152,6 +152,46 @@ def poll_status(device: torch.device | None = None) -> None:
   _pollers[idx].poll()
 
 
+# ---- checked build (RECML_DEBUG=1): canary words around buffers that kernels write --------------------------
+DEBUG = _build.DEBUG
+_CANARY = 0x5AC0FFEE
+_GUARD = 64           # int32 words before and after the payload
+_guarded: list[tuple[torch.Tensor, int, str]] = []
+
+
+def debug_empty(shape, dtype: torch.dtype, device, what: str = "buffer") -> torch.Tensor:
+  """`torch.empty` in the optimised build.  In the checked build the tensor sits between two guard zones
+  filled with a known word; `debug_check()` verifies them after the kernels that wrote the tensor have
+  run, so a kernel that writes outside its output (wrong pitch, tile overhang, bad offset) is caught where
+  it happens instead of corrupting a neighbour."""
+  if not DEBUG:
+    return torch.empty(shape, dtype=dtype, device=device)
+  n = 1
+  for s_ in shape:
+    n *= int(s_)
+  nbytes = n * torch.empty((), dtype=dtype).element_size()
+  words = (nbytes + 3) // 4
+  raw = torch.full((2 * _GUARD + words,), _CANARY, dtype=torch.int32, device=device)
+  _guarded.append((raw, words, what))
+  payload = raw[_GUARD:_GUARD + words].view(torch.uint8)[:nbytes].view(dtype)
+  return payload.view(*shape)
+
+
+def debug_check() -> None:
+  """Verifies (and forgets) every guard zone handed out since the last call; synchronises."""
+  if not DEBUG or not _guarded:
+    return
+  torch.cuda.synchronize()
+  bad = []
+  for raw, words, what in _guarded:
+    head, tail = raw[:_GUARD], raw[_GUARD + words:]
+    if not (bool((head == _CANARY).all()) and bool((tail == _CANARY).all())):
+      bad.append(what)
+  _guarded.clear()
+  if bad:
+    raise DeviceStatusError(f"guard words overwritten around: {', '.join(bad)}")
+
+
 def check_rc(rc: int, what: str) -> None:
   if rc != 0:
     raise NativeError(f"{what} failed with code {rc}")

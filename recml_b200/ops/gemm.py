@@ -68,9 +68,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     d, out_f32, acc = accumulate_into, 1, 1
     assert d.dtype == torch.float32
   else:
-    d = out if out is not None else torch.empty(M, N, dtype=out_dtype, device=a.device)
+    d = out if out is not None else _lib.debug_empty((M, N), out_dtype, a.device, f"gemm output [{M}, {N}]")
     out_f32, acc = int(d.dtype == torch.float32), 0
-  out2 = torch.empty(M, N, dtype=torch.bfloat16, device=a.device) if want_out2 else None
+  out2 = _lib.debug_empty((M, N), torch.bfloat16, a.device, "gemm second output") if want_out2 else None
   if split_k == 0:
     split_k = 1
     if out_f32 and epi == EPI_LINEAR and bias is None and not relu:

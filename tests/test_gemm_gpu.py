@@ -64,3 +64,26 @@ def test_bias_relu_and_epilogues():
          G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_ADD, aux0=x0.cpu()).cuda())
   _check(G.gemm(a, b, epi=G.EPI_ADD, aux0=x0, aux1=xl),
          G.gemm_reference(a.cpu(), b.cpu(), epi=G.EPI_ADD, aux0=x0.cpu(), aux1=xl.cpu()).cuda())
+
+
+def test_checked_build_guard_words():
+  """The RECML_DEBUG build puts guard words around kernel outputs; a GEMM whose N is not a tile multiple and an
+  embedding lookup leave them intact (run in a child process: the build flavour is fixed at import time)."""
+  import os
+  import subprocess
+  import sys
+  code = (
+      "import torch\n"
+      "from recml_b200.ops import _lib, gemm as G\n"
+      "assert _lib.DEBUG and 'dbg' in _lib._build.cuda_lib_path()\n"
+      "a = torch.randn(300, 72, device='cuda', dtype=torch.bfloat16); b = torch.randn(200, 72, device='cuda', dtype=torch.bfloat16)\n"
+      "y = G.gemm(a, b); _lib.debug_check()\n"
+      "torch.testing.assert_close(y.float(), a.float() @ b.float().t(), rtol=3e-2, atol=3e-1)\n"
+      "t = _lib.debug_empty((8, 8), torch.float32, 'cuda', 'probe'); t.view(-1)[:64].fill_(1.0)\n"
+      "base = t.view(-1); torch.as_strided(base, (80,), (1,)).fill_(2.0)\n"     # runs 16 floats past the payload
+      "try:\n  _lib.debug_check(); print('MISSED')\nexcept _lib.DeviceStatusError as e:\n  print('CAUGHT', e)\n")
+  env = dict(os.environ, RECML_DEBUG="1")
+  out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+  assert out.returncode == 0, out.stderr[-2000:]
+  assert "CAUGHT" in out.stdout and "probe" in out.stdout
