@@ -1,23 +1,29 @@
-// Jagged HSTU attention for sm_100a:  O = mask( silu(Q·K^T·scale + bias) / n ) · V   per sequence,
-// with the learned relative-position and time-bucket bias evaluated in the kernel.
+// Jagged HSTU attention for sm_100a:  O = silu(Q·K^T·scale + bias) / n · V   per sequence, where `bias`
+// carries the learned relative-position and time-bucket terms AND every mask (causal, sequence end,
+// sliding window, segment ids) as a large negative value.
 //
 // Sequences are packed back to back ([T, H, Dh] bf16, seq_offsets[B+1]).  One CTA owns a 128-query
 // tile of one sequence and one head and walks over the key/value tiles it may see (causal: tiles up
 // to its own).  Per key tile:
 //   TMA (warp 0)        K_j, V_j -> shared memory (2 stages)
 //   tcgen05.mma (warp 1) S = Q·K_j^T into tensor memory
-//   warps 2..17          (each 32 rows x 32 columns of the score tile) tcgen05.ld S;
-//                        p = silu(s·scale + pos_w[kj-qi+N-1] + ts_w[bucket(Δt)]) / n;
-//                        causal / length mask; bf16 P written to shared memory in the 128-byte-swizzled
+//   warps 2..17          (each 32 rows x 32 columns of the score tile) tcgen05.ld S, load the matching
+//                        piece of the pair's BIAS TILE, h = s·scale/2 + bias/2, p = h·tanh(h) + h
+//                        (= x·sigmoid(x)); bf16 P written to shared memory in the 128-byte-swizzled
 //                        K-major layout the tensor core expects
 //   tcgen05.mma (warp 1) O += P·V_j    (V consumed as an MN-major operand straight from its [kv, Dh] tile)
-// The backward kernel (one CTA per key tile and head, walking over the query tiles that see it)
-// recomputes S and forms dV += P^T·dO, dK += dS^T·Q, dQ += dS·K on the tensor cores, with
-// dS = dP ⊙ d/ds[silu]/n.  The position-bias gradient is summed along the diagonals of each warp's block in
-// registers (a partial sum per diagonal moves one lane per column) before it reaches a shared-memory
-// histogram; the time-bucket gradient is summed per run of equal buckets.
+// Bias tiles: the bias of a (query tile, key tile) pair depends on the batch (lengths, timestamps) and on
+// the two small weight tables, not on the head or the layer, so it is evaluated ONCE per step by
+// bias_tile_kernel into bf16 blocks of 128 x 128 (already halved; masked entries hold -15000, for which
+// tanh gives exactly -1 and the element and its derivative vanish).  The per-element work of the attention
+// kernels is then one fused multiply-add, one tanh and one more fused multiply-add, with no predicates and
+// no table lookups.  The backward kernel (one CTA per key tile and head, walking over the query tiles that
+// see it) recomputes S and forms dV += P^T·dO, dK += dS^T·Q, dQ += dS·K on the tensor cores; it adds dS
+// (fp32 vector reductions) into a gradient block per tile pair, summed over heads and layers, from which
+// bias_grad_kernel takes the gradients of the two tables once per step (diagonal sums by a lane-rotating
+// accumulator, time buckets by runs of equal buckets).
 // CTAs take their tiles from a list sorted by decreasing work (the backward has its own order) with the
-// heads varying fastest, and read the time-bucket indices from blocks computed once per batch.
+// heads varying fastest.  A softmax mode (SASRec / BERT4Rec blocks) shares the pipeline.
 // All waits are bounded; a CTA that gives up drains and frees its tensor memory.
 #include "tcgen05.cuh"
 
@@ -61,8 +67,30 @@ struct Params {
   // pair_base[s] + (causal ? qt (qt + 1) / 2 + kt : qt * n_tiles(s) + kt).  Null: buckets are computed inline.
   const unsigned char* bucket_cache;
   const int* pair_base;       // [B + 1]
-  int cap_pairs;              // blocks the cache can hold; a sequence whose blocks would not fit computes inline
+  int cap_pairs;              // blocks the caches can hold
+  // Bias tiles (SiLU mode): pair-indexed like the bucket cache, 16384 bf16 per pair in the element order of
+  // the attention kernels' threads (tile_offset below); values are HALF the bias, masked entries -15000.
+  const __nv_bfloat16* bias_tiles;
+  float* dbias_tiles;         // backward: 16384 fp32 per pair, same order, accumulated with reductions (or null)
+  int window;                 // >= 0: query i sees keys i - window .. i + window (intersected with causality)
+  const int* segment_ids;     // [T] or null: a query sees only keys of its own segment
 };
+
+constexpr float kMaskedHalfBias = -15000.f;
+
+// 16-byte fp32 vector reduction into global memory (no return value)
+__device__ __forceinline__ void red_add_v4(float4* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Element (r, c) of a 128 x 128 tile as the attention kernels' threads see it: warp (quarter = r / 32,
+// cb = c / 32), lane = r % 32, 32 consecutive columns per thread in vectors of `vec` elements.  A warp's
+// vector load or reduction of one vector index touches consecutive memory.
+__device__ __forceinline__ int tile_offset(int r, int c, int vec) {
+  const int quarter = r >> 5, lane = r & 31, cb = c >> 5, within = c & 31;
+  const int per_thread = 32 / vec;
+  return (((cb * 4 + quarter) * per_thread + within / vec) * 32 + lane) * vec + within % vec;
+}
 
 // Lists the 128-row tiles of every sequence: tile t belongs to sequence tile_seq[t] and starts at
 // position tile_row0[t].  Slots beyond the real number of tiles keep -1.  The list is ordered by
@@ -90,13 +118,13 @@ __global__ void tile_list_kernel(const int* seq_offsets, int B, int* tile_seq, i
   }
 }
 
-// sigmoid through the single-instruction tanh approximation: one special-function op instead of exp + rcp
-__device__ __forceinline__ float sigmoid_fast(float x) {
+// the single-instruction tanh approximation (one special-function op instead of exp + rcp); exactly -1 / +1
+// for arguments of large magnitude
+__device__ __forceinline__ float tanh_fast(float x) {
   float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
-  return fmaf(0.5f, t, 0.5f);
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
 }
-__device__ __forceinline__ float silu(float x) { return x * sigmoid_fast(x); }
 
 // bucket = clip(int(ln(clip(|dt|, 1, 1e9)) / 0.301), 0, num_buckets), with ln taken as log2 * ln(2)
 __device__ __forceinline__ int time_bucket(int dt, int num_buckets) {
@@ -159,16 +187,6 @@ __global__ void __launch_bounds__(256) bucket_cache_kernel(const int* seq_offset
   }
 }
 
-// Per-warp scratch in shared memory for the bias terms of one (query tile, key tile) pair: the 128 key
-// timestamps, the 160-entry window of the relative-position table the warp's 32 rows touch, and a copy
-// of the time-bucket table.  Only __syncwarp is needed to publish it.
-struct WarpBias {      // a warp covers 32 rows x 32 columns of the score tile (the staging covers 64 columns)
-  int ts_k[64];
-  float pos[96];
-  float tsw[260];
-  float diag[32];      // backward: diagonals of the position-bias gradient completed by lane 31, one per column
-};
-
 // One lane polls the mbarrier, the result is broadcast: the whole warp takes the same branch, so warp-level
 // synchronisation after it can never be left waiting for a lane that gave up.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
@@ -179,22 +197,153 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
   return ok != 0;
 }
 
-// `kv0` here is the first key of the warp's columns.
-__device__ __forceinline__ void stage_bias(WarpBias& wb, const Params& p, int lane, int seq_start, int L, int kv0,
-                                           int q0, int quarter, bool cached) {
-  __syncwarp();
-  if (p.ts_w != nullptr && !cached) {
-    for (int i = lane; i < 64; i += 32) wb.ts_k[i] = (kv0 + i < L) ? __ldg(p.timestamps + seq_start + kv0 + i) : 0;
+// ---- bias tiles: half the bias (position + time-bucket terms) of every visible element, a large negative
+// value for every masked one.  One block per (query tile of the forward list, key tile); thread = (row,
+// 64-column half).
+struct BiasParams {
+  const int* seq_offsets; const int* tile_seq; const int* tile_row0; const int* pair_base;
+  int causal, cap_pairs, max_seq_len, window, num_buckets;
+  const int* segment_ids; const float* pos_w; const float* ts_w;
+  const unsigned char* bucket_cache;
+  __nv_bfloat16* tiles;
+  float* dbias; float* dpos_w; float* dts_w;     // gradient pass
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) bias_tile_kernel(const BiasParams p) {
+  const int seq = p.tile_seq[blockIdx.x];
+  if (seq < 0) return;
+  const int q0 = p.tile_row0[blockIdx.x], qt = q0 / BQ, kt = blockIdx.y;
+  const int seq_start = p.seq_offsets[seq];
+  const int L = p.seq_offsets[seq + 1] - seq_start;
+  const int nt = (L + BQ - 1) / BQ;
+  if (kt >= nt || (p.causal && kt > qt)) return;
+  const int pair = p.pair_base[seq] + (p.causal ? qt * (qt + 1) / 2 + kt : qt * nt + kt);
+  if (pair >= p.cap_pairs) { report(p.status, kCapacity, 2); return; }
+  __shared__ float posw[256];
+  __shared__ float tsw[256];
+  __shared__ int seg_k[BKV];
+  const int kv0 = kt * BKV;
+  {
+    // element (r, c) needs pos_w[(kv0 + c) - (q0 + r) + N - 1] = window[c - r + 127]
+    const int base = kv0 - q0 + p.max_seq_len - 1 - 127;
+    const int idx = base + static_cast<int>(threadIdx.x);
+    posw[threadIdx.x] = (p.pos_w != nullptr && threadIdx.x < 255 && idx >= 0 && idx < 2 * p.max_seq_len - 1)
+                            ? __ldg(p.pos_w + idx) : 0.f;
+    tsw[threadIdx.x] = (p.ts_w != nullptr && static_cast<int>(threadIdx.x) <= p.num_buckets) ? __ldg(p.ts_w + threadIdx.x) : 0.f;
+    if (threadIdx.x < BKV)
+      seg_k[threadIdx.x] = (p.segment_ids != nullptr && kv0 + threadIdx.x < L) ? p.segment_ids[seq_start + kv0 + threadIdx.x] : 0;
   }
-  if (p.pos_w != nullptr) {
-    // rows r = quarter*32 + lane, columns c: index (kv0 + c) - (q0 + r) + N - 1 = base + c - lane, lane in [0,32)
-    const int base = kv0 - q0 - quarter * 32 + p.max_seq_len - 1 - 31;
-    for (int i = lane; i < 96; i += 32) {
-      const int idx = base + i;
-      wb.pos[i] = (idx >= 0 && idx < 2 * p.max_seq_len - 1) ? __ldg(p.pos_w + idx) : 0.f;
+  __syncthreads();
+  const int r = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * 64;
+  const int qi = q0 + r;
+  const bool row_ok = qi < L;
+  const int seg_q = (p.segment_ids != nullptr && row_ok) ? p.segment_ids[seq_start + qi] : 0;
+  const unsigned char* brow = p.bucket_cache != nullptr
+      ? p.bucket_cache + (static_cast<size_t>(pair) << 14) + r * BKV + c0 : nullptr;
+  __nv_bfloat16* out = p.tiles + (static_cast<size_t>(pair) << 14);
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint32_t bytes[2] = {0u, 0u};
+    if (brow != nullptr && p.ts_w != nullptr) {
+      const uint2 t = *reinterpret_cast<const uint2*>(brow + g * 8);
+      bytes[0] = t.x; bytes[1] = t.y;
     }
+    float val[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = c0 + g * 8 + e;
+      const int kj = kv0 + c;
+      bool vis = row_ok && kj < L && (!p.causal || kj <= qi);
+      if (p.window >= 0) vis = vis && kj >= qi - p.window && kj <= qi + p.window;
+      if (p.segment_ids != nullptr) vis = vis && seg_q == seg_k[c];
+      float b = posw[c - r + 127];
+      if (p.ts_w != nullptr) b += tsw[(bytes[e >> 2] >> ((e & 3) * 8)) & 0xff];
+      val[e] = vis ? 0.5f * b : kMaskedHalfBias;
+    }
+    *reinterpret_cast<uint4*>(out + tile_offset(r, c0 + g * 8, 8)) =
+        make_uint4(pack_bf16(val[0], val[1]), pack_bf16(val[2], val[3]), pack_bf16(val[4], val[5]), pack_bf16(val[6], val[7]));
   }
-  __syncwarp();
+}
+
+// ---- gradients of the two bias tables from the per-pair gradient blocks (which are cleared on the way, so
+// the buffer is all zeros again for the next step).  One block of 16 warps per tile pair, the same
+// thread-to-element map as the attention kernels.  Masked elements hold exact zeros.
+__global__ void __launch_bounds__(512) bias_grad_kernel(const BiasParams p) {
+  const int seq = p.tile_seq[blockIdx.x];
+  if (seq < 0) return;
+  const int q0 = p.tile_row0[blockIdx.x], qt = q0 / BQ, kt = blockIdx.y;
+  const int seq_start = p.seq_offsets[seq];
+  const int L = p.seq_offsets[seq + 1] - seq_start;
+  const int nt = (L + BQ - 1) / BQ;
+  if (kt >= nt || (p.causal && kt > qt)) return;
+  const int pair = p.pair_base[seq] + (p.causal ? qt * (qt + 1) / 2 + kt : qt * nt + kt);
+  if (pair >= p.cap_pairs) return;
+  __shared__ float hist[512];           // [0, 255) diagonals, [256, 512) time buckets
+  __shared__ float diag[16][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quarter = warp & 3, cb = warp >> 2;
+  const int r = quarter * 32 + lane;
+  hist[threadIdx.x] = 0.f;
+  __syncthreads();
+  float ds[32];
+  float4* src = reinterpret_cast<float4*>(p.dbias + (static_cast<size_t>(pair) << 14)) + (cb * 4 + quarter) * 8 * 32 + lane;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const float4 t = src[g * 32];
+    src[g * 32] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ds[4 * g] = t.x; ds[4 * g + 1] = t.y; ds[4 * g + 2] = t.z; ds[4 * g + 3] = t.w;
+  }
+  if (p.dpos_w != nullptr) {
+    // This lane's element lies on diagonal (col - lane) of the warp's 32 x 32 block; the partial sum of a
+    // diagonal travels one lane up per column, so every lane adds its element to the sum passing through it.
+    // The diagonal leaving lane 31 is complete and is parked; after the last column those 31 and the 32
+    // diagonals still in flight go to the histogram (bin = c - r + 127).
+    float dacc = 0.f;
+#pragma unroll
+    for (int col = 0; col < 32; ++col) {
+      dacc += ds[col];
+      if (col < 31) {
+        if (lane == 31) diag[warp][col] = dacc;
+        const float below = __shfl_sync(0xffffffffu, dacc, (lane + 31) & 31);
+        dacc = lane == 0 ? 0.f : below;
+      }
+    }
+    atomicAdd(hist + (cb * 32 + 31 - r + 127), dacc);
+    __syncwarp();
+    if (lane < 31) atomicAdd(hist + (cb * 32 + lane - (quarter * 32 + 31) + 127), diag[warp][lane]);
+  }
+  if (p.dts_w != nullptr && p.bucket_cache != nullptr) {
+    // along a row the bucket changes rarely (log-spaced buckets, increasing timestamps): runs of equal buckets
+    // are summed in a register and flushed with one atomic
+    const uint4* bc = reinterpret_cast<const uint4*>(p.bucket_cache + (static_cast<size_t>(pair) << 14) + r * BKV + cb * 32);
+    const uint4 b0 = __ldg(bc), b1 = __ldg(bc + 1);
+    const uint32_t bk[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    int run_bucket = -1;
+    float run_sum = 0.f;
+#pragma unroll
+    for (int col = 0; col < 32; ++col) {
+      const int bucket = bucket_byte(bk, col);
+      if (bucket != run_bucket) {
+        if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(hist + 256 + run_bucket, run_sum);
+        run_bucket = bucket;
+        run_sum = 0.f;
+      }
+      run_sum += ds[col];
+    }
+    if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(hist + 256 + run_bucket, run_sum);
+  }
+  __syncthreads();
+  const int kv0 = kt * BKV;
+  if (threadIdx.x < 255) {
+    const float v = hist[threadIdx.x];
+    const int idx = (kv0 - q0) + (static_cast<int>(threadIdx.x) - 127) + p.max_seq_len - 1;
+    if (v != 0.f && p.dpos_w != nullptr && idx >= 0 && idx < 2 * p.max_seq_len - 1) atomicAdd(p.dpos_w + idx, v);
+  } else if (threadIdx.x >= 256) {
+    const int b = threadIdx.x - 256;
+    const float v = hist[threadIdx.x];
+    if (v != 0.f && p.dts_w != nullptr && b <= p.num_buckets) atomicAdd(p.dts_w + b, v);
+  }
 }
 
 template <int DH>
@@ -206,12 +355,11 @@ struct Smem {
   static constexpr int kV = kK + 2 * kTile;            // 2 stages
   static constexpr int kP = kV + 2 * kTile;            // [128, 128] bf16 = 32 KB
   static constexpr int kBars = kP + BQ * BKV * 2;
-  static constexpr int kBias = kBars + 128;            // 4 x WarpBias
-  static constexpr int kTotal = kBias + 16 * static_cast<int>(sizeof(WarpBias)) + 1024;
+  static constexpr int kTotal = kBars + 128 + 1024;
   static constexpr int kTmemCols = 512;                // S: 2 x 128 columns, O: DH columns
 };
 
-template <int DH>
+template <int DH, bool SOFTMAX>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -221,6 +369,10 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int tile_id = lin / p.H;
   const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;   // whole CTA leaves before touching barriers or tensor memory
+  if (!SOFTMAX && p.pair_base[seq + 1] > p.cap_pairs) {   // the bias tiles of this sequence do not exist
+    if (threadIdx.x == 0) report(p.status, kCapacity, 3);
+    return;
+  }
   const int h = lin % p.H;
   const int q0 = p.tile_row0[tile_id];
   const int seq_start = p.seq_offsets[seq];
@@ -316,18 +468,11 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int r = quarter * 32 + lane;
     const int qi = q0 + r;
     const bool row_ok = qi < L;
-    WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
-    if (p.ts_w != nullptr)
-      for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
-    int tq = 0;
-    if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
-    const bool cached = p.ts_w != nullptr && p.bucket_cache != nullptr && L <= p.max_seq_len &&
-                        p.pair_base[seq + 1] <= p.cap_pairs;
     const int n_tiles_seq = (L + BQ - 1) / BQ;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    float out_scale = 1.f;
-    if (p.softmax) {
+    float out_scale = SOFTMAX ? 1.f : p.inv_n;
+    if constexpr (SOFTMAX) {
       // Exact softmax over at most two score tiles that are both resident in tensor memory: every warp
       // scans the whole row (all 128 columns of each tile) for the maximum and the sum, then writes
       // only its own 32 columns of P.
@@ -386,53 +531,45 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       out_scale = l > 0.f ? 1.f / l : 0.f;
       if (ok && cb == 0 && row_ok && p.lse != nullptr)
         p.lse[static_cast<size_t>(tok0 + r) * p.H + h] = l > 0.f ? m + logf(l) : 0.f;
-    }
-    for (int j = 0; j < n_kv && ok && !p.softmax; ++j) {
-      const int kv0 = j * BKV + cb * 32;
-      const int sb = j & 1;
-      stage_bias(wb, p, lane, seq_start, L, kv0, q0, quarter, cached);
-      uint32_t bk[8];
-      if (cached) {
-        const uint4* bc = reinterpret_cast<const uint4*>(
-            p.bucket_cache + (static_cast<size_t>(pair_index(p, seq, n_tiles_seq, q0 / BQ, j)) << 14) + r * BKV + cb * 32);
-        const uint4 b0 = __ldg(bc), b1 = __ldg(bc + 1);
-        bk[0] = b0.x; bk[1] = b0.y; bk[2] = b0.z; bk[3] = b0.w; bk[4] = b1.x; bk[5] = b1.y; bk[6] = b1.z; bk[7] = b1.w;
-      }
-      if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
-      tc_fence_after();
-      if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
-      {
-        uint32_t v[32];
-        tmem_ld32(tmem_slot + sb * 128 + lane_off + cb * 32, v);
-        uint32_t packed[16];
+    } else {
+      // SiLU mode.  With h = (s * scale + bias) / 2:  silu(2h) = 2h * sigmoid(2h) = h * tanh(h) + h.  The
+      // pair's bias tile brings bias / 2 (and the masks); 1 / n is applied once, to the output.
+      const float hs = 0.5f * p.scale;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int sb = j & 1;
+        const uint4* bt = reinterpret_cast<const uint4*>(
+            p.bias_tiles + (static_cast<size_t>(pair_index(p, seq, n_tiles_seq, q0 / BQ, j)) << 14)) +
+            (cb * 4 + quarter) * 4 * 32 + lane;
+        uint4 hb[4];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pr[2];
+        for (int g = 0; g < 4; ++g) hb[g] = __ldg(bt + g * 32);
+        if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
+        tc_fence_after();
+        if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
+        {
+          uint32_t v[32];
+          tmem_ld32(tmem_slot + sb * 128 + lane_off + cb * 32, v);
+          uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = e + u;                // within the warp's 32 columns
-            const int kj = kv0 + col;
-            float x = __uint_as_float(v[e + u]) * p.scale;
-            const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-            if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
-            if (p.ts_w != nullptr) x += wb.tsw[cached ? bucket_byte(bk, col) : time_bucket(tq - wb.ts_k[col], p.num_buckets)];
-            pr[u] = visible ? silu(x) * p.inv_n : 0.f;
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t w[4] = {hb[g].x, hb[g].y, hb[g].z, hb[g].w};
+            uint32_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float h0 = fmaf(__uint_as_float(v[g * 8 + 2 * k]), hs, bf16_lo(w[k]));
+              const float h1 = fmaf(__uint_as_float(v[g * 8 + 2 * k + 1]), hs, bf16_hi(w[k]));
+              packed[k] = pack_bf16(fmaf(h0, tanh_fast(h0), h0), fmaf(h1, tanh_fast(h1), h1));
+            }
+            // 32 columns = 64 bytes = four 16-byte chunks of row r in 64-column sub-tile cb / 2
+            const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
+            *reinterpret_cast<uint4*>(row_ptr + chunk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-          packed[e >> 1] = pack_bf16(pr[0], pr[1]);
         }
-        // 32 columns = 64 bytes = four 16-byte chunks of row r in 64-column sub-tile cb / 2
-        uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
-          *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
-              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-        }
+        tc_fence_before();
+        mbar_arrive(bar(7 + sb));   // this S buffer may be overwritten
+        fence_async_smem();
+        mbar_arrive(bar(9));        // P is in shared memory
       }
-      tc_fence_before();
-      mbar_arrive(bar(7 + sb));   // this S buffer may be overwritten
-      fence_async_smem();
-      mbar_arrive(bar(9));        // P is in shared memory
     }
     if (ok && warp_wait(bar(11), 0, abortp, p.status, 47, lane)) {
       tc_fence_after();
@@ -477,14 +614,12 @@ struct SmemB {
   static constexpr int kP = kDO + kStages * kTile;      // [128 q, 128 kv] bf16
   static constexpr int kDS = kP + BQ * BKV * 2;
   static constexpr int kBars = kDS + BQ * BKV * 2;
-  static constexpr int kHist = kBars + 128;             // 2 x 256 diagonal bins (by step parity) + 256 time bins, fp32
-  static constexpr int kBias = kHist + 768 * 4;
-  static constexpr int kTotal = kBias + 16 * static_cast<int>(sizeof(WarpBias)) + 1024;
+  static constexpr int kTotal = kBars + 128 + 1024;
   // tensor memory columns: [0,128) S then dQ, [128,256) dP, [256,256+DH) dV, [256+DH,256+2DH) dK
   static constexpr int kTmemCols = 512;
 };
 
-template <int DH>
+template <int DH, bool SOFTMAX>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -494,6 +629,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int tile_id = lin / p.H;
   const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;
+  if (!SOFTMAX && p.pair_base[seq + 1] > p.cap_pairs) {
+    if (threadIdx.x == 0) report(p.status, kCapacity, 4);
+    return;
+  }
   const int h = lin % p.H;
   const int kv0 = p.tile_row0[tile_id];
   const int seq_start = p.seq_offsets[seq];
@@ -508,7 +647,6 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bars = base + S::kBars;
   // 0 kv_full, 1-2 qdo_full, 3-4 qdo_empty, 5 sp_full, 6 pds_full, 7 dq_full, 8 dq_empty, 9 final
   auto bar = [&](int i) { return bars + 8u * i; };
-  float* hist = reinterpret_cast<float*>(base_ptr + S::kHist);   // [0,512) diagonals x2, [512,768) time buckets
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -525,7 +663,6 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar(9), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = threadIdx.x; i < 768; i += kThreads) hist[i] = 0.f;
   if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -598,120 +735,84 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int cb = cw >> 2;               // which 32 key columns of the tile this warp handles
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    WarpBias& wb = reinterpret_cast<WarpBias*>(base_ptr + S::kBias)[cw];
-    if (p.ts_w != nullptr)
-      for (int i = lane; i <= p.num_buckets; i += 32) wb.tsw[i] = __ldg(p.ts_w + i);
-    const bool cached = p.ts_w != nullptr && p.bucket_cache != nullptr && L <= p.max_seq_len &&
-                        p.pair_base[seq + 1] <= p.cap_pairs;
+    const float hs = 0.5f * p.scale;
+    // what multiplies the accumulated dQ: the score scale, and in SiLU mode the 1 / n that P and dS leave out
+    const float dq_scale = SOFTMAX ? p.scale : p.scale * p.inv_n;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int q0 = (i_first + it) * BQ;
       const int qi = q0 + r;
       const bool row_ok = qi < L;
-      int tq = 0;
-      if (p.ts_w != nullptr && row_ok) tq = p.timestamps[seq_start + (qi + 1 < L ? qi + 1 : L - 1)];
       float lse_r = 0.f, delta_r = 0.f;
-      if (p.softmax && row_ok) {
-        lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
-        delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
-      }
-      stage_bias(wb, p, lane, seq_start, L, kv0 + cb * 32, q0, quarter, cached);
-      uint32_t bk[8];
-      if (cached) {
-        const uint4* bc = reinterpret_cast<const uint4*>(
-            p.bucket_cache + (static_cast<size_t>(pair_index(p, seq, n_q_total, i_first + it, kv0 / BKV)) << 14) + r * BKV + cb * 32);
-        const uint4 b0 = __ldg(bc), b1 = __ldg(bc + 1);
-        bk[0] = b0.x; bk[1] = b0.y; bk[2] = b0.z; bk[3] = b0.w; bk[4] = b1.x; bk[5] = b1.y; bk[6] = b1.z; bk[7] = b1.w;
+      uint4 hb[4];
+      size_t pair_off = 0;
+      if constexpr (SOFTMAX) {
+        if (row_ok) {
+          lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
+          delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
+        }
+      } else {
+        pair_off = static_cast<size_t>(pair_index(p, seq, n_q_total, i_first + it, kv0 / BKV)) << 14;
+        const uint4* bt = reinterpret_cast<const uint4*>(p.bias_tiles + pair_off) + (cb * 4 + quarter) * 4 * 32 + lane;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) hb[g] = __ldg(bt + g * 32);
       }
       if (!warp_wait(bar(5), it & 1, abortp, p.status, 55, lane)) { ok = false; break; }
       tc_fence_after();
-      // time-bucket gradient: along a row the bucket changes rarely (log-spaced buckets, increasing
-      // timestamps), so equal-bucket runs are summed in a register and flushed with one atomic
-      int run_bucket = -1;
-      float run_sum = 0.f;
-      float dacc = 0.f;
       {
         uint32_t sv[32], dpv[32];
         tmem_ld32(tmem_s + lane_off + cb * 32, sv);
         tmem_ld32(tmem_dp + lane_off + cb * 32, dpv);
-        uint32_t pp[16], dd[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pr[2], dr[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = e + u;                       // within the warp's 32 columns
-            const int kj = kv0 + cb * 32 + col;
-            const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-            float x = __uint_as_float(sv[e + u]) * p.scale;
-            int bucket = 0;
-            if (p.pos_w != nullptr) x += wb.pos[col - lane + 31];
-            if (p.ts_w != nullptr) {
-              bucket = cached ? bucket_byte(bk, col) : time_bucket(tq - wb.ts_k[col], p.num_buckets);
-              x += wb.tsw[bucket];
-            }
-            float ds;
-            if (p.softmax) {
-              // P = exp(x - lse);  dS = P * (dP - delta)
-              const float pv = visible ? __expf(x - lse_r) : 0.f;
-              ds = visible ? pv * (__uint_as_float(dpv[e + u]) - delta_r) : 0.f;
-              pr[u] = pv;
-            } else {
-              const float sig = sigmoid_fast(x);
-              ds = visible ? __uint_as_float(dpv[e + u]) * sig * (1.f + x * (1.f - sig)) * p.inv_n : 0.f;
-              pr[u] = visible ? x * sig * p.inv_n : 0.f;
-            }
-            dr[u] = ds;
-            // Position-bias gradient.  This lane's element lies on diagonal (col - lane) of the warp's
-            // 32x32 block; the partial sum of a diagonal travels one lane up per column, so every lane
-            // adds its element to the sum that is passing through it.  The diagonal leaving lane 31 is
-            // complete and is parked in the warp's scratch; after the last column those 31 and the 32
-            // diagonals still in flight go to the shared histogram (bin = (kj - qi) - (kv0 - q0) + 127).
-            if (p.dpos_w != nullptr) {
-              dacc += ds;
-              if (col < 31) {
-                if (lane == 31) wb.diag[col] = dacc;
-                const float below = __shfl_sync(0xffffffffu, dacc, (lane + 31) & 31);
-                dacc = lane == 0 ? 0.f : below;
-              }
-            }
-            if (p.dts_w != nullptr && visible) {
-              if (bucket != run_bucket) {
-                if (run_bucket >= 0) atomicAdd(hist + 512 + run_bucket, run_sum);
-                run_bucket = bucket;
-                run_sum = 0.f;
-              }
-              run_sum += ds;
-            }
-          }
-          pp[e >> 1] = pack_bf16(pr[0], pr[1]);
-          dd[e >> 1] = pack_bf16(dr[0], dr[1]);
-        }
         uint8_t* prow = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
         uint8_t* drow = base_ptr + S::kDS + (cb >> 1) * 16384 + r * 128;
+        float4* dbias = nullptr;
+        if constexpr (!SOFTMAX) {
+          if (p.dbias_tiles != nullptr)
+            dbias = reinterpret_cast<float4*>(p.dbias_tiles + pair_off) + (cb * 4 + quarter) * 8 * 32 + lane;
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
-          *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
-        }
-      }
-      if (p.dpos_w != nullptr) {
-        atomicAdd(hist + (it & 1) * 256 + (cb * 32 + 31 - r + 127), dacc);
-        __syncwarp();
-        // the diagonals that left lane 31 at columns 0..30 (row quarter * 32 + 31)
-        if (lane < 31) atomicAdd(hist + (it & 1) * 256 + (cb * 32 + lane - (quarter * 32 + 31) + 127), wb.diag[lane]);
-      }
-      if (p.dts_w != nullptr) {
-        // far from the diagonal a whole 32x32 block usually falls into one bucket: one atomic per warp
-        const int b0 = __shfl_sync(0xffffffffu, run_bucket, 0);
-        if (__all_sync(0xffffffffu, run_bucket == b0)) {
-          float s = run_sum;
+          uint32_t pp[4], dd[4];
+          float dsv[8];
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          if (lane == 0 && b0 >= 0) atomicAdd(hist + 512 + b0, s);
-        } else if (run_bucket >= 0) {
-          atomicAdd(hist + 512 + run_bucket, run_sum);
+          for (int k = 0; k < 4; ++k) {
+            float pr[2], dr[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = g * 8 + 2 * k + u;       // within the warp's 32 columns
+              const float s_raw = __uint_as_float(sv[col]), dp = __uint_as_float(dpv[col]);
+              if constexpr (SOFTMAX) {
+                const int kj = kv0 + cb * 32 + col;
+                const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+                // P = exp(x - lse);  dS = P * (dP - delta)
+                const float pv = visible ? __expf(s_raw * p.scale - lse_r) : 0.f;
+                pr[u] = pv;
+                dr[u] = visible ? pv * (dp - delta_r) : 0.f;
+              } else {
+                // h = x / 2;  P = x sigmoid(x) = h tanh(h) + h;  dP/dx = sig + P (1 - sig), sig = (tanh(h) + 1) / 2
+                const uint32_t w = k == 0 ? hb[g].x : k == 1 ? hb[g].y : k == 2 ? hb[g].z : hb[g].w;
+                const float hv = fmaf(s_raw, hs, u == 0 ? bf16_lo(w) : bf16_hi(w));
+                const float t = tanh_fast(hv);
+                const float pv = fmaf(hv, t, hv);
+                const float sig = fmaf(0.5f, t, 0.5f);
+                pr[u] = pv;
+                dr[u] = dp * fmaf(pv, 1.f - sig, sig);
+              }
+              dsv[2 * k + u] = dr[u];
+            }
+            pp[k] = pack_bf16(pr[0], pr[1]);
+            dd[k] = pack_bf16(dr[0], dr[1]);
+          }
+          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+          *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+          if constexpr (!SOFTMAX) {
+            if (dbias != nullptr) {
+              // gradient of the bias: dS / n, summed over heads and layers in the pair's gradient block
+              red_add_v4(dbias + (2 * g) * 32, dsv[0] * p.inv_n, dsv[1] * p.inv_n, dsv[2] * p.inv_n, dsv[3] * p.inv_n);
+              red_add_v4(dbias + (2 * g + 1) * 32, dsv[4] * p.inv_n, dsv[5] * p.inv_n, dsv[6] * p.inv_n, dsv[7] * p.inv_n);
+            }
+          }
         }
       }
       tc_fence_before();
@@ -725,31 +826,21 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t v[32];
         tmem_ld32(tmem_s + lane_off + c * 32, v);
         if (row_ok) {
-          float* dst = p.dq + static_cast<size_t>(seq_start + qi) * p.H * DH + h * DH + c * 32;
+          float4* dst = reinterpret_cast<float4*>(p.dq + static_cast<size_t>(seq_start + qi) * p.H * DH + h * DH + c * 32);
 #pragma unroll
           for (int g = 0; g < 8; ++g)
-            atomicAdd(reinterpret_cast<float4*>(dst) + g,
-                      make_float4(__uint_as_float(v[4 * g]) * p.scale, __uint_as_float(v[4 * g + 1]) * p.scale,
-                                  __uint_as_float(v[4 * g + 2]) * p.scale, __uint_as_float(v[4 * g + 3]) * p.scale));
+            red_add_v4(dst + g, __uint_as_float(v[4 * g]) * dq_scale, __uint_as_float(v[4 * g + 1]) * dq_scale,
+                       __uint_as_float(v[4 * g + 2]) * dq_scale, __uint_as_float(v[4 * g + 3]) * dq_scale);
         }
       }
       tc_fence_before();
       mbar_arrive(bar(8));
-      // flush the diagonal bins of this (q tile, kv tile) pair: 128 compute threads, 255 bins
-      if (p.dpos_w != nullptr) {
-        // every compute thread must be past its last histogram atomic: they all arrived on bar(6) before the
-        // dQ commit could complete, and this thread observed that commit
-        const int tid = threadIdx.x - 64;
-        for (int b = tid; b < 255; b += kCompute) {
-          const float val = atomicExch(hist + (it & 1) * 256 + b, 0.f);   // the other parity is being filled by step it+1
-          if (val != 0.f) atomicAdd(p.dpos_w + (kv0 - q0) + (b - 127) + p.max_seq_len - 1, val);
-        }
-      }
     }
     if (ok && warp_wait(bar(9), 0, abortp, p.status, 57, lane)) {
       tc_fence_after();
       const int kj = kv0 + r;
       const bool kv_ok = kj < L;
+      const float dv_scale = SOFTMAX ? 1.f : p.inv_n, dk_scale = dq_scale;
 #pragma unroll 1
       for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32], w[32];
@@ -760,15 +851,15 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             *reinterpret_cast<uint4*>(p.dv + off + g * 8) =
-                make_uint4(pack_bf16(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                           pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                           pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                           pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+                make_uint4(pack_bf16(__uint_as_float(v[8 * g]) * dv_scale, __uint_as_float(v[8 * g + 1]) * dv_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 2]) * dv_scale, __uint_as_float(v[8 * g + 3]) * dv_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 4]) * dv_scale, __uint_as_float(v[8 * g + 5]) * dv_scale),
+                           pack_bf16(__uint_as_float(v[8 * g + 6]) * dv_scale, __uint_as_float(v[8 * g + 7]) * dv_scale));
             *reinterpret_cast<uint4*>(p.dk + off + g * 8) =
-                make_uint4(pack_bf16(__uint_as_float(w[8 * g]) * p.scale, __uint_as_float(w[8 * g + 1]) * p.scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 2]) * p.scale, __uint_as_float(w[8 * g + 3]) * p.scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 4]) * p.scale, __uint_as_float(w[8 * g + 5]) * p.scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 6]) * p.scale, __uint_as_float(w[8 * g + 7]) * p.scale));
+                make_uint4(pack_bf16(__uint_as_float(w[8 * g]) * dk_scale, __uint_as_float(w[8 * g + 1]) * dk_scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 2]) * dk_scale, __uint_as_float(w[8 * g + 3]) * dk_scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 4]) * dk_scale, __uint_as_float(w[8 * g + 5]) * dk_scale),
+                           pack_bf16(__uint_as_float(w[8 * g + 6]) * dk_scale, __uint_as_float(w[8 * g + 7]) * dk_scale));
           }
         }
       }
@@ -779,12 +870,6 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (p.dts_w != nullptr) {
-    for (int b = threadIdx.x; b <= p.num_buckets && b < 256; b += kThreads) {
-      const float val = hist[512 + b];
-      if (val != 0.f) atomicAdd(p.dts_w + b, val);
-    }
-  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_slot, S::kTmemCols);
@@ -819,7 +904,7 @@ extern "C" int recml_hstu_bucket_cache(const int* seq_offsets, int B, const int*
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-template <int DH>
+template <int DH, bool SOFTMAX>
 static int launch_fwd(const void* q, const void* k, const void* v, const Params& p, int n_tiles, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   const long long cols = static_cast<long long>(p.H) * DH;
@@ -827,7 +912,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
   if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
       recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV))
     return -2;
-  auto kern = hstu_fwd_kernel<DH>;
+  auto kern = hstu_fwd_kernel<DH, SOFTMAX>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<DH>::kTotal) != cudaSuccess) return -3;
@@ -843,12 +928,13 @@ extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, 
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->softmax && p->max_seq_len > 2 * BKV) return -11;   // the softmax forward keeps the whole key row in tensor memory
-  if (p->Dh == 64) return launch_fwd<64>(q, k, v, *p, n_tiles, stream);
-  if (p->Dh == 128) return launch_fwd<128>(q, k, v, *p, n_tiles, stream);
+  if (!p->softmax && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->Dh == 64) return p->softmax ? launch_fwd<64, true>(q, k, v, *p, n_tiles, stream) : launch_fwd<64, false>(q, k, v, *p, n_tiles, stream);
+  if (p->Dh == 128) return p->softmax ? launch_fwd<128, true>(q, k, v, *p, n_tiles, stream) : launch_fwd<128, false>(q, k, v, *p, n_tiles, stream);
   return -10;
 }
 
-template <int DH>
+template <int DH, bool SOFTMAX>
 static int launch_bwd(const void* q, const void* k, const void* v, const void* d_o, const Params& p, int n_tiles,
                       cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo;
@@ -857,7 +943,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
       recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV) || recml::tc::make_map_bf16(&mdo, d_o, p.T, cols, pitch(p.ld_do), BQ))
     return -2;
-  auto kern = hstu_bwd_kernel<DH>;
+  auto kern = hstu_bwd_kernel<DH, SOFTMAX>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB<DH>::kTotal) != cudaSuccess) return -3;
@@ -875,7 +961,33 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
                                    int n_tiles, cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->num_buckets + 1 > 256) return -11;
-  if (p->Dh == 64) return launch_bwd<64>(q, k, v, d_o, *p, n_tiles, stream);
-  if (p->Dh == 128) return launch_bwd<128>(q, k, v, d_o, *p, n_tiles, stream);
+  if (!p->softmax && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->Dh == 64) return p->softmax ? launch_bwd<64, true>(q, k, v, d_o, *p, n_tiles, stream) : launch_bwd<64, false>(q, k, v, d_o, *p, n_tiles, stream);
+  if (p->Dh == 128) return p->softmax ? launch_bwd<128, true>(q, k, v, d_o, *p, n_tiles, stream) : launch_bwd<128, false>(q, k, v, d_o, *p, n_tiles, stream);
   return -10;
+}
+
+extern "C" int recml_hstu_bias_struct_size() { return static_cast<int>(sizeof(BiasParams)); }
+
+// pair_base [B + 1] alone (when there is no time-bucket cache to build).
+extern "C" int recml_hstu_pair_base(const int* seq_offsets, int B, int causal, int* pair_base, cudaStream_t stream) {
+  pair_base_kernel<<<1, 32, 0, stream>>>(seq_offsets, B, causal, pair_base);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Bias tiles of every tile pair the attention kernels will visit (forward tile list of capacity n_tiles).
+extern "C" int recml_hstu_bias_tiles(const BiasParams* p, int n_tiles, int max_tiles_per_seq, cudaStream_t stream) {
+  if (n_tiles <= 0 || max_tiles_per_seq <= 0) return 0;
+  if (p->num_buckets + 1 > 256) return -11;
+  dim3 grid(n_tiles, max_tiles_per_seq);
+  bias_tile_kernel<<<grid, 256, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// dpos_w / dts_w (pre-zeroed, either may be null) from the gradient blocks, which are zeroed again.
+extern "C" int recml_hstu_bias_grads(const BiasParams* p, int n_tiles, int max_tiles_per_seq, cudaStream_t stream) {
+  if (n_tiles <= 0 || max_tiles_per_seq <= 0) return 0;
+  dim3 grid(n_tiles, max_tiles_per_seq);
+  bias_grad_kernel<<<grid, 512, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

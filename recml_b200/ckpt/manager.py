@@ -89,7 +89,7 @@ class CheckpointManager:
   def __init__(self, directory: str, *, max_to_keep: int | None = 5,
                should_save_fn: Callable[[int, int | None], bool] | None = None,
                save_interval_steps: int = 1, async_save: bool = True,
-               item_name: str = "state", compressor: str | None = None, group=None):
+               item_name: str = "state", compressor: str | None = None, group=None, use_ocdbt: bool = False):
     self.directory = os.fspath(directory)
     self.max_to_keep = max_to_keep
     self.should_save_fn = should_save_fn
@@ -98,6 +98,10 @@ class CheckpointManager:
     self.item_name = item_name
     self.compressor = compressor
     self.group = group
+    # True: every item is written as an OCDBT store (the reference's default: `manifest.ocdbt`, `d/`, one
+    # `ocdbt.process_<rank>` store per writing rank) instead of one directory per array.  Reading detects
+    # the form by itself.
+    self.use_ocdbt = use_ocdbt
     self._thread: threading.Thread | None = None
     self._error: BaseException | None = None
     self._last_saved: int | None = None
@@ -214,12 +218,15 @@ class CheckpointManager:
         sharding[key] = {"sharding_type": "block", "chunk_shape": list(leaf.chunk_shape)}
         if leaf.mod:
           sharding[key]["mod"] = leaf.mod
-    zarr_io.write_chunks_parallel(pending, self.compressor)
+    if self.use_ocdbt:
+      self._write_ocdbt(item, pending, rank, world)
+    else:
+      zarr_io.write_chunks_parallel(pending, self.compressor)
     if rank == 0:
       with open(os.path.join(item, TREE_METADATA), "w") as f:
         json.dump({"tree_metadata": meta_tree,
                    "containers": {".".join(k): v for k, v in kinds.items()},
-                   "use_zarr3": False, "use_ocdbt": False}, f)
+                   "use_zarr3": False, "use_ocdbt": bool(self.use_ocdbt)}, f)
       with open(os.path.join(item, SHARDING_FILE), "w") as f:
         json.dump(sharding, f)
       if metrics is not None:
@@ -233,9 +240,41 @@ class CheckpointManager:
                    "init_timestamp_nsecs": time.time_ns(),
                    "commit_timestamp_nsecs": time.time_ns()}, f)
 
+  def _write_ocdbt(self, item, pending, rank, world):
+    """This rank's chunks (and, on rank 0, every array's `.zarray`) as the store `ocdbt.process_<rank>` of the
+    item; rank 0 also writes the item's own (empty) manifest, whose presence marks the item as an OCDBT one.
+    The `.zarray` files that `_write` put into per-array directories are folded in and removed."""
+    from recml_b200.ckpt import ocdbt
+    import glob
+    w = ocdbt.Writer(os.path.join(item, f"ocdbt.process_{rank}"))
+    if rank == 0:
+      for meta in glob.glob(os.path.join(item, "*", ".zarray")):
+        key = os.path.basename(os.path.dirname(meta))
+        with open(meta, "rb") as f:
+          w.add(f"{key}/.zarray", f.read())
+    for leaf_dir, index, arr in pending:
+      raw = arr.tobytes(order="C")
+      if self.compressor == "zstd":
+        raw = zarr_io.zstd_compress(raw)
+      w.add(f"{os.path.basename(leaf_dir)}/{zarr_io.chunk_name(index)}", raw)
+    w.commit(compress_nodes=zarr_io.zstd_available())
+    if rank == 0:
+      ocdbt.Writer(item).commit(compress_nodes=False)
+    if world == 1:
+      self._drop_array_dirs(item)
+
+  @staticmethod
+  def _drop_array_dirs(item):
+    for name in os.listdir(item):
+      d = os.path.join(item, name)
+      if os.path.isdir(d) and not name.startswith("ocdbt.process_") and name != "d":
+        shutil.rmtree(d, ignore_errors=True)
+
   def _finalize(self, step, tmp, final):
     if self._error:
       return
+    if self.use_ocdbt:        # every rank has folded the per-array directories into its store by now
+      self._drop_array_dirs(os.path.join(tmp, self.item_name))
     with open(os.path.join(tmp, COMMIT_FILE), "w") as f:
       f.write("Checkpoint commit was successful.")
     os.replace(tmp, final)
@@ -283,8 +322,11 @@ def restore_tree(item: str, target: Mapping[str, Any] | None = None) -> Any:
     raise FileNotFoundError(f"{item} is not a complete checkpoint item")
   with open(os.path.join(item, TREE_METADATA)) as f:
     meta = json.load(f)
+  from recml_b200.ckpt import ocdbt
+  in_store = ocdbt.is_store(item)
+  leaf_at = (lambda key: ocdbt.leaf_path(item, key)) if in_store else (lambda key: os.path.join(item, key))
   if target is None:
-    leaves = {tuple(m["key_path"]): zarr_io.read_region(os.path.join(item, key))
+    leaves = {tuple(m["key_path"]): zarr_io.read_region(leaf_at(key))
               for key, m in meta["tree_metadata"].items()}
     kinds = {tuple(k.split(".")) if k else (): v for k, v in meta.get("containers", {}).items()}
     return tree_lib.restore_containers(tree_lib.unflatten(leaves), kinds)
@@ -297,7 +339,7 @@ def restore_tree(item: str, target: Mapping[str, Any] | None = None) -> Any:
     key = ".".join(path)
     if key not in meta["tree_metadata"]:
       raise KeyError(f"Checkpoint has no leaf {key!r}")
-    leaf_dir = os.path.join(item, key)
+    leaf_dir = leaf_at(key)
     if isinstance(leaf, ShardedLeaf):
       stored_shape = tuple(zarr_io.read_meta(leaf_dir)["shape"])
       stored_mod = (sharding_meta.get(key) or {}).get("mod")

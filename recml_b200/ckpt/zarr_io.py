@@ -125,7 +125,20 @@ def write_array(path: str, value, compressor: str | None = None) -> None:
   write_chunk(path, [0] * arr.ndim, arr, compressor)
 
 
+def _is_ocdbt(path: str) -> bool:
+  return path.startswith("ocdbt:")
+
+
+def _ocdbt_get(path: str, name: str) -> bytes:
+  """Value of `<array key>/<name>` for an array that lives in an OCDBT store (`ckpt/ocdbt.py`)."""
+  from recml_b200.ckpt import ocdbt
+  store_dir, key = ocdbt.split_path(path)
+  return ocdbt.open_store(store_dir).get(f"{key}/{name}" if key else name)
+
+
 def read_meta(path: str) -> dict:
+  if _is_ocdbt(path):
+    return json.loads(_ocdbt_get(path, ".zarray"))
   with open(os.path.join(path, ".zarray")) as f:
     return json.load(f)
 
@@ -206,6 +219,8 @@ def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> 
   to one contiguous piece of `out`, so the native reader fills `out` directly, many threads at once and
   in segments of 16 MB (a table shard is one large chunk).  False: the caller takes the general path."""
   nd = len(shape)
+  if _is_ocdbt(path):
+    return False
   if any(chunks[d] != shape[d] or start[d] != 0 or stop[d] != shape[d] for d in range(1, nd)) or out.size == 0:
     return False
   try:
@@ -241,8 +256,11 @@ def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> 
 
 
 def _read_chunk(path, cidx, chunks, dt, comp) -> np.ndarray:
-  with open(os.path.join(path, chunk_name(cidx)), "rb") as f:
-    blob = f.read()
+  if _is_ocdbt(path):
+    blob = _ocdbt_get(path, chunk_name(cidx))
+  else:
+    with open(os.path.join(path, chunk_name(cidx)), "rb") as f:
+      blob = f.read()
   n = int(np.prod(chunks)) if len(chunks) else 1
   if comp is not None:
     if comp.get("id") != "zstd" or not zstd_available():

@@ -126,12 +126,17 @@ class HSTUBlock(nn.Module):
     return self._finish(inputs, u, attn)
 
   def forward_jagged(self, tokens: torch.Tensor, seq_offsets: torch.Tensor, max_seq_len: int, *,
-                     pos_w=None, ts_w=None, timestamps=None):
-    """Packed form: tokens `[T, D]`; causal pointwise attention inside every sequence."""
+                     pos_w=None, ts_w=None, timestamps=None, segment_ids=None, row_mask=None):
+    """Packed form: tokens `[T, D]`; causal pointwise attention inside every sequence.  `segment_ids [T]`
+    restricts a query to keys of its own segment; `row_mask [T]` zeroes the attention output of the rows
+    where it is 0 (padded positions of a dense batch that is run through the packed kernels)."""
     u, q, k, v = self._project(tokens)
     scale = 1.0 / math.sqrt(self.head_dim) if self.scaled else 1.0
     attn = attn_ops.jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
-                                               timestamps=timestamps, causal=True, scale=scale)
+                                               timestamps=timestamps, causal=True, scale=scale,
+                                               segment_ids=segment_ids)
+    if row_mask is not None:
+      attn = attn * row_mask[:, None, None].to(attn.dtype)
     return self._finish(tokens, u, attn)
 
 
@@ -178,6 +183,8 @@ class HSTU(nn.Module):
     if attention_mask is None:
       if padding_mask is None:
         raise ValueError("Either `attention_mask` or `padding_mask` must be set.")
+      if self._packed_kernels_apply(e):
+        return self._forward_dense_through_packed_kernels(e, padding_mask, timestamps)
       attention_mask = utils.make_causal_mask(padding_mask)
     bias = None
     if self.relative_bias is not None:
@@ -187,6 +194,38 @@ class HSTU(nn.Module):
       e = block(e, attention_mask, bias)
     e = self._final_norm(e)
     return e if not self.add_head else self.item_embedding(e, reverse=True)
+
+  def _packed_kernels_apply(self, e: torch.Tensor) -> bool:
+    """The dense (padded) call can run on the packed attention kernels: CUDA, head dim 64 / 128, SiLU
+    attention without attention dropout, and (when there is a relative bias) a position table made for this
+    padded length."""
+    b = self.decoder_blocks[0]
+    if not e.is_cuda or b.head_dim not in (64, 128) or b.softmax or b.scaled:
+      return False
+    if self.training and b.dropout_p > 0:
+      return False
+    return self.relative_bias is None or self.max_seq_len == e.shape[1]
+
+  def _forward_dense_through_packed_kernels(self, e, padding_mask, timestamps):
+    """`[B, L, D]` padded batch as B packed sequences of length L: the mask `valid[i] & valid[j] & (j <= i)` of
+    the dense formulation becomes causality plus segment ids (every padded position is a segment of its own)
+    plus zeroing the padded query rows; the normaliser is L in both."""
+    B, L, D = e.shape
+    dev = e.device
+    valid = padding_mask.reshape(-1) != 0
+    pos = torch.arange(B * L, device=dev, dtype=torch.int32)
+    seg = torch.where(valid, torch.zeros_like(pos), -1 - pos)
+    offs = torch.arange(B + 1, device=dev, dtype=torch.int32) * L
+    pos_w = ts_w = None
+    ts = None
+    if self.relative_bias is not None:
+      pos_w, ts_w = self.relative_bias.positional_bias.pos_biases, self.relative_bias.ts_w
+      ts = (timestamps if timestamps is not None else torch.zeros(B, L, device=dev, dtype=torch.int64)).reshape(-1)
+    x = e.reshape(B * L, D)
+    for block in self.decoder_blocks:
+      x = block.forward_jagged(x, offs, L, pos_w=pos_w, ts_w=ts_w, timestamps=ts, segment_ids=seg, row_mask=valid)
+    x = self._final_norm(x).reshape(B, L, D)
+    return x if not self.add_head else self.item_embedding(x, reverse=True)
 
   def forward_jagged(self, ids: torch.Tensor, seq_offsets: torch.Tensor, timestamps: torch.Tensor | None = None):
     """Packed form: ids `[T]`, `seq_offsets [B+1]` → token states `[T, D]` (heads are applied by the

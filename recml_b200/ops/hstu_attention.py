@@ -151,7 +151,8 @@ def q_sharded_pointwise_attention(mask_type: MaskType | str, q, k, v, *, group=N
 
 
 def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
-                               timestamps=None, causal: bool = True, scale: float = 1.0):
+                               timestamps=None, causal: bool = True, scale: float = 1.0,
+                               sliding_window_size: int | None = None, segment_ids=None):
   """fp32 torch oracle for the packed kernel: q, k, v `[T, H, Dh]`, `seq_offsets [B+1]`."""
   out = torch.zeros_like(q, dtype=torch.float32)
   offs = seq_offsets.tolist()
@@ -166,39 +167,57 @@ def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=
     if bias is not None:
       s = s + bias.float()
     p = torch.nn.functional.silu(s) / max_seq_len
-    if causal:
-      p = torch.tril(p)
+    m = attention_mask("causal" if causal else "full", L, L, sliding_window_size=sliding_window_size, device=q.device)
+    if segment_ids is not None:
+      m = m & (segment_ids[a:e, None] == segment_ids[None, a:e])
+    p = torch.where(m[None], p, torch.zeros_like(p))
     out[a:e] = torch.einsum("hts,shd->thd", p, v[a:e].float())
   return out.to(q.dtype)
 
 
 class _JaggedAttnFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, q, k, v, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale):
+  def forward(ctx, q, k, v, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids):
     from recml_b200.ops import hstu_cuda
-    o = hstu_cuda.forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale)
-    ctx.save_for_backward(q, k, v, pos_w, ts_w, seq_offsets, timestamps)
+    bc = hstu_cuda.bias_context(seq_offsets, timestamps, pos_w, ts_w, q.shape[0], max_seq_len, causal, window,
+                                segment_ids)
+    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    ctx.save_for_backward(q, k, v, pos_w, ts_w, seq_offsets)
     ctx.meta = (max_seq_len, causal, scale)
+    ctx.bias_ctx = bc
+    if any(ctx.needs_input_grad):       # this call may see a backward: the step's last one finishes the bias tables
+      bc.pending += 1
+      bc.want_bias_grad = bc.want_bias_grad or ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
     return o
 
   @staticmethod
   def backward(ctx, do):
     from recml_b200.ops import hstu_cuda
-    q, k, v, pos_w, ts_w, seq_offsets, timestamps = ctx.saved_tensors
+    q, k, v, pos_w, ts_w, seq_offsets = ctx.saved_tensors
     max_seq_len, causal, scale = ctx.meta
-    dq, dk, dv, dpos, dts = hstu_cuda.backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w,
-                                               max_seq_len, causal, scale)
-    return dq, dk, dv, dpos, dts, None, None, None, None, None
+    bc = ctx.bias_ctx
+    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    bc.pending -= 1
+    dpos = dts = None
+    if bc.pending <= 0 and bc.want_bias_grad:
+      dpos, dts = bc.table_gradients(pos_w, ts_w)
+      bc.want_bias_grad = False
+    return dq, dk, dv, dpos, dts, None, None, None, None, None, None, None
 
 
 def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
-                               timestamps=None, causal: bool = True, scale: float = 1.0):
-  """Packed HSTU attention.  CUDA bf16 inputs with head dim 64 or 128 run the sm_100a kernel;
-  everything else takes the torch oracle (differentiable through autograd)."""
+                               timestamps=None, causal: bool = True, scale: float = 1.0,
+                               sliding_window_size: int | None = None, segment_ids=None):
+  """Packed HSTU attention.  CUDA bf16 inputs with head dim 64 or 128 run the sm_100a kernels (masks —
+  causal, sequence ends, an inclusive sliding window, equal segment ids `[T]` — and the learned bias all
+  arrive through the step's bias tiles); everything else takes the torch oracle (differentiable through
+  autograd)."""
   if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
     from recml_b200.ops import hstu_cuda
     if hstu_cuda.available():
       return _JaggedAttnFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), pos_w, ts_w,
-                                 hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len, causal, scale)
+                                 hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len, causal, scale,
+                                 sliding_window_size, segment_ids)
   return jagged_attention_reference(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
-                                    timestamps=timestamps, causal=causal, scale=scale)
+                                    timestamps=timestamps, causal=causal, scale=scale,
+                                    sliding_window_size=sliding_window_size, segment_ids=segment_ids)

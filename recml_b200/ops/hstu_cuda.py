@@ -17,7 +17,15 @@ class _Params(ctypes.Structure):
               ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
               ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("softmax", c_int), ("lse", c_vp),
               ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int),
-              ("bucket_cache", c_vp), ("pair_base", c_vp), ("cap_pairs", c_int)]
+              ("bucket_cache", c_vp), ("pair_base", c_vp), ("cap_pairs", c_int), ("bias_tiles", c_vp),
+              ("dbias_tiles", c_vp), ("window", c_int), ("segment_ids", c_vp)]
+
+
+class _BiasParams(ctypes.Structure):
+  _fields_ = [("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("pair_base", c_vp), ("causal", c_int),
+              ("cap_pairs", c_int), ("max_seq_len", c_int), ("window", c_int), ("num_buckets", c_int),
+              ("segment_ids", c_vp), ("pos_w", c_vp), ("ts_w", c_vp), ("bucket_cache", c_vp), ("tiles", c_vp),
+              ("dbias", c_vp), ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp)]
 
 
 _ok: bool | None = None
@@ -27,7 +35,8 @@ def available() -> bool:
   global _ok
   if _ok is None:
     try:
-      _ok = int(_lib.cuda().recml_hstu_struct_size()) == ctypes.sizeof(_Params)
+      _ok = (int(_lib.cuda().recml_hstu_struct_size()) == ctypes.sizeof(_Params) and
+             int(_lib.cuda().recml_hstu_bias_struct_size()) == ctypes.sizeof(_BiasParams))
     except Exception:  # pylint: disable=broad-except
       _ok = False
   return _ok
@@ -87,22 +96,27 @@ def _make_tiles(seq_offsets: torch.Tensor, T: int, backward: bool = False):
   return tile_seq, tile_row0, cap
 
 
-BUCKET_CACHE_MAX_BYTES = 1 << 30
+# Per-pair blocks (time buckets 16 KB, bias 32 KB, bias gradient 64 KB) are sized for the worst case the
+# token capacity allows; beyond this many pairs the caller falls back to the torch formulation.
+MAX_PAIRS = 1 << 17
+
+
+def _pair_capacity(T: int, B: int, max_seq_len: int, causal: bool) -> tuple[int, int, int]:
+  """(tile capacity, tiles of the longest sequence, pair capacity): with n_i 128-row tiles per sequence,
+  sum n_i <= cap and n_i <= max_nt bound the pairs (n_i (n_i + 1) / 2 causal, n_i^2 full) by cap times
+  (max_nt + 1) / 2, respectively max_nt."""
+  cap = (T + 127) // 128 + B
+  max_nt = (max_seq_len + 127) // 128
+  cap_pairs = cap * (max_nt + 1) // 2 + 1 if causal else cap * max_nt
+  return cap, max_nt, cap_pairs
 
 
 def _bucket_cache(seq_offsets, ts32, T: int, max_seq_len: int, num_buckets: int, causal: bool):
   """Time-bucket indices of every (query tile, key tile) pair of the batch as uint8 blocks of 128 x 128,
-  computed once per batch: all heads, all layers and both passes read the same ones.  Returns
-  (cache, pair_base, cap_pairs) or None when the blocks would not fit the size limit (the kernels then
-  compute the buckets inline)."""
-  if ts32 is None or num_buckets + 1 > 256:
-    return None
+  computed once per batch: the bias tiles of the step and the bias-gradient pass read them.  Returns
+  (cache, pair_base, cap_pairs, seq_offsets)."""
   B = seq_offsets.numel() - 1
-  cap = (T + 127) // 128 + B
-  max_nt = (max_seq_len + 127) // 128
-  cap_pairs = cap * ((max_nt + 2) // 2 if causal else max_nt)
-  if cap_pairs * 16384 > BUCKET_CACHE_MAX_BYTES:
-    return None
+  cap, max_nt, cap_pairs = _pair_capacity(T, B, max_seq_len, causal)
 
   def make():
     tiles = _tiles(seq_offsets, T)
@@ -112,11 +126,138 @@ def _bucket_cache(seq_offsets, ts32, T: int, max_seq_len: int, num_buckets: int,
         _lib.ptr(seq_offsets), c_int(B), _lib.ptr(tiles[0]), _lib.ptr(tiles[1]), c_int(tiles[2]), _lib.ptr(ts32),
         c_int(num_buckets), c_int(int(causal)), c_int(max_nt), _lib.ptr(pair_base), _lib.ptr(cache), c_int(cap_pairs),
         _lib.stream()), "hstu_bucket_cache")
+    _lib.LAUNCHES["count"] += 1
     return cache, pair_base, cap_pairs, seq_offsets   # the offsets the blocks were made for stay alive with them
 
   hit = _remember("buckets", ts32, make, (T, max_seq_len, num_buckets, bool(causal)))
   same = hit[3] is seq_offsets or (hit[3].data_ptr() == seq_offsets.data_ptr() and hit[3]._version == seq_offsets._version)
-  return hit if same else None
+  if not same:          # same timestamps tensor, other offsets: rebuild
+    _memo.pop("buckets", None)
+    hit = _remember("buckets", ts32, make, (T, max_seq_len, num_buckets, bool(causal)))
+  return hit
+
+
+def _ident(t):
+  return None if t is None else (t.data_ptr(), t._version, tuple(t.shape))
+
+
+# Free lists of the per-pair block buffers (hundreds of megabytes each): a context takes what it needs and gives
+# it back when it dies, so a training loop keeps re-using the same two buffers while two contexts that are alive
+# at the same time (say a causal and a full call whose backward passes come later) never share one.
+_free: dict[tuple, list[torch.Tensor]] = {}
+
+
+def _take(kind: str, numel: int, dtype, device, zero: bool = False) -> torch.Tensor:
+  key = (kind, str(device), dtype)
+  pool = _free.setdefault(key, [])
+  for i, t in enumerate(pool):
+    if t.numel() >= numel:
+      pool.pop(i)
+      if zero and getattr(t, "_recml_dirty", False):
+        t.zero_()
+        t._recml_dirty = False
+      return t
+  pool.clear()            # too small for what is needed now: let them go
+  return (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=device)
+
+
+def _give_back(kind: str, t: torch.Tensor) -> None:
+  pool = _free.setdefault((kind, str(t.device), t.dtype), [])
+  if len(pool) < 2:
+    pool.append(t)
+
+
+class BiasContext:
+  """What every attention call of one training step shares: the bias tiles of the batch (built once, from the
+  relative-position / time-bucket tables, the masks and the batch's lengths and timestamps) and the block
+  buffer into which every backward call adds its score gradients.  The LAST backward call of the step (the
+  count of forward calls that can reach a backward is kept here) turns that buffer into the gradients of the
+  two tables and returns them; the earlier ones return none for the tables, which autograd treats as zero."""
+
+  def __init__(self, seq_offsets, ts32, pos_w, ts_w, T, max_seq_len, causal, window, segment_ids):
+    lib = _lib.cuda()
+    dev = seq_offsets.device
+    B = seq_offsets.numel() - 1
+    self.seq_offsets, self.ts32, self.segment_ids = seq_offsets, ts32, segment_ids
+    self.causal, self.window, self.max_seq_len, self.T = bool(causal), window, max_seq_len, T
+    self.pos_w = None if pos_w is None else pos_w.detach().float().contiguous()
+    self.ts_w = None if (ts_w is None or ts32 is None) else ts_w.detach().float().contiguous()
+    self.num_buckets = self.ts_w.numel() - 1 if self.ts_w is not None else 0
+    self.tiles_f = _tiles(seq_offsets, T)
+    cap, self.max_nt, self.cap_pairs = _pair_capacity(T, B, max_seq_len, causal)
+    if self.cap_pairs > MAX_PAIRS:
+      raise MemoryError(f"{self.cap_pairs} tile pairs exceed the per-pair cache limit ({MAX_PAIRS})")
+    self.bucket_cache = None
+    if self.ts_w is not None:
+      bc = _bucket_cache(seq_offsets, ts32, T, max_seq_len, self.num_buckets, causal)
+      self.bucket_cache, self.pair_base = bc[0], bc[1]
+    else:
+      self.pair_base = torch.empty(B + 1, dtype=torch.int32, device=dev)
+      _lib.check_rc(lib.recml_hstu_pair_base(_lib.ptr(seq_offsets), c_int(B), c_int(int(causal)),
+                                             _lib.ptr(self.pair_base), _lib.stream()), "hstu_pair_base")
+    self.tiles = _take("bias_tiles", self.cap_pairs * 16384, torch.bfloat16, dev)
+    self.dbias = None
+    self.pending = 0
+    self.want_bias_grad = False
+    _lib.check_rc(lib.recml_hstu_bias_tiles(ctypes.byref(self._params()), c_int(self.tiles_f[2]), c_int(self.max_nt),
+                                            _lib.stream()), "hstu_bias_tiles")
+
+  def _params(self, dpos=None, dts=None) -> _BiasParams:
+    p = _BiasParams()
+    p.seq_offsets, p.tile_seq, p.tile_row0 = self.seq_offsets.data_ptr(), self.tiles_f[0].data_ptr(), self.tiles_f[1].data_ptr()
+    p.pair_base, p.causal, p.cap_pairs, p.max_seq_len = self.pair_base.data_ptr(), int(self.causal), self.cap_pairs, self.max_seq_len
+    p.window = -1 if self.window is None else int(self.window)
+    p.num_buckets = self.num_buckets
+    p.segment_ids = None if self.segment_ids is None else self.segment_ids.data_ptr()
+    p.pos_w = None if self.pos_w is None else self.pos_w.data_ptr()
+    p.ts_w = None if self.ts_w is None else self.ts_w.data_ptr()
+    p.bucket_cache = None if self.bucket_cache is None else self.bucket_cache.data_ptr()
+    p.tiles = self.tiles.data_ptr()
+    p.dbias = None if self.dbias is None else self.dbias.data_ptr()
+    p.dpos_w = None if dpos is None else dpos.data_ptr()
+    p.dts_w = None if dts is None else dts.data_ptr()
+    p.status = _lib.status_buffer(self.seq_offsets.device).data_ptr()
+    return p
+
+  def gradient_blocks(self) -> torch.Tensor:
+    """The fp32 block buffer the backward kernels reduce into (all zeros between steps: the gradient pass
+    clears what it reads; a step that was abandoned half-way leaves it marked dirty and it is cleared here)."""
+    if self.dbias is None:
+      self.dbias = _take("bias_grads", self.cap_pairs * 16384, torch.float32, self.seq_offsets.device, zero=True)
+      self.dbias._recml_dirty = True
+    return self.dbias
+
+  def __del__(self):
+    try:
+      if getattr(self, "tiles", None) is not None:
+        _give_back("bias_tiles", self.tiles)
+      if getattr(self, "dbias", None) is not None:
+        _give_back("bias_grads", self.dbias)        # still marked dirty: cleared by whoever takes it next
+    except Exception:  # pylint: disable=broad-except
+      pass
+
+  def table_gradients(self, pos_w, ts_w):
+    dpos = torch.zeros_like(self.pos_w) if self.pos_w is not None else None
+    dts = torch.zeros_like(self.ts_w) if self.ts_w is not None else None
+    if self.dbias is not None and (dpos is not None or dts is not None):
+      _lib.check_rc(_lib.cuda().recml_hstu_bias_grads(ctypes.byref(self._params(dpos, dts)), c_int(self.tiles_f[2]),
+                                                      c_int(self.max_nt), _lib.stream()), "hstu_bias_grads")
+      self.dbias._recml_dirty = False
+      _give_back("bias_grads", self.dbias)
+      self.dbias = None
+    out_pos = None if (pos_w is None or dpos is None) else dpos.to(pos_w.dtype)
+    out_ts = None if ts_w is None else (dts.to(ts_w.dtype) if dts is not None else torch.zeros_like(ts_w))
+    return out_pos, out_ts
+
+
+def bias_context(seq_offsets, timestamps, pos_w, ts_w, T, max_seq_len, causal, window=None, segment_ids=None) -> BiasContext:
+  """The step's shared context: one per (batch, table values, mask description); every layer's call finds it."""
+  ts32 = _ts32(timestamps)
+  if segment_ids is not None and segment_ids.dtype != torch.int32:
+    segment_ids = _remember("seg32", segment_ids, lambda: segment_ids.to(torch.int32).contiguous())
+  extra = (T, max_seq_len, bool(causal), window, _ident(ts32), _ident(pos_w), _ident(ts_w), _ident(segment_ids))
+  return _remember("bias_ctx", seq_offsets,
+                   lambda: BiasContext(seq_offsets, ts32, pos_w, ts_w, T, max_seq_len, causal, window, segment_ids), extra)
 
 
 def rows_ok(t: torch.Tensor) -> bool:
@@ -146,68 +287,42 @@ def _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale,
   p.pos_w = pos_w.data_ptr() if pos_w is not None else None
   p.ts_w = ts_w.data_ptr() if (ts_w is not None and timestamps is not None) else None
   p.status = _lib.status_buffer(q.device).data_ptr()
-  if p.ts_w is not None:
-    bc = _bucket_cache(seq_offsets, timestamps, T, max_seq_len, p.num_buckets, bool(causal))
-    if bc is not None:
-      p.bucket_cache, p.pair_base, p.cap_pairs = bc[0].data_ptr(), bc[1].data_ptr(), bc[2]
+  p.window = -1
   return p
 
 
-def forward(q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
+def _attach(p: _Params, bc: BiasContext) -> None:
+  p.pair_base, p.cap_pairs, p.bias_tiles = bc.pair_base.data_ptr(), bc.cap_pairs, bc.tiles.data_ptr()
+
+
+def forward(q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale):
   assert rows_ok(q) and rows_ok(k) and rows_ok(v)
-  timestamps = _ts32(timestamps)
-  pos_w = None if pos_w is None else pos_w.detach().float().contiguous()
-  ts_w = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0])
   out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-  p = _params(q, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale, tiles, k, v)
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v)
+  _attach(p, bc)
   p.out = out.data_ptr()
-  keep = (timestamps, pos_w, ts_w, tiles)  # referenced until the launch is enqueued
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "hstu_attn_fwd")
-  del keep
   return out
 
 
-def backward(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
-  """Gradients w.r.t. q, k, v, pos_w, ts_w."""
+def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale):
+  """Gradients w.r.t. q, k, v; the score gradients go into the context's block buffer when a bias table
+  wants a gradient."""
   lib = _lib.cuda()
-  if not hasattr(lib._lib, "recml_hstu_attn_bwd"):
-    return _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale)
-  timestamps = _ts32(timestamps)
-  pw = None if pos_w is None else pos_w.detach().float().contiguous()
-  tw = None if ts_w is None else ts_w.detach().float().contiguous()
   tiles = _tiles(seq_offsets, q.shape[0], backward=True)
   do = as_rows(do)
   dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
   dk, dv = (torch.empty(k.shape, dtype=k.dtype, device=k.device) for _ in range(2))
-  dpos = torch.zeros_like(pw) if pw is not None else None
-  dts = torch.zeros_like(tw) if (tw is not None and timestamps is not None) else None
-  p = _params(q, seq_offsets, timestamps, pw, tw, max_seq_len, causal, scale, tiles, k, v, do)
+  p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v, do)
+  _attach(p, bc)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-  p.dpos_w = dpos.data_ptr() if dpos is not None else None
-  p.dts_w = dts.data_ptr() if dts is not None else None
+  if bc.want_bias_grad:
+    p.dbias_tiles = bc.gradient_blocks().data_ptr()
   _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do),
                                         ctypes.byref(p), c_int(tiles[2]), _lib.stream()), "hstu_attn_bwd")
-  return (dq.to(q.dtype), dk, dv, None if dpos is None else dpos.to(pos_w.dtype),
-          None if ts_w is None else (dts.to(ts_w.dtype) if dts is not None else torch.zeros_like(ts_w)))
-
-
-def _backward_reference(do, q, k, v, seq_offsets, timestamps, pos_w, ts_w, max_seq_len, causal, scale):
-  from recml_b200.ops import hstu_attention as A
-  with torch.enable_grad():
-    leaves = [t.detach().float().requires_grad_() for t in (q, k, v)]
-    pw = None if pos_w is None else pos_w.detach().float().requires_grad_()
-    tw = None if ts_w is None else ts_w.detach().float().requires_grad_()
-    o = A.jagged_attention_reference(*leaves, seq_offsets, max_seq_len, pos_w=pw, ts_w=tw, timestamps=timestamps,
-                                     causal=causal, scale=scale)
-    params = leaves + [t for t in (pw, tw) if t is not None]
-    grads = list(torch.autograd.grad(o, params, do.float(), allow_unused=True))
-  dq, dk, dv = (g.to(q.dtype) for g in grads[:3])
-  rest = grads[3:]
-  dpos = rest.pop(0) if pw is not None else None
-  dts = rest.pop(0) if tw is not None else None
-  return dq, dk, dv, dpos, dts
+  return dq.to(q.dtype), dk, dv
 
 
 # ---- softmax mode: the same kernels with P = softmax(scale * QK^T) over the visible keys ----------------------

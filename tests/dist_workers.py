@@ -39,7 +39,7 @@ def entry(rank, world, backend, port, fn_name, args, result_dir):
         pass
 
 
-def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank):
+def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank, use_ocdbt=False):
   """Trains a row-sharded (MOD) embedding for two steps and checkpoints it.  With `fail_rank` >= 0 that
   rank's chunk writer raises, and the save must commit nothing on any rank."""
   from recml_b200 import ckpt, embedding as emb
@@ -53,7 +53,7 @@ def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank):
     feats = {k: [gen.integers(0, s.input_dim, size=3).tolist() for _ in range(4)] for k, s in specs.items()}
     out = m(emb.KeyedJagged.from_lists(feats))
     (out if isinstance(out, torch.Tensor) else sum(o.sum() for o in out.values())).sum().backward()
-  mgr = ckpt.CheckpointManager(ckpt_dir, async_save=False)
+  mgr = ckpt.CheckpointManager(ckpt_dir, async_save=False, use_ocdbt=use_ocdbt)
   mgr.save(1, {"sharded": m.sharded_state_dict()})           # a good checkpoint first
   raised = None
   if fail_rank >= 0:

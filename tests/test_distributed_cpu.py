@@ -65,6 +65,26 @@ def test_row_wise_table_saved_by_two_ranks_restores_on_one(tmp_path):
     torch.testing.assert_close(m.gather_table(n, "accumulator"), res[0]["slots"][n])
 
 
+def test_ocdbt_checkpoint_of_two_ranks_restores_on_one(tmp_path):
+  """The OCDBT form with one store per writing process (`ocdbt.process_0`, `ocdbt.process_1`): a stacked,
+  MOD-sharded table written by 2 ranks is re-sharded into a 1-rank job."""
+  import os
+  from recml_b200 import ckpt, embedding as emb
+  d = str(tmp_path / "ck")
+  res = dist_utils.run_ranks("save_row_wise_tables", 2, "gloo", "cpu", d, -1, True)
+  item = os.path.join(d, "1", "state")
+  assert {"manifest.ocdbt", "ocdbt.process_0", "ocdbt.process_1"} <= set(os.listdir(item))
+  specs = {"a": emb.EmbeddingSpec(37, 8, combiner="sum"), "b": emb.EmbeddingSpec(10, 8, combiner="sum")}
+  cfg = emb.ShardedEmbeddingConfig(specs, emb.AdagradOptimizerSpec(learning_rate=0.1), sharding_strategy="MOD",
+                                   backend="collective")
+  m = emb.ShardedEmbedding(cfg, device="cpu")
+  got = ckpt.CheckpointManager(d, async_save=False).restore(1, target={"sharded": m.sharded_state_dict()})
+  m.load_sharded_state_dict(got["sharded"])
+  for n in specs:
+    torch.testing.assert_close(m.gather_table(n), res[0]["tables"][n])
+    torch.testing.assert_close(m.gather_table(n, "accumulator"), res[0]["slots"][n])
+
+
 def test_failed_shard_write_commits_nothing_on_any_rank(tmp_path):
   d = str(tmp_path / "ck")
   res = dist_utils.run_ranks("save_row_wise_tables", 2, "gloo", "cpu", d, 1)

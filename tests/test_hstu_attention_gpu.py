@@ -178,3 +178,102 @@ def test_bucket_cache_equals_inline_buckets(causal, monkeypatch):
   assert torch.equal(g_c[1], g_i[1]) and torch.equal(g_c[2], g_i[2])
   for a, b in zip(g_c, g_i):
     torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
+
+
+def _compare(ref, got, tol, what):
+  err = (got.float().cpu() - ref).abs().max().item()
+  scale = ref.abs().max().item() + 1e-6
+  assert err / scale < tol, (what, err, scale)
+
+
+def test_long_sequence_4096_forward_backward():
+  """The configuration's longest sequences: 32 x 32 tile pairs per sequence, bias tables of 8191 entries."""
+  lengths, H, Dh = [4096, 130], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=5)
+  leaves = [t.float().requires_grad_() for t in (q, k, v)] + [pos_w.clone().requires_grad_(), ts_w.clone().requires_grad_()]
+  ref = A.jagged_attention_reference(leaves[0], leaves[1], leaves[2], offs, N, pos_w=leaves[3], ts_w=leaves[4], timestamps=ts)
+  go = torch.randn(ref.shape, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+  ref.backward(go.float())
+  gl = [t.cuda().requires_grad_() for t in (q, k, v)] + [pos_w.cuda().requires_grad_(), ts_w.cuda().requires_grad_()]
+  out = A.jagged_pointwise_attention(gl[0], gl[1], gl[2], offs.cuda(), N, pos_w=gl[3], ts_w=gl[4], timestamps=ts.cuda())
+  out.backward(go.cuda())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  _compare(ref.detach(), out.detach(), 2e-2, "out")
+  for name, a, b in zip("q k v pos_w ts_w".split(), gl, leaves):
+    _compare(b.grad, a.grad, 3e-2, name)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_window_and_segment_masks_in_the_kernel(causal):
+  lengths, H, Dh = [300, 129, 64], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=7)
+  g = torch.Generator().manual_seed(1)
+  seg = torch.cat([torch.sort(torch.randint(0, 3, (L,), generator=g)).values for L in lengths]).to(torch.int32)
+  kw = dict(causal=causal, sliding_window_size=37)
+  leaves = [t.float().requires_grad_() for t in (q, k, v)]
+  ref = A.jagged_attention_reference(*leaves, offs, N, pos_w=pos_w, ts_w=ts_w, timestamps=ts, segment_ids=seg, **kw)
+  go = torch.randn(ref.shape, generator=g).to(torch.bfloat16)
+  ref.backward(go.float())
+  gl = [t.cuda().requires_grad_() for t in (q, k, v)]
+  out = A.jagged_pointwise_attention(*gl, offs.cuda(), N, pos_w=pos_w.cuda(), ts_w=ts_w.cuda(), timestamps=ts.cuda(),
+                                     segment_ids=seg.cuda(), **kw)
+  out.backward(go.cuda())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  _compare(ref.detach(), out.detach(), 2e-2, "out")
+  for name, a, b in zip("qkv", gl, leaves):
+    _compare(b.grad, a.grad, 3e-2, name)
+
+
+def test_bias_tables_shared_by_two_layers_get_the_summed_gradient():
+  """Two attention calls of one step use the same tables (as the layers of a model do): the step's bias tiles are
+  built once, and the tables' gradients, returned by the backward call that runs last, are the sum over both."""
+  lengths, H, Dh = [200, 90], 2, 64
+  q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=11)
+  q2 = (q.float() * 0.7).to(torch.bfloat16)
+  lp, lt = pos_w.clone().requires_grad_(), ts_w.clone().requires_grad_()
+  r1 = A.jagged_attention_reference(q.float(), k.float(), v.float(), offs, N, pos_w=lp, ts_w=lt, timestamps=ts)
+  r2 = A.jagged_attention_reference(q2.float(), k.float(), v.float(), offs, N, pos_w=lp, ts_w=lt, timestamps=ts)
+  go = torch.randn(r1.shape, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+  (r1 * go.float()).sum().add((r2 * go.float()).sum() * 0.5).backward()
+  gp, gt = pos_w.cuda().requires_grad_(), ts_w.cuda().requires_grad_()
+  o, tsg = offs.cuda(), ts.cuda()
+  o1 = A.jagged_pointwise_attention(q.cuda(), k.cuda(), v.cuda(), o, N, pos_w=gp, ts_w=gt, timestamps=tsg)
+  o2 = A.jagged_pointwise_attention(q2.cuda(), k.cuda(), v.cuda(), o, N, pos_w=gp, ts_w=gt, timestamps=tsg)
+  ((o1.float() * go.cuda().float()).sum() + (o2.float() * go.cuda().float()).sum() * 0.5).backward()
+  torch.cuda.synchronize()
+  _lib.check_status()
+  _compare(lp.grad, gp.grad, 3e-2, "pos_w")
+  _compare(lt.grad, gt.grad, 3e-2, "ts_w")
+
+
+def test_dense_hstu_runs_on_the_packed_kernels_and_matches_the_dense_formulation():
+  """`HSTU.forward(ids, padding_mask)` on CUDA goes through the packed attention kernels (head dim 64); on CPU the
+  same module evaluates the dense `[B, L, L]` formulation.  Same weights, same inputs: same outputs at the valid
+  positions, same gradients."""
+  from recml_b200.layers import hstu as H
+  torch.manual_seed(0)
+  B, L, V = 3, 160, 50
+  model = H.HSTU(vocab_size=V, max_positions=L, model_dim=128, num_heads=2, num_layers=2, add_head=False,
+                 use_relative_bias=True, max_seq_len=L)
+  ids = torch.randint(1, V, (B, L))
+  lens = torch.tensor([160, 97, 5])
+  mask = (torch.arange(L)[None] < lens[:, None]).long()
+  ts = torch.cumsum(torch.randint(1, 5000, (B, L)), dim=1)
+  ref = model(ids, padding_mask=mask, timestamps=ts)
+  w = torch.randn(B, L, 128) * mask[..., None]
+  (ref * w).sum().backward()
+  ref_grads = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+  model.zero_grad()
+  gm = model.cuda()
+  assert gm._packed_kernels_apply(torch.empty(B, L, 128, device="cuda"))
+  out = gm(ids.cuda(), padding_mask=mask.cuda(), timestamps=ts.cuda())
+  (out.float() * w.cuda()).sum().backward()
+  torch.cuda.synchronize()
+  _lib.check_status()
+  m3 = mask[..., None].bool()
+  _compare((ref * m3).detach(), (out.float().cpu() * m3).detach(), 4e-2, "hidden states")
+  for n, p in gm.named_parameters():
+    if n in ref_grads and ref_grads[n].abs().max() > 0:
+      _compare(ref_grads[n], p.grad, 8e-2, n)
