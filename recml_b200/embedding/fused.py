@@ -143,6 +143,12 @@ class FusedBackend:
     self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
     self.fwd_tiled = os.environ.get("RECML_EMB_FWD_TILED", "1") != "0"
     self.dropped = torch.zeros(1, dtype=torch.int32, device=module.device) if module.config.allow_id_dropping else None
+    # lookups that may be in flight before their update runs: 1 for the ordinary step; 2 under software
+    # pipelining (`training/pipeline.py`), where lookup(i + 1) precedes update(i).  Each in-flight lookup has
+    # its own occurrence list, and sequence numbers are launch-time literals (the device-side counter, which
+    # exists for CUDA-graph replay, would have moved on by the time a delayed backward reads it).
+    self.pipeline_depth = 1
+    self._train_calls = 0
     self._hp_slot = 0
     from recml_b200.utils import graphs
     graphs.register(self)
@@ -162,6 +168,14 @@ class FusedBackend:
 
   def graph_pre_replay(self) -> None:
     self._push_hyper()
+
+  def set_pipeline_depth(self, depth: int) -> None:
+    if self._occ_ready_flag():
+      raise RuntimeError("set the pipeline depth before the first training lookup")
+    self.pipeline_depth = int(depth)
+
+  def _occ_ready_flag(self) -> bool:
+    return bool(getattr(self, "_occ_ready", False))
 
   # -- row-optimizer hyper-parameters live on the device (a replayed graph follows a schedule) -----------
   HP_RING = 256
@@ -242,7 +256,6 @@ class FusedBackend:
           continue
         names.append(fname)
       info: dict[str, Any] = {"n_feats": len(names), "feat_names": names, "descs": {}}
-      info["count"] = torch.zeros(1, dtype=torch.int32, device=dev)
       info["done"] = torch.zeros(4, dtype=torch.int32, device=dev)
       self.stacks.append(info)
     self.combine_dev = _device_struct_array(self.combine_descs, dev)
@@ -330,15 +343,18 @@ class FusedBackend:
         cap += n
       cap = int(cap * self.capacity_factor) + 1024
       info["occ_cap"] = cap
-      info["keys"] = torch.empty(2, cap, dtype=torch.int32, device=dev)
-      info["vals"] = torch.empty(2, cap, dtype=torch.int32, device=dev)
-      info["gain"] = torch.empty(cap, 2, dtype=torch.float32, device=dev) if self.has_gains else None
+      # one occurrence list per lookup that can be in flight; `sorted` says which of the two (keys, vals)
+      # buffers of a set holds the sorted list
+      info["sets"] = [dict(keys=torch.empty(2, cap, dtype=torch.int32, device=dev),
+                           vals=torch.empty(2, cap, dtype=torch.int32, device=dev),
+                           gain=torch.empty(cap, 2, dtype=torch.float32, device=dev) if self.has_gains else None,
+                           count=torch.zeros(1, dtype=torch.int32, device=dev), sorted=0)
+                      for _ in range(self.pipeline_depth)]
       dloc = m.plan.stacks[si].dim
       info["scratch"] = torch.zeros((cap + 127) // 128, dloc, dtype=torch.float32, device=dev)
       words = int(self.lib.recml_radix_sort_scratch_words(c_ll(cap)))
       info["sort_scratch"] = torch.empty(words, dtype=torch.int32, device=dev)
       info["key_bits"] = max(1, int(max(m.plan.stacks[si].rows, 1) - 1).bit_length())
-      info["sorted"] = 0     # which of the two (keys, vals) buffers holds the sorted list
     self._occ_ready = True
     self._push_hyper()
 
@@ -368,7 +384,11 @@ class FusedBackend:
     par = (self.seq & 1) if W > 1 else 0
     st = _lib.stream()
     _lib.check_rc(self.lib.recml_tick(_lib.ptr(self.seq_dev), st), "tick")
-    seq = SeqRef(self.seq_dev.data_ptr(), 1, 0, 0)
+    seq = SeqRef(self.seq_dev.data_ptr(), 1, 0, 0) if self.pipeline_depth == 1 else SeqRef(None, 0, 0, self.seq)
+    oset = 0
+    if training:
+      oset = self._train_calls % self.pipeline_depth
+      self._train_calls += 1
     gains = self.has_gains
     B = self.B
     if out is None:
@@ -404,8 +424,9 @@ class FusedBackend:
       ids.values[0], ids.offsets[0] = kjt.values.data_ptr(), kjt.offsets.data_ptr()
       ids.weights[0] = kjt.weights.data_ptr() if kjt.weights is not None else None
     for si, info in enumerate(self.stacks):
+      occ = info["sets"][oset] if training else None
       if training:
-        info["count"].zero_()
+        occ["count"].zero_()
       fp = FwdParams()
       fp.ids = ids
       fp.feats, fp.n_feats = self._feat_descs(si, direct).data_ptr(), info["n_feats"]
@@ -416,9 +437,9 @@ class FusedBackend:
         fp.flags[r] = self._flag_ptr(r, 1 + si, m.rank)
       fp.grad_ld = direct[0] if direct is not None else 0
       if training:
-        fp.occ_key, fp.occ_val = info["keys"][0].data_ptr(), info["vals"][0].data_ptr()
-        fp.occ_gain = info["gain"].data_ptr() if gains else None
-        fp.occ_count, fp.occ_cap = info["count"].data_ptr(), info["occ_cap"]
+        fp.occ_key, fp.occ_val = occ["keys"][0].data_ptr(), occ["vals"][0].data_ptr()
+        fp.occ_gain = occ["gain"].data_ptr() if gains else None
+        fp.occ_count, fp.occ_cap = occ["count"].data_ptr(), info["occ_cap"]
         fp.dropped = self.dropped.data_ptr() if self.dropped is not None else None
       fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
       fp.prefetch = self.fwd_prefetch
@@ -428,12 +449,12 @@ class FusedBackend:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
                       "emb_fwd")
     if training:
-      self._sort_occurrences()
+      self._sort_occurrences(oset)
     odt = m.config.output_dtype or torch.bfloat16
     if direct is not None:
       res = out[:, out_col:out_col + self.width]
       res = res if odt == torch.bfloat16 else res.to(odt)
-      return res, ({"seq": seq, "par": par, "kjt": kjt, "direct": direct} if training else None)
+      return res, ({"seq": seq, "par": par, "kjt": kjt, "direct": direct, "set": oset} if training else None)
     cp = CombineParams()
     cp.pooled = self.buf.peer_ptr(m.rank, self.pooled_off[par])
     cp.feats, cp.n_feats, cp.B = self.combine_dev.data_ptr(), len(self.combine_descs), B
@@ -444,10 +465,10 @@ class FusedBackend:
     _lib.check_rc(self.lib.recml_emb_combine(ctypes.byref(cp), st), "emb_combine")
     res = out[:, out_col:out_col + self.width]
     res = res if odt == torch.bfloat16 else res.to(odt)
-    saved = {"seq": seq, "par": par, "kjt": kjt, "direct": None} if training else None
+    saved = {"seq": seq, "par": par, "kjt": kjt, "direct": None, "set": oset} if training else None
     return res, saved
 
-  def _sort_occurrences(self) -> None:
+  def _sort_occurrences(self, oset: int = 0) -> None:
     """Groups the step's occurrence list by row.  The list is complete once the forward kernels have run
     and nothing else of the forward pass needs the result, so the sort goes to a side stream and runs
     beside the dense forward; the backward waits for it."""
@@ -459,14 +480,15 @@ class FusedBackend:
         n = info["occ_cap"]
         if n <= 0 or info["n_feats"] == 0:
           continue
+        occ = info["sets"][oset]
         rc = self.lib.recml_radix_sort_pairs(
-            _lib.ptr(info["keys"][0]), _lib.ptr(info["vals"][0]), _lib.ptr(info["keys"][1]),
-            _lib.ptr(info["vals"][1]), _lib.ptr(info["count"]), c_ll(n), c_int(info["key_bits"]),
+            _lib.ptr(occ["keys"][0]), _lib.ptr(occ["vals"][0]), _lib.ptr(occ["keys"][1]),
+            _lib.ptr(occ["vals"][1]), _lib.ptr(occ["count"]), c_ll(n), c_int(info["key_bits"]),
             _lib.ptr(info["sort_scratch"]), _lib.ptr(self.status), st)
         if rc < 0:
           raise _lib.NativeError(f"radix sort failed with code {rc}")
         _lib.LAUNCHES["count"] += 4 * ((info["key_bits"] + 8) // 9) - 1    # four kernels per pass
-        info["sorted"] = rc
+        occ["sorted"] = rc
 
   # -- backward ----------------------------------------------------------------------------------------------
   @torch.no_grad()
@@ -522,11 +544,12 @@ class FusedBackend:
       # synchronises with the host.
       n = info["occ_cap"]
       opt = m.plan.stacks[si].optimizer
-      srt = info["sorted"]
+      occ = info["sets"][saved.get("set", 0)]
+      srt = occ["sorted"]
       bp = BwdParams()
-      bp.keys, bp.vals = info["keys"][srt].data_ptr(), info["vals"][srt].data_ptr()
-      bp.occ_gain = info["gain"].data_ptr() if self.has_gains else None
-      bp.n_occ = info["count"].data_ptr()
+      bp.keys, bp.vals = occ["keys"][srt].data_ptr(), occ["vals"][srt].data_ptr()
+      bp.occ_gain = occ["gain"].data_ptr() if self.has_gains else None
+      bp.n_occ = occ["count"].data_ptr()
       bp.grads = grads_ptr
       bp.val_scale = val_scale if val_scale is not None else m.plan.stacks[si].dim
       bp.table = m.stack_weights[si].data_ptr()

@@ -21,8 +21,9 @@ for the first call).  `finalize()` runs the two drain steps and returns the last
 `ShardedEmbedding`: the lookup keeps the autograd node of the embedding output, the dense stage
 works on a detached copy and the update stage feeds the copy's gradient into that node, which runs
 the exchange + row-optimizer kernels.  Two lookups are in flight before the first update, so the
-embedding backend must keep per-call state: the collective backend does; the fused NVLink backend
-keeps ONE occurrence list per stack and is refused.
+embedding backend must keep per-call state: the collective backend does by construction; the fused
+NVLink backend is switched to two occurrence lists per table stack and launch-time sequence numbers
+(`FusedBackend.set_pipeline_depth(2)`, done here before its first lookup).
 """
 from __future__ import annotations
 
@@ -111,9 +112,8 @@ def for_sharded_embedding(embedding, dense_fn: Callable[[torch.Tensor, Any], tup
   activations that require grad, and their `.grad` after it returns is what the update stage
   pushes to the table owners."""
   backend = getattr(embedding, "_backend", None)
-  if type(backend).__name__ == "FusedBackend":
-    raise ValueError("software pipelining keeps two lookups in flight; the fused backend holds one occurrence "
-                     "list per stack — build the embedding with backend='collective' to pipeline it")
+  if hasattr(backend, "set_pipeline_depth") and backend.pipeline_depth < 2:
+    backend.set_pipeline_depth(2)
 
   def lookup(batch):
     with torch.enable_grad():

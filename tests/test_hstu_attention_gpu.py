@@ -159,25 +159,23 @@ def test_non_causal_with_bias_matches_reference():
     assert err / (b.grad.abs().max().item() + 1e-6) < 3e-2, (name, err)
 
 
-@pytest.mark.parametrize("causal", [True, False])
-def test_bucket_cache_equals_inline_buckets(causal, monkeypatch):
-  """Cached bucket indices and buckets computed in the kernel come from the same function: forward outputs
-  and dk / dv agree exactly, the atomically accumulated gradients to rounding."""
+def test_step_context_is_shared_and_rebuilt_when_a_table_changes():
+  """Calls with the same batch and tables share one bias context (tiles built once); changing a table in place
+  (what an optimizer step does) gives a new one."""
   from recml_b200.ops import hstu_cuda
   lengths, H, Dh = [300, 17, 260], 2, 64
   q, k, v, offs, N, pos_w, ts_w, ts = _inputs(lengths, H, Dh, seed=7)
-  go = torch.randn(sum(lengths), H, Dh, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+  o, tsg, pw, tw = offs.cuda(), ts.cuda(), pos_w.cuda(), ts_w.cuda()
   hstu_cuda._memo.clear()
-  out_c, g_c = _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, causal, go)
-  assert "buckets" in hstu_cuda._memo
-  monkeypatch.setattr(hstu_cuda, "BUCKET_CACHE_MAX_BYTES", 0)
-  hstu_cuda._memo.clear()
-  out_i, g_i = _run_cuda(q, k, v, offs, N, pos_w, ts_w, ts, causal, go)
-  assert "buckets" not in hstu_cuda._memo
-  assert torch.equal(out_c, out_i)
-  assert torch.equal(g_c[1], g_i[1]) and torch.equal(g_c[2], g_i[2])
-  for a, b in zip(g_c, g_i):
-    torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
+  out1 = A.jagged_pointwise_attention(q.cuda(), k.cuda(), v.cuda(), o, N, pos_w=pw, ts_w=tw, timestamps=tsg)
+  ctx1 = hstu_cuda._memo["bias_ctx"][2]
+  out2 = A.jagged_pointwise_attention(q.cuda(), k.cuda(), v.cuda(), o, N, pos_w=pw, ts_w=tw, timestamps=tsg)
+  assert hstu_cuda._memo["bias_ctx"][2] is ctx1 and torch.equal(out1, out2)
+  pw.add_(0.25)
+  out3 = A.jagged_pointwise_attention(q.cuda(), k.cuda(), v.cuda(), o, N, pos_w=pw, ts_w=tw, timestamps=tsg)
+  assert hstu_cuda._memo["bias_ctx"][2] is not ctx1 and not torch.equal(out1, out3)
+  torch.cuda.synchronize()
+  _lib.check_status()
 
 
 def _compare(ref, got, tol, what):
