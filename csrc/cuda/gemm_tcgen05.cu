@@ -21,6 +21,8 @@
 //
 // Every wait is bounded (see common.cuh); on expiry the CTA drains and frees its tensor
 // memory before returning, and the launcher's status word is set.
+#include <cstdlib>
+
 #include "tcgen05.cuh"
 
 namespace recml {
@@ -529,7 +531,15 @@ extern "C" int recml_gemm_bf16(const void* a, int lda, int a_mn, const void* b, 
     while (split_k > 1 && ((kb + split_k - 1) / split_k) * (split_k - 1) >= kb) --split_k;
     p.split_k = split_k > 1 ? split_k : 1;
   }
-  const bool wide = N > 128;
+  // Tile width: 256 columns amortise the operand traffic of long-K products; products whose epilogue streams
+  // auxiliary operands through the tile (cross / add / mask epilogues) are bound by that epilogue when K is
+  // short, and then twice as many half-width tiles keep more of it in flight and balance the last wave.
+  static const int forced_bn = [] { const char* e = getenv("RECML_GEMM_BN"); return e ? atoi(e) : 0; }();
+  bool wide = N > 128;
+  if (wide && epi != kEpiLinear && !out_f32 && K <= 1024 &&
+      static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256) < 8LL * sm_count()) wide = false;
+  if (forced_bn == 128) wide = false;
+  if (forced_bn == 256) wide = N > 128;
   if (!a_mn && !b_mn) return wide ? launch<256, false, false>(a, lda, b, ldb, p, stream)
                                   : launch<128, false, false>(a, lda, b, ldb, p, stream);
   if (!a_mn && b_mn) return wide ? launch<256, false, true>(a, lda, b, ldb, p, stream)

@@ -52,6 +52,7 @@ def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("case")
   ap.add_argument("--iters", type=int, default=5)
+  ap.add_argument("--rows", type=int, default=32768, help="M of the gemm_* cases")
   args = ap.parse_args()
   from recml_b200.ops import _lib, gemm as G
   hbm, tf, tag = peaks()
@@ -59,7 +60,7 @@ def main():
   out = {"case": args.case}
   c = args.case
   if c.startswith("gemm"):
-    M, N, K = 32768, 1024, 3456
+    M, N, K = args.rows, 1024, 3456
     if c == "gemm_fwd":
       a, b = rnd(M, K), rnd(N, K)
       bias = torch.randn(N, device="cuda")

@@ -46,7 +46,8 @@ class SeqRef(ctypes.Structure):
 class FeatDesc(ctypes.Structure):
   _fields_ = [("feat_index", c_int), ("kind", c_int), ("owner", c_int), ("rot", c_int), ("row_base", c_int),
               ("combiner", c_int), ("dim", c_int), ("col_lo", c_int), ("slot_off", c_ll), ("grad_off", c_ll),
-              ("seq_len", c_int), ("dst_stride", c_int), ("vocab", c_int), ("pad", c_int)]
+              ("seq_len", c_int), ("dst_stride", c_int), ("vocab", c_int), ("tile_shift", c_int),
+              ("tile_start", c_ll)]
 
 
 class IdPtrs(ctypes.Structure):
@@ -58,7 +59,7 @@ class FwdParams(ctypes.Structure):
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
               ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
               ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp), ("dropped", c_vp),
-              ("prefetch", c_int), ("tiled", c_int)]
+              ("prefetch", c_int), ("tiled", c_int), ("total_tiles", c_ll)]
 
 
 class CombineDesc(ctypes.Structure):
@@ -86,7 +87,7 @@ class BwdParams(ctypes.Structure):
               ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
               ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
               ("wait_flags", c_vp), ("W", c_int), ("seq", SeqRef), ("status", c_vp), ("hp_dev", c_vp),
-              ("n_cap", c_uint), ("pad", c_int)]
+              ("n_cap", c_uint), ("rowq", c_int)]
 
 
 class PushIdsParams(ctypes.Structure):
@@ -137,8 +138,9 @@ class FusedBackend:
     self.B = None
     self.status = _lib.status_buffer(m.device)
     # resident 128-thread blocks per SM of the backward update kernel: 0 = fill the GPU; a model that runs
-    # weight-gradient GEMMs beside the embedding backward sets 3 so that a GEMM CTA fits on every SM
+    # weight-gradient GEMMs beside the embedding backward sets -1 so that a GEMM CTA fits on every SM
     self.bwd_blocks_per_sm = int(os.environ.get("RECML_EMB_BWD_BLOCKS", "0"))
+    self.bwd_rowq = int(os.environ.get("RECML_EMB_ROWQ", "0"))
     self.side_streams = os.environ.get("RECML_EMB_STREAMS", "1") != "0"
     self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
     self.fwd_tiled = os.environ.get("RECML_EMB_FWD_TILED", "1") != "0"
@@ -209,6 +211,10 @@ class FusedBackend:
     self.B = B
     F = len(m.feature_names)
     self.n_offsets = F * B + 1
+    # ids per bag of every feature in this first batch (one small read-back at set-up): sizes the forward's tiles
+    bounds = kjt.offsets[::B].to(torch.int64).cpu().tolist() if kjt.offsets.numel() == F * B + 1 else None
+    self._avg_bag = ({f: (bounds[i + 1] - bounds[i]) / max(B, 1) for i, f in enumerate(m.feature_names)}
+                     if bounds is not None and len(bounds) == F + 1 else {})
     nnz_cap = int(kjt.values.numel() * self.capacity_factor) + 1024
     if W > 1:  # all ranks must agree on the layout
       import torch.distributed as dist
@@ -309,6 +315,7 @@ class FusedBackend:
     if direct not in info["descs"]:
       m = self.m
       feats = []
+      tiles = 0
       for fname, col, width, L in self.layout:
         if fname not in info["feat_names"]:
           continue
@@ -319,9 +326,16 @@ class FusedBackend:
           slot, goff, stride = out_col + col, out_col + col, ld
         else:
           slot, goff, stride = self.slot_off[fname], self.grad_off[m.rank][fname], width
+        # bags per warp of the tiled forward: a few hundred ids per tile whatever the bag size
+        avg = self._avg_bag.get(fname, 1.0) * (1.0 if tp.placement is not Placement.ROW_WISE else 1.0)
+        shift = 5 if avg <= 8 else 4 if avg <= 16 else 3 if avg <= 32 else 2 if avg <= 64 else 1
+        bpt = 1 << shift
         feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
-                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot, goff, L, stride, tp.vocab, 0))
+                              tp.row_base, COMBINER[spec.combiner], tp.dim, tp.col_lo, slot, goff, L, stride, tp.vocab,
+                              shift, tiles))
+        tiles += m.world * ((self.B + bpt - 1) // bpt)
       info["descs"][direct] = _device_struct_array(feats, m.device)
+      info["tiles"] = tiles
     return info["descs"][direct]
 
   def _ensure_occ(self, kjt):
@@ -444,6 +458,7 @@ class FusedBackend:
       fp.wait_flags = self._flag_ptr(m.rank, 0, 0) if W > 1 else None
       fp.prefetch = self.fwd_prefetch
       fp.tiled = int(self.fwd_tiled and all(L == 0 for f_, _, _, L in self.layout if f_ in info["feat_names"]))
+      fp.total_tiles = info.get("tiles", 0)
       fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),
@@ -567,6 +582,7 @@ class FusedBackend:
       bp.W, bp.seq, bp.status = W, seq, self.status.data_ptr()
       bp.hp_dev = self._hp_dev[si].data_ptr()
       bp.n_cap = n
+      bp.rowq = self.bwd_rowq
       if n > 0 or W > 1:
         _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),
                                                     c_int(self.bwd_blocks_per_sm), st), "emb_bwd_update")

@@ -58,7 +58,7 @@ class DLRMDCNv2(nn.Module):
       self.top.defer_wgrad = True
       backend_obj = getattr(self.embedding, "_backend", None)
       if hasattr(backend_obj, "bwd_blocks_per_sm") and backend_obj.bwd_blocks_per_sm == 0:
-        backend_obj.bwd_blocks_per_sm = 3
+        backend_obj.bwd_blocks_per_sm = -1
 
   def forward(self, dense_x: torch.Tensor, sparse: emb.KeyedJagged) -> torch.Tensor:
     if dense_x.is_cuda:
