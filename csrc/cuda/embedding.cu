@@ -673,7 +673,7 @@ struct BwdParams {
   const float* hp_dev;          // non-null: the six hyper-parameters are read from device memory (so that a
                                 // captured CUDA graph follows a learning-rate schedule) instead of `hp`
   unsigned int n_cap;           // >0: *n_occ is clamped to this (capacity of the occurrence list)
-  int rowq;                     // 1: SGD / row-wise Adagrad take the register-queue kernel
+  int reserved;
 };
 
 __device__ __forceinline__ float hpv(const BwdParams& p, int i) {
@@ -936,156 +936,6 @@ __global__ void __launch_bounds__(kBwdThreads, 8) emb_bwd_update_kernel(const Bw
   }
 }
 
-// The same walk for the two optimizers whose state is at most one scalar per row (SGD, row-wise Adagrad),
-// which is what large tables train with.  Applying a row is a chain of dependent memory operations (load
-// the row, reduce, store), and a range of 128 occurrences of a long-tailed id distribution ends dozens of
-// runs; with few resident warps (the kernel shares the SMs with GEMMs) those chains, one after the other,
-// are what the kernel's duration consists of.  Here the warp parks up to kQueue reduced gradients in
-// registers and applies them together, all row loads issued before the first is used.  The queue is emptied
-// between batches of gradient loads (when the runs ending in the next batch might not fit), so the code that
-// applies it exists once.  At most 80 registers: two blocks fit beside a GEMM CTA.
-constexpr int kQueue = 4;
-
-template <int VPL, bool GAINS>
-__global__ void __maxnreg__(80) emb_bwd_update_rowq_kernel(const BwdParams p) {
-  if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 2)) return;
-  const int lane = threadIdx.x & 31;
-  const unsigned int n = occ_count_of(p);
-  const unsigned int warps = (gridDim.x * blockDim.x) >> 5;
-  const bool lane_on = lane * VPL < p.dloc;
-  const int grad_bytes = p.dloc * 2, row_bytes = p.dloc * 4;
-  const bool adagrad = p.opt == kRowAdagrad;
-  const float lr = hpv(p, 0), eps = hpv(p, 1), inv_d = 1.f / p.dloc;
-  constexpr int kBatch = kQueue;
-  for (unsigned int range = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; range * kRange < n; range += warps) {
-    const unsigned int start = range * kRange;
-    const unsigned int end = min(start + kRange, n);
-    const bool has_prev = start > 0, has_next = end < n;
-    const uint32_t prev_key = has_prev ? p.keys[start - 1] : 0;
-    const uint32_t next_key = has_next ? p.keys[end] : 0;
-    Vec<VPL> acc;
-#pragma unroll
-    for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-    bool first_run = true;
-    // parked rows: slot u's reduced gradient is gq[u] (every lane holds its VPL columns), its row id sits in lane u
-    Vec<VPL> gq[kQueue];
-    uint32_t rowq = 0;
-    int q = 0;
-    auto flush = [&]() {
-      Vec<VPL> wq[kQueue];
-#pragma unroll
-      for (int u = 0; u < kQueue; ++u) {
-        const uint32_t row = __shfl_sync(0xffffffffu, rowq, u);
-        if (u < q && lane_on) wq[u] = load_f32_rw<VPL>(p.table + static_cast<size_t>(row) * p.dloc + lane * VPL);
-      }
-      float s_mine = 0.f;
-      if (adagrad && lane < q) s_mine = p.slot0[rowq];
-#pragma unroll
-      for (int u = 0; u < kQueue; ++u) {
-        if (u >= q) break;
-        const uint32_t row = __shfl_sync(0xffffffffu, rowq, u);
-        float sq = 0.f;
-#pragma unroll
-        for (int e = 0; e < VPL; ++e) {
-          gq[u].v[e] *= p.grad_scale;
-          if (lane_on) sq += gq[u].v[e] * gq[u].v[e];
-        }
-        float step = lr;
-        if (adagrad) {
-          const float s = __shfl_sync(0xffffffffu, s_mine, u) + warp_sum(sq) * inv_d;
-          if (lane == u) s_mine = s;
-          step = lr / (sqrtf(s) + eps);
-        }
-        if (lane_on) {
-#pragma unroll
-          for (int e = 0; e < VPL; ++e) wq[u].v[e] -= step * gq[u].v[e];
-          store_f32<VPL>(p.table + static_cast<size_t>(row) * p.dloc + lane * VPL, wq[u]);
-        }
-      }
-      if (adagrad && lane < q) p.slot0[rowq] = s_mine;
-      q = 0;
-    };
-    uint32_t key = 0xffffffffu; unsigned int gv = 0; float gain = 1.f;
-    auto fetch = [&](unsigned int w0, uint32_t& k, unsigned int& g, float& gn) {
-      k = 0xffffffffu; g = 0; gn = 1.f;
-      if (w0 + lane < end) {
-        k = p.keys[w0 + lane];
-        const uint32_t val = p.vals[w0 + lane];
-        g = val;
-        if (GAINS) {
-          g = __float_as_uint(p.occ_gain[2 * static_cast<size_t>(val)]);
-          gn = p.occ_gain[2 * static_cast<size_t>(val) + 1];
-        }
-        prefetch_l2(p.grads + static_cast<size_t>(g) * p.val_scale, grad_bytes);
-      }
-    };
-    fetch(start, key, gv, gain);
-    for (unsigned int w0 = start; w0 < end; w0 += 32u) {
-      const int cnt = static_cast<int>(min(32u, end - w0));
-      const bool window_is_last = w0 + cnt >= end;
-      uint32_t nkey = 0xffffffffu; unsigned int ngv = 0; float ngain = 1.f;
-      if (!window_is_last) fetch(w0 + 32u, nkey, ngv, ngain);
-      const uint32_t after = __shfl_sync(0xffffffffu, nkey, 0);
-      uint32_t knext = __shfl_down_sync(0xffffffffu, key, 1);
-      if (lane == cnt - 1) knext = after;
-      const bool ends_run = lane < cnt && ((window_is_last && lane == cnt - 1) || knext != key);
-      const unsigned int last_mask = __ballot_sync(0xffffffffu, ends_run);
-      if (ends_run) {
-        prefetch_l2(p.table + static_cast<size_t>(key) * p.dloc, row_bytes);
-        if (adagrad) prefetch_l2(p.slot0 + key, 4);
-      }
-#pragma unroll 1
-      for (int j0 = 0; j0 < cnt; j0 += kBatch) {
-        // runs that end inside this batch (at most kBatch = kQueue): make room for them first
-        if (q + __popc((last_mask >> j0) & ((1u << kBatch) - 1u)) > kQueue) flush();
-        RawBf16<VPL> g[kBatch]; float gj[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-          const int j = min(j0 + u, cnt - 1);
-          const unsigned int gvj = __shfl_sync(0xffffffffu, gv, j);
-          gj[u] = GAINS ? __shfl_sync(0xffffffffu, gain, j) : 1.f;
-          if (lane_on && j0 + u < cnt)
-            g[u] = load_raw_bf16<VPL>(p.grads + static_cast<size_t>(gvj) * p.val_scale + lane * VPL);
-        }
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-          const int j = j0 + u;
-          if (j >= cnt) break;
-          if (lane_on) fma_raw_bf16<VPL>(acc, gj[u], g[u]);
-          if (!((last_mask >> j) & 1u)) continue;
-          const uint32_t kj = __shfl_sync(0xffffffffu, key, j);
-          const bool at_range_end = window_is_last && j == cnt - 1;
-          const bool begins = !first_run || !has_prev || (prev_key != kj);
-          const bool ends = !at_range_end || !has_next || (next_key != kj);
-          if (begins && ends) {
-#pragma unroll
-            for (int s = 0; s < kQueue; ++s)
-              if (q == s) gq[s] = acc;
-            if (lane == q) rowq = kj;
-            ++q;
-          } else {
-            unsigned int slot = range;
-            if (!begins) {
-              if (lane == 0) slot = lower_bound(p.keys, start, kj) / kRange;
-              slot = __shfl_sync(0xffffffffu, slot, 0);
-            }
-            if (lane_on) {
-              float* sp = p.scratch + static_cast<size_t>(slot) * p.dloc + lane * VPL;
-#pragma unroll
-              for (int e = 0; e < VPL; ++e) atomicAdd(sp + e, acc.v[e]);
-            }
-          }
-#pragma unroll
-          for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
-          first_run = false;
-        }
-      }
-      key = nkey; gv = ngv; gain = ngain;
-    }
-    if (q > 0) flush();
-  }
-}
-
 template <int VPL>
 __global__ void __launch_bounds__(256) emb_bwd_finalize_kernel(const BwdParams p) {
   const int lane = threadIdx.x & 31;
@@ -1208,9 +1058,8 @@ extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int g
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool rowq = (p->opt == kSGD || p->opt == kRowAdagrad) && p->rowq != 0;
-  if (blocks_per_sm < 0) blocks_per_sm = rowq ? 2 : 3;
-  if (blocks_per_sm == 0) blocks_per_sm = rowq ? 6 : 8;
+  if (blocks_per_sm < 0) blocks_per_sm = 3;      // what fits beside a resident GEMM CTA
+  if (blocks_per_sm == 0) blocks_per_sm = 8;
   long long want = (ranges + (kBwdThreads / 32) - 1) / (kBwdThreads / 32);
   const long long cap = static_cast<long long>(sms) * blocks_per_sm;
   const int blocks = static_cast<int>(want < cap ? want : cap);
@@ -1221,15 +1070,10 @@ extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int g
     if (!configured) {                                                                    \
       recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, true>);                  \
       recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, false>);                 \
-      recml::prefer_max_shared_carveout(emb_bwd_update_rowq_kernel<V, true>);             \
-      recml::prefer_max_shared_carveout(emb_bwd_update_rowq_kernel<V, false>);            \
       recml::prefer_max_shared_carveout(emb_bwd_finalize_kernel<V>);                      \
       configured = true;                                                                  \
     }                                                                                     \
-    if (rowq) {                                                                           \
-      if (gains) emb_bwd_update_rowq_kernel<V, true><<<blocks, kBwdThreads, 0, stream>>>(*p);  \
-      else emb_bwd_update_rowq_kernel<V, false><<<blocks, kBwdThreads, 0, stream>>>(*p);  \
-    } else if (gains) emb_bwd_update_kernel<V, true><<<blocks, kBwdThreads, 0, stream>>>(*p);  \
+    if (gains) emb_bwd_update_kernel<V, true><<<blocks, kBwdThreads, 0, stream>>>(*p);    \
     else emb_bwd_update_kernel<V, false><<<blocks, kBwdThreads, 0, stream>>>(*p);         \
     emb_bwd_finalize_kernel<V><<<fin_blocks, 256, 0, stream>>>(*p);                       \
   } while (0)

@@ -87,7 +87,7 @@ class BwdParams(ctypes.Structure):
               ("table", c_vp), ("slot0", c_vp), ("slot1", c_vp), ("dloc", c_int), ("opt", c_int),
               ("hp", c_float * 6), ("grad_scale", c_float), ("slot1_rowwise", c_int), ("scratch", c_vp),
               ("wait_flags", c_vp), ("W", c_int), ("seq", SeqRef), ("status", c_vp), ("hp_dev", c_vp),
-              ("n_cap", c_uint), ("rowq", c_int)]
+              ("n_cap", c_uint), ("reserved", c_int)]
 
 
 class PushIdsParams(ctypes.Structure):
@@ -140,7 +140,6 @@ class FusedBackend:
     # resident 128-thread blocks per SM of the backward update kernel: 0 = fill the GPU; a model that runs
     # weight-gradient GEMMs beside the embedding backward sets -1 so that a GEMM CTA fits on every SM
     self.bwd_blocks_per_sm = int(os.environ.get("RECML_EMB_BWD_BLOCKS", "0"))
-    self.bwd_rowq = int(os.environ.get("RECML_EMB_ROWQ", "0"))
     self.side_streams = os.environ.get("RECML_EMB_STREAMS", "1") != "0"
     self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
     self.fwd_tiled = os.environ.get("RECML_EMB_FWD_TILED", "1") != "0"
@@ -582,7 +581,6 @@ class FusedBackend:
       bp.W, bp.seq, bp.status = W, seq, self.status.data_ptr()
       bp.hp_dev = self._hp_dev[si].data_ptr()
       bp.n_cap = n
-      bp.rowq = self.bwd_rowq
       if n > 0 or W > 1:
         _lib.check_rc(self.lib.recml_emb_bwd_update(ctypes.byref(bp), c_ll(max(n, 1)), c_int(int(self.has_gains)),
                                                     c_int(self.bwd_blocks_per_sm), st), "emb_bwd_update")
