@@ -57,7 +57,7 @@ struct Params {
   // softmax mode (SASRec / BERT4Rec blocks): P = softmax over the visible keys instead of SiLU / n.
   // The forward needs the whole key row in tensor memory (max_seq_len <= 256: two score tiles) and
   // writes the row log-sum-exp; the backward reads it back together with delta = rowsum(dO * O).
-  int softmax;
+  int mode;                   // Mode below
   float* lse;                 // [T, H]
   const float* delta;         // [T, H] (backward)
   // row pitch in elements of q / k / v / dO when they are column slices of a wider matrix (0: H * Dh)
@@ -74,7 +74,21 @@ struct Params {
   float* dbias_tiles;         // backward: 16384 fp32 per pair, same order, accumulated with reductions (or null)
   int window;                 // >= 0: query i sees keys i - window .. i + window (intersected with causality)
   const int* segment_ids;     // [T] or null: a query sees only keys of its own segment
+  // Decay mode (the quadratic form of the Mamba2 state-space recurrence): P[l, s] = S[l, s] * 2^(cum[l] - cum[s])
+  // for s <= l, with q = C and k = B shared by all heads ([T, Dh]), v = X [T, H * Dh].
+  const float* cum;           // [H, cum_pitch]: inclusive prefix sums of a * log2(e) along each sequence
+  long long cum_pitch;        // >= T + 128 so that a tile may read past the last token
+  int qk_shared;              // 1: q / k (and dq / dk) have one head that all heads of v share
+  float* dk_acc;              // decay mode: dk accumulated in fp32 [T, Dh] (pre-zeroed) like dq
+  // Gradient w.r.t. the (natural-log) prefix sums, [H, cum_pitch], pre-zeroed:
+  //   dcum[l] = sum_s dP[l, s] P[l, s] - sum_l' dP[l', l] P[l', l]
+  // The row sums are taken where dP and P are formed; the column sums equal x_s . dx_s (dx = P^T dO), taken when dv
+  // is read out.  Both use the bf16-rounded P that the tensor cores saw, so the two halves cancel as they should.
+  float* dcum;
+  const __nv_bfloat16* v_rows;   // v as a plain pointer (row pitch ld_v) for that dot product
 };
+
+enum Mode { kSilu = 0, kSoftmax = 1, kDecay = 2 };
 
 constexpr float kMaskedHalfBias = -15000.f;
 
@@ -124,6 +138,26 @@ __device__ __forceinline__ float tanh_fast(float x) {
   float t;
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
   return t;
+}
+
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 consecutive prefix sums, the same for every lane of the warp: 16-byte loads when the address allows
+__device__ __forceinline__ void load_cum32(const float* src, float (&dst)[32]) {
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(src) + g);
+      dst[4 * g] = t.x; dst[4 * g + 1] = t.y; dst[4 * g + 2] = t.z; dst[4 * g + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) dst[e] = __ldg(src + e);
+  }
 }
 
 // bucket = clip(int(ln(clip(|dt|, 1, 1e9)) / 0.301), 0, num_buckets), with ln taken as log2 * ln(2)
@@ -359,17 +393,18 @@ struct Smem {
   static constexpr int kTmemCols = 512;                // S: 2 x 128 columns, O: DH columns
 };
 
-template <int DH, bool SOFTMAX>
+template <int DH, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
+  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu, DECAY = MODE == kDecay;
   using S = Smem<DH>;
   // CTAs are dispatched in linear block order; heads vary fastest so that this order follows the work-sorted list
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;
   const int tile_id = lin / p.H;
   const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;   // whole CTA leaves before touching barriers or tensor memory
-  if (!SOFTMAX && p.pair_base[seq + 1] > p.cap_pairs) {   // the bias tiles of this sequence do not exist
+  if (SILU && p.pair_base[seq + 1] > p.cap_pairs) {   // the bias tiles of this sequence do not exist
     if (threadIdx.x == 0) report(p.status, kCapacity, 3);
     return;
   }
@@ -411,14 +446,15 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(bar(0), S::kTile);
-      for (int d = 0; d < S::kSub; ++d) tma_load_2d(base + S::kQ + d * 16384, &map_q, h * DH + 64 * d, tok0, bar(0));
+      const int hq = p.qk_shared ? 0 : h * DH;   // column of this head in q / k
+      for (int d = 0; d < S::kSub; ++d) tma_load_2d(base + S::kQ + d * 16384, &map_q, hq + 64 * d, tok0, bar(0));
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         if (!mbar_wait(bar(3 + s), ((j >> 1) & 1) ^ 1, abortp, p.status, 40)) break;
         mbar_expect_tx(bar(1 + s), 2 * S::kTile);
         const int row = seq_start + j * BKV;
         for (int d = 0; d < S::kSub; ++d) {
-          tma_load_2d(base + S::kK + s * S::kTile + d * 16384, &map_k, h * DH + 64 * d, row, bar(1 + s));
+          tma_load_2d(base + S::kK + s * S::kTile + d * 16384, &map_k, hq + 64 * d, row, bar(1 + s));
           tma_load_2d(base + S::kV + s * S::kTile + d * 16384, &map_v, h * DH + 64 * d, row, bar(1 + s));
         }
       }
@@ -471,8 +507,47 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int n_tiles_seq = (L + BQ - 1) / BQ;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    float out_scale = SOFTMAX ? 1.f : p.inv_n;
-    if constexpr (SOFTMAX) {
+    float out_scale = SILU ? p.inv_n : 1.f;
+    if constexpr (DECAY) {
+      // P = S * 2^(cum[l] - cum[s]) below and on the diagonal, 0 above it and for rows past the sequence end
+      const float* cum_h = p.cum + static_cast<size_t>(h) * p.cum_pitch + seq_start;
+      const float cl = cum_h[qi];
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int sb = j & 1;
+        float cs[32];
+        load_cum32(cum_h + j * BKV + cb * 32, cs);
+        if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
+        tc_fence_after();
+        if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
+        {
+          uint32_t v[32];
+          tmem_ld32(tmem_slot + sb * 128 + lane_off + cb * 32, v);
+          uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
+          const int kj0 = j * BKV + cb * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float pr[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int col = g * 8 + 2 * k + u;
+                const bool visible = row_ok && kj0 + col <= qi;
+                pr[u] = visible ? __uint_as_float(v[col]) * exp2_fast(cl - cs[col]) : 0.f;
+              }
+              packed[k] = pack_bf16(pr[0], pr[1]);
+            }
+            const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
+            *reinterpret_cast<uint4*>(row_ptr + chunk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar(7 + sb));
+        fence_async_smem();
+        mbar_arrive(bar(9));
+      }
+    } else if constexpr (SOFTMAX) {
       // Exact softmax over at most two score tiles that are both resident in tensor memory: every warp
       // scans the whole row (all 128 columns of each tile) for the maximum and the sum, then writes
       // only its own 32 columns of P.
@@ -619,17 +694,18 @@ struct SmemB {
   static constexpr int kTmemCols = 512;
 };
 
-template <int DH, bool SOFTMAX>
+template <int DH, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const Params p) {
+  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu, DECAY = MODE == kDecay;
   using S = SmemB<DH>;
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;   // heads fastest: dispatch order = work-sorted list order
   const int tile_id = lin / p.H;
   const int seq = p.tile_seq[tile_id];
   if (seq < 0) return;
-  if (!SOFTMAX && p.pair_base[seq + 1] > p.cap_pairs) {
+  if (SILU && p.pair_base[seq + 1] > p.cap_pairs) {
     if (threadIdx.x == 0) report(p.status, kCapacity, 4);
     return;
   }
@@ -674,8 +750,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(bar(0), 2 * S::kTile);
+      const int hq = p.qk_shared ? 0 : h * DH;
       for (int d = 0; d < S::kSub; ++d) {
-        tma_load_2d(base + S::kK + d * 16384, &map_k, h * DH + 64 * d, seq_start + kv0, bar(0));
+        tma_load_2d(base + S::kK + d * 16384, &map_k, hq + 64 * d, seq_start + kv0, bar(0));
         tma_load_2d(base + S::kV + d * 16384, &map_v, h * DH + 64 * d, seq_start + kv0, bar(0));
       }
       for (int it = 0; it < n_it; ++it) {
@@ -684,7 +761,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_expect_tx(bar(1 + st), 2 * S::kTile);
         const int row = seq_start + (i_first + it) * BQ;
         for (int d = 0; d < S::kSub; ++d) {
-          tma_load_2d(base + S::kQ + st * S::kTile + d * 16384, &map_q, h * DH + 64 * d, row, bar(1 + st));
+          tma_load_2d(base + S::kQ + st * S::kTile + d * 16384, &map_q, hq + 64 * d, row, bar(1 + st));
           tma_load_2d(base + S::kDO + st * S::kTile + d * 16384, &map_do, h * DH + 64 * d, row, bar(1 + st));
         }
       }
@@ -737,8 +814,14 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float hs = 0.5f * p.scale;
     // what multiplies the accumulated dQ: the score scale, and in SiLU mode the 1 / n that P and dS leave out
-    const float dq_scale = SOFTMAX ? p.scale : p.scale * p.inv_n;
+    const float dq_scale = SILU ? p.scale * p.inv_n : p.scale;
     bool ok = true;
+    const float* cum_h = nullptr;
+    float cs[32];
+    if constexpr (DECAY) {
+      cum_h = p.cum + static_cast<size_t>(h) * p.cum_pitch + seq_start;
+      load_cum32(cum_h + kv0 + cb * 32, cs);     // this CTA's keys stay the same for all query tiles
+    }
     for (int it = 0; it < n_it && ok; ++it) {
       const int q0 = (i_first + it) * BQ;
       const int qi = q0 + r;
@@ -746,7 +829,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       float lse_r = 0.f, delta_r = 0.f;
       uint4 hb[4];
       size_t pair_off = 0;
-      if constexpr (SOFTMAX) {
+      float cl = 0.f;
+      if constexpr (DECAY) {
+        cl = cum_h[qi];
+      } else if constexpr (SOFTMAX) {
         if (row_ok) {
           lse_r = p.lse[static_cast<size_t>(seq_start + qi) * p.H + h];
           delta_r = p.delta[static_cast<size_t>(seq_start + qi) * p.H + h];
@@ -761,12 +847,13 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after();
       {
         uint32_t sv[32], dpv[32];
+        float row_acc = 0.f;
         tmem_ld32(tmem_s + lane_off + cb * 32, sv);
         tmem_ld32(tmem_dp + lane_off + cb * 32, dpv);
         uint8_t* prow = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
         uint8_t* drow = base_ptr + S::kDS + (cb >> 1) * 16384 + r * 128;
         float4* dbias = nullptr;
-        if constexpr (!SOFTMAX) {
+        if constexpr (SILU) {
           if (p.dbias_tiles != nullptr)
             dbias = reinterpret_cast<float4*>(p.dbias_tiles + pair_off) + (cb * 4 + quarter) * 8 * 32 + lane;
         }
@@ -781,7 +868,13 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int u = 0; u < 2; ++u) {
               const int col = g * 8 + 2 * k + u;       // within the warp's 32 columns
               const float s_raw = __uint_as_float(sv[col]), dp = __uint_as_float(dpv[col]);
-              if constexpr (SOFTMAX) {
+              if constexpr (DECAY) {
+                // P = S * D, dS = dP * D with D = 2^(cum[l] - cum[s]) on and below the diagonal
+                const bool visible = row_ok && kv0 + cb * 32 + col <= qi;
+                const float dec = visible ? exp2_fast(cl - cs[col]) : 0.f;
+                pr[u] = s_raw * dec;
+                dr[u] = dp * dec;
+              } else if constexpr (SOFTMAX) {
                 const int kj = kv0 + cb * 32 + col;
                 const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
                 // P = exp(x - lse);  dS = P * (dP - delta)
@@ -802,17 +895,23 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             pp[k] = pack_bf16(pr[0], pr[1]);
             dd[k] = pack_bf16(dr[0], dr[1]);
+            if constexpr (DECAY)
+              row_acc = fmaf(__uint_as_float(dpv[g * 8 + 2 * k + 1]), bf16_hi(pp[k]),
+                             fmaf(__uint_as_float(dpv[g * 8 + 2 * k]), bf16_lo(pp[k]), row_acc));
           }
           const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-          if constexpr (!SOFTMAX) {
+          if constexpr (SILU) {
             if (dbias != nullptr) {
               // gradient of the bias: dS / n, summed over heads and layers in the pair's gradient block
               red_add_v4(dbias + (2 * g) * 32, dsv[0] * p.inv_n, dsv[1] * p.inv_n, dsv[2] * p.inv_n, dsv[3] * p.inv_n);
               red_add_v4(dbias + (2 * g + 1) * 32, dsv[4] * p.inv_n, dsv[5] * p.inv_n, dsv[6] * p.inv_n, dsv[7] * p.inv_n);
             }
           }
+        }
+        if constexpr (DECAY) {
+          if (row_ok && p.dcum != nullptr) atomicAdd(p.dcum + static_cast<size_t>(h) * p.cum_pitch + seq_start + qi, row_acc);
         }
       }
       tc_fence_before();
@@ -826,7 +925,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t v[32];
         tmem_ld32(tmem_s + lane_off + c * 32, v);
         if (row_ok) {
-          float4* dst = reinterpret_cast<float4*>(p.dq + static_cast<size_t>(seq_start + qi) * p.H * DH + h * DH + c * 32);
+          float4* dst = reinterpret_cast<float4*>(
+              p.qk_shared ? p.dq + static_cast<size_t>(seq_start + qi) * DH + c * 32
+                          : p.dq + static_cast<size_t>(seq_start + qi) * p.H * DH + h * DH + c * 32);
 #pragma unroll
           for (int g = 0; g < 8; ++g)
             red_add_v4(dst + g, __uint_as_float(v[4 * g]) * dq_scale, __uint_as_float(v[4 * g + 1]) * dq_scale,
@@ -840,7 +941,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after();
       const int kj = kv0 + r;
       const bool kv_ok = kj < L;
-      const float dv_scale = SOFTMAX ? 1.f : p.inv_n, dk_scale = dq_scale;
+      const float dv_scale = SILU ? p.inv_n : 1.f, dk_scale = dq_scale;
 #pragma unroll 1
       for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32], w[32];
@@ -848,6 +949,23 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_ld32(tmem_dk + lane_off + c * 32, w);
         if (kv_ok) {
           const size_t off = static_cast<size_t>(seq_start + kj) * p.H * DH + h * DH + c * 32;
+          if constexpr (DECAY) {
+            if (p.dcum != nullptr) {
+              const uint4* xr = reinterpret_cast<const uint4*>(
+                  p.v_rows + static_cast<size_t>(seq_start + kj) * (p.ld_v > 0 ? p.ld_v : p.H * DH) + h * DH + c * 32);
+              float dot = 0.f;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const uint4 xv = __ldg(xr + g);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  dot = fmaf(__uint_as_float(v[8 * g + 2 * k + 1]), bf16_hi(xw[k]),
+                             fmaf(__uint_as_float(v[8 * g + 2 * k]), bf16_lo(xw[k]), dot));
+              }
+              atomicAdd(p.dcum + static_cast<size_t>(h) * p.cum_pitch + seq_start + kj, -dot);
+            }
+          }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             *reinterpret_cast<uint4*>(p.dv + off + g * 8) =
@@ -855,11 +973,20 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                            pack_bf16(__uint_as_float(v[8 * g + 2]) * dv_scale, __uint_as_float(v[8 * g + 3]) * dv_scale),
                            pack_bf16(__uint_as_float(v[8 * g + 4]) * dv_scale, __uint_as_float(v[8 * g + 5]) * dv_scale),
                            pack_bf16(__uint_as_float(v[8 * g + 6]) * dv_scale, __uint_as_float(v[8 * g + 7]) * dv_scale));
-            *reinterpret_cast<uint4*>(p.dk + off + g * 8) =
-                make_uint4(pack_bf16(__uint_as_float(w[8 * g]) * dk_scale, __uint_as_float(w[8 * g + 1]) * dk_scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 2]) * dk_scale, __uint_as_float(w[8 * g + 3]) * dk_scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 4]) * dk_scale, __uint_as_float(w[8 * g + 5]) * dk_scale),
-                           pack_bf16(__uint_as_float(w[8 * g + 6]) * dk_scale, __uint_as_float(w[8 * g + 7]) * dk_scale));
+            if constexpr (!DECAY)
+              *reinterpret_cast<uint4*>(p.dk + off + g * 8) =
+                  make_uint4(pack_bf16(__uint_as_float(w[8 * g]) * dk_scale, __uint_as_float(w[8 * g + 1]) * dk_scale),
+                             pack_bf16(__uint_as_float(w[8 * g + 2]) * dk_scale, __uint_as_float(w[8 * g + 3]) * dk_scale),
+                             pack_bf16(__uint_as_float(w[8 * g + 4]) * dk_scale, __uint_as_float(w[8 * g + 5]) * dk_scale),
+                             pack_bf16(__uint_as_float(w[8 * g + 6]) * dk_scale, __uint_as_float(w[8 * g + 7]) * dk_scale));
+          }
+          if constexpr (DECAY) {
+            // the key operand is shared by all heads: their gradients meet in one fp32 row
+            float4* dst = reinterpret_cast<float4*>(p.dk_acc + static_cast<size_t>(seq_start + kj) * DH + c * 32);
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              red_add_v4(dst + g, __uint_as_float(w[4 * g]) * dk_scale, __uint_as_float(w[4 * g + 1]) * dk_scale,
+                         __uint_as_float(w[4 * g + 2]) * dk_scale, __uint_as_float(w[4 * g + 3]) * dk_scale);
           }
         }
       }
@@ -904,15 +1031,17 @@ extern "C" int recml_hstu_bucket_cache(const int* seq_offsets, int B, const int*
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-template <int DH, bool SOFTMAX>
+template <int DH, int MODE>
 static int launch_fwd(const void* q, const void* k, const void* v, const Params& p, int n_tiles, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   const long long cols = static_cast<long long>(p.H) * DH;
+  const long long qk_cols = p.qk_shared ? DH : cols;
   auto pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : cols; };
-  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
+  auto qk_pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : qk_cols; };
+  if (recml::tc::make_map_bf16(&mq, q, p.T, qk_cols, qk_pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, qk_cols, qk_pitch(p.ld_k), BKV) ||
       recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV))
     return -2;
-  auto kern = hstu_fwd_kernel<DH, SOFTMAX>;
+  auto kern = hstu_fwd_kernel<DH, MODE>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<DH>::kTotal) != cudaSuccess) return -3;
@@ -927,23 +1056,35 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
 extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, const Params* p, int n_tiles,
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
-  if (p->softmax && p->max_seq_len > 2 * BKV) return -11;   // the softmax forward keeps the whole key row in tensor memory
-  if (!p->softmax && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
-  if (p->Dh == 64) return p->softmax ? launch_fwd<64, true>(q, k, v, *p, n_tiles, stream) : launch_fwd<64, false>(q, k, v, *p, n_tiles, stream);
-  if (p->Dh == 128) return p->softmax ? launch_fwd<128, true>(q, k, v, *p, n_tiles, stream) : launch_fwd<128, false>(q, k, v, *p, n_tiles, stream);
+  if (p->mode == kSoftmax && p->max_seq_len > 2 * BKV) return -11;   // the softmax forward keeps the whole key row in tensor memory
+  if (p->mode == kSilu && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->cum_pitch < p->T + BKV)) return -13;
+  if (p->mode != kDecay && p->qk_shared) return -13;
+#define RECML_ATTN_FWD(D)                                                                  \
+  switch (p->mode) {                                                                       \
+    case kSilu: return launch_fwd<D, kSilu>(q, k, v, *p, n_tiles, stream);                 \
+    case kSoftmax: return launch_fwd<D, kSoftmax>(q, k, v, *p, n_tiles, stream);           \
+    case kDecay: return launch_fwd<D, kDecay>(q, k, v, *p, n_tiles, stream);               \
+    default: return -10;                                                                   \
+  }
+  if (p->Dh == 64) RECML_ATTN_FWD(64)
+  if (p->Dh == 128) RECML_ATTN_FWD(128)
+#undef RECML_ATTN_FWD
   return -10;
 }
 
-template <int DH, bool SOFTMAX>
+template <int DH, int MODE>
 static int launch_bwd(const void* q, const void* k, const void* v, const void* d_o, const Params& p, int n_tiles,
                       cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo;
   const long long cols = static_cast<long long>(p.H) * DH;
+  const long long qk_cols = p.qk_shared ? DH : cols;
   auto pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : cols; };
-  if (recml::tc::make_map_bf16(&mq, q, p.T, cols, pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, cols, pitch(p.ld_k), BKV) ||
+  auto qk_pitch = [&](int ld) { return ld > 0 ? static_cast<long long>(ld) : qk_cols; };
+  if (recml::tc::make_map_bf16(&mq, q, p.T, qk_cols, qk_pitch(p.ld_q), BQ) || recml::tc::make_map_bf16(&mk, k, p.T, qk_cols, qk_pitch(p.ld_k), BKV) ||
       recml::tc::make_map_bf16(&mv, v, p.T, cols, pitch(p.ld_v), BKV) || recml::tc::make_map_bf16(&mdo, d_o, p.T, cols, pitch(p.ld_do), BQ))
     return -2;
-  auto kern = hstu_bwd_kernel<DH, SOFTMAX>;
+  auto kern = hstu_bwd_kernel<DH, MODE>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB<DH>::kTotal) != cudaSuccess) return -3;
@@ -961,9 +1102,20 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
                                    int n_tiles, cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->num_buckets + 1 > 256) return -11;
-  if (!p->softmax && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
-  if (p->Dh == 64) return p->softmax ? launch_bwd<64, true>(q, k, v, d_o, *p, n_tiles, stream) : launch_bwd<64, false>(q, k, v, d_o, *p, n_tiles, stream);
-  if (p->Dh == 128) return p->softmax ? launch_bwd<128, true>(q, k, v, d_o, *p, n_tiles, stream) : launch_bwd<128, false>(q, k, v, d_o, *p, n_tiles, stream);
+  if (p->mode == kSilu && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->dk_acc == nullptr || p->cum_pitch < p->T + BKV))
+    return -13;
+  if (p->mode != kDecay && p->qk_shared) return -13;
+#define RECML_ATTN_BWD(D)                                                                  \
+  switch (p->mode) {                                                                       \
+    case kSilu: return launch_bwd<D, kSilu>(q, k, v, d_o, *p, n_tiles, stream);            \
+    case kSoftmax: return launch_bwd<D, kSoftmax>(q, k, v, d_o, *p, n_tiles, stream);      \
+    case kDecay: return launch_bwd<D, kDecay>(q, k, v, d_o, *p, n_tiles, stream);          \
+    default: return -10;                                                                   \
+  }
+  if (p->Dh == 64) RECML_ATTN_BWD(64)
+  if (p->Dh == 128) RECML_ATTN_BWD(128)
+#undef RECML_ATTN_BWD
   return -10;
 }
 

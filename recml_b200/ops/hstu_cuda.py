@@ -15,10 +15,13 @@ class _Params(ctypes.Structure):
               ("num_buckets", c_int), ("causal", c_int), ("scale", c_float), ("inv_n", c_float),
               ("seq_offsets", c_vp), ("tile_seq", c_vp), ("tile_row0", c_vp), ("timestamps", c_vp),
               ("pos_w", c_vp), ("ts_w", c_vp), ("out", c_vp), ("dq", c_vp), ("dk", c_vp), ("dv", c_vp),
-              ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("softmax", c_int), ("lse", c_vp),
+              ("dpos_w", c_vp), ("dts_w", c_vp), ("status", c_vp), ("mode", c_int), ("lse", c_vp),
               ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int),
               ("bucket_cache", c_vp), ("pair_base", c_vp), ("cap_pairs", c_int), ("bias_tiles", c_vp),
-              ("dbias_tiles", c_vp), ("window", c_int), ("segment_ids", c_vp)]
+              ("dbias_tiles", c_vp), ("window", c_int), ("segment_ids", c_vp), ("cum", c_vp),
+              ("cum_pitch", ctypes.c_longlong), ("qk_shared", c_int), ("dk_acc", c_vp), ("dcum", c_vp), ("v_rows", c_vp)]
+
+MODE_SILU, MODE_SOFTMAX, MODE_DECAY = 0, 1, 2
 
 
 class _BiasParams(ctypes.Structure):
@@ -337,7 +340,7 @@ def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
   out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
   lse = torch.empty(q.shape[0], q.shape[1], dtype=torch.float32, device=q.device)
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v)
-  p.out, p.softmax, p.lse = out.data_ptr(), 1, lse.data_ptr()
+  p.out, p.mode, p.lse = out.data_ptr(), MODE_SOFTMAX, lse.data_ptr()
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "softmax_attn_fwd")
   return out, lse
@@ -351,7 +354,52 @@ def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, sc
   dk, dv = (torch.empty(k.shape, dtype=k.dtype, device=k.device) for _ in range(2))
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v, do)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-  p.softmax, p.lse, p.delta = 1, lse.data_ptr(), delta.data_ptr()
+  p.mode, p.lse, p.delta = MODE_SOFTMAX, lse.data_ptr(), delta.data_ptr()
   _lib.check_rc(_lib.cuda().recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "softmax_attn_bwd")
   return dq.to(q.dtype), dk, dv
+
+
+# ---- decay mode: the quadratic ("attention") form of a diagonal state-space recurrence -----------------------
+#   y[l] = sum_{s <= l} (c_l . b_s) * exp(cum[l] - cum[s]) * x_s        cum = inclusive prefix sum of a <= 0
+# c and b play the parts of q and k and are shared by all heads; x is v.
+CUM_PAD = 128
+LOG2E = 1.4426950408889634
+
+
+def _decay_params(c, b, x, cum2, seq_offsets, max_seq_len, tiles, do=None):
+  p = _params(x, seq_offsets, None, None, None, max_seq_len, True, 1.0, tiles, x, x, do)
+  p.ld_q, p.ld_k = c.stride(0), b.stride(0)
+  p.inv_n = 1.0
+  p.mode, p.qk_shared, p.cum, p.cum_pitch = MODE_DECAY, 1, cum2.data_ptr(), cum2.stride(0)
+  return p
+
+
+def decay_forward(c, b, x, cum2, seq_offsets, max_seq_len):
+  """c, b `[T, N]` bf16, x `[T, H, N]` bf16, cum2 `[H, >= T + 128]` fp32 (prefix sums times log2 e).  Returns
+  y `[T, H, N]` bf16."""
+  assert rows_ok(x) and c.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and c.stride(1) == 1 and b.stride(1) == 1
+  assert c.shape[1] == x.shape[2] == b.shape[1] and cum2.stride(1) == 1 and cum2.shape[1] >= x.shape[0] + CUM_PAD
+  tiles = _tiles(seq_offsets, x.shape[0])
+  out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+  p = _decay_params(c, b, x, cum2, seq_offsets, max_seq_len, tiles)
+  p.out = out.data_ptr()
+  _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(c), _lib.ptr(b), _lib.ptr(x), ctypes.byref(p),
+                                                c_int(tiles[2]), _lib.stream()), "decay_attn_fwd")
+  return out
+
+
+def decay_backward(do, c, b, x, cum2, seq_offsets, max_seq_len):
+  """Returns (dc `[T, N]` fp32, db `[T, N]` fp32, dx `[T, H, N]` bf16, dcum `[H, pitch]` fp32 w.r.t. the natural-log
+  prefix sums)."""
+  tiles = _tiles(seq_offsets, x.shape[0], backward=True)
+  do = as_rows(do)
+  dc = torch.zeros(c.shape, dtype=torch.float32, device=c.device)
+  db = torch.zeros(b.shape, dtype=torch.float32, device=b.device)
+  dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+  dcum = torch.zeros(cum2.shape, dtype=torch.float32, device=x.device)
+  p = _decay_params(c, b, x, cum2, seq_offsets, max_seq_len, tiles, do)
+  p.dq, p.dk_acc, p.dv, p.dcum, p.v_rows = dc.data_ptr(), db.data_ptr(), dx.data_ptr(), dcum.data_ptr(), x.data_ptr()
+  _lib.check_rc(_lib.cuda().recml_hstu_attn_bwd(_lib.ptr(c), _lib.ptr(b), _lib.ptr(x), _lib.ptr(do), ctypes.byref(p),
+                                                c_int(tiles[2]), _lib.stream()), "decay_attn_bwd")
+  return dc, db, dx, dcum

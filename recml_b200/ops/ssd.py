@@ -142,11 +142,91 @@ class _ScanFn(torch.autograd.Function):
     return (dx.to(xdt), da.to(adt), db.sum(2).reshape(bshape).to(bdt), dc.sum(2).reshape(bshape).to(cdt), gi)
 
 
+# ---- tensor-core path: the quadratic form on the attention kernels' decay mode ------------------------------
+QUAD_MAX_LEN = 1024      # beyond this the O(L^2) form costs more than the recurrence
+
+
+def _quad_supported(x, b) -> bool:
+  from recml_b200.ops import hstu_cuda
+  P, N = x.shape[-1], b.shape[-1]
+  return (x.is_cuda and b.shape[-2] == 1 and P == N and P in (64, 128) and x.shape[1] <= QUAD_MAX_LEN and
+          hstu_cuda.available())
+
+
+_dense_offsets: dict = {}
+
+
+def _offsets_for(B: int, L: int, device) -> torch.Tensor:
+  key = (B, L, str(device))
+  if key not in _dense_offsets:
+    if len(_dense_offsets) > 16:
+      _dense_offsets.clear()
+    _dense_offsets[key] = (torch.arange(B + 1, device=device, dtype=torch.int32) * L).contiguous()
+  return _dense_offsets[key]
+
+
+class _QuadFn(torch.autograd.Function):
+  """y[l] = sum_{s <= l} (c_l . b_s) exp(cum[l] - cum[s]) x_s over each sequence: scores, decay mask and the
+  product with x run on the tensor cores (`csrc/cuda/hstu_attention.cu`, decay mode), the chunk-wise
+  formulation of the reference (`recml/layers/keras/mamba.py:53-146`) with the whole sequence as one chunk."""
+
+  @staticmethod
+  def forward(ctx, x, a, b, c):
+    from recml_b200.ops import hstu_cuda
+    B, L, H, P = x.shape
+    T = B * L
+    offs = _offsets_for(B, L, x.device)
+    cum = torch.cumsum(a.float(), dim=1)                                     # [B, L, H]
+    cum2 = torch.empty(H, T + hstu_cuda.CUM_PAD, dtype=torch.float32, device=x.device)
+    cum2[:, T:].zero_()
+    torch.mul(cum.permute(2, 0, 1).reshape(H, T), hstu_cuda.LOG2E, out=cum2[:, :T])
+    xb = x.reshape(T, H, P).to(torch.bfloat16).contiguous()
+    bb = b.reshape(T, P).to(torch.bfloat16).contiguous()
+    cb = c.reshape(T, P).to(torch.bfloat16).contiguous()
+    y = hstu_cuda.decay_forward(cb, bb, xb, cum2, offs, L)
+    ctx.save_for_backward(xb, bb, cb, cum2, offs)
+    ctx.meta = (x.dtype, a.dtype, b.dtype, c.dtype, tuple(x.shape), tuple(b.shape))
+    return y.reshape(B, L, H, P).to(x.dtype)
+
+  @staticmethod
+  def backward(ctx, dy):
+    from recml_b200.ops import hstu_cuda
+    xb, bb, cb, cum2, offs = ctx.saved_tensors
+    xdt, adt, bdt, cdt, xshape, bshape = ctx.meta
+    B, L, H, P = xshape
+    T = B * L
+    do = dy.reshape(T, H, P).to(torch.bfloat16)
+    dc, db, dx, dcum = hstu_cuda.decay_backward(do, cb, bb, xb, cum2, offs, L)
+    # cum[l] = sum_{t <= l} a[t]  =>  da[t] = sum_{l >= t} dcum[l]
+    g = dcum[:, :T].reshape(H, B, L)
+    da = (g.sum(-1, keepdim=True) - torch.cumsum(g, dim=-1) + g).permute(1, 2, 0)
+    return (dx.reshape(xshape).to(xdt), da.to(adt), db.reshape(bshape).to(bdt), dc.reshape(bshape).to(cdt))
+
+
+def _initial_state_term(a, c, initial_states):
+  """Contribution of the state the sequence starts from: y_off[l] = exp(cum[l]) * (h0 c_l)."""
+  B, L, H = a.shape
+  cum = torch.cumsum(a.float(), dim=1)
+  h0 = initial_states.float()
+  cf = c.float().reshape(B, L, -1)
+  if h0.dim() == 3:
+    proj = torch.einsum("bln,hpn->blhp", cf, h0)
+  else:
+    proj = torch.einsum("bln,bhpn->blhp", cf, h0)
+  return proj * torch.exp(cum)[..., None]
+
+
 def ssd_scan(x, a, b, c, block_len: int = 64, initial_states=None):
   """The SSD recurrence over the whole sequence: x `[B, L, H, P]`, a `[B, L, H]`, b / c `[B, L, G, N]`,
-  initial state `[H, P, N]` or `[B, H, P, N]`.  On CUDA (one group, P in {8..64}, N in {16, 32, 64})
-  this is the register-resident scan kernel; elsewhere the chunked formulation with zero padding to
-  a multiple of `block_len`."""
+  initial state `[H, P, N]` or `[B, H, P, N]`.  On CUDA with one group and P == N in {64, 128} this is the
+  tensor-core quadratic form (bf16 operands, fp32 accumulation); other CUDA shapes with one group take the
+  register-resident scan kernel (fp32); elsewhere the chunked formulation with zero padding to a multiple of
+  `block_len`."""
+  if _quad_supported(x, b):
+    y = _QuadFn.apply(x, a, b, c)
+    if initial_states is not None:
+      y = y + _initial_state_term(a, c, initial_states).to(y.dtype)
+    return y
   if _cuda_supported(x, b):
     return _ScanFn.apply(x, a, b, c, initial_states)
   L = x.shape[1]
@@ -159,6 +239,12 @@ def ssd_scan(x, a, b, c, block_len: int = 64, initial_states=None):
   if init is not None and init.dim() == 3:
     init = init[None].expand(x.shape[0], -1, -1, -1)
   return ssd_chunked(x, a, b, c, block_len, init)[:, :L]
+
+
+def ssd_scan_recurrent_kernel(x, a, b, c, initial_states=None):
+  """The fp32 scan kernel regardless of shape preferences (tests and precision comparisons)."""
+  assert _cuda_supported(x, b)
+  return _ScanFn.apply(x, a, b, c, initial_states)
 
 
 class _ConvFn(torch.autograd.Function):

@@ -23,7 +23,7 @@ def test_scan_matches_recurrence(B, L, H, P, N, init_dim):
     init = torch.randn(B, H, P, N, device=dev) * 0.3
   leaves = [t.clone().requires_grad_() for t in (x, a, b, c)] + ([init.clone().requires_grad_()] if init is not None else [])
   ref_leaves = [t.clone().requires_grad_() for t in (x, a, b, c)] + ([init.clone().requires_grad_()] if init is not None else [])
-  y = ssd.ssd_scan(*leaves[:4], 64, leaves[4] if init is not None else None)
+  y = ssd.ssd_scan_recurrent_kernel(*leaves[:4], leaves[4] if init is not None else None)
   ri = ref_leaves[4] if init is not None else None
   if ri is not None and ri.dim() == 3:
     ri = ri[None].expand(B, -1, -1, -1)
@@ -34,6 +34,44 @@ def test_scan_matches_recurrence(B, L, H, P, N, init_dim):
   y_ref.backward(g)
   for name, u, v in zip(("dx", "da", "db", "dc", "dinit"), leaves, ref_leaves):
     torch.testing.assert_close(u.grad, v.grad, rtol=2e-3, atol=2e-3, msg=lambda m, n=name: f"{n}: {m}")
+
+
+@pytest.mark.parametrize("B,L,H,P,init_dim", [(2, 200, 4, 64, 0), (3, 128, 2, 64, 3), (2, 300, 2, 128, 4), (5, 37, 8, 64, 0),
+                                              (1, 520, 1, 64, 0)])
+def test_tensor_core_quadratic_form_matches_recurrence(B, L, H, P, init_dim):
+  """P == N in {64, 128} takes the decay mode of the attention kernels: operands are rounded to bf16 (the oracle
+  gets the same rounded inputs), products accumulate in fp32, so the tolerance is that of bf16 scores."""
+  torch.manual_seed(2)
+  dev = "cuda"
+  rb = lambda t: t.to(torch.bfloat16).float()
+  x = rb(torch.randn(B, L, H, P, device=dev) * 0.5)
+  a = -torch.rand(B, L, H, device=dev) * 0.7
+  a[:, ::7] *= 8.0                                        # some strong forgetting steps
+  b = rb(torch.randn(B, L, 1, P, device=dev) * 0.3)
+  c = rb(torch.randn(B, L, 1, P, device=dev) * 0.3)
+  init = None
+  if init_dim == 3:
+    init = torch.randn(H, P, P, device=dev) * 0.3
+  elif init_dim == 4:
+    init = torch.randn(B, H, P, P, device=dev) * 0.3
+  mk = lambda: [t.clone().requires_grad_() for t in (x, a, b, c)] + ([init.clone().requires_grad_()] if init is not None else [])
+  leaves, ref_leaves = mk(), mk()
+  assert ssd._quad_supported(x, b)
+  y = ssd.ssd_scan(*leaves[:4], 64, leaves[4] if init is not None else None)
+  ri = ref_leaves[4] if init is not None else None
+  if ri is not None and ri.dim() == 3:
+    ri = ri[None].expand(B, -1, -1, -1)
+  y_ref = ssd.ssd_recurrent(*ref_leaves[:4], ri)
+  tol = lambda ref: 1.5e-2 * float(ref.abs().max())
+  assert float((y - y_ref).abs().max()) <= tol(y_ref)
+  g = rb(torch.randn_like(y))
+  y.backward(g)
+  y_ref.backward(g)
+  for name, u, v in zip(("dx", "da", "db", "dc", "dinit"), leaves, ref_leaves):
+    err = float((u.grad - v.grad).abs().max())
+    assert err <= tol(v.grad), f"{name}: {err} vs max {float(v.grad.abs().max())}"
+    rel = float((u.grad - v.grad).norm() / v.grad.norm())
+    assert rel < 1e-2, f"{name}: relative l2 error {rel}"
 
 
 @pytest.mark.parametrize("K,use_bias", [(4, True), (4, False), (3, True), (2, False)])
