@@ -423,6 +423,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto bar = [&](int i) { return bars + 8u * i; };
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ float softmax_xchg[SOFTMAX ? 1024 : 1];     // [parity][column block][row]: row maxima / partial sums
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -433,6 +434,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar(9), kCompute);
     mbar_init(bar(10), 1);
     mbar_init(bar(11), 1);
+    for (int i = 12; i <= 15; ++i) mbar_init(bar(i), 128);    // softmax mode: the four warps of a lane quarter
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
@@ -548,64 +550,91 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(bar(9));
       }
     } else if constexpr (SOFTMAX) {
-      // Exact softmax over at most two score tiles that are both resident in tensor memory: every warp
-      // scans the whole row (all 128 columns of each tile) for the maximum and the sum, then writes
-      // only its own 32 columns of P.
-      for (int j = 0; j < n_kv && ok; ++j)
-        if (!warp_wait(bar(5 + j), 0, abortp, p.status, 45, lane)) ok = false;
+      // Streaming softmax.  The four warps that share a row (one per 32-column block of the score tile) agree on
+      // the tile's row maximum through shared memory, then each keeps the running sum of its own columns; when
+      // the maximum grows the accumulated output is rescaled in tensor memory (it is idle between P_{j-1}·V and
+      // P_j·V).  exp is evaluated as 2^(x log2 e - m).
+      const float sc2 = p.scale * 1.4426950408889634f;
       float m = -INFINITY, l = 0.f;
-      if (ok) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass)
-#pragma unroll 1
-          for (int jc = 0; jc < n_kv * 4; ++jc) {
-            uint32_t v[32];
-            tmem_ld32(tmem_slot + (jc >> 2) * 128 + lane_off + (jc & 3) * 32, v);
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int kj = jc * 32 + e;
-              const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-              const float x = __uint_as_float(v[e]) * p.scale;
-              if (visible) {
-                if (pass == 0) m = fmaxf(m, x); else l += __expf(x - m);
-              }
-            }
-          }
-      }
+      float* mx = softmax_xchg + quarter * 32 + lane;      // [parity][cb][row]: + parity * 512 + cb * 128
+      const uint32_t xbar = bar(12 + quarter);
+      int xphase = 0;
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (j > 0 && !warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }
-        {
-          uint32_t v[32];
-          tmem_ld32(tmem_slot + j * 128 + lane_off + cb * 32, v);
-          uint32_t packed[16];
+        const int sb = j & 1;
+        if (!warp_wait(bar(5 + sb), (j >> 1) & 1, abortp, p.status, 45, lane)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(tmem_slot + sb * 128 + lane_off + cb * 32, v);
+        tc_fence_before();
+        mbar_arrive(bar(7 + sb));           // the scores are in registers: this S buffer may be overwritten
+        const int kj0 = j * BKV + cb * 32;
+        float tmax = -INFINITY;
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float pr[2];
+        for (int e = 0; e < 32; ++e) {
+          const int kj = kj0 + e;
+          const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
+          const float x = visible ? __uint_as_float(v[e]) * sc2 : -INFINITY;
+          v[e] = __float_as_uint(x);
+          tmax = fmaxf(tmax, x);
+        }
+        mx[sb * 512 + cb * 128] = tmax;
+        mbar_arrive(xbar);
+        if (!warp_wait(xbar, xphase, abortp, p.status, 48, lane)) { ok = false; break; }
+        xphase ^= 1;
+        const float* mrow = softmax_xchg + sb * 512 + quarter * 32 + lane;
+        const float m_new = fmaxf(fmaxf(m, fmaxf(mrow[0], mrow[128])), fmaxf(mrow[256], mrow[384]));
+        const float alpha = m == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : exp2_fast(m - m_new);
+        m = m_new;
+        float psum = 0.f;
+        uint32_t packed[16];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int kj = j * BKV + cb * 32 + e + u;
-              const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
-              pr[u] = visible ? __expf(__uint_as_float(v[e + u]) * p.scale - m) : 0.f;
+        for (int e = 0; e < 32; e += 2) {
+          const float x0 = __uint_as_float(v[e]), x1 = __uint_as_float(v[e + 1]);
+          const float p0 = x0 == -INFINITY ? 0.f : exp2_fast(x0 - m_new);
+          const float p1 = x1 == -INFINITY ? 0.f : exp2_fast(x1 - m_new);
+          psum += p0 + p1;
+          packed[e >> 1] = pack_bf16(p0, p1);
+        }
+        l = fmaf(l, alpha, psum);
+        if (j > 0) {
+          if (!warp_wait(bar(10), (j - 1) & 1, abortp, p.status, 46, lane)) { ok = false; break; }   // P_{j-1}·V done
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = cb; c < DH / 32; c += 4) {
+              uint32_t o[32];
+              tmem_ld32(tmem_o + lane_off + c * 32, o);
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tmem_o + lane_off + c * 32, o);
             }
-            packed[e >> 1] = pack_bf16(pr[0], pr[1]);
-          }
-          uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
-            *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
-                make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
           }
         }
+        uint8_t* row_ptr = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(row_ptr + chunk * 16) =
+              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
         tc_fence_before();
-        mbar_arrive(bar(7 + j));
         fence_async_smem();
         mbar_arrive(bar(9));
       }
+      // the row sum is the sum of the four column blocks' partial sums (all scaled to the final maximum)
+      if (ok) {
+        // (the buffer half that tile n_kv would use: nobody can still be reading it)
+        mx[(n_kv & 1) * 512 + cb * 128] = l;
+        mbar_arrive(xbar);
+        if (!warp_wait(xbar, xphase, abortp, p.status, 49, lane)) ok = false;
+        if (ok) {
+          const float* lrow = softmax_xchg + (n_kv & 1) * 512 + quarter * 32 + lane;
+          l = (lrow[0] + lrow[128]) + (lrow[256] + lrow[384]);
+        }
+      }
       out_scale = l > 0.f ? 1.f / l : 0.f;
       if (ok && cb == 0 && row_ok && p.lse != nullptr)
-        p.lse[static_cast<size_t>(tok0 + r) * p.H + h] = l > 0.f ? m + logf(l) : 0.f;
+        p.lse[static_cast<size_t>(tok0 + r) * p.H + h] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : 0.f;
     } else {
       // SiLU mode.  With h = (s * scale + bias) / 2:  silu(2h) = 2h * sigmoid(2h) = h * tanh(h) + h.  The
       // pair's bias tile brings bias / 2 (and the masks); 1 / n is applied once, to the output.
@@ -1056,7 +1085,6 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
 extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, const Params* p, int n_tiles,
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
-  if (p->mode == kSoftmax && p->max_seq_len > 2 * BKV) return -11;   // the softmax forward keeps the whole key row in tensor memory
   if (p->mode == kSilu && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
   if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->cum_pitch < p->T + BKV)) return -13;
   if (p->mode != kDecay && p->qk_shared) return -13;

@@ -64,7 +64,7 @@ def jagged_softmax_attention(q, k, v, seq_offsets, max_seq_len: int, causal: boo
 
 
 def _kernel_ok(q, L: int) -> bool:
-  if not q.is_cuda or q.shape[-1] not in (64, 128) or L > 256:
+  if not q.is_cuda or q.shape[-1] not in (64, 128):
     return False
   from recml_b200.ops import hstu_cuda
   return hstu_cuda.available()
@@ -73,10 +73,12 @@ def _kernel_ok(q, L: int) -> bool:
 def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: bool, dropout_p: float = 0.0,
                          training: bool = False):
   """Attention whose mask is `key is not padding` ∧ (`key <= query` when causal): q, k, v `[B, L, H, Dh]`,
-  `padding_mask [B, L]` (True = real token).  On a GPU (head dim 64 / 128, L ≤ 256, no attention
-  dropout) the valid tokens are packed and run through the jagged tcgen05 kernels in softmax mode, so
-  no `[B, H, L, L]` score tensor is ever written; rows of padded queries come back as zeros (the
-  dense formulation gives them the average of the visible values; nothing downstream reads them).
+  `padding_mask [B, L]` (True = real token).  On a GPU (head dim 64 / 128, no attention dropout) the valid
+  tokens are packed and run through the jagged tcgen05 kernels in softmax mode (streaming softmax, any
+  length), so no `[B, H, L, L]` score tensor is ever written; rows of padded queries come back as zeros
+  (the dense formulation gives them the average of the visible values; nothing downstream reads them).
+  Packing happens on the device without a host synchronisation: every real token goes to its rank among
+  the real tokens, padding goes to a spare row, and the kernels see `B * L` rows of capacity.
   Everywhere else this is `softmax_attention` with the merged mask."""
   B, L, H, Dh = q.shape
   if not _kernel_ok(q, L) or (training and dropout_p > 0):
@@ -88,11 +90,13 @@ def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: boo
     offs = torch.arange(B + 1, device=q.device, dtype=torch.int32) * L
     out = jagged_softmax_attention(flat(q), flat(k), flat(v), offs, L, causal)
     return out.reshape(B, L, H, Dh).to(dt)
-  valid = padding_mask.bool()
-  idx = valid.reshape(-1).nonzero().squeeze(1)          # packs the real tokens (one host sync for the count)
+  T = B * L
+  valid = padding_mask.bool().reshape(T)
+  rank = torch.cumsum(valid, 0, dtype=torch.int32) - 1
+  dest = torch.where(valid, rank, torch.full_like(rank, T)).long()       # padding lands in the spare row T
   offs = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
-  offs[1:] = valid.sum(1).cumsum(0)
-  pick = lambda t: flat(t).index_select(0, idx)
-  packed = jagged_softmax_attention(pick(q), pick(k), pick(v), offs, L, causal)
-  out = torch.zeros(B * L, H, Dh, dtype=packed.dtype, device=q.device).index_copy(0, idx, packed)
+  offs[1:] = valid.reshape(B, L).sum(1).cumsum(0)
+  pack = lambda t: torch.zeros(T + 1, H, Dh, dtype=torch.bfloat16, device=q.device).index_copy(0, dest, flat(t))[:T]
+  packed = jagged_softmax_attention(pack(q), pack(k), pack(v), offs, L, causal)
+  out = packed.index_select(0, dest.clamp(max=T - 1)) * valid[:, None, None].to(packed.dtype)
   return out.reshape(B, L, H, Dh).to(dt)

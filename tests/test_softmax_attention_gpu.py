@@ -17,11 +17,14 @@ def _dense(q, k, v, padding_mask, causal):
 
 @pytest.mark.parametrize("B,L,H,Dh,causal,pad", [(3, 200, 4, 64, True, "left"), (2, 256, 2, 64, False, "right"),
                                                  (4, 50, 2, 64, True, None), (2, 130, 1, 128, True, "left"),
-                                                 (2, 128, 2, 64, False, None)])
+                                                 (2, 128, 2, 64, False, None), (2, 700, 2, 64, True, "right"),
+                                                 (1, 1100, 1, 128, False, "left"), (2, 513, 2, 64, False, None)])
 def test_structured_attention_matches_dense(B, L, H, Dh, causal, pad):
   torch.manual_seed(0)
   dev = "cuda"
   q, k, v = (torch.randn(B, L, H, Dh, device=dev).to(torch.bfloat16).float() for _ in range(3))
+  # keys grow along the sequence so that the running maximum of a row keeps rising from tile to tile
+  k = (k * torch.linspace(0.5, 2.0, L, device=dev)[None, :, None, None]).to(torch.bfloat16).float()
   padding_mask = None
   if pad is not None:
     lens = torch.randint(L // 3, L + 1, (B,), device=dev)
