@@ -17,6 +17,7 @@
 //            fp32 and apply the row optimizer in the same kernel (emb_bwd_update/finalize).
 // Peer flags are monotonically increasing sequence numbers; all waits are bounded.
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -237,6 +238,187 @@ __global__ void emb_push_ids_kernel(const PushIdsParams p) {
   grid_done_then_signal(p.done_counter, p.flags, p.W, seq_of(p.seq));
 }
 
+// =================================== ids: bucketize by owner, then push =============================
+// Every destination rank receives a jagged batch of its own: the offsets of all (feature, sample) bags, and only
+// the ids it will look up: all ids of a feature whose table it holds whole (or by columns), the ids of ITS rows
+// of a row-sharded table, nothing of the other features (their bags are empty for it).  The owner's lookup
+// kernel then gathers every id it is given.  Three launches: count the ids of each row-sharded bag per owner,
+// turn the counts into offsets (one block per feature and owner), then write ids and offsets into the peers'
+// buffers and raise their flags.
+struct BucketFeat { int kind; int owner; int rot; int rw_index; };   // rw_index: position among the row-sharded features
+struct BucketizeParams {
+  const int* values; const int* offsets; const float* weights;
+  int n_feats, B, W, me, n_rw;
+  const BucketFeat* feats;   // [n_feats]
+  int* cnt;                  // [n_rw, W, B]: ids of bag b owned by rank r, then their exclusive prefix over b
+  int* tot;                  // [n_rw, W]
+  int* dst_values[kMaxWorld]; int* dst_offsets[kMaxWorld]; float* dst_weights[kMaxWorld];
+  unsigned int* done_counter; PeerFlags flags; SeqRef seq;
+};
+
+__device__ __forceinline__ int row_owner(int id, int W, int rot) {
+  int m = id % W;
+  if (m < 0) m += W;          // ids outside the vocabulary are reported by the owner's lookup, not here
+  return (m + rot) % W;
+}
+
+__global__ void __launch_bounds__(256) bucket_count_kernel(const BucketizeParams p) {
+  extern __shared__ int rw_feat[];      // [n_rw]: feature index of the j-th row-sharded feature
+  for (int f = threadIdx.x; f < p.n_feats; f += blockDim.x)
+    if (p.feats[f].kind == kRowWise) rw_feat[p.feats[f].rw_index] = f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = static_cast<long long>(p.n_rw) * p.B;
+  for (long long jb = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; jb < total; jb += warps) {
+    const int j = static_cast<int>(jb / p.B), b = static_cast<int>(jb % p.B);
+    const int fi = rw_feat[j];
+    const int rot = p.feats[fi].rot;
+    const long long fb = static_cast<long long>(fi) * p.B + b;
+    const int o0 = p.offsets[fb], o1 = p.offsets[fb + 1];
+    int mine = 0;                   // lane r counts the ids of rank r
+    for (int base = o0; base < o1; base += 32) {
+      const int i = base + lane;
+      const int r = i < o1 ? row_owner(p.values[i], p.W, rot) : -1;
+      for (int q = 0; q < p.W; ++q) {
+        const int c = __popc(__ballot_sync(0xffffffffu, r == q));
+        if (lane == q) mine += c;
+      }
+    }
+    if (lane < p.W) p.cnt[(static_cast<long long>(j) * p.W + lane) * p.B + b] = mine;
+  }
+}
+
+// One block per (row-sharded feature, owner): exclusive prefix sum of its B counts in place, total to tot.
+__global__ void __launch_bounds__(1024) bucket_scan_kernel(const BucketizeParams p) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  int* c = p.cnt + static_cast<long long>(blockIdx.x) * p.B;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = (p.B + 1023) / 1024;
+  const int lo = min(static_cast<int>(threadIdx.x) * per, p.B), hi = min(lo + per, p.B);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += c[i];
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sums[lane], wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    warp_sums[lane] = wi - w;
+    if (lane == 31) carry_s = wi;
+  }
+  __syncthreads();
+  int run = warp_sums[warp] + incl - sum;
+  for (int i = lo; i < hi; ++i) {
+    const int v = c[i];
+    c[i] = run;
+    run += v;
+  }
+  if (threadIdx.x == 0) p.tot[blockIdx.x] = carry_s;
+}
+
+__global__ void __launch_bounds__(256) bucket_push_kernel(const BucketizeParams p) {
+  extern __shared__ int base_s[];      // [W][n_feats + 1]: first id of feature f in rank r's batch
+  const int lane = threadIdx.x & 31;
+  const int F = p.n_feats;
+  int* feat_lo = base_s + p.W * (F + 1);    // [n_feats + 1]: first id of feature f in the local batch
+  int* rw_feat = feat_lo + F + 1;           // [n_rw]: feature index of the j-th row-sharded feature
+  for (int f = threadIdx.x; f <= F; f += blockDim.x) {
+    feat_lo[f] = p.offsets[static_cast<long long>(f) * p.B];
+    if (f < F && p.feats[f].kind == kRowWise) rw_feat[p.feats[f].rw_index] = f;
+  }
+  if (threadIdx.x < p.W) {
+    const int r = threadIdx.x;
+    int run = 0;
+    for (int f = 0; f < F; ++f) {
+      base_s[r * (F + 1) + f] = run;
+      const BucketFeat bf = p.feats[f];
+      const int len = p.offsets[static_cast<long long>(f + 1) * p.B] - p.offsets[static_cast<long long>(f) * p.B];
+      if (bf.kind == kRowWise) run += p.tot[bf.rw_index * p.W + r];
+      else if (bf.kind == kColumnWise || bf.owner == r) run += len;
+    }
+    base_s[r * (F + 1) + F] = run;
+    if (blockIdx.x == 0) p.dst_offsets[r][static_cast<long long>(F) * p.B] = run;     // end of the last bag
+  }
+  __syncthreads();
+  const long long total = static_cast<long long>(F) * p.B;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  // (a) offsets of the bags of whole features, one thread per bag
+  for (long long fb = tid; fb < total; fb += nthreads) {
+    const int fi = static_cast<int>(fb / p.B);
+    const BucketFeat f = p.feats[fi];
+    if (f.kind == kRowWise) continue;
+    const int within = p.offsets[fb] - feat_lo[fi];
+    for (int r = 0; r < p.W; ++r) {
+      const bool needs = f.kind == kColumnWise || f.owner == r;
+      p.dst_offsets[r][fb] = base_s[r * (F + 1) + fi] + (needs ? within : 0);
+    }
+  }
+  // (b) ids of whole features, one thread per id: the feature is found by bisection over the feature boundaries
+  const long long nnz = feat_lo[F];
+  for (long long i = tid; i < nnz; i += nthreads) {
+    int lo = 0, hi = F;                 // feat_lo[lo] <= i < feat_lo[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (feat_lo[mid] <= i) lo = mid; else hi = mid;
+    }
+    const BucketFeat f = p.feats[lo];
+    if (f.kind == kRowWise) continue;
+    const int v = p.values[i];
+    const float w = p.weights != nullptr ? p.weights[i] : 0.f;
+    const int within = static_cast<int>(i) - feat_lo[lo];
+    const int r0 = f.kind == kColumnWise ? 0 : f.owner, r1 = f.kind == kColumnWise ? p.W : f.owner + 1;
+    for (int r = max(r0, 0); r < r1; ++r) {
+      const int at = base_s[r * (F + 1) + lo] + within;
+      p.dst_values[r][at] = v;
+      if (p.weights != nullptr) p.dst_weights[r][at] = w;
+    }
+  }
+  // (c) row-sharded features, one warp per bag: every id goes to the rank that owns its row, behind the ids
+  // that rank already got from this bag
+  const long long warps = nthreads >> 5;
+  const long long rw_total = static_cast<long long>(p.n_rw) * p.B;
+  for (long long jb = tid >> 5; jb < rw_total; jb += warps) {
+    const int fi = rw_feat[jb / p.B], b = static_cast<int>(jb % p.B);
+    const BucketFeat f = p.feats[fi];
+    const long long fb = static_cast<long long>(fi) * p.B + b;
+    const int o0 = p.offsets[fb], o1 = p.offsets[fb + 1];
+    int run = 0;      // lane r: where the next id of rank r goes
+    if (lane < p.W) {
+      run = base_s[lane * (F + 1) + fi] + p.cnt[(static_cast<long long>(f.rw_index) * p.W + lane) * p.B + b];
+      p.dst_offsets[lane][fb] = run;
+    }
+    for (int base = o0; base < o1; base += 32) {
+      const int i = base + lane;
+      const bool on = i < o1;
+      const int id = on ? p.values[i] : 0;
+      const int r = on ? row_owner(id, p.W, f.rot) : p.W;     // idle lanes form a group of their own
+      const unsigned int peers = __match_any_sync(0xffffffffu, r);
+      const int at = __shfl_sync(0xffffffffu, run, r & 31) + __popc(peers & ((1u << lane) - 1u));
+      if (on) {
+        p.dst_values[r][at] = id;
+        if (p.weights != nullptr) p.dst_weights[r][at] = p.weights[i];
+      }
+      for (int q = 0; q < p.W; ++q) {
+        const int c = __popc(__ballot_sync(0xffffffffu, r == q));
+        if (lane == q) run += c;
+      }
+    }
+  }
+  grid_done_then_signal(p.done_counter, p.flags, p.W, seq_of(p.seq));
+}
+
 // =================================== forward: gather + pool + peer store ===========================
 struct FwdParams {
   IdPtrs ids;
@@ -253,9 +435,12 @@ struct FwdParams {
   int* status;
   unsigned int* dropped;    // non-null: ids that do not fit the occurrence list are dropped from the lookup and
                             // counted here (allow_id_dropping); null: an overflow is a kCapacity error
-  int prefetch;             // 1: ask L2 for a bag's rows as soon as their ids are known
+  int prefetch;             // bit 0: ask L2 for a bag's rows as soon as their ids are known; bit 1 (tiled kernel):
+                            // let owned ids wait in the warp's queue across chunks
   int tiled;                // 1: no sequence feature in this launch -> the bags-in-tiles kernel
   long long total_tiles;    // tiled: sum over features of W * ceil(B / bags per tile)
+  int prefiltered;          // 1: the senders bucketized the ids: every id of a row-sharded pooled feature found here
+                            //    is owned (sequence features keep their positions, so they still arrive whole)
 };
 
 template <int VPL, bool TRAIN, bool GAINS>
@@ -311,13 +496,13 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
       }
       unsigned int lrow = 0;
       if (f.kind == kRowWise) {
-        owned = owned && ((id % p.W + f.rot) % p.W == p.me);
+        owned = owned && ((p.prefiltered && f.seq_len == 0) || (id % p.W + f.rot) % p.W == p.me);
         lrow = f.row_base + id / p.W;
       } else {
         lrow = f.row_base + id;
       }
       if (f.seq_len > 0 && i - o0 >= f.seq_len) owned = false;
-      if (owned && p.prefetch) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
+      if (owned && (p.prefetch & 1)) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
       unsigned int mask = __ballot_sync(0xffffffffu, owned);
       if (TRAIN && mask != 0) {
         // claim room in the occurrence list; the count may run past the capacity (readers clamp it), and
@@ -484,6 +669,37 @@ __global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
         ++cur;
       }
     };
+    unsigned int q_row = 0;
+    float q_w = 1.f;
+    int q_bag = 0, qn = 0;
+    auto drain = [&]() {      // gathers the queued rows kDepth at a time, in order, and adds them to their bags
+      for (int t0 = 0; t0 < qn; t0 += kDepth) {
+        unsigned int rj[kDepth]; float wj[kDepth]; int bj[kDepth];
+        const int n = min(kDepth, qn - t0);
+#pragma unroll
+        for (int u = 0; u < kDepth; ++u) {
+          rj[u] = __shfl_sync(0xffffffffu, q_row, (t0 + u) & 31);
+          wj[u] = GAINS ? __shfl_sync(0xffffffffu, q_w, (t0 + u) & 31) : 1.f;
+          bj[u] = __shfl_sync(0xffffffffu, q_bag, (t0 + u) & 31);
+        }
+        Vec<VPL> r[kDepth];
+        if (lane_on) {
+#pragma unroll
+          for (int u = 0; u < kDepth; ++u)
+            if (u < n) r[u] = load_f32<VPL>(p.table + static_cast<size_t>(rj[u]) * p.dloc + lane * VPL);
+        }
+#pragma unroll
+        for (int u = 0; u < kDepth; ++u) {
+          if (u >= n) break;
+          if (bj[u] != cur) store_upto(bj[u]);
+          if (lane_on) {
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(wj[u], r[u].v[e], acc.v[e]);
+          }
+        }
+      }
+      qn = 0;
+    };
     for (int base = p0; base < p1; base += 32) {
       const int i = base + lane;
       int id = -1;
@@ -510,12 +726,12 @@ __global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
       }
       unsigned int lrow = 0;
       if (f.kind == kRowWise) {
-        owned = owned && ((id % p.W + f.rot) % p.W == p.me);
+        owned = owned && ((p.prefiltered && f.seq_len == 0) || (id % p.W + f.rot) % p.W == p.me);
         lrow = f.row_base + id / p.W;
       } else {
         lrow = f.row_base + id;
       }
-      if (owned && p.prefetch) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
+      if (owned && (p.prefetch & 1)) prefetch_l2(p.table + static_cast<size_t>(lrow) * p.dloc, p.dloc * 4);
       unsigned int mask = __ballot_sync(0xffffffffu, owned);
       if (TRAIN && mask != 0) {
         const int n_own = __popc(mask);
@@ -548,34 +764,23 @@ __global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
           }
         }
       }
-      while (mask) {
-        unsigned int rj[kDepth]; float wj[kDepth]; int bj[kDepth];
-        int n = 0;
-#pragma unroll
-        for (int u = 0; u < kDepth; ++u) {
-          const int j = mask ? __ffs(mask) - 1 : 0;
-          if (mask) { mask &= mask - 1; n = u + 1; }
-          rj[u] = __shfl_sync(0xffffffffu, lrow, j);
-          wj[u] = GAINS ? __shfl_sync(0xffffffffu, w, j) : 1.f;
-          bj[u] = __shfl_sync(0xffffffffu, bag, j);
-        }
-        Vec<VPL> r[kDepth];
-        if (lane_on) {
-#pragma unroll
-          for (int u = 0; u < kDepth; ++u)
-            if (u < n) r[u] = load_f32<VPL>(p.table + static_cast<size_t>(rj[u]) * p.dloc + lane * VPL);
-        }
-#pragma unroll
-        for (int u = 0; u < kDepth; ++u) {
-          if (u >= n) break;
-          if (bj[u] != cur) store_upto(bj[u]);
-          if (lane_on) {
-#pragma unroll
-            for (int e = 0; e < VPL; ++e) acc.v[e] = fmaf(wj[u], r[u].v[e], acc.v[e]);
-          }
-        }
+      // Owned ids wait in a queue (entry t in lane t) until a chunk no longer fits behind them: a rank owns only
+      // 1/W of a row-sharded feature's ids, and gathering the few rows of each chunk by themselves would leave the
+      // loads of a warp one short round trip after the other.
+      const int n_own = __popc(mask);
+      if (qn + n_own > 32) drain();
+      if (n_own > 0) {
+        const bool mine = lane >= qn && lane < qn + n_own;
+        const int src = mine ? __fns(mask, 0, lane - qn + 1) : 0;
+        const unsigned int r_in = __shfl_sync(0xffffffffu, lrow, src);
+        const float w_in = GAINS ? __shfl_sync(0xffffffffu, w, src) : 1.f;
+        const int b_in = __shfl_sync(0xffffffffu, bag, src);
+        if (mine) { q_row = r_in; q_w = w_in; q_bag = b_in; }
+        qn += n_own;
+        if (!(p.prefetch & 2)) drain();
       }
     }
+    drain();
     store_upto(nb);       // the open bag and the (empty or un-owned) bags after it
   }
   grid_done_then_signal(p.done_counter, p.flags, p.W, seq);
@@ -1038,14 +1243,17 @@ extern "C" int recml_emb_combine(const CombineParams* p, cudaStream_t stream) {
 extern "C" int recml_emb_push_grads(const PushGradParams* p, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) { recml::prefer_max_shared_carveout(emb_push_grads_kernel); configured = true; }
-  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * 4);
+  // three resident blocks per SM (256 threads x 32 registers each): a GEMM CTA of another stream (the
+  // weight-gradient products run at the same time) still finds its threads and registers on every SM
+  static const int per_sm = [] { const char* e = getenv("RECML_EMB_PUSH_BLOCKS"); return e ? atoi(e) : 3; }();
+  const int blocks = blocks_for(static_cast<long long>(p->n_feats) * p->B, 148 * per_sm);
   emb_push_grads_kernel<<<blocks, 256, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 // max_occ: host-side upper bound of *n_occ used to size the grid (the persistent grid strides over the ranges
 // that exist).  blocks_per_sm: resident 128-thread blocks per SM: 0 = fill the GPU; -1 = leave room for a GEMM
-// CTA of another stream on every SM (three blocks of the 64-register kernel, two of the 80-register one).
+// CTA of another stream on every SM (three blocks of this 64-register kernel).
 extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int gains, int blocks_per_sm,
                                     cudaStream_t stream) {
   const int vpl = vpl_for(p->dloc);
@@ -1086,6 +1294,28 @@ extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int g
 #undef RECML_BWD
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+extern "C" int recml_emb_bucketize_push(const BucketizeParams* p, cudaStream_t stream) {
+  if (p->W > kMaxWorld || p->n_feats <= 0 || p->B <= 0) return -2;
+  const size_t smem = (static_cast<size_t>(p->W + 1) * (p->n_feats + 1) + p->n_rw) * sizeof(int);
+  if (smem > 40 * 1024) return -2;
+  // (the push kernel's work is one thread per id or per bag of a whole feature, one warp per row-sharded bag)
+  const long long bags = static_cast<long long>(p->n_feats) * p->B;
+  int blocks = static_cast<int>((bags + 255) / 256);
+  const int cap = 148 * 8;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  if (p->n_rw > 0) {
+    const long long rw_bags = static_cast<long long>(p->n_rw) * p->B;
+    int cblocks = static_cast<int>((rw_bags + 7) / 8);
+    cblocks = cblocks < 1 ? 1 : (cblocks > cap ? cap : cblocks);
+    bucket_count_kernel<<<cblocks, 256, p->n_rw * sizeof(int), stream>>>(*p);
+    bucket_scan_kernel<<<p->n_rw * p->W, 1024, 0, stream>>>(*p);
+  }
+  bucket_push_kernel<<<blocks, 256, smem, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_emb_bucketize_struct_size() { return static_cast<int>(sizeof(BucketizeParams)); }
 
 extern "C" int recml_emb_struct_sizes(int* out) {
   out[0] = sizeof(FeatDesc); out[1] = sizeof(FwdParams); out[2] = sizeof(CombineDesc); out[3] = sizeof(CombineParams);

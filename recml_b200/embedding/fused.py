@@ -59,7 +59,7 @@ class FwdParams(ctypes.Structure):
               ("dloc", c_int), ("table", c_vp), ("pooled", c_vp * MAXW), ("occ_key", c_vp), ("occ_val", c_vp),
               ("occ_gain", c_vp), ("occ_count", c_vp), ("occ_cap", c_uint), ("grad_ld", c_ll), ("wait_flags", c_vp),
               ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef), ("status", c_vp), ("dropped", c_vp),
-              ("prefetch", c_int), ("tiled", c_int), ("total_tiles", c_ll)]
+              ("prefetch", c_int), ("tiled", c_int), ("total_tiles", c_ll), ("prefiltered", c_int)]
 
 
 class CombineDesc(ctypes.Structure):
@@ -97,6 +97,17 @@ class PushIdsParams(ctypes.Structure):
               ("seq", SeqRef), ("need", c_vp), ("n_feats", c_int), ("B", c_int)]
 
 
+class BucketFeat(ctypes.Structure):
+  _fields_ = [("kind", c_int), ("owner", c_int), ("rot", c_int), ("rw_index", c_int)]
+
+
+class BucketizeParams(ctypes.Structure):
+  _fields_ = [("values", c_vp), ("offsets", c_vp), ("weights", c_vp), ("n_feats", c_int), ("B", c_int), ("W", c_int),
+              ("me", c_int), ("n_rw", c_int), ("feats", c_vp), ("cnt", c_vp), ("tot", c_vp),
+              ("dst_values", c_vp * MAXW), ("dst_offsets", c_vp * MAXW), ("dst_weights", c_vp * MAXW),
+              ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef)]
+
+
 _layout_checked = False
 
 
@@ -109,6 +120,7 @@ def _check_layout(lib):
   mine = [ctypes.sizeof(t) for t in (FeatDesc, FwdParams, CombineDesc, CombineParams, PushGradDesc,
                                      PushGradParams, BwdParams, PushIdsParams)]
   assert list(sizes) == mine, f"struct layout mismatch: C {list(sizes)} vs ctypes {mine}"
+  assert int(lib.recml_emb_bucketize_struct_size()) == ctypes.sizeof(BucketizeParams)
   _layout_checked = True
 
 
@@ -141,8 +153,12 @@ class FusedBackend:
     # weight-gradient GEMMs beside the embedding backward sets -1 so that a GEMM CTA fits on every SM
     self.bwd_blocks_per_sm = int(os.environ.get("RECML_EMB_BWD_BLOCKS", "0"))
     self.side_streams = os.environ.get("RECML_EMB_STREAMS", "1") != "0"
-    self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "1"))
+    self.fwd_prefetch = int(os.environ.get("RECML_EMB_FWD_PREFETCH", "3"))    # bit 0: L2 prefetch, bit 1: id queue
     self.fwd_tiled = os.environ.get("RECML_EMB_FWD_TILED", "1") != "0"
+    # Senders sort the ids of row-sharded pooled features by owning rank, so that a rank receives (and scans)
+    # only its own; needs whole-bag combiner denominators to be unnecessary, i.e. sum combiners on those features.
+    self.bucketize = os.environ.get("RECML_EMB_BUCKETIZE", "1") != "0"
+    self._bucket = None
     self.dropped = torch.zeros(1, dtype=torch.int32, device=module.device) if module.config.allow_id_dropping else None
     # lookups that may be in flight before their update runs: 1 for the ordinary step; 2 under software
     # pipelining (`training/pipeline.py`), where lookup(i + 1) precedes update(i).  Each in-flight lookup has
@@ -294,6 +310,35 @@ class FusedBackend:
     self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
     self.buf = symm.SymmBuffer(cv.off, m.group, m.device)
 
+  def _bucket_state(self):
+    """Device-side description of the features for the bucketizing id push, or None when it does not apply (a
+    row-sharded pooled feature with a mean / sqrtn combiner needs the whole bag at the owner)."""
+    if self._bucket is not None:
+      return self._bucket or None
+    m = self.m
+    ok = self.bucketize and m.world > 1
+    feats, n_rw = [], 0
+    seq_len = {f: L for f, _, _, L in self.layout}
+    for fname in m.feature_names:
+      tp = m.plan.tables[m.feature_to_table[fname]]
+      kind, rw_index = KIND.get(tp.placement, KIND[Placement.TABLE_WISE]), -1    # replicated: no rank is sent ids
+      if tp.placement is Placement.ROW_WISE:
+        if seq_len.get(fname, 0) > 0:
+          kind = KIND[Placement.COLUMN_WISE]        # positions matter: every owner gets the whole sequence
+        else:
+          if m.config.specs[fname].combiner != "sum":
+            ok = False
+          rw_index, n_rw = n_rw, n_rw + 1
+      feats.append(BucketFeat(kind, tp.owner if tp.placement is Placement.TABLE_WISE else -1, tp.rotation, rw_index))
+    if not ok:
+      self._bucket = False
+      return None
+    dev = m.device
+    self._bucket = {"feats": _device_struct_array(feats, dev), "n_rw": n_rw,
+                    "cnt": torch.zeros(max(n_rw, 1) * m.world * self.B, dtype=torch.int32, device=dev),
+                    "tot": torch.zeros(max(n_rw, 1) * m.world, dtype=torch.int32, device=dev)}
+    return self._bucket
+
   def _need_mask(self) -> torch.Tensor:
     """uint8 per feature: bit r set when rank r holds rows (or columns) of the feature's table, i.e.
     needs its ids."""
@@ -326,7 +371,8 @@ class FusedBackend:
         else:
           slot, goff, stride = self.slot_off[fname], self.grad_off[m.rank][fname], width
         # bags per warp of the tiled forward: a few hundred ids per tile whatever the bag size
-        avg = self._avg_bag.get(fname, 1.0) * (1.0 if tp.placement is not Placement.ROW_WISE else 1.0)
+        # (a rank scans all ids of a row-sharded feature and gathers 1 / W of them: weigh the two)
+        avg = self._avg_bag.get(fname, 1.0) * (0.5 if tp.placement is Placement.ROW_WISE and m.world > 2 else 1.0)
         shift = 5 if avg <= 8 else 4 if avg <= 16 else 3 if avg <= 32 else 2 if avg <= 64 else 1
         bpt = 1 << shift
         feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
@@ -414,7 +460,28 @@ class FusedBackend:
     if direct is None:
       self._alloc_symm()
     ids = IdPtrs()
-    if W > 1:
+    bucket = self._bucket_state() if W > 1 else None
+    if bucket is not None:
+      p = BucketizeParams()
+      p.values, p.offsets = kjt.values.data_ptr(), kjt.offsets.data_ptr()
+      p.weights = kjt.weights.data_ptr() if kjt.weights is not None else None
+      p.n_feats, p.B, p.W, p.me, p.n_rw = len(m.feature_names), B, W, m.rank, bucket["n_rw"]
+      p.feats, p.cnt, p.tot = bucket["feats"].data_ptr(), bucket["cnt"].data_ptr(), bucket["tot"].data_ptr()
+      vo, oo, wo = self.ids_off[par][m.rank]
+      for r in range(W):
+        p.dst_values[r] = self.buf.peer_ptr(r, vo)
+        p.dst_offsets[r] = self.buf.peer_ptr(r, oo)
+        p.dst_weights[r] = self.buf.peer_ptr(r, wo)
+        p.flags[r] = self._flag_ptr(r, 0, m.rank)
+      p.done_counter, p.seq = self.done_ids.data_ptr(), seq
+      _lib.check_rc(self.lib.recml_emb_bucketize_push(ctypes.byref(p), st), "emb_bucketize_push")
+      _lib.LAUNCHES["count"] += 2 if bucket["n_rw"] else 0
+      for s in range(W):
+        vo, oo, wo = self.ids_off[par][s]
+        ids.values[s] = self.buf.peer_ptr(m.rank, vo)
+        ids.offsets[s] = self.buf.peer_ptr(m.rank, oo)
+        ids.weights[s] = self.buf.peer_ptr(m.rank, wo) if kjt.weights is not None else None
+    elif W > 1:
       p = PushIdsParams()
       p.values, p.offsets = kjt.values.data_ptr(), kjt.offsets.data_ptr()
       p.weights = kjt.weights.data_ptr() if kjt.weights is not None else None
@@ -458,6 +525,7 @@ class FusedBackend:
       fp.prefetch = self.fwd_prefetch
       fp.tiled = int(self.fwd_tiled and all(L == 0 for f_, _, _, L in self.layout if f_ in info["feat_names"]))
       fp.total_tiles = info.get("tiles", 0)
+      fp.prefiltered = int(bucket is not None)
       fp.done_counter, fp.seq, fp.status = info["done"].data_ptr(), seq, self.status.data_ptr()
       if info["n_feats"] or W > 1:
         _lib.check_rc(self.lib.recml_emb_fwd(ctypes.byref(fp), c_int(int(training)), c_int(int(gains)), st),

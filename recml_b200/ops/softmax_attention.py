@@ -98,5 +98,6 @@ def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: boo
   offs[1:] = valid.reshape(B, L).sum(1).cumsum(0)
   pack = lambda t: torch.zeros(T + 1, H, Dh, dtype=torch.bfloat16, device=q.device).index_copy(0, dest, flat(t))[:T]
   packed = jagged_softmax_attention(pack(q), pack(k), pack(v), offs, L, causal)
-  out = packed.index_select(0, dest.clamp(max=T - 1)) * valid[:, None, None].to(packed.dtype)
+  # (rows past the last real token are never written by the kernels: select, do not multiply)
+  out = torch.where(valid[:, None, None], packed.index_select(0, dest.clamp(max=T - 1)), torch.zeros((), dtype=packed.dtype, device=q.device))
   return out.reshape(B, L, H, Dh).to(dt)
