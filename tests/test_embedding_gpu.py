@@ -128,3 +128,34 @@ def test_out_of_range_ids_are_reported_not_dereferenced():
   with pytest.raises(_lib.DeviceStatusError, match="outside its table"):
     _lib.check_status(torch.device("cuda"))
   _lib.check_status(torch.device("cuda"))  # the status word was cleared
+
+
+def test_id_dropping_counts_overflow_instead_of_failing():
+  """The occurrence lists are sized from the first batch.  A later batch with far more ids overflows them: with
+  `allow_id_dropping` the surplus ids are left out of the lookup and counted (reference
+  `recml/layers/linen/sparsecore.py:107-108`), without it the overflow is an error at the next status check."""
+  dev = torch.device("cuda")
+  spec = {"f": emb.EmbeddingSpec(5000, 64, combiner="sum")}
+  rng = np.random.default_rng(5)
+  small = emb.KeyedJagged.from_lists({"f": [list(rng.integers(0, 5000, 2)) for _ in range(256)]})
+  big = emb.KeyedJagged.from_lists({"f": [list(rng.integers(0, 5000, 40)) for _ in range(256)]})
+  for allow in (True, False):
+    m = emb.ShardedEmbedding(emb.ShardedEmbeddingConfig(spec, emb.SGDOptimizerSpec(0.1), allow_id_dropping=allow),
+                             device="cuda")
+    m(small.to_device(dev)).sum().backward()
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    before = m.gather_table("f").clone()
+    out = m(big.to_device(dev))
+    out.float().sum().backward()
+    torch.cuda.synchronize()
+    if allow:
+      _lib.check_status(dev)
+      cap = m._backend.stacks[0]["occ_cap"]
+      assert m._backend.dropped_ids() == 256 * 40 - cap
+      assert bool(torch.isfinite(out.float()).all())
+      assert float((m.gather_table("f") - before).abs().max()) > 0       # the ids that fitted were trained
+    else:
+      with pytest.raises(_lib.DeviceStatusError):
+        _lib.check_status(dev)
+      _lib.check_status(dev)
