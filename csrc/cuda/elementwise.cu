@@ -243,6 +243,69 @@ __global__ void relu_mask_kernel(const __nv_bfloat16* __restrict__ dy, long long
   *reinterpret_cast<uint4*>(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// ---- SiLU over a bf16 matrix, and its backward fused with the gathering of the four gradient blocks ------
+// h = z * sigmoid(z), evaluated as t * tanh(t) + t with t = z / 2 (one special-function op per element)
+__device__ __forceinline__ float tanh_approx(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+__device__ __forceinline__ float silu_of(float z) {
+  const float t = 0.5f * z;
+  return fmaf(t, tanh_approx(t), t);
+}
+// d silu / dz = sig + z sig (1 - sig), sig = (tanh(z / 2) + 1) / 2
+__device__ __forceinline__ float silu_grad_of(float z) {
+  const float sig = fmaf(0.5f, tanh_approx(0.5f * z), 0.5f);
+  return fmaf(z * sig, 1.f - sig, sig);
+}
+
+__global__ void silu_fwd_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ h, long long n8) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 A = reinterpret_cast<const uint4*>(z)[i];
+  const uint32_t aw[4] = {A.x, A.y, A.z, A.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = pack_bf16(silu_of(bf16_lo(aw[j])), silu_of(bf16_hi(aw[j])));
+  reinterpret_cast<uint4*>(h)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// The fused u | q | k | v projection of an attention block: z is [T, 4 D]; its four column blocks received the
+// gradients g0 (bf16, row pitch ld0), g1 (FP32 [T, D]: the attention kernels accumulate dq in fp32), g2 and g3
+// (bf16 [T, D]).  dz = (g0 | g1 | g2 | g3) * silu'(z) in one pass instead of a cast, a concatenation and the
+// activation's backward.
+__global__ void silu_bwd_gather4_kernel(const __nv_bfloat16* __restrict__ z, const __nv_bfloat16* __restrict__ g0,
+                                        long long ld0, const float* __restrict__ g1,
+                                        const __nv_bfloat16* __restrict__ g2, const __nv_bfloat16* __restrict__ g3,
+                                        __nv_bfloat16* __restrict__ dz, long long T, int D) {
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8;
+  const long long width = 4LL * D;
+  if (i >= T * width) return;
+  const long long r = i / width;
+  const int c = static_cast<int>(i - r * width);
+  const int part = c / D, cc = c - part * D;
+  float g[8];
+  if (part == 1) {
+    const float4 a = *reinterpret_cast<const float4*>(g1 + r * D + cc);
+    const float4 b = *reinterpret_cast<const float4*>(g1 + r * D + cc + 4);
+    g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+  } else {
+    const __nv_bfloat16* src = part == 0 ? g0 + r * ld0 + cc : (part == 2 ? g2 : g3) + r * D + cc;
+    const uint4 A = *reinterpret_cast<const uint4*>(src);
+    const uint32_t aw[4] = {A.x, A.y, A.z, A.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { g[2 * j] = bf16_lo(aw[j]); g[2 * j + 1] = bf16_hi(aw[j]); }
+  }
+  const uint4 Z = *reinterpret_cast<const uint4*>(z + i);
+  const uint32_t zw[4] = {Z.x, Z.y, Z.z, Z.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    o[j] = pack_bf16(g[2 * j] * silu_grad_of(bf16_lo(zw[j])), g[2 * j + 1] * silu_grad_of(bf16_hi(zw[j])));
+  *reinterpret_cast<uint4*>(dz + i) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // ---- output layer with one unit: y[m] = x[m,:]·w + b ------------------------------------------------
 __global__ void gemv_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int K,
                                 const float* __restrict__ w, const float* __restrict__ bias,
@@ -369,6 +432,26 @@ extern "C" int recml_relu_mask_bf16(const void* dy, long long lddy, const void* 
   relu_mask_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), lddy, static_cast<const __nv_bfloat16*>(y), ldy,
       static_cast<__nv_bfloat16*>(out), ldo, M, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_silu_fwd_bf16(const void* z, void* h, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8) return -2;
+  const long long n8 = n / 8;
+  silu_fwd_kernel<<<static_cast<int>((n8 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(h), n8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_silu_bwd_gather4(const void* z, const void* g0, long long ld0, const float* g1, const void* g2,
+                                      const void* g3, void* dz, long long T, int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || ld0 % 8) return -2;
+  const long long n8 = T * 4 * D / 8;
+  silu_bwd_gather4_kernel<<<static_cast<int>((n8 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(g0), ld0, g1,
+      static_cast<const __nv_bfloat16*>(g2), static_cast<const __nv_bfloat16*>(g3), static_cast<__nv_bfloat16*>(dz), T, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

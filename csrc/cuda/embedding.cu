@@ -834,12 +834,15 @@ struct PushGradParams {
   PeerBf16 dst; unsigned int* done_counter; PeerFlags flags; SeqRef seq;
 };
 
+// Half a warp per (feature, sample): 16 lanes x 16 bytes cover a 128-wide bf16 gradient in one load, which is then
+// stored to every rank that holds rows of the feature's table.
 __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParams p) {
   const int lane = threadIdx.x & 31;
-  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int sub = lane >> 4, sl = lane & 15;
+  const long long halves = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
   const long long total = static_cast<long long>(p.n_feats) * p.B;
-  for (long long item = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; item < total;
-       item += warps) {
+  for (long long item = (((blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5) << 1) + sub; item < total;
+       item += halves) {
     const int fi = static_cast<int>(item % p.n_feats);
     const long long b = item / p.n_feats;
     const PushGradDesc& f = p.feats[fi];
@@ -848,7 +851,7 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
     const long long row = static_cast<long long>(p.me) * p.B + b;
     if (f.kind == kColumnWise) {
       const int dl = f.dim / p.W;
-      for (int e = lane * 2; e < f.dim; e += 64) {
+      for (int e = sl * 2; e < f.dim; e += 32) {
         const int r = e / dl;
         *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * dl + (e - r * dl)) =
             *reinterpret_cast<const uint32_t*>(src + e);
@@ -856,10 +859,21 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
     } else {
       const int r0 = f.kind == kTableWise ? f.owner : 0;
       const int r1 = f.kind == kTableWise ? f.owner + 1 : p.W;
-      for (int e = lane * 2; e < width; e += 64) {
-        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + e);
-        for (int r = r0; r < r1; ++r)
-          *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+      bool vec = (width & 7) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+      for (int r = r0; r < r1; ++r)
+        vec = vec && (reinterpret_cast<uintptr_t>(p.dst.p[r] + f.grad_off[r] + row * width) & 15u) == 0;
+      if (vec) {
+        for (int e = sl * 8; e < width; e += 128) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src + e);
+          for (int r = r0; r < r1; ++r)
+            *reinterpret_cast<uint4*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+        }
+      } else {
+        for (int e = sl * 2; e < width; e += 32) {
+          const uint32_t v = *reinterpret_cast<const uint32_t*>(src + e);
+          for (int r = r0; r < r1; ++r)
+            *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+        }
       }
     }
   }

@@ -29,7 +29,7 @@ import torch.distributed as dist
 from recml_b200 import embedding as emb
 from recml_b200.data import synthetic
 
-NVLINK_BPS = 770e9          # measured peer-copy bandwidth per direction per GPU on this pool
+NVLINK_BPS = 770e9          # measured peer-copy bandwidth per direction per B200 over NVSwitch (900e9 nominal)
 
 
 def _hbm_bps() -> float:
@@ -39,7 +39,7 @@ def _hbm_bps() -> float:
     with open(path) as f:
       return float(json.load(f)["hbm_gbs"]) * 1e9
   except (OSError, KeyError, ValueError):
-    return 6.65e12         # earlier measurement on the same pool, used when the file is absent
+    return 6.65e12         # a measured B200 copy bandwidth, used when the file is absent
 
 
 def geometry(n_tables: int, vocab_scale: float):

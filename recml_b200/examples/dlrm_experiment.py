@@ -11,6 +11,7 @@ from __future__ import annotations
 import dataclasses
 from typing import Any, Mapping, Sequence
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -58,6 +59,46 @@ class CriteoFactory(types.Factory[Any]):
         seed=self.seed, rank=rank, alpha=self.alpha, steps=self.steps, num_dense=self.model.num_dense,
         pin=torch.cuda.is_available())
     return iterator_lib.IterableIterator(ds)
+
+
+@dataclasses.dataclass
+class CriteoExampleFactory(types.Factory[Any]):
+  """Per-example Criteo `tf.Example` files (`label`, `dense` = 13 floats, `cat_0` .. `cat_25` = id lists) read
+  through the native TFRecord factory.  The host id pipeline finishes every batch: it packs the categorical
+  features into the jagged layout the sharded embedding consumes, in the embedding's feature order, and (with
+  `stats_dir`) keeps the per-table maxima of ids and unique ids per shard that feedback-directed sizing reads
+  back (`StatsRecorder.load`)."""
+  model: ModelConfig
+  input_path: str
+  batch_size: int            # global
+  is_training: bool = True
+  stats_dir: str | None = None
+
+  def make(self):
+    from recml_b200.data import tfrecord_factory as F
+    from recml_b200.embedding import id_pipeline
+    n_cat = len(self.model.vocab_sizes)
+    names = [f"cat_{i}" for i in range(n_cat)]
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    recorder = id_pipeline.StatsRecorder(self.stats_dir, rank) if self.stats_dir else None
+    pack = id_pipeline.ShardedPreprocessor(names, output_key="sparse", world=world, recorder=recorder,
+                                           pin=torch.cuda.is_available())
+
+    def finish(feats: dict) -> dict:
+      out = pack(feats)
+      out["dense"] = torch.from_numpy(np.ascontiguousarray(out["dense"], dtype=np.float32))
+      out["label"] = torch.from_numpy(np.ascontiguousarray(out["label"], dtype=np.float32).reshape(-1))
+      return out
+
+    spec = {"label": F.FixedLenFeature((1,), "float32"), "dense": F.FixedLenFeature((self.model.num_dense,), "float32")}
+    spec.update({n: F.VarLenFeature("int64") for n in names})
+    fac = F.TFDatasetFactory(input_path=self.input_path, global_batch_size=self.batch_size, feature_spec=spec,
+                             shuffle=self.is_training, shuffle_buffer_size=10_000 if self.is_training else 0,
+                             repeat=self.is_training, postprocessors=[finish])
+    it = fac.make()
+    it.stats_recorder = recorder
+    return it
 
 
 class PredictionTask(task_lib.Task):

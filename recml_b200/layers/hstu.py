@@ -104,7 +104,7 @@ class HSTUBlock(nn.Module):
   def _finish(self, x, u, attn):
     y = norm_ops.layer_norm(attn, self.attn_norm_w, self.attn_norm_b, self.eps, gate=u, norm_dims=2)
     y = y.reshape(*x.shape[:-1], self.model_dim)
-    return dense_ops.linear(y, self.out, self.out_bias).to(x.dtype) + x
+    return dense_ops.linear(y, self.out, self.out_bias, residual=x).to(x.dtype)
 
   def forward(self, inputs: torch.Tensor, attention_mask: torch.Tensor, attention_bias: torch.Tensor | None = None):
     """Dense form: inputs `[B, L, D]`, mask / bias `[B, L, L]`."""
@@ -130,11 +130,24 @@ class HSTUBlock(nn.Module):
     """Packed form: tokens `[T, D]`; causal pointwise attention inside every sequence.  `segment_ids [T]`
     restricts a query to keys of its own segment; `row_mask [T]` zeroes the attention output of the rows
     where it is 0 (padded positions of a dense batch that is run through the packed kernels)."""
-    u, q, k, v = self._project(tokens)
     scale = 1.0 / math.sqrt(self.head_dim) if self.scaled else 1.0
-    attn = attn_ops.jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
-                                               timestamps=timestamps, causal=True, scale=scale,
-                                               segment_ids=segment_ids)
+    z = None
+    if self.activation is torch.nn.functional.silu and tokens.is_cuda:
+      n = norm_ops.layer_norm(tokens, self.input_norm_w, self.input_norm_b, self.eps)
+      z = dense_ops.linear(n, self.uqkv, self.uqkv_bias)
+    if z is not None and attn_ops.fused_block_ok(z, self.head_dim):
+      # activation, split and attention as one autograd node: see `silu_split_attention`
+      u, attn = attn_ops.silu_split_attention(z, self.num_heads, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
+                                              timestamps=timestamps, causal=True, scale=scale,
+                                              segment_ids=segment_ids)
+    else:
+      if z is not None:
+        u, q, k, v = self.activation(z).reshape(*tokens.shape[:-1], 4, self.num_heads, self.head_dim).unbind(dim=-3)
+      else:
+        u, q, k, v = self._project(tokens)
+      attn = attn_ops.jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
+                                                 timestamps=timestamps, causal=True, scale=scale,
+                                                 segment_ids=segment_ids)
     if row_mask is not None:
       attn = attn * row_mask[:, None, None].to(attn.dtype)
     return self._finish(tokens, u, attn)

@@ -319,19 +319,26 @@ class JoinColumnsFn(torch.autograd.Function):
 
 
 class LinearFn(torch.autograd.Function):
-  """Single linear layer (+ optional ReLU) for callers outside an MLP stack; works on the last
-  dim of an arbitrary-rank bf16 activation."""
+  """Single linear layer (+ optional ReLU, or + a residual added in the GEMM's epilogue) for callers outside
+  an MLP stack; works on the last dim of an arbitrary-rank bf16 activation."""
 
   @staticmethod
-  def forward(ctx, x, w, b, relu):
+  def forward(ctx, x, w, b, relu, residual=None):
     shp = x.shape
     x2 = x.detach().reshape(-1, shp[-1])
     if x2.dtype != torch.bfloat16 or x2.stride(-1) != 1 or x2.stride(0) % 8:
       x2 = x2.to(torch.bfloat16).contiguous()
     w16 = bf16_weight(w)
-    y = G.gemm(x2, w16, bias=None if b is None else b.detach(), relu=relu)
+    if residual is not None:
+      r2 = residual.detach().reshape(-1, w.shape[0])
+      if r2.dtype != torch.bfloat16 or r2.stride(-1) != 1 or r2.stride(0) % 8:
+        r2 = r2.to(torch.bfloat16).contiguous()
+      y = G.gemm(x2, w16, bias=None if b is None else b.detach(), epi=G.EPI_ADD, aux0=r2)
+    else:
+      y = G.gemm(x2, w16, bias=None if b is None else b.detach(), relu=relu)
     ctx.save = (x2, w16, y if relu else None)
     ctx.has_bias, ctx.shape, ctx.dtype, ctx.w_dtype = b is not None, shp, x.dtype, w.dtype
+    ctx.res = None if residual is None else (residual.shape, residual.dtype)
     return y.view(*shp[:-1], w.shape[0])
 
   @staticmethod
@@ -345,11 +352,16 @@ class LinearFn(torch.autograd.Function):
     dw = G.gemm(g, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
     db = ew.colsum(g) if ctx.has_bias else None
     dx = G.gemm(g, w16, b_mn=True).view(ctx.shape).to(ctx.dtype)
-    return dx, dw.to(ctx.w_dtype), db, None
+    dres = None if ctx.res is None else dy.reshape(ctx.res[0]).to(ctx.res[1])
+    return dx, dw.to(ctx.w_dtype), db, None, dres
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, relu: bool = False):
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, relu: bool = False,
+           residual: torch.Tensor | None = None):
+  """y = x w^T + b (+ ReLU) (+ residual).  `residual` (same shape as y) is added in the GEMM's epilogue."""
   if not x.is_cuda or w.shape[0] % 8 or w.shape[1] % 8:
     y = torch.nn.functional.linear(x.to(w.dtype), w, b)
-    return torch.relu(y) if relu else y
-  return LinearFn.apply(x, w, b, relu)
+    y = torch.relu(y) if relu else y
+    return y if residual is None else y + residual.to(y.dtype)
+  assert not (relu and residual is not None)
+  return LinearFn.apply(x, w, b, relu, residual)

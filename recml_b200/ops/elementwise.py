@@ -87,6 +87,26 @@ def relu_mask(dy, y, out=None):
   return out
 
 
+def silu_bf16(z: torch.Tensor) -> torch.Tensor:
+  """SiLU of a contiguous bf16 tensor (one pass, tanh-based)."""
+  h = torch.empty_like(z)
+  _lib.check_rc(_lib.cuda().recml_silu_fwd_bf16(_lib.ptr(z), _lib.ptr(h), c_ll(z.numel()), _lib.stream()), "silu_fwd")
+  return h
+
+
+def silu_bwd_gather4(z, g0, g1_f32, g2, g3):
+  """dz `[T, 4 D]` = (g0 | g1 | g2 | g3) * silu'(z) for the pre-activation `z [T, 4 D]` of a fused four-way
+  projection: g0 bf16 `[T, D]` (any row pitch), g1 fp32 `[T, D]`, g2 / g3 bf16 `[T, D]`, all with unit column
+  stride."""
+  T, W4 = z.shape
+  D = W4 // 4
+  dz = torch.empty_like(z)
+  _lib.check_rc(_lib.cuda().recml_silu_bwd_gather4(_lib.ptr(z), _lib.ptr(g0), c_ll(g0.stride(0)), _lib.ptr(g1_f32),
+                                                   _lib.ptr(g2), _lib.ptr(g3), _lib.ptr(dz), c_ll(T), c_int(D),
+                                                   _lib.stream()), "silu_bwd_gather4")
+  return dz
+
+
 def gemv_fwd(x, w, bias):
   """fp32 `[M]` = bf16 `[M, K]` · fp32 `[K]` + bias."""
   if not x.is_cuda:

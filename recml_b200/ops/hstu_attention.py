@@ -205,6 +205,66 @@ class _JaggedAttnFn(torch.autograd.Function):
     return dq, dk, dv, dpos, dts, None, None, None, None, None, None, None
 
 
+class _SiluSplitAttnFn(torch.autograd.Function):
+  """(u, attention(q, k, v)) with u | q | k | v = silu(z) for the pre-activation `z [T, 4 H Dh]` of a block's
+  fused projection.  One pass computes the activation; the backward takes dq from the attention kernels as the
+  fp32 they accumulate and forms dz = (du | dq | dk | dv) * silu'(z) in one pass (no cast, no concatenation, no
+  separate activation backward)."""
+
+  @staticmethod
+  def forward(ctx, z, num_heads, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids):
+    from recml_b200.ops import elementwise as ew, hstu_cuda
+    T, W4 = z.shape
+    D = W4 // 4
+    h = ew.silu_bf16(z).view(T, 4, num_heads, D // num_heads)
+    u, q, k, v = h.unbind(1)
+    bc = hstu_cuda.bias_context(seq_offsets, timestamps, pos_w, ts_w, T, max_seq_len, causal, window, segment_ids)
+    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    ctx.save_for_backward(z, h, pos_w, ts_w, seq_offsets)
+    ctx.meta = (max_seq_len, causal, scale)
+    ctx.bias_ctx = bc
+    bc.pending += 1
+    bc.want_bias_grad = bc.want_bias_grad or ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
+    return u, o
+
+  @staticmethod
+  def backward(ctx, du, do):
+    from recml_b200.ops import elementwise as ew, hstu_cuda
+    z, h, pos_w, ts_w, seq_offsets = ctx.saved_tensors
+    max_seq_len, causal, scale = ctx.meta
+    bc = ctx.bias_ctx
+    _, q, k, v = h.unbind(1)
+    T, D = z.shape[0], z.shape[1] // 4
+    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dq_fp32=True)
+    bc.pending -= 1
+    dpos = dts = None
+    if bc.pending <= 0 and bc.want_bias_grad:
+      dpos, dts = bc.table_gradients(pos_w, ts_w)
+      bc.want_bias_grad = False
+    g0 = du.reshape(T, D)
+    if g0.dtype != torch.bfloat16 or g0.stride(1) != 1 or g0.stride(0) % 8:
+      g0 = g0.to(torch.bfloat16).contiguous()
+    dz = ew.silu_bwd_gather4(z, g0, dq.view(T, D), dk.view(T, D), dv.view(T, D))
+    return dz, None, dpos, dts, None, None, None, None, None, None, None
+
+
+def silu_split_attention(z, num_heads: int, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None, timestamps=None,
+                         causal: bool = True, scale: float = 1.0, sliding_window_size: int | None = None,
+                         segment_ids=None):
+  """`z [T, 4 D]` bf16, contiguous: the pre-activation of an HSTU block's u | q | k | v projection.  Returns
+  (u `[T, H, Dh]`, attention output `[T, H, Dh]`); CUDA only (callers check `fused_block_ok`)."""
+  from recml_b200.ops import hstu_cuda
+  return _SiluSplitAttnFn.apply(z, num_heads, pos_w, ts_w, hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len,
+                                causal, scale, sliding_window_size, segment_ids)
+
+
+def fused_block_ok(z: torch.Tensor, head_dim: int) -> bool:
+  if not (z.is_cuda and z.dtype == torch.bfloat16 and z.is_contiguous() and head_dim in (64, 128)):
+    return False
+  from recml_b200.ops import hstu_cuda
+  return hstu_cuda.available()
+
+
 def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
                                timestamps=None, causal: bool = True, scale: float = 1.0,
                                sliding_window_size: int | None = None, segment_ids=None):

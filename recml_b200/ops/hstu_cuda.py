@@ -310,9 +310,10 @@ def forward(q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale):
   return out
 
 
-def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale):
+def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale, dq_fp32: bool = False):
   """Gradients w.r.t. q, k, v; the score gradients go into the context's block buffer when a bias table
-  wants a gradient."""
+  wants a gradient.  `dq_fp32` returns dq as the kernel accumulated it (fp32) for a caller that converts it
+  in a pass of its own."""
   lib = _lib.cuda()
   tiles = _tiles(seq_offsets, q.shape[0], backward=True)
   do = as_rows(do)
@@ -325,7 +326,7 @@ def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, sca
     p.dbias_tiles = bc.gradient_blocks().data_ptr()
   _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do),
                                         ctypes.byref(p), c_int(tiles[2]), _lib.stream()), "hstu_attn_bwd")
-  return dq.to(q.dtype), dk, dv
+  return (dq if dq_fp32 else dq.to(q.dtype)), dk, dv
 
 
 # ---- softmax mode: the same kernels with P = softmax(scale * QK^T) over the visible keys ----------------------

@@ -275,3 +275,41 @@ def test_dense_hstu_runs_on_the_packed_kernels_and_matches_the_dense_formulation
   for n, p in gm.named_parameters():
     if n in ref_grads and ref_grads[n].abs().max() > 0:
       _compare(ref_grads[n], p.grad, 8e-2, n)
+
+
+def test_block_with_fused_activation_node_matches_unfused(monkeypatch):
+  """`HSTUBlock.forward_jagged` runs activation + split + attention as one autograd node (fp32 dq consumed by the
+  fused SiLU backward, residual added in the output GEMM's epilogue); the unfused composition of the same kernels
+  must give the same outputs and parameter gradients."""
+  from recml_b200.layers import hstu as hstu_layers
+  from recml_b200.ops import hstu_attention as attn_ops
+  torch.manual_seed(0)
+  D, H = 256, 4
+  lens = torch.tensor([300, 17, 129, 256])
+  offs = torch.zeros(5, dtype=torch.int64)
+  offs[1:] = lens.cumsum(0)
+  T = int(offs[-1])
+  x = (torch.randn(T, D, device="cuda") * 0.5).to(torch.bfloat16)
+  g = (torch.randn(T, D, device="cuda") * 0.1).to(torch.bfloat16)
+  pos_w = (torch.randn(2 * 512 - 1, device="cuda") * 0.1).requires_grad_()
+
+  def run(fused: bool):
+    torch.manual_seed(1)
+    blk = hstu_layers.HSTUBlock(D, H).cuda().to(torch.bfloat16)
+    if not fused:
+      monkeypatch.setattr(attn_ops, "fused_block_ok", lambda z, hd: False)
+    xi = x.clone().requires_grad_()
+    pw = pos_w.detach().clone().requires_grad_()
+    out = blk.forward_jagged(xi, offs.cuda(), 512, pos_w=pw)
+    out.backward(g)
+    monkeypatch.undo()
+    return out.detach().float(), xi.grad.float(), pw.grad.float(), {n: p.grad.float() for n, p in blk.named_parameters()}
+
+  of, dxf, dpf, gf = run(True)
+  ou, dxu, dpu, gu = run(False)
+  tol = lambda ref: 2e-2 * float(ref.abs().max()) + 1e-6
+  assert float((of - ou).abs().max()) <= tol(ou)
+  assert float((dxf - dxu).abs().max()) <= tol(dxu)
+  assert float((dpf - dpu).abs().max()) <= tol(dpu)
+  for n in gu:
+    assert float((gf[n] - gu[n]).abs().max()) <= tol(gu[n]), n

@@ -298,3 +298,40 @@ def test_repeat_fills_batches_across_epochs(tmp_path):
                            sharding_info=F.DatasetShardingInfo(1, 0))
   it = iter(big.make())
   assert next(it)["x"][:, 0].tolist() == [0, 1, 2, 3, 4, 0, 1, 2]
+
+
+def test_criteo_example_factory_packs_with_the_host_id_pipeline(tmp_path):
+  """Per-example Criteo records -> batches whose `sparse` entry is the jagged layout of the embedding (feature
+  major, the ids in record order) built by the native packer, with per-table shard statistics recorded."""
+  from recml_b200.embedding import id_pipeline
+  from recml_b200.examples import dlrm_experiment as D
+  vocab, bags = (50, 1000, 7), (2, 5, 1)
+  cfg = D.ModelConfig(vocab_sizes=vocab, bag_sizes=bags, num_dense=4)
+  rng = np.random.default_rng(0)
+  rows = []
+  for i in range(24):
+    f = {"label": [float(i % 2)], "dense": [float(x) for x in rng.random(4)]}
+    for c, (v, b) in enumerate(zip(vocab, bags)):
+      f[f"cat_{c}"] = [int(x) for x in rng.integers(0, v, int(rng.integers(0, b + 1)))]
+    rows.append(f)
+  tfrecord.write_tfrecord(str(tmp_path / "criteo-0.tfrecord"), [tfrecord.encode_example(f) for f in rows])
+  fac = D.CriteoExampleFactory(model=cfg, input_path=str(tmp_path / "criteo-*.tfrecord"), batch_size=8,
+                               is_training=False, stats_dir=str(tmp_path / "fdo"))
+  it = fac.make()
+  seen = 0
+  for batch in it:
+    kjt = batch["sparse"]
+    B = kjt.batch_size()
+    assert kjt.keys == ("cat_0", "cat_1", "cat_2") and batch["dense"].shape == (B, 4) and batch["label"].shape == (B,)
+    offs, vals = kjt.offsets.numpy(), kjt.values.numpy()
+    for c in range(3):
+      for b in range(B):
+        want = rows[seen + b][f"cat_{c}"]
+        got = vals[offs[c * B + b]:offs[c * B + b + 1]].tolist()
+        assert got == want
+    seen += B
+  assert seen == 24
+  path = it.stats_recorder.publish()
+  assert os.path.exists(path)
+  stats = id_pipeline.StatsRecorder(str(tmp_path / "fdo")).load()
+  assert set(stats) == {"cat_0", "cat_1", "cat_2"} and stats["cat_1"].max_ids_per_partition >= 1
