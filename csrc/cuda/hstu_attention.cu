@@ -86,9 +86,28 @@ struct Params {
   // is read out.  Both use the bf16-rounded P that the tensor cores saw, so the two halves cancel as they should.
   float* dcum;
   const __nv_bfloat16* v_rows;   // v as a plain pointer (row pitch ld_v) for that dot product
+  // Attention-weight dropout (SiLU mode): element (head, query token, key token) is kept when a counter-based hash
+  // of its indices and the 64-bit key is at or above drop_threshold = p * 2^32; kept weights are scaled by keep_scale
+  // = 1 / (1 - p).  The backward pass regenerates the same mask from the same key.
+  const unsigned long long* dropout_key;
+  unsigned int drop_threshold;
+  float keep_scale;
 };
 
-enum Mode { kSilu = 0, kSoftmax = 1, kDecay = 2 };
+enum Mode { kSilu = 0, kSoftmax = 1, kDecay = 2, kSiluDropout = 3 };
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+// per (head, query token) part of the dropout hash, and the per-element decision
+__device__ __forceinline__ uint32_t dropout_row_hash(unsigned long long key, int head, int q_token) {
+  return mix32(static_cast<uint32_t>(key) ^ (static_cast<uint32_t>(q_token) * 0x9E3779B1u) ^
+               (static_cast<uint32_t>(head + 1) * 0x85EBCA6Bu));
+}
+__device__ __forceinline__ bool dropout_keep(uint32_t row_hash, uint32_t key_hi, int k_token, uint32_t threshold) {
+  return mix32(row_hash ^ (static_cast<uint32_t>(k_token) * 0xC2B2AE35u + key_hi)) >= threshold;
+}
 
 constexpr float kMaskedHalfBias = -15000.f;
 
@@ -397,7 +416,8 @@ template <int DH, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
-  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu, DECAY = MODE == kDecay;
+  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu || MODE == kSiluDropout, DECAY = MODE == kDecay;
+  constexpr bool DROP = MODE == kSiluDropout;
   using S = Smem<DH>;
   // CTAs are dispatched in linear block order; heads vary fastest so that this order follows the work-sorted list
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;
@@ -639,6 +659,12 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // SiLU mode.  With h = (s * scale + bias) / 2:  silu(2h) = 2h * sigmoid(2h) = h * tanh(h) + h.  The
       // pair's bias tile brings bias / 2 (and the masks); 1 / n is applied once, to the output.
       const float hs = 0.5f * p.scale;
+      uint32_t drop_row = 0, drop_hi = 0;
+      if constexpr (DROP) {
+        const unsigned long long key = *p.dropout_key;
+        drop_row = dropout_row_hash(key, h, tok0 + r);
+        drop_hi = static_cast<uint32_t>(key >> 32);
+      }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int sb = j & 1;
         const uint4* bt = reinterpret_cast<const uint4*>(
@@ -662,7 +688,13 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int k = 0; k < 4; ++k) {
               const float h0 = fmaf(__uint_as_float(v[g * 8 + 2 * k]), hs, bf16_lo(w[k]));
               const float h1 = fmaf(__uint_as_float(v[g * 8 + 2 * k + 1]), hs, bf16_hi(w[k]));
-              packed[k] = pack_bf16(fmaf(h0, tanh_fast(h0), h0), fmaf(h1, tanh_fast(h1), h1));
+              float p0 = fmaf(h0, tanh_fast(h0), h0), p1 = fmaf(h1, tanh_fast(h1), h1);
+              if constexpr (DROP) {
+                const int kt = seq_start + j * BKV + cb * 32 + g * 8 + 2 * k;
+                p0 = dropout_keep(drop_row, drop_hi, kt, p.drop_threshold) ? p0 * p.keep_scale : 0.f;
+                p1 = dropout_keep(drop_row, drop_hi, kt + 1, p.drop_threshold) ? p1 * p.keep_scale : 0.f;
+              }
+              packed[k] = pack_bf16(p0, p1);
             }
             // 32 columns = 64 bytes = four 16-byte chunks of row r in 64-column sub-tile cb / 2
             const int chunk = ((cb & 1) * 4 + g) ^ (r & 7);
@@ -728,7 +760,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const Params p) {
-  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu, DECAY = MODE == kDecay;
+  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu || MODE == kSiluDropout, DECAY = MODE == kDecay;
+  constexpr bool DROP = MODE == kSiluDropout;
   using S = SmemB<DH>;
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;   // heads fastest: dispatch order = work-sorted list order
   const int tile_id = lin / p.H;
@@ -859,6 +892,12 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint4 hb[4];
       size_t pair_off = 0;
       float cl = 0.f;
+      uint32_t drop_row = 0, drop_hi = 0;
+      if constexpr (DROP) {
+        const unsigned long long key = *p.dropout_key;
+        drop_row = dropout_row_hash(key, h, seq_start + qi);
+        drop_hi = static_cast<uint32_t>(key >> 32);
+      }
       if constexpr (DECAY) {
         cl = cum_h[qi];
       } else if constexpr (SOFTMAX) {
@@ -917,8 +956,11 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const float t = tanh_fast(hv);
                 const float pv = fmaf(hv, t, hv);
                 const float sig = fmaf(0.5f, t, 0.5f);
-                pr[u] = pv;
-                dr[u] = dp * fmaf(pv, 1.f - sig, sig);
+                float keep = 1.f;
+                if constexpr (DROP)
+                  keep = dropout_keep(drop_row, drop_hi, seq_start + kv0 + cb * 32 + col, p.drop_threshold) ? p.keep_scale : 0.f;
+                pr[u] = pv * keep;
+                dr[u] = dp * keep * fmaf(pv, 1.f - sig, sig);
               }
               dsv[2 * k + u] = dr[u];
             }
@@ -1085,7 +1127,8 @@ static int launch_fwd(const void* q, const void* k, const void* v, const Params&
 extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, const Params* p, int n_tiles,
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
-  if (p->mode == kSilu && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if ((p->mode == kSilu || p->mode == kSiluDropout) && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->mode == kSiluDropout && p->dropout_key == nullptr) return -14;
   if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->cum_pitch < p->T + BKV)) return -13;
   if (p->mode != kDecay && p->qk_shared) return -13;
 #define RECML_ATTN_FWD(D)                                                                  \
@@ -1093,6 +1136,7 @@ extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, 
     case kSilu: return launch_fwd<D, kSilu>(q, k, v, *p, n_tiles, stream);                 \
     case kSoftmax: return launch_fwd<D, kSoftmax>(q, k, v, *p, n_tiles, stream);           \
     case kDecay: return launch_fwd<D, kDecay>(q, k, v, *p, n_tiles, stream);               \
+    case kSiluDropout: return launch_fwd<D, kSiluDropout>(q, k, v, *p, n_tiles, stream);   \
     default: return -10;                                                                   \
   }
   if (p->Dh == 64) RECML_ATTN_FWD(64)
@@ -1130,7 +1174,8 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
                                    int n_tiles, cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->num_buckets + 1 > 256) return -11;
-  if (p->mode == kSilu && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if ((p->mode == kSilu || p->mode == kSiluDropout) && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
+  if (p->mode == kSiluDropout && p->dropout_key == nullptr) return -14;
   if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->dk_acc == nullptr || p->cum_pitch < p->T + BKV))
     return -13;
   if (p->mode != kDecay && p->qk_shared) return -13;
@@ -1139,6 +1184,7 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
     case kSilu: return launch_bwd<D, kSilu>(q, k, v, d_o, *p, n_tiles, stream);            \
     case kSoftmax: return launch_bwd<D, kSoftmax>(q, k, v, d_o, *p, n_tiles, stream);      \
     case kDecay: return launch_bwd<D, kDecay>(q, k, v, d_o, *p, n_tiles, stream);          \
+    case kSiluDropout: return launch_bwd<D, kSiluDropout>(q, k, v, d_o, *p, n_tiles, stream); \
     default: return -10;                                                                   \
   }
   if (p->Dh == 64) RECML_ATTN_BWD(64)

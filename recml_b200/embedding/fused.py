@@ -432,8 +432,8 @@ class FusedBackend:
     if kjt.batch_size() != self.B:
       raise ValueError(f"fused backend was set up for batch {self.B}, got {kjt.batch_size()}")
     streams.join("emb_bwd", "emb_sort", device=dev)    # the previous step's table update comes first
-    if kjt.values.numel() > self.nnz_cap:
-      raise ValueError(f"batch has {kjt.values.numel()} ids, capacity is {self.nnz_cap}")
+    if W > 1 and kjt.values.numel() > self.nnz_cap:      # the exchange buffers of the peers are sized for this
+      raise ValueError(f"batch has {kjt.values.numel()} ids, the id exchange buffers hold {self.nnz_cap}")
     assert kjt.values.dtype == torch.int32 and kjt.offsets.dtype == torch.int32
     if training:
       self._ensure_occ(kjt)

@@ -139,7 +139,8 @@ class HSTUBlock(nn.Module):
       # activation, split and attention as one autograd node: see `silu_split_attention`
       u, attn = attn_ops.silu_split_attention(z, self.num_heads, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
                                               timestamps=timestamps, causal=True, scale=scale,
-                                              segment_ids=segment_ids)
+                                              segment_ids=segment_ids,
+                                              dropout_p=self.dropout_p if self.training else 0.0)
     else:
       if z is not None:
         u, q, k, v = self.activation(z).reshape(*tokens.shape[:-1], 4, self.num_heads, self.head_dim).unbind(dim=-3)
@@ -147,7 +148,8 @@ class HSTUBlock(nn.Module):
         u, q, k, v = self._project(tokens)
       attn = attn_ops.jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
                                                  timestamps=timestamps, causal=True, scale=scale,
-                                                 segment_ids=segment_ids)
+                                                 segment_ids=segment_ids,
+                                                 dropout_p=self.dropout_p if self.training else 0.0)
     if row_mask is not None:
       attn = attn * row_mask[:, None, None].to(attn.dtype)
     return self._finish(tokens, u, attn)
@@ -210,12 +212,10 @@ class HSTU(nn.Module):
 
   def _packed_kernels_apply(self, e: torch.Tensor) -> bool:
     """The dense (padded) call can run on the packed attention kernels: CUDA, head dim 64 / 128, SiLU
-    attention without attention dropout, and (when there is a relative bias) a position table made for this
-    padded length."""
+    attention (attention-weight dropout included) and, when there is a relative bias, a position table made for
+    this padded length."""
     b = self.decoder_blocks[0]
     if not e.is_cuda or b.head_dim not in (64, 128) or b.softmax or b.scaled:
-      return False
-    if self.training and b.dropout_p > 0:
       return False
     return self.relative_bias is None or self.max_seq_len == e.shape[1]
 

@@ -152,8 +152,11 @@ def q_sharded_pointwise_attention(mask_type: MaskType | str, q, k, v, *, group=N
 
 def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
                                timestamps=None, causal: bool = True, scale: float = 1.0,
-                               sliding_window_size: int | None = None, segment_ids=None):
-  """fp32 torch oracle for the packed kernel: q, k, v `[T, H, Dh]`, `seq_offsets [B+1]`."""
+                               sliding_window_size: int | None = None, segment_ids=None, dropout_p: float = 0.0,
+                               dropout_key: int | None = None):
+  """fp32 torch oracle for the packed kernel: q, k, v `[T, H, Dh]`, `seq_offsets [B+1]`.  With `dropout_key`
+  the attention weights are dropped with the kernels' own mask (`hstu_cuda.dropout_keep_mask`); with a rate and
+  no key, by `torch.nn.functional.dropout`."""
   out = torch.zeros_like(q, dtype=torch.float32)
   offs = seq_offsets.tolist()
   for b in range(len(offs) - 1):
@@ -171,19 +174,45 @@ def jagged_attention_reference(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=
     if segment_ids is not None:
       m = m & (segment_ids[a:e, None] == segment_ids[None, a:e])
     p = torch.where(m[None], p, torch.zeros_like(p))
+    if dropout_p > 0 and dropout_key is not None:
+      from recml_b200.ops import hstu_cuda
+      tok = torch.arange(a, e, device=q.device)
+      keep = torch.stack([hstu_cuda.dropout_keep_mask(dropout_key, h, tok, tok, dropout_p) for h in range(q.shape[1])])
+      p = torch.where(keep, p / (1.0 - dropout_p), torch.zeros_like(p))
+    elif dropout_p > 0:
+      p = torch.nn.functional.dropout(p, dropout_p)
     out[a:e] = torch.einsum("hts,shd->thd", p, v[a:e].float())
   return out.to(q.dtype)
 
 
+LAST_DROPOUT_KEY: torch.Tensor | None = None     # key of the most recent dropout mask (tests read it back)
+
+
+def _draw_dropout(rate: float, device):
+  """(rate, key) for the kernels, or None: the key is one random int64 drawn on the device (no host sync; under
+  CUDA-graph capture it comes from the generator's captured state like any other random op)."""
+  global LAST_DROPOUT_KEY
+  if not rate or rate <= 0.0:
+    return None
+  if rate >= 1.0:
+    raise ValueError("attention dropout rate must be below 1")
+  key = torch.empty(1, dtype=torch.int64, device=device).random_()
+  LAST_DROPOUT_KEY = key
+  return (float(rate), key)
+
+
 class _JaggedAttnFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, q, k, v, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids):
+  def forward(ctx, q, k, v, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids,
+              dropout_p=0.0):
     from recml_b200.ops import hstu_cuda
     bc = hstu_cuda.bias_context(seq_offsets, timestamps, pos_w, ts_w, q.shape[0], max_seq_len, causal, window,
                                 segment_ids)
-    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    drop = _draw_dropout(dropout_p, q.device)
+    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dropout=drop)
     ctx.save_for_backward(q, k, v, pos_w, ts_w, seq_offsets)
     ctx.meta = (max_seq_len, causal, scale)
+    ctx.drop = drop
     ctx.bias_ctx = bc
     if any(ctx.needs_input_grad):       # this call may see a backward: the step's last one finishes the bias tables
       bc.pending += 1
@@ -196,13 +225,13 @@ class _JaggedAttnFn(torch.autograd.Function):
     q, k, v, pos_w, ts_w, seq_offsets = ctx.saved_tensors
     max_seq_len, causal, scale = ctx.meta
     bc = ctx.bias_ctx
-    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dropout=ctx.drop)
     bc.pending -= 1
     dpos = dts = None
     if bc.pending <= 0 and bc.want_bias_grad:
       dpos, dts = bc.table_gradients(pos_w, ts_w)
       bc.want_bias_grad = False
-    return dq, dk, dv, dpos, dts, None, None, None, None, None, None, None
+    return dq, dk, dv, dpos, dts, None, None, None, None, None, None, None, None
 
 
 class _SiluSplitAttnFn(torch.autograd.Function):
@@ -212,16 +241,19 @@ class _SiluSplitAttnFn(torch.autograd.Function):
   separate activation backward)."""
 
   @staticmethod
-  def forward(ctx, z, num_heads, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids):
+  def forward(ctx, z, num_heads, pos_w, ts_w, seq_offsets, timestamps, max_seq_len, causal, scale, window, segment_ids,
+              dropout_p=0.0):
     from recml_b200.ops import elementwise as ew, hstu_cuda
     T, W4 = z.shape
     D = W4 // 4
     h = ew.silu_bf16(z).view(T, 4, num_heads, D // num_heads)
     u, q, k, v = h.unbind(1)
     bc = hstu_cuda.bias_context(seq_offsets, timestamps, pos_w, ts_w, T, max_seq_len, causal, window, segment_ids)
-    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale)
+    drop = _draw_dropout(dropout_p, z.device)
+    o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dropout=drop)
     ctx.save_for_backward(z, h, pos_w, ts_w, seq_offsets)
     ctx.meta = (max_seq_len, causal, scale)
+    ctx.drop = drop
     ctx.bias_ctx = bc
     bc.pending += 1
     bc.want_bias_grad = bc.want_bias_grad or ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
@@ -235,7 +267,8 @@ class _SiluSplitAttnFn(torch.autograd.Function):
     bc = ctx.bias_ctx
     _, q, k, v = h.unbind(1)
     T, D = z.shape[0], z.shape[1] // 4
-    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dq_fp32=True)
+    dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dq_fp32=True,
+                                    dropout=ctx.drop)
     bc.pending -= 1
     dpos = dts = None
     if bc.pending <= 0 and bc.want_bias_grad:
@@ -245,17 +278,17 @@ class _SiluSplitAttnFn(torch.autograd.Function):
     if g0.dtype != torch.bfloat16 or g0.stride(1) != 1 or g0.stride(0) % 8:
       g0 = g0.to(torch.bfloat16).contiguous()
     dz = ew.silu_bwd_gather4(z, g0, dq.view(T, D), dk.view(T, D), dv.view(T, D))
-    return dz, None, dpos, dts, None, None, None, None, None, None, None
+    return dz, None, dpos, dts, None, None, None, None, None, None, None, None
 
 
 def silu_split_attention(z, num_heads: int, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None, timestamps=None,
                          causal: bool = True, scale: float = 1.0, sliding_window_size: int | None = None,
-                         segment_ids=None):
+                         segment_ids=None, dropout_p: float = 0.0):
   """`z [T, 4 D]` bf16, contiguous: the pre-activation of an HSTU block's u | q | k | v projection.  Returns
   (u `[T, H, Dh]`, attention output `[T, H, Dh]`); CUDA only (callers check `fused_block_ok`)."""
   from recml_b200.ops import hstu_cuda
   return _SiluSplitAttnFn.apply(z, num_heads, pos_w, ts_w, hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len,
-                                causal, scale, sliding_window_size, segment_ids)
+                                causal, scale, sliding_window_size, segment_ids, dropout_p)
 
 
 def fused_block_ok(z: torch.Tensor, head_dim: int) -> bool:
@@ -267,7 +300,7 @@ def fused_block_ok(z: torch.Tensor, head_dim: int) -> bool:
 
 def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=None, ts_w=None,
                                timestamps=None, causal: bool = True, scale: float = 1.0,
-                               sliding_window_size: int | None = None, segment_ids=None):
+                               sliding_window_size: int | None = None, segment_ids=None, dropout_p: float = 0.0):
   """Packed HSTU attention.  CUDA bf16 inputs with head dim 64 or 128 run the sm_100a kernels (masks —
   causal, sequence ends, an inclusive sliding window, equal segment ids `[T]` — and the learned bias all
   arrive through the step's bias tiles); everything else takes the torch oracle (differentiable through
@@ -277,7 +310,8 @@ def jagged_pointwise_attention(q, k, v, seq_offsets, max_seq_len: int, *, pos_w=
     if hstu_cuda.available():
       return _JaggedAttnFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), pos_w, ts_w,
                                  hstu_cuda.offsets32(seq_offsets), timestamps, max_seq_len, causal, scale,
-                                 sliding_window_size, segment_ids)
+                                 sliding_window_size, segment_ids, dropout_p)
   return jagged_attention_reference(q, k, v, seq_offsets, max_seq_len, pos_w=pos_w, ts_w=ts_w,
                                     timestamps=timestamps, causal=causal, scale=scale,
-                                    sliding_window_size=sliding_window_size, segment_ids=segment_ids)
+                                    sliding_window_size=sliding_window_size, segment_ids=segment_ids,
+                                    dropout_p=dropout_p)

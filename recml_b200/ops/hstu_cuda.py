@@ -19,9 +19,10 @@ class _Params(ctypes.Structure):
               ("delta", c_vp), ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_do", c_int),
               ("bucket_cache", c_vp), ("pair_base", c_vp), ("cap_pairs", c_int), ("bias_tiles", c_vp),
               ("dbias_tiles", c_vp), ("window", c_int), ("segment_ids", c_vp), ("cum", c_vp),
-              ("cum_pitch", ctypes.c_longlong), ("qk_shared", c_int), ("dk_acc", c_vp), ("dcum", c_vp), ("v_rows", c_vp)]
+              ("cum_pitch", ctypes.c_longlong), ("qk_shared", c_int), ("dk_acc", c_vp), ("dcum", c_vp), ("v_rows", c_vp),
+              ("dropout_key", c_vp), ("drop_threshold", ctypes.c_uint), ("keep_scale", ctypes.c_float)]
 
-MODE_SILU, MODE_SOFTMAX, MODE_DECAY = 0, 1, 2
+MODE_SILU, MODE_SOFTMAX, MODE_DECAY, MODE_SILU_DROPOUT = 0, 1, 2, 3
 
 
 class _BiasParams(ctypes.Structure):
@@ -298,19 +299,53 @@ def _attach(p: _Params, bc: BiasContext) -> None:
   p.pair_base, p.cap_pairs, p.bias_tiles = bc.pair_base.data_ptr(), bc.cap_pairs, bc.tiles.data_ptr()
 
 
-def forward(q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale):
+def _set_dropout(p: _Params, dropout) -> None:
+  """`dropout` = (rate, key): key is an int64 device tensor of one element that seeds the mask."""
+  if dropout is None:
+    return
+  rate, key = dropout
+  p.mode = MODE_SILU_DROPOUT
+  p.dropout_key = key.data_ptr()
+  p.drop_threshold = min(int(rate * 4294967296.0), 4294967295)
+  p.keep_scale = 1.0 / (1.0 - rate)
+
+
+def dropout_keep_mask(key: int, head: int, q_tokens: torch.Tensor, k_tokens: torch.Tensor, rate: float) -> torch.Tensor:
+  """The kernels' keep / drop decision for (head, query token, key token), restated with integer tensor ops:
+  boolean `[len(q_tokens), len(k_tokens)]`.  For tests and for callers that need the mask of a small case."""
+  M = 0xFFFFFFFF
+
+  def mix(x):
+    x = x ^ (x >> 16)
+    x = (x * 0x7feb352d) & M
+    x = x ^ (x >> 15)
+    x = (x * 0x846ca68b) & M
+    return x ^ (x >> 16)
+
+  key &= 0xFFFFFFFFFFFFFFFF
+  lo, hi = key & M, key >> 32
+  q = q_tokens.to(torch.int64)
+  kk = k_tokens.to(torch.int64)
+  row = mix((lo ^ ((q * 0x9E3779B1) & M) ^ (((head + 1) * 0x85EBCA6B) & M)) & M)
+  x = mix((row[:, None] ^ (((kk * 0xC2B2AE35) & M) + hi)[None, :] & M) & M)
+  return x >= min(int(rate * 4294967296.0), 4294967295)
+
+
+def forward(q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale, dropout=None):
   assert rows_ok(q) and rows_ok(k) and rows_ok(v)
   tiles = _tiles(seq_offsets, q.shape[0])
   out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v)
   _attach(p, bc)
+  _set_dropout(p, dropout)
   p.out = out.data_ptr()
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "hstu_attn_fwd")
   return out
 
 
-def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale, dq_fp32: bool = False):
+def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, scale, dq_fp32: bool = False,
+             dropout=None):
   """Gradients w.r.t. q, k, v; the score gradients go into the context's block buffer when a bias table
   wants a gradient.  `dq_fp32` returns dq as the kernel accumulated it (fp32) for a caller that converts it
   in a pass of its own."""
@@ -322,6 +357,7 @@ def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, sca
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v, do)
   _attach(p, bc)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+  _set_dropout(p, dropout)
   if bc.want_bias_grad:
     p.dbias_tiles = bc.gradient_blocks().data_ptr()
   _lib.check_rc(lib.recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do),

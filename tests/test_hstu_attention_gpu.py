@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from recml_b200.ops import _lib, hstu_attention as A
+from recml_b200.ops import _lib, hstu_attention as A, hstu_cuda
 
 pytestmark = pytest.mark.gpu
 
@@ -313,3 +313,40 @@ def test_block_with_fused_activation_node_matches_unfused(monkeypatch):
   assert float((dpf - dpu).abs().max()) <= tol(dpu)
   for n in gu:
     assert float((gf[n] - gu[n]).abs().max()) <= tol(gu[n]), n
+
+
+@pytest.mark.parametrize("rate", [0.25, 0.6])
+def test_attention_weight_dropout_in_the_kernels(rate):
+  """Dropout on the attention weights (reference `recml/layers/keras/hstu.py:386-387`) is applied inside the
+  kernels from a counter-based hash of (key, head, query token, key token); forward and backward regenerate the
+  same mask.  The oracle applies the same mask, rebuilt with integer tensor ops from the key the call drew."""
+  from recml_b200.ops import hstu_attention as A
+  torch.manual_seed(3)
+  H, Dh = 2, 64
+  lens = torch.tensor([200, 70, 130])
+  offs = torch.zeros(4, dtype=torch.int64)
+  offs[1:] = lens.cumsum(0)
+  T = int(offs[-1])
+  mk = lambda: (torch.randn(T, H, Dh, device="cuda") * 0.7).to(torch.bfloat16)
+  q, k, v = mk(), mk(), mk()
+  a = [t.clone().requires_grad_() for t in (q, k, v)]
+  r = [t.float().clone().requires_grad_() for t in (q, k, v)]
+  out = A.jagged_pointwise_attention(*a, offs.cuda(), 256, causal=True, dropout_p=rate)
+  key = int(A.LAST_DROPOUT_KEY.item())
+  ref = A.jagged_attention_reference(*r, offs.cuda(), 256, causal=True, dropout_p=rate, dropout_key=key)
+  tol = lambda x: 1.5e-2 * float(x.abs().max())
+  assert float((out.float() - ref).abs().max()) <= tol(ref)
+  # the mask drops about `rate` of the weights and differs between heads and positions
+  tok = torch.arange(0, 200, device="cuda")
+  keep0 = hstu_cuda.dropout_keep_mask(key, 0, tok, tok, rate)
+  keep1 = hstu_cuda.dropout_keep_mask(key, 1, tok, tok, rate)
+  assert abs(float(keep0.float().mean()) - (1 - rate)) < 0.02 and bool((keep0 != keep1).any())
+  g = (torch.randn_like(ref) * 0.1).to(torch.bfloat16)
+  out.backward(g)
+  ref.backward(g.float())
+  for name, x, y in zip("qkv", a, r):
+    assert float((x.grad.float() - y.grad).abs().max()) <= tol(y.grad), name
+  # without a rate nothing is dropped
+  o0 = A.jagged_pointwise_attention(q, k, v, offs.cuda(), 256, causal=True)
+  r0 = A.jagged_attention_reference(q.float(), k.float(), v.float(), offs.cuda(), 256, causal=True)
+  assert float((o0.float() - r0).abs().max()) <= tol(r0)
