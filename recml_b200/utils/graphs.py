@@ -56,13 +56,26 @@ def _tree_tensors(tree, out):
 
 
 def _clone_tree(tree, fast: bool = False):
-  """Deep copy of the tensors of a tree.  `fast` copies all of them with one multi-tensor launch per
-  dtype instead of one memcpy each (a step returns ~16 tiny metric tensors: launch-bound)."""
+  """Deep copy of the tensors of a tree.  `fast` gathers all tensors of a dtype with ONE concatenation kernel
+  and hands out views of the result instead of one memcpy each (a step returns ~16 tiny metric tensors, and 16
+  launches between two graph replays are a visible share of a 3 ms step)."""
   if fast:
     src = _leaf_tensors(tree, [])
     if src:
-      dst = [torch.empty_like(t) for t in src]
-      torch._foreach_copy_(dst, src)   # pylint: disable=protected-access
+      dst: list = [None] * len(src)
+      groups: dict = {}
+      for i, t in enumerate(src):
+        groups.setdefault((t.dtype, t.device), []).append(i)
+      for idxs in groups.values():
+        if len(idxs) == 1:
+          dst[idxs[0]] = src[idxs[0]].clone()
+          continue
+        flat = torch.cat([src[i].reshape(-1) for i in idxs])
+        at = 0
+        for i in idxs:
+          n = src[i].numel()
+          dst[i] = flat[at:at + n].view(src[i].shape)
+          at += n
       it = iter(dst)
       return _rebuild(tree, it)
   return _clone_slow(tree)
