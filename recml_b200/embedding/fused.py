@@ -339,6 +339,20 @@ class FusedBackend:
                     "tot": torch.zeros(max(n_rw, 1) * m.world, dtype=torch.int32, device=dev)}
     return self._bucket
 
+  def partition_stats(self) -> dict[str, list[int]]:
+    """Ids that the LAST bucketized batch of this rank sent to each owner, per row-sharded pooled feature
+    (`{feature: [count for owner 0, owner 1, ...]}`; synchronises).  The maximum over owners and ranks is the
+    `max_ids_per_partition` statistic of feedback-directed sizing (`id_pipeline.StatsRecorder`)."""
+    b = self._bucket
+    if not b or not b["n_rw"]:
+      return {}
+    m = self.m
+    tot = b["tot"].reshape(b["n_rw"], m.world).cpu().tolist()
+    seq_len = {f: L for f, _, _, L in self.layout}
+    names = [f for f in m.feature_names
+             if m.plan.tables[m.feature_to_table[f]].placement is Placement.ROW_WISE and seq_len.get(f, 0) == 0]
+    return dict(zip(names, tot))
+
   def _need_mask(self) -> torch.Tensor:
     """uint8 per feature: bit r set when rank r holds rows (or columns) of the feature's table, i.e.
     needs its ids."""

@@ -247,6 +247,15 @@ def sharded_embedding_steps(rank, world, device_type, backend_name, placements, 
     torch.cuda.synchronize()
     from recml_b200.ops import _lib
     _lib.check_status(device)
+  backend = getattr(m, "_backend", None)
+  if world > 1 and hasattr(backend, "partition_stats"):
+    # the bucketizing id push counted, per row-sharded feature, the ids it sent to every owner
+    stats = backend.partition_stats()
+    for fname, per_owner in stats.items():
+      tp = m.plan.tables[m.feature_to_table[fname]]
+      ids = np.concatenate([np.asarray(r, dtype=np.int64) for r in mine[fname]]) if len(mine[fname]) else np.zeros(0, np.int64)
+      want = [int(((ids % world + tp.rotation) % world == r).sum()) for r in range(world)]
+      assert per_owner == want, (fname, per_owner, want)
   tables = {n: m.gather_table(n).cpu() for n in m.plan.tables}
   return {"outs": outs, "tables": tables}
 
