@@ -271,6 +271,24 @@ __global__ void silu_fwd_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat
   reinterpret_cast<uint4*>(h)[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// SiLU of the [T, 4 D] pre-activation of a fused u | q | k | v projection, written as two matrices: u [T, D]
+// (contiguous: it gates a LayerNorm that wants whole rows) and q | k | v [T, 3 D].
+__global__ void silu_fwd_split_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ u,
+                                      __nv_bfloat16* __restrict__ qkv, long long T, int D) {
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8;
+  const long long width = 4LL * D;
+  if (i >= T * width) return;
+  const long long r = i / width;
+  const int c = static_cast<int>(i - r * width);
+  const uint4 A = *reinterpret_cast<const uint4*>(z + i);
+  const uint32_t aw[4] = {A.x, A.y, A.z, A.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = pack_bf16(silu_of(bf16_lo(aw[j])), silu_of(bf16_hi(aw[j])));
+  __nv_bfloat16* dst = c < D ? u + r * D + c : qkv + r * 3LL * D + (c - D);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // The fused u | q | k | v projection of an attention block: z is [T, 4 D]; its four column blocks received the
 // gradients g0 (bf16, row pitch ld0), g1 (FP32 [T, D]: the attention kernels accumulate dq in fp32), g2 and g3
 // (bf16 [T, D]).  dz = (g0 | g1 | g2 | g3) * silu'(z) in one pass instead of a cast, a concatenation and the
@@ -441,6 +459,15 @@ extern "C" int recml_silu_fwd_bf16(const void* z, void* h, long long n, cudaStre
   const long long n8 = n / 8;
   silu_fwd_kernel<<<static_cast<int>((n8 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(h), n8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int recml_silu_fwd_split(const void* z, void* u, void* qkv, long long T, int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D % 8) return -2;
+  const long long n8 = T * 4 * D / 8;
+  silu_fwd_split_kernel<<<static_cast<int>((n8 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(qkv), T, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -799,14 +799,19 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar(7), 1);
     mbar_init(bar(8), kCompute);
     mbar_init(bar(9), 1);
+    mbar_init(bar(10), kCompute);      // S / dP are in registers: their tensor-memory columns may be overwritten
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), S::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // With head dim 64 there is room for dQ in columns of its own (448 of 512 in use) and for two Q / dO stages:
+  // the score products of the NEXT query tile are then issued while the element-wise warps still work on this
+  // one.  With head dim 128 dQ shares the columns of S and the steps run one after the other.
+  constexpr bool kAhead = DH == 64;
   const uint32_t tmem_s = tmem_slot, tmem_dp = tmem_slot + 128, tmem_dv = tmem_slot + 256,
-                 tmem_dk = tmem_slot + 256 + DH;
+                 tmem_dk = tmem_slot + 256 + DH, tmem_dq = kAhead ? tmem_slot + 256 + 2 * DH : tmem_slot;
   volatile int* abortp = &abort_flag;
 
   if (warp == 0) {
@@ -834,10 +839,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_t = idesc_bf16(BKV, DH, true, true);       // dV = P^T·dO, dK = dS^T·Q
       const uint32_t idesc_q = idesc_bf16(BQ, DH, false, true);       // dQ = dS·K
       bool ok = mbar_wait(bar(0), 0, abortp, p.status, 51);
-      for (int it = 0; it < n_it && ok; ++it) {
+      // S = Q_i K^T and dP = dO_i V^T of query tile `it` (its Q / dO stage must have landed)
+      auto issue_scores = [&](int it) -> bool {
         const int st = it % S::kStages;
-        if (!mbar_wait(bar(1 + st), (it / S::kStages) & 1, abortp, p.status, 52)) break;
-        if (it > 0 && !mbar_wait(bar(8), (it - 1) & 1, abortp, p.status, 53)) break;   // dQ of tile it-1 read out
+        if (!mbar_wait(bar(1 + st), (it / S::kStages) & 1, abortp, p.status, 52)) return false;
         tc_fence_after();
         const uint32_t sq = base + S::kQ + st * S::kTile, sdo = base + S::kDO + st * S::kTile;
 #pragma unroll
@@ -850,7 +855,24 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                         make_desc(base + S::kV + d * 16384 + k * 32, 16, 1024), idesc_s, (d | k) ? 1u : 0u);
           }
         tc_commit(bar(5));
+        return true;
+      };
+      if (kAhead && ok && n_it > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % S::kStages;
+        if constexpr (kAhead) {
+          // the next tile's scores as soon as this tile's are in the element-wise warps' registers
+          if (it + 1 < n_it) {
+            if (!mbar_wait(bar(10), it & 1, abortp, p.status, 58)) break;
+            if (!issue_scores(it + 1)) break;
+          }
+        } else {
+          if (it > 0 && !mbar_wait(bar(8), (it - 1) & 1, abortp, p.status, 53)) break;   // dQ of tile it-1 read out
+          if (!issue_scores(it)) break;
+        }
+        const uint32_t sq = base + S::kQ + st * S::kTile, sdo = base + S::kDO + st * S::kTile;
         if (!mbar_wait(bar(6), it & 1, abortp, p.status, 54)) break;   // P and dS are in shared memory
+        if (kAhead && it > 0 && !mbar_wait(bar(8), (it - 1) & 1, abortp, p.status, 53)) break;   // dQ of tile it-1 read out
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {   // contraction over the 128 query rows
@@ -860,8 +882,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                       idesc_t, (it | kk) ? 1u : 0u);
         }
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk)    // contraction over the 128 keys; dQ reuses S's columns
-          tc_mma_bf16(tmem_s, make_desc(base + S::kDS + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+        for (int kk = 0; kk < BKV / 16; ++kk)    // contraction over the 128 keys
+          tc_mma_bf16(tmem_dq, make_desc(base + S::kDS + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                       make_desc(base + S::kK + kk * 2048, 16384, 1024), idesc_q, kk ? 1u : 0u);
         tc_commit(bar(7));           // dQ ready; P / dS / this Q,dO stage no longer read
         tc_commit(bar(3 + st));
@@ -918,6 +940,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         float row_acc = 0.f;
         tmem_ld32(tmem_s + lane_off + cb * 32, sv);
         tmem_ld32(tmem_dp + lane_off + cb * 32, dpv);
+        if constexpr (kAhead) {
+          tc_fence_before();
+          mbar_arrive(bar(10));
+        }
         uint8_t* prow = base_ptr + S::kP + (cb >> 1) * 16384 + r * 128;
         uint8_t* drow = base_ptr + S::kDS + (cb >> 1) * 16384 + r * 128;
         float4* dbias = nullptr;
@@ -994,7 +1020,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll 1
       for (int c = cb; c < DH / 32; c += 4) {
         uint32_t v[32];
-        tmem_ld32(tmem_s + lane_off + c * 32, v);
+        tmem_ld32(tmem_dq + lane_off + c * 32, v);
         if (row_ok) {
           float4* dst = reinterpret_cast<float4*>(
               p.qk_shared ? p.dq + static_cast<size_t>(seq_start + qi) * DH + c * 32

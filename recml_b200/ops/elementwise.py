@@ -94,6 +94,17 @@ def silu_bf16(z: torch.Tensor) -> torch.Tensor:
   return h
 
 
+def silu_split(z: torch.Tensor):
+  """silu(z) for `z [T, 4 D]` as (u `[T, D]`, qkv `[T, 3 D]`), both contiguous."""
+  T, W4 = z.shape
+  D = W4 // 4
+  u = torch.empty(T, D, dtype=z.dtype, device=z.device)
+  qkv = torch.empty(T, 3 * D, dtype=z.dtype, device=z.device)
+  _lib.check_rc(_lib.cuda().recml_silu_fwd_split(_lib.ptr(z), _lib.ptr(u), _lib.ptr(qkv), c_ll(T), c_int(D),
+                                                 _lib.stream()), "silu_fwd_split")
+  return u, qkv
+
+
 def silu_bwd_gather4(z, g0, g1_f32, g2, g3):
   """dz `[T, 4 D]` = (g0 | g1 | g2 | g3) * silu'(z) for the pre-activation `z [T, 4 D]` of a fused four-way
   projection: g0 bf16 `[T, D]` (any row pitch), g1 fp32 `[T, D]`, g2 / g3 bf16 `[T, D]`, all with unit column

@@ -246,13 +246,14 @@ class _SiluSplitAttnFn(torch.autograd.Function):
     from recml_b200.ops import elementwise as ew, hstu_cuda
     T, W4 = z.shape
     D = W4 // 4
-    h = ew.silu_bf16(z).view(T, 4, num_heads, D // num_heads)
-    u, q, k, v = h.unbind(1)
+    u2, qkv = ew.silu_split(z)
+    u = u2.view(T, num_heads, D // num_heads)
+    q, k, v = qkv.view(T, 3, num_heads, D // num_heads).unbind(1)
     bc = hstu_cuda.bias_context(seq_offsets, timestamps, pos_w, ts_w, T, max_seq_len, causal, window, segment_ids)
     drop = _draw_dropout(dropout_p, z.device)
     o = hstu_cuda.forward(q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dropout=drop)
-    ctx.save_for_backward(z, h, pos_w, ts_w, seq_offsets)
-    ctx.meta = (max_seq_len, causal, scale)
+    ctx.save_for_backward(z, qkv, pos_w, ts_w, seq_offsets)
+    ctx.meta = (max_seq_len, causal, scale, num_heads)
     ctx.drop = drop
     ctx.bias_ctx = bc
     bc.pending += 1
@@ -262,11 +263,11 @@ class _SiluSplitAttnFn(torch.autograd.Function):
   @staticmethod
   def backward(ctx, du, do):
     from recml_b200.ops import elementwise as ew, hstu_cuda
-    z, h, pos_w, ts_w, seq_offsets = ctx.saved_tensors
-    max_seq_len, causal, scale = ctx.meta
+    z, qkv, pos_w, ts_w, seq_offsets = ctx.saved_tensors
+    max_seq_len, causal, scale, num_heads = ctx.meta
     bc = ctx.bias_ctx
-    _, q, k, v = h.unbind(1)
     T, D = z.shape[0], z.shape[1] // 4
+    q, k, v = qkv.view(T, 3, num_heads, D // num_heads).unbind(1)
     dq, dk, dv = hstu_cuda.backward(do, q, k, v, seq_offsets, bc, max_seq_len, causal, scale, dq_fp32=True,
                                     dropout=ctx.drop)
     bc.pending -= 1

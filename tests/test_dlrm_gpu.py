@@ -9,7 +9,7 @@ from recml_b200.training import optim_factory, partitioning
 pytestmark = pytest.mark.gpu
 
 
-def _run(device, steps=30, graph=False, embedding_lr=0.05, return_state=False):
+def _run(device, steps=30, graph=False, embedding_lr=0.05, return_state=False, snapshot_at=None):
   cfg = D.ModelConfig(vocab_sizes=(2000, 300, 17, 4096), bag_sizes=(3, 1, 2, 20), embedding_dim=128,
                       bottom_mlp_dims=(64, 128), top_mlp_dims=(256, 64, 1), num_cross_layers=2, cross_rank=64,
                       embedding_learning_rate=embedding_lr, embedding_init_scale=0.05)
@@ -26,9 +26,15 @@ def _run(device, steps=30, graph=False, embedding_lr=0.05, return_state=False):
   if graph:
     from recml_b200.utils import graphs
     step = graphs.GraphedStep(step, warmup=3)
-  for _ in range(steps):
+  snap = None
+  for i in range(steps):
     state, m = step(part.shard_inputs(next(it)), state)
     losses.append(float(m["loss"].localize().compute()))
+    if snapshot_at is not None and i + 1 == snapshot_at:
+      emb_mod = state.model.embedding
+      snap = {n: emb_mod.gather_table(n).clone() for n in emb_mod.plan.tables}
+  if snapshot_at is not None:
+    return losses, state, snap
   return (losses, state) if return_state else losses
 
 
@@ -57,18 +63,15 @@ def test_cuda_graph_replay_matches_eager():
 def test_embedding_learning_rate_schedule_survives_graph_replay():
   """The row optimizer reads its hyper-parameters from device memory, refreshed before every replay: a schedule
   that switches the embedding learning rate off after 5 steps must freeze the tables in the captured run
-  exactly as in the eager run (a rate captured as a launch argument would keep training them)."""
+  exactly as in the eager run (a rate captured as a launch argument would keep training them: the graphs are
+  captured at steps 4 and 5, while the rate is still 0.05)."""
   schedule = lambda step: 0.05 if step < 5 else 0.0
-  _, s_probe = _run("cuda", steps=5, embedding_lr=schedule, return_state=True)
-  _, s_eager = _run("cuda", steps=12, embedding_lr=schedule, return_state=True)
-  _, s_graph = _run("cuda", steps=12, graph=True, embedding_lr=schedule, return_state=True)
-  torch.cuda.synchronize()
-  _lib.check_status()
-  for name in s_eager.model.embedding.plan.tables:
-    t5 = s_probe.model.embedding.gather_table(name)
-    te = s_eager.model.embedding.gather_table(name)
-    tg = s_graph.model.embedding.gather_table(name)
-    torch.testing.assert_close(te, t5, rtol=1e-4, atol=1e-5)     # eager: nothing moved after step 5 (two runs differ
-                                                                 # only by the order of their atomic sums)
-    torch.testing.assert_close(tg, te, rtol=1e-2, atol=3e-3)     # replayed: the same tables (a rate frozen at capture
-                                                                 # would have moved them by ~0.05 per further step)
+  for graph in (False, True):
+    _, state, at5 = _run("cuda", steps=12, graph=graph, embedding_lr=schedule, snapshot_at=5)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _, _, at3 = _run("cuda", steps=3, graph=False, embedding_lr=schedule, snapshot_at=3)
+    for name, frozen in at5.items():
+      final = state.model.embedding.gather_table(name)
+      torch.testing.assert_close(final, frozen, rtol=0, atol=0)            # nothing moved after step 5
+      assert float((frozen - at3[name]).abs().max()) > 1e-4                  # ... and it did move before
