@@ -133,11 +133,9 @@ class PredictionTask(task_lib.Task):
         "common/batch_size": M.scalar(float(n)),
     }
     if r.hist_pos is not None:
-      # one pass over the histograms feeds both curves
-      tp, tn, fp, fn = M.confusion_from_histograms(r.hist_pos, r.hist_neg)
-      counts = dict(true_positives=tp, true_negatives=tn, false_positives=fp, false_negatives=fn)
-      out["auc"] = M.AUCPR(**counts)
-      out["aucroc"] = M.AUCROC(**counts)
+      # both curves keep the loss kernel's histograms as their state; the suffix sums run on the host at report time
+      out["auc"] = M.HistogramAUCPR(pos_hist=r.hist_pos, neg_hist=r.hist_neg)
+      out["aucroc"] = M.HistogramAUCROC(pos_hist=r.hist_pos, neg_hist=r.hist_neg)
     return out
 
   def train_step(self, batch, state, rng):

@@ -1,7 +1,7 @@
 """Public metrics API (names of `recml/core/metrics/__init__.py:19-34` plus the ranking
 metrics the reference README promises)."""
 from recml_b200.metrics.base import Metric, ScalarMetric, scalar
-from recml_b200.metrics.confusion import (AUCPR, AUCROC, FBeta, Precision, PrecisionAtRecall,
+from recml_b200.metrics.confusion import (AUCPR, AUCROC, HistogramAUCPR, HistogramAUCROC, FBeta, Precision, PrecisionAtRecall,
                                           Recall, aucpr, aucroc, default_thresholds,
                                           confusion_from_histograms, estimate_confusion_matrix, f1_score,
                                           fbeta_score,

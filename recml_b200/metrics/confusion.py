@@ -177,6 +177,37 @@ class AUCPR(ConfusionMetric):
     return float(np.sum(inc))
 
 
+class _FromHistograms(base.Metric):
+  """Curve metric whose state is the pair of `[T+1]` prediction histograms of the fused loss kernel (weight of
+  positives / negatives with exactly b thresholds below the prediction).  Histograms add like confusion counts do,
+  so steps and ranks merge by addition, and the suffix sums that turn them into tp / fp / fn / tn are taken once,
+  on the host, when the value is asked for: nothing but the loss kernel runs inside the training step."""
+  pos_hist: Any
+  neg_hist: Any
+
+  def merge(self, other):
+    return self.replace(pos_hist=self.pos_hist + other.pos_hist, neg_hist=self.neg_hist + other.neg_hist)
+
+  def _curve(self):
+    raise NotImplementedError
+
+  def compute(self):
+    hp = torch.as_tensor(np.asarray(base.to_numpy(self.pos_hist), dtype=np.float64))
+    hn = torch.as_tensor(np.asarray(base.to_numpy(self.neg_hist), dtype=np.float64))
+    tp, tn, fp, fn = confusion_from_histograms(hp, hn)
+    return self._curve()(true_positives=tp, true_negatives=tn, false_positives=fp, false_negatives=fn).compute()
+
+
+class HistogramAUCPR(_FromHistograms):
+  def _curve(self):
+    return AUCPR
+
+
+class HistogramAUCROC(_FromHistograms):
+  def _curve(self):
+    return AUCROC
+
+
 class AUCROC(AUCPR):
   def compute(self):
     tp, tn, fp, fn = self._np()

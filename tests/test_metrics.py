@@ -161,3 +161,27 @@ def test_accumulator_and_writer(tmp_path):
   np.testing.assert_allclose(out["lr"], 0.2, rtol=1e-6)
   assert any(f.startswith("events.out") for f in __import__("os").listdir(tmp_path / "train"))
   assert acc.compute_and_log_scalars(2) == {}
+
+
+def test_histogram_auc_states_match_confusion_states():
+  """AUC metrics that keep the loss kernel's histograms as state give the same value as the ones built from the
+  confusion counts, also after merging steps."""
+  import numpy as np
+  import torch
+  from recml_b200 import metrics as M
+  rng = np.random.default_rng(0)
+  T = 200
+  parts = []
+  for _ in range(3):
+    hp = torch.from_numpy(rng.random(T + 1).astype(np.float32) * 10)
+    hn = torch.from_numpy(rng.random(T + 1).astype(np.float32) * 30)
+    parts.append((hp, hn))
+  for hist_cls, cls in ((M.HistogramAUCPR, M.AUCPR), (M.HistogramAUCROC, M.AUCROC)):
+    a = b = None
+    for hp, hn in parts:
+      x = hist_cls(pos_hist=hp, neg_hist=hn)
+      tp, tn, fp, fn = M.confusion_from_histograms(hp, hn)
+      y = cls(true_positives=tp, true_negatives=tn, false_positives=fp, false_negatives=fn)
+      a = x if a is None else a.merge(x)
+      b = y if b is None else b.merge(y)
+    assert abs(a.localize().compute() - b.localize().compute()) < 1e-5
