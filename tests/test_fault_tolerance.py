@@ -107,3 +107,53 @@ def test_device_wait_expires_and_reports_status():
                        ctypes.c_int(7), _lib.ptr(result), _lib.stream())
   torch.cuda.synchronize()
   assert result.item() == 1 and status.tolist()[0] == 0
+
+
+@pytest.mark.gpu
+def test_no_checkpoint_is_written_after_a_device_error_status(tmp_path):
+  """A kernel that gave up on a wait leaves a status word; the trainer looks at it before every checkpoint and at
+  loop ends, so a step whose collective timed out can never be committed as a good checkpoint.  The status is
+  produced by the bounded-wait probe (a flag nothing raises), not by a fault."""
+  import os
+  import numpy as np
+  from torch import nn
+  import recml_b200 as recml
+  from recml_b200 import ckpt
+  from recml_b200.data import iterator as iterator_lib
+  from recml_b200.ops import _lib
+
+  class Data:
+    def __iter__(self):
+      rng = np.random.default_rng(0)
+      for _ in range(100):
+        x = rng.normal(size=(8, 4)).astype(np.float32)
+        yield {"x": x, "y": x.sum(1, keepdims=True)}
+
+  class Task(recml.Task):
+    steps = 0
+
+    def create_datasets(self):
+      return iterator_lib.IterableIterator(Data())
+
+    def create_state(self, batch, rng):
+      return recml.State.create(model=nn.Linear(4, 1).cuda(), tx=recml.AdamFactory(learning_rate=0.05).make())
+
+    def train_step(self, batch, state, rng):
+      loss = ((state.model(batch["x"]) - batch["y"]) ** 2).mean()
+      loss.backward()
+      state.update()
+      Task.steps += 1
+      if Task.steps == 2:     # a wait that runs out, reported through the library's status word of this device
+        flag = torch.zeros(1, dtype=torch.int64, device="cuda")
+        result = torch.zeros(1, dtype=torch.int32, device="cuda")
+        _lib.cuda().recml_wait_probe(_lib.ptr(flag), ctypes.c_ulonglong(1), ctypes.c_ulonglong(5_000_000),
+                                     _lib.ptr(_lib.status_buffer()), ctypes.c_int(9), _lib.ptr(result), _lib.stream())
+      return state, {"loss": recml.metrics.mean(loss.detach())}
+
+  _lib.check_status()
+  trainer = recml.Trainer(partitioner=recml.DataParallelPartitioner(device="cuda"), model_dir=str(tmp_path),
+                          train_steps=12, steps_per_loop=4, checkpoint_interval=4)
+  with pytest.raises(_lib.DeviceStatusError):
+    recml.run_experiment(recml.Experiment(Task(), trainer), "train")
+  assert ckpt.all_steps(os.path.join(tmp_path, "checkpoints")) == []
+  _lib.check_status()          # the word was cleared by the raise
