@@ -21,7 +21,7 @@ using namespace recml::tc;
 
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;     // TMA warp, MMA warp, 8 epilogue warps (two per tensor-memory lane quarter)
 constexpr int kMaxWorld = 8;
 constexpr int kMaxRows = 4096;     // query rows per call (per-CTA count array in shared memory)
 
@@ -68,7 +68,7 @@ vocab_rank_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int i = 0; i < 2 * kStages; ++i) mbar_init(bar(i), 1);
     mbar_init(bar(8), 1); mbar_init(bar(9), 1);
     mbar_init(bar(10), 1); mbar_init(bar(11), 1);
-    mbar_init(bar(12), 128); mbar_init(bar(13), 128);
+    mbar_init(bar(12), 256); mbar_init(bar(13), 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = threadIdx.x; i < p.M; i += kThreads) counts[i] = 0;
@@ -158,11 +158,13 @@ vocab_rank_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;      // the two warps of a lane quarter take alternate 32-column chunks
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t acc_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       const int n0 = tile * BN;
+      const bool whole = n0 + BN <= p.V_local;        // no item of the tile lies beyond the shard
       for (int mb = 0; mb < m_blocks; ++mb, ++acc_it) {
         const int acc = acc_it & 1;
         int okw = 1;
@@ -172,20 +174,29 @@ vocab_rank_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tc_fence_after();
         const int row = mb * BM + quarter * 32 + lane;
         const bool row_ok = row < p.M;
-        const float pos = row_ok ? p.pos_score[row] : 0.f;
-        const long long tgt = row_ok ? p.target[row] : -1;
+        const float pos = row_ok ? p.pos_score[row] : INFINITY;     // rows past M count nothing
+        // local column of this row's own target (it does not compete with itself), -1 when another rank holds it
+        int tgt_col = -1;
+        if (row_ok) {
+          const long long d = p.target[row] - p.id_add;
+          if (d >= 0 && d % p.id_mul == 0 && d / p.id_mul < p.V_local) tgt_col = static_cast<int>(d / p.id_mul);
+        }
         int c = 0;
 #pragma unroll 1
-        for (int ch = 0; ch < BN / 32; ++ch) {
+        for (int ch = half; ch < BN / 32; ch += 2) {
           uint32_t v[32];
           tmem_ld32(tmem_base + acc * BN + lane_off + ch * 32, v);
           const int col0 = n0 + ch * 32;
+          const bool plain = whole && static_cast<unsigned>(tgt_col - col0) >= 32u;
+          if (__all_sync(0xffffffffu, plain)) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int item = col0 + e;
-            const bool better = __uint_as_float(v[e]) > pos && item < p.V_local &&
-                                static_cast<long long>(item) * p.id_mul + p.id_add != tgt;
-            c += better ? 1 : 0;
+            for (int e = 0; e < 32; ++e) c += __uint_as_float(v[e]) > pos ? 1 : 0;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int item = col0 + e;
+              c += (__uint_as_float(v[e]) > pos && item < p.V_local && item != tgt_col) ? 1 : 0;
+            }
           }
         }
         tc_fence_before();
