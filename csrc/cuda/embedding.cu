@@ -252,6 +252,8 @@ struct BucketizeParams {
   const BucketFeat* feats;   // [n_feats]
   int* cnt;                  // [n_rw, W, B]: ids of bag b owned by rank r, then their exclusive prefix over b
   int* tot;                  // [n_rw, W]
+  int* cnt_raw;              // [n_rw, W, B] or null: the counts themselves, kept for the combine and the gradient push
+                             // (an owner that got no id of a bag neither writes its slot nor needs its gradient)
   int* dst_values[kMaxWorld]; int* dst_offsets[kMaxWorld]; float* dst_weights[kMaxWorld];
   unsigned int* done_counter; PeerFlags flags; SeqRef seq;
 };
@@ -285,7 +287,10 @@ __global__ void __launch_bounds__(256) bucket_count_kernel(const BucketizeParams
         if (lane == q) mine += c;
       }
     }
-    if (lane < p.W) p.cnt[(static_cast<long long>(j) * p.W + lane) * p.B + b] = mine;
+    if (lane < p.W) {
+      p.cnt[(static_cast<long long>(j) * p.W + lane) * p.B + b] = mine;
+      if (p.cnt_raw != nullptr) p.cnt_raw[(static_cast<long long>(j) * p.W + lane) * p.B + b] = mine;
+    }
   }
 }
 
@@ -593,8 +598,8 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
         for (int pos = covered; pos < f.seq_len; ++pos)
           store_bf16<VPL>(dst_base + slot_row * f.dst_stride + static_cast<long long>(pos) * f.dim, z);
       }
-    } else if (lane_on) {
-      store_bf16<VPL>(dst_base + slot_row * f.dst_stride, acc);
+    } else if (lane_on && !(p.prefiltered && f.kind == kRowWise && o1 == o0)) {
+      store_bf16<VPL>(dst_base + slot_row * f.dst_stride, acc);      // (a bucketized bag with no id for this rank: no store)
     }
   }
   grid_done_then_signal(p.done_counter, p.flags, p.W, seq);
@@ -661,9 +666,17 @@ __global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
 #pragma unroll
     for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
     int cur = 0;          // bag whose sum is being built; bags below it have been stored
+    // Bucketized row-sharded features: the sender knows which owners got ids of a bag and reads only their slots,
+    // so a bag of which this rank received nothing is not stored at all.
+    unsigned int store_mask = 0xffffffffu;
+    if (p.prefiltered && f.kind == kRowWise) {
+      const int o_next = __shfl_down_sync(0xffffffffu, o_mine, 1);
+      const int o_end = lane == nb - 1 ? p1 : o_next;
+      store_mask = __ballot_sync(0xffffffffu, lane < nb && o_end > o_mine);
+    }
     auto store_upto = [&](int bag) {      // stores bag `cur` (acc) and zeros for the bags between, then cur = bag
       while (cur < bag) {
-        if (lane_on) store_bf16<VPL>(dst_base + (slot_row0 + cur) * f.dst_stride, acc);
+        if (lane_on && ((store_mask >> cur) & 1u)) store_bf16<VPL>(dst_base + (slot_row0 + cur) * f.dst_stride, acc);
 #pragma unroll
         for (int e = 0; e < VPL; ++e) acc.v[e] = 0.f;
         ++cur;
@@ -787,11 +800,13 @@ __global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
 }
 
 // =================================== combine: sum source slots, write concat =======================
-struct CombineDesc { long long slot_off; int nslots; int dim; int out_col; int seq_len; };
+struct CombineDesc { long long slot_off; int nslots; int dim; int out_col; int seq_len; int rw_index; int pad; };
 struct CombineParams {
   const __nv_bfloat16* pooled; const CombineDesc* feats; int n_feats; int B;
   __nv_bfloat16* out; long long ld_out;
   const unsigned long long* wait_flags; int W; int n_chan; SeqRef seq; int* status;
+  const int* cnt_raw;       // [n_rw, W, B] or null: ids of bag b this rank sent to owner r (bucketized features: a slot
+                            // is read only when its owner received ids of the bag, and only then was it written)
 };
 
 __global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p) {
@@ -811,7 +826,10 @@ __global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p)
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      const int* own = (p.cnt_raw != nullptr && f.rw_index >= 0)
+          ? p.cnt_raw + static_cast<long long>(f.rw_index) * p.W * p.B + b : nullptr;
       for (int sl = 0; sl < f.nslots; ++sl) {
+        if (own != nullptr && own[static_cast<long long>(sl) * p.B] == 0) continue;
         const uint4 t = *reinterpret_cast<const uint4*>(src + sl * slot_stride);
         const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -826,12 +844,14 @@ __global__ void __launch_bounds__(256) emb_combine_kernel(const CombineParams p)
 
 // =================================== backward: push activation gradients ===========================
 struct PushGradDesc {
-  int kind; int owner; int dim; int in_col; int seq_len; int pad;
+  int kind; int owner; int dim; int in_col; int seq_len;
+  int rw_index;   // >= 0: position among the bucketized row-sharded features (-1: every owner gets the gradient)
   long long grad_off[kMaxWorld];   // element offset of the feature block in rank r's gradient buffer (-1: none)
 };
 struct PushGradParams {
   const __nv_bfloat16* grad; long long ld; const PushGradDesc* feats; int n_feats; int B; int W; int me;
   PeerBf16 dst; unsigned int* done_counter; PeerFlags flags; SeqRef seq;
+  const int* cnt_raw;   // [n_rw, W, B] or null: owners that received no id of a bag do not need its gradient
 };
 
 // Half a warp per (feature, sample): 16 lanes x 16 bytes cover a 128-wide bf16 gradient in one load, which is then
@@ -859,6 +879,13 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
     } else {
       const int r0 = f.kind == kTableWise ? f.owner : 0;
       const int r1 = f.kind == kTableWise ? f.owner + 1 : p.W;
+      unsigned int to = 0;          // the ranks that get this gradient
+      for (int r = r0; r < r1; ++r) to |= 1u << r;
+      if (p.cnt_raw != nullptr && f.kind == kRowWise && f.rw_index >= 0) {
+        const int* own = p.cnt_raw + static_cast<long long>(f.rw_index) * p.W * p.B + b;
+        for (int r = 0; r < p.W; ++r)
+          if (own[static_cast<long long>(r) * p.B] == 0) to &= ~(1u << r);
+      }
       bool vec = (width & 7) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
       for (int r = r0; r < r1; ++r)
         vec = vec && (reinterpret_cast<uintptr_t>(p.dst.p[r] + f.grad_off[r] + row * width) & 15u) == 0;
@@ -866,13 +893,13 @@ __global__ void __launch_bounds__(256) emb_push_grads_kernel(const PushGradParam
         for (int e = sl * 8; e < width; e += 128) {
           const uint4 v = *reinterpret_cast<const uint4*>(src + e);
           for (int r = r0; r < r1; ++r)
-            *reinterpret_cast<uint4*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+            if ((to >> r) & 1u) *reinterpret_cast<uint4*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
         }
       } else {
         for (int e = sl * 2; e < width; e += 32) {
           const uint32_t v = *reinterpret_cast<const uint32_t*>(src + e);
           for (int r = r0; r < r1; ++r)
-            *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
+            if ((to >> r) & 1u) *reinterpret_cast<uint32_t*>(p.dst.p[r] + f.grad_off[r] + row * width + e) = v;
         }
       }
     }

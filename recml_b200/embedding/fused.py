@@ -63,23 +63,25 @@ class FwdParams(ctypes.Structure):
 
 
 class CombineDesc(ctypes.Structure):
-  _fields_ = [("slot_off", c_ll), ("nslots", c_int), ("dim", c_int), ("out_col", c_int), ("seq_len", c_int)]
+  _fields_ = [("slot_off", c_ll), ("nslots", c_int), ("dim", c_int), ("out_col", c_int), ("seq_len", c_int),
+              ("rw_index", c_int), ("pad", c_int)]
 
 
 class CombineParams(ctypes.Structure):
   _fields_ = [("pooled", c_vp), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("out", c_vp), ("ld_out", c_ll),
-              ("wait_flags", c_vp), ("W", c_int), ("n_chan", c_int), ("seq", SeqRef), ("status", c_vp)]
+              ("wait_flags", c_vp), ("W", c_int), ("n_chan", c_int), ("seq", SeqRef), ("status", c_vp),
+              ("cnt_raw", c_vp)]
 
 
 class PushGradDesc(ctypes.Structure):
   _fields_ = [("kind", c_int), ("owner", c_int), ("dim", c_int), ("in_col", c_int), ("seq_len", c_int),
-              ("pad", c_int), ("grad_off", c_ll * MAXW)]
+              ("rw_index", c_int), ("grad_off", c_ll * MAXW)]
 
 
 class PushGradParams(ctypes.Structure):
   _fields_ = [("grad", c_vp), ("ld", c_ll), ("feats", c_vp), ("n_feats", c_int), ("B", c_int), ("W", c_int),
               ("me", c_int), ("dst", c_vp * MAXW), ("done_counter", c_vp), ("flags", c_vp * MAXW),
-              ("seq", SeqRef)]
+              ("seq", SeqRef), ("cnt_raw", c_vp)]
 
 
 class BwdParams(ctypes.Structure):
@@ -103,7 +105,7 @@ class BucketFeat(ctypes.Structure):
 
 class BucketizeParams(ctypes.Structure):
   _fields_ = [("values", c_vp), ("offsets", c_vp), ("weights", c_vp), ("n_feats", c_int), ("B", c_int), ("W", c_int),
-              ("me", c_int), ("n_rw", c_int), ("feats", c_vp), ("cnt", c_vp), ("tot", c_vp),
+              ("me", c_int), ("n_rw", c_int), ("feats", c_vp), ("cnt", c_vp), ("tot", c_vp), ("cnt_raw", c_vp),
               ("dst_values", c_vp * MAXW), ("dst_offsets", c_vp * MAXW), ("dst_weights", c_vp * MAXW),
               ("done_counter", c_vp), ("flags", c_vp * MAXW), ("seq", SeqRef)]
 
@@ -244,7 +246,7 @@ class FusedBackend:
       tp = m.plan.tables[m.feature_to_table[fname]]
       nslots = W if tp.placement is Placement.ROW_WISE else 1
       slot_off[fname] = off
-      self.combine_descs.append(CombineDesc(off, nslots, tp.dim, col, L))
+      self.combine_descs.append(CombineDesc(off, nslots, tp.dim, col, L, self._rw_index_of(fname), 0))
       off += nslots * B * width
     pooled_elems = off
     # ---- gradient-buffer layout per destination rank ----
@@ -283,7 +285,7 @@ class FusedBackend:
     push = []
     for fname, col, width, L in self.layout:
       tp = m.plan.tables[m.feature_to_table[fname]]
-      d = PushGradDesc(KIND[tp.placement], tp.owner, tp.dim, col, L, 0)
+      d = PushGradDesc(KIND[tp.placement], tp.owner, tp.dim, col, L, self._rw_index_of(fname))
       for r in range(MAXW):
         d.grad_off[r] = self.grad_off[r].get(fname, -1) if r < W else -1
       push.append(d)
@@ -309,6 +311,19 @@ class FusedBackend:
     self.pooled_off = [cv.take(pooled_elems * 2) for _ in range(2 if W > 1 else 1)]
     self.grad_buf_off = [cv.take(grad_cap * 2) for _ in range(2 if W > 1 else 1)]
     self.buf = symm.SymmBuffer(cv.off, m.group, m.device)
+
+  def _rw_index_of(self, fname: str) -> int:
+    """Position of `fname` among the row-sharded pooled features in feature order (what the bucketizing id push
+    counts per owner), -1 for every other feature."""
+    m = self.m
+    seq_len = {f: L for f, _, _, L in self.layout}
+    j = 0
+    for f in m.feature_names:
+      if m.plan.tables[m.feature_to_table[f]].placement is Placement.ROW_WISE and seq_len.get(f, 0) == 0:
+        if f == fname:
+          return j
+        j += 1
+    return -1
 
   def _bucket_state(self):
     """Device-side description of the features for the bucketizing id push, or None when it does not apply (a
@@ -336,7 +351,11 @@ class FusedBackend:
     dev = m.device
     self._bucket = {"feats": _device_struct_array(feats, dev), "n_rw": n_rw,
                     "cnt": torch.zeros(max(n_rw, 1) * m.world * self.B, dtype=torch.int32, device=dev),
-                    "tot": torch.zeros(max(n_rw, 1) * m.world, dtype=torch.int32, device=dev)}
+                    "tot": torch.zeros(max(n_rw, 1) * m.world, dtype=torch.int32, device=dev),
+                    # per-owner id counts of every bag, one array per lookup that can be in flight: the combine of
+                    # the forward and the gradient push of the backward skip the owners that got nothing of a bag
+                    "raw": [torch.zeros(max(n_rw, 1) * m.world * self.B, dtype=torch.int32, device=dev)
+                            for _ in range(max(self.pipeline_depth, 1))]}
     return self._bucket
 
   def partition_stats(self) -> dict[str, list[int]]:
@@ -481,6 +500,9 @@ class FusedBackend:
       p.weights = kjt.weights.data_ptr() if kjt.weights is not None else None
       p.n_feats, p.B, p.W, p.me, p.n_rw = len(m.feature_names), B, W, m.rank, bucket["n_rw"]
       p.feats, p.cnt, p.tot = bucket["feats"].data_ptr(), bucket["cnt"].data_ptr(), bucket["tot"].data_ptr()
+      if len(bucket["raw"]) < self.pipeline_depth:      # the depth was raised after the first lookup
+        bucket["raw"] += [torch.zeros_like(bucket["raw"][0]) for _ in range(self.pipeline_depth - len(bucket["raw"]))]
+      p.cnt_raw = bucket["raw"][oset % len(bucket["raw"])].data_ptr()
       vo, oo, wo = self.ids_off[par][m.rank]
       for r in range(W):
         p.dst_values[r] = self.buf.peer_ptr(r, vo)
@@ -558,6 +580,7 @@ class FusedBackend:
     # wait on the pooled channels of every stack: channels 1..n_stacks are contiguous
     cp.wait_flags = self._flag_ptr(m.rank, 1, 0) if W > 1 else None
     cp.W, cp.n_chan, cp.seq, cp.status = W, len(self.stacks), seq, self.status.data_ptr()
+    cp.cnt_raw = bucket["raw"][oset % len(bucket["raw"])].data_ptr() if bucket is not None else None
     _lib.check_rc(self.lib.recml_emb_combine(ctypes.byref(cp), st), "emb_combine")
     res = out[:, out_col:out_col + self.width]
     res = res if odt == torch.bfloat16 else res.to(odt)
@@ -633,6 +656,8 @@ class FusedBackend:
         pg.dst[r] = self.buf.peer_ptr(r, self.grad_buf_off[par])
         pg.flags[r] = self._flag_ptr(r, gchan, m.rank)
       pg.done_counter, pg.seq = self.done_grads.data_ptr(), seq
+      bucket = self._bucket if isinstance(self._bucket, dict) else None
+      pg.cnt_raw = bucket["raw"][saved.get("set", 0) % len(bucket["raw"])].data_ptr() if bucket is not None else None
       _lib.check_rc(self.lib.recml_emb_push_grads(ctypes.byref(pg), st), "emb_push_grads")
       grads_ptr, val_scale = self.buf.peer_ptr(m.rank, self.grad_buf_off[par]), None
     for si, info in enumerate(self.stacks):
