@@ -100,8 +100,9 @@ def sharded_state_training(rank, world, device_type, axes, dp_axes, rules, steps
   FULL parameters (gathered) and the loss history, for comparison with a replicated single-process run."""
   from recml_b200 import ckpt
   from recml_b200.training import optim_factory, partitioning, state as state_lib
-  part = partitioning.ModelParallelPartitioner(axes, dp_axes=dp_axes, rules=rules, device="cpu") if world > 1 or axes \
-      else partitioning.NullPartitioner("cpu")
+  dev = torch.device("cuda", rank) if device_type == "cuda" else torch.device("cpu")
+  part = partitioning.ModelParallelPartitioner(axes, dp_axes=dp_axes, rules=rules, device=dev) if world > 1 or axes \
+      else partitioning.NullPartitioner(dev)
   tp_group = part.axis_group("model") if (with_tp and hasattr(part, "axis_group")) else (None if with_tp else "none")
   factory = optim_factory.AdamFactory(learning_rate=1e-2, grad_clip_norm=1.0)
   state = part.partition_init(lambda b: state_lib.State.create(model=_ToyNet(tp_group), tx=factory.make()))(None)
@@ -124,7 +125,7 @@ def sharded_state_training(rank, world, device_type, axes, dp_axes, rules, steps
   n = 16
   for x, y in _toy_batches(steps, n):
     sl = slice(dp_rank * n // dp, (dp_rank + 1) * n // dp)
-    state, loss = step((x[sl], y[sl]), state)
+    state, loss = step((x[sl].to(dev), y[sl].to(dev)), state)
     losses.append(float(loss))
   shapes = {k: tuple(p.shape) for k, p in state.params.items()}
   slot_shapes = {k: tuple(t.shape) for k, t in zip(state.optimizer.names, state.optimizer.slots["mu"])}
@@ -145,7 +146,7 @@ def sharded_state_training(rank, world, device_type, axes, dp_axes, rules, steps
     stored = None
   if hasattr(part, "gather_params"):
     part.gather_params()
-  full = {k: p.detach().clone() for k, p in state.model.named_parameters() if "tp." not in k}
+  full = {k: p.detach().cpu().clone() for k, p in state.model.named_parameters() if "tp." not in k}
   return {"losses": losses, "full": full, "shapes": shapes, "slot_shapes": slot_shapes, "restored_ok": restored_ok,
           "stored": stored}
 

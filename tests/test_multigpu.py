@@ -56,3 +56,19 @@ def test_vocab_rank_two_gpus():
 def test_sequence_experiments_two_gpus(which):
   res = dist_utils.run_ranks("sequence_experiment", 2, "nccl", "cuda", which, 30)
   assert res[0]["train"]["loss"] == res[0]["train"]["loss"]   # finite
+
+
+def test_sharded_state_partitioner_two_gpus(tmp_path):
+  """mesh (data 1) x (model 2) over NCCL: a model whose layers are sharded over "model" (gathered before use,
+  gradients cut back onto the shards, shard-sized Adam slots, global-norm clipping across shards) follows the
+  replicated single-process run, and its checkpoint restores."""
+  from tests import dist_workers
+  rules = [(r"b\.weight", ("model", None)), (r"b\.bias", ("model",)), (r"c\.weight", (None, "model"))]
+  ref = dist_workers.sharded_state_training(0, 1, "cpu", [], 1, None, 4, None, False)
+  res = dist_utils.run_ranks("sharded_state_training", 2, "nccl", "cuda", [("data", 1), ("model", 2)], 1, rules, 4,
+                             str(tmp_path / "ck"), False)
+  for r in res:
+    assert r["shapes"]["b.weight"] == (8, 16) and r["slot_shapes"]["b.weight"] == (8, 16) and r["restored_ok"]
+    torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=2e-2, atol=2e-3)
+    for k, v in ref["full"].items():
+      torch.testing.assert_close(r["full"][k], v, rtol=2e-2, atol=2e-3)
