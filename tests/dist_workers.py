@@ -105,7 +105,7 @@ def sharded_state_training(rank, world, device_type, axes, dp_axes, rules, steps
       else partitioning.NullPartitioner(dev)
   tp_group = part.axis_group("model") if (with_tp and hasattr(part, "axis_group")) else (None if with_tp else "none")
   factory = optim_factory.AdamFactory(learning_rate=1e-2, grad_clip_norm=1.0)
-  state = part.partition_init(lambda b: state_lib.State.create(model=_ToyNet(tp_group), tx=factory.make()))(None)
+  state = part.partition_init(lambda b: state_lib.State.create(model=_ToyNet(tp_group).to(dev), tx=factory.make()))(None)
   dp = getattr(part, "dp_size", 1)
   # data-parallel rank = position along the data axes (ranks along "model" see the same slice)
   dp_rank = 0

@@ -150,6 +150,9 @@ def test_no_checkpoint_is_written_after_a_device_error_status(tmp_path):
                                      _lib.ptr(_lib.status_buffer()), ctypes.c_int(9), _lib.ptr(result), _lib.stream())
       return state, {"loss": recml.metrics.mean(loss.detach())}
 
+    def eval_step(self, batch, state):
+      return {"loss": recml.metrics.mean(((state.model(batch["x"]) - batch["y"]) ** 2).mean())}
+
   _lib.check_status()
   trainer = recml.Trainer(partitioner=recml.DataParallelPartitioner(device="cuda"), model_dir=str(tmp_path),
                           train_steps=12, steps_per_loop=4, checkpoint_interval=4)

@@ -64,11 +64,12 @@ def test_sharded_state_partitioner_two_gpus(tmp_path):
   replicated single-process run, and its checkpoint restores."""
   from tests import dist_workers
   rules = [(r"b\.weight", ("model", None)), (r"b\.bias", ("model",)), (r"c\.weight", (None, "model"))]
-  ref = dist_workers.sharded_state_training(0, 1, "cpu", [], 1, None, 4, None, False)
+  # the replicated run uses the same GPU kernels (bf16 products), so the two differ by reduction order only
+  ref = dist_workers.sharded_state_training(0, 1, "cuda", [], 1, None, 4, None, False)
   res = dist_utils.run_ranks("sharded_state_training", 2, "nccl", "cuda", [("data", 1), ("model", 2)], 1, rules, 4,
                              str(tmp_path / "ck"), False)
   for r in res:
     assert r["shapes"]["b.weight"] == (8, 16) and r["slot_shapes"]["b.weight"] == (8, 16) and r["restored_ok"]
-    torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=2e-2, atol=2e-3)
+    torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=1e-3, atol=1e-4)
     for k, v in ref["full"].items():
-      torch.testing.assert_close(r["full"][k], v, rtol=2e-2, atol=2e-3)
+      torch.testing.assert_close(r["full"][k], v, rtol=1e-3, atol=1e-4)
