@@ -64,12 +64,14 @@ def test_sharded_state_partitioner_two_gpus(tmp_path):
   replicated single-process run, and its checkpoint restores."""
   from tests import dist_workers
   rules = [(r"b\.weight", ("model", None)), (r"b\.bias", ("model",)), (r"c\.weight", (None, "model"))]
-  # the replicated run uses the same GPU kernels (bf16 products), so the two differ by reduction order only
+  # The replicated run uses the same GPU kernels.  bf16 products and atomically accumulated weight gradients are
+  # not bit-reproducible between two runs, and Adam turns a sign flip of a tiny gradient into a full learning-rate
+  # step, so after four steps the runs agree to a few learning rates (the tight comparison is the gloo test's).
   ref = dist_workers.sharded_state_training(0, 1, "cuda", [], 1, None, 4, None, False)
   res = dist_utils.run_ranks("sharded_state_training", 2, "nccl", "cuda", [("data", 1), ("model", 2)], 1, rules, 4,
                              str(tmp_path / "ck"), False)
   for r in res:
     assert r["shapes"]["b.weight"] == (8, 16) and r["slot_shapes"]["b.weight"] == (8, 16) and r["restored_ok"]
-    torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(torch.tensor(r["losses"]), torch.tensor(ref["losses"]), rtol=5e-2, atol=5e-3)
     for k, v in ref["full"].items():
-      torch.testing.assert_close(r["full"][k], v, rtol=1e-3, atol=1e-4)
+      torch.testing.assert_close(r["full"][k], v, rtol=0, atol=5e-2)
