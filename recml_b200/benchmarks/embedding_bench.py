@@ -5,7 +5,8 @@ cycling through {64, 128, 256}, fp32 weights, bf16 pooled outputs, bag sizes log
 [1, 100], Zipf(1.05) ids, row-wise Adagrad.  For every per-GPU batch of the sweep it times, on the
 device and as the max over ranks,
   forward   ids exchange + lookup + pooling + pooled all-to-all (+ recording what backward needs)
-  backward  gradient all-to-all + dedup + row-wise Adagrad update
+  backward  gradient all-to-all + dedup (radix sort of the occurrence list, counted in the roofline) + row-wise
+            Adagrad update
 for `backend="fused"` (peer-memory kernels, `csrc/cuda/embedding.cu`) and `backend="collective"`
 (NCCL `all_gather` / `all_to_all_single` + torch ops: the stand-in for the reference's own NCCL
 path, which cannot be installed).  Each fused number is also reported as a fraction of its
@@ -28,6 +29,7 @@ import torch.distributed as dist
 
 from recml_b200 import embedding as emb
 from recml_b200.data import synthetic
+from recml_b200.utils import streams
 
 NVLINK_BPS = 770e9          # measured peer-copy bandwidth per direction per B200 over NVSwitch (900e9 nominal)
 
@@ -93,6 +95,11 @@ def roofline(module, kjt_dev, B, world, hbm_bps):
       uniq = int(torch.unique(sel).numel())
       fwd_hbm[r] += sel.numel() * D * 4                      # rows gathered
       bwd_hbm[r] += sel.numel() * D * 2 + 2 * uniq * D * 4    # gradient vectors read + rows read and written
+      # de-duplication: the radix sort of the (row, gradient index) pairs reads every pair twice and writes it once
+      # per 9-bit pass over the significant bits of the local row number
+      local_rows = tp.vocab if tp.placement is P.TABLE_WISE else (tp.vocab + world - 1) // world
+      passes = max(1, -(-max(1, int(local_rows) - 1).bit_length() // 9))
+      bwd_hbm[r] += sel.numel() * 24 * passes
   f = max(fwd_hbm.max() / hbm_bps, wire.max() / NVLINK_BPS)
   b = max(bwd_hbm.max() / hbm_bps, wire.max() / NVLINK_BPS)
   return f, b, {"fwd_hbm_gb": fwd_hbm.max() / 1e9, "bwd_hbm_gb": bwd_hbm.max() / 1e9, "nvlink_gb": wire.max() / 1e9}
@@ -123,6 +130,8 @@ def run_case(backend, B, vocabs, dims, bags, device, rank, world, iters, warmup)
     if grads is None:
       grads = [torch.randn_like(o) * 1e-3 for o in outs]
     torch.autograd.backward(outs, grads)
+    # the sort and the table update run on side streams of their own: the timed stream waits for them
+    streams.join("emb_bwd", "emb_sort", device=device)
     e2.record()
     torch.cuda.synchronize()
     if it >= warmup:
