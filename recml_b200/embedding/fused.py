@@ -404,8 +404,12 @@ class FusedBackend:
         else:
           slot, goff, stride = self.slot_off[fname], self.grad_off[m.rank][fname], width
         # bags per warp of the tiled forward: a few hundred ids per tile whatever the bag size
-        # (a rank scans all ids of a row-sharded feature and gathers 1 / W of them: weigh the two)
-        avg = self._avg_bag.get(fname, 1.0) * (0.5 if tp.placement is Placement.ROW_WISE and m.world > 2 else 1.0)
+        # (of a row-sharded feature a rank receives 1 / W of every bag when the senders bucketize the ids;
+        # otherwise it scans all of them and gathers 1 / W: weigh the two)
+        avg = self._avg_bag.get(fname, 1.0)
+        if tp.placement is Placement.ROW_WISE and m.world > 1:
+          sparse = self._bucket_state() is not None and L == 0
+          avg = avg / m.world if sparse else (avg * 0.5 if m.world > 2 else avg)
         shift = 5 if avg <= 8 else 4 if avg <= 16 else 3 if avg <= 32 else 2 if avg <= 64 else 1
         bpt = 1 << shift
         feats.append(FeatDesc(m.feature_names.index(fname), KIND[tp.placement], tp.owner, tp.rotation,
