@@ -23,7 +23,8 @@ class NativeError(RuntimeError):
 # call counts the kernels it launches (the radix sort: four per pass, counted by its caller).
 LAUNCHES = {"count": 0}
 _KERNELS_PER_CALL = {"recml_emb_bwd_update": 2, "recml_allreduce_bucket": 3, "recml_radix_sort_scratch_words": 0,
-                     "recml_radix_sort_passes": 0,
+                     "recml_radix_sort_passes": 0, "recml_id_unique_scratch_words": 0, "recml_id_unique_sorted": 3,
+                     "recml_emb_bucketize_struct_size": 0,
                      "recml_emb_struct_sizes": 0, "recml_optim_struct_sizes": 0, "recml_ar_struct_sizes": 0,
                      "recml_ssd_struct_size": 0, "recml_ssd_ckpt_interval": 0, "recml_conv1d_silu_bwd": 2,
                      "recml_hstu_struct_size": 0, "recml_vocab_rank_struct_size": 0}
@@ -39,7 +40,7 @@ class _CountingLib:
     if fn is None:
       raw = getattr(self._lib, name)
       n = _KERNELS_PER_CALL.get(name, 1)
-      if name == "recml_radix_sort_scratch_words":
+      if name in ("recml_radix_sort_scratch_words", "recml_id_unique_scratch_words"):
         raw.restype = ctypes.c_longlong
 
       def fn(*args, _raw=raw, _n=n):
