@@ -35,6 +35,22 @@ def zipf_ids(rng: np.random.Generator, vocab: int, shape, alpha: float = 1.05) -
   return np.clip(np.floor(x).astype(np.int64) - 1, 0, vocab - 1).astype(np.int32)
 
 
+def zipf_head_shares(vocab: int, alpha: float = 1.05, rows: int = 16) -> list[float]:
+  """Probabilities of ids 0 .. rows-1 (the most frequent ones) under `zipf_ids`."""
+  k = np.arange(min(rows, vocab), dtype=np.float64)
+  if abs(alpha - 1.0) < 1e-9:
+    p = (np.log(k + 2.0) - np.log(k + 1.0)) / np.log(vocab + 1.0)
+  else:
+    a = 1.0 - alpha
+    p = ((k + 2.0) ** a - (k + 1.0) ** a) / ((vocab + 1.0) ** a - 1.0)
+  return [float(x) for x in p]
+
+
+def zipf_head_share(vocab: int, alpha: float = 1.05) -> float:
+  """Probability of id 0 (the most frequent one) under `zipf_ids`."""
+  return zipf_head_shares(vocab, alpha, 1)[0]
+
+
 def lognormal_dense(rng: np.random.Generator, batch: int, num_dense: int = 13) -> np.ndarray:
   """log(1 + LogNormal(0, 1)) per dense feature."""
   return np.log1p(rng.lognormal(0.0, 1.0, size=(batch, num_dense))).astype(np.float32)

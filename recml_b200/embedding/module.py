@@ -40,6 +40,8 @@ class ShardedEmbeddingConfig:
   replicate_max_rows: int = 0
   allow_id_dropping: bool = False
   ids_per_sample: Mapping[str, float] | None = None
+  # per FEATURE: share of its ids on the most frequent row, or the shares of rows 0, 1, 2, ... (planner)
+  hot_row_share: Mapping[str, Any] | None = None
   backend: str = "auto"                    # "auto" | "fused" | "collective"
   output_dtype: torch.dtype | None = None
   seed: int = 0
@@ -118,8 +120,21 @@ class ShardedEmbedding(nn.Module):
     table_ids = {}
     for f, t in self.feature_to_table.items():
       table_ids[t] = table_ids.get(t, 0.0) + ids.get(f, 1.0)
+    hot: dict[str, list] = {}      # per table: ids-weighted mean of its features' share lists
+    wsum: dict[str, float] = {}
+    for f, share in (config.hot_row_share or {}).items():
+      t = self.feature_to_table[f]
+      w = ids.get(f, 1.0)
+      lst = [float(share)] if isinstance(share, (int, float)) else [float(x) for x in share]
+      acc = hot.setdefault(t, [])
+      for k, x in enumerate(lst):
+        if k >= len(acc):
+          acc.append(0.0)
+        acc[k] += x * w
+      wsum[t] = wsum.get(t, 0.0) + w
     self.plan = planner_lib.plan_tables(
         tables, self.world, self.rank, ids_per_sample=table_ids,
+        hot_row_share={t: [x / max(wsum[t], 1e-9) for x in acc] for t, acc in hot.items()},
         row_wise_min_bytes=config.row_wise_min_bytes,
         replicate_max_rows=config.replicate_max_rows, overrides=overrides, default=default)
     # Storage: one weight buffer per stack (+ optimizer slots), tagged so the dense

@@ -84,13 +84,17 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
                 row_wise_min_bytes: int | None = None, replicate_max_rows: int = 0,
                 column_wise: Sequence[str] = (), overrides: Mapping[str, Placement] | None = None,
                 default: Placement | None = None, hot_fraction: float = 0.75,
-                table_wise_max_bytes: int = 48 << 30, rank_budget_bytes: int = 140 << 30
-                ) -> ShardingPlan:
+                table_wise_max_bytes: int = 48 << 30, rank_budget_bytes: int = 140 << 30,
+                hot_row_share: Mapping[str, float | Sequence[float]] | None = None) -> ShardingPlan:
   """Greedy plan.  Cost of a table = ids per sample × dim (its gather work and its wire
   bytes).  Tables hotter than `hot_fraction` × (total cost / world), or larger than
   `table_wise_max_bytes`, are row-sharded; the rest go table-wise, largest cost first, to
   the rank with the least accumulated cost that still has `rank_budget_bytes` of room.
-  `row_wise_min_bytes`, when given, replaces the cost rule with a plain size threshold."""
+  `row_wise_min_bytes`, when given, replaces the cost rule with a plain size threshold.
+  `hot_row_share[table]` is the share of a table's ids that hit its most frequent row, or a sequence with the
+  shares of rows 0, 1, 2, ... (from recorded statistics or a known id distribution).  Row sharding spreads the
+  rows evenly but not the ids: the rank that holds row k of a skewed table carries that row's share on top of
+  its 1 / world of the rest, and the greedy pass gives it fewer whole tables in exchange."""
   overrides = dict(overrides or {})
   ids_per_sample = ids_per_sample or {}
   plans: dict[str, TablePlan] = {}
@@ -121,9 +125,24 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
     return Placement.TABLE_WISE
 
   chosen = {t.name: overrides.get(t.name) or auto(t) for t in tables}
-  # row-/column-wise tables load every rank equally: account for them before the greedy pass
-  for t in tables:
-    if chosen[t.name] in (Placement.ROW_WISE, Placement.COLUMN_WISE):
+  hot_row_share = dict(hot_row_share or {})
+  # row-/column-wise tables load every rank equally (up to the hot row of a skewed row-wise table, which sits on
+  # the rank its rotation names): account for them before the greedy pass.  Rotations are handed out in the
+  # order of the second pass below.
+  rot_preview = 0
+  for t in order:
+    if chosen[t.name] is Placement.ROW_WISE:
+      shares = hot_row_share.get(t.name, ())
+      shares = [float(shares)] if isinstance(shares, (int, float)) else [float(x) for x in shares]
+      shares = [min(max(x, 0.0), 1.0) for x in shares]
+      rest = max(1.0 - sum(shares), 0.0)
+      for r in range(world):
+        load[r] += cost_of(t) * rest / world
+        used[r] += t.vocabulary_size * row_bytes(t) // world
+      for k, x in enumerate(shares):          # row k lives on rank (k % world + rotation) % world
+        load[(k % world + rot_preview) % world] += cost_of(t) * x
+      rot_preview += 1
+    elif chosen[t.name] is Placement.COLUMN_WISE:
       for r in range(world):
         load[r] += cost_of(t) / world
         used[r] += t.vocabulary_size * row_bytes(t) // world

@@ -26,7 +26,7 @@ class DLRMDCNv2(nn.Module):
                feature_names: Sequence[str] | None = None, device=None, group=None,
                sharding_strategy: str = "auto", row_wise_min_bytes: int | None = None,
                backend: str = "auto", seed: int = 0, init_scale: float | None = None,
-               overlap_backward: bool = True):
+               overlap_backward: bool = True, hot_row_share: Sequence | None = None):
     super().__init__()
     if bottom_mlp_dims[-1] != embedding_dim:
       raise ValueError("bottom MLP must end in embedding_dim so it can join the feature concat")
@@ -41,7 +41,10 @@ class DLRMDCNv2(nn.Module):
         emb.ShardedEmbeddingConfig(
             specs, embedding_optimizer or emb.RowWiseAdagradOptimizerSpec(learning_rate=0.01),
             sharding_strategy=sharding_strategy, row_wise_min_bytes=row_wise_min_bytes,
-            ids_per_sample=ids, backend=backend, seed=seed),
+            ids_per_sample=ids, backend=backend, seed=seed,
+            # share of each feature's ids on its most frequent row: lets the planner offset the rank that holds the
+            # hot row of a row-sharded table
+            hot_row_share=dict(zip(names, hot_row_share)) if hot_row_share is not None else None),
         device=device, group=group)
     self.bottom = dense.MLP([num_dense, *bottom_mlp_dims], activate_last=True)
     d = embedding_dim * (1 + len(vocab_sizes))

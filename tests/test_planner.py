@@ -70,3 +70,36 @@ def test_oversized_table_is_split_and_budget_is_respected():
   q = [P.plan_tables(big, 2, r, rank_budget_bytes=20 << 30, hot_fraction=10.0) for r in range(2)]
   tw = [n for n in ("t0", "t1") if q[0].tables[n].placement is P.Placement.TABLE_WISE]
   assert len({q[0].tables[n].owner for n in tw}) == len(tw)       # two 15 GB tables cannot share a 20 GB rank
+
+
+def test_hot_row_shares_offset_the_rank_that_holds_them():
+  """Row sharding spreads rows, not ids: with the shares of the most frequent rows known, the greedy pass gives the
+  ranks that hold them fewer whole tables, and the expected ids per rank even out (Criteo geometry, Zipf 1.05)."""
+  import numpy as np
+  from recml_b200.data import synthetic
+  V, bags, W = synthetic.CRITEO_VOCAB_SIZES, synthetic.CRITEO_MULTI_HOT_SIZES, 8
+  opt = S.RowWiseAdagradOptimizerSpec(learning_rate=0.01)
+  tables = [S.TableSpec(name=f"t{i}", vocabulary_size=v, embedding_dim=128, optimizer=opt) for i, v in enumerate(V)]
+  ids = {f"t{i}": float(b) for i, b in enumerate(bags)}
+
+  def expected_ids(plan):
+    load = np.zeros(W)
+    for i, (v, b) in enumerate(zip(V, bags)):
+      tp = plan.tables[f"t{i}"]
+      if tp.placement is P.Placement.TABLE_WISE:
+        load[tp.owner] += b
+      else:
+        ps = synthetic.zipf_head_shares(v, 1.05, 256)
+        for k, pk in enumerate(ps):
+          load[(k % W + tp.rotation) % W] += b * pk
+        load += b * (1 - sum(ps)) / W
+    return load
+
+  even = P.plan_tables(tables, W, 0, ids_per_sample=ids)
+  hot = {f"t{i}": synthetic.zipf_head_shares(v) for i, v in enumerate(V)}
+  skewed = [P.plan_tables(tables, W, r, ids_per_sample=ids, hot_row_share=hot) for r in range(W)]
+  a, b = expected_ids(even), expected_ids(skewed[0])
+  assert a.max() / a.mean() > 1.12 and b.max() / b.mean() < 1.05
+  for p in skewed[1:]:          # every rank derives the same plan
+    assert {n: (t.placement, t.owner, t.rotation) for n, t in p.tables.items()} == \
+        {n: (t.placement, t.owner, t.rotation) for n, t in skewed[0].tables.items()}
