@@ -13,6 +13,8 @@ Two interchangeable backends share the plan, the storage and the semantics:
 """
 from __future__ import annotations
 
+import os
+
 import dataclasses
 import math
 from typing import Any, Callable, Mapping, Sequence
@@ -42,6 +44,9 @@ class ShardedEmbeddingConfig:
   ids_per_sample: Mapping[str, float] | None = None
   # per FEATURE: share of its ids on the most frequent row, or the shares of rows 0, 1, 2, ... (planner)
   hot_row_share: Mapping[str, Any] | None = None
+  # per FEATURE: (ids per sample by residue class id % world, distinct ids per sample by class), e.g. from
+  # `embedding.stats.batch_residue_stats` on the first batch; the planner's most precise cost input
+  residue_stats: Mapping[str, Any] | None = None
   backend: str = "auto"                    # "auto" | "fused" | "collective"
   output_dtype: torch.dtype | None = None
   seed: int = 0
@@ -132,8 +137,18 @@ class ShardedEmbedding(nn.Module):
           acc.append(0.0)
         acc[k] += x * w
       wsum[t] = wsum.get(t, 0.0) + w
+    res: dict[str, list] = {}      # per table: sums over its features; distinct ids capped by the rows of a class
+    for f, (occ, uniq) in (config.residue_stats or {}).items():
+      if len(occ) != self.world:
+        continue
+      t = self.feature_to_table[f]
+      acc = res.setdefault(t, [[0.0] * self.world, [0.0] * self.world])
+      for q in range(self.world):
+        acc[0][q] += float(occ[q])
+        acc[1][q] += float(uniq[q])
     self.plan = planner_lib.plan_tables(
-        tables, self.world, self.rank, ids_per_sample=table_ids,
+        tables, self.world, self.rank, ids_per_sample=table_ids, residue_stats=res,
+        imbalance_tolerance=float(os.environ.get("RECML_PLAN_TOLERANCE", "0.15")),
         hot_row_share={t: [x / max(wsum[t], 1e-9) for x in acc] for t, acc in hot.items()},
         row_wise_min_bytes=config.row_wise_min_bytes,
         replicate_max_rows=config.replicate_max_rows, overrides=overrides, default=default)

@@ -85,7 +85,9 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
                 column_wise: Sequence[str] = (), overrides: Mapping[str, Placement] | None = None,
                 default: Placement | None = None, hot_fraction: float = 0.75,
                 table_wise_max_bytes: int = 48 << 30, rank_budget_bytes: int = 140 << 30,
-                hot_row_share: Mapping[str, float | Sequence[float]] | None = None) -> ShardingPlan:
+                hot_row_share: Mapping[str, float | Sequence[float]] | None = None,
+                residue_stats: Mapping[str, Sequence[Sequence[float]]] | None = None,
+                unique_row_cost: float = 8.0, imbalance_tolerance: float = 0.15) -> ShardingPlan:
   """Greedy plan.  Cost of a table = ids per sample × dim (its gather work and its wire
   bytes).  Tables hotter than `hot_fraction` × (total cost / world), or larger than
   `table_wise_max_bytes`, are row-sharded; the rest go table-wise, largest cost first, to
@@ -94,14 +96,32 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
   `hot_row_share[table]` is the share of a table's ids that hit its most frequent row, or a sequence with the
   shares of rows 0, 1, 2, ... (from recorded statistics or a known id distribution).  Row sharding spreads the
   rows evenly but not the ids: the rank that holds row k of a skewed table carries that row's share on top of
-  its 1 / world of the rest, and the greedy pass gives it fewer whole tables in exchange."""
+  its 1 / world of the rest, and the greedy pass gives it fewer whole tables in exchange.
+  `residue_stats[table] = (ids[world], distinct[world])`, measured on a batch and expressed per sample, says how
+  many ids and how many DISTINCT ids fall into each residue class `id % world`.  With it the cost of a table is
+  ids + `unique_row_cost` x distinct ids (a distinct row costs a read-modify-write of the row and its optimizer
+  state, and a cache miss in the lookup: about eight times an occurrence in the measured update kernel), a
+  row-sharded table loads rank (q + rotation) % world with class q's cost, and its rotation is the one that
+  keeps the most loaded rank lowest.  Tables without statistics use `ids_per_sample` / `hot_row_share`.
+  Going through the tables from the costliest down, a table is also row-sharded when the rank that held it whole
+  would, with its share of the tables row-sharded so far, exceed the mean load by more than
+  `imbalance_tolerance`: no assignment of whole tables can hide such a table."""
   overrides = dict(overrides or {})
   ids_per_sample = ids_per_sample or {}
   plans: dict[str, TablePlan] = {}
   load = [0.0] * world
   used = [0] * world
   rot = 0
-  cost_of = lambda t: ids_per_sample.get(t.name, 1.0) * t.embedding_dim
+  residue_stats = dict(residue_stats or {})
+
+  def class_costs(t):       # cost of each residue class of a table with statistics
+    occ, uniq = residue_stats[t.name]
+    return [(float(occ[q]) + unique_row_cost * float(uniq[q])) * t.embedding_dim for q in range(world)]
+
+  def cost_of(t):
+    if t.name in residue_stats and len(residue_stats[t.name][0]) == world:
+      return sum(class_costs(t))
+    return ids_per_sample.get(t.name, 1.0) * t.embedding_dim
   mean_cost = sum(cost_of(t) for t in tables) / max(world, 1)
   order = sorted(tables, key=lambda t: -cost_of(t))
 
@@ -124,14 +144,34 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
       return Placement.ROW_WISE
     return Placement.TABLE_WISE
 
-  chosen = {t.name: overrides.get(t.name) or auto(t) for t in tables}
+  chosen: dict[str, Placement] = {}
+  total_cost = sum(cost_of(t) for t in tables)
+  split_cost = 0.0          # cost of the tables row-sharded so far (every rank carries 1 / world of it)
+  for t in order:
+    p = overrides.get(t.name) or auto(t)
+    if (p is Placement.TABLE_WISE and t.name not in overrides and world > 1 and default is None and
+        row_wise_min_bytes is None and t.name not in column_wise and t.vocabulary_size >= world and
+        cost_of(t) + split_cost / world > (1.0 + imbalance_tolerance) * total_cost / world):
+      p = Placement.ROW_WISE
+    if p is Placement.ROW_WISE:
+      split_cost += cost_of(t)
+    chosen[t.name] = p
   hot_row_share = dict(hot_row_share or {})
   # row-/column-wise tables load every rank equally (up to the hot row of a skewed row-wise table, which sits on
   # the rank its rotation names): account for them before the greedy pass.  Rotations are handed out in the
   # order of the second pass below.
   rot_preview = 0
+  rot_of: dict[str, int] = {}
   for t in order:
-    if chosen[t.name] is Placement.ROW_WISE:
+    if chosen[t.name] is Placement.ROW_WISE and t.name in residue_stats and len(residue_stats[t.name][0]) == world:
+      per = class_costs(t)
+      best = min(range(world), key=lambda ro: (max(load[r] + per[(r - ro) % world] for r in range(world)), ro))
+      for r in range(world):
+        load[r] += per[(r - best) % world]
+        used[r] += t.vocabulary_size * row_bytes(t) // world
+      rot_of[t.name] = best
+    elif chosen[t.name] is Placement.ROW_WISE:
+      rot_of[t.name] = rot_preview % world
       shares = hot_row_share.get(t.name, ())
       shares = [float(shares)] if isinstance(shares, (int, float)) else [float(x) for x in shares]
       shares = [min(max(x, 0.0), 1.0) for x in shares]
@@ -158,8 +198,9 @@ def plan_tables(tables: Sequence[specs_lib.TableSpec], world: int, rank: int, *,
     cost = cost_of(t)
     tp = TablePlan(t.name, t.vocabulary_size, t.embedding_dim, p)
     if p is Placement.ROW_WISE:
-      tp.rotation = rot % world
-      rot += 1
+      tp.rotation = rot_of.get(t.name, rot % world)
+      if t.name not in residue_stats or len(residue_stats[t.name][0]) != world:
+        rot += 1
       tp.local_rows = _local_rows(t.vocabulary_size, world, rank, tp.rotation)
       tp.local_dim = t.embedding_dim
     elif p is Placement.TABLE_WISE:

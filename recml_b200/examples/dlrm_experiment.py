@@ -9,6 +9,7 @@ concat, top 64-1, batch 256, Adagrad 0.01); `experiment()` is the full Criteo-1T
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Any, Mapping, Sequence
 
 import numpy as np
@@ -115,18 +116,18 @@ class PredictionTask(task_lib.Task):
     c = self.cfg
     device = batch["dense"].device
     torch.manual_seed(rng.initial_seed())
-    # the synthetic generator's id distribution is known: tell the planner how much of each feature's traffic
-    # its hottest row carries (for recorded data this comes from the feedback-directed statistics)
-    hot = None
-    if isinstance(self.train_data, CriteoFactory):
-      hot = [synthetic.zipf_head_shares(v, self.train_data.alpha) for v in c.vocab_sizes]
+    # Placement statistics from this first batch (a collective: every rank contributes its share and derives the
+    # same plan): ids and distinct ids of every feature per residue class of the row sharding.
+    world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+    stats = emb.batch_residue_stats(batch["sparse"], world, self.group) \
+        if os.environ.get("RECML_PLAN_STATS", "1") != "0" else None
     model = dlrm.DLRMDCNv2(
         vocab_sizes=c.vocab_sizes, embedding_dim=c.embedding_dim, num_dense=c.num_dense,
         bottom_mlp_dims=c.bottom_mlp_dims, top_mlp_dims=c.top_mlp_dims,
         num_cross_layers=c.num_cross_layers, cross_rank=c.cross_rank, bag_sizes=c.bag_sizes,
         embedding_optimizer=emb.RowWiseAdagradOptimizerSpec(learning_rate=c.embedding_learning_rate),
         device=device, group=self.group, row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend,
-        init_scale=c.embedding_init_scale, seed=rng.initial_seed(), hot_row_share=hot)
+        init_scale=c.embedding_init_scale, seed=rng.initial_seed(), residue_stats=stats)
     return state_lib.State.create(model=model, tx=self.optimizer.make())
 
   def _metrics(self, r: bce.BCEResult, n: int) -> Mapping[str, M.Metric]:

@@ -26,7 +26,8 @@ class DLRMDCNv2(nn.Module):
                feature_names: Sequence[str] | None = None, device=None, group=None,
                sharding_strategy: str = "auto", row_wise_min_bytes: int | None = None,
                backend: str = "auto", seed: int = 0, init_scale: float | None = None,
-               overlap_backward: bool = True, hot_row_share: Sequence | None = None):
+               overlap_backward: bool = True, hot_row_share: Sequence | None = None,
+               residue_stats=None):
     super().__init__()
     if bottom_mlp_dims[-1] != embedding_dim:
       raise ValueError("bottom MLP must end in embedding_dim so it can join the feature concat")
@@ -44,7 +45,9 @@ class DLRMDCNv2(nn.Module):
             ids_per_sample=ids, backend=backend, seed=seed,
             # share of each feature's ids on its most frequent row: lets the planner offset the rank that holds the
             # hot row of a row-sharded table
-            hot_row_share=dict(zip(names, hot_row_share)) if hot_row_share is not None else None),
+            hot_row_share=dict(zip(names, hot_row_share)) if hot_row_share is not None else None,
+            # ids and distinct ids per residue class, measured on a batch (see `embedding.stats`)
+            residue_stats=residue_stats),
         device=device, group=group)
     self.bottom = dense.MLP([num_dense, *bottom_mlp_dims], activate_last=True)
     d = embedding_dim * (1 + len(vocab_sizes))

@@ -103,3 +103,38 @@ def test_hot_row_shares_offset_the_rank_that_holds_them():
   for p in skewed[1:]:          # every rank derives the same plan
     assert {n: (t.placement, t.owner, t.rotation) for n, t in p.tables.items()} == \
         {n: (t.placement, t.owner, t.rotation) for n, t in skewed[0].tables.items()}
+
+
+def test_residue_statistics_weigh_distinct_rows_and_split_what_cannot_be_hidden():
+  """With per-class counts of ids and DISTINCT ids (what `embedding.stats.batch_residue_stats` measures), a table whose
+  many distinct rows make it too costly for one rank is row-sharded although its id count alone is modest, and the
+  ranks' costs (ids + 8 x distinct ids) even out."""
+  from recml_b200.data import synthetic
+  V, bags, W, B = synthetic.CRITEO_VOCAB_SIZES, synthetic.CRITEO_MULTI_HOT_SIZES, 8, 8192
+  opt = S.RowWiseAdagradOptimizerSpec(learning_rate=0.01)
+  tables = [S.TableSpec(name=f"t{i}", vocabulary_size=v, embedding_dim=128, optimizer=opt) for i, v in enumerate(V)]
+  ids = {f"t{i}": float(b) for i, b in enumerate(bags)}
+  rng = np.random.default_rng(0)
+  draws = [synthetic.zipf_ids(rng, v, (B * b,), 1.05) for v, b in zip(V, bags)]
+  stats = {f"t{i}": ((np.bincount(x % W, minlength=W) / B).tolist(),
+                     (np.bincount(np.unique(x) % W, minlength=W) / B).tolist()) for i, x in enumerate(draws)}
+
+  def cost(plan):
+    c = np.zeros(W)
+    for i, x in enumerate(draws):
+      tp = plan.tables[f"t{i}"]
+      owner = np.full(x.shape, tp.owner) if tp.placement is P.Placement.TABLE_WISE else (x % W + tp.rotation) % W
+      for r in range(W):
+        sel = x[owner == r]
+        c[r] += sel.size + 8 * np.unique(sel).size
+    return c
+
+  plain = P.plan_tables(tables, W, 0, ids_per_sample=ids)
+  informed = [P.plan_tables(tables, W, r, ids_per_sample=ids, residue_stats=stats) for r in range(W)]
+  split = lambda plan: {n for n, t in plan.tables.items() if t.placement is P.Placement.ROW_WISE}
+  assert split(plain) == {"t20", "t21"} and split(informed[0]) >= {"t20", "t21", "t19"} and len(split(informed[0])) <= 4
+  a, b = cost(plain), cost(informed[0])
+  assert b.max() / b.mean() < a.max() / a.mean() - 0.1
+  for p in informed[1:]:
+    assert {n: (t.placement, t.owner, t.rotation) for n, t in p.tables.items()} == \
+        {n: (t.placement, t.owner, t.rotation) for n, t in informed[0].tables.items()}
