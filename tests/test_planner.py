@@ -138,3 +138,14 @@ def test_residue_statistics_weigh_distinct_rows_and_split_what_cannot_be_hidden(
   for p in informed[1:]:
     assert {n: (t.placement, t.owner, t.rotation) for n, t in p.tables.items()} == \
         {n: (t.placement, t.owner, t.rotation) for n, t in informed[0].tables.items()}
+
+
+def test_batch_residue_stats_counts_ids_and_distinct_ids_per_class():
+  import torch
+  from recml_b200 import embedding as emb
+  kjt = emb.KeyedJagged.from_lists({"a": [[0, 4, 4], [1], [8, 9]], "b": [[3], [], [3, 7]]})
+  st = emb.batch_residue_stats(kjt, 4)          # no process group: the local batch is the global one
+  # feature a: ids 0 4 4 1 8 9 -> classes 0,0,0,1,0,1 ; distinct 0 4 1 8 9 -> classes 0,0,1,0,1
+  assert st["a"][0] == [4 / 3, 2 / 3, 0.0, 0.0] and st["a"][1] == [3 / 3, 2 / 3, 0.0, 0.0]
+  assert st["b"][0] == [0.0, 0.0, 0.0, 3 / 3] and st["b"][1] == [0.0, 0.0, 0.0, 2 / 3]
+  assert emb.batch_residue_stats(kjt, 1) is None
