@@ -34,6 +34,7 @@ class ModelConfig:
   bag_sizes: Sequence[int] = synthetic.CRITEO_MULTI_HOT_SIZES
   embedding_dim: int = 128
   num_dense: int = 13
+  placement_statistics: bool = False    # plan the table placement from statistics of the first batch
   bottom_mlp_dims: Sequence[int] = (512, 256, 128)
   top_mlp_dims: Sequence[int] = (1024, 1024, 512, 256, 1)
   num_cross_layers: int = 3
@@ -116,11 +117,15 @@ class PredictionTask(task_lib.Task):
     c = self.cfg
     device = batch["dense"].device
     torch.manual_seed(rng.initial_seed())
-    # Placement statistics from this first batch (a collective: every rank contributes its share and derives the
-    # same plan): ids and distinct ids of every feature per residue class of the row sharding.
-    world = dist.get_world_size(self.group) if dist.is_initialized() else 1
-    stats = emb.batch_residue_stats(batch["sparse"], world, self.group) \
-        if os.environ.get("RECML_PLAN_STATS", "1") != "0" else None
+    # Optional placement statistics from this first batch (a collective: every rank contributes its share and all
+    # derive the same plan): ids and distinct ids of every feature per residue class of the row sharding.  Off by
+    # default: on the Criteo geometry at 8 GPUs the plan it produces (a third table row-sharded, update kernels
+    # within 635 - 800 us instead of 567 - 857 us) lost more in the lookup and the gradient push than it gained
+    # (2.93 against 2.88 ms per step).
+    stats = None
+    if c.placement_statistics or os.environ.get("RECML_PLAN_STATS", "0") == "1":
+      world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+      stats = emb.batch_residue_stats(batch["sparse"], world, self.group)
     model = dlrm.DLRMDCNv2(
         vocab_sizes=c.vocab_sizes, embedding_dim=c.embedding_dim, num_dense=c.num_dense,
         bottom_mlp_dims=c.bottom_mlp_dims, top_mlp_dims=c.top_mlp_dims,
