@@ -616,7 +616,7 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const FwdParams p) {
 // chain, and with a small per-GPU batch the longest chains decide the kernel's duration.  Pooled features
 // only (a launch with a sequence feature takes the per-bag kernel).
 template <int VPL, bool TRAIN, bool GAINS>
-__global__ void __launch_bounds__(256) emb_fwd_tiled_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(256, 2) emb_fwd_tiled_kernel(const FwdParams p) {
   const unsigned long long seq = seq_of(p.seq);
   if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq, p.status, 0)) return;
   const int lane = threadIdx.x & 31;
