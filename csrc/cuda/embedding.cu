@@ -1082,10 +1082,10 @@ __device__ __forceinline__ unsigned int lower_bound(const uint32_t* keys, unsign
 constexpr unsigned int kRange = 128;
 constexpr int kBwdThreads = 128;
 
-// MAXR: register cap.  64 registers let three blocks share an SM with a GEMM CTA; 56 (one allocation unit of 256
-// registers per warp less) let four.
-template <int VPL, bool GAINS, int MAXR>
-__global__ void __maxnreg__(MAXR) emb_bwd_update_kernel(const BwdParams p) {
+// At most 64 registers: three blocks then share an SM with a GEMM CTA.  (A 56-register build, one allocation unit of
+// 256 registers per warp less, lets four blocks in; it measured the same step time and is not kept.)
+template <int VPL, bool GAINS>
+__global__ void __launch_bounds__(kBwdThreads, 8) emb_bwd_update_kernel(const BwdParams p) {
   if (p.wait_flags != nullptr && !wait_all_sources(p.wait_flags, p.W, seq_of(p.seq), p.status, 2)) return;
   const int lane = threadIdx.x & 31;
   const unsigned int n = occ_count_of(p);
@@ -1309,8 +1309,6 @@ extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int g
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool lean = blocks_per_sm == -2;         // four blocks of the 56-register build beside a GEMM CTA
-  if (lean) blocks_per_sm = 4;
   if (blocks_per_sm < 0) blocks_per_sm = 3;      // what fits beside a resident GEMM CTA
   if (blocks_per_sm == 0) blocks_per_sm = 8;
   long long want = (ranges + (kBwdThreads / 32) - 1) / (kBwdThreads / 32);
@@ -1321,18 +1319,13 @@ extern "C" int recml_emb_bwd_update(const BwdParams* p, long long max_occ, int g
   do {                                                                                    \
     static bool configured = false;                                                       \
     if (!configured) {                                                                    \
-      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, true, 64>);              \
-      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, false, 64>);             \
-      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, true, 56>);              \
-      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, false, 56>);             \
+      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, true>);                  \
+      recml::prefer_max_shared_carveout(emb_bwd_update_kernel<V, false>);                 \
       recml::prefer_max_shared_carveout(emb_bwd_finalize_kernel<V>);                      \
       configured = true;                                                                  \
     }                                                                                     \
-    if (lean) {                                                                           \
-      if (gains) emb_bwd_update_kernel<V, true, 56><<<blocks, kBwdThreads, 0, stream>>>(*p);  \
-      else emb_bwd_update_kernel<V, false, 56><<<blocks, kBwdThreads, 0, stream>>>(*p);   \
-    } else if (gains) emb_bwd_update_kernel<V, true, 64><<<blocks, kBwdThreads, 0, stream>>>(*p);  \
-    else emb_bwd_update_kernel<V, false, 64><<<blocks, kBwdThreads, 0, stream>>>(*p);     \
+    if (gains) emb_bwd_update_kernel<V, true><<<blocks, kBwdThreads, 0, stream>>>(*p);    \
+    else emb_bwd_update_kernel<V, false><<<blocks, kBwdThreads, 0, stream>>>(*p);         \
     emb_bwd_finalize_kernel<V><<<fin_blocks, 256, 0, stream>>>(*p);                       \
   } while (0)
   switch (vpl) {
