@@ -94,7 +94,7 @@ struct Params {
   float keep_scale;
 };
 
-enum Mode { kSilu = 0, kSoftmax = 1, kDecay = 2, kSiluDropout = 3 };
+enum Mode { kSilu = 0, kSoftmax = 1, kDecay = 2, kSiluDropout = 3, kSoftmaxDropout = 4 };
 
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
@@ -416,8 +416,8 @@ template <int DH, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const Params p) {
-  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu || MODE == kSiluDropout, DECAY = MODE == kDecay;
-  constexpr bool DROP = MODE == kSiluDropout;
+  constexpr bool SOFTMAX = MODE == kSoftmax || MODE == kSoftmaxDropout, SILU = MODE == kSilu || MODE == kSiluDropout;
+  constexpr bool DECAY = MODE == kDecay, DROP = MODE == kSiluDropout || MODE == kSoftmaxDropout;
   using S = Smem<DH>;
   // CTAs are dispatched in linear block order; heads vary fastest so that this order follows the work-sorted list
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;
@@ -575,6 +575,12 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // the maximum grows the accumulated output is rescaled in tensor memory (it is idle between P_{j-1}·V and
       // P_j·V).  exp is evaluated as 2^(x log2 e - m).
       const float sc2 = p.scale * 1.4426950408889634f;
+      uint32_t sm_drop_row = 0, sm_drop_hi = 0;
+      if constexpr (DROP) {
+        const unsigned long long key = *p.dropout_key;
+        sm_drop_row = dropout_row_hash(key, h, tok0 + r);
+        sm_drop_hi = static_cast<uint32_t>(key >> 32);
+      }
       float m = -INFINITY, l = 0.f;
       float* mx = softmax_xchg + quarter * 32 + lane;      // [parity][cb][row]: + parity * 512 + cb * 128
       const uint32_t xbar = bar(12 + quarter);
@@ -610,9 +616,14 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const float x0 = __uint_as_float(v[e]), x1 = __uint_as_float(v[e + 1]);
-          const float p0 = x0 == -INFINITY ? 0.f : exp2_fast(x0 - m_new);
-          const float p1 = x1 == -INFINITY ? 0.f : exp2_fast(x1 - m_new);
+          float p0 = x0 == -INFINITY ? 0.f : exp2_fast(x0 - m_new);
+          float p1 = x1 == -INFINITY ? 0.f : exp2_fast(x1 - m_new);
           psum += p0 + p1;
+          if constexpr (DROP) {      // dropout acts on the normalised weights: the row sum keeps all of them
+            const int kt = seq_start + kj0 + e;
+            p0 = dropout_keep(sm_drop_row, sm_drop_hi, kt, p.drop_threshold) ? p0 * p.keep_scale : 0.f;
+            p1 = dropout_keep(sm_drop_row, sm_drop_hi, kt + 1, p.drop_threshold) ? p1 * p.keep_scale : 0.f;
+          }
           packed[e >> 1] = pack_bf16(p0, p1);
         }
         l = fmaf(l, alpha, psum);
@@ -760,8 +771,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const Params p) {
-  constexpr bool SOFTMAX = MODE == kSoftmax, SILU = MODE == kSilu || MODE == kSiluDropout, DECAY = MODE == kDecay;
-  constexpr bool DROP = MODE == kSiluDropout;
+  constexpr bool SOFTMAX = MODE == kSoftmax || MODE == kSoftmaxDropout, SILU = MODE == kSilu || MODE == kSiluDropout;
+  constexpr bool DECAY = MODE == kDecay, DROP = MODE == kSiluDropout || MODE == kSoftmaxDropout;
   using S = SmemB<DH>;
   const int lin = blockIdx.x + gridDim.x * blockIdx.y;   // heads fastest: dispatch order = work-sorted list order
   const int tile_id = lin / p.H;
@@ -973,8 +984,12 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const bool visible = row_ok && kj < L && (!p.causal || kj <= qi);
                 // P = exp(x - lse);  dS = P * (dP - delta)
                 const float pv = visible ? __expf(s_raw * p.scale - lse_r) : 0.f;
-                pr[u] = pv;
-                dr[u] = visible ? pv * (dp - delta_r) : 0.f;
+                float keep = 1.f;
+                if constexpr (DROP)
+                  keep = dropout_keep(drop_row, drop_hi, seq_start + kj, p.drop_threshold) ? p.keep_scale : 0.f;
+                // O = sum_j P_j M_j V_j with the dropout mask M:  dV uses P M, dS = P (dP M - delta)
+                pr[u] = pv * keep;
+                dr[u] = visible ? pv * (dp * keep - delta_r) : 0.f;
               } else {
                 // h = x / 2;  P = x sigmoid(x) = h tanh(h) + h;  dP/dx = sig + P (1 - sig), sig = (tanh(h) + 1) / 2
                 const uint32_t w = k == 0 ? hb[g].x : k == 1 ? hb[g].y : k == 2 ? hb[g].z : hb[g].w;
@@ -1154,7 +1169,7 @@ extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, 
                                    cudaStream_t stream) {
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if ((p->mode == kSilu || p->mode == kSiluDropout) && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
-  if (p->mode == kSiluDropout && p->dropout_key == nullptr) return -14;
+  if ((p->mode == kSiluDropout || p->mode == kSoftmaxDropout) && p->dropout_key == nullptr) return -14;
   if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->cum_pitch < p->T + BKV)) return -13;
   if (p->mode != kDecay && p->qk_shared) return -13;
 #define RECML_ATTN_FWD(D)                                                                  \
@@ -1163,6 +1178,7 @@ extern "C" int recml_hstu_attn_fwd(const void* q, const void* k, const void* v, 
     case kSoftmax: return launch_fwd<D, kSoftmax>(q, k, v, *p, n_tiles, stream);           \
     case kDecay: return launch_fwd<D, kDecay>(q, k, v, *p, n_tiles, stream);               \
     case kSiluDropout: return launch_fwd<D, kSiluDropout>(q, k, v, *p, n_tiles, stream);   \
+    case kSoftmaxDropout: return launch_fwd<D, kSoftmaxDropout>(q, k, v, *p, n_tiles, stream); \
     default: return -10;                                                                   \
   }
   if (p->Dh == 64) RECML_ATTN_FWD(64)
@@ -1201,7 +1217,7 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
   if (p->T <= 0 || n_tiles <= 0) return 0;
   if (p->num_buckets + 1 > 256) return -11;
   if ((p->mode == kSilu || p->mode == kSiluDropout) && (p->bias_tiles == nullptr || p->pair_base == nullptr)) return -12;
-  if (p->mode == kSiluDropout && p->dropout_key == nullptr) return -14;
+  if ((p->mode == kSiluDropout || p->mode == kSoftmaxDropout) && p->dropout_key == nullptr) return -14;
   if (p->mode == kDecay && (p->cum == nullptr || !p->causal || !p->qk_shared || p->dk_acc == nullptr || p->cum_pitch < p->T + BKV))
     return -13;
   if (p->mode != kDecay && p->qk_shared) return -13;
@@ -1211,6 +1227,7 @@ extern "C" int recml_hstu_attn_bwd(const void* q, const void* k, const void* v, 
     case kSoftmax: return launch_bwd<D, kSoftmax>(q, k, v, d_o, *p, n_tiles, stream);      \
     case kDecay: return launch_bwd<D, kDecay>(q, k, v, d_o, *p, n_tiles, stream);          \
     case kSiluDropout: return launch_bwd<D, kSiluDropout>(q, k, v, d_o, *p, n_tiles, stream); \
+    case kSoftmaxDropout: return launch_bwd<D, kSoftmaxDropout>(q, k, v, d_o, *p, n_tiles, stream); \
     default: return -10;                                                                   \
   }
   if (p->Dh == 64) RECML_ATTN_BWD(64)

@@ -22,7 +22,7 @@ class _Params(ctypes.Structure):
               ("cum_pitch", ctypes.c_longlong), ("qk_shared", c_int), ("dk_acc", c_vp), ("dcum", c_vp), ("v_rows", c_vp),
               ("dropout_key", c_vp), ("drop_threshold", ctypes.c_uint), ("keep_scale", ctypes.c_float)]
 
-MODE_SILU, MODE_SOFTMAX, MODE_DECAY, MODE_SILU_DROPOUT = 0, 1, 2, 3
+MODE_SILU, MODE_SOFTMAX, MODE_DECAY, MODE_SILU_DROPOUT, MODE_SOFTMAX_DROPOUT = 0, 1, 2, 3, 4
 
 
 class _BiasParams(ctypes.Structure):
@@ -299,12 +299,12 @@ def _attach(p: _Params, bc: BiasContext) -> None:
   p.pair_base, p.cap_pairs, p.bias_tiles = bc.pair_base.data_ptr(), bc.cap_pairs, bc.tiles.data_ptr()
 
 
-def _set_dropout(p: _Params, dropout) -> None:
+def _set_dropout(p: _Params, dropout, mode: int = MODE_SILU_DROPOUT) -> None:
   """`dropout` = (rate, key): key is an int64 device tensor of one element that seeds the mask."""
   if dropout is None:
     return
   rate, key = dropout
-  p.mode = MODE_SILU_DROPOUT
+  p.mode = mode
   p.dropout_key = key.data_ptr()
   p.drop_threshold = min(int(rate * 4294967296.0), 4294967295)
   p.keep_scale = 1.0 / (1.0 - rate)
@@ -368,20 +368,23 @@ def backward(do, q, k, v, seq_offsets, bc: BiasContext, max_seq_len, causal, sca
 # ---- softmax mode: the same kernels with P = softmax(scale * QK^T) over the visible keys ----------------------
 
 
-def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale):
-  """Jagged softmax attention; returns (out `[T, H, Dh]` bf16, row log-sum-exp `[T, H]` fp32)."""
+def softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale, dropout=None):
+  """Jagged softmax attention; returns (out `[T, H, Dh]` bf16, row log-sum-exp `[T, H]` fp32).  With
+  `dropout` = (rate, key) the normalised weights are dropped and rescaled before they multiply the values;
+  the log-sum-exp is that of all visible keys."""
   assert rows_ok(q) and rows_ok(k) and rows_ok(v)
   tiles = _tiles(seq_offsets, q.shape[0])
   out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
   lse = torch.empty(q.shape[0], q.shape[1], dtype=torch.float32, device=q.device)
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v)
   p.out, p.mode, p.lse = out.data_ptr(), MODE_SOFTMAX, lse.data_ptr()
+  _set_dropout(p, dropout, MODE_SOFTMAX_DROPOUT)
   _lib.check_rc(_lib.cuda().recml_hstu_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "softmax_attn_fwd")
   return out, lse
 
 
-def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, scale):
+def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, scale, dropout=None):
   tiles = _tiles(seq_offsets, q.shape[0], backward=True)
   do = as_rows(do)
   delta = (do.float() * out.float()).sum(-1).contiguous()          # [T, H]
@@ -390,6 +393,7 @@ def softmax_backward(do, out, lse, q, k, v, seq_offsets, max_seq_len, causal, sc
   p = _params(q, seq_offsets, None, None, None, max_seq_len, causal, scale, tiles, k, v, do)
   p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
   p.mode, p.lse, p.delta = MODE_SOFTMAX, lse.data_ptr(), delta.data_ptr()
+  _set_dropout(p, dropout, MODE_SOFTMAX_DROPOUT)
   _lib.check_rc(_lib.cuda().recml_hstu_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do), ctypes.byref(p),
                                                 c_int(tiles[2]), _lib.stream()), "softmax_attn_bwd")
   return dq.to(q.dtype), dk, dv

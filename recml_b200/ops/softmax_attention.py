@@ -41,26 +41,32 @@ class _JaggedSoftmaxFn(torch.autograd.Function):
   """Softmax attention over packed sequences: q, k, v `[T, H, Dh]` bf16, `seq_offsets [B+1]`."""
 
   @staticmethod
-  def forward(ctx, q, k, v, seq_offsets, max_seq_len, causal, scale):
+  def forward(ctx, q, k, v, seq_offsets, max_seq_len, causal, scale, dropout_p=0.0):
     from recml_b200.ops import hstu_cuda
-    out, lse = hstu_cuda.softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale)
+    from recml_b200.ops.hstu_attention import _draw_dropout
+    drop = _draw_dropout(dropout_p, q.device)
+    out, lse = hstu_cuda.softmax_forward(q, k, v, seq_offsets, max_seq_len, causal, scale, dropout=drop)
     ctx.save_for_backward(q, k, v, out, lse, seq_offsets)
     ctx.meta = (max_seq_len, causal, scale)
+    ctx.drop = drop
     return out
 
   @staticmethod
   def backward(ctx, do):
     from recml_b200.ops import hstu_cuda
     q, k, v, out, lse, seq_offsets = ctx.saved_tensors
-    dq, dk, dv = hstu_cuda.softmax_backward(do, out, lse, q, k, v, seq_offsets, *ctx.meta)
-    return dq, dk, dv, None, None, None, None
+    dq, dk, dv = hstu_cuda.softmax_backward(do, out, lse, q, k, v, seq_offsets, *ctx.meta, dropout=ctx.drop)
+    return dq, dk, dv, None, None, None, None, None
 
 
-def jagged_softmax_attention(q, k, v, seq_offsets, max_seq_len: int, causal: bool, scale: float | None = None):
+def jagged_softmax_attention(q, k, v, seq_offsets, max_seq_len: int, causal: bool, scale: float | None = None,
+                             dropout_p: float = 0.0):
+  """`dropout_p` > 0 drops attention weights inside the kernels (a counter-based hash of head, query token and
+  key token seeded by one random key per call; the backward pass recomputes the same mask)."""
   scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
   from recml_b200.ops import hstu_cuda
   return _JaggedSoftmaxFn.apply(hstu_cuda.as_rows(q), hstu_cuda.as_rows(k), hstu_cuda.as_rows(v), seq_offsets, max_seq_len,
-                                causal, scale)
+                                causal, scale, dropout_p)
 
 
 def _kernel_ok(q, L: int) -> bool:
@@ -73,7 +79,7 @@ def _kernel_ok(q, L: int) -> bool:
 def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: bool, dropout_p: float = 0.0,
                          training: bool = False):
   """Attention whose mask is `key is not padding` ∧ (`key <= query` when causal): q, k, v `[B, L, H, Dh]`,
-  `padding_mask [B, L]` (True = real token).  On a GPU (head dim 64 / 128, no attention dropout) the valid
+  `padding_mask [B, L]` (True = real token).  On a GPU (head dim 64 / 128) the valid
   tokens are packed and run through the jagged tcgen05 kernels in softmax mode (streaming softmax, any
   length), so no `[B, H, L, L]` score tensor is ever written; rows of padded queries come back as zeros
   (the dense formulation gives them the average of the visible values; nothing downstream reads them).
@@ -81,14 +87,15 @@ def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: boo
   the real tokens, padding goes to a spare row, and the kernels see `B * L` rows of capacity.
   Everywhere else this is `softmax_attention` with the merged mask."""
   B, L, H, Dh = q.shape
-  if not _kernel_ok(q, L) or (training and dropout_p > 0):
+  drop = dropout_p if training else 0.0
+  if not _kernel_ok(q, L):
     mask = merge_masks(B, L, q.device, padding_mask=padding_mask, causal=causal)
     return softmax_attention(q, k, v, mask, dropout_p, training)
   dt = q.dtype
   flat = lambda t: t.reshape(B * L, H, Dh).to(torch.bfloat16)
   if padding_mask is None:
     offs = torch.arange(B + 1, device=q.device, dtype=torch.int32) * L
-    out = jagged_softmax_attention(flat(q), flat(k), flat(v), offs, L, causal)
+    out = jagged_softmax_attention(flat(q), flat(k), flat(v), offs, L, causal, dropout_p=drop)
     return out.reshape(B, L, H, Dh).to(dt)
   T = B * L
   valid = padding_mask.bool().reshape(T)
@@ -97,7 +104,7 @@ def structured_attention(q, k, v, padding_mask: torch.Tensor | None, causal: boo
   offs = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
   offs[1:] = valid.reshape(B, L).sum(1).cumsum(0)
   pack = lambda t: torch.zeros(T + 1, H, Dh, dtype=torch.bfloat16, device=q.device).index_copy(0, dest, flat(t))[:T]
-  packed = jagged_softmax_attention(pack(q), pack(k), pack(v), offs, L, causal)
+  packed = jagged_softmax_attention(pack(q), pack(k), pack(v), offs, L, causal, dropout_p=drop)
   # (rows past the last real token are never written by the kernels: select, do not multiply)
   out = torch.where(valid[:, None, None], packed.index_select(0, dest.clamp(max=T - 1)), torch.zeros((), dtype=packed.dtype, device=q.device))
   return out.reshape(B, L, H, Dh).to(dt)

@@ -63,3 +63,38 @@ def test_sasrec_block_uses_the_kernel_and_trains():
     opt.step()
     losses.append(float(loss.detach()))
   assert all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("rate,L,causal", [(0.2, 200, True), (0.5, 330, False)])
+def test_attention_dropout_in_the_softmax_kernels(rate, L, causal):
+  """Dropout on the softmax weights (reference `recml/layers/keras/sasrec.py:84-97`: Keras MultiHeadAttention with
+  a dropout rate) runs inside the kernels: the weights are normalised over ALL visible keys, then dropped and
+  rescaled before they multiply the values.  The oracle rebuilds the mask from the key that the call drew."""
+  from recml_b200.ops import hstu_attention as A, hstu_cuda
+  torch.manual_seed(5)
+  B, H, Dh = 2, 2, 64
+  dev = "cuda"
+  q, k, v = ((torch.randn(B, L, H, Dh, device=dev) * 0.8).to(torch.bfloat16).float() for _ in range(3))
+  a = [t.clone().requires_grad_() for t in (q, k, v)]
+  r = [t.clone().requires_grad_() for t in (q, k, v)]
+  out = sm.structured_attention(*a, None, causal, dropout_p=rate, training=True)
+  key = int(A.LAST_DROPOUT_KEY.item())
+  # the kernels number tokens over the packed batch: sequence b holds tokens b * L .. b * L + L - 1
+  keep = torch.stack([torch.stack([hstu_cuda.dropout_keep_mask(key, h, torch.arange(b * L, (b + 1) * L, device=dev),
+                                                                torch.arange(b * L, (b + 1) * L, device=dev), rate)
+                                   for h in range(H)]) for b in range(B)])            # [B, H, L, L]
+  s = torch.einsum("bqhd,bkhd->bhqk", r[0], r[1]) / math.sqrt(Dh)
+  if causal:
+    s = s.masked_fill(~torch.tril(torch.ones(L, L, dtype=torch.bool, device=dev)), float("-inf"))
+  p = torch.softmax(s, -1) * keep.float() / (1.0 - rate)
+  ref = torch.einsum("bhqk,bkhd->bqhd", p, r[2])
+  torch.testing.assert_close(out, ref, rtol=2e-2, atol=2e-2)
+  assert abs(float(keep.float().mean()) - (1 - rate)) < 0.02
+  g = torch.randn_like(out)
+  out.backward(g)
+  ref.backward(g)
+  for name, x, y in zip("qkv", a, r):
+    torch.testing.assert_close(x.grad, y.grad, rtol=3e-2, atol=3e-2, msg=lambda m, n=name: f"d{n}: {m}")
+  # evaluation mode drops nothing
+  o_eval = sm.structured_attention(q, k, v, None, causal, dropout_p=rate, training=False)
+  torch.testing.assert_close(o_eval, _dense(q, k, v, None, causal), rtol=2e-2, atol=2e-2)
