@@ -7,6 +7,7 @@ import torch
 from torch import nn
 
 from recml_b200.layers import embeddings as emb_layers
+from recml_b200.layers import utils as layer_utils
 from recml_b200.layers import transformer, utils
 from recml_b200.ops import dense as dense_ops
 from recml_b200.ops import norm as norm_ops
@@ -36,7 +37,7 @@ class MaskedLMHead(nn.Module):
     return self.token_embedding[0](h, reverse=True).float() + self.bias
 
 
-class BERT4Rec(nn.Module):
+class BERT4Rec(layer_utils.Configurable, nn.Module):
   def __init__(self, *, vocab_size: int, max_positions: int, num_types: int | None = None, model_dim: int,
                mlp_dim: int, num_heads: int, num_layers: int, dropout: float = 0.0, norm_eps: float = 1e-12,
                add_head: bool = True):
@@ -55,6 +56,16 @@ class BERT4Rec(nn.Module):
                                      normalize_first=False, causal=False, init=_trunc02_)
         for _ in range(num_layers))
     self.head = MaskedLMHead(self.item_embedding, model_dim, vocab_size) if add_head else None
+
+  def compute_output_shape(self, inputs_shape, mask_positions_shape=None):
+    """Output shape for ids of `inputs_shape`; with the masked-LM head the rows are the masked positions
+    (`recml/layers/keras/bert4rec.py:194-205`)."""
+    c = self.__dict__["_init_config"]
+    if c["add_head"]:
+      if mask_positions_shape is None:
+        raise ValueError("`mask_positions_shape` cannot be None when `add_head` is True.")
+      return (*inputs_shape[:-1], mask_positions_shape[-1], c["vocab_size"])
+    return (*inputs_shape, c["model_dim"])
 
   def forward(self, inputs, type_ids=None, padding_mask=None, attention_mask=None, mask_positions=None):
     e = self.item_embedding(inputs)

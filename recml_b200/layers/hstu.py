@@ -19,6 +19,7 @@ import torch
 from torch import nn
 
 from recml_b200.layers import embeddings as emb_layers
+from recml_b200.layers import utils as layer_utils
 from recml_b200.layers import utils
 from recml_b200.ops import dense as dense_ops
 from recml_b200.ops import hstu_attention as attn_ops
@@ -30,7 +31,7 @@ def default_bucketization(tensor: torch.Tensor, bucket_size: float = 0.301) -> t
   return (torch.log(v) / bucket_size).to(torch.int64)
 
 
-class RelativePositionalBias(nn.Module):
+class RelativePositionalBias(layer_utils.Configurable, nn.Module):
   """2N−1 learned scalars expanded to a Toeplitz `[1, n, n]` bias: bias[i, j] = w[(j − i) + n − 1]."""
 
   def __init__(self, max_seq_len: int, init_std: float = 0.02):
@@ -45,7 +46,7 @@ class RelativePositionalBias(nn.Module):
     return w[(i[None, :] - i[:, None]) + n - 1][None]
 
 
-class RelativeBucketedTimeAndPositionBasedBias(nn.Module):
+class RelativeBucketedTimeAndPositionBasedBias(layer_utils.Configurable, nn.Module):
   """ts_w[bucket(t_ext[i+1] − t[j])] (+ positional bias); `[B, N] → [B, N, N]`."""
 
   def __init__(self, num_buckets: int = 128, bucketization_fn: Callable = default_bucketization,
@@ -73,7 +74,7 @@ def _glorot_uniform_(w: torch.Tensor, fan_in: int, fan_out: int) -> None:
   nn.init.uniform_(w, -lim, lim)
 
 
-class HSTUBlock(nn.Module):
+class HSTUBlock(layer_utils.Configurable, nn.Module):
   def __init__(self, model_dim: int, num_heads: int, use_bias: bool = False, activation=torch.nn.functional.silu,
                layer_norm_epsilon: float = 1e-6, scaled_pointwise_attn: bool = False,
                softmax_attention: bool = False, dropout: float = 0.0):
@@ -155,7 +156,7 @@ class HSTUBlock(nn.Module):
     return self._finish(tokens, u, attn)
 
 
-class HSTU(nn.Module):
+class HSTU(layer_utils.Configurable, nn.Module):
   def __init__(self, *, vocab_size: int, max_positions: int | None = None, model_dim: int, num_heads: int,
                num_layers: int, dropout: float = 0.0, norm_eps: float = 1e-6, scale_by_sqrt_dim: bool = False,
                add_head: bool = True, use_relative_bias: bool = False, num_time_buckets: int = 128,
@@ -179,6 +180,11 @@ class HSTU(nn.Module):
       assert self.max_seq_len is not None, "relative bias needs max_seq_len"
       self.relative_bias = RelativeBucketedTimeAndPositionBasedBias(
           num_time_buckets, position_bias_layer=RelativePositionalBias(self.max_seq_len))
+
+  def compute_output_shape(self, inputs_shape):
+    """Output shape for ids of `inputs_shape` (`recml/layers/keras/hstu.py:623-625`)."""
+    c = self.__dict__["_init_config"]
+    return (*inputs_shape, c["vocab_size"] if c["add_head"] else c["model_dim"])
 
   def _final_norm(self, x):
     return norm_ops.layer_norm(x, self.final_norm_w, self.final_norm_b, self.norm_eps)

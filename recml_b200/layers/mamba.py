@@ -12,6 +12,7 @@ import torch
 from torch import nn
 
 from recml_b200.layers import embeddings as emb_layers
+from recml_b200.layers import utils as layer_utils
 from recml_b200.ops import dense as dense_ops
 from recml_b200.ops import norm as norm_ops
 from recml_b200.ops import ssd as ssd_ops
@@ -19,7 +20,7 @@ from recml_b200.ops import ssd as ssd_ops
 segsum_chunked = ssd_ops.ssd_chunked
 
 
-class Mamba2(nn.Module):
+class Mamba2(layer_utils.Configurable, nn.Module):
   def __init__(self, d_model: int, d_state: int = 64, d_conv: int = 4, conv_init: float | None = None,
                expand: int = 4, nheads: int = 8, chunk_size: int = 256, init_range_a=(1, 16), dt_min: float = 0.001,
                dt_max: float = 0.1, dt_init_floor: float = 1e-4, dt_limit=(0.0, float("inf")),
@@ -77,7 +78,7 @@ class Mamba2(nn.Module):
     return dense_ops.linear(y, self.out_proj, self.out_bias)
 
 
-class Mamba2Block(nn.Module):
+class Mamba2Block(layer_utils.Configurable, nn.Module):
   def __init__(self, d_model: int, d_state: int = 64, d_conv: int = 4, expand: int = 2, nheads: int = 8,
                chunk_size: int = 64, ffn_expand: int = 12, norm_eps: float = 1e-12, dropout: float = 0.0):
     super().__init__()
@@ -102,7 +103,7 @@ class Mamba2Block(nn.Module):
     return y
 
 
-class Mamba2Stack(nn.Module):
+class Mamba2Stack(layer_utils.Configurable, nn.Module):
   def __init__(self, num_layers: int, **block_kwargs):
     super().__init__()
     self.blocks = nn.ModuleList(Mamba2Block(**block_kwargs) for _ in range(num_layers))
@@ -113,7 +114,7 @@ class Mamba2Stack(nn.Module):
     return x
 
 
-class Mamba4Rec(nn.Module):
+class Mamba4Rec(layer_utils.Configurable, nn.Module):
   def __init__(self, vocab_size: int, model_dim: int, mlp_expand: int, num_heads: int, num_layers: int,
                d_expand: int, d_state: int = 64, d_conv: int = 4, chunk_size: int = 256, norm_eps: float = 1e-6,
                dropout: float = 0.0, add_head: bool = True):
@@ -125,6 +126,11 @@ class Mamba4Rec(nn.Module):
         Mamba2Block(model_dim, d_state, d_conv, expand=d_expand, nheads=num_heads, ffn_expand=mlp_expand,
                     chunk_size=chunk_size, norm_eps=norm_eps, dropout=dropout) for _ in range(num_layers))
     self.norm_eps, self.add_head = norm_eps, add_head
+
+  def compute_output_shape(self, inputs_shape):
+    """Output shape for ids of `inputs_shape` (`recml/layers/keras/mamba.py:747-749`)."""
+    c = self.__dict__["_init_config"]
+    return (*inputs_shape, c["vocab_size"] if c["add_head"] else c["model_dim"])
 
   def forward(self, inputs, padding_mask=None):
     x = self.dropout_layer(self.item_embedding(inputs))

@@ -9,11 +9,12 @@ import torch
 from torch import nn
 
 from recml_b200.layers import embeddings as emb_layers
+from recml_b200.layers import utils as layer_utils
 from recml_b200.layers import transformer
 from recml_b200.ops import norm as norm_ops
 
 
-class SASRec(nn.Module):
+class SASRec(layer_utils.Configurable, nn.Module):
   def __init__(self, *, vocab_size: int, max_positions: int, model_dim: int, mlp_dim: int, num_heads: int,
                num_layers: int, dropout: float = 0.0, norm_eps: float = 1e-6, scale_by_sqrt_dim: bool = False,
                add_head: bool = True):
@@ -29,6 +30,11 @@ class SASRec(nn.Module):
     self.final_norm_w, self.final_norm_b = nn.Parameter(torch.ones(model_dim)), nn.Parameter(torch.zeros(model_dim))
     self.norm_eps, self.model_dim, self.scale_by_sqrt_dim, self.add_head = norm_eps, model_dim, \
         scale_by_sqrt_dim, add_head
+
+  def compute_output_shape(self, inputs_shape):
+    """Output shape for ids of `inputs_shape` (`recml/layers/keras/sasrec.py:165-167`)."""
+    c = self.__dict__["_init_config"]
+    return (*inputs_shape, c["vocab_size"] if c["add_head"] else c["model_dim"])
 
   def _norm(self, x):
     return norm_ops.layer_norm(x, self.final_norm_w, self.final_norm_b, self.norm_eps)

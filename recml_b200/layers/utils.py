@@ -57,3 +57,97 @@ def apply_rotary_encoding(x: torch.Tensor, *, positions: torch.Tensor | None = N
 
 def large_negative_for_attention(dtype: torch.dtype) -> float:
   return -3e4 if dtype == torch.float16 else -1e9
+
+
+# ---- constructor-argument round trip ----------------------------------------------------------------------
+
+
+def _config_value(v: Any) -> Any:
+  """A constructor argument as something JSON can hold: functions become their dotted import path, a nested
+  layer its class and its own config."""
+  if isinstance(v, Configurable):
+    return {"layer": f"{type(v).__module__}:{type(v).__qualname__}", "config": v.get_config()}
+  if callable(v) and not isinstance(v, torch.nn.Module) and hasattr(v, "__module__") and hasattr(v, "__qualname__"):
+    return {"callable": f"{v.__module__}.{v.__qualname__}"}
+  if isinstance(v, torch.dtype):
+    return {"dtype": str(v).removeprefix("torch.")}
+  if isinstance(v, (list, tuple)):
+    return [_config_value(x) for x in v]
+  if isinstance(v, dict):
+    return {str(k): _config_value(x) for k, x in v.items()}
+  return v
+
+
+def _config_restore(v: Any) -> Any:
+  if isinstance(v, dict) and set(v) == {"callable"}:
+    import importlib
+    parts = v["callable"].split(".")
+    for cut in range(len(parts) - 1, 0, -1):              # longest importable module prefix, then attributes
+      try:
+        obj = importlib.import_module(".".join(parts[:cut]))
+      except ImportError:
+        continue
+      for name in parts[cut:]:
+        obj = getattr(obj, name)
+      return obj
+    raise ImportError(f"cannot resolve {v['callable']!r}")
+  if isinstance(v, dict) and set(v) == {"dtype"}:
+    return getattr(torch, v["dtype"])
+  if isinstance(v, dict) and set(v) == {"layer", "config"}:
+    return build_from_config(v["layer"], v["config"])
+  if isinstance(v, list):
+    return [_config_restore(x) for x in v]
+  if isinstance(v, dict):
+    return {k: _config_restore(x) for k, x in v.items()}
+  return v
+
+
+class Configurable:
+  """`get_config()` / `from_config()` for a layer, the pair every layer of the reference carries
+  (`recml/layers/keras/hstu.py:93-101,269-292,603-628`, `sasrec.py:152-170`, `bert4rec.py:186-208`,
+  `mamba.py:363-385,727-752`).  The config is the constructor call: the arguments the outermost `__init__`
+  received (defaults included), with functions written as dotted import paths so that the dictionary survives
+  JSON; `cls(**config)` and `cls.from_config(config)` rebuild an identically shaped, freshly initialised layer.
+  """
+
+  def __init_subclass__(cls, **kwargs):
+    super().__init_subclass__(**kwargs)
+    init = cls.__dict__.get("__init__")
+    if init is None:
+      return
+    import functools
+    import inspect
+    sig = inspect.signature(init)
+
+    @functools.wraps(init)
+    def wrapped(self, *args, **kw):
+      if "_init_config" not in self.__dict__:               # the outermost constructor wins
+        bound = sig.bind(self, *args, **kw)
+        bound.apply_defaults()
+        cfg = {}
+        for name, value in list(bound.arguments.items())[1:]:
+          kind = sig.parameters[name].kind
+          if kind is inspect.Parameter.VAR_KEYWORD:
+            cfg.update(value)
+          elif kind is not inspect.Parameter.VAR_POSITIONAL:
+            cfg[name] = value
+        object.__setattr__(self, "_init_config", cfg)
+      init(self, *args, **kw)
+
+    cls.__init__ = wrapped
+
+  def get_config(self) -> dict[str, Any]:
+    return {k: _config_value(v) for k, v in self.__dict__["_init_config"].items()}
+
+  @classmethod
+  def from_config(cls, config: dict[str, Any]):
+    return cls(**{k: _config_restore(v) for k, v in config.items()})
+
+
+def build_from_config(cls: str, config: dict[str, Any], device=None, group=None):
+  """Rebuilds a `Configurable` layer from `"package.module:Class"` and its `get_config()` dictionary on
+  `device`: the recipe `serving.export` writes for a layer that is exported without a builder of its own."""
+  import importlib
+  mod_name, cls_name = cls.split(":")
+  layer = getattr(importlib.import_module(mod_name), cls_name).from_config(config)
+  return layer.to(device) if device is not None else layer

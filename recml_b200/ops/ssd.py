@@ -65,6 +65,18 @@ def ssd_chunked(x, a, b, c, block_len: int, initial_states=None):
   return (y_diag + y_off).reshape(B, L, H, P).to(x.dtype)
 
 
+ssd_minimal_discrete = ssd_chunked        # the reference's name (`recml/layers/keras/mamba.py:53-146`)
+
+
+def segsum(x):
+  """`out[..., i, j] = x[..., j + 1] + ... + x[..., i]` for j <= i and -inf above the diagonal: the log of the
+  decay between two positions (`recml/layers/keras/mamba.py:30-50`), here as a difference of prefix sums."""
+  T = x.shape[-1]
+  cum = torch.cumsum(x, dim=-1)
+  tri = torch.tril(torch.ones(T, T, dtype=torch.bool, device=x.device))
+  return (cum[..., :, None] - cum[..., None, :]).masked_fill(~tri, float("-inf"))
+
+
 def causal_depthwise_conv1d_silu(x, weight, bias=None):
   """x `[B, L, C]`, weight `[C, K]` (tap k multiplies x[t − (K−1) + k]); SiLU fused."""
   K = weight.shape[1]

@@ -71,9 +71,17 @@ def _weights_tree(model: nn.Module, with_slots: bool = False) -> dict[str, Any]:
   return tree
 
 
-def export(model: nn.Module, export_dir: str, *, builder: str, kwargs: Mapping[str, Any], step: int = 0) -> str:
+def export(model: nn.Module, export_dir: str, *, builder: str | None = None, kwargs: Mapping[str, Any] | None = None,
+           step: int = 0) -> str:
   """Collective over the job's ranks (every rank writes its table shards; rank 0 writes the rest).
-  `builder` is "package.module:Class"; `builder(**kwargs, device=..., group=...)` must rebuild the module."""
+  `builder` is "package.module:Class"; `builder(**kwargs, device=..., group=...)` must rebuild the module.
+  A layer that carries `get_config()` (`layers.utils.Configurable`) needs neither: its class and config are the
+  recipe, the counterpart of a saved `model.keras` (`recml/core/training/keras_trainer.py:99`)."""
+  if builder is None:
+    if not hasattr(model, "get_config"):
+      raise ValueError("export needs a builder for a module without get_config()")
+    builder = "recml_b200.layers.utils:build_from_config"
+    kwargs = {"cls": f"{type(model).__module__}:{type(model).__qualname__}", "config": model.get_config()}
   if _rank() == 0:
     os.makedirs(export_dir, exist_ok=True)
   mgr = ckpt.CheckpointManager(os.path.join(export_dir, "weights"), async_save=False, max_to_keep=None)
@@ -81,7 +89,7 @@ def export(model: nn.Module, export_dir: str, *, builder: str, kwargs: Mapping[s
   mgr.close()
   if _rank() == 0:
     with open(os.path.join(export_dir, MODEL_FILE), "w") as f:
-      json.dump({"builder": builder, "kwargs": _jsonable(dict(kwargs)), "step": int(step)}, f, indent=1)
+      json.dump({"builder": builder, "kwargs": _jsonable(dict(kwargs or {})), "step": int(step)}, f, indent=1)
     from recml_b200.embedding import spec_sidecar
     docs = {name or "root": spec_sidecar.describe(mod) for name, mod in model.named_modules()
             if hasattr(mod, "sharded_state_dict") and hasattr(mod, "plan")}

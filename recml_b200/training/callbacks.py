@@ -35,6 +35,9 @@ class Callback:
 
   def on_train_end(self, logs: Mapping[str, Any] | None = None) -> None: ...
 
+  def on_test_end(self, logs: Mapping[str, Any] | None = None) -> None:
+    """After an evaluation pass that is not part of an epoch (`ModuleTrainer.evaluate`)."""
+
 
 def restore_state(state: state_lib.State, checkpoint_dir: str, step: int | None = None, *,
                   restore_optimizer_vars: bool = True, restore_steps: bool = True,
@@ -67,6 +70,22 @@ def restore_state(state: state_lib.State, checkpoint_dir: str, step: int | None 
   return step
 
 
+class EpochCheckpointManager(ckpt_lib.CheckpointManager):
+  """A checkpoint manager keyed by epoch that saves and restores a training `State` (parameters, buffers,
+  optimizer slots; metric accumulators are per epoch and are not saved) — the part of
+  `recml/core/utils/keras_utils.py:36-137` that the epoch callback needs."""
+
+  def __init__(self, checkpoint_dir: str, max_to_keep: int = 5, save_interval_epochs: int = 1, **kwargs):
+    kwargs.setdefault("item_name", core.ORBAX_CHECKPOINT_DEFAULT_KEY)
+    super().__init__(checkpoint_dir, max_to_keep=max_to_keep, save_interval_steps=save_interval_epochs, **kwargs)
+
+  def save_model_variables(self, state: state_lib.State, epoch: int, logs: Mapping[str, Any] | None = None) -> bool:
+    return self.save(epoch, state.state_dict(), metrics=dict(logs or {}))
+
+  def restore_model_variables(self, state: state_lib.State, epoch: int) -> state_lib.State:
+    return state.load_state_dict(self.restore(epoch, target=state.state_dict()))
+
+
 class EpochCheckpointAndRestoreCallback(Callback):
   """Restores the newest epoch checkpoint when training begins, saves one per epoch and writes the
   completion marker when training ends."""
@@ -95,37 +114,64 @@ class EpochCheckpointAndRestoreCallback(Callback):
 
 
 class EpochSummaryCallback(Callback):
-  """Epoch-level scalars: the epoch's metrics under `train`, the `val_*` ones under `val`,
-  parameter counts, learning rate(s) and steps per second."""
+  """Epoch-level scalars at step `epoch * steps_per_epoch`: the epoch's metrics under `train`, the `val_*`
+  ones under `val`, the parameter counts (trainable, non-trainable, optimizer slots, total) in both, and
+  learning rate(s) and steps per second with the training ones (`recml/core/utils/keras_utils.py:299-384`)."""
 
-  def __init__(self, log_dir: str, steps_per_epoch: int):
+  def __init__(self, log_dir: str, steps_per_epoch: int, write_steps_per_second: bool = True):
     self._train = metrics_tools.AsyncMultiWriter(log_dir=log_dir, name=core.TRAIN_LOG_DIRNAME)
     self._val = metrics_tools.AsyncMultiWriter(log_dir=log_dir, name=core.EVAL_LOG_DIRNAME)
     self._steps = steps_per_epoch
+    self._write_rate = write_steps_per_second
     self._t0 = time.time()
+    self._num_params: dict[str, float] | None = None
 
   def on_epoch_begin(self, epoch, logs=None):
     self._t0 = time.time()
 
+  def _count_params(self) -> dict[str, float]:
+    st = self.state
+    if st is None:
+      return {}
+    if self._num_params is None:
+      n = {"num_params/trainable": float(st.num_trainable()),
+           "num_params/non_trainable": float(st.num_non_trainable()),
+           "num_params/optimizer": float(st.optimizer.num_params()) if st.optimizer is not None else 0.0}
+      n["num_params/total"] = sum(n.values())
+      self._num_params = n
+    return self._num_params
+
   def on_epoch_end(self, epoch, logs=None):
-    logs = dict(logs or {})
+    if not logs:
+      return
+    step = epoch * self._steps
     train = {k: v for k, v in logs.items() if not k.startswith("val_")}
     val = {k[4:]: v for k, v in logs.items() if k.startswith("val_")}
     st = self.state
-    train.setdefault("steps_per_second", self._steps / max(time.time() - self._t0, 1e-9))
-    if st is not None:
-      train["num_params/trainable"] = float(st.num_trainable())
-      train["num_params/non_trainable"] = float(st.num_non_trainable())
-      if st.optimizer is not None:
-        for name, value in st.optimizer.hyperparams.items():
-          if "learning_rate" in name:
-            train[name] = float(value)
-    self._train.write_scalars(epoch, train)
-    self._train.flush()
+    if st is not None and st.optimizer is not None:
+      for name, value in st.optimizer.hyperparams.items():
+        if "learning_rate" in name:
+          train[name] = float(value)
+    if self._write_rate:
+      train.setdefault("steps_per_second", self._steps / max(time.time() - self._t0, 1e-9))
+    if train:
+      train.update(self._count_params())
+      self._train.write_scalars(step, train)
+      self._train.flush()
     if val:
-      self._val.write_scalars(epoch, val)
+      val.update(self._count_params())
+      self._val.write_scalars(step, val)
       self._val.flush()
+
+  def on_test_end(self, logs=None):
+    self._val.flush()
 
   def on_train_end(self, logs=None):
     self._train.flush()
     self._val.flush()
+
+
+# The reference's names for the same parts (`recml/core/utils/keras_utils.py`).
+KerasOrbaxCheckpointManager = EpochCheckpointManager
+EpochOrbaxCheckpointAndRestoreCallback = EpochCheckpointAndRestoreCallback
+restore_keras_model = restore_state

@@ -200,7 +200,10 @@ class ModuleTrainer(core.Trainer[ModuleTask]):
     if self._enable_checkpointing and ckpt_lib.latest_step(self._ckpt_dir) is not None:
       st = self._state(cm)
       st.load_state_dict(self._manager().restore(None, target=st.state_dict()))
-    return self._evaluate(cm, task.create_dataset(training=False))
+    logs = self._evaluate(cm, task.create_dataset(training=False))
+    for cb in self._callbacks:
+      cb.on_test_end(logs)
+    return logs
 
   def evaluate_continuously(self, task: ModuleTask) -> core.Logs:
     cm = task.create_model_for_eval()

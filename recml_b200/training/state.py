@@ -92,6 +92,11 @@ class State:
   def __call__(self, *args, **kwargs):
     return self.model(*args, **kwargs)
 
+  @property
+  def opt_state(self) -> dict[str, Any]:
+    """The optimizer's slots by name (`recml/core/training/jax_trainer.py:60-62`); empty without an optimizer."""
+    return {} if self.optimizer is None else self.optimizer.state_dict()
+
   # -- introspection (logged by the trainer) ----------------------------------------
   def num_trainable(self) -> int:
     return sum(p.numel() for p in self.params.values() if p.requires_grad)

@@ -111,7 +111,7 @@ class Trainer(core.Trainer[task_lib.Task]):
     self._rng_impl = rng_impl
     self._enable_checkpointing = enable_checkpointing
     self._check_for_checkpoints = check_for_checkpoints
-    self._progress = profiling.ReportProgress()
+    self._progress = None
     self._failure_detection = failure_detection
     self._heartbeat_timeout_s = heartbeat_timeout_s
     self._health = None
@@ -133,6 +133,14 @@ class Trainer(core.Trainer[task_lib.Task]):
     return metrics_tools.AsyncMultiWriter(
         log_dir=os.path.join(self._model_dir, core.LOG_DIR), name=core.TRAIN_LOG_DIRNAME)
 
+  @property
+  def report_progress(self) -> profiling.ReportProgress:
+    """The periodic progress action (`recml/core/training/jax_trainer.py:496-501`): steps per second and uptime
+    to the log and to the training summaries, with the share of wall time spent in checkpointing and eval."""
+    if self._progress is None:
+      self._progress = profiling.ReportProgress(writer=self.train_summary_writer, every_steps=self._steps_per_loop)
+    return self._progress
+
   def _eval_writers(self, eval_iters) -> dict[str, metrics_tools.AsyncMultiWriter]:
     return {k: metrics_tools.AsyncMultiWriter(
         log_dir=os.path.join(self._model_dir, core.LOG_DIR), name=_val_logdir(k))
@@ -146,7 +154,7 @@ class Trainer(core.Trainer[task_lib.Task]):
     if torch.cuda.is_available():
       from recml_b200.ops import _lib
       _lib.check_status()      # raises before anything is written if a kernel reported an error
-    with self._progress.timed("checkpointing"):
+    with self.report_progress.timed("checkpointing"):
       mgr.save(step, state.state_dict(), metrics=metrics)
 
   def _maybe_restore_checkpoint(self, state: state_lib.State, step: int | None = None
@@ -214,7 +222,7 @@ class Trainer(core.Trainer[task_lib.Task]):
         examples += _batch_size_of(host_batch)
         timed_steps += 1
       accum.accumulate({**metrics, **state_metrics(state)}, step)
-      self._progress(step)
+      self.report_progress(step)
       if step != start_step + num_steps - 1:
         self._maybe_save_checkpoint(step, state)
     device_ms = timer.stop()
@@ -301,7 +309,7 @@ class Trainer(core.Trainer[task_lib.Task]):
     msg = (f"running {self._steps_per_eval} steps of evaluation..."
            if self._steps_per_eval is not None else "running complete evaluation...")
     log.info("eval | step: %6d | %s", step, msg)
-    with self._progress.timed("eval"):
+    with self.report_progress.timed("eval"):
       for key, it in eval_iters.items():
         it.reset()
         m = self._evaluate_n_steps(eval_iter=it, eval_step=eval_step, state=state,

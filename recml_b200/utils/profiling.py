@@ -95,11 +95,16 @@ class PhaseTimers:
 
 
 class ReportProgress:
-  """steps/sec every call window + wall-clock share of timed side activities."""
+  """steps/sec every call window + wall-clock share of timed side activities.  With a summary `writer` the
+  window also closes every `every_steps` steps and `steps_per_sec` / `uptime` go out as scalars, like the
+  periodic action the reference's trainer runs after each step (`recml/core/training/jax_trainer.py:496-501,583`).
+  """
 
-  def __init__(self, every_secs: float = 60.0):
+  def __init__(self, every_secs: float = 60.0, *, writer=None, every_steps: int | None = None):
     self._every = every_secs
-    self._last_t = time.time()
+    self._every_steps = every_steps
+    self._writer = writer
+    self._t0 = self._last_t = time.time()
     self._last_step = None
     self._timed: dict[str, float] = collections.defaultdict(float)
     self.steps_per_sec: float | None = None
@@ -109,11 +114,16 @@ class ReportProgress:
     if self._last_step is None:
       self._last_step, self._last_t = step, now
       return
-    if now - self._last_t >= self._every:
-      dt = now - self._last_t
+    due = now - self._last_t >= self._every
+    if self._every_steps is not None and step - self._last_step >= self._every_steps:
+      due = True
+    if due and step > self._last_step:
+      dt = max(now - self._last_t, 1e-9)
       self.steps_per_sec = (step - self._last_step) / dt
       shares = ", ".join(f"{k}: {100 * v / dt:.1f}%" for k, v in self._timed.items())
       log.info("step %d | %.2f steps/s | %s", step, self.steps_per_sec, shares)
+      if self._writer is not None:
+        self._writer.write_scalars(step, {"steps_per_sec": self.steps_per_sec, "uptime": now - self._t0})
       self._timed.clear()
       self._last_step, self._last_t = step, now
 

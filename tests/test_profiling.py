@@ -47,3 +47,17 @@ def test_trace_writes_a_chrome_trace(tmp_path):
 def test_preprocessing_mode_values():
   assert str(PreprocessingMode.TRAINING) == "training" and PreprocessingMode("eval") is PreprocessingMode.EVAL
   assert {m.value for m in PreprocessingMode} == {"training", "eval", "serving"}
+
+
+def test_report_progress_writes_scalars_every_n_steps():
+  class W:
+    def __init__(self):
+      self.rows = []
+    def write_scalars(self, step, scalars):
+      self.rows.append((step, dict(scalars)))
+  w = W()
+  rp = profiling.ReportProgress(every_secs=1e9, writer=w, every_steps=5)
+  for step in range(12):
+    rp(step)
+  assert [s for s, _ in w.rows] == [5, 10]
+  assert set(w.rows[0][1]) == {"steps_per_sec", "uptime"} and w.rows[0][1]["steps_per_sec"] > 0

@@ -147,3 +147,63 @@ def test_tiny_hstu_retrieval_experiment(tmp_path):
   cfg.trainer.partitioner = C.Config(__import__("recml_b200").DataParallelPartitioner, device="cpu")
   logs = run_experiment(C.build(cfg), "train_and_eval")
   assert logs["train"]["loss"] < 3.0 and "hit@1_sampled" in logs["val"]
+
+
+def test_layers_round_trip_through_their_config(tmp_path):
+  """`get_config()` holds the constructor call (JSON-serialisable, functions as import paths) and
+  `from_config` rebuilds a layer with the same parameter shapes — the reference's Keras layers carry the same
+  pair (`recml/layers/keras/hstu.py:603-628`, `sasrec.py:152-170`, `bert4rec.py:186-208`, `mamba.py:727-752`).
+  A layer exported without a builder reloads from that config with its weights."""
+  import json
+  from recml_b200 import serving
+  from recml_b200.layers import bert4rec, hstu, mamba, sasrec
+  layers = [
+      hstu.HSTU(vocab_size=50, max_positions=16, model_dim=32, num_heads=2, num_layers=2, dropout=0.1),
+      hstu.HSTUBlock(32, 2, use_bias=True, scaled_pointwise_attn=True),
+      hstu.RelativeBucketedTimeAndPositionBasedBias(num_buckets=16, position_bias_layer=hstu.RelativePositionalBias(16)),
+      sasrec.SASRec(vocab_size=50, max_positions=16, model_dim=32, mlp_dim=64, num_heads=2, num_layers=1),
+      bert4rec.BERT4Rec(vocab_size=50, max_positions=16, num_types=3, model_dim=32, mlp_dim=64, num_heads=2, num_layers=1),
+      mamba.Mamba4Rec(50, 32, 2, 4, 1, 2, d_state=16, chunk_size=8),
+  ]
+  for layer in layers:
+    cfg = json.loads(json.dumps(layer.get_config()))
+    twin = type(layer).from_config(cfg)
+    assert {n: p.shape for n, p in twin.named_parameters()} == {n: p.shape for n, p in layer.named_parameters()}
+    assert twin.get_config() == layer.get_config()
+  block_cfg = layers[1].get_config()
+  assert block_cfg["activation"] == {"callable": "torch.nn.functional.silu"} and block_cfg["use_bias"] is True
+  assert layers[0].get_config()["num_layers"] == 2 and layers[0].get_config()["max_seq_len"] is None
+
+  model = layers[3].eval()
+  serving.export(model, str(tmp_path / "sasrec"))
+  loaded = serving.load(str(tmp_path / "sasrec"), device="cpu")
+  ids = torch.randint(1, 50, (3, 16))
+  with torch.no_grad():
+    torch.testing.assert_close(loaded(ids), model(ids))
+
+
+def test_compute_output_shape_matches_the_forward():
+  from recml_b200.layers import bert4rec, hstu, mamba, sasrec
+  ids = torch.randint(1, 50, (3, 16))
+  for add_head in (True, False):
+    models = [hstu.HSTU(vocab_size=50, max_positions=16, model_dim=32, num_heads=2, num_layers=1, add_head=add_head),
+              sasrec.SASRec(vocab_size=50, max_positions=16, model_dim=32, mlp_dim=64, num_heads=2, num_layers=1,
+                            add_head=add_head),
+              mamba.Mamba4Rec(50, 32, 2, 4, 1, 2, d_state=16, chunk_size=8, add_head=add_head)]
+    mask = torch.ones(3, 16, dtype=torch.bool)
+    for m in models:
+      assert tuple(m.eval()(ids, padding_mask=mask).shape) == tuple(m.compute_output_shape(ids.shape)), type(m).__name__
+  b = bert4rec.BERT4Rec(vocab_size=50, max_positions=16, model_dim=32, mlp_dim=64, num_heads=2, num_layers=1).eval()
+  pos = torch.randint(0, 16, (3, 5))
+  assert tuple(b(ids, padding_mask=torch.ones(3, 16, dtype=torch.bool), mask_positions=pos).shape) == tuple(b.compute_output_shape(ids.shape, pos.shape))
+
+
+def test_segsum_is_the_log_decay_between_positions():
+  from recml_b200.ops import ssd
+  x = torch.randn(2, 3, 7, dtype=torch.float64)
+  out = ssd.segsum(x)
+  for i in range(7):
+    for j in range(7):
+      want = x[..., j + 1:i + 1].sum(-1) if j <= i else torch.full((2, 3), float("-inf"), dtype=torch.float64)
+      torch.testing.assert_close(out[..., i, j], want)
+  assert ssd.ssd_minimal_discrete is ssd.ssd_chunked

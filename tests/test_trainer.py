@@ -179,6 +179,14 @@ def test_callbacks_and_selective_restore(tmp_path):
   assert open(os.path.join(side, "marker.txt")).read() == "COMPLETED"
   assert ckpt.all_steps(os.path.join(side, "checkpoints")) == [0, 1]
   assert os.path.isdir(os.path.join(side, "logs", "train"))
+  # the epoch summaries sit at step epoch * steps_per_epoch and carry all four parameter counts
+  from tensorboard.backend.event_processing import event_accumulator
+  acc = event_accumulator.EventAccumulator(os.path.join(side, "logs", "train")).Reload()
+  tags = set(acc.Tags()["scalars"])
+  assert {"loss", "learning_rate", "steps_per_second", "num_params/trainable", "num_params/non_trainable",
+          "num_params/optimizer", "num_params/total"} <= tags
+  assert [e.step for e in acc.Scalars("loss")] == [0, 10]
+  assert acc.Scalars("num_params/total")[0].value == 4 + 2 * 4    # a 4 -> 1 layer without bias and two Adam slots
 
   # selective restore into a fresh state
   def fresh():
@@ -199,3 +207,25 @@ def test_callbacks_and_selective_restore(tmp_path):
     callbacks.restore_state(fresh(), ckdir, step=7)
   with pytest.raises(FileNotFoundError):
     callbacks.restore_state(fresh(), os.path.join(tmp_path, "nothing"))
+
+
+def test_epoch_checkpoint_manager_round_trip(tmp_path):
+  """`save_model_variables` / `restore_model_variables` on a `State`, every second epoch
+  (`recml/core/utils/keras_utils.py:36-137`); the reference's names resolve to the same classes."""
+  from recml_b200.training import callbacks
+  assert callbacks.KerasOrbaxCheckpointManager is callbacks.EpochCheckpointManager
+  assert callbacks.restore_keras_model is callbacks.restore_state
+  mk = lambda seed: (torch.manual_seed(seed),
+                     recml.State.create(model=nn.Linear(4, 2), tx=recml.AdamFactory(learning_rate=0.1).make()))[1]
+  st = mk(0)
+  mgr = callbacks.EpochCheckpointManager(str(tmp_path / "ck"), max_to_keep=2, save_interval_epochs=2)
+  for epoch in range(5):
+    st.model(torch.randn(3, 4)).sum().backward()
+    st.update()
+    mgr.save_model_variables(st, epoch, {"loss": 1.0})
+  mgr.wait_until_finished()
+  assert ckpt.all_steps(str(tmp_path / "ck")) == [2, 4]
+  other = mk(1)
+  mgr.restore_model_variables(other, 4)
+  assert other.step == 5 and torch.equal(other.params["weight"], st.params["weight"])
+  assert torch.equal(other.opt_state["mu"]["weight"], st.opt_state["mu"]["weight"])
