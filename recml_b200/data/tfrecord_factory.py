@@ -1,11 +1,15 @@
 """Dataset factory over TFRecord files (`recml/core/data/tf_dataset_factory.py:214-583`): file
-globbing, per-process file sharding, file / record shuffling, batching, `tf.Example` parsing by a
-feature spec, preprocessors / postprocessors, label popping, a `debug` single cached batch, repeat
-and a background prefetch thread that stages batches in pinned memory.  Field names follow the
-reference where they are meaningful without tf.data."""
+globbing, per-process file sharding (or none), directory groups read newest first, file / record
+shuffling, interleaved reading, batching, `tf.Example` / `tf.SequenceExample` parsing by a feature spec, a
+vectorised filter with re-batching, preprocessor(s) / postprocessors, label popping, a `debug` single cached
+batch, repeat (of the records or of the file list) and a background prefetch thread that stages batches in
+pinned memory.  Field names follow the reference where they are meaningful without tf.data; its TFDS,
+tf.Transform and tf.data-service hooks name external services and have no counterpart."""
 from __future__ import annotations
 
 import dataclasses
+import enum
+import functools
 import glob as glob_lib
 import queue
 import threading
@@ -50,16 +54,34 @@ class VarLenFeature:
   dtype: str = "int64"
 
 
-def get_file_groups(input_path: str | Sequence[str], sharding: DatasetShardingInfo) -> list[str]:
-  """Expands glob(s) and keeps every `num_processes`-th file starting at `process_index`; with fewer
-  files than processes every process reads all files (records are then sharded instead)."""
+class FileFormat(enum.Enum):
+  """Container formats the reference can read (`tf_dataset_factory.py:58-64`).  TFRecord is the one with a
+  reader here; the others are Google-internal or need the array_record library."""
+  TFRECORD = "tfrecord"
+  RECORDIO = "recordio"
+  SSTABLE = "sstable"
+  ARRAY_RECORD = "array_record"
+
+
+def expand_input_paths(input_path: str | Sequence[str]) -> list[str]:
+  """All files matching the glob(s), sorted."""
   pats = [input_path] if isinstance(input_path, str) else list(input_path)
   files = sorted(f for p in pats for f in glob_lib.glob(p))
   if not files:
-    raise FileNotFoundError(f"No files match {pats}")
-  if len(files) >= sharding.num_processes:
-    return files[sharding.process_index::sharding.num_processes]
+    raise FileNotFoundError(f"No input files found for patterns: {pats}.")
   return files
+
+
+def get_file_groups(files: Sequence[str]) -> list[str]:
+  """Groups files by their directory; every group is its paths joined by commas and the groups come in
+  DESCENDING directory order, so that with `Span-<n>/...` layouts the newest span is read first
+  (`tf_dataset_factory.py:809-868`)."""
+  if not files:
+    raise ValueError("`files` is empty.")
+  groups: dict[str, list[str]] = {}
+  for f in files:
+    groups.setdefault(f[:f.rfind("/")], []).append(f)
+  return [",".join(groups[d]) for d in sorted(groups, reverse=True)]
 
 
 def _take(features: dict, idx: np.ndarray) -> dict:
@@ -98,13 +120,37 @@ def _rows_of(features: dict) -> int:
 class _RecordDataset:
   def __init__(self, fac: "TFDatasetFactory"):
     self.fac = fac
+    if fac.file_format not in (FileFormat.TFRECORD, "tfrecord"):
+      raise ValueError(f"File format: {fac.file_format} is not supported. Expected one of: {[FileFormat.TFRECORD]}.")
     self.sharding = fac.sharding_info or DatasetShardingInfo.current()
-    self.files = get_file_groups(fac.input_path, self.sharding)
-    all_files = sorted(f for p in ([fac.input_path] if isinstance(fac.input_path, str) else fac.input_path)
-                       for f in glob_lib.glob(p))
-    self.shard_records = len(all_files) < self.sharding.num_processes
+    # A reading unit is one file, or with `group_uris_by_dir` all files of one directory read one after the
+    # other.  Units (not records) are what gets shuffled, sharded over processes and interleaved; with fewer
+    # units than processes every process opens all of them and takes every n-th record instead.
+    files = fac.input_filepaths
+    groups = [g.split(",") for g in get_file_groups(files)] if fac.group_uris_by_dir else [[f] for f in files]
+    self.files = [f for g in groups for f in g]
+    at = 0
+    self.units: list[list[int]] = []
+    for g in groups:
+      self.units.append(list(range(at, at + len(g))))
+      at += len(g)
+    shard = fac.sharding and self.sharding.num_processes > 1
+    self.shard_records = shard and len(self.units) < self.sharding.num_processes
+    self.shard_units = shard and not self.shard_records
     self.batch = self.sharding.per_process_batch_size(fac.global_batch_size)
     self._cached = None
+
+  def _units_of_epoch(self, epoch: int) -> list[int]:
+    ids = list(range(len(self.units)))
+    if not self.shard_units:
+      return ids
+    n, p = self.sharding.num_processes, self.sharding.process_index
+    if self.fac.repeat and self.fac.repeat_files:
+      # the unit list is repeated BEFORE it is dealt out, so a process sees other units in the next pass
+      # unless the number of units is a multiple of the number of processes
+      base = epoch * len(ids)
+      return [i for i in ids if (base + i) % n == p]
+    return ids[p::n]
 
   def _parse_features(self, rf: tfrecord.RecordFile, rows: np.ndarray) -> dict:
     out = {}
@@ -132,6 +178,8 @@ class _RecordDataset:
     return out
 
   def _finish(self, out: dict):
+    if self.fac.preprocessor is not None:
+      out = self.fac.preprocessor(out)
     for fn in self.fac.preprocessors:
       out = fn(out)
     if self.fac.label_name is not None:
@@ -141,55 +189,59 @@ class _RecordDataset:
       out = fn(out)
     return out
 
-  def _record_stream(self, rng):
+  def _record_stream(self, rng, epoch: int = 0):
     """(file indices, record indices) array pairs in reading order: `cycle_length` files are open at a time
     and `block_length` records are taken from each in turn (tf.data `interleave`); then an optional shuffle
     window.  The order is produced in blocks with numpy, not record by record."""
     fac = self.fac
-    files = list(range(len(self.files)))
+    units = self._units_of_epoch(epoch)
     if fac.file_shuffle:
-      rng.shuffle(files)
+      rng.shuffle(units)
 
-    def rows_of(fi):
-      n = len(self._open(fi))
-      rows = np.arange(n, dtype=np.int64)
-      if self.shard_records:
-        rows = rows[self.sharding.process_index::self.sharding.num_processes]
-      if fac.shuffle and not fac.shuffle_buffer_size:
-        rng.shuffle(rows)
-      return rows
+    def rows_of(ui):
+      """(file index, record index) of every record of a unit, in reading order."""
+      fs, rs = [], []
+      for fi in self.units[ui]:
+        n = len(self._open(fi))
+        rows = np.arange(n, dtype=np.int64)
+        if self.shard_records:
+          rows = rows[self.sharding.process_index::self.sharding.num_processes]
+        if fac.shuffle and not fac.shuffle_buffer_size:
+          rng.shuffle(rows)
+        fs.append(np.full(len(rows), fi, dtype=np.int64))
+        rs.append(rows)
+      return (np.concatenate(fs), np.concatenate(rs)) if len(fs) > 1 else (fs[0], rs[0])
 
     def interleaved():
       cycle = max(1, fac.cycle_length or 1)
       blk = max(1, fac.block_length)
-      pending = list(files)
-      active: list[tuple[int, np.ndarray, int]] = []
+      pending = list(units)
+      active: list[tuple[np.ndarray, np.ndarray, int]] = []       # (file indices, record indices, position)
       while pending or active:
         while pending and len(active) < cycle:
-          fi = pending.pop(0)
-          active.append((fi, rows_of(fi), 0))
+          active.append((*rows_of(pending.pop(0)), 0))
         active = [a for a in active if a[2] < len(a[1])]
         if not active:
           continue
         if len(active) == 1 and (cycle == 1 or not pending):
-          fi, rows, at = active[0]                  # one open file: its blocks follow one another anyway
-          yield np.full(len(rows) - at, fi, dtype=np.int64), rows[at:]
+          fs, rows, at = active[0]                  # one open unit: its blocks follow one another anyway
+          yield fs[at:], rows[at:]
           active = []
           continue
-        # whole rounds (one block from every open file) until the first file runs short of a full block
+        # whole rounds (one block from every open unit) until the first unit runs short of a full block
         k = min((len(rows) - at) // blk for _, rows, at in active)
         if k >= 1:
           parts_r = np.stack([rows[at:at + k * blk].reshape(k, blk) for _, rows, at in active], axis=1)
-          parts_f = np.broadcast_to(np.array([fi for fi, _, _ in active], dtype=np.int64)[None, :, None], parts_r.shape)
+          parts_f = np.stack([fs[at:at + k * blk].reshape(k, blk) for fs, _, at in active], axis=1)
           yield parts_f.reshape(-1), parts_r.reshape(-1)
-          active = [(fi, rows, at + k * blk) for fi, rows, at in active]
+          active = [(fs, rows, at + k * blk) for fs, rows, at in active]
           continue
         nxt = []                                   # a round with a short last block
-        for fi, rows, at in active:
+        for fs, rows, at in active:
           hi = min(at + blk, len(rows))
-          yield np.full(hi - at, fi, dtype=np.int64), rows[at:hi]
+          yield fs[at:hi], rows[at:hi]
           if hi < len(rows):
-            nxt.append((fi, rows, hi))
+            nxt.append((fs, rows, hi))
         active = nxt
 
     if not (fac.shuffle and fac.shuffle_buffer_size):
@@ -212,8 +264,8 @@ class _RecordDataset:
 
   def _open(self, fi: int) -> tfrecord.RecordFile:
     if fi not in self._open_cache:
-      if len(self._open_cache) > 2 * max(1, self.fac.cycle_length or 1) + 2:
-        self._open_cache.clear()
+      if not self.fac.cache_reading and len(self._open_cache) > 2 * max(1, self.fac.cycle_length or 1) + 2:
+        self._open_cache.clear()          # `cache_reading` keeps every file (mapping and record index) open
       self._open_cache[fi] = tfrecord.RecordFile(self.files[fi], verify=self.fac.verify_checksums)
     return self._open_cache[fi]
 
@@ -262,7 +314,7 @@ class _RecordDataset:
       epoch = 0
       while True:
         seen = 0
-        for bf, br in self._record_stream(rng):
+        for bf, br in self._record_stream(rng, epoch):
           seen += len(br)
           yield bf, br
         epoch += 1
@@ -348,6 +400,19 @@ class TFDatasetFactory(types.Factory[iterator_lib.Iterator]):
   shuffle_buffer_size: int = 0                     # > 0: shuffle records in a window instead of per file
   cycle_length: int | None = None                  # files read concurrently (interleave)
   block_length: int = 1                            # consecutive records taken from a file per turn
+  file_format: FileFormat = FileFormat.TFRECORD
+  sharding: bool = True                            # False: every process reads the whole input
+  group_uris_by_dir: bool = False                  # read, shard and interleave whole directories, newest first
+  repeat_files: bool = False                       # with `repeat`: repeat the file list before it is sharded
+  cache_reading: bool = False                      # keep every input file mapped and indexed between passes
+  preprocessor: Callable[[Any], Any] | None = None  # applied before `preprocessors`
+
+  @functools.cached_property
+  def input_filepaths(self) -> Sequence[str]:
+    """The input files (`tf_dataset_factory.py:340-367`)."""
+    if not self.input_path:
+      raise ValueError("`input_path` must be set.")
+    return expand_input_paths(self.input_path)
 
   def make(self) -> iterator_lib.Iterator:
     return iterator_lib.IterableIterator(_RecordDataset(self))

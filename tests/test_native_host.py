@@ -335,3 +335,42 @@ def test_criteo_example_factory_packs_with_the_host_id_pipeline(tmp_path):
   assert os.path.exists(path)
   stats = id_pipeline.StatsRecorder(str(tmp_path / "fdo")).load()
   assert set(stats) == {"cat_0", "cat_1", "cat_2"} and stats["cat_1"].max_ids_per_partition >= 1
+
+
+def test_factory_directory_groups_unsharded_reading_and_repeated_file_lists(tmp_path):
+  """`group_uris_by_dir` reads, shards and interleaves whole directories with the lexically largest first
+  (`recml/core/data/tf_dataset_factory.py:151-162,809-868`); `sharding=False` gives every process the whole
+  input; `repeat_files` repeats the file list before it is dealt out to the processes (`:470-478`)."""
+  def write_ids(path, ids):
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    tfrecord.write_tfrecord(path, [tfrecord.encode_example({"id": [i]}) for i in ids])
+  write_ids(str(tmp_path / "Span-0" / "Shard-0"), [0, 1])
+  write_ids(str(tmp_path / "Span-0" / "Shard-1"), [2, 3])
+  write_ids(str(tmp_path / "Span-1" / "Shard-0"), [10, 11, 12])
+  files = sorted(str(p) for p in tmp_path.glob("Span-*/Shard-*"))
+  groups = tff.get_file_groups(files)
+  assert groups == [files[2], files[0] + "," + files[1]]
+  with pytest.raises(ValueError):
+    tff.get_file_groups([])
+  spec = {"id": tff.FixedLenFeature((1,), "int64")}
+  mk = lambda **kw: tff.TFDatasetFactory(**{**dict(input_path=str(tmp_path / "Span-*" / "Shard-*"), feature_spec=spec,
+                                                   global_batch_size=1, prefetch_buffer_size=0), **kw})
+  ids = lambda fac: [int(x) for b in fac.make() for x in np.asarray(b["id"]).reshape(-1)]
+  assert mk().input_filepaths == files
+  assert ids(mk()) == [0, 1, 2, 3, 10, 11, 12]
+  assert ids(mk(group_uris_by_dir=True)) == [10, 11, 12, 0, 1, 2, 3]              # newest directory first
+  # directories are the unit of sharding: process 1 of 2 reads all of Span-0 and nothing of Span-1
+  two = lambda i, **kw: mk(global_batch_size=2, drop_remainder=False, sharding_info=tff.DatasetShardingInfo(2, i), **kw)
+  assert ids(two(1, group_uris_by_dir=True)) == [0, 1, 2, 3]
+  assert ids(two(0, group_uris_by_dir=True)) == [10, 11, 12]
+  # and of interleaving: one record from each directory in turn
+  assert ids(mk(group_uris_by_dir=True, cycle_length=2)) == [10, 0, 11, 1, 12, 2, 3]
+  assert ids(two(1, sharding=False)) == [0, 1, 2, 3, 10, 11, 12]
+  # three files over two processes: process 0 gets files 0 and 2; with the list repeated before sharding its
+  # second pass starts at offset 3, so it gets file 1 there
+  assert ids(two(0, repeat=True, num_epochs=2)) == [0, 1, 10, 11, 12] * 2
+  assert ids(two(0, repeat=True, repeat_files=True, num_epochs=2)) == [0, 1, 10, 11, 12, 2, 3]
+  assert ids(mk(preprocessor=lambda b: {"id": b["id"] + 100}, preprocessors=[lambda b: {"id": b["id"] * 2}]))[0] == 200
+  assert ids(mk(cache_reading=True, repeat=True, num_epochs=2)) == [0, 1, 2, 3, 10, 11, 12] * 2
+  with pytest.raises(ValueError, match="not supported"):
+    mk(file_format=tff.FileFormat.SSTABLE).make().__next__()
