@@ -29,6 +29,62 @@ from recml_b200.utils import types
 
 
 @dataclasses.dataclass
+class Feature:
+  name: str
+
+
+@dataclasses.dataclass
+class DenseFeature(Feature):
+  """One scalar input of the bottom MLP."""
+
+
+@dataclasses.dataclass
+class SparseFeature(Feature):
+  """One categorical input with a table of its own (`recml/examples/dlrm_experiment.py:57-66`); `bag_size` ids
+  per sample are pooled with `combiner`."""
+  vocab_size: int = 0
+  embedding_dim: int = 128
+  max_sequence_length: int | None = None
+  combiner: str = "mean"
+  sparsity: float = 0.8
+  bag_size: int = 1
+
+
+class FeatureSet:
+  """An ordered collection of uniquely named features (`recml/examples/dlrm_experiment.py:68-98`)."""
+
+  def __init__(self, features: Sequence[Feature]):
+    self.features = list(features)
+    names = [f.name for f in self.features]
+    if len(names) != len(set(names)):
+      raise ValueError(f"Feature names must be unique. Got names: {names}.")
+
+  def dense_features(self) -> "FeatureSet":
+    return FeatureSet([f for f in self if isinstance(f, DenseFeature)])
+
+  def sparse_features(self) -> "FeatureSet":
+    return FeatureSet([f for f in self if isinstance(f, SparseFeature)])
+
+  def __iter__(self):
+    return iter(self.features)
+
+  def __len__(self) -> int:
+    return len(self.features)
+
+  def __or__(self, other: "FeatureSet") -> "FeatureSet":
+    return FeatureSet([*self.features, *other.features])
+
+
+def features(embedding_dim: int = 128) -> FeatureSet:
+  """The Criteo-1TB feature set: 13 dense features and 26 categorical ones with the benchmark's vocabulary and
+  multi-hot sizes."""
+  dense = [DenseFeature(f"float-feature-{i}") for i in range(13)]
+  sparse = [SparseFeature(f"categorical-feature-{14 + i}", vocab_size=v, embedding_dim=embedding_dim, bag_size=b)
+            for i, (v, b) in enumerate(zip(synthetic.CRITEO_VOCAB_SIZES, synthetic.CRITEO_MULTI_HOT_SIZES))]
+  return FeatureSet(dense) | FeatureSet(sparse)
+
+
+@dataclasses.dataclass
 class ModelConfig:
   vocab_sizes: Sequence[int] = synthetic.CRITEO_VOCAB_SIZES
   bag_sizes: Sequence[int] = synthetic.CRITEO_MULTI_HOT_SIZES
@@ -43,6 +99,17 @@ class ModelConfig:
   embedding_init_scale: float | None = None
   row_wise_min_bytes: int | None = None
   backend: str = "auto"
+
+  @classmethod
+  def from_features(cls, feature_set: FeatureSet, **kwargs) -> "ModelConfig":
+    """The geometry a `FeatureSet` describes: one table per sparse feature (all of one embedding width, which
+    the interaction layer needs), the dense features as the bottom MLP's input."""
+    sparse = list(feature_set.sparse_features())
+    dims = {f.embedding_dim for f in sparse}
+    if len(dims) != 1:
+      raise ValueError(f"all sparse features must share one embedding_dim, got {sorted(dims)}")
+    return cls(vocab_sizes=tuple(f.vocab_size for f in sparse), bag_sizes=tuple(f.bag_size for f in sparse),
+               embedding_dim=dims.pop(), num_dense=len(feature_set.dense_features()), **kwargs)
 
 
 class CriteoFactory(types.Factory[Any]):
