@@ -88,17 +88,24 @@ def test_hstu_retrieval_trains_on_gpu():
   assert lg[-1] < lg[0] * 0.7, lg
 
 
-def test_sampled_softmax_kernel_matches_torch():
+@pytest.mark.parametrize("C", [1000, 256, 512, 1024])
+def test_sampled_softmax_kernel_matches_torch(C):
+  """C = 256 / 512 / 1024 take the kernel that holds a row in registers; other widths the strided one.  The ids
+  go past 32 bits, and one candidate shares only its LOW word with a target: it must not be dropped."""
   import torch
   from recml_b200.ops import sampled_softmax as S
   torch.manual_seed(0)
-  T, C = 777, 1000
+  T = 777
   pos = torch.randn(T, device="cuda") * 0.5
   neg = (torch.randn(T, C, device="cuda") * 0.5).to(torch.bfloat16)
-  cand = torch.randint(0, 3000, (C,), device="cuda")
-  tgt = torch.randint(0, 3000, (T,), device="cuda")
+  cand = torch.randint(0, 3000, (C,), device="cuda") + (1 << 33)
+  tgt = torch.randint(0, 3000, (T,), device="cuda") + (1 << 33)
   tgt[:50] = cand[:50]                      # accidental hits
+  tgt[60] = 5 + (1 << 33)
+  cand[7] = 5 + (1 << 34)                   # same low word as target 60, another item
+  cand[8] = 5 + (1 << 33)                   # and the real accidental hit beside it
   w = (torch.rand(T, device="cuda") > 0.2).float()
+  w[60] = 1.0
   a = [pos.clone().requires_grad_(), neg.clone().requires_grad_()]
   r = [pos.clone().requires_grad_(), neg.float().clone().requires_grad_()]
   loss, hit = S.sampled_softmax_loss(a[0], a[1], cand, tgt, w, 0.05)
@@ -109,6 +116,12 @@ def test_sampled_softmax_kernel_matches_torch():
   (loss_r * 3.0).backward()
   torch.testing.assert_close(a[0].grad, r[0].grad, rtol=1e-3, atol=1e-5)
   torch.testing.assert_close(a[1].grad.float(), r[1].grad, rtol=2e-2, atol=1e-5)
+  assert float(a[1].grad[60, 8]) == 0.0 and float(a[1].grad[60, 7]) != 0.0
+  # the plain backward (incoming gradient exactly 1) leaves the stored gradient as the kernel wrote it
+  b = [pos.clone().requires_grad_(), neg.clone().requires_grad_()]
+  S.sampled_softmax_loss(b[0], b[1], cand, tgt, w, 0.05)[0].backward()
+  torch.testing.assert_close(b[1].grad.float() * 3.0, a[1].grad.float(), rtol=2e-2, atol=1e-6)
+  torch.testing.assert_close(b[0].grad * 3.0, a[0].grad, rtol=1e-5, atol=1e-7)
 
 
 def test_attention_accepts_column_slices_of_a_fused_projection():
