@@ -13,7 +13,7 @@ import os
 
 
 def run(steps: int = 10, warmup: int = 3, vocab: int = 10_000_000, use_graph: bool = False, layers: int = 8,
-        sequences: int = 128) -> dict:
+        sequences: int = 128, timeline: str | None = None) -> dict:
   import torch
   import torch.distributed as dist
   from recml_b200.examples import hstu_experiment as E
@@ -59,7 +59,11 @@ def run(steps: int = 10, warmup: int = 3, vocab: int = 10_000_000, use_graph: bo
     dist.all_reduce(tok)
   _lib.check_status(device)
   ms_step = float(ms.item()) / steps
-  return {"metric": "hstu_train_tokens_per_sec", "value": float(tok.item()) / (ms_step * 1e-3), "unit": "tokens/s",
+  extra = {}
+  if timeline:        # after the timed region: the profiler slows the steps it records
+    from recml_b200.utils import profiling
+    extra["timeline"] = profiling.kernel_timeline(step, timeline)
+  return {**extra, "metric": "hstu_train_tokens_per_sec", "value": float(tok.item()) / (ms_step * 1e-3), "unit": "tokens/s",
           "ms_per_step": ms_step, "tokens_per_step": float(tok.item()), "n_gpus": world,
           "loss": float(m["loss"].localize().compute()),
           "config": {"vocab": vocab, "model_dim": cfg.model_dim, "layers": layers, "heads": cfg.num_heads,
@@ -75,12 +79,13 @@ def main():
   ap.add_argument("--vocab", type=int, default=10_000_000)
   ap.add_argument("--layers", type=int, default=8)
   ap.add_argument("--sequences", type=int, default=128)
+  ap.add_argument("--timeline", default=None, help="write the per-kernel totals and launch order of one step here")
   args = ap.parse_args()
   local = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local)
   if int(os.environ.get("WORLD_SIZE", "1")) > 1:
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-  out = run(args.steps, args.warmup, args.vocab, layers=args.layers, sequences=args.sequences)
+  out = run(args.steps, args.warmup, args.vocab, layers=args.layers, sequences=args.sequences, timeline=args.timeline)
   if int(os.environ.get("RANK", "0")) == 0:
     print(json.dumps(out))
   if dist.is_initialized():

@@ -148,3 +148,37 @@ def trace(path: str, enabled: bool = True):
   with torch.profiler.profile(activities=acts) as prof:
     yield
   prof.export_chrome_trace(path)
+
+
+def kernel_timeline(step_fn, path: str, *, steps: int = 4, pick: int = 2, top: int = 40) -> dict:
+  """Runs `step_fn` `steps` times under the profiler's CUDA activity records and writes, for step `pick`:
+  the total duration and launch count per kernel name (the `top` largest), then every kernel in launch order
+  with its start offset and duration in microseconds.  Returns {"kernels_per_step", "span_us", "busy_us"}.
+  The steps must launch the same kernels each time (a steady-state training step does)."""
+  import collections
+  from torch.profiler import ProfilerActivity, profile
+  with profile(activities=[ProfilerActivity.CUDA]) as prof:
+    for _ in range(steps):
+      step_fn()
+    torch.cuda.synchronize()
+  events = [e for e in prof.profiler.kineto_results.events() if str(e.device_type()).endswith("CUDA")]
+  events.sort(key=lambda e: e.start_ns())
+  per = len(events) // steps
+  seg = events[pick * per:(pick + 1) * per]
+  if not seg:
+    raise RuntimeError("the profiler recorded no CUDA activity")
+  t0 = seg[0].start_ns()
+  span = (max(e.start_ns() + e.duration_ns() for e in seg) - t0) / 1e3
+  busy = sum(e.duration_ns() for e in seg) / 1e3
+  total, count = collections.Counter(), collections.Counter()
+  for e in seg:
+    total[e.name()[:90]] += e.duration_ns() / 1e3
+    count[e.name()[:90]] += 1
+  with open(path, "w") as f:
+    f.write(f"kernels/step {per}; span {span:.0f} us; busy {busy:.0f} us\n")
+    for name, us in total.most_common(top):
+      f.write(f"{us:9.1f} us x{count[name]:4d}  {name}\n")
+    f.write("----\n")
+    for e in seg:
+      f.write(f"{(e.start_ns() - t0) / 1e3:9.1f} +{e.duration_ns() / 1e3:8.1f} {e.name()[:110]}\n")
+  return {"kernels_per_step": per, "span_us": span, "busy_us": busy}

@@ -1,6 +1,8 @@
 """Tracing / profiling helpers on a machine without a GPU: scopes are no-ops, timers report nothing, the
 progress reporter measures steps per second and the share of timed side work, the trace is a Chrome trace."""
 import json
+
+import pytest
 import time
 
 import torch
@@ -61,3 +63,13 @@ def test_report_progress_writes_scalars_every_n_steps():
     rp(step)
   assert [s for s, _ in w.rows] == [5, 10]
   assert set(w.rows[0][1]) == {"steps_per_sec", "uptime"} and w.rows[0][1]["steps_per_sec"] > 0
+
+
+@pytest.mark.gpu
+def test_kernel_timeline_lists_the_kernels_of_a_step(tmp_path):
+  x = torch.randn(1 << 20, device="cuda")
+  def step():
+    (x * 2).sum()
+  out = profiling.kernel_timeline(step, str(tmp_path / "t.txt"), steps=4, pick=2)
+  text = open(tmp_path / "t.txt").read()
+  assert out["kernels_per_step"] >= 2 and "----" in text and "us x" in text
