@@ -16,7 +16,6 @@ import threading
 from typing import Any, Callable, Mapping, Sequence
 
 import numpy as np
-import torch
 import torch.distributed as dist
 
 from recml_b200.data import iterator as iterator_lib

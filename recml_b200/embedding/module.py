@@ -26,7 +26,6 @@ from torch import nn
 from recml_b200.ckpt.manager import ShardedLeaf
 from recml_b200.embedding import jagged as jagged_lib
 from recml_b200.embedding import planner as planner_lib
-from recml_b200.embedding import row_optim
 from recml_b200.embedding import specs as specs_lib
 from recml_b200.embedding.planner import Placement
 

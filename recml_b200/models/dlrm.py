@@ -8,7 +8,7 @@ tcgen05 GEMM and the embedding bags on the fused sharded-embedding kernels.
 """
 from __future__ import annotations
 
-from typing import Mapping, Sequence
+from typing import Sequence
 
 import torch
 from torch import nn

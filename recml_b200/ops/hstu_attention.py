@@ -13,13 +13,10 @@ normaliser is the configured `max_seq_len` (the reference divides by the padded 
 """
 from __future__ import annotations
 
-import ctypes
 import enum
 import math
 
 import torch
-
-from recml_b200.ops import _lib
 
 BUCKET_SIZE = 0.301
 

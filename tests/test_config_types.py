@@ -1,7 +1,6 @@
 """Config graph, the `config:/fiddler:/set:` flag and dataclass factories
 (cases follow `recml/core/utils/config_test.py` and `types_test.py`)."""
 import dataclasses
-import sys
 
 import pytest
 from absl import flags
