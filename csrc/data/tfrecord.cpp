@@ -114,10 +114,13 @@ inline bool field(Slice& s, uint32_t& num, uint32_t& wire, Slice& payload, uint6
 }
 
 // Feature { bytes_list = 1; float_list = 2; int64_list = 3 }, each list has `repeated value = 1`.
-void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floats, std::vector<std::string>* bytes) {
+// Returns false when the bytes do not decode as a Feature to their end (a field that runs past the buffer, an
+// unknown wire type, a truncated packed list); what was decoded up to there has been appended.
+bool parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floats, std::vector<std::string>* bytes) {
   uint32_t kind, wire, num;
   Slice pl;
   uint64_t sc;
+  bool ok = true;
   while (f.n > 0 && field(f, kind, wire, pl, sc)) {
     if (wire != 2) continue;   // kind: 1 bytes_list, 2 float_list, 3 int64_list
     Slice list = pl;
@@ -125,6 +128,7 @@ void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floa
       if (num != 1) continue;
       if (kind == 3 && ints != nullptr) {
         if (wire == 2) {         // packed varints: one terminating byte (high bit clear) per value
+          if (pl.n > 0 && (pl.p[pl.n - 1] & 0x80)) ok = false;      // the last value has no end
           size_t n_vals = 0;
           for (size_t i = 0; i < pl.n; ++i) n_vals += !(pl.p[i] & 0x80);
           const size_t at = ints->size();
@@ -134,12 +138,13 @@ void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floa
           uint64_t v;
           size_t k = 0;
           while (k < n_vals && pk.n > 0 && varint(pk, v)) out[k++] = static_cast<int64_t>(v);
-          if (k < n_vals) ints->resize(at + k);      // truncated payload
+          if (k < n_vals) { ints->resize(at + k); ok = false; }      // truncated payload
         } else if (wire == 0) {
           ints->push_back(static_cast<int64_t>(sc));
         }
       } else if (kind == 2 && floats != nullptr) {
         if (wire == 2) {         // packed floats
+          if (pl.n % 4) ok = false;
           const size_t at = floats->size(), n_vals = pl.n / 4;
           floats->resize(at + n_vals);
           if (n_vals) memcpy(floats->data() + at, pl.p, n_vals * 4);
@@ -148,9 +153,43 @@ void parse_feature(Slice f, std::vector<int64_t>* ints, std::vector<float>* floa
         }
       } else if (kind == 1 && bytes != nullptr && wire == 2) {
         bytes->emplace_back(reinterpret_cast<const char*>(pl.p), pl.n);
+      } else if (wire == 2 && ((kind == 3 && pl.n > 0 && (pl.p[pl.n - 1] & 0x80)) || (kind == 2 && pl.n % 4))) {
+        ok = false;              // a list nobody asked for is still checked for a whole number of values
       }
     }
+    ok = ok && list.n == 0;
   }
+  return ok && f.n == 0;
+}
+
+// Structural check of one serialized Example / SequenceExample: every nested message (the feature maps, their
+// entries, the features and feature lists) must decode to its last byte.
+bool record_ok(Slice example) {
+  uint32_t num, wire;
+  Slice pl;
+  uint64_t sc;
+  while (example.n > 0 && field(example, num, wire, pl, sc)) {
+    if (wire != 2 || (num != 1 && num != 2)) continue;
+    const bool lists = num == 2;
+    Slice feats = pl;
+    while (feats.n > 0 && field(feats, num, wire, pl, sc)) {
+      if (num != 1 || wire != 2) continue;
+      Slice entry = pl, val{nullptr, 0};
+      while (entry.n > 0 && field(entry, num, wire, pl, sc))
+        if (num == 2) val = pl;
+      if (entry.n > 0) return false;
+      if (!lists) {
+        if (!parse_feature(val, nullptr, nullptr, nullptr)) return false;
+        continue;
+      }
+      Slice list = val;
+      while (list.n > 0 && field(list, num, wire, pl, sc))
+        if (num == 1 && wire == 2 && !parse_feature(pl, nullptr, nullptr, nullptr)) return false;
+      if (list.n > 0) return false;
+    }
+    if (feats.n > 0) return false;
+  }
+  return example.n == 0;
 }
 
 // Example { Features features = 1 }; Features { map<string, Feature> feature = 1 } (map entry: key = 1, value = 2)
@@ -238,6 +277,21 @@ long long recml_tfrecord_frame(const uint8_t* payload, long long len, uint8_t* o
   const uint32_t c2 = masked(crc32c(payload, static_cast<size_t>(len)));
   memcpy(out + 12 + len, &c2, 4);
   return len + 16;
+}
+
+// Index of the first record that does not decode as an Example / SequenceExample (`record_ok`), or -1.
+long long recml_validate_examples(const uint8_t* data, const long long* offsets, const long long* lengths,
+                                  long long count) {
+  std::atomic<long long> first_bad{-1};
+  recml::ThreadPool::global().parallel_for(count, [&](long long r0, long long r1, int) {
+    for (long long r = r0; r < r1; ++r) {
+      if (record_ok(Slice{data + offsets[r], static_cast<size_t>(lengths[r])})) continue;
+      long long seen = first_bad.load();
+      while ((seen < 0 || r < seen) && !first_bad.compare_exchange_weak(seen, r)) {}
+      break;
+    }
+  }, 64);
+  return first_bad.load();
 }
 
 // Parses one named feature from `count` serialized Examples in parallel.
@@ -411,6 +465,7 @@ struct MultiParse {
   std::vector<int> kind;                               // 0 int64, 1 float
   std::vector<std::vector<std::vector<int64_t>>> ints; // [chunk][feature]
   std::vector<std::vector<std::vector<float>>> floats;
+  std::atomic<long long> first_bad{-1};                // lowest index of a record that did not decode to its end
 };
 
 void* recml_parse_multi(const uint8_t* data, const long long* offsets, const long long* lengths, long long count,
@@ -453,6 +508,7 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
         Slice pl;
         uint64_t sc;
         int guess = 0;      // records usually list their features in the same order: try the next one first
+        bool ok = true;
         while (example.n > 0 && field(example, num, wire, pl, sc)) {
           if (wire != 2 || (num != 1 && num != 2)) continue;
           const int src = num == 2 ? 1 : 0;
@@ -464,6 +520,7 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
               if (num == 1) key = pl;
               if (num == 2) val = pl;
             }
+            ok = ok && entry.n == 0;
             int f = -1;
             for (int t = 0; t < n_feat; ++t) {
               const int cand = guess + t < n_feat ? guess + t : guess + t - n_feat;
@@ -481,9 +538,10 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
               Slice list = val;
               while (list.n > 0 && field(list, num, wire, pl, sc)) {
                 if (num != 1 || wire != 2) continue;
-                parse_feature(pl, di, df, nullptr);
+                ok = parse_feature(pl, di, df, nullptr) && ok;
                 ++n_steps;
               }
+              ok = ok && list.n == 0;
               row_lengths[f][r] = static_cast<long long>((di != nullptr ? di->size() : df->size()) - before);
               if (steps_out != nullptr && steps_out[f] != nullptr) steps_out[f][r] = n_steps;
               continue;
@@ -493,7 +551,7 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
               std::vector<int64_t>& dst = fl > 0 ? iv : mp->ints[c][f];
               const size_t before = dst.size();
               if (fl > 0) iv.clear();
-              parse_feature(val, &dst, nullptr, nullptr);
+              ok = parse_feature(val, &dst, nullptr, nullptr) && ok;
               if (fl > 0) {
                 int64_t* out = static_cast<int64_t*>(dense_out[f]) + r * fl;
                 for (int i = 0; i < fl; ++i) out[i] = i < static_cast<int>(iv.size()) ? iv[i] : default_int[f];
@@ -504,7 +562,7 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
               std::vector<float>& dst = fl > 0 ? fv : mp->floats[c][f];
               const size_t before = dst.size();
               if (fl > 0) fv.clear();
-              parse_feature(val, nullptr, &dst, nullptr);
+              ok = parse_feature(val, nullptr, &dst, nullptr) && ok;
               if (fl > 0) {
                 float* out = static_cast<float*>(dense_out[f]) + r * fl;
                 for (int i = 0; i < fl; ++i) out[i] = i < static_cast<int>(fv.size()) ? fv[i] : default_float[f];
@@ -513,6 +571,11 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
               }
             }
           }
+          ok = ok && feats.n == 0;
+        }
+        if (!ok || example.n > 0) {
+          long long seen_bad = mp->first_bad.load();
+          while ((seen_bad < 0 || r < seen_bad) && !mp->first_bad.compare_exchange_weak(seen_bad, r)) {}
         }
         for (int f = 0; f < n_feat; ++f) {      // features the record does not have
           if (seen[f]) continue;
@@ -531,6 +594,11 @@ void* recml_parse_multi(const uint8_t* data, const long long* offsets, const lon
     }
   }, 1);
   return mp;
+}
+
+// Lowest index of a record that did not decode as an Example / SequenceExample, or -1.
+long long recml_parse_multi_first_bad(const void* handle) {
+  return static_cast<const MultiParse*>(handle)->first_bad.load();
 }
 
 // Total number of values collected for variable-length feature f.

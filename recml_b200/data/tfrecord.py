@@ -71,9 +71,12 @@ def write_tfrecord(path: str, records: Iterable[bytes]) -> int:
 
 
 class RecordFile:
-  """A TFRecord file mapped into memory and indexed (payload offsets / lengths); CRCs verified."""
+  """A TFRecord file mapped into memory and indexed (payload offsets / lengths); CRCs verified.  The parse
+  methods raise `ValueError` for a record that does not decode as a `tf.Example` / `tf.SequenceExample` to its
+  last byte (a field running past the record, a truncated packed list), as TensorFlow's parser does."""
 
   def __init__(self, path: str, verify: bool = True):
+    self.path = path
     # mapped, not read: only the pages of the records a process parses are brought in
     self.data = (np.memmap(path, dtype=np.uint8, mode="r") if os.path.getsize(path) > 0
                  else np.zeros(0, dtype=np.uint8))
@@ -93,10 +96,33 @@ class RecordFile:
   def record(self, i: int) -> bytes:
     return self.data[self.offsets[i]:self.offsets[i] + self.lengths[i]].tobytes()
 
+  def _malformed(self, rows: np.ndarray, k: int) -> ValueError:
+    return ValueError(f"{self.path}: record {int(np.asarray(rows)[k])} is not a valid serialized example")
+
+  def validate(self, rows: np.ndarray) -> None:
+    """Structural check of the given records (every nested message decodes to its end); a record is checked
+    once, however many per-feature parses ask for it."""
+    rows = np.asarray(rows, dtype=np.int64)
+    if getattr(self, "_checked", None) is None:
+      self._checked = np.zeros(len(self), dtype=bool)
+    todo = rows[~self._checked[rows]]
+    if todo.size == 0:
+      return
+    lib = _lib_host()
+    lib.recml_validate_examples.restype = c_ll
+    offs = np.ascontiguousarray(self.offsets[todo])
+    lens = np.ascontiguousarray(self.lengths[todo])
+    k = lib.recml_validate_examples(self.data.ctypes.data_as(ctypes.c_void_p), offs.ctypes.data_as(ctypes.c_void_p),
+                                    lens.ctypes.data_as(ctypes.c_void_p), c_ll(len(todo)))
+    if k >= 0:
+      raise self._malformed(todo, k)
+    self._checked[todo] = True
+
   def parse(self, rows: np.ndarray, name: str, dtype: str, fixed_len: int = 0, default=0):
     """Parses feature `name` of the given record indices with all host threads.
     fixed_len > 0 → dense `[len(rows), fixed_len]`; else (values, row_lengths) jagged."""
     lib = _lib_host()
+    self.validate(rows)
     kind = 0 if dtype in ("int64", "int") else 1
     np_dt = np.int64 if kind == 0 else np.float32
     offs = np.ascontiguousarray(self.offsets[rows])
@@ -160,6 +186,10 @@ class RecordFile:
         c_dense, c_rows, c_src, c_steps))
     out = {}
     try:
+      lib.recml_parse_multi_first_bad.restype = c_ll
+      bad = lib.recml_parse_multi_first_bad(handle)
+      if bad >= 0:
+        raise self._malformed(rows, bad)
       for f, ((nm, _, fl, _), k) in enumerate(zip(specs, kinds)):
         if fl > 0:
           out[nm] = dense[f]
@@ -175,6 +205,7 @@ class RecordFile:
     """Feature list `name` of tf.SequenceExample records: (values, values per record, steps per record);
     the values of a record's steps are concatenated in step order."""
     lib = _lib_host()
+    self.validate(rows)
     kind = 0 if dtype in ("int64", "int") else 1
     np_dt = np.int64 if kind == 0 else np.float32
     offs = np.ascontiguousarray(self.offsets[rows])

@@ -374,3 +374,29 @@ def test_factory_directory_groups_unsharded_reading_and_repeated_file_lists(tmp_
   assert ids(mk(cache_reading=True, repeat=True, num_epochs=2)) == [0, 1, 2, 3, 10, 11, 12] * 2
   with pytest.raises(ValueError, match="not supported"):
     mk(file_format=tff.FileFormat.SSTABLE).make().__next__()
+
+
+def test_malformed_examples_raise_instead_of_parsing_to_defaults(tmp_path):
+  """A record that does not decode to its last byte (truncated, or a length that runs past the record) is an
+  error in every parse entry point, as it is for TensorFlow's example parser; valid neighbours do not hide it."""
+  good = tfrecord.encode_example({"a": [1, 2, 3], "f": [0.5, 1.5], "s": [b"xy"]})
+  seq = tfrecord.encode_sequence_example({"a": [7]}, {"steps": [[1, 2], [3]]})
+  cases = {"truncated": good[:len(good) - 3], "overlong_length": bytes([0x0a, 0x7f]) + good[2:],
+           "garbage": bytes(range(200, 230))}
+  for name, bad in cases.items():
+    p = str(tmp_path / f"{name}.tfrecord")
+    tfrecord.write_tfrecord(p, [good, bad, good])
+    rows = np.arange(3)
+    for call in (lambda rf: rf.parse_many(rows, [("a", "int64", 0, 0), ("f", "float32", 2, 0.0)]),
+                 lambda rf: rf.parse(rows, "a", "int64"),
+                 lambda rf: rf.parse_sequence(rows, "steps", "int64")):
+      with pytest.raises(ValueError, match="record 1 is not a valid"):
+        call(tfrecord.RecordFile(p))
+    ok = tfrecord.RecordFile(p)
+    assert ok.parse(np.array([0, 2]), "a", "int64")[0].tolist() == [1, 2, 3, 1, 2, 3]     # the valid ones still parse
+  p = str(tmp_path / "ok.tfrecord")
+  tfrecord.write_tfrecord(p, [good, seq])
+  rf = tfrecord.RecordFile(p)
+  rf.validate(np.arange(2))
+  vals, lens, steps = rf.parse_sequence(np.arange(2), "steps", "int64")
+  assert vals.tolist() == [1, 2, 3] and steps.tolist() == [0, 2]
