@@ -66,7 +66,7 @@ def encode_record(labels: np.ndarray, dense: np.ndarray, ids: Sequence[np.ndarra
   feats: dict[str, Any] = {LABEL: [int(x) for x in labels]}
   for j, name in enumerate(DENSE):
     feats[name] = [float(x) for x in dense[:, j]]
-  for f, name in enumerate(SPARSE):
+  for f, name in enumerate(SPARSE[:len(ids)]):
     feats[name] = [np.ascontiguousarray(row, dtype="<i8").tobytes() for row in ids[f]]
   return tfrecord.encode_example(feats)
 
