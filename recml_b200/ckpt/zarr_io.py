@@ -167,14 +167,14 @@ def read_region(path: str, start: Sequence[int] | None = None,
     t = torch.from_numpy(out)
     return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd == 0:
-    out = np.array(_read_chunk(path, [], [], dt, comp).reshape(()))      # a writable 0-d copy
+    out = np.array(_read_chunk(path, [], [], dt, comp, []).reshape(()))      # a writable 0-d copy
   else:
     lo = [a // c for a, c in zip(start, chunks)]
     hi = [(b - 1) // c for b, c in zip(stop, chunks)]
     for idx in np.ndindex(*[h - l + 1 for l, h in zip(lo, hi)]):
       cidx = [l + i for l, i in zip(lo, idx)]
       c0 = [ci * c for ci, c in zip(cidx, chunks)]
-      data = _read_chunk(path, cidx, chunks, dt, comp)
+      data = _read_chunk(path, cidx, chunks, dt, comp, shape)
       # zarr stores edge chunks at full chunk shape; clip to the array and to the request
       src = tuple(slice(max(a, o) - o, min(b, o + c, s) - o)
                   for a, b, o, c, s in zip(start, stop, c0, chunks, shape))
@@ -255,25 +255,35 @@ def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> 
   return True
 
 
-def _read_chunk(path, cidx, chunks, dt, comp) -> np.ndarray:
+def _read_chunk(path, cidx, chunks, dt, comp, shape) -> np.ndarray:
+  """One chunk at full chunk shape.  A stored chunk holds either the full chunk or, for the last chunk along the
+  first dimension, exactly the rows that exist (a writer that clips its edge chunk); any other size is a
+  damaged file and raises instead of restoring zeros."""
+  name = chunk_name(cidx)
   if _is_ocdbt(path):
-    blob = _ocdbt_get(path, chunk_name(cidx))
+    blob = _ocdbt_get(path, name)
   else:
-    with open(os.path.join(path, chunk_name(cidx)), "rb") as f:
+    with open(os.path.join(path, name), "rb") as f:
       blob = f.read()
   n = int(np.prod(chunks)) if len(chunks) else 1
   if comp is not None:
     if comp.get("id") != "zstd" or not zstd_available():
       raise IOError(f"Unsupported chunk compressor {comp}")
     blob = zstd_decompress(blob, n * dt.itemsize)
-  if len(blob) < n * dt.itemsize:
-    # writer stored a clipped edge chunk: pad
-    arr = np.zeros(n, dtype=dt)
-    part = np.frombuffer(blob, dtype=dt)
-    arr[:part.size] = part
-    return arr.reshape(chunks)
-  return np.frombuffer(blob, dtype=dt, count=n).reshape(chunks) if len(chunks) else \
-      np.frombuffer(blob, dtype=dt, count=1)
+  if len(blob) == n * dt.itemsize:
+    return np.frombuffer(blob, dtype=dt, count=n).reshape(chunks) if len(chunks) else \
+        np.frombuffer(blob, dtype=dt, count=1)
+  clipped = -1
+  if len(chunks):
+    rows = min(int(chunks[0]), int(shape[0]) - int(cidx[0]) * int(chunks[0]))
+    clipped = rows * (n // int(chunks[0])) * dt.itemsize if chunks[0] else 0
+  if len(blob) != clipped:
+    raise IOError(f"{os.path.join(path, name)}: chunk holds {len(blob)} bytes, expected {n * dt.itemsize}"
+                  + (f" (or {clipped} for the clipped last chunk)" if 0 <= clipped < n * dt.itemsize else ""))
+  arr = np.zeros(n, dtype=dt)
+  part = np.frombuffer(blob, dtype=dt)
+  arr[:part.size] = part
+  return arr.reshape(chunks)
 
 
 def write_chunks_parallel(items, compressor: str | None = None) -> None:

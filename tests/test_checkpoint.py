@@ -202,3 +202,30 @@ def test_checkpoint_in_ocdbt_form_is_detected_and_restored(tmp_path):
   assert int(back["step"]) == 7
   tgt = {"params": {"w": ckpt.ShardedLeaf(torch.zeros(3, 4), (6, 4), (1, 0), (3, 4))}}
   torch.testing.assert_close(m.restore(3, target=tgt)["params"]["w"], tree["params"]["w"][3:])
+
+
+def test_truncated_chunk_raises_instead_of_restoring_zeros(tmp_path):
+  """A chunk file that lost its tail is an error on restore, with or without a sharded target; the one short
+  form that is accepted is the last chunk along the first dimension stored with exactly the rows that exist."""
+  tree = {"w": torch.arange(4096, dtype=torch.float32).reshape(64, 64), "b": torch.randn(33).to(torch.bfloat16)}
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  m.save(1, tree)
+  back = ckpt.CheckpointManager(str(tmp_path), async_save=False).restore(1, target=tree)
+  assert torch.equal(back["w"], tree["w"])
+  chunk = tmp_path / "1" / "state" / "w" / "0.0"
+  raw = chunk.read_bytes()
+  chunk.write_bytes(raw[:len(raw) - 100])
+  with pytest.raises(IOError, match="chunk holds"):
+    ckpt.CheckpointManager(str(tmp_path), async_save=False).restore(1, target=tree)
+  # a writer that clips its last chunk: 10 rows of 4 in chunks of 4 rows, the last chunk stored with 2 rows
+  d = tmp_path / "clipped"
+  os.makedirs(d)
+  full = np.arange(40, dtype=np.float32).reshape(10, 4)
+  zarr_io.write_zarray(str(d), (10, 4), (4, 4), "<f4", None)
+  for ci in range(3):
+    zarr_io.write_chunk(str(d), [ci, 0], full[ci * 4:(ci + 1) * 4], None)
+  assert torch.equal(zarr_io.read_region(str(d)), torch.from_numpy(full))
+  assert torch.equal(zarr_io.read_region(str(d), [7, 1], [10, 3]), torch.from_numpy(full[7:10, 1:3]))
+  (d / "2.0").write_bytes((d / "2.0").read_bytes()[:-4])
+  with pytest.raises(IOError, match="clipped last chunk"):
+    zarr_io.read_region(str(d))
