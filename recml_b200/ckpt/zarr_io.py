@@ -49,6 +49,13 @@ def _zstd():
                                     ctypes.c_size_t]
     lib.ZSTD_isError.restype = ctypes.c_uint
     lib.ZSTD_isError.argtypes = [ctypes.c_size_t]
+    if hasattr(lib, "ZSTD_compress2"):          # the context API (1.4+): frames with a content checksum
+      lib.ZSTD_createCCtx.restype = ctypes.c_void_p
+      lib.ZSTD_freeCCtx.argtypes = [ctypes.c_void_p]
+      lib.ZSTD_CCtx_setParameter.restype = ctypes.c_size_t
+      lib.ZSTD_CCtx_setParameter.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+      lib.ZSTD_compress2.restype = ctypes.c_size_t
+      lib.ZSTD_compress2.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t]
     return lib
   return None
 
@@ -60,10 +67,25 @@ def zstd_available() -> bool:
   return _ZSTD is not None
 
 
+_ZSTD_C_LEVEL, _ZSTD_C_CHECKSUM = 100, 201       # ZSTD_c_compressionLevel, ZSTD_c_checksumFlag
+
+
 def zstd_compress(raw: bytes, level: int = 1) -> bytes:
+  """One standard zstd frame; with the context API the frame carries a content checksum (XXH64, four bytes at
+  its end), which every zstd reader verifies while decompressing: a flipped bit in a stored chunk is an error
+  at restore instead of a wrong weight."""
   bound = _ZSTD.ZSTD_compressBound(len(raw))
   dst = ctypes.create_string_buffer(bound)
-  n = _ZSTD.ZSTD_compress(dst, bound, raw, len(raw), level)
+  if hasattr(_ZSTD, "ZSTD_compress2"):
+    cctx = _ZSTD.ZSTD_createCCtx()
+    try:
+      _ZSTD.ZSTD_CCtx_setParameter(cctx, _ZSTD_C_LEVEL, level)
+      _ZSTD.ZSTD_CCtx_setParameter(cctx, _ZSTD_C_CHECKSUM, 1)
+      n = _ZSTD.ZSTD_compress2(cctx, dst, bound, raw, len(raw))
+    finally:
+      _ZSTD.ZSTD_freeCCtx(cctx)
+  else:
+    n = _ZSTD.ZSTD_compress(dst, bound, raw, len(raw), level)
   if _ZSTD.ZSTD_isError(n):
     raise IOError("zstd compression failed")
   return dst.raw[:n]

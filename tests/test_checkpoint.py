@@ -106,6 +106,19 @@ def test_zstd_chunks(tmp_path):
   assert os.path.getsize(tmp_path / "1" / "state" / "x" / "0.0") < x.numel()
   assert json.load(open(tmp_path / "1" / "state" / "x" / ".zarray"))["compressor"]["id"] == "zstd"
   torch.testing.assert_close(m.restore(1)["x"], x)
+  # the frames carry a content checksum: one flipped bit anywhere in a stored chunk fails the restore
+  y = torch.randn(300, 16)
+  m.save(2, {"x": y})
+  chunk = tmp_path / "2" / "state" / "x" / "0.0"
+  raw = bytearray(chunk.read_bytes())
+  for at in (len(raw) // 3, len(raw) - 1):
+    bad = bytearray(raw)
+    bad[at] ^= 0x10
+    chunk.write_bytes(bytes(bad))
+    with pytest.raises(IOError, match="zstd"):
+      m.restore(2)
+  chunk.write_bytes(bytes(raw))
+  torch.testing.assert_close(m.restore(2)["x"], y)
 
 
 def test_checkpoints_iterator_sees_new_steps_and_stops_on_marker(tmp_path):
