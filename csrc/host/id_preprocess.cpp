@@ -10,6 +10,7 @@
 //                          with (max ids / max unique ids per partition, drop count).
 // Row -> shard follows the MOD layout: shard = (id % shards + rotation) % shards, local row = id / shards.
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <numeric>
@@ -96,20 +97,28 @@ int recml_pack_jagged(int num_features, int batch, const int64_t* const* feature
 // ids[nnz] with offsets[batch+1] (bag b = ids[offsets[b]:offsets[b+1]]), optional gains[nnz].
 // Outputs (caller-allocated, capacity nnz): out_rows / out_samples / out_gains sorted by (shard, row, sample);
 // shard_ptr[shards+1] delimits each shard's slice; stats[0..2] = max ids per shard, max unique rows
-// per shard, dropped ids.  max_ids_per_shard <= 0 disables dropping.  Returns the number of entries kept.
+// per shard, dropped ids.  max_ids_per_shard <= 0 disables dropping.  Returns the number of entries kept, -1 for a
+// negative id (nothing is written then), -2 for a shard count below 1 or offsets that do not ascend from 0.
 long long recml_partition_csr(const int32_t* ids, const int32_t* offsets, const float* gains, int batch, int shards,
                               int rotation, int max_ids_per_shard, int32_t* out_rows, int32_t* out_samples,
                               float* out_gains, int64_t* shard_ptr, int64_t* stats) {
+  if (shards < 1 || batch < 0 || offsets[0] != 0) return -2;
+  for (int b = 0; b < batch; ++b)
+    if (offsets[b + 1] < offsets[b]) return -2;
   const long long nnz = offsets[batch];
+  rotation = ((rotation % shards) + shards) % shards;
   std::vector<Entry> e(static_cast<size_t>(nnz));
+  std::atomic<int> negative{0};
   recml::ThreadPool::global().parallel_for(batch, [&](long long b0, long long b1, int) {
     for (long long b = b0; b < b1; ++b)
       for (int i = offsets[b]; i < offsets[b + 1]; ++i) {
         const int32_t id = ids[i];
+        if (id < 0) { negative.store(1); continue; }
         e[i] = Entry{static_cast<int32_t>((id % shards + rotation) % shards), id / shards, static_cast<int32_t>(b),
                      gains ? gains[i] : 1.0f};
       }
   }, 1024);
+  if (negative.load()) return -1;
   // bucket by shard (counting sort), then every shard is sorted by (row, sample), merged and capped on its
   // own thread; the shards' survivors are laid end to end afterwards
   std::vector<long long> start(shards + 1, 0);

@@ -30,6 +30,10 @@ def pack_jagged(features: Mapping[str, Sequence[np.ndarray]], weights: Mapping[s
   ids = [np.ascontiguousarray(features[n][0], dtype=np.int64) for n in names]
   lens = [np.ascontiguousarray(features[n][1], dtype=np.int32) for n in names]
   batch = int(lens[0].size) if F else 0
+  for n, a, l in zip(names, ids, lens):       # the native packer trusts these
+    if l.size != batch or (l.size and int(l.min()) < 0) or int(l.sum(dtype=np.int64)) != a.size:
+      raise ValueError(f"feature {n!r}: {a.size} ids, lengths of {l.size} samples summing to "
+                       f"{int(l.sum(dtype=np.int64))} (batch {batch})")
   total = int(sum(a.size for a in ids))
   mk = (lambda *s, dtype: torch.empty(*s, dtype=dtype).pin_memory()) if (pin and torch.cuda.is_available()) else \
       (lambda *s, dtype: torch.empty(*s, dtype=dtype))
@@ -76,6 +80,10 @@ def partition_csr(ids: np.ndarray, offsets: np.ndarray, shards: int, *, rotation
                                  c_int(batch), c_int(shards), c_int(rotation), c_int(max_ids_per_partition),
                                  P(rows.ctypes.data), P(samples.ctypes.data), P(out_g.ctypes.data),
                                  P(ptr.ctypes.data), P(stats.ctypes.data))
+  if kept == -1:
+    raise ValueError("negative id in the batch")
+  if kept < 0:
+    raise ValueError(f"bad partition request: {shards} shards, offsets must ascend from 0")
   return rows[:kept], samples[:kept], out_g[:kept], ptr, PartitionStats(int(stats[0]), int(stats[1]), int(stats[2]))
 
 

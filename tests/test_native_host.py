@@ -400,3 +400,21 @@ def test_malformed_examples_raise_instead_of_parsing_to_defaults(tmp_path):
   rf.validate(np.arange(2))
   vals, lens, steps = rf.parse_sequence(np.arange(2), "steps", "int64")
   assert vals.tolist() == [1, 2, 3] and steps.tolist() == [0, 2]
+
+
+def test_id_preprocessing_rejects_inputs_it_cannot_index():
+  """A negative id, lengths that do not add up to the ids, a shard count of zero: errors, not reads or writes
+  past the buffers (the native code trusts what the wrappers let through); a rotation outside [0, shards) wraps."""
+  ids = np.array([5, -3, 7], dtype=np.int64)
+  offs = np.array([0, 2, 3], dtype=np.int32)
+  with pytest.raises(ValueError, match="negative id"):
+    ip.partition_csr(ids, offs, 4)
+  with pytest.raises(ValueError, match="shards"):
+    ip.partition_csr(np.abs(ids), offs, 0)
+  a = ip.partition_csr(np.abs(ids), offs, 4, rotation=1)
+  b = ip.partition_csr(np.abs(ids), offs, 4, rotation=-3)
+  assert all(np.array_equal(x, y) for x, y in zip(a[:4], b[:4]))
+  with pytest.raises(ValueError, match="summing to"):
+    ip.pack_jagged({"a": (np.arange(4), np.array([2, 3], dtype=np.int32))})
+  with pytest.raises(ValueError, match="lengths of 1 samples"):
+    ip.pack_jagged({"a": (np.arange(2), np.array([1, 1], dtype=np.int32)), "b": (np.arange(2), np.array([2], dtype=np.int32))})
