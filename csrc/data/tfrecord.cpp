@@ -244,7 +244,8 @@ extern "C" {
 uint32_t recml_crc32c(const uint8_t* p, long long n) { return crc32c(p, static_cast<size_t>(n)); }
 
 // Scans a TFRecord file image: fills offsets[i] / lengths[i] of each record payload (up to cap).
-// Returns the record count, or -(1+index) of the first corrupt record when verify != 0.
+// Returns the record count, or -(1+index) of the first record that is corrupt: a frame that runs past the file
+// (or a tail too short to hold a frame header) always, a checksum mismatch when verify != 0.
 long long recml_tfrecord_index(const uint8_t* data, long long size, long long* offsets, long long* lengths,
                                long long cap, int verify) {
   long long pos = 0, n = 0;
@@ -254,7 +255,7 @@ long long recml_tfrecord_index(const uint8_t* data, long long size, long long* o
     memcpy(&len, data + pos, 8);
     memcpy(&len_crc, data + pos + 8, 4);
     if (verify && masked(crc32c(data + pos, 8)) != len_crc) return -(1 + n);
-    if (pos + 12 + static_cast<long long>(len) + 4 > size) return -(1 + n);
+    if (len > static_cast<uint64_t>(size) || pos + 12 + static_cast<long long>(len) + 4 > size) return -(1 + n);
     if (verify) {
       uint32_t data_crc;
       memcpy(&data_crc, data + pos + 12 + len, 4);
@@ -264,7 +265,7 @@ long long recml_tfrecord_index(const uint8_t* data, long long size, long long* o
     ++n;
     pos += 12 + static_cast<long long>(len) + 4;
   }
-  return n;
+  return pos == size ? n : -(1 + n);
 }
 
 // Frames one payload as a TFRecord into out (capacity >= len + 16); returns bytes written.

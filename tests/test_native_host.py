@@ -418,3 +418,23 @@ def test_id_preprocessing_rejects_inputs_it_cannot_index():
     ip.pack_jagged({"a": (np.arange(4), np.array([2, 3], dtype=np.int32))})
   with pytest.raises(ValueError, match="lengths of 1 samples"):
     ip.pack_jagged({"a": (np.arange(2), np.array([1, 1], dtype=np.int32)), "b": (np.arange(2), np.array([2], dtype=np.int32))})
+
+
+def test_tfrecord_index_rejects_frames_that_run_past_the_file(tmp_path):
+  """A length field of 2^63 - 1 (read as a negative offset once), a cut-off frame and stray bytes after the last
+  frame are corruption with and without checksum verification."""
+  good = tfrecord.encode_example({"a": [1, 2]})
+  p = str(tmp_path / "x.tfrecord")
+  tfrecord.write_tfrecord(p, [good, good])
+  raw = open(p, "rb").read()
+  frame = len(raw) // 2
+  cases = {"huge_length": raw[:frame] + (2**63 - 1).to_bytes(8, "little") + raw[frame + 8:],
+           "negative_length": raw[:frame] + (2**64 - 40).to_bytes(8, "little") + raw[frame + 8:],
+           "cut_frame": raw[:-5], "stray_tail": raw + b"\\x01\\x02\\x03"}
+  for name, blob in cases.items():
+    q = str(tmp_path / f"{name}.tfrecord")
+    open(q, "wb").write(blob)
+    for verify in (True, False):
+      with pytest.raises(IOError, match="corrupt TFRecord"):
+        tfrecord.RecordFile(q, verify=verify)
+  assert len(tfrecord.RecordFile(p)) == 2
