@@ -129,6 +129,8 @@ class Writer:
   def commit(self, compress_nodes: bool = True, node_fanout: int = 64) -> None:
     h, self._h = self._h, None
     rc = self._lib.recml_ocdbt_writer_commit(h, int(compress_nodes), node_fanout)
+    if rc == -2:
+      raise ValueError(f"OCDBT store {self.directory}: a key was added twice")
     if rc != 0:
       raise IOError(f"writing OCDBT store {self.directory} failed with code {rc}")
 
