@@ -1,0 +1,102 @@
+"""Property tests (hypothesis) of host-side invariants: whatever the tables and the world size, the planner
+places every table once, stores every row exactly once across the ranks and decides the same on every rank;
+the reference stacking layout round-trips and addresses rows as its rule says; the host id partition agrees
+with a numpy restatement."""
+import numpy as np
+import pytest
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st      # noqa: E402
+
+from recml_b200.embedding import id_pipeline as ip, layout_compat as lc, planner as P, specs as S   # noqa: E402
+
+
+@settings(max_examples=60, deadline=None)
+@given(vocabs=st.lists(st.integers(1, 5_000_000), min_size=1, max_size=12),
+       hots=st.lists(st.floats(0.5, 120.0), min_size=12, max_size=12),
+       dim=st.sampled_from([8, 64, 128]), world=st.sampled_from([1, 2, 3, 4, 8]),
+       replicate=st.sampled_from([0, 100]), budget_gb=st.sampled_from([1, 140]))
+def test_planner_places_every_row_once_and_identically_on_every_rank(vocabs, hots, dim, world, replicate, budget_gb):
+  opt = S.RowWiseAdagradOptimizerSpec(learning_rate=0.01)
+  tables = [S.TableSpec(f"t{i}", v, dim, opt) for i, v in enumerate(vocabs)]
+  ids = {t.name: hots[i] for i, t in enumerate(tables)}
+  plans = [P.plan_tables(tables, world, r, ids_per_sample=ids, replicate_max_rows=replicate,
+                         rank_budget_bytes=budget_gb << 30) for r in range(world)]
+  ref = plans[0]
+  assert set(ref.tables) == {t.name for t in tables}
+  for t in tables:
+    tps = [p.tables[t.name] for p in plans]
+    assert len({(tp.placement, tp.owner, tp.rotation) for tp in tps}) == 1
+    tp = tps[0]
+    if tp.placement is P.Placement.REPLICATED:
+      assert all(x.local_rows == t.vocabulary_size and x.local_dim == dim for x in tps)
+    elif tp.placement is P.Placement.COLUMN_WISE:
+      assert sum(x.local_dim for x in tps) == dim and all(x.local_rows == t.vocabulary_size for x in tps)
+    else:
+      assert sum(x.local_rows for x in tps) == t.vocabulary_size
+      assert all(x.local_dim == dim for x in tps if x.local_rows)
+    if tp.placement is P.Placement.TABLE_WISE:
+      assert 0 <= tp.owner < world and all((x.local_rows > 0) == (r == tp.owner) for r, x in enumerate(tps))
+    if tp.placement is P.Placement.ROW_WISE:
+      # rank r holds the rows whose id is congruent to (r - rotation) mod world
+      for r, x in enumerate(tps):
+        q = (r - tp.rotation) % world
+        assert x.local_rows == len(range(q, t.vocabulary_size, world))
+  # rows of one stack do not overlap on a rank
+  for p in plans:
+    spans = {}
+    for tp in p.tables.values():
+      if tp.local_rows:
+        spans.setdefault(tp.stack, []).append((tp.row_base, tp.row_base + tp.local_rows))
+    for spans_of_stack in spans.values():
+      spans_of_stack.sort()
+      assert all(a[1] <= b[0] for a, b in zip(spans_of_stack, spans_of_stack[1:]))
+
+
+@settings(max_examples=60, deadline=None)
+@given(shapes=st.lists(st.tuples(st.integers(1, 70), st.integers(1, 9)), min_size=1, max_size=5),
+       shards=st.sampled_from([1, 2, 4, 8]), rotation=st.integers(0, 3), seed=st.integers(0, 100))
+def test_reference_stack_layout_round_trips_and_addresses_rows(shapes, shards, rotation, seed):
+  rng = np.random.default_rng(seed)
+  tabs = {f"t{i}": rng.normal(size=s).astype(np.float32) for i, s in enumerate(shapes)}
+  lay = lc.stack_layout([(n, *t.shape) for n, t in tabs.items()], num_shards=shards, rotation=rotation)
+  stacked = lc.to_reference_stack(lay, tabs)
+  back = lc.from_reference_stack(lay, stacked)
+  for n, t in tabs.items():
+    np.testing.assert_array_equal(back[n], t)
+  per_shard = stacked.reshape(shards, lay.rows_per_shard, -1)
+  for n, t in tabs.items():
+    for row in {0, t.shape[0] // 2, t.shape[0] - 1}:
+      shard, local = lc.reference_location(lay, n, row)
+      np.testing.assert_array_equal(per_shard[shard, local, :t.shape[1]], t[row])
+
+
+@settings(max_examples=60, deadline=None)
+@given(lens=st.lists(st.integers(0, 6), min_size=1, max_size=30), shards=st.integers(1, 8), rotation=st.integers(0, 7),
+       vocab=st.integers(1, 50), cap=st.integers(0, 6), seed=st.integers(0, 1000), weighted=st.booleans())
+def test_id_partition_matches_a_numpy_restatement(lens, shards, rotation, vocab, cap, seed, weighted):
+  rng = np.random.default_rng(seed)
+  offs = np.zeros(len(lens) + 1, np.int32)
+  offs[1:] = np.cumsum(lens)
+  ids = rng.integers(0, vocab, int(offs[-1]))
+  gains = rng.integers(1, 4, ids.size).astype(np.float32) if weighted else None
+  rows, samples, g, ptr, stats = ip.partition_csr(ids, offs, shards, rotation=rotation, gains=gains,
+                                                  max_ids_per_partition=cap)
+  # restatement: (shard, row, sample) triples with summed gains, sorted, capped per shard
+  merged = {}
+  for b in range(len(lens)):
+    for i in range(offs[b], offs[b + 1]):
+      key = ((int(ids[i]) % shards + rotation) % shards, int(ids[i]) // shards, b)
+      merged[key] = merged.get(key, 0.0) + (float(gains[i]) if weighted else 1.0)
+  want, dropped, max_ids, max_unique = [], 0, 0, 0
+  for s in range(shards):
+    entries = sorted(k for k in merged if k[0] == s)
+    kept = entries if cap <= 0 else entries[:cap]
+    dropped += len(entries) - len(kept)
+    max_ids = max(max_ids, len(kept))
+    max_unique = max(max_unique, len({k[1] for k in kept}))
+    want += kept
+    assert ptr[s + 1] - ptr[s] == len(kept)
+  assert [(r, b) for _, r, b in want] == list(zip(rows.tolist(), samples.tolist()))
+  np.testing.assert_allclose(g, [merged[k] for k in want])
+  assert (stats.max_ids_per_partition, stats.max_unique_ids_per_partition, stats.dropped_ids) == (max_ids, max_unique, dropped)
