@@ -100,3 +100,54 @@ def test_id_partition_matches_a_numpy_restatement(lens, shards, rotation, vocab,
   assert [(r, b) for _, r, b in want] == list(zip(rows.tolist(), samples.tolist()))
   np.testing.assert_allclose(g, [merged[k] for k in want])
   assert (stats.max_ids_per_partition, stats.max_unique_ids_per_partition, stats.dropped_ids) == (max_ids, max_unique, dropped)
+
+
+@settings(max_examples=25, deadline=None)
+@given(n=st.integers(200, 3000), pos_rate=st.floats(0.1, 0.9), sep=st.floats(0.0, 3.0), seed=st.integers(0, 10_000),
+       weighted=st.booleans())
+def test_auc_metrics_agree_with_scikit_learn(n, pos_rate, sep, seed, weighted):
+  """The 200-threshold AUC estimates against scikit-learn's exact curves (an independent implementation) on
+  random scores of varying separability, merged from two halves the way the trainer merges steps."""
+  sk = pytest.importorskip("sklearn.metrics")
+  from recml_b200 import metrics as M
+  rng = np.random.default_rng(seed)
+  y = (rng.random(n) < pos_rate).astype(np.float32)
+  if y.min() == y.max():
+    y[0], y[1] = 0.0, 1.0
+  logits = rng.normal(size=n) + sep * (y - 0.5)
+  p = 1.0 / (1.0 + np.exp(-logits))
+  w = rng.integers(1, 4, n).astype(np.float32) if weighted else None
+  half = n // 2
+  parts = [(slice(0, half)), (slice(half, n))]
+  roc = [M.aucroc(y[s], p[s], None if w is None else w[s]) for s in parts]
+  pr = [M.aucpr(y[s], p[s], None if w is None else w[s]) for s in parts]
+  got_roc = float(roc[0].merge(roc[1]).compute())
+  got_pr = float(pr[0].merge(pr[1]).compute())
+  want_roc = sk.roc_auc_score(y, p, sample_weight=w)
+  prec, rec, _ = sk.precision_recall_curve(y, p, sample_weight=w)
+  want_pr = sk.auc(rec, prec)
+  assert abs(got_roc - want_roc) < 0.02, (got_roc, want_roc)
+  assert abs(got_pr - want_pr) < 0.03, (got_pr, want_pr)
+
+
+@settings(max_examples=25, deadline=None)
+@given(n=st.integers(1, 40), c=st.integers(2, 60), k=st.integers(1, 20), seed=st.integers(0, 10_000))
+def test_ranking_metrics_agree_with_scikit_learn(n, c, k, seed):
+  """NDCG@K and top-K accuracy with one relevant item per row against scikit-learn (distinct scores: ties are
+  broken differently by design — a tie counts against the target here)."""
+  sk = pytest.importorskip("sklearn.metrics")
+  import torch
+  from recml_b200 import metrics as M
+  rng = np.random.default_rng(seed)
+  scores = rng.permuted(np.tile(np.arange(c, dtype=np.float32), (n, 1)), axis=1) / c      # distinct per row
+  y = rng.integers(0, c, n)
+  rel = np.zeros((n, c), dtype=np.float32)
+  rel[np.arange(n), y] = 1.0
+  kk = min(k, c)
+  got_ndcg = float(M.ndcg_at_k(torch.from_numpy(y), torch.from_numpy(scores), k=kk).compute())
+  got_rec = float(M.recall_at_k(torch.from_numpy(y), torch.from_numpy(scores), k=kk).compute())
+  want_ndcg = sk.ndcg_score(rel, scores, k=kk) if c > 1 else 1.0
+  want_rec = float(np.mean([(np.argsort(-scores[i])[:kk] == y[i]).any() for i in range(n)]))
+  assert abs(got_ndcg - want_ndcg) < 1e-5 and abs(got_rec - want_rec) < 1e-6
+  ranks = np.array([1 + int((scores[i] > scores[i, y[i]]).sum()) for i in range(n)])
+  assert abs(float(M.mrr(torch.from_numpy(y), torch.from_numpy(scores)).compute()) - float(np.mean(1.0 / ranks))) < 1e-6
