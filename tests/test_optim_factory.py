@@ -128,3 +128,37 @@ def test_state_dict_round_trip_continues_identically():
     o.step()
   for (_, a), (_, b) in zip(n1.items(), n2.items()):
     torch.testing.assert_close(a, b)
+
+
+@pytest.mark.parametrize("clip", [None, 0.5])
+def test_adam_and_sgd_factories_follow_torch_optimizers(clip):
+  """An independent oracle: AdamFactory is `torch.optim.AdamW` (decoupled decay on the matrices only) behind
+  `clip_grad_norm_`, SGDFactory is `torch.optim.SGD`, over ten steps with a cosine schedule."""
+  total = 10
+  sched = lambda step: 0.02 * 0.5 * (1.0 + math.cos(math.pi * step / total))
+  for kind in ("adam", "sgd"):
+    m, named = _params()
+    twin, twin_named = _params()
+    if kind == "adam":
+      opt = recml.AdamFactory(learning_rate=sched, b1=0.9, b2=0.98, eps=1e-8, weight_decay=0.1, grad_clip_norm=clip).make() \
+          .init(list(named.items()))
+      ref = torch.optim.AdamW([{"params": [p for p in twin_named.values() if p.ndim > 1], "weight_decay": 0.1},
+                               {"params": [p for p in twin_named.values() if p.ndim <= 1], "weight_decay": 0.0}],
+                              lr=1.0, betas=(0.9, 0.98), eps=1e-8)
+    else:
+      opt = recml.SGDFactory(learning_rate=sched, grad_clip_norm=clip).make().init(list(named.items()))
+      ref = torch.optim.SGD(twin_named.values(), lr=1.0)
+    for step in range(total):
+      grads = _grads(named, step)
+      for n in named:
+        named[n].grad = grads[n].clone()
+        twin_named[n].grad = grads[n].clone()
+      if clip is not None:
+        torch.nn.utils.clip_grad_norm_(list(twin_named.values()), clip)
+      for group in ref.param_groups:
+        group["lr"] = sched(step)
+      opt.step()
+      ref.step()
+    for n in named:
+      torch.testing.assert_close(named[n].detach(), twin_named[n].detach(), rtol=2e-5, atol=2e-6,
+                                 msg=lambda s, n=n, kind=kind: f"{kind} {n}: {s}")
