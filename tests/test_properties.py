@@ -151,3 +151,57 @@ def test_ranking_metrics_agree_with_scikit_learn(n, c, k, seed):
   assert abs(got_ndcg - want_ndcg) < 1e-5 and abs(got_rec - want_rec) < 1e-6
   ranks = np.array([1 + int((scores[i] > scores[i, y[i]]).sum()) for i in range(n)])
   assert abs(float(M.mrr(torch.from_numpy(y), torch.from_numpy(scores)).compute()) - float(np.mean(1.0 / ranks))) < 1e-6
+
+
+def test_cpu_reference_ops_agree_with_torch_builtins():
+  """The plain-torch formulations that serve as oracles for the CUDA kernels, themselves checked against torch's
+  own operators: attention vs `scaled_dot_product_attention`, the causal depthwise convolution vs `conv1d`, the
+  layer / RMS norm vs `layer_norm` / `rms_norm`, the multi-head attention layer vs `nn.MultiheadAttention`."""
+  import torch
+  import torch.nn.functional as F
+  from recml_b200.layers import transformer
+  from recml_b200.ops import norm as norm_ops, softmax_attention as sm, ssd
+  torch.manual_seed(0)
+  B, L, H, Dh = 3, 17, 2, 8
+  q, k, v = (torch.randn(B, L, H, Dh) for _ in range(3))
+  pad = torch.ones(B, L, dtype=torch.bool)
+  pad[0, :5] = False
+  pad[2, 11:] = False
+  for causal in (False, True):
+    mask = sm.merge_masks(B, L, q.device, padding_mask=pad, causal=causal)
+    got = sm.softmax_attention(q, k, v, mask)
+    want = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                          attn_mask=mask[:, None]).transpose(1, 2)
+    rows = mask.any(-1)                      # a query that sees no key has no defined output
+    torch.testing.assert_close(got[rows], want[rows], rtol=1e-5, atol=1e-5)
+
+  C, K = 6, 4
+  x, w, b = torch.randn(B, L, C), torch.randn(C, K), torch.randn(C)
+  got = ssd.causal_depthwise_conv1d_silu(x, w, b)
+  want = F.silu(F.conv1d(x.transpose(1, 2), w[:, None, :], b, padding=K - 1, groups=C)[..., :L]).transpose(1, 2)
+  torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+
+  D = 12
+  x, g, beta = torch.randn(5, 7, D), torch.randn(D), torch.randn(D)
+  torch.testing.assert_close(norm_ops.layer_norm(x, g, beta, 1e-5), F.layer_norm(x, (D,), g, beta, 1e-5), rtol=1e-5, atol=1e-5)
+  torch.testing.assert_close(norm_ops.layer_norm(x, g, None, 1e-5, rms=True), F.rms_norm(x, (D,), g, 1e-5), rtol=1e-5, atol=1e-5)
+
+  # the attention layer with its weights copied into torch's module
+  E = H * Dh
+  mine = transformer.MultiHeadAttention(E, H).eval()
+  ref = torch.nn.MultiheadAttention(E, H, batch_first=True).eval()
+  with torch.no_grad():
+    mine.qkv_bias.normal_()
+    mine.out_bias.normal_()
+    ref.in_proj_weight.copy_(mine.qkv)             # rows q | k | v in both
+    ref.in_proj_bias.copy_(mine.qkv_bias)
+    ref.out_proj.weight.copy_(mine.out)
+    ref.out_proj.bias.copy_(mine.out_bias)
+  h = torch.randn(B, L, E)
+  got = mine(h, sm.merge_masks(B, L, h.device, padding_mask=pad, causal=True))
+  got2 = mine(h, None, padding_mask=pad, causal=True, structured=True)
+  causal = torch.triu(torch.ones(L, L, dtype=torch.bool), 1)
+  want, _ = ref(h, h, h, key_padding_mask=~pad, attn_mask=causal, need_weights=False)
+  rows = pad          # padded queries are undefined
+  torch.testing.assert_close(got[rows], want[rows], rtol=1e-4, atol=1e-5)
+  torch.testing.assert_close(got2[rows], want[rows], rtol=1e-4, atol=1e-5)
