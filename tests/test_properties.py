@@ -205,3 +205,44 @@ def test_cpu_reference_ops_agree_with_torch_builtins():
   rows = pad          # padded queries are undefined
   torch.testing.assert_close(got[rows], want[rows], rtol=1e-4, atol=1e-5)
   torch.testing.assert_close(got2[rows], want[rows], rtol=1e-4, atol=1e-5)
+
+
+@settings(max_examples=30, deadline=None)
+@given(bags=st.lists(st.lists(st.integers(0, 19), min_size=0, max_size=5), min_size=1, max_size=9),
+       combiner=st.sampled_from(["sum", "mean", "sqrtn"]), weighted=st.booleans(), seed=st.integers(0, 1000))
+def test_embedding_lookup_agrees_with_embedding_bag(bags, combiner, weighted, seed):
+  """The sharded-embedding module on one CPU rank and the host oracle `cpu_lookup` against
+  `torch.nn.functional.embedding_bag` (sum, mean; weighted sums through `per_sample_weights`) and the
+  definition of the sqrtn combiner (sum / sqrt(sum of squared weights))."""
+  import torch
+  import torch.nn.functional as F
+  from recml_b200 import embedding as emb
+  rng = np.random.default_rng(seed)
+  V, D = 20, 8
+  cfg = emb.ShardedEmbeddingConfig({"f": emb.EmbeddingSpec(V, D, combiner=combiner)}, emb.SGDOptimizerSpec(0.1),
+                                   backend="collective", seed=seed)
+  m = emb.ShardedEmbedding(cfg, device="cpu")
+  table = m.gather_table("f")
+  weights = {"f": [[float(x) for x in rng.integers(1, 4, len(b))] for b in bags]} if weighted else None
+  kjt = emb.KeyedJagged.from_lists({"f": bags}, weights)
+  out = m(kjt)
+  out = out["f"] if isinstance(out, dict) else out.reshape(len(bags), -1)
+  host = emb.cpu_lookup(cfg, {"f": table}, kjt)["f"]
+  flat = torch.tensor([i for b in bags for i in b], dtype=torch.long)
+  offs = torch.tensor(np.cumsum([0] + [len(b) for b in bags[:-1]]), dtype=torch.long)
+  w = torch.tensor([x for b in weights["f"] for x in b]) if weighted else None
+  if combiner == "mean" and not weighted:
+    want = F.embedding_bag(flat, table, offs, mode="mean")
+  else:
+    want = F.embedding_bag(flat, table, offs, mode="sum", per_sample_weights=w)
+    ww = [np.asarray(x, dtype=np.float64) if weighted else np.ones(len(b)) for b, x in
+          zip(bags, weights["f"] if weighted else bags)]
+    if combiner == "mean":
+      den = torch.tensor([x.sum() for x in ww], dtype=torch.float32)
+    elif combiner == "sqrtn":
+      den = torch.tensor([np.sqrt((x ** 2).sum()) for x in ww], dtype=torch.float32)
+    else:
+      den = torch.ones(len(bags))
+    want = torch.where(den[:, None] > 0, want / den[:, None].clamp_min(1e-30), torch.zeros(()))
+  torch.testing.assert_close(host, want, rtol=1e-5, atol=1e-6)
+  torch.testing.assert_close(out.float(), want, rtol=1e-5, atol=1e-6)
