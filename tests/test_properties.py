@@ -246,3 +246,37 @@ def test_embedding_lookup_agrees_with_embedding_bag(bags, combiner, weighted, se
     want = torch.where(den[:, None] > 0, want / den[:, None].clamp_min(1e-30), torch.zeros(()))
   torch.testing.assert_close(host, want, rtol=1e-5, atol=1e-6)
   torch.testing.assert_close(out.float(), want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("kind", ["sgd", "adagrad"])
+def test_embedding_training_follows_torch_embedding_bag_and_optimizer(kind):
+  """Five training steps of the sharded-embedding module on one CPU rank (update inside the backward, duplicate
+  ids in a batch, empty bags) against `nn.EmbeddingBag` trained by `torch.optim.SGD` / `Adagrad`."""
+  import torch
+  from torch import nn
+  from recml_b200 import embedding as emb
+  torch.manual_seed(0)
+  rng = np.random.default_rng(0)
+  V, D, B, lr = 30, 6, 12, 0.2
+  spec = emb.SGDOptimizerSpec(lr) if kind == "sgd" else emb.AdagradOptimizerSpec(lr, initial_accumulator_value=0.1)
+  cfg = emb.ShardedEmbeddingConfig({"f": emb.EmbeddingSpec(V, D, combiner="sum")}, spec, backend="collective", seed=1)
+  m = emb.ShardedEmbedding(cfg, device="cpu")
+  ref = nn.EmbeddingBag(V, D, mode="sum")
+  with torch.no_grad():
+    ref.weight.copy_(m.gather_table("f"))
+  opt = torch.optim.SGD(ref.parameters(), lr=lr) if kind == "sgd" else \
+      torch.optim.Adagrad(ref.parameters(), lr=lr, initial_accumulator_value=0.1, eps=0.0)
+  head = torch.randn(D)
+  for _ in range(5):
+    bags = [rng.integers(0, V, int(rng.integers(0, 5))).tolist() for _ in range(B)]
+    bags[3] = [7, 7, 7]                                  # one row three times in a bag
+    kjt = emb.KeyedJagged.from_lists({"f": bags})
+    out = m(kjt)
+    out = out["f"] if isinstance(out, dict) else out.reshape(B, -1)
+    ((out.float() * head).sum(-1) ** 2).sum().backward()
+    flat = torch.tensor([i for b in bags for i in b], dtype=torch.long)
+    offs = torch.tensor(np.cumsum([0] + [len(b) for b in bags[:-1]]), dtype=torch.long)
+    opt.zero_grad()
+    ((ref(flat, offs) * head).sum(-1) ** 2).sum().backward()
+    opt.step()
+    torch.testing.assert_close(m.gather_table("f"), ref.weight.detach(), rtol=1e-4, atol=1e-5)
