@@ -280,3 +280,32 @@ def test_embedding_training_follows_torch_embedding_bag_and_optimizer(kind):
     ((ref(flat, offs) * head).sum(-1) ** 2).sum().backward()
     opt.step()
     torch.testing.assert_close(m.gather_table("f"), ref.weight.detach(), rtol=1e-4, atol=1e-5)
+
+
+@settings(max_examples=30, deadline=None)
+@given(n=st.integers(1, 500), seed=st.integers(0, 10_000), weighted=st.booleans(), scale=st.floats(0.1, 30.0))
+def test_bce_reference_agrees_with_torch_and_its_histograms_with_the_auc_metrics(n, seed, weighted, scale):
+  """The loss op's host formulation (the oracle of the CUDA kernel): loss and gradient against
+  `binary_cross_entropy_with_logits` + autograd, and its two histograms against the threshold-based confusion
+  counts that the AUC metrics use."""
+  import torch
+  import torch.nn.functional as F
+  from recml_b200 import metrics as M
+  from recml_b200.metrics import confusion
+  from recml_b200.ops import bce
+  g = torch.Generator().manual_seed(seed)
+  x = (torch.randn(n, generator=g) * scale).requires_grad_()
+  y = (torch.rand(n, generator=g) < 0.3).float()
+  w = torch.randint(1, 4, (n,), generator=g).float() if weighted else None
+  r = bce.bce_with_logits(x.detach(), y, w, grad_scale=1.0 / n)
+  want = F.binary_cross_entropy_with_logits(x, y, weight=w, reduction="sum")
+  torch.testing.assert_close(r.loss_sum, want.detach(), rtol=1e-5, atol=1e-5)
+  (want / n).backward()
+  torch.testing.assert_close(r.dlogits, x.grad, rtol=1e-5, atol=1e-7)
+  tp, tn, fp, fn = confusion.confusion_from_histograms(r.hist_pos, r.hist_neg)
+  p = torch.sigmoid(x.detach())
+  etp, etn, efp, efn = confusion.estimate_confusion_matrix(p, y, w, thresholds=confusion.default_thresholds(200))
+  for got, exp in ((tp, etp), (tn, etn), (fp, efp), (fn, efn)):
+    np.testing.assert_allclose(np.asarray(got, dtype=np.float64), np.asarray(exp, dtype=np.float64), rtol=0, atol=1e-3)
+  np.testing.assert_allclose(float(M.HistogramAUCROC(pos_hist=r.hist_pos, neg_hist=r.hist_neg).compute()),
+                             float(M.aucroc(y, p, w).compute()), atol=1e-6)
