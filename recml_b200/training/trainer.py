@@ -216,7 +216,12 @@ class Trainer(core.Trainer[task_lib.Task]):
         timer.start()
         t0 = time.time()
       with profiling.step_annotation("train", step):
-        inputs, host_batch = self._prefetcher.next_with_host()
+        try:
+          inputs, host_batch = self._prefetcher.next_with_host()
+        except StopIteration:
+          # a bare StopIteration would end any generator above us silently; say what ran out
+          raise RuntimeError(f"the training dataset ended at step {step} of {self._train_steps}: repeat it or "
+                             "lower `train_steps`") from None
         state, metrics = train_step(inputs, state)
       if t0 is not None:
         examples += _batch_size_of(host_batch)

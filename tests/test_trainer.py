@@ -229,3 +229,8 @@ def test_epoch_checkpoint_manager_round_trip(tmp_path):
   mgr.restore_model_variables(other, 4)
   assert other.step == 5 and torch.equal(other.params["weight"], st.params["weight"])
   assert torch.equal(other.opt_state["mu"]["weight"], st.opt_state["mu"]["weight"])
+
+
+def test_training_dataset_that_runs_out_is_a_clear_error(tmp_path):
+  with pytest.raises(RuntimeError, match="training dataset ended at step 5 of 12"):
+    _trainer(tmp_path, train_steps=12, steps_per_loop=4).train(_Task(n_train=5))
