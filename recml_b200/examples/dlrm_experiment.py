@@ -99,6 +99,8 @@ class ModelConfig:
   embedding_init_scale: float | None = None
   row_wise_min_bytes: int | None = None
   backend: str = "auto"
+  # an occurrence list that overflows drops (and counts) the ids that do not fit instead of raising
+  allow_id_dropping: bool = False
 
   @classmethod
   def from_features(cls, feature_set: FeatureSet, **kwargs) -> "ModelConfig":
@@ -199,7 +201,8 @@ class PredictionTask(task_lib.Task):
         num_cross_layers=c.num_cross_layers, cross_rank=c.cross_rank, bag_sizes=c.bag_sizes,
         embedding_optimizer=emb.RowWiseAdagradOptimizerSpec(learning_rate=c.embedding_learning_rate),
         device=device, group=self.group, row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend,
-        init_scale=c.embedding_init_scale, seed=rng.initial_seed(), residue_stats=stats)
+        init_scale=c.embedding_init_scale, seed=rng.initial_seed(), residue_stats=stats,
+        allow_id_dropping=c.allow_id_dropping)
     return state_lib.State.create(model=model, tx=self.optimizer.make())
 
   def _metrics(self, r: bce.BCEResult, n: int) -> Mapping[str, M.Metric]:
@@ -236,7 +239,8 @@ class PredictionTask(task_lib.Task):
     return dict(vocab_sizes=list(c.vocab_sizes), embedding_dim=c.embedding_dim, num_dense=c.num_dense,
                 bottom_mlp_dims=list(c.bottom_mlp_dims), top_mlp_dims=list(c.top_mlp_dims),
                 num_cross_layers=c.num_cross_layers, cross_rank=c.cross_rank, bag_sizes=list(c.bag_sizes),
-                row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend, init_scale=c.embedding_init_scale)
+                row_wise_min_bytes=c.row_wise_min_bytes, backend=c.backend, init_scale=c.embedding_init_scale,
+                allow_id_dropping=c.allow_id_dropping)
 
   def export_model(self, state, model_dir: str) -> None:
     """Writes `<model_dir>/export`: the module's weights (tables shard by shard) and the recipe to rebuild

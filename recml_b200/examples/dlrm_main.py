@@ -33,13 +33,14 @@ flags.DEFINE_integer("num_dense_features", 13, "Number of dense features.")
 flags.DEFINE_integer("embedding_size", 128, "Embedding size.")
 flags.DEFINE_integer("embedding_threshold", 0, "Tables with at most this many rows are replicated on every GPU "
                      "instead of sharded (the reference keeps them on the dense cores at 21000).")
-flags.DEFINE_enum("mode", "train", ["train", "eval"], "'train', or 'eval' for evaluation only.")
+flags.DEFINE_enum("mode", "train", ["train", "eval"], "'train', or 'eval' for evaluation only.", allow_override=True)
 flags.DEFINE_integer("batch_size", 8192, "Global batch size.")
 flags.DEFINE_string("file_pattern", None, "Training TFRecords (pre-batched Criteo); synthetic data when unset.")
 flags.DEFINE_float("learning_rate", 0.0034, "Learning rate (dense Adam and embedding Adagrad).")
 flags.DEFINE_integer("num_steps", 28000, "Training steps.")
 flags.DEFINE_integer("logging_interval", 6000, "Log training metrics every N steps.")
-flags.DEFINE_bool("allow_id_dropping", True, "Accepted for command-line parity; ids are never dropped here.")
+flags.DEFINE_bool("allow_id_dropping", True, "An embedding occurrence list that overflows drops and counts the ids "
+                  "that do not fit instead of ending the run.")
 flags.DEFINE_string("eval_file_pattern", None, "Evaluation TFRecords.")
 flags.DEFINE_integer("eval_interval", 5000, "Evaluate every N steps.")
 flags.DEFINE_integer("eval_steps", 0, "Steps per evaluation, 0 for all.")
@@ -120,7 +121,7 @@ def run() -> dict:
   vocab = tuple(max(3, int(v * FLAGS.vocab_scale)) for v in synthetic.CRITEO_VOCAB_SIZES)
   base = D.ModelConfig()
   cfg = D.ModelConfig(vocab_sizes=vocab, embedding_dim=FLAGS.embedding_size, num_dense=FLAGS.num_dense_features,
-                      embedding_learning_rate=FLAGS.learning_rate,
+                      embedding_learning_rate=FLAGS.learning_rate, allow_id_dropping=FLAGS.allow_id_dropping,
                       bottom_mlp_dims=tuple(base.bottom_mlp_dims[:-1]) + (FLAGS.embedding_size,))
   task = D.PredictionTask(cfg, None, None, optim_factory.AdamFactory(learning_rate=FLAGS.learning_rate))
   device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")

@@ -26,7 +26,8 @@ from recml_b200.training import core
 FLAGS = flags.FLAGS
 _EXPERIMENT = config_lib.DEFINE_fiddle_config(
     "experiment", help_string="Experiment config: config:<module.fn>, then fiddler:/set: directives.", required=True)
-flags.DEFINE_enum("mode", "train_and_eval", [m.value for m in core.Experiment.Mode], "What to run.")
+# (allow_override: the standalone DLRM trainer has a --mode of its own; importing both modules must not fail)
+flags.DEFINE_enum("mode", "train_and_eval", [m.value for m in core.Experiment.Mode], "What to run.", allow_override=True)
 
 
 def init_distributed() -> None:

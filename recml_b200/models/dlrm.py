@@ -27,7 +27,7 @@ class DLRMDCNv2(nn.Module):
                sharding_strategy: str = "auto", row_wise_min_bytes: int | None = None,
                backend: str = "auto", seed: int = 0, init_scale: float | None = None,
                overlap_backward: bool = True, hot_row_share: Sequence | None = None,
-               residue_stats=None):
+               residue_stats=None, allow_id_dropping: bool = False):
     super().__init__()
     if bottom_mlp_dims[-1] != embedding_dim:
       raise ValueError("bottom MLP must end in embedding_dim so it can join the feature concat")
@@ -42,7 +42,7 @@ class DLRMDCNv2(nn.Module):
         emb.ShardedEmbeddingConfig(
             specs, embedding_optimizer or emb.RowWiseAdagradOptimizerSpec(learning_rate=0.01),
             sharding_strategy=sharding_strategy, row_wise_min_bytes=row_wise_min_bytes,
-            ids_per_sample=ids, backend=backend, seed=seed,
+            ids_per_sample=ids, backend=backend, seed=seed, allow_id_dropping=allow_id_dropping,
             # share of each feature's ids on its most frequent row: lets the planner offset the rank that holds the
             # hot row of a row-sharded table
             hot_row_share=dict(zip(names, hot_row_share)) if hot_row_share is not None else None,

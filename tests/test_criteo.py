@@ -125,3 +125,12 @@ def test_loader_takes_ids_modulo_vocab_like_numpy_and_rejects_wrong_bag_sizes(tm
                                   is_training=False)
   with pytest.raises(ValueError):
     next(iter(wrong))
+
+
+def test_every_module_imports_in_one_process():
+  """Both command-line entry points define a `--mode` flag; importing the whole package must still work."""
+  import importlib
+  import pkgutil
+  import recml_b200
+  for m in pkgutil.walk_packages(recml_b200.__path__, "recml_b200."):
+    importlib.import_module(m.name)
