@@ -11,7 +11,7 @@ from hypothesis import given, settings, strategies as st      # noqa: E402
 from recml_b200.embedding import id_pipeline as ip, layout_compat as lc, planner as P, specs as S   # noqa: E402
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(vocabs=st.lists(st.integers(1, 5_000_000), min_size=1, max_size=12),
        hots=st.lists(st.floats(0.5, 120.0), min_size=12, max_size=12),
        dim=st.sampled_from([8, 64, 128]), world=st.sampled_from([1, 2, 3, 4, 8]),
@@ -46,14 +46,14 @@ def test_planner_places_every_row_once_and_identically_on_every_rank(vocabs, hot
   for p in plans:
     spans = {}
     for tp in p.tables.values():
-      if tp.local_rows:
+      if tp.local_rows and tp.stack >= 0:          # replicated tables are dense parameters outside the stacks
         spans.setdefault(tp.stack, []).append((tp.row_base, tp.row_base + tp.local_rows))
     for spans_of_stack in spans.values():
       spans_of_stack.sort()
       assert all(a[1] <= b[0] for a, b in zip(spans_of_stack, spans_of_stack[1:]))
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(shapes=st.lists(st.tuples(st.integers(1, 70), st.integers(1, 9)), min_size=1, max_size=5),
        shards=st.sampled_from([1, 2, 4, 8]), rotation=st.integers(0, 3), seed=st.integers(0, 100))
 def test_reference_stack_layout_round_trips_and_addresses_rows(shapes, shards, rotation, seed):
@@ -71,7 +71,7 @@ def test_reference_stack_layout_round_trips_and_addresses_rows(shapes, shards, r
       np.testing.assert_array_equal(per_shard[shard, local, :t.shape[1]], t[row])
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(lens=st.lists(st.integers(0, 6), min_size=1, max_size=30), shards=st.integers(1, 8), rotation=st.integers(0, 7),
        vocab=st.integers(1, 50), cap=st.integers(0, 6), seed=st.integers(0, 1000), weighted=st.booleans())
 def test_id_partition_matches_a_numpy_restatement(lens, shards, rotation, vocab, cap, seed, weighted):
@@ -102,7 +102,7 @@ def test_id_partition_matches_a_numpy_restatement(lens, shards, rotation, vocab,
   assert (stats.max_ids_per_partition, stats.max_unique_ids_per_partition, stats.dropped_ids) == (max_ids, max_unique, dropped)
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(n=st.integers(200, 3000), pos_rate=st.floats(0.1, 0.9), sep=st.floats(0.0, 3.0), seed=st.integers(0, 10_000),
        weighted=st.booleans())
 def test_auc_metrics_agree_with_scikit_learn(n, pos_rate, sep, seed, weighted):
@@ -130,7 +130,7 @@ def test_auc_metrics_agree_with_scikit_learn(n, pos_rate, sep, seed, weighted):
   assert abs(got_pr - want_pr) < 0.03, (got_pr, want_pr)
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(n=st.integers(1, 40), c=st.integers(2, 60), k=st.integers(1, 20), seed=st.integers(0, 10_000))
 def test_ranking_metrics_agree_with_scikit_learn(n, c, k, seed):
   """NDCG@K and top-K accuracy with one relevant item per row against scikit-learn (distinct scores: ties are
@@ -207,7 +207,7 @@ def test_cpu_reference_ops_agree_with_torch_builtins():
   torch.testing.assert_close(got2[rows], want[rows], rtol=1e-4, atol=1e-5)
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(bags=st.lists(st.lists(st.integers(0, 19), min_size=0, max_size=5), min_size=1, max_size=9),
        combiner=st.sampled_from(["sum", "mean", "sqrtn"]), weighted=st.booleans(), seed=st.integers(0, 1000))
 def test_embedding_lookup_agrees_with_embedding_bag(bags, combiner, weighted, seed):
@@ -282,7 +282,7 @@ def test_embedding_training_follows_torch_embedding_bag_and_optimizer(kind):
     torch.testing.assert_close(m.gather_table("f"), ref.weight.detach(), rtol=1e-4, atol=1e-5)
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(n=st.integers(1, 500), seed=st.integers(0, 10_000), weighted=st.booleans(), scale=st.floats(0.1, 30.0))
 def test_bce_reference_agrees_with_torch_and_its_histograms_with_the_auc_metrics(n, seed, weighted, scale):
   """The loss op's host formulation (the oracle of the CUDA kernel): loss and gradient against
