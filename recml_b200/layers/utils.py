@@ -104,8 +104,8 @@ def _config_restore(v: Any) -> Any:
 
 class Configurable:
   """`get_config()` / `from_config()` for a layer, the pair every layer of the reference carries
-  (`recml/layers/keras/hstu.py:93-101,269-292,603-628`, `sasrec.py:152-170`, `bert4rec.py:186-208`,
-  `mamba.py:363-385,727-752`).  The config is the constructor call: the arguments the outermost `__init__`
+  (`recml/layers/keras/hstu.py:115-127,165-174,476-492,623-628`, `sasrec.py:165-170`, `bert4rec.py:194-208`,
+  `mamba.py:417-424,528,622,747-752`).  The config is the constructor call: the arguments the outermost `__init__`
   received (defaults included), with functions written as dotted import paths so that the dictionary survives
   JSON; `cls(**config)` and `cls.from_config(config)` rebuild an identically shaped, freshly initialised layer.
   """

@@ -152,7 +152,7 @@ def test_tiny_hstu_retrieval_experiment(tmp_path):
 def test_layers_round_trip_through_their_config(tmp_path):
   """`get_config()` holds the constructor call (JSON-serialisable, functions as import paths) and
   `from_config` rebuilds a layer with the same parameter shapes — the reference's Keras layers carry the same
-  pair (`recml/layers/keras/hstu.py:603-628`, `sasrec.py:152-170`, `bert4rec.py:186-208`, `mamba.py:727-752`).
+  pair (`recml/layers/keras/hstu.py:476-492,623-628`, `sasrec.py:165-170`, `bert4rec.py:194-208`, `mamba.py:747-752`).
   A layer exported without a builder reloads from that config with its weights."""
   import json
   from recml_b200 import serving

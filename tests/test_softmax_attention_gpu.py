@@ -67,8 +67,8 @@ def test_sasrec_block_uses_the_kernel_and_trains():
 
 @pytest.mark.parametrize("rate,L,causal", [(0.2, 200, True), (0.5, 330, False)])
 def test_attention_dropout_in_the_softmax_kernels(rate, L, causal):
-  """Dropout on the softmax weights (reference `recml/layers/keras/sasrec.py:84-97`: Keras MultiHeadAttention with
-  a dropout rate) runs inside the kernels: the weights are normalised over ALL visible keys, then dropped and
+  """Dropout on the softmax weights (reference `recml/layers/keras/sasrec.py:89-101`: the decoder blocks are built
+  with the model's dropout rate) runs inside the kernels: the weights are normalised over ALL visible keys, then dropped and
   rescaled before they multiply the values.  The oracle rebuilds the mask from the key that the call drew."""
   from recml_b200.ops import hstu_attention as A, hstu_cuda
   torch.manual_seed(5)
