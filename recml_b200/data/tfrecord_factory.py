@@ -54,7 +54,7 @@ class VarLenFeature:
 
 
 class FileFormat(enum.Enum):
-  """Container formats the reference can read (`tf_dataset_factory.py:58-64`).  TFRecord is the one with a
+  """Container formats the reference can read (`tf_dataset_factory.py:65-76`).  TFRecord is the one with a
   reader here; the others are Google-internal or need the array_record library."""
   TFRECORD = "tfrecord"
   RECORDIO = "recordio"
@@ -408,7 +408,7 @@ class TFDatasetFactory(types.Factory[iterator_lib.Iterator]):
 
   @functools.cached_property
   def input_filepaths(self) -> Sequence[str]:
-    """The input files (`tf_dataset_factory.py:340-367`)."""
+    """The input files (`tf_dataset_factory.py:326-353`)."""
     if not self.input_path:
       raise ValueError("`input_path` must be set.")
     return expand_input_paths(self.input_path)
