@@ -57,6 +57,13 @@ int recml_write_chunks(int count, const char* const* paths, const uint8_t* const
   return failed.load();
 }
 
+// CRC-32C of count buffers, computed by all host threads (the per-segment checksums stored beside raw chunks).
+void recml_crc32c_many(int count, const uint8_t* const* bufs, const long long* sizes, uint32_t* out) {
+  recml::ThreadPool::global().parallel_for(count, [&](long long i0, long long i1, int) {
+    for (long long i = i0; i < i1; ++i) out[i] = recml_crc32c(bufs[i], sizes[i]);
+  }, 1);
+}
+
 // Reads count files fully into caller buffers of the given sizes; short files fail.
 int recml_read_chunks(int count, const char* const* paths, uint8_t* const* bufs, const long long* sizes) {
   std::atomic<int> failed{0};

@@ -210,6 +210,51 @@ def read_region(path: str, start: Sequence[int] | None = None,
 _SEGMENT_BYTES = 16 << 20
 
 
+def _checksums_enabled() -> bool:
+  return os.environ.get("RECML_CKPT_CHECKSUMS", "1") != "0"
+
+
+def _checksum_path(chunk_path: str) -> str:
+  d, name = os.path.split(chunk_path)
+  return os.path.join(d, "." + name + ".crc32c")
+
+
+def _write_checksums(chunk_path: str, crcs: list[int]) -> None:
+  tmp = _checksum_path(chunk_path) + ".partial"
+  with open(tmp, "w") as f:
+    json.dump({"segment_bytes": _SEGMENT_BYTES, "crc32c": crcs}, f)
+  os.replace(tmp, _checksum_path(chunk_path))
+
+
+def _stored_checksums(chunk_path: str) -> list[int] | None:
+  """The segment checksums written beside a raw chunk, or None (another writer, an older checkpoint, checks
+  switched off with RECML_CKPT_CHECKSUMS=0)."""
+  if not _checksums_enabled():
+    return None
+  try:
+    with open(_checksum_path(chunk_path)) as f:
+      doc = json.load(f)
+  except (OSError, ValueError):
+    return None
+  if doc.get("segment_bytes") != _SEGMENT_BYTES:
+    return None
+  return [int(c) for c in doc.get("crc32c", [])]
+
+
+def _verify_segments(chunk_path: str, lib, base_ptr: int, nbytes: int, want: list[int]) -> None:
+  k = (nbytes + _SEGMENT_BYTES - 1) // _SEGMENT_BYTES
+  if k != len(want):
+    raise IOError(f"{chunk_path}: {len(want)} stored checksums for {k} segments")
+  bufs = (ctypes.c_void_p * k)(*[base_ptr + i * _SEGMENT_BYTES for i in range(k)])
+  sizes = (ctypes.c_longlong * k)(*[min(_SEGMENT_BYTES, nbytes - i * _SEGMENT_BYTES) for i in range(k)])
+  got = (ctypes.c_uint32 * k)()
+  lib.recml_crc32c_many(ctypes.c_int(k), bufs, sizes, got)
+  for i in range(k):
+    if int(got[i]) != want[i]:
+      raise IOError(f"{chunk_path}: checksum mismatch in bytes [{i * _SEGMENT_BYTES}, "
+                    f"{i * _SEGMENT_BYTES + int(sizes[i])}) — the chunk is damaged")
+
+
 def _write_raw_native(lib, items) -> None:
   """Uncompressed chunks straight from the arrays' memory (no intermediate copy): each chunk goes to a
   `.partial` file created at its final size, written in 16 MB segments by all host threads, then renamed."""
@@ -232,6 +277,16 @@ def _write_raw_native(lib, items) -> None:
     rc = lib.recml_write_ranges(ctypes.c_int(n), paths, offs, bufs, sizes)
     if rc != 0:
       raise IOError(f"native chunk write failed for {segs[-rc - 1][0].decode()}")
+    if _checksums_enabled() and hasattr(lib, "recml_crc32c_many"):
+      # CRC-32C of every 16 MB segment, kept in a dot-file beside the chunk (array-store readers ignore it):
+      # raw chunks carry no checksum of their own, so a flipped bit would otherwise restore as a wrong weight
+      crcs = (ctypes.c_uint32 * n)()
+      lib.recml_crc32c_many(ctypes.c_int(n), bufs, sizes, crcs)
+      at = 0
+      for arr, final in zip(arrays, finals):
+        k = (arr.nbytes + _SEGMENT_BYTES - 1) // _SEGMENT_BYTES
+        _write_checksums(final, [int(c) for c in crcs[at:at + k]])
+        at += k
   for final in finals:
     os.rename(final + ".partial", final)
 
@@ -267,6 +322,12 @@ def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> 
       items.append((fpath.encode(), f_off + seg, d_off + seg, min(_SEGMENT_BYTES, size - seg)))
   n = len(items)
   base = out.ctypes.data
+  whole = []          # (path, offset in out, bytes) of every chunk file read from its first to its last byte
+  for ci in range(a // c, (b - 1) // c + 1):
+    fpath = os.path.join(path, chunk_name([ci] + [0] * (nd - 1)))
+    lo, hi = max(a, ci * c), min(b, (ci + 1) * c, shape[0])
+    if lo == ci * c and (hi - lo) * row_bytes == os.path.getsize(fpath):
+      whole.append((fpath, (lo - a) * row_bytes, (hi - lo) * row_bytes))
   paths = (ctypes.c_char_p * n)(*[it[0] for it in items])
   offs = (ctypes.c_longlong * n)(*[it[1] for it in items])
   bufs = (ctypes.c_void_p * n)(*[base + it[2] for it in items])
@@ -274,7 +335,24 @@ def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> 
   rc = lib.recml_read_ranges(ctypes.c_int(n), paths, offs, bufs, sizes, ctypes.c_int(0))
   if rc != 0:
     raise IOError(f"native chunk read failed for {items[-rc - 1][0].decode()}")
+  if hasattr(lib, "recml_crc32c_many"):
+    for fpath, d_off, nbytes in whole:        # a range inside a chunk cannot be checked against segment sums
+      want = _stored_checksums(fpath)
+      if want is not None:
+        _verify_segments(fpath, lib, base + d_off, nbytes, want)
   return True
+
+
+def _verify_blob(chunk_path: str, blob: bytes, want: list[int]) -> None:
+  try:
+    from recml_b200.ops import _lib
+    lib = _lib.host()
+  except Exception:  # pylint: disable=broad-except
+    return
+  if lib is None or not hasattr(lib, "recml_crc32c_many"):
+    return
+  buf = np.frombuffer(blob, dtype=np.uint8)
+  _verify_segments(chunk_path, lib, buf.ctypes.data, buf.size, want)
 
 
 def _read_chunk(path, cidx, chunks, dt, comp, shape) -> np.ndarray:
@@ -288,20 +366,25 @@ def _read_chunk(path, cidx, chunks, dt, comp, shape) -> np.ndarray:
     with open(os.path.join(path, name), "rb") as f:
       blob = f.read()
   n = int(np.prod(chunks)) if len(chunks) else 1
-  if comp is not None:
+  raw = comp is None
+  if not raw:
     if comp.get("id") != "zstd" or not zstd_available():
       raise IOError(f"Unsupported chunk compressor {comp}")
     blob = zstd_decompress(blob, n * dt.itemsize)
-  if len(blob) == n * dt.itemsize:
-    return np.frombuffer(blob, dtype=dt, count=n).reshape(chunks) if len(chunks) else \
-        np.frombuffer(blob, dtype=dt, count=1)
   clipped = -1
   if len(chunks):
     rows = min(int(chunks[0]), int(shape[0]) - int(cidx[0]) * int(chunks[0]))
     clipped = rows * (n // int(chunks[0])) * dt.itemsize if chunks[0] else 0
-  if len(blob) != clipped:
+  if len(blob) not in (n * dt.itemsize, clipped):
     raise IOError(f"{os.path.join(path, name)}: chunk holds {len(blob)} bytes, expected {n * dt.itemsize}"
                   + (f" (or {clipped} for the clipped last chunk)" if 0 <= clipped < n * dt.itemsize else ""))
+  if raw and not _is_ocdbt(path):            # compressed chunks carry their own content checksum
+    want = _stored_checksums(os.path.join(path, name))
+    if want is not None:
+      _verify_blob(os.path.join(path, name), blob, want)
+  if len(blob) == n * dt.itemsize:
+    return np.frombuffer(blob, dtype=dt, count=n).reshape(chunks) if len(chunks) else \
+        np.frombuffer(blob, dtype=dt, count=1)
   arr = np.zeros(n, dtype=dt)
   part = np.frombuffer(blob, dtype=dt)
   arr[:part.size] = part

@@ -242,3 +242,29 @@ def test_truncated_chunk_raises_instead_of_restoring_zeros(tmp_path):
   (d / "2.0").write_bytes((d / "2.0").read_bytes()[:-4])
   with pytest.raises(IOError, match="clipped last chunk"):
     zarr_io.read_region(str(d))
+
+
+def test_raw_chunks_carry_segment_checksums(tmp_path, monkeypatch):
+  """Uncompressed chunks get a CRC-32C per 16 MB segment in a dot-file beside them; a flipped bit fails the restore
+  on the fast whole-file path and on the general path, a checkpoint without the dot-files still restores, and
+  RECML_CKPT_CHECKSUMS=0 switches the check off."""
+  monkeypatch.setattr(zarr_io, "_SEGMENT_BYTES", 4096)            # several segments in a small array
+  tree = {"w": torch.arange(3 * 4096, dtype=torch.float32).reshape(96, 128), "s": torch.tensor(2.5)}
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=False)
+  m.save(1, tree)
+  leaf = tmp_path / "1" / "state" / "w"
+  side = json.load(open(leaf / ".0.0.crc32c"))
+  assert side["segment_bytes"] == 4096 and len(side["crc32c"]) == 12
+  assert torch.equal(m.restore(1, target=tree)["w"], tree["w"])
+  raw = bytearray((leaf / "0.0").read_bytes())
+  raw[5000] ^= 0x01
+  (leaf / "0.0").write_bytes(bytes(raw))
+  with pytest.raises(IOError, match=r"checksum mismatch in bytes \[4096, 8192\)"):
+    m.restore(1, target=tree)                                      # whole rows, read by the native reader
+  with pytest.raises(IOError, match="checksum mismatch"):
+    zarr_io.read_region(str(leaf), [0, 3], [96, 64])               # a column range: the general path
+  monkeypatch.setenv("RECML_CKPT_CHECKSUMS", "0")
+  assert not torch.equal(m.restore(1, target=tree)["w"], tree["w"])   # unchecked: the flipped bit comes back
+  monkeypatch.delenv("RECML_CKPT_CHECKSUMS")
+  os.remove(leaf / ".0.0.crc32c")                                  # another writer's checkpoint has no dot-files
+  assert m.restore(1, target=tree)["w"].shape == (96, 128)
