@@ -87,7 +87,8 @@ def _run(cmd: list[str]) -> None:
 
 def _compile_all(srcs, hdrs, compiler_cmd, tag) -> tuple[list[str], bool]:
   os.makedirs(OBJ_DIR, exist_ok=True)
-  hdr_digest = _digest(hdrs, tag)
+  # the flags are part of the key: another RECML_SANITIZE value or a debug build never reuses these objects
+  hdr_digest = _digest(hdrs, tag + "|" + " ".join(NVCC_FLAGS if tag == "cuda" else CXX_FLAGS))
   jobs, objs = [], []
   for src in srcs:
     obj = os.path.join(OBJ_DIR, os.path.basename(src) + (_SUFFIX if tag == "host" else ("_dbg" if DEBUG else "")) + ".o")
@@ -127,7 +128,7 @@ def build(verbose: bool = False, force: bool = False, only: tuple[str, ...] = ("
                           *([f"-fsanitize={SANITIZE}"] if SANITIZE else [])])):
     if not srcs or name not in only:
       continue
-    want = _digest(srcs + hdrs, name)
+    want = _digest(srcs + hdrs, name + "|" + " ".join(NVCC_FLAGS if name == "cuda" else CXX_FLAGS))
     stamp = lib + ".sha"
     if not force and os.path.exists(lib) and os.path.exists(stamp) and _read_text(stamp) == want:
       out[name] = lib
