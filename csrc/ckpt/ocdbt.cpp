@@ -23,9 +23,12 @@
 //                interior: file[0..n) offset[0..n) length[0..n) num_indirect_value_bytes[0..n)
 //                          num_tree_bytes[0..n) num_keys[0..n)
 #include <dlfcn.h>
+#include <fcntl.h>
 #include <sys/stat.h>
+#include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -34,6 +37,8 @@
 #include <mutex>
 #include <string>
 #include <vector>
+
+#include "host/thread_pool.h"
 
 extern "C" uint32_t recml_crc32c(const uint8_t* p, long long n);
 
@@ -171,9 +176,33 @@ struct Ref { uint64_t file = 0, offset = 0, length = 0; };
 struct Entry {
   std::string key;
   bool inline_value = true;
-  std::string value;     // inline bytes
+  std::string value;     // the bytes, when the writer owns them (always so for inline values)
+  const uint8_t* ext = nullptr;   // the bytes, when the caller keeps them alive until the commit
+  uint64_t ext_len = 0;
+  uint64_t size() const { return ext != nullptr ? ext_len : value.size(); }
   Ref ref;               // out-of-line location (length = value length)
 };
+
+constexpr long long kIoSegment = 16 << 20;     // large values are read and written in pieces of this size
+
+// pread / pwrite of [off, off + len) of an open file in segments by all host threads.
+bool parallel_io(int fd, uint8_t* rbuf, const uint8_t* wbuf, uint64_t off, uint64_t len) {
+  const long long segs = static_cast<long long>((len + kIoSegment - 1) / kIoSegment);
+  std::atomic<bool> ok{true};
+  recml::ThreadPool::global().parallel_for(segs, [&](long long s0, long long s1, int) {
+    for (long long sgm = s0; sgm < s1; ++sgm) {
+      uint64_t at = static_cast<uint64_t>(sgm) * kIoSegment;
+      const uint64_t end = std::min<uint64_t>(len, at + kIoSegment);
+      while (at < end) {
+        const ssize_t r = rbuf != nullptr ? ::pread(fd, rbuf + at, end - at, static_cast<off_t>(off + at))
+                                          : ::pwrite(fd, wbuf + at, end - at, static_cast<off_t>(off + at));
+        if (r <= 0) { ok.store(false); return; }
+        at += static_cast<uint64_t>(r);
+      }
+    }
+  }, 1);
+  return ok.load();
+}
 
 std::string encode_node_payload(const Writer& payload, bool compress) {
   Writer body;
@@ -464,10 +493,11 @@ long long recml_ocdbt_read(void* h, const char* key, uint8_t* out, long long cap
     memcpy(out, loc.value.data(), loc.length);
     return static_cast<long long>(loc.length);
   }
-  std::string buf;
-  if (!read_range(loc.path, loc.offset, loc.length, &buf)) return -3;
-  memcpy(out, buf.data(), buf.size());
-  return static_cast<long long>(loc.length);
+  const int fd = ::open(loc.path.c_str(), O_RDONLY);       // straight into the caller's memory, many threads
+  if (fd < 0) return -3;
+  const bool ok = parallel_io(fd, out, nullptr, loc.offset, loc.length);
+  ::close(fd);
+  return ok ? static_cast<long long>(loc.length) : -3;
 }
 
 // ---- writing ----------------------------------------------------------------------------------------
@@ -483,6 +513,18 @@ int recml_ocdbt_writer_add(void* h, const char* key, const uint8_t* data, long l
   Entry e;
   e.key = key;
   e.value.assign(reinterpret_cast<const char*>(data), static_cast<size_t>(n));
+  w->entries.push_back(std::move(e));
+  return 0;
+}
+
+// Like recml_ocdbt_writer_add without the copy: the caller keeps [data, data + n) alive and unchanged until the
+// commit (or abort) returns.
+int recml_ocdbt_writer_add_ref(void* h, const char* key, const uint8_t* data, long long n) {
+  auto* w = static_cast<PendingStore*>(h);
+  Entry e;
+  e.key = key;
+  if (n <= w->inline_limit) e.value.assign(reinterpret_cast<const char*>(data), static_cast<size_t>(n));
+  else { e.ext = data; e.ext_len = static_cast<uint64_t>(n); }
   w->entries.push_back(std::move(e));
   return 0;
 }
@@ -503,27 +545,40 @@ int recml_ocdbt_writer_commit(void* h, int compress_nodes, int node_fanout) {
   snprintf(name, sizeof(name), "%08x%08x%08x%08x", hsh, hsh * 2654435761u, static_cast<uint32_t>(w->entries.size()), 0x0cdb0001u);
   const std::vector<DataFile> files = {{"d/", name}};
   const std::string data_path = w->dir + "/d/" + name;
-  FILE* f = fopen((data_path + ".tmp").c_str(), "wb");
-  if (f == nullptr) return -3;
+  const int fd = ::open((data_path + ".tmp").c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
+  if (fd < 0) return -3;
   uint64_t pos = 0;
   bool ok = true;
-  auto append = [&](const std::string& bytes) {
+  auto append = [&](const std::string& bytes) {        // nodes: small, written where the file ends
     const uint64_t at = pos;
-    if (!bytes.empty() && fwrite(bytes.data(), 1, bytes.size(), f) != bytes.size()) ok = false;
+    size_t put = 0;
+    while (ok && put < bytes.size()) {
+      const ssize_t r = ::pwrite(fd, bytes.data() + put, bytes.size() - put, static_cast<off_t>(at + put));
+      if (r <= 0) ok = false; else put += static_cast<size_t>(r);
+    }
     pos += bytes.size();
     return at;
   };
+  // out-of-line values first: their offsets are fixed up front, then every value is written in 16 MB pieces
+  // by all host threads, from the caller's memory when it was added by reference
   uint64_t indirect_total = 0;
   for (auto& e : w->entries) {
-    if (static_cast<long long>(e.value.size()) > w->inline_limit) {
+    if (static_cast<long long>(e.size()) > w->inline_limit) {
       e.inline_value = false;
       e.ref.file = 0;
-      e.ref.length = e.value.size();
-      e.ref.offset = append(e.value);
-      indirect_total += e.value.size();
-      e.value.clear();
-      e.value.shrink_to_fit();
+      e.ref.length = e.size();
+      e.ref.offset = pos;
+      pos += e.size();
+      indirect_total += e.size();
     }
+  }
+  if (pos > 0 && ::ftruncate(fd, static_cast<off_t>(pos)) != 0) ok = false;
+  for (auto& e : w->entries) {
+    if (e.inline_value || !ok) continue;
+    const uint8_t* src = e.ext != nullptr ? e.ext : reinterpret_cast<const uint8_t*>(e.value.data());
+    ok = parallel_io(fd, nullptr, src, e.ref.offset, e.ref.length);
+    e.value.clear();
+    e.value.shrink_to_fit();
   }
   // leaves
   std::vector<Child> level;
@@ -556,7 +611,7 @@ int recml_ocdbt_writer_commit(void* h, int compress_nodes, int node_fanout) {
     }
     level.swap(up);
   }
-  if (fclose(f) != 0) ok = false;
+  if (::close(fd) != 0) ok = false;
   if (!ok) return -3;
   if (rename((data_path + ".tmp").c_str(), data_path.c_str()) != 0) return -3;
   // manifest

@@ -253,10 +253,11 @@ class CheckpointManager:
         with open(meta, "rb") as f:
           w.add(f"{key}/.zarray", f.read())
     for leaf_dir, index, arr in pending:
-      raw = arr.tobytes(order="C")
+      key = f"{os.path.basename(leaf_dir)}/{zarr_io.chunk_name(index)}"
       if self.compressor == "zstd":
-        raw = zarr_io.zstd_compress(raw)
-      w.add(f"{os.path.basename(leaf_dir)}/{zarr_io.chunk_name(index)}", raw)
+        w.add(key, zarr_io.zstd_compress(arr.tobytes(order="C")))
+      else:
+        w.add_array(key, arr)           # written from the array's own memory at the commit
     w.commit(compress_nodes=zarr_io.zstd_available())
     if rank == 0:
       ocdbt.Writer(item).commit(compress_nodes=False)

@@ -49,6 +49,7 @@ def _host():
     lib.recml_ocdbt_writer_new.restype = ctypes.c_void_p
     lib.recml_ocdbt_writer_new.argtypes = [ctypes.c_char_p, ctypes.c_longlong]
     lib.recml_ocdbt_writer_add.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_longlong]
+    lib.recml_ocdbt_writer_add_ref.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_longlong]
     lib.recml_ocdbt_writer_commit.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     lib.recml_ocdbt_writer_abort.argtypes = [ctypes.c_void_p]
     lib._ocdbt_ready = True
@@ -82,6 +83,22 @@ class Store:
     if got != n:
       raise IOError(f"{self.directory}: reading {key!r} failed with code {got}")
     return buf.raw[:n]
+
+  def value_size(self, key: str) -> int:
+    n = self._lib.recml_ocdbt_value_size(self._h, key.encode())
+    if n < 0:
+      raise FileNotFoundError(f"{self.directory}: no key {key!r}")
+    return int(n)
+
+  def read_into(self, key: str, out) -> None:
+    """The value of `key` straight into `out`, a contiguous writable numpy array of exactly its size in bytes:
+    no intermediate copy, read in 16 MB pieces by all host threads."""
+    n = self.value_size(key)
+    if not out.flags["C_CONTIGUOUS"] or not out.flags["WRITEABLE"] or out.nbytes != n:
+      raise ValueError(f"{key!r} holds {n} bytes, the buffer {out.nbytes}")
+    got = self._lib.recml_ocdbt_read(self._h, key.encode(), out.ctypes.data, n)
+    if got != n:
+      raise IOError(f"{self.directory}: reading {key!r} failed with code {got}")
 
   def close(self) -> None:
     if self._h:
@@ -121,14 +138,24 @@ class Writer:
     os.makedirs(directory, exist_ok=True)
     self._h = self._lib.recml_ocdbt_writer_new(directory.encode(), max_inline_value_bytes)
     self.directory = directory
+    self._keep: list = []       # arrays added by reference
 
   def add(self, key: str, data: bytes | memoryview) -> None:
     data = bytes(data) if not isinstance(data, bytes) else data
     self._lib.recml_ocdbt_writer_add(self._h, key.encode(), data, len(data))
 
+  def add_array(self, key: str, arr) -> None:
+    """The bytes of a numpy array as the value, without a copy: the array is kept alive until the commit, which
+    writes it from its own memory."""
+    import numpy as np
+    arr = np.ascontiguousarray(arr)
+    self._keep.append(arr)
+    self._lib.recml_ocdbt_writer_add_ref(self._h, key.encode(), arr.ctypes.data, arr.nbytes)
+
   def commit(self, compress_nodes: bool = True, node_fanout: int = 64) -> None:
     h, self._h = self._h, None
     rc = self._lib.recml_ocdbt_writer_commit(h, int(compress_nodes), node_fanout)
+    self._keep = []
     if rc == -2:
       raise ValueError(f"OCDBT store {self.directory}: a key was added twice")
     if rc != 0:

@@ -188,6 +188,9 @@ def read_region(path: str, start: Sequence[int] | None = None,
   if nd >= 1 and comp is None and _read_rows_native(path, shape, chunks, dt, start, stop, out):
     t = torch.from_numpy(out)
     return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
+  if nd >= 1 and comp is None and _is_ocdbt(path) and _read_whole_chunk_ocdbt(path, shape, chunks, start, stop, out):
+    t = torch.from_numpy(out)
+    return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd == 0:
     out = np.array(_read_chunk(path, [], [], dt, comp, []).reshape(()))      # a writable 0-d copy
   else:
@@ -289,6 +292,28 @@ def _write_raw_native(lib, items) -> None:
         at += k
   for final in finals:
     os.rename(final + ".partial", final)
+
+
+def _read_whole_chunk_ocdbt(path, shape, chunks, start, stop, out: np.ndarray) -> bool:
+  """A raw chunk of an OCDBT store that is exactly the requested region (a leaf or a shard stored as one chunk
+  and read back whole): its value is read straight into `out` by the store's parallel reader.  False: the
+  caller takes the general path."""
+  cidx = [a // c if c else 0 for a, c in zip(start, chunks)]
+  for d, ci in enumerate(cidx):
+    c0 = ci * chunks[d]
+    if start[d] != c0 or stop[d] != min(c0 + chunks[d], shape[d]) or (stop[d] - start[d] != chunks[d] and d > 0):
+      return False
+  from recml_b200.ckpt import ocdbt
+  store_dir, leaf = ocdbt.split_path(path)
+  store = ocdbt.open_store(store_dir)
+  key = f"{leaf}/{chunk_name(cidx)}"
+  try:
+    if store.value_size(key) != out.nbytes:
+      return False                       # a clipped or padded chunk: the general path sorts it out
+  except FileNotFoundError:
+    raise FileNotFoundError(os.path.join(path, chunk_name(cidx))) from None
+  store.read_into(key, out)
+  return True
 
 
 def _read_rows_native(path, shape, chunks, dt, start, stop, out: np.ndarray) -> bool:

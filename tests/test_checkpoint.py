@@ -268,3 +268,26 @@ def test_raw_chunks_carry_segment_checksums(tmp_path, monkeypatch):
   monkeypatch.delenv("RECML_CKPT_CHECKSUMS")
   os.remove(leaf / ".0.0.crc32c")                                  # another writer's checkpoint has no dot-files
   assert m.restore(1, target=tree)["w"].shape == (96, 128)
+
+
+def test_ocdbt_large_values_go_through_the_parallel_zero_copy_path(tmp_path):
+  """A leaf larger than one 16 MB I/O segment in OCDBT form: written from the array's own memory and read
+  straight into the restored tensor (several threads, several segments); a row range of it and a store-level
+  `read_into` with a buffer of the wrong size take their own paths."""
+  from recml_b200.ckpt import ocdbt
+  big = torch.arange(5_000_000, dtype=torch.float32).reshape(50_000, 100) * 0.5        # 20 MB
+  tree = {"big": big, "half": torch.randn(1000, 8).to(torch.bfloat16), "step": torch.tensor(4)}
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=True, use_ocdbt=True)
+  m.save(1, tree)
+  m.wait_until_finished()
+  back = ckpt.CheckpointManager(str(tmp_path), async_save=False).restore(1, target=tree)
+  assert torch.equal(back["big"], big) and torch.equal(back["half"], tree["half"]) and int(back["step"]) == 4
+  item = os.path.join(str(tmp_path), "1", "state")
+  rows = zarr_io.read_region(ocdbt.leaf_path(item, "big"), [123, 0], [4567, 100])
+  assert torch.equal(rows, big[123:4567])
+  store = ocdbt.open_store(item)
+  buf = np.empty(big.numel(), dtype=np.float32)
+  store.read_into("big/0.0", buf)
+  assert np.array_equal(buf, big.numpy().reshape(-1))
+  with pytest.raises(ValueError, match="holds"):
+    store.read_into("big/0.0", np.empty(10, dtype=np.float32))
