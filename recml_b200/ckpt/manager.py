@@ -255,7 +255,7 @@ class CheckpointManager:
     for leaf_dir, index, arr in pending:
       key = f"{os.path.basename(leaf_dir)}/{zarr_io.chunk_name(index)}"
       if self.compressor == "zstd":
-        w.add(key, zarr_io.zstd_compress(arr.tobytes(order="C")))
+        w.add(key, zarr_io.zstd_compress(arr))
       else:
         w.add_array(key, arr)           # written from the array's own memory at the commit
     w.commit(compress_nodes=zarr_io.zstd_available())

@@ -67,36 +67,50 @@ def zstd_available() -> bool:
   return _ZSTD is not None
 
 
-_ZSTD_C_LEVEL, _ZSTD_C_CHECKSUM = 100, 201       # ZSTD_c_compressionLevel, ZSTD_c_checksumFlag
+_ZSTD_C_LEVEL, _ZSTD_C_CHECKSUM, _ZSTD_C_WORKERS = 100, 201, 400   # compressionLevel, checksumFlag, nbWorkers
+_ZSTD_MT_BYTES = 8 << 20          # inputs from this size on are compressed by several threads
 
 
-def zstd_compress(raw: bytes, level: int = 1) -> bytes:
-  """One standard zstd frame; with the context API the frame carries a content checksum (XXH64, four bytes at
-  its end), which every zstd reader verifies while decompressing: a flipped bit in a stored chunk is an error
-  at restore instead of a wrong weight."""
-  bound = _ZSTD.ZSTD_compressBound(len(raw))
+def zstd_compress(raw, level: int = 1) -> bytes:
+  """One standard zstd frame from `bytes` or a contiguous numpy array (no copy of the input).  With the context
+  API the frame carries a content checksum (XXH64, four bytes at its end), which every zstd reader verifies
+  while decompressing: a flipped bit in a stored chunk is an error at restore instead of a wrong weight.
+  Large inputs use the library's worker threads when it was built with them (the frame stays standard)."""
+  if isinstance(raw, np.ndarray):
+    raw = np.ascontiguousarray(raw)
+    src, n_src = ctypes.c_void_p(raw.ctypes.data), raw.nbytes
+  else:
+    src, n_src = raw, len(raw)
+  bound = _ZSTD.ZSTD_compressBound(n_src)
   dst = ctypes.create_string_buffer(bound)
   if hasattr(_ZSTD, "ZSTD_compress2"):
     cctx = _ZSTD.ZSTD_createCCtx()
     try:
       _ZSTD.ZSTD_CCtx_setParameter(cctx, _ZSTD_C_LEVEL, level)
       _ZSTD.ZSTD_CCtx_setParameter(cctx, _ZSTD_C_CHECKSUM, 1)
-      n = _ZSTD.ZSTD_compress2(cctx, dst, bound, raw, len(raw))
+      if n_src >= _ZSTD_MT_BYTES:      # an error (a single-threaded build of the library) leaves one thread
+        _ZSTD.ZSTD_CCtx_setParameter(cctx, _ZSTD_C_WORKERS, min(8, os.cpu_count() or 1))
+      n = _ZSTD.ZSTD_compress2(cctx, dst, bound, src, n_src)
     finally:
       _ZSTD.ZSTD_freeCCtx(cctx)
   else:
-    n = _ZSTD.ZSTD_compress(dst, bound, raw, len(raw), level)
+    n = _ZSTD.ZSTD_compress(dst, bound, src, n_src, level)
   if _ZSTD.ZSTD_isError(n):
     raise IOError("zstd compression failed")
-  return dst.raw[:n]
+  return ctypes.string_at(dst, n)
 
 
 def zstd_decompress(blob: bytes, raw_size: int) -> bytes:
-  dst = ctypes.create_string_buffer(raw_size)
-  n = _ZSTD.ZSTD_decompress(dst, raw_size, blob, len(blob))
-  if _ZSTD.ZSTD_isError(n) or n != raw_size:
+  out = np.empty(raw_size, dtype=np.uint8)
+  zstd_decompress_into(blob, out)
+  return out.tobytes()
+
+
+def zstd_decompress_into(blob: bytes, out: np.ndarray) -> None:
+  """Decompresses one frame straight into `out` (contiguous, exactly the decompressed size in bytes)."""
+  n = _ZSTD.ZSTD_decompress(ctypes.c_void_p(out.ctypes.data), out.nbytes, blob, len(blob))
+  if _ZSTD.ZSTD_isError(n) or n != out.nbytes:
     raise IOError("zstd decompression failed (truncated or corrupt chunk)")
-  return dst.raw
 
 
 def to_host_numpy(t) -> tuple[np.ndarray, str]:
@@ -395,7 +409,9 @@ def _read_chunk(path, cidx, chunks, dt, comp, shape) -> np.ndarray:
   if not raw:
     if comp.get("id") != "zstd" or not zstd_available():
       raise IOError(f"Unsupported chunk compressor {comp}")
-    blob = zstd_decompress(blob, n * dt.itemsize)
+    full = np.empty(n, dtype=dt)               # zstd chunks are always stored at full chunk shape
+    zstd_decompress_into(blob, full.view(np.uint8).reshape(-1) if n else full.view(np.uint8))
+    return full.reshape(chunks) if len(chunks) else full[:1]
   clipped = -1
   if len(chunks):
     rows = min(int(chunks[0]), int(shape[0]) - int(cidx[0]) * int(chunks[0]))
@@ -436,9 +452,7 @@ def write_chunks_parallel(items, compressor: str | None = None) -> None:
     return
   blobs = []
   for path, index, arr in items:
-    raw = arr.tobytes(order="C")
-    if compressor == "zstd":
-      raw = zstd_compress(raw)
+    raw = zstd_compress(np.ascontiguousarray(arr)) if compressor == "zstd" else arr.tobytes(order="C")
     blobs.append((os.path.join(path, chunk_name(index)).encode(), raw))
   n = len(blobs)
   paths = (ctypes.c_char_p * n)(*[b[0] for b in blobs])
