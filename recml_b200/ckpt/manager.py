@@ -130,15 +130,18 @@ class CheckpointManager:
       return False
     self.wait_until_finished()
     rank, world = _rank_world(self.group)
-    # Snapshot to host NOW (the step may mutate device tensors right after we return).
+    # Snapshot to host NOW (the step may mutate the tensors right after we return): device tensors are copied
+    # to the host anyway; tensors that live in host memory are copied too when the files are written in the
+    # background, or the writer would read them while the next steps change them
+    snapshot = self.async_save and world == 1
     staged: list[tuple[tuple[str, ...], Any]] = []
     for path, leaf in tree_lib.flatten(state):
       if isinstance(leaf, ShardedLeaf):
-        arr, dt = zarr_io.to_host_numpy(leaf.local) if leaf.write else (None, None)
+        arr, dt = zarr_io.to_host_numpy(leaf.local, copy=snapshot) if leaf.write else (None, None)
         staged.append((path, ("sharded", leaf, arr, dt,
                               zarr_io.to_host_numpy(leaf.local[:0])[1])))
       elif rank == 0:
-        staged.append((path, ("full",) + zarr_io.to_host_numpy(leaf)))
+        staged.append((path, ("full",) + zarr_io.to_host_numpy(leaf, copy=snapshot)))
       else:
         staged.append((path, ("skip",)))
     kinds = tree_lib.key_types(state)

@@ -113,15 +113,21 @@ def zstd_decompress_into(blob: bytes, out: np.ndarray) -> None:
     raise IOError("zstd decompression failed (truncated or corrupt chunk)")
 
 
-def to_host_numpy(t) -> tuple[np.ndarray, str]:
-  """Returns (array viewable as bytes, zarr dtype string)."""
+def to_host_numpy(t, copy: bool = False) -> tuple[np.ndarray, str]:
+  """Returns (array viewable as bytes, zarr dtype string).  A tensor that already lives in host memory is
+  returned as a VIEW of that memory unless `copy` is set: a caller that writes it later, while training goes on
+  (an asynchronous save), must ask for the copy."""
   if isinstance(t, torch.Tensor):
     t = t.detach()
+    host = t.cpu().contiguous()
+    if copy and host.data_ptr() == t.data_ptr():
+      host = host.clone()
     if t.dtype == torch.bfloat16:
-      return t.cpu().contiguous().view(torch.int16).numpy(), BFLOAT16
-    arr = t.cpu().contiguous().numpy()
+      return host.view(torch.int16).numpy(), BFLOAT16
+    arr = host.numpy()
   else:
-    arr = np.ascontiguousarray(np.asarray(t))
+    arr = np.array(t, copy=True) if copy else np.ascontiguousarray(np.asarray(t))
+    arr = np.ascontiguousarray(arr)
   if arr.dtype not in _ZARR_DTYPES:
     raise TypeError(f"Unsupported checkpoint dtype {arr.dtype}")
   return arr, _ZARR_DTYPES[arr.dtype]

@@ -291,3 +291,16 @@ def test_ocdbt_large_values_go_through_the_parallel_zero_copy_path(tmp_path):
   assert np.array_equal(buf, big.numpy().reshape(-1))
   with pytest.raises(ValueError, match="holds"):
     store.read_into("big/0.0", np.empty(10, dtype=np.float32))
+
+
+def test_async_save_snapshots_host_tensors(tmp_path):
+  """An asynchronous save of tensors that live in host memory writes what they held when `save` was called, not
+  what later steps made of them while the writer thread ran (device tensors are copied to the host anyway)."""
+  w = torch.zeros(2_000_000)
+  m = ckpt.CheckpointManager(str(tmp_path), async_save=True)
+  m.save(1, {"w": w, "n": np.zeros(4, dtype=np.float32)})
+  for k in range(1, 30):          # "training" goes on while the chunk is written
+    w.add_(1.0)
+  m.wait_until_finished()
+  back = m.restore(1)
+  assert float(back["w"].abs().max()) == 0.0
