@@ -500,6 +500,25 @@ long long recml_ocdbt_read(void* h, const char* key, uint8_t* out, long long cap
   return ok ? static_cast<long long>(loc.length) : -3;
 }
 
+// Copies bytes [value_offset, value_offset + n) of the value of `key` into out: a row range of a large chunk
+// without reading the rest of it.  Returns n, -1 unknown key, -2 range outside the value, -3 I/O.
+long long recml_ocdbt_read_range(void* h, const char* key, long long value_offset, uint8_t* out, long long n) {
+  auto* s = static_cast<Store*>(h);
+  auto it = s->keys.find(key);
+  if (it == s->keys.end()) return -1;
+  const Located& loc = it->second;
+  if (value_offset < 0 || n < 0 || static_cast<uint64_t>(value_offset) + static_cast<uint64_t>(n) > loc.length) return -2;
+  if (loc.inline_value) {
+    memcpy(out, loc.value.data() + value_offset, static_cast<size_t>(n));
+    return n;
+  }
+  const int fd = ::open(loc.path.c_str(), O_RDONLY);
+  if (fd < 0) return -3;
+  const bool ok = parallel_io(fd, out, nullptr, loc.offset + static_cast<uint64_t>(value_offset), static_cast<uint64_t>(n));
+  ::close(fd);
+  return ok ? n : -3;
+}
+
 // ---- writing ----------------------------------------------------------------------------------------
 void* recml_ocdbt_writer_new(const char* dir, long long max_inline_value_bytes) {
   auto* w = new PendingStore();

@@ -46,6 +46,9 @@ def _host():
     lib.recml_ocdbt_value_size.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
     lib.recml_ocdbt_read.restype = ctypes.c_longlong
     lib.recml_ocdbt_read.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_longlong]
+    lib.recml_ocdbt_read_range.restype = ctypes.c_longlong
+    lib.recml_ocdbt_read_range.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_longlong, ctypes.c_void_p,
+                                           ctypes.c_longlong]
     lib.recml_ocdbt_writer_new.restype = ctypes.c_void_p
     lib.recml_ocdbt_writer_new.argtypes = [ctypes.c_char_p, ctypes.c_longlong]
     lib.recml_ocdbt_writer_add.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_longlong]
@@ -99,6 +102,17 @@ class Store:
     got = self._lib.recml_ocdbt_read(self._h, key.encode(), out.ctypes.data, n)
     if got != n:
       raise IOError(f"{self.directory}: reading {key!r} failed with code {got}")
+
+  def read_range_into(self, key: str, value_offset: int, out) -> None:
+    """Bytes [value_offset, value_offset + out.nbytes) of the value of `key` into `out` (contiguous, writable):
+    a row range of a large chunk without reading the rest of it."""
+    if not out.flags["C_CONTIGUOUS"] or not out.flags["WRITEABLE"]:
+      raise ValueError("the destination must be a contiguous writable array")
+    got = self._lib.recml_ocdbt_read_range(self._h, key.encode(), int(value_offset), out.ctypes.data, out.nbytes)
+    if got == -1:
+      raise FileNotFoundError(f"{self.directory}: no key {key!r}")
+    if got != out.nbytes:
+      raise IOError(f"{self.directory}: reading {out.nbytes} bytes at {value_offset} of {key!r} failed with code {got}")
 
   def close(self) -> None:
     if self._h:

@@ -208,7 +208,9 @@ def read_region(path: str, start: Sequence[int] | None = None,
   if nd >= 1 and comp is None and _read_rows_native(path, shape, chunks, dt, start, stop, out):
     t = torch.from_numpy(out)
     return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
-  if nd >= 1 and comp is None and _is_ocdbt(path) and _read_whole_chunk_ocdbt(path, shape, chunks, start, stop, out):
+  if nd >= 1 and comp is None and _is_ocdbt(path) and (
+      _read_whole_chunk_ocdbt(path, shape, chunks, start, stop, out) or
+      _read_rows_ocdbt(path, shape, chunks, dt, start, stop, out)):
     t = torch.from_numpy(out)
     return t.view(torch.bfloat16) if meta["dtype"] == BFLOAT16 else t
   if nd == 0:
@@ -333,6 +335,35 @@ def _read_whole_chunk_ocdbt(path, shape, chunks, start, stop, out: np.ndarray) -
   except FileNotFoundError:
     raise FileNotFoundError(os.path.join(path, chunk_name(cidx))) from None
   store.read_into(key, out)
+  return True
+
+
+def _read_rows_ocdbt(path, shape, chunks, dt, start, stop, out: np.ndarray) -> bool:
+  """Raw arrays of an OCDBT store chunked along the first dimension only, whole rows requested (a rank taking
+  its rows out of a table that another world size saved): only the bytes of the requested rows are read from
+  each chunk's value, straight into `out`.  False: the caller takes the general path."""
+  nd = len(shape)
+  if any(chunks[d] != shape[d] or start[d] != 0 or stop[d] != shape[d] for d in range(1, nd)) or out.size == 0:
+    return False
+  from recml_b200.ckpt import ocdbt
+  store_dir, leaf = ocdbt.split_path(path)
+  store = ocdbt.open_store(store_dir)
+  row_bytes = int(np.prod(shape[1:], dtype=np.int64)) * dt.itemsize if nd > 1 else dt.itemsize
+  a, b, c = start[0], stop[0], chunks[0]
+  flat = out.reshape(-1).view(np.uint8)
+  plan = []
+  for ci in range(a // c, (b - 1) // c + 1):
+    key = f"{leaf}/{chunk_name([ci] + [0] * (nd - 1))}"
+    lo, hi = max(a, ci * c), min(b, (ci + 1) * c, shape[0])
+    f_off, d_off, size = (lo - ci * c) * row_bytes, (lo - a) * row_bytes, (hi - lo) * row_bytes
+    try:
+      if store.value_size(key) < f_off + size:
+        return False                     # a foreign chunk layout: the general path sorts it out
+    except FileNotFoundError:
+      raise FileNotFoundError(os.path.join(path, chunk_name([ci] + [0] * (nd - 1)))) from None
+    plan.append((key, f_off, d_off, size))
+  for key, f_off, d_off, size in plan:
+    store.read_range_into(key, f_off, flat[d_off:d_off + size])
   return True
 
 

@@ -291,6 +291,13 @@ def test_ocdbt_large_values_go_through_the_parallel_zero_copy_path(tmp_path):
   assert np.array_equal(buf, big.numpy().reshape(-1))
   with pytest.raises(ValueError, match="holds"):
     store.read_into("big/0.0", np.empty(10, dtype=np.float32))
+  part = np.empty(1000, dtype=np.float32)
+  store.read_range_into("big/0.0", 4 * 777, part)                     # floats 777 .. 1776 of the value
+  assert np.array_equal(part, big.numpy().reshape(-1)[777:1777])
+  with pytest.raises(IOError, match="code -2"):
+    store.read_range_into("big/0.0", big.numel() * 4 - 100, part)     # runs past the value
+  with pytest.raises(FileNotFoundError):
+    store.read_range_into("nothing/0", 0, part)
 
 
 def test_async_save_snapshots_host_tensors(tmp_path):
