@@ -2,6 +2,8 @@
 places every table once, stores every row exactly once across the ranks and decides the same on every rank;
 the reference stacking layout round-trips and addresses rows as its rule says; the host id partition agrees
 with a numpy restatement."""
+import os
+
 import numpy as np
 import pytest
 
@@ -309,3 +311,50 @@ def test_bce_reference_agrees_with_torch_and_its_histograms_with_the_auc_metrics
     np.testing.assert_allclose(np.asarray(got, dtype=np.float64), np.asarray(exp, dtype=np.float64), rtol=0, atol=1e-3)
   np.testing.assert_allclose(float(M.HistogramAUCROC(pos_hist=r.hist_pos, neg_hist=r.hist_neg).compute()),
                              float(M.aucroc(y, p, w).compute()), atol=1e-6)
+
+
+@settings(max_examples=80, deadline=None, derandomize=True)
+@given(shape=st.lists(st.integers(1, 13), min_size=1, max_size=3), data=st.data(),
+       form=st.sampled_from(["raw", "raw_clipped", "zstd", "ocdbt"]), seed=st.integers(0, 1000))
+def test_region_reads_of_any_chunk_grid_equal_numpy_slicing(tmp_path_factory, shape, data, form, seed):
+  """`read_region` has a general path and several direct ones (whole rows of raw chunks, a chunk that is exactly
+  the request, row ranges out of an OCDBT value); whatever the chunk grid, the stored form and the requested
+  region, the result is the slice numpy gives."""
+  import json
+  import torch
+  from recml_b200.ckpt import ocdbt, zarr_io
+  if form == "zstd" and not zarr_io.zstd_available():
+    return
+  nd = len(shape)
+  chunks = [data.draw(st.integers(1, s + 2)) for s in shape]
+  start = [data.draw(st.integers(0, s - 1)) for s in shape]
+  stop = [data.draw(st.integers(a + 1, s)) for a, s in zip(start, shape)]
+  arr = np.random.default_rng(seed).normal(size=shape).astype(np.float32)
+  d = str(tmp_path_factory.mktemp("zr"))
+  leaf = os.path.join(d, "leaf")
+  comp = "zstd" if form == "zstd" else None
+  zarr_io.write_zarray(leaf, shape, chunks, "<f4", comp)
+  grid = [(s + c - 1) // c for s, c in zip(shape, chunks)]
+  pieces = {}
+  for idx in np.ndindex(*grid):
+    sl = tuple(slice(i * c, min((i + 1) * c, s)) for i, c, s in zip(idx, chunks, shape))
+    full = np.zeros(chunks, dtype=np.float32)                    # edge chunks are stored at full chunk shape
+    part = arr[sl]
+    full[tuple(slice(0, n) for n in part.shape)] = part
+    clip_rows = form == "raw_clipped" and idx[0] == grid[0] - 1  # ... or clipped along the first dimension
+    pieces[idx] = np.ascontiguousarray(full[:part.shape[0]] if clip_rows else full)
+  if form == "ocdbt":
+    w = ocdbt.Writer(d, max_inline_value_bytes=16)
+    w.add("leaf/.zarray", open(os.path.join(leaf, ".zarray"), "rb").read())
+    for idx, piece in pieces.items():
+      w.add_array("leaf/" + zarr_io.chunk_name(idx), piece)
+    w.commit(compress_nodes=False, node_fanout=4)
+    os.remove(os.path.join(leaf, ".zarray"))
+    path = ocdbt.leaf_path(d, "leaf")
+  else:
+    for idx, piece in pieces.items():
+      zarr_io.write_chunk(leaf, idx, piece, comp)
+    path = leaf
+  want = arr[tuple(slice(a, b) for a, b in zip(start, stop))]
+  np.testing.assert_array_equal(zarr_io.read_region(path, start, stop).numpy(), want)
+  np.testing.assert_array_equal(zarr_io.read_region(path).numpy(), arr)
