@@ -12,8 +12,10 @@ once every rank finished writing, so a reader never sees a partial step director
 `commit_success.txt` is written last inside it as the completion marker.  In a multi-rank job
 the ranks agree on success before the rename: if any rank failed to write its shards the
 staging directory is removed, nothing is committed or rotated out, and every rank raises.
-`async_save` moves the file writes of a single-process job to a background thread; a
-multi-rank save returns once it is committed (the agreement is a collective).
+`async_save` moves the file writes to a background thread (tensors that live in host memory are copied first).
+In a multi-rank job the ranks then agree through marker files in the staging directory instead of a collective,
+so nothing touches the process group off the main thread; `wait_until_finished` (and the next `save`) raises on
+every rank when the checkpoint was not committed.  A synchronous multi-rank save agrees with a collective.
 """
 from __future__ import annotations
 
@@ -89,7 +91,8 @@ class CheckpointManager:
   def __init__(self, directory: str, *, max_to_keep: int | None = 5,
                should_save_fn: Callable[[int, int | None], bool] | None = None,
                save_interval_steps: int = 1, async_save: bool = True,
-               item_name: str = "state", compressor: str | None = None, group=None, use_ocdbt: bool = False):
+               item_name: str = "state", compressor: str | None = None, group=None, use_ocdbt: bool = False,
+               commit_timeout_s: float = 1800.0):
     self.directory = os.fspath(directory)
     self.max_to_keep = max_to_keep
     self.should_save_fn = should_save_fn
@@ -102,6 +105,8 @@ class CheckpointManager:
     # `ocdbt.process_<rank>` store per writing rank) instead of one directory per array.  Reading detects
     # the form by itself.
     self.use_ocdbt = use_ocdbt
+    # how long rank 0 waits for the other ranks' shards (and they for its commit) in a multi-rank asynchronous save
+    self.commit_timeout_s = commit_timeout_s
     self._thread: threading.Thread | None = None
     self._error: BaseException | None = None
     self._last_saved: int | None = None
@@ -133,7 +138,7 @@ class CheckpointManager:
     # Snapshot to host NOW (the step may mutate the tensors right after we return): device tensors are copied
     # to the host anyway; tensors that live in host memory are copied too when the files are written in the
     # background, or the writer would read them while the next steps change them
-    snapshot = self.async_save and world == 1
+    snapshot = self.async_save
     staged: list[tuple[tuple[str, ...], Any]] = []
     for path, leaf in tree_lib.flatten(state):
       if isinstance(leaf, ShardedLeaf):
@@ -164,6 +169,10 @@ class CheckpointManager:
       self._thread = threading.Thread(target=lambda: (work(), self._finalize(step, tmp, final)),
                                       name="recml-ckpt", daemon=True)
       self._thread.start()
+    elif self.async_save:
+      self._thread = threading.Thread(target=self._write_and_agree, args=(step, tmp, final, rank, world, work),
+                                      name="recml-ckpt", daemon=True)
+      self._thread.start()
     else:
       work()
       ok = self._all_ranks_ok(self._error is None)
@@ -180,6 +189,47 @@ class CheckpointManager:
         raise RuntimeError(f"checkpoint {step}: another rank failed to write its shards; nothing was committed")
     self._last_saved = step
     return True
+
+  def _write_and_agree(self, step, tmp, final, rank, world, work) -> None:
+    """The background half of a multi-rank asynchronous save.  No collective runs off the main thread: every
+    rank leaves a marker file in the temporary directory when its shards are written (or failed), rank 0 commits
+    once all markers say ok and removes the directory otherwise, and the other ranks learn the outcome from the
+    directory names.  The ranks must see one file system (one node, or a shared mount)."""
+    work()
+    kind = "ok" if self._error is None else "failed"
+    try:
+      with open(os.path.join(tmp, f".rank_{rank}.{kind}"), "w"):
+        pass
+    except OSError as e:
+      self._error = self._error or e
+    deadline = time.time() + self.commit_timeout_s
+    nothing = RuntimeError(f"checkpoint {step}: a rank failed to write its shards (or did not finish within "
+                           f"{self.commit_timeout_s:.0f} s); nothing was committed")
+    if rank == 0:
+      done, failed = [], []
+      while time.time() <= deadline:
+        names = os.listdir(tmp) if os.path.isdir(tmp) else []
+        done = [n for n in names if n.startswith(".rank_") and n.endswith(".ok")]
+        failed = [n for n in names if n.startswith(".rank_") and n.endswith(".failed")]
+        if failed or len(done) == world:
+          break
+        time.sleep(0.01)
+      if len(done) == world and not failed and self._error is None:
+        for n in done:
+          os.remove(os.path.join(tmp, n))
+        self._finalize(step, tmp, final)
+      else:
+        shutil.rmtree(tmp, ignore_errors=True)
+        self._error = self._error or nothing
+      return
+    while time.time() <= deadline:
+      if os.path.isdir(final) and not os.path.isdir(tmp):
+        return                                       # committed
+      if not os.path.isdir(tmp):
+        self._error = self._error or nothing         # rank 0 gave up
+        return
+      time.sleep(0.01)
+    self._error = self._error or nothing
 
   def _all_ranks_ok(self, ok: bool) -> bool:
     """True when every rank of the group reports success (also a barrier)."""

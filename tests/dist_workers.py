@@ -73,6 +73,44 @@ def save_row_wise_tables(rank, world, device_type, ckpt_dir, fail_rank, use_ocdb
           "listing": sorted(os.listdir(ckpt_dir))}
 
 
+def async_multi_rank_save(rank, world, device_type, ckpt_dir, fail_rank):
+  """An asynchronous save from two ranks: `save` returns while a (slowed) writer thread still runs, the tensors
+  change meanwhile, and the committed checkpoint holds what they were at the call.  With `fail_rank` >= 0 that
+  rank's writer raises: nothing is committed and every rank raises at `wait_until_finished`."""
+  import time
+  from recml_b200 import ckpt
+  from recml_b200.ckpt import zarr_io
+  local = torch.full((4, 3), float(rank + 1))
+  whole = torch.arange(6, dtype=torch.float32)
+  tree = lambda: {"shard": ckpt.ShardedLeaf(local, (4 * world, 3), (rank, 0)), "whole": whole}
+  mgr = ckpt.CheckpointManager(ckpt_dir, async_save=True, commit_timeout_s=30.0)
+  real = zarr_io.write_chunks_parallel
+  def slow(*a, **k):
+    time.sleep(0.4 if rank == 1 else 0.05)
+    if rank == fail_rank:
+      raise IOError("disk full (injected)")
+    return real(*a, **k)
+  zarr_io.write_chunks_parallel = slow
+  t = time.time()
+  mgr.save(1, tree())
+  returned_after = time.time() - t
+  local.add_(100.0)                  # training goes on while the files are written
+  whole.add_(100.0)
+  raised = None
+  try:
+    mgr.wait_until_finished()
+  except Exception as e:  # pylint: disable=broad-except
+    raised = f"{type(e).__name__}: {e}"
+  zarr_io.write_chunks_parallel = real
+  torch.distributed.barrier()
+  out = {"returned_after": returned_after, "raised": raised, "steps": mgr.all_steps(),
+         "listing": sorted(os.listdir(ckpt_dir))}
+  if raised is None:
+    back = mgr.restore(1, target=tree())
+    out["shard"], out["whole"] = back["shard"], back["whole"]
+  return out
+
+
 class _ToyNet(torch.nn.Module):
   def __init__(self, tp_group=None):
     super().__init__()

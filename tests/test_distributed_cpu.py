@@ -1,5 +1,7 @@
 """Multi-process (gloo, world_size 2 and 3) tests of the sharded-embedding plumbing, gradient
 averaging and the tiny DLRM-DCNv2 job.  The reference has no multi-process test at all."""
+import os
+
 import pytest
 import torch
 
@@ -173,3 +175,22 @@ def test_sliding_window_is_inclusive_like_the_reference_local_mask():
   assert m[5].tolist() == [False, False, False, True, True, True, False, False]      # keys 3, 4, 5: w + 1 of them
   f = A.attention_mask("full", 8, 8, sliding_window_size=1)
   assert f[4].tolist() == [False, False, False, True, True, True, False, False]
+
+
+def test_asynchronous_save_from_two_ranks(tmp_path):
+  """`save` returns before the slower rank has written its shard, the checkpoint holds the values of the moment of
+  the call although they changed meanwhile, and the staging directory's marker files are gone after the commit."""
+  res = dist_utils.run_ranks("async_multi_rank_save", 2, "gloo", "cpu", str(tmp_path / "ck"), -1)
+  for r, out in enumerate(res):
+    assert out["raised"] is None and out["steps"] == [1] and out["listing"] == ["1"], out
+    assert out["returned_after"] < 0.3, out["returned_after"]
+    torch.testing.assert_close(out["shard"], torch.full((4, 3), float(r + 1)))
+    torch.testing.assert_close(out["whole"], torch.arange(6, dtype=torch.float32))
+  assert not [n for n in os.listdir(tmp_path / "ck" / "1") if n.startswith(".rank_")]
+
+
+def test_asynchronous_save_commits_nothing_when_a_rank_fails(tmp_path):
+  res = dist_utils.run_ranks("async_multi_rank_save", 2, "gloo", "cpu", str(tmp_path / "ck"), 1)
+  assert "disk full" in res[1]["raised"] and "nothing was committed" in res[0]["raised"]
+  for out in res:
+    assert out["steps"] == [] and out["listing"] == []
