@@ -86,11 +86,12 @@ def async_multi_rank_save(rank, world, device_type, ckpt_dir, fail_rank):
   mgr = ckpt.CheckpointManager(ckpt_dir, async_save=True, commit_timeout_s=30.0)
   real = zarr_io.write_chunks_parallel
   def slow(*a, **k):
-    time.sleep(0.4 if rank == 1 else 0.05)
+    time.sleep(1.0 if rank == 1 else 0.05)
     if rank == fail_rank:
       raise IOError("disk full (injected)")
     return real(*a, **k)
   zarr_io.write_chunks_parallel = slow
+  torch.distributed.barrier()        # both ranks enter the save together: the timing below is the save's own
   t = time.time()
   mgr.save(1, tree())
   returned_after = time.time() - t

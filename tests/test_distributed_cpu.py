@@ -183,7 +183,7 @@ def test_asynchronous_save_from_two_ranks(tmp_path):
   res = dist_utils.run_ranks("async_multi_rank_save", 2, "gloo", "cpu", str(tmp_path / "ck"), -1)
   for r, out in enumerate(res):
     assert out["raised"] is None and out["steps"] == [1] and out["listing"] == ["1"], out
-    assert out["returned_after"] < 0.3, out["returned_after"]
+    assert out["returned_after"] < 0.6, out["returned_after"]        # the slower writer alone takes 1 s
     torch.testing.assert_close(out["shard"], torch.full((4, 3), float(r + 1)))
     torch.testing.assert_close(out["whole"], torch.arange(6, dtype=torch.float32))
   assert not [n for n in os.listdir(tmp_path / "ck" / "1") if n.startswith(".rank_")]
