@@ -358,3 +358,39 @@ def test_region_reads_of_any_chunk_grid_equal_numpy_slicing(tmp_path_factory, sh
   want = arr[tuple(slice(a, b) for a, b in zip(start, stop))]
   np.testing.assert_array_equal(zarr_io.read_region(path, start, stop).numpy(), want)
   np.testing.assert_array_equal(zarr_io.read_region(path).numpy(), arr)
+
+
+@pytest.mark.parametrize("normalize_first", [True, False])
+def test_transformer_block_equals_torch_encoder_layer(normalize_first):
+  """The SASRec (pre-norm, causal) and BERT4Rec (post-norm) blocks against `nn.TransformerEncoderLayer` carrying the
+  same weights: attention with padding and causal masks, tanh-GELU feed-forward, both residual arrangements."""
+  import torch
+  from torch import nn
+  from recml_b200.layers import transformer
+  torch.manual_seed(0)
+  B, L, E, H, FF = 3, 11, 16, 4, 40
+  mine = transformer.TransformerBlock(E, FF, H, normalize_first=normalize_first, causal=normalize_first,
+                                      layer_norm_epsilon=1e-5).eval()
+  with torch.no_grad():
+    for p in mine.parameters():
+      if p.ndim == 1:
+        p.add_(torch.randn_like(p) * 0.1)
+  ref = nn.TransformerEncoderLayer(E, H, FF, dropout=0.0, activation=lambda x: nn.functional.gelu(x, approximate="tanh"),
+                                   layer_norm_eps=1e-5, batch_first=True, norm_first=normalize_first).eval()
+  with torch.no_grad():
+    ref.self_attn.in_proj_weight.copy_(mine.attn.qkv)
+    ref.self_attn.in_proj_bias.copy_(mine.attn.qkv_bias)
+    ref.self_attn.out_proj.weight.copy_(mine.attn.out)
+    ref.self_attn.out_proj.bias.copy_(mine.attn.out_bias)
+    ref.norm1.weight.copy_(mine.attn_norm_w); ref.norm1.bias.copy_(mine.attn_norm_b)
+    ref.norm2.weight.copy_(mine.ffn_norm_w); ref.norm2.bias.copy_(mine.ffn_norm_b)
+    ref.linear1.weight.copy_(mine.ffn_in); ref.linear1.bias.copy_(mine.ffn_in_bias)
+    ref.linear2.weight.copy_(mine.ffn_out); ref.linear2.bias.copy_(mine.ffn_out_bias)
+  x = torch.randn(B, L, E)
+  pad = torch.ones(B, L, dtype=torch.bool)
+  pad[1, 8:] = False                                 # right padding: every real query still sees a key
+  got = mine(x, padding_mask=pad)
+  causal = torch.triu(torch.ones(L, L, dtype=torch.bool), 1) if normalize_first else None
+  with torch.no_grad():
+    want = ref(x, src_mask=causal, src_key_padding_mask=~pad)
+  torch.testing.assert_close(got[pad], want[pad], rtol=1e-4, atol=1e-5)
