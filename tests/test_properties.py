@@ -394,3 +394,28 @@ def test_transformer_block_equals_torch_encoder_layer(normalize_first):
   with torch.no_grad():
     want = ref(x, src_mask=causal, src_key_padding_mask=~pad)
   torch.testing.assert_close(got[pad], want[pad], rtol=1e-4, atol=1e-5)
+
+
+def test_sampled_softmax_reference_is_cross_entropy_over_the_kept_candidates():
+  """The loss op's host formulation (the oracle of its CUDA kernel) against `cross_entropy` over [positive |
+  candidates that are not the row's own target] built row by row."""
+  import torch
+  import torch.nn.functional as F
+  from recml_b200.ops import sampled_softmax as S
+  torch.manual_seed(0)
+  T, C, temp = 23, 17, 0.2
+  pos, neg = torch.randn(T), torch.randn(T, C)
+  cand = torch.randint(0, 40, (C,))
+  tgt = torch.randint(0, 40, (T,))
+  tgt[:5] = cand[:5]                       # accidental hits
+  w = (torch.rand(T) > 0.3).float()
+  loss, hit = S.reference(pos, neg, cand, tgt, w, temp)
+  nll, hits = [], []
+  for t in range(T):
+    keep = cand != tgt[t]
+    logits = torch.cat([pos[t:t + 1], neg[t][keep]]) / temp
+    nll.append(F.cross_entropy(logits[None], torch.zeros(1, dtype=torch.long)))
+    hits.append(float(logits.argmax() == 0))
+  want = (torch.stack(nll) * w).sum() / w.sum().clamp_min(1.0)
+  torch.testing.assert_close(loss, want, rtol=1e-5, atol=1e-6)
+  torch.testing.assert_close(hit, (torch.tensor(hits) * w).sum() / w.sum().clamp_min(1.0))
