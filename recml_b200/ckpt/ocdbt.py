@@ -78,14 +78,13 @@ class Store:
     return self._lib.recml_ocdbt_value_size(self._h, key.encode()) >= 0
 
   def get(self, key: str) -> bytes:
-    n = self._lib.recml_ocdbt_value_size(self._h, key.encode())
-    if n < 0:
-      raise FileNotFoundError(f"{self.directory}: no key {key!r}")
-    buf = ctypes.create_string_buffer(max(int(n), 1))
-    got = self._lib.recml_ocdbt_read(self._h, key.encode(), buf, n)
+    import numpy as np
+    n = self.value_size(key)
+    buf = np.empty(max(n, 1), dtype=np.uint8)          # no zero fill, one copy on the way out
+    got = self._lib.recml_ocdbt_read(self._h, key.encode(), buf.ctypes.data, n)
     if got != n:
       raise IOError(f"{self.directory}: reading {key!r} failed with code {got}")
-    return buf.raw[:n]
+    return buf[:n].tobytes()
 
   def value_size(self, key: str) -> int:
     n = self._lib.recml_ocdbt_value_size(self._h, key.encode())
