@@ -225,10 +225,21 @@ class ModelParallelPartitioner(DataParallelPartitioner):
   their shards already: they are tagged by the layer and only get their mesh placement here.
   """
 
-  def __init__(self, axes: Sequence[tuple[str, int]], dp_axes: int = 1,
-               rules: Sequence[tuple[str, Sequence[str | None]]] | None = None, *,
+  def __init__(self, axes: Sequence[tuple[str, int]] = (("batch", -1),), dp_axes: int | None = 1,
+               rules: Sequence[tuple[str, Sequence[str | None]]] | None = None, aot_compile: bool = False,
+               options: Mapping[str, Any] | None = None, devices: Sequence[Any] | None = None, *,
                device=None, inputs_are_global: bool = False):
+    """`aot_compile`, `options` and `devices` are the reference's remaining constructor arguments
+    (`recml/core/training/partitioning.py:166-174`): ahead-of-time compilation, compiler options and an explicit
+    device list.  There is no compiler here and a process owns the one device it was started on (`device`), so
+    they are accepted for experiment files written against the reference and have no effect.  `dp_axes=None`
+    makes every axis a data axis, as there."""
     super().__init__(device=device, inputs_are_global=inputs_are_global)
+    del aot_compile, options, devices
+    if not axes:
+      raise ValueError("At least one axis must be specified in `axes`.")
+    if dp_axes == 0:
+      raise ValueError("Data parallelism axes range must be positive or negative.")
     world = dist.get_world_size() if dist.is_initialized() else 1
     names = [a for a, _ in axes]
     sizes = [s for _, s in axes]

@@ -234,3 +234,14 @@ def test_epoch_checkpoint_manager_round_trip(tmp_path):
 def test_training_dataset_that_runs_out_is_a_clear_error(tmp_path):
   with pytest.raises(RuntimeError, match="training dataset ended at step 5 of 12"):
     _trainer(tmp_path, train_steps=12, steps_per_loop=4).train(_Task(n_train=5))
+
+
+def test_model_parallel_partitioner_takes_the_reference_constructor_arguments():
+  p = recml.ModelParallelPartitioner(axes=[("data", 1)], dp_axes=None, rules=None, aot_compile=True, options=None,
+                                     devices=None, device="cpu")
+  assert p.axis_names == ["data"] and p.dp_axis_names == ["data"]
+  assert recml.ModelParallelPartitioner(device="cpu").axis_names == ["batch"]
+  with pytest.raises(ValueError, match="At least one axis"):
+    recml.ModelParallelPartitioner(axes=[], device="cpu")
+  with pytest.raises(ValueError, match="positive or negative"):
+    recml.ModelParallelPartitioner(axes=[("data", 1)], dp_axes=0, device="cpu")
