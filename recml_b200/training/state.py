@@ -92,6 +92,16 @@ class State:
   def __call__(self, *args, **kwargs):
     return self.model(*args, **kwargs)
 
+  def apply(self, *args, **kwargs):
+    """Runs the model on the state's parameters (`JaxState.apply`, `recml/core/training/jax_trainer.py:105-107`):
+    the module holds them, so this is the module call."""
+    return self.model(*args, **kwargs)
+
+  def sync_model_variables(self) -> None:
+    """`KerasState.sync_model_variables` copies the state's arrays back into the Keras model
+    (`recml/core/training/jax_trainer.py:277-288`).  Here the state's parameters ARE the module's tensors, so there
+    is nothing to copy; the method exists for tasks written against the reference."""
+
   @property
   def opt_state(self) -> dict[str, Any]:
     """The optimizer's slots by name (`recml/core/training/jax_trainer.py:60-62`); empty without an optimizer."""
