@@ -419,3 +419,45 @@ def test_sampled_softmax_reference_is_cross_entropy_over_the_kept_candidates():
   want = (torch.stack(nll) * w).sum() / w.sum().clamp_min(1.0)
   torch.testing.assert_close(loss, want, rtol=1e-5, atol=1e-6)
   torch.testing.assert_close(hit, (torch.tensor(hits) * w).sum() / w.sum().clamp_min(1.0))
+
+
+@pytest.mark.parametrize("scaled,use_bias", [(False, False), (True, True)])
+def test_hstu_block_equals_a_loop_restatement(scaled, use_bias):
+  """The dense HSTU block against its definition written with explicit loops over batch, head and position
+  (`recml/layers/keras/hstu.py:356-460`): LN, one u|q|k|v projection with SiLU, SiLU attention weights divided by
+  the padded length (or scaled queries), masked, then LN over (heads, head dim) gated by u, output projection,
+  residual."""
+  import math
+  import torch
+  import torch.nn.functional as F
+  from recml_b200.layers import hstu
+  torch.manual_seed(0)
+  B, L, D, H = 2, 6, 8, 2
+  Dh = D // H
+  blk = hstu.HSTUBlock(D, H, use_bias=use_bias, scaled_pointwise_attn=scaled, layer_norm_epsilon=1e-5).eval()
+  with torch.no_grad():
+    for p in blk.parameters():
+      if p.ndim <= 2 and p is not blk.uqkv and p is not blk.out:
+        p.add_(torch.randn_like(p) * 0.1)
+  x = torch.randn(B, L, D)
+  mask = torch.tril(torch.ones(L, L, dtype=torch.bool))[None].repeat(B, 1, 1)
+  mask[1, :, 0] = False                                   # a padded key in the second sequence
+  mask[1, 0, 0] = True
+  bias = torch.randn(B, L, L) * 0.3
+  got = blk(x, mask, bias)
+  n = F.layer_norm(x, (D,), blk.input_norm_w, blk.input_norm_b, 1e-5)
+  z = F.silu(F.linear(n, blk.uqkv, blk.uqkv_bias)).reshape(B, L, 4, H, Dh)
+  u, q, k, v = z[:, :, 0], z[:, :, 1], z[:, :, 2], z[:, :, 3]
+  attn = torch.zeros(B, L, H, Dh)
+  for b in range(B):
+    for h in range(H):
+      for t in range(L):
+        for s in range(L):
+          if not mask[b, t, s]:
+            continue
+          qv = q[b, t, h] / math.sqrt(Dh) if scaled else q[b, t, h]
+          wgt = F.silu(qv @ k[b, s, h] + bias[b, t, s])
+          attn[b, t, h] += (wgt if scaled else wgt / L) * v[b, s, h]
+  y = F.layer_norm(attn, (H, Dh), blk.attn_norm_w, blk.attn_norm_b, 1e-5) * u
+  want = F.linear(y.reshape(B, L, D), blk.out, blk.out_bias) + x
+  torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
