@@ -461,3 +461,40 @@ def test_hstu_block_equals_a_loop_restatement(scaled, use_bias):
   y = F.layer_norm(attn, (H, Dh), blk.attn_norm_w, blk.attn_norm_b, 1e-5) * u
   want = F.linear(y.reshape(B, L, D), blk.out, blk.out_bias) + x
   torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+
+
+def test_mamba2_layer_equals_a_token_by_token_recurrence():
+  """The Mamba2 layer (chunked scan over the whole sequence) against the same layer run as a recurrence, one token
+  at a time with an explicit convolution window and state `h <- exp(dt A) h + dt x B^T`, `y = h C`
+  (`recml/layers/keras/mamba.py:253-360`), using the layer's own weights."""
+  import torch
+  import torch.nn.functional as F
+  from recml_b200.layers import mamba
+  torch.manual_seed(0)
+  B, L, D = 2, 12, 8
+  layer = mamba.Mamba2(D, d_state=4, d_conv=3, expand=2, nheads=4, chunk_size=4, use_dense_bias=True, use_conv_bias=True).eval()
+  with torch.no_grad():
+    for p in layer.parameters():
+      if p.ndim == 1 and p is not layer.dt_bias and p is not layer.a_log:
+        p.add_(torch.randn_like(p) * 0.1)
+  x_in = torch.randn(B, L, D)
+  got = layer(x_in)
+  H, P, N, K = layer.nheads, layer.headdim, layer.d_state, layer.d_conv
+  a = -torch.exp(layer.a_log)
+  out = torch.zeros(B, L, D)
+  for bi in range(B):
+    h = torch.zeros(H, P, N)
+    window = torch.zeros(K, layer.d_inner + 2 * N)             # the last K pre-convolution rows, oldest first
+    for t in range(L):
+      u = x_in[bi, t]
+      z = F.linear(u, layer.z_proj, layer.z_bias)
+      xbc = F.linear(u, layer.xbc_proj, layer.xbc_bias)
+      dt = F.softplus(F.linear(u, layer.dt_proj, layer.dt_proj_bias) + layer.dt_bias)       # [H]
+      window = torch.cat([window[1:], xbc[None]])
+      conv = F.silu((window * layer.conv_weight.t()).sum(0) + layer.conv_bias)
+      xs, bt, ct = conv[:layer.d_inner].reshape(H, P), conv[layer.d_inner:layer.d_inner + N], conv[layer.d_inner + N:]
+      h = torch.exp(dt * a)[:, None, None] * h + (dt[:, None] * xs)[:, :, None] * bt[None, None, :]
+      y = (h * ct[None, None, :]).sum(-1).reshape(-1) * F.silu(z)
+      y = y * torch.rsqrt(y.pow(2).mean() + 1e-5) * layer.norm_w + layer.norm_b
+      out[bi, t] = F.linear(y, layer.out_proj, layer.out_bias)
+  torch.testing.assert_close(got, out, rtol=1e-4, atol=1e-5)
